@@ -1,0 +1,142 @@
+"""In-tree native build: every ``.cu`` under ``csrc/cuda`` is compiled for sm_100a into
+``lib/libnexus_b200_cuda.so`` and every ``.cpp`` under ``csrc/host`` into the pybind11 module
+``_native``.  Plain ``nvcc`` / ``g++`` invocations, run in parallel, rebuilt only when a source or
+header is newer than the object; nothing is installed outside the package directory.
+
+``python -m nexus_b200._build`` builds everything; ``--force`` rebuilds from scratch.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+LIB_DIR = PKG / "lib"
+OBJ_DIR = PKG / "lib" / "obj"
+CUDA_LIB = LIB_DIR / "libnexus_b200_cuda.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",
+]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-pthread"]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), "/usr/local/cuda/bin/nvcc", shutil.which("nvcc")):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _newest_header(dirs) -> float:
+    t = 0.0
+    for d in dirs:
+        for pat in ("*.h", "*.cuh", "*.hpp"):
+            for f in Path(d).glob(pat):
+                t = max(t, f.stat().st_mtime)
+    return t
+
+
+def _run(cmd) -> None:
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("command failed: %s\n%s\n%s" % (" ".join(map(str, cmd)), r.stdout, r.stderr))
+
+
+def _compile_many(jobs, force: bool) -> bool:
+    """jobs: (src, obj, cmd).  Returns True when anything was rebuilt."""
+    todo = []
+    for src, obj, cmd, dep_time in jobs:
+        if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, dep_time):
+            todo.append(cmd)
+    if todo:
+        with ThreadPoolExecutor(max_workers=min(8, len(todo))) as ex:
+            list(ex.map(_run, todo))
+    return bool(todo)
+
+
+def cuda_sources():
+    return sorted((CSRC / "cuda").glob("*.cu"))
+
+
+def host_sources():
+    return sorted((CSRC / "host").glob("*.cpp"))
+
+
+def native_module_path() -> Path:
+    return PKG / ("_native" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_cuda(force: bool = False, verbose: bool = False) -> Path:
+    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    nvcc = _nvcc()
+    hdr = _newest_header([CSRC / "cuda"])
+    jobs = []
+    for src in cuda_sources():
+        obj = OBJ_DIR / (src.stem + ".o")
+        cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC / "cuda"), "-c", str(src), "-o", str(obj)]
+        jobs.append((src, obj, cmd, hdr))
+    rebuilt = _compile_many(jobs, force)
+    if rebuilt or not CUDA_LIB.exists():
+        objs = [str(j[1]) for j in jobs]
+        _run([nvcc, "-shared", "-o", str(CUDA_LIB), *objs, "-gencode", "arch=compute_100a,code=sm_100a",
+              "-cudart", "static"])
+        if verbose:
+            print("linked", CUDA_LIB)
+    return CUDA_LIB
+
+
+def build_host(force: bool = False, verbose: bool = False) -> Path:
+    import pybind11
+
+    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    out = native_module_path()
+    hdr = _newest_header([CSRC / "host"])
+    inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", str(CSRC / "host")]
+    jobs = []
+    for src in host_sources():
+        obj = OBJ_DIR / ("host_" + src.stem + ".o")
+        cmd = ["g++", *CXX_FLAGS, *inc, "-c", str(src), "-o", str(obj)]
+        jobs.append((src, obj, cmd, hdr))
+    if not jobs:
+        return out
+    rebuilt = _compile_many(jobs, force)
+    if rebuilt or not out.exists():
+        _run(["g++", "-shared", "-o", str(out), *[str(j[1]) for j in jobs], "-pthread"])
+        if verbose:
+            print("linked", out)
+    return out
+
+
+def build_tools(force: bool = False, verbose: bool = False):
+    """Stand-alone native executables (launcher)."""
+    outs = []
+    tdir = CSRC / "tools"
+    if not tdir.exists():
+        return outs
+    bindir = PKG / "bin"
+    bindir.mkdir(exist_ok=True)
+    for src in sorted(tdir.glob("*.cpp")):
+        out = bindir / src.stem.replace("_", "-")
+        if force or not out.exists() or out.stat().st_mtime < src.stat().st_mtime:
+            _run(["g++", "-O2", "-std=c++17", "-pthread", "-o", str(out), str(src)])
+            if verbose:
+                print("built", out)
+        outs.append(out)
+    return outs
+
+
+def build_all(force: bool = False, verbose: bool = False):
+    return build_cuda(force, verbose), build_host(force, verbose), build_tools(force, verbose)
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv, verbose=True)
+    print("ok")

@@ -1,0 +1,1017 @@
+// Flash-style attention for sm_100a on tcgen05 tensor cores: forward, and a two-kernel
+// deterministic backward (dK/dV kernel with the kv block resident, dQ kernel with the q block
+// resident; no atomics, every gradient tile accumulates in TMEM).
+//
+// Shared design:
+//   * Q/K/V/dO tiles arrive by TMA (4-D maps over [B, T, H, D] with arbitrary strides, so packed
+//     QKV needs no split kernel) into 128B-swizzled shared memory;
+//   * one elected thread issues tcgen05.mma; score tiles live in TMEM; each softmax thread owns one
+//     TMEM lane (= one row), so row statistics need no shuffles;
+//   * probabilities / dS are written back to swizzled shared memory as BF16 operands of the next MMA;
+//   * the same shared-memory tile is consumed K-major or MN-major just by changing the descriptor,
+//     which replaces every explicit transpose of a mma.sync implementation;
+//   * every mbarrier wait is bounded and reports through the status word.
+//
+// Features: causal, sliding window, GQA (H % Hkv == 0), Tq != Tk (bottom-right aligned causal
+// mask), head_dim 64 or 128, softmax scale.  Parity: src/cuda/flash_attention.cu:230-857 and
+// include/nexus/attention/params.hpp:18-46 of the reference (which uses mma.sync m16n8k16).
+#include "nx_api_attention.h"
+#include "sm100_ptx.cuh"
+#include "tensor_map.h"
+#include <algorithm>
+
+namespace {
+using namespace nx;
+
+constexpr int kThreads = 192;  // warps 0-3: softmax / row math, warp 4: TMA, warp 5: MMA + TMEM
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnDev {
+  void* out;        // fwd: O [B,Tq,H,D] bf16;   dq kernel: dQ;   dkdv kernel: dK
+  void* out2;       // dkdv kernel: dV
+  float* lse;       // [B,H,Tq] natural-log LSE (fwd: written; bwd: read)
+  const float* dsum;  // [B,H,Tq] rowsum(dO * O) (bwd)
+  int* status;
+  int64_t o_row, o_head, o_batch;      // element strides of `out`
+  int64_t o2_row, o2_head, o2_batch;   // element strides of `out2`
+  int B, H, Hkv, Tq, Tk;
+  int causal, window;  // window <= 0: unlimited
+  int hfirst;          // TMA coordinate order, see load_tile
+  float scale;
+};
+
+// byte offset of the 16-byte chunk (8 bf16) `chunk` (0..7) of row `r` inside a [rows][64] swizzled slab
+__device__ __forceinline__ uint32_t sw128_off(int r, int chunk) {
+  return static_cast<uint32_t>((r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4));
+}
+
+// Load a [rows][HD] tile as HD/64 slabs of [rows][64].
+// The map's dimension order follows the memory strides ({D,H,T,B} when heads are interleaved
+// inside a token row, {D,T,H,B} when each head owns a contiguous [T, D] plane); `hfirst` selects it.
+template <int HD>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int rows, int row0,
+                                          int head, int batch, int hfirst) {
+#pragma unroll
+  for (int s = 0; s < HD / 64; ++s) {
+    if (hfirst)
+      tma_load_4d(dst + s * rows * 128, tm, bar, 64 * s, head, row0, batch);
+    else
+      tma_load_4d(dst + s * rows * 128, tm, bar, 64 * s, row0, head, batch);
+  }
+}
+
+// K-major operand: address of k-step `ks` (16 elements) in a tile of HD/64 (or cols/64) slabs of `rows` rows.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t tile_addr, int rows, int ks) {
+  const uint32_t a = tile_addr + static_cast<uint32_t>((ks >> 2) * rows * 128 + (ks & 3) * 32);
+  return make_smem_desc_sw128(a, 16, 1024);
+}
+// MN-major view of a [k_rows][mn] tile stored as mn/64 slabs of [k_rows][64]: k-step `ks` = 16 rows.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_addr, int k_rows, int ks) {
+  const uint32_t a = tile_addr + static_cast<uint32_t>(ks * 2048);
+  return make_smem_desc_sw128(a, static_cast<uint32_t>(k_rows * 128), 1024);
+}
+
+__device__ __forceinline__ bool masked(const AttnDev& p, int q, int k) {
+  const int off = p.Tk - p.Tq;
+  if (k >= p.Tk) return true;
+  if (p.causal && k > q + off) return true;
+  if (p.window > 0 && k < q + off - p.window + 1) return true;
+  return false;
+}
+
+// first/last (exclusive) kv index that any row in [q0, q0+nq) can see
+__device__ __forceinline__ void kv_range(const AttnDev& p, int q0, int nq, int& lo, int& hi) {
+  const int off = p.Tk - p.Tq;
+  hi = p.Tk;
+  lo = 0;
+  if (p.causal) hi = min(p.Tk, q0 + nq - 1 + off + 1);
+  if (p.window > 0) lo = max(0, q0 + off - p.window + 1);
+  if (hi < 0) hi = 0;
+}
+
+// ================================================================================================
+// forward
+// ================================================================================================
+template <int HD>
+struct FwdCfg {
+  static constexpr int kQBytes = 128 * HD * 2;
+  static constexpr int kKVBytes = 128 * HD * 2;
+  static constexpr int kPBytes = 128 * 128 * 2;
+  static constexpr int kSmem = kQBytes + 4 * kKVBytes + kPBytes + 128;
+  static constexpr int kTmemCols = 256;  // S: 128, PV: HD
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads, (HD == 64 ? 2 : 1))
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const AttnDev p) {
+  using C = FwdCfg<HD>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {  // the swizzled tiles need a 1 KiB aligned base; uniform early exit
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, kStatusBadArgument);
+    return;
+  }
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + C::kQBytes;               // 2 stages
+  uint8_t* sV = sK + 2 * C::kKVBytes;          // 2 stages
+  uint8_t* sP = sV + 2 * C::kKVBytes;          // [128][128] bf16 as 2 slabs
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::kPBytes);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_full = bars + 6;
+  uint64_t* o_full = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = gridDim.x - 1 - blockIdx.x;  // heavy (late) q blocks first under a causal mask
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  const int q0 = qb * 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base;
+  const uint32_t tmem_o = tmem_base + 128;
+
+  int kv_lo, kv_hi;
+  kv_range(p, q0, min(128, p.Tq - q0), kv_lo, kv_hi);
+  const int jb = kv_lo / 128;
+  const int je = (kv_hi + 127) / 128;  // exclusive; may equal jb when the block sees nothing
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, C::kQBytes);
+      load_tile<HD>(sQ, &tm_q, q_full, 128, q0, h, b, p.hfirst);
+      for (int j = jb; j < je; ++j) {
+        const int it = j - jb, s = it & 1;
+        if (!mbar_wait_bounded(&kv_empty[s], ((it >> 1) & 1) ^ 1u, abort_flag)) {
+          atomicCAS(p.status, 0, kStatusTimeoutProducer);
+          break;
+        }
+        mbar_arrive_expect_tx(&kv_full[s], 2 * C::kKVBytes);
+        load_tile<HD>(sK + s * C::kKVBytes, &tm_k, &kv_full[s], 128, j * 128, hk, b, p.hfirst);
+        load_tile<HD>(sV + s * C::kKVBytes, &tm_v, &kv_full[s], 128, j * 128, hk, b, p.hfirst);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, false, false, 128, 128);
+      const uint32_t idesc_o = make_idesc(kFmtBF16, kFmtBF16, false, true, 128, HD);
+      bool ok = mbar_wait_bounded(q_full, 0, abort_flag);
+      if (!ok) atomicCAS(p.status, 0, kStatusTimeoutMma);
+      for (int j = jb; j < je && ok; ++j) {
+        const int it = j - jb, s = it & 1;
+        if (!mbar_wait_bounded(&kv_full[s], (it >> 1) & 1, abort_flag)) {
+          atomicCAS(p.status, 0, kStatusTimeoutMma);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK + s * C::kKVBytes), aV = smem_u32(sV + s * C::kKVBytes);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_f16_ss(tmem_s, desc_kmajor(aQ, 128, ks), desc_kmajor(aK, 128, ks), idesc_s, ks > 0 ? 1u : 0u);
+        umma_commit(s_full);
+        if (!mbar_wait_bounded(p_full, it & 1, abort_flag)) {
+          atomicCAS(p.status, 0, kStatusTimeoutMma);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t aP = smem_u32(sP);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_f16_ss(tmem_o, desc_kmajor(aP, 128, ks), desc_mnmajor(aV, 128, ks), idesc_o, ks > 0 ? 1u : 0u);
+        umma_commit(o_full);
+        umma_commit(&kv_empty[s]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + output rows
+    const int r = warp * 32 + lane;  // row inside the q block == TMEM lane
+    const int q = q0 + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const float sc = p.scale * kLog2e;
+    float m_run = -INFINITY, l_run = 0.0f;
+    float o_acc[HD];
+#pragma unroll
+    for (int c = 0; c < HD; ++c) o_acc[c] = 0.0f;
+    bool ok = true;
+    for (int j = jb; j < je; ++j) {
+      const int it = j - jb;
+      const int k0 = j * 128;
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(s_full, it & 1, abort_flag));
+      if (!ok) {
+        if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after_sync();
+      // does this tile need per-element masking?  (warp-uniform by construction of the bounds)
+      const int off = p.Tk - p.Tq;
+      const bool need_mask = (k0 + 128 > p.Tk) || (p.causal && (k0 + 127 > q0 + off)) ||
+                             (p.window > 0 && (k0 < q0 + 127 + off - p.window + 1));
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_s + lane_addr + cc * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          float s = __uint_as_float(v[c]);
+          if (need_mask && masked(p, q, k0 + cc * 32 + c)) s = -INFINITY;
+          mx = fmaxf(mx, s);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx * sc);
+      const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+      const float alpha = exp2f(m_run - m_use);  // m_run == -inf -> 0
+      float rs = 0.0f;
+      // pass 2: probabilities -> swizzled shared memory (A operand of P V)
+#pragma unroll 1
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_s + lane_addr + cc * 32, v);
+        tmem_ld_wait();
+        float pr[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          float s = __uint_as_float(v[c]);
+          float e = exp2f(s * sc - m_use);
+          if (need_mask && masked(p, q, k0 + cc * 32 + c)) e = 0.0f;
+          pr[c] = e;
+          rs += e;
+        }
+        uint8_t* slab = sP + (cc >> 1) * (128 * 128);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = pack_bf16x2(pr[8 * g + 0], pr[8 * g + 1]);
+          w.y = pack_bf16x2(pr[8 * g + 2], pr[8 * g + 3]);
+          w.z = pack_bf16x2(pr[8 * g + 4], pr[8 * g + 5]);
+          w.w = pack_bf16x2(pr[8 * g + 6], pr[8 * g + 7]);
+          *reinterpret_cast<uint4*>(slab + sw128_off(r, (cc & 1) * 4 + g)) = w;
+        }
+      }
+      l_run = l_run * alpha + rs;
+      m_run = m_new;
+      fence_proxy_async_smem();  // generic-proxy writes of P -> visible to the tensor core's async proxy
+      tc_fence_before_sync();
+      mbar_arrive(p_full);
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(o_full, it & 1, abort_flag));
+      if (!ok) {
+        if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after_sync();
+#pragma unroll
+      for (int cc = 0; cc < HD / 32; ++cc) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_o + lane_addr + cc * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) o_acc[cc * 32 + c] = o_acc[cc * 32 + c] * alpha + __uint_as_float(v[c]);
+      }
+      tc_fence_before_sync();
+    }
+    if (ok && q < p.Tq) {
+      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(b) * p.o_batch +
+                            static_cast<int64_t>(q) * p.o_row + static_cast<int64_t>(h) * p.o_head;
+#pragma unroll
+      for (int g = 0; g < HD / 8; ++g) {
+        uint4 w;
+        w.x = pack_bf16x2(o_acc[8 * g + 0] * inv, o_acc[8 * g + 1] * inv);
+        w.y = pack_bf16x2(o_acc[8 * g + 2] * inv, o_acc[8 * g + 3] * inv);
+        w.z = pack_bf16x2(o_acc[8 * g + 4] * inv, o_acc[8 * g + 5] * inv);
+        w.w = pack_bf16x2(o_acc[8 * g + 6] * inv, o_acc[8 * g + 7] * inv);
+        reinterpret_cast<uint4*>(orow)[g] = w;
+      }
+      if (p.lse)
+        p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Tq + q] =
+            l_run > 0.0f ? (m_run / kLog2e + logf(l_run)) : -INFINITY;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(2000);
+    __syncthreads();
+  }
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ================================================================================================
+// backward, part 0: dsum[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]
+// ================================================================================================
+__global__ void attn_bwd_dsum_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                                     float* __restrict__ dsum, int B, int T, int H, int HD, int64_t o_row,
+                                     int64_t o_head, int64_t o_batch, int64_t do_row, int64_t do_head,
+                                     int64_t do_batch) {
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  const int64_t total = static_cast<int64_t>(B) * H * T;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5); i < total;
+       i += static_cast<int64_t>(gridDim.x) * warps) {
+    const int t = static_cast<int>(i % T);
+    const int h = static_cast<int>((i / T) % H);
+    const int b = static_cast<int>(i / (static_cast<int64_t>(T) * H));
+    const __nv_bfloat16* po = o + b * o_batch + t * o_row + h * o_head;
+    const __nv_bfloat16* pd = d_o + b * do_batch + t * do_row + h * do_head;
+    float acc = 0.0f;
+    for (int d = lane * 2; d < HD; d += 64) {
+      __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(po + d);
+      __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(pd + d);
+      acc += __low2float(a) * __low2float(g) + __high2float(a) * __high2float(g);
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (lane == 0) dsum[i] = acc;
+  }
+}
+
+// ================================================================================================
+// backward, part 1: dK / dV.  One CTA per (kv block of 128, kv head, batch); loops over the q heads
+// of the group and over q chunks of 64 rows.  TMEM: S^T [128 kv][64 q], dP^T [128][64], dV [128][HD],
+// dK [128][HD].  Thread r owns kv row r.
+// ================================================================================================
+template <int HD>
+struct DkvCfg {
+  static constexpr int kKVBytes = 128 * HD * 2;   // K and V tiles (resident)
+  static constexpr int kQBytes = 64 * HD * 2;     // Q / dO chunk
+  static constexpr int kPBytes = 128 * 64 * 2;    // P^T and dS^T
+  static constexpr int kSmem = 2 * kKVBytes + 4 * kQBytes + 2 * kPBytes + 2 * 2 * 64 * 4 + 128;
+  static constexpr int kTmemCols = (HD == 64) ? 256 : 512;  // 64 + 64 + 2*HD
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads, (HD == 64 ? 2 : 1))
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                     const AttnDev p) {
+  using C = DkvCfg<HD>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {  // the swizzled tiles need a 1 KiB aligned base; uniform early exit
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, kStatusBadArgument);
+    return;
+  }
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + C::kKVBytes;
+  uint8_t* sQ = sV + C::kKVBytes;        // 2 stages
+  uint8_t* sDO = sQ + 2 * C::kQBytes;    // 2 stages
+  uint8_t* sPT = sDO + 2 * C::kQBytes;   // [128 kv][64 q] bf16
+  uint8_t* sDST = sPT + C::kPBytes;      // [128 kv][64 q] bf16
+  float* sLse = reinterpret_cast<float*>(sDST + C::kPBytes);  // [2][64] (log2 domain)
+  float* sDsum = sLse + 2 * 64;                               // [2][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDsum + 2 * 64);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = bars + 1;    // [2]
+  uint64_t* q_empty = bars + 3;   // [2]
+  uint64_t* s_full = bars + 5;    // S^T and dP^T ready
+  uint64_t* p_full = bars + 6;    // P^T and dS^T written
+  uint64_t* acc_done = bars + 7;  // dV/dK MMAs of this chunk retired (P^T/dS^T reusable)
+  uint64_t* stat_full = bars + 8;  // per-q statistics of the chunk staged in shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int k0 = kb * 128;
+  const int group = p.H / p.Hkv;
+  const int off = p.Tk - p.Tq;
+
+  // q rows that can see this kv block: q >= k0 - off (causal), q <= k0 + 127 - off + window - 1 (window)
+  int q_lo = 0, q_hi = p.Tq;
+  if (p.causal) q_lo = max(0, k0 - off);
+  if (p.window > 0) q_hi = min(p.Tq, k0 + 127 - off + p.window);
+  const int cb = q_lo / 64;
+  const int ce = q_hi > q_lo ? (q_hi + 63) / 64 : cb;
+  const int nchunk = ce - cb;
+  const int iters = nchunk * group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(acc_done, 1);
+    mbar_init(stat_full, 64);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_st = tmem_base;         // S^T   64 cols
+  const uint32_t tmem_dpt = tmem_base + 64;   // dP^T  64 cols
+  const uint32_t tmem_dv = tmem_base + 128;   // dV    HD cols
+  const uint32_t tmem_dk = tmem_base + 128 + HD;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * C::kKVBytes);
+      load_tile<HD>(sK, &tm_k, kv_full, 128, k0, hk, b, p.hfirst);
+      load_tile<HD>(sV, &tm_v, kv_full, 128, k0, hk, b, p.hfirst);
+      for (int it = 0; it < iters; ++it) {
+        const int s = it & 1;
+        const int hq = hk * group + it / nchunk;
+        const int c0 = (cb + it % nchunk) * 64;
+        if (!mbar_wait_bounded(&q_empty[s], ((it >> 1) & 1) ^ 1u, abort_flag)) {
+          atomicCAS(p.status, 0, kStatusTimeoutProducer);
+          break;
+        }
+        mbar_arrive_expect_tx(&q_full[s], 2 * C::kQBytes);
+        load_tile<HD>(sQ + s * C::kQBytes, &tm_q, &q_full[s], 64, c0, hq, b, p.hfirst);
+        load_tile<HD>(sDO + s * C::kQBytes, &tm_do, &q_full[s], 64, c0, hq, b, p.hfirst);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, false, false, 128, 64);   // K Q^T, V dO^T
+      const uint32_t idesc_g = make_idesc(kFmtBF16, kFmtBF16, false, true, 128, HD);    // P^T dO, dS^T Q
+      bool ok = mbar_wait_bounded(kv_full, 0, abort_flag);
+      if (!ok) atomicCAS(p.status, 0, kStatusTimeoutMma);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aPT = smem_u32(sPT), aDST = smem_u32(sDST);
+      for (int it = 0; it < iters && ok; ++it) {
+        const int s = it & 1;
+        if (!mbar_wait_bounded(&q_full[s], (it >> 1) & 1, abort_flag)) {
+          atomicCAS(p.status, 0, kStatusTimeoutMma);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t aQ = smem_u32(sQ + s * C::kQBytes), aDO = smem_u32(sDO + s * C::kQBytes);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_f16_ss(tmem_st, desc_kmajor(aK, 128, ks), desc_kmajor(aQ, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_f16_ss(tmem_dpt, desc_kmajor(aV, 128, ks), desc_kmajor(aDO, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
+        umma_commit(s_full);
+        if (!mbar_wait_bounded(p_full, it & 1, abort_flag)) {
+          atomicCAS(p.status, 0, kStatusTimeoutMma);
+          break;
+        }
+        tc_fence_after_sync();
+        // dV += P^T dO ; dK += dS^T Q   (reduction over the 64 q rows of the chunk: 4 k-steps)
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_f16_ss(tmem_dv, desc_kmajor(aPT, 128, ks), desc_mnmajor(aDO, 64, ks), idesc_g,
+                      (it > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_f16_ss(tmem_dk, desc_kmajor(aDST, 128, ks), desc_mnmajor(aQ, 64, ks), idesc_g,
+                      (it > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&q_empty[s]);
+        umma_commit(acc_done);
+      }
+    }
+  } else {
+    const int r = warp * 32 + lane;  // kv row inside the block == TMEM lane
+    const int k = k0 + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const float sc = p.scale * kLog2e;
+    bool ok = true;
+    for (int it = 0; it < iters; ++it) {
+      const int hq = hk * group + it / nchunk;
+      const int c0 = (cb + it % nchunk) * 64;
+      // stage the per-q statistics of this chunk (double-buffered by iteration parity)
+      float* lse_s = sLse + (it & 1) * 64;
+      float* ds_s = sDsum + (it & 1) * 64;
+      if (r < 64) {
+        const int q = c0 + r;
+        const int64_t idx = (static_cast<int64_t>(b) * p.H + hq) * p.Tq + q;
+        float l = q < p.Tq ? p.lse[idx] : INFINITY;
+        if (l == -INFINITY) l = INFINITY;  // row that saw no key: probabilities are zero
+        lse_s[r] = l * kLog2e;
+        ds_s[r] = q < p.Tq ? p.dsum[idx] : 0.0f;
+        mbar_arrive(stat_full);
+      }
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(stat_full, it & 1, abort_flag));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(s_full, it & 1, abort_flag));
+      if (ok && it > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(acc_done, (it - 1) & 1, abort_flag));
+      if (!ok) {
+        if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after_sync();
+      const bool need_mask = (k0 + 128 > p.Tk) || (c0 + 64 > p.Tq) || (p.causal && (k0 + 127 > c0 + off)) ||
+                             (p.window > 0 && (k0 < c0 + 63 + off - p.window + 1));
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32b_x32(tmem_st + lane_addr + cc * 32, sv);
+        tmem_ld_32x32b_x32(tmem_dpt + lane_addr + cc * 32, dv);
+        tmem_ld_wait();
+        float pr[32], dsv[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          const int qi = cc * 32 + c;
+          float e = exp2f(__uint_as_float(sv[c]) * sc - lse_s[qi]);
+          if (need_mask && (c0 + qi >= p.Tq || masked(p, c0 + qi, k))) e = 0.0f;
+          pr[c] = e;
+          dsv[c] = e * (__uint_as_float(dv[c]) - ds_s[qi]) * p.scale;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w, z;
+          w.x = pack_bf16x2(pr[8 * g + 0], pr[8 * g + 1]);
+          w.y = pack_bf16x2(pr[8 * g + 2], pr[8 * g + 3]);
+          w.z = pack_bf16x2(pr[8 * g + 4], pr[8 * g + 5]);
+          w.w = pack_bf16x2(pr[8 * g + 6], pr[8 * g + 7]);
+          z.x = pack_bf16x2(dsv[8 * g + 0], dsv[8 * g + 1]);
+          z.y = pack_bf16x2(dsv[8 * g + 2], dsv[8 * g + 3]);
+          z.z = pack_bf16x2(dsv[8 * g + 4], dsv[8 * g + 5]);
+          z.w = pack_bf16x2(dsv[8 * g + 6], dsv[8 * g + 7]);
+          const uint32_t o = sw128_off(r, cc * 4 + g);
+          *reinterpret_cast<uint4*>(sPT + o) = w;
+          *reinterpret_cast<uint4*>(sDST + o) = z;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(p_full);
+    }
+    // drain: wait for the last accumulation, then write dK / dV rows
+    if (ok && iters > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(acc_done, (iters - 1) & 1, abort_flag));
+      if (!ok && lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+    }
+    if (ok) {  // warp-uniform: the TMEM loads below are warp-collective, only the stores are per row
+      tc_fence_after_sync();
+      const bool row_ok = k < p.Tk;
+      __nv_bfloat16* dk = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(b) * p.o_batch +
+                          static_cast<int64_t>(k) * p.o_row + static_cast<int64_t>(hk) * p.o_head;
+      __nv_bfloat16* dvp = reinterpret_cast<__nv_bfloat16*>(p.out2) + static_cast<int64_t>(b) * p.o2_batch +
+                           static_cast<int64_t>(k) * p.o2_row + static_cast<int64_t>(hk) * p.o2_head;
+#pragma unroll 1
+      for (int cc = 0; cc < HD / 32; ++cc) {
+        uint32_t a[32], c[32];
+        if (iters > 0) {
+          tmem_ld_32x32b_x32(tmem_dk + lane_addr + cc * 32, a);
+          tmem_ld_32x32b_x32(tmem_dv + lane_addr + cc * 32, c);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) a[i] = c[i] = 0u;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w, z;
+          w.x = pack_bf16x2(__uint_as_float(a[8 * g + 0]), __uint_as_float(a[8 * g + 1]));
+          w.y = pack_bf16x2(__uint_as_float(a[8 * g + 2]), __uint_as_float(a[8 * g + 3]));
+          w.z = pack_bf16x2(__uint_as_float(a[8 * g + 4]), __uint_as_float(a[8 * g + 5]));
+          w.w = pack_bf16x2(__uint_as_float(a[8 * g + 6]), __uint_as_float(a[8 * g + 7]));
+          z.x = pack_bf16x2(__uint_as_float(c[8 * g + 0]), __uint_as_float(c[8 * g + 1]));
+          z.y = pack_bf16x2(__uint_as_float(c[8 * g + 2]), __uint_as_float(c[8 * g + 3]));
+          z.z = pack_bf16x2(__uint_as_float(c[8 * g + 4]), __uint_as_float(c[8 * g + 5]));
+          z.w = pack_bf16x2(__uint_as_float(c[8 * g + 6]), __uint_as_float(c[8 * g + 7]));
+          if (row_ok) {
+            reinterpret_cast<uint4*>(dk + cc * 32)[g] = w;
+            reinterpret_cast<uint4*>(dvp + cc * 32)[g] = z;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(2000);
+    __syncthreads();
+  }
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ================================================================================================
+// backward, part 2: dQ.  One CTA per (q block of 128, head, batch); loops over kv chunks of 64.
+// TMEM: S [128 q][64 kv], dP [128][64], dQ [128][HD].  Thread r owns q row r.
+// ================================================================================================
+template <int HD>
+struct DqCfg {
+  static constexpr int kQBytes = 128 * HD * 2;   // Q and dO tiles (resident)
+  static constexpr int kKVBytes = 64 * HD * 2;   // K / V chunk
+  static constexpr int kPBytes = 128 * 64 * 2;   // dS
+  static constexpr int kSmem = 2 * kQBytes + 4 * kKVBytes + kPBytes + 128;
+  static constexpr int kTmemCols = 256;  // 64 + 64 + HD
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads, (HD == 64 ? 2 : 1))
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                   const AttnDev p) {
+  using C = DqCfg<HD>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {  // the swizzled tiles need a 1 KiB aligned base; uniform early exit
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, kStatusBadArgument);
+    return;
+  }
+  uint8_t* sQ = smem;
+  uint8_t* sDO = sQ + C::kQBytes;
+  uint8_t* sK = sDO + C::kQBytes;       // 2 stages
+  uint8_t* sV = sK + 2 * C::kKVBytes;   // 2 stages
+  uint8_t* sDS = sV + 2 * C::kKVBytes;  // [128 q][64 kv] bf16
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + C::kPBytes);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_full = bars + 6;
+  uint64_t* acc_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  const int q0 = qb * 128;
+
+  int kv_lo, kv_hi;
+  kv_range(p, q0, min(128, p.Tq - q0), kv_lo, kv_hi);
+  const int jb = kv_lo / 64;
+  const int je = kv_hi > kv_lo ? (kv_hi + 63) / 64 : jb;
+  const int iters = je - jb;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base;
+  const uint32_t tmem_dp = tmem_base + 64;
+  const uint32_t tmem_dq = tmem_base + 128;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, 2 * C::kQBytes);
+      load_tile<HD>(sQ, &tm_q, q_full, 128, q0, h, b, p.hfirst);
+      load_tile<HD>(sDO, &tm_do, q_full, 128, q0, h, b, p.hfirst);
+      for (int it = 0; it < iters; ++it) {
+        const int s = it & 1;
+        if (!mbar_wait_bounded(&kv_empty[s], ((it >> 1) & 1) ^ 1u, abort_flag)) {
+          atomicCAS(p.status, 0, kStatusTimeoutProducer);
+          break;
+        }
+        mbar_arrive_expect_tx(&kv_full[s], 2 * C::kKVBytes);
+        load_tile<HD>(sK + s * C::kKVBytes, &tm_k, &kv_full[s], 64, (jb + it) * 64, hk, b, p.hfirst);
+        load_tile<HD>(sV + s * C::kKVBytes, &tm_v, &kv_full[s], 64, (jb + it) * 64, hk, b, p.hfirst);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, false, false, 128, 64);  // Q K^T, dO V^T
+      const uint32_t idesc_g = make_idesc(kFmtBF16, kFmtBF16, false, true, 128, HD);   // dS K
+      bool ok = mbar_wait_bounded(q_full, 0, abort_flag);
+      if (!ok) atomicCAS(p.status, 0, kStatusTimeoutMma);
+      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
+      for (int it = 0; it < iters && ok; ++it) {
+        const int s = it & 1;
+        if (!mbar_wait_bounded(&kv_full[s], (it >> 1) & 1, abort_flag)) {
+          atomicCAS(p.status, 0, kStatusTimeoutMma);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t aK = smem_u32(sK + s * C::kKVBytes), aV = smem_u32(sV + s * C::kKVBytes);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_f16_ss(tmem_s, desc_kmajor(aQ, 128, ks), desc_kmajor(aK, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_f16_ss(tmem_dp, desc_kmajor(aDO, 128, ks), desc_kmajor(aV, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
+        umma_commit(s_full);
+        if (!mbar_wait_bounded(p_full, it & 1, abort_flag)) {
+          atomicCAS(p.status, 0, kStatusTimeoutMma);
+          break;
+        }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_f16_ss(tmem_dq, desc_kmajor(aDS, 128, ks), desc_mnmajor(aK, 64, ks), idesc_g,
+                      (it > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&kv_empty[s]);
+        umma_commit(acc_done);
+      }
+    }
+  } else {
+    const int r = warp * 32 + lane;
+    const int q = q0 + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const float sc = p.scale * kLog2e;
+    const int off = p.Tk - p.Tq;
+    const int64_t sidx = (static_cast<int64_t>(b) * p.H + h) * p.Tq + q;
+    float lse_n = q < p.Tq ? p.lse[sidx] : INFINITY;
+    if (lse_n == -INFINITY) lse_n = INFINITY;  // row that saw no key: probabilities are zero
+    const float lse2 = lse_n * kLog2e;
+    const float dsum = q < p.Tq ? p.dsum[sidx] : 0.0f;
+    bool ok = true;
+    for (int it = 0; it < iters; ++it) {
+      const int k0 = (jb + it) * 64;
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(s_full, it & 1, abort_flag));
+      if (ok && it > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(acc_done, (it - 1) & 1, abort_flag));
+      if (!ok) {
+        if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after_sync();
+      const bool need_mask = (k0 + 64 > p.Tk) || (q0 + 128 > p.Tq) || (p.causal && (k0 + 63 > q0 + off)) ||
+                             (p.window > 0 && (k0 < q0 + 127 + off - p.window + 1));
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32b_x32(tmem_s + lane_addr + cc * 32, sv);
+        tmem_ld_32x32b_x32(tmem_dp + lane_addr + cc * 32, dv);
+        tmem_ld_wait();
+        float dsv[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          float e = exp2f(__uint_as_float(sv[c]) * sc - lse2);
+          if (need_mask && (q >= p.Tq || masked(p, q, k0 + cc * 32 + c))) e = 0.0f;
+          dsv[c] = e * (__uint_as_float(dv[c]) - dsum) * p.scale;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 z;
+          z.x = pack_bf16x2(dsv[8 * g + 0], dsv[8 * g + 1]);
+          z.y = pack_bf16x2(dsv[8 * g + 2], dsv[8 * g + 3]);
+          z.z = pack_bf16x2(dsv[8 * g + 4], dsv[8 * g + 5]);
+          z.w = pack_bf16x2(dsv[8 * g + 6], dsv[8 * g + 7]);
+          *reinterpret_cast<uint4*>(sDS + sw128_off(r, cc * 4 + g)) = z;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(p_full);
+    }
+    if (ok && iters > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(acc_done, (iters - 1) & 1, abort_flag));
+      if (!ok && lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+    }
+    if (ok) {  // warp-uniform: the TMEM loads below are warp-collective, only the stores are per row
+      tc_fence_after_sync();
+      const bool row_ok = q < p.Tq;
+      __nv_bfloat16* dq = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(b) * p.o_batch +
+                          static_cast<int64_t>(q) * p.o_row + static_cast<int64_t>(h) * p.o_head;
+#pragma unroll 1
+      for (int cc = 0; cc < HD / 32; ++cc) {
+        uint32_t a[32];
+        if (iters > 0) {
+          tmem_ld_32x32b_x32(tmem_dq + lane_addr + cc * 32, a);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) a[i] = 0u;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(a[8 * g + 0]), __uint_as_float(a[8 * g + 1]));
+          w.y = pack_bf16x2(__uint_as_float(a[8 * g + 2]), __uint_as_float(a[8 * g + 3]));
+          w.z = pack_bf16x2(__uint_as_float(a[8 * g + 4]), __uint_as_float(a[8 * g + 5]));
+          w.w = pack_bf16x2(__uint_as_float(a[8 * g + 6]), __uint_as_float(a[8 * g + 7]));
+          if (row_ok) reinterpret_cast<uint4*>(dq + cc * 32)[g] = w;
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(2000);
+    __syncthreads();
+  }
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+int check_view(const NxAttnView& v) {
+  if (v.ptr == nullptr) return -1;
+  if (reinterpret_cast<uintptr_t>(v.ptr) & 15) return -1;
+  if ((v.row_stride & 7) || (v.head_stride & 7) || (v.batch_stride & 7)) return -1;
+  return 0;
+}
+
+bool head_first(const NxAttnView& v) { return v.head_stride <= v.row_stride; }
+
+int make_map(CUtensorMap* m, const NxAttnView& v, int T, int H, int B, int HD, int box_rows) {
+  if (head_first(v))
+    return nx::make_tensor_map_4d(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v.ptr, HD, H, T, B, v.head_stride,
+                                  v.row_stride, v.batch_stride, 64, 1, box_rows);
+  return nx::make_tensor_map_4d(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, v.ptr, HD, T, H, B, v.row_stride,
+                                v.head_stride, v.batch_stride, 64, box_rows, 1);
+}
+
+template <typename K>
+int set_smem(K kern, int bytes) {
+  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess ? 0 : -2;
+}
+
+AttnDev base_params(const NxAttnArgs* a) {
+  AttnDev p{};
+  p.lse = a->lse;
+  p.dsum = a->dsum;
+  p.status = a->status;
+  p.B = a->batch;
+  p.H = a->heads;
+  p.Hkv = a->kv_heads;
+  p.Tq = a->tq;
+  p.Tk = a->tk;
+  p.causal = a->causal;
+  p.window = a->window;
+  p.scale = a->scale;
+  p.hfirst = head_first(a->q) ? 1 : 0;
+  return p;
+}
+
+int check_args(const NxAttnArgs* a) {
+  if (a == nullptr || a->status == nullptr) return -1;
+  if (a->head_dim != 64 && a->head_dim != 128) return -1;
+  if (a->batch <= 0 || a->heads <= 0 || a->kv_heads <= 0 || a->heads % a->kv_heads) return -1;
+  if (a->tq <= 0 || a->tk <= 0) return -1;
+  // every TMA-read view must share one coordinate order
+  const bool hf = head_first(a->q);
+  if (head_first(a->k) != hf || head_first(a->v) != hf) return -1;
+  if (a->d_o.ptr != nullptr && head_first(a->d_o) != hf) return -1;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int nx_attention_fwd(const NxAttnArgs* a, nx_stream_t stream_) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream_);
+  if (check_args(a) || check_view(a->q) || check_view(a->k) || check_view(a->v) || check_view(a->o)) return -1;
+  const int HD = a->head_dim;
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_map(&tq, a->q, a->tq, a->heads, a->batch, HD, 128))) return rc;
+  if ((rc = make_map(&tk, a->k, a->tk, a->kv_heads, a->batch, HD, 128))) return rc;
+  if ((rc = make_map(&tv, a->v, a->tk, a->kv_heads, a->batch, HD, 128))) return rc;
+  AttnDev p = base_params(a);
+  p.out = a->o.ptr;
+  p.o_row = a->o.row_stride;
+  p.o_head = a->o.head_stride;
+  p.o_batch = a->o.batch_stride;
+  dim3 grid((a->tq + 127) / 128, a->heads, a->batch);
+  if (HD == 64) {
+    static bool once = false;
+    if (!once) {
+      if (set_smem(attn_fwd_kernel<64>, FwdCfg<64>::kSmem)) return -2;
+      once = true;
+    }
+    attn_fwd_kernel<64><<<grid, kThreads, FwdCfg<64>::kSmem, st>>>(tq, tk, tv, p);
+  } else {
+    static bool once = false;
+    if (!once) {
+      if (set_smem(attn_fwd_kernel<128>, FwdCfg<128>::kSmem)) return -2;
+      once = true;
+    }
+    attn_fwd_kernel<128><<<grid, kThreads, FwdCfg<128>::kSmem, st>>>(tq, tk, tv, p);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int nx_attention_bwd(const NxAttnArgs* a, nx_stream_t stream_) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream_);
+  if (check_args(a) || check_view(a->q) || check_view(a->k) || check_view(a->v) || check_view(a->o) ||
+      check_view(a->d_o) || check_view(a->dq) || check_view(a->dk) || check_view(a->dv))
+    return -1;
+  if (a->lse == nullptr || a->dsum == nullptr) return -1;
+  const int HD = a->head_dim;
+  // part 0
+  {
+    const int64_t total = static_cast<int64_t>(a->batch) * a->heads * a->tq;
+    const int blocks = static_cast<int>(std::min<int64_t>((total + 7) / 8, 148 * 16));
+    attn_bwd_dsum_kernel<<<blocks, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(a->o.ptr), static_cast<const __nv_bfloat16*>(a->d_o.ptr), a->dsum, a->batch,
+        a->tq, a->heads, HD, a->o.row_stride, a->o.head_stride, a->o.batch_stride, a->d_o.row_stride,
+        a->d_o.head_stride, a->d_o.batch_stride);
+    if (cudaGetLastError() != cudaSuccess) return -2;
+  }
+  int rc;
+  // part 1: dK, dV
+  {
+    CUtensorMap tq, tk, tv, tdo;
+    if ((rc = make_map(&tq, a->q, a->tq, a->heads, a->batch, HD, 64))) return rc;
+    if ((rc = make_map(&tdo, a->d_o, a->tq, a->heads, a->batch, HD, 64))) return rc;
+    if ((rc = make_map(&tk, a->k, a->tk, a->kv_heads, a->batch, HD, 128))) return rc;
+    if ((rc = make_map(&tv, a->v, a->tk, a->kv_heads, a->batch, HD, 128))) return rc;
+    AttnDev p = base_params(a);
+    p.out = a->dk.ptr;
+    p.o_row = a->dk.row_stride;
+    p.o_head = a->dk.head_stride;
+    p.o_batch = a->dk.batch_stride;
+    p.out2 = a->dv.ptr;
+    p.o2_row = a->dv.row_stride;
+    p.o2_head = a->dv.head_stride;
+    p.o2_batch = a->dv.batch_stride;
+    dim3 grid((a->tk + 127) / 128, a->kv_heads, a->batch);
+    if (HD == 64) {
+      static bool once = false;
+      if (!once) {
+        if (set_smem(attn_bwd_dkdv_kernel<64>, DkvCfg<64>::kSmem)) return -2;
+        once = true;
+      }
+      attn_bwd_dkdv_kernel<64><<<grid, kThreads, DkvCfg<64>::kSmem, st>>>(tq, tk, tv, tdo, p);
+    } else {
+      static bool once = false;
+      if (!once) {
+        if (set_smem(attn_bwd_dkdv_kernel<128>, DkvCfg<128>::kSmem)) return -2;
+        once = true;
+      }
+      attn_bwd_dkdv_kernel<128><<<grid, kThreads, DkvCfg<128>::kSmem, st>>>(tq, tk, tv, tdo, p);
+    }
+    if (cudaGetLastError() != cudaSuccess) return -2;
+  }
+  // part 2: dQ
+  {
+    CUtensorMap tq, tk, tv, tdo;
+    if ((rc = make_map(&tq, a->q, a->tq, a->heads, a->batch, HD, 128))) return rc;
+    if ((rc = make_map(&tdo, a->d_o, a->tq, a->heads, a->batch, HD, 128))) return rc;
+    if ((rc = make_map(&tk, a->k, a->tk, a->kv_heads, a->batch, HD, 64))) return rc;
+    if ((rc = make_map(&tv, a->v, a->tk, a->kv_heads, a->batch, HD, 64))) return rc;
+    AttnDev p = base_params(a);
+    p.out = a->dq.ptr;
+    p.o_row = a->dq.row_stride;
+    p.o_head = a->dq.head_stride;
+    p.o_batch = a->dq.batch_stride;
+    dim3 grid((a->tq + 127) / 128, a->heads, a->batch);
+    if (HD == 64) {
+      static bool once = false;
+      if (!once) {
+        if (set_smem(attn_bwd_dq_kernel<64>, DqCfg<64>::kSmem)) return -2;
+        once = true;
+      }
+      attn_bwd_dq_kernel<64><<<grid, kThreads, DqCfg<64>::kSmem, st>>>(tq, tk, tv, tdo, p);
+    } else {
+      static bool once = false;
+      if (!once) {
+        if (set_smem(attn_bwd_dq_kernel<128>, DqCfg<128>::kSmem)) return -2;
+        once = true;
+      }
+      attn_bwd_dq_kernel<128><<<grid, kThreads, DqCfg<128>::kSmem, st>>>(tq, tk, tv, tdo, p);
+    }
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

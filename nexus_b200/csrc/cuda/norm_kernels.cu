@@ -1,0 +1,334 @@
+// LayerNorm / RMSNorm forward (optionally fused with the residual add that feeds them) and a
+// deterministic backward: dx per row (optionally fused with the residual-path gradient) plus
+// column-wise parameter gradients reduced in a fixed order through caller-provided partials.
+// Statistics are always FP32.  Parity: src/cuda/kernels_norm.cu:80-434 of the reference
+// (layernorm_forward, residual_layernorm_forward, rmsnorm_forward, norm backward + 2-stage
+// deterministic parameter reduce).
+#include "common.cuh"
+#include "nx_api_kernels.h"
+
+namespace {
+using namespace nx;
+
+template <typename T>
+struct Vec4;
+template <>
+struct Vec4<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    float4 q = *reinterpret_cast<const float4*>(p);
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <>
+struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
+    uint2 q = *reinterpret_cast<const uint2*>(p);
+    __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&q.x);
+    __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&q.y);
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4]) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]);
+    __nv_bfloat162 b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 q;
+    q.x = *reinterpret_cast<uint32_t*>(&a);
+    q.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = q;
+  }
+};
+
+// One warp per row; the row is re-read from L1/L2 for the second and third pass.
+template <typename XT, typename PT, typename YT, bool kRms>
+__global__ void norm_fwd_kernel(const XT* __restrict__ x, const XT* __restrict__ res, XT* __restrict__ sum_out,
+                                const PT* __restrict__ gamma, const PT* __restrict__ beta, YT* __restrict__ y,
+                                float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int cols,
+                                float eps) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nvec = cols >> 2;
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
+    const XT* xr = x + static_cast<int64_t>(row) * cols;
+    const XT* rr = res ? res + static_cast<int64_t>(row) * cols : nullptr;
+    XT* sr = sum_out ? sum_out + static_cast<int64_t>(row) * cols : nullptr;
+    float s = 0.0f;
+    for (int i = lane; i < nvec; i += 32) {
+      float v[4];
+      Vec4<XT>::load(xr + 4 * i, v);
+      if (rr) {
+        float q[4];
+        Vec4<XT>::load(rr + 4 * i, q);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] += q[j];
+        if (sr) Vec4<XT>::store(sr + 4 * i, v);
+      }
+      s += kRms ? (v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]) : (v[0] + v[1] + v[2] + v[3]);
+    }
+    if (rr && sr) __syncwarp();
+    // After the fused add the normalised input is the sum; read it back from where it was written.
+    const XT* src = (rr && sr) ? sr : xr;
+    s = warp_sum(s);
+    float mean = 0.0f, rstd;
+    if (kRms) {
+      rstd = rsqrtf(s / cols + eps);
+    } else {
+      mean = s / cols;
+      float var = 0.0f;
+      for (int i = lane; i < nvec; i += 32) {
+        float v[4];
+        Vec4<XT>::load(src + 4 * i, v);
+        if (rr && !sr) {
+          float q[4];
+          Vec4<XT>::load(rr + 4 * i, q);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) v[j] += q[j];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) var += (v[j] - mean) * (v[j] - mean);
+      }
+      var = warp_sum(var);
+      rstd = rsqrtf(var / cols + eps);
+    }
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+    YT* yr = y + static_cast<int64_t>(row) * cols;
+    for (int i = lane; i < nvec; i += 32) {
+      float v[4], g[4], o[4];
+      Vec4<XT>::load(src + 4 * i, v);
+      if (rr && !sr) {
+        float q[4];
+        Vec4<XT>::load(rr + 4 * i, q);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] += q[j];
+      }
+      Vec4<PT>::load(gamma + 4 * i, g);
+      if (!kRms && beta) {
+        float b[4];
+        Vec4<PT>::load(beta + 4 * i, b);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = (v[j] - mean) * rstd * g[j] + b[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = (v[j] - mean) * rstd * g[j];
+      }
+      Vec4<YT>::store(yr + 4 * i, o);
+    }
+  }
+}
+
+// dx[row] = (add ? add[row] : 0) + rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat))        (LayerNorm)
+// dx[row] = (add ? add[row] : 0) + rstd * (g*dy - xhat * mean(g*dy*xhat))                     (RMSNorm)
+template <typename XT, typename PT, typename GT, typename DT, bool kRms>
+__global__ void norm_bwd_dx_kernel(const GT* __restrict__ dy, const XT* __restrict__ x,
+                                   const PT* __restrict__ gamma, const float* __restrict__ mean,
+                                   const float* __restrict__ rstd, const DT* __restrict__ add, DT* __restrict__ dx,
+                                   int rows, int cols) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nvec = cols >> 2;
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
+    const XT* xr = x + static_cast<int64_t>(row) * cols;
+    const GT* gr = dy + static_cast<int64_t>(row) * cols;
+    const float mu = kRms ? 0.0f : mean[row];
+    const float rs = rstd[row];
+    float s1 = 0.0f, s2 = 0.0f;
+    for (int i = lane; i < nvec; i += 32) {
+      float v[4], d[4], g[4];
+      Vec4<XT>::load(xr + 4 * i, v);
+      Vec4<GT>::load(gr + 4 * i, d);
+      Vec4<PT>::load(gamma + 4 * i, g);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float gd = g[j] * d[j];
+        s1 += gd;
+        s2 += gd * (v[j] - mu) * rs;
+      }
+    }
+    s1 = warp_sum(s1) / cols;
+    s2 = warp_sum(s2) / cols;
+    if (kRms) s1 = 0.0f;
+    DT* dxr = dx + static_cast<int64_t>(row) * cols;
+    const DT* ar = add ? add + static_cast<int64_t>(row) * cols : nullptr;
+    for (int i = lane; i < nvec; i += 32) {
+      float v[4], d[4], g[4], o[4];
+      Vec4<XT>::load(xr + 4 * i, v);
+      Vec4<GT>::load(gr + 4 * i, d);
+      Vec4<PT>::load(gamma + 4 * i, g);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o[j] = rs * (g[j] * d[j] - s1 - (v[j] - mu) * rs * s2);
+      if (ar) {
+        float a[4];
+        Vec4<DT>::load(ar + 4 * i, a);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] += a[j];
+      }
+      Vec4<DT>::store(dxr + 4 * i, o);
+    }
+  }
+}
+
+// Column partials: block (32 columns x 8 row lanes) covers one column strip and one row chunk.
+// partial[chunk][0][c] = sum dy*xhat, partial[chunk][1][c] = sum dy, both in a fixed order.
+template <typename XT, typename GT, bool kRms>
+__global__ void norm_bwd_param_partial_kernel(const GT* __restrict__ dy, const XT* __restrict__ x,
+                                              const float* __restrict__ mean, const float* __restrict__ rstd,
+                                              float* __restrict__ partial, int rows, int cols,
+                                              int rows_per_chunk) {
+  __shared__ float sg[8][33];
+  __shared__ float sb[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  const int chunk = blockIdx.y;
+  const int r_begin = chunk * rows_per_chunk;
+  const int r_end = min(rows, r_begin + rows_per_chunk);
+  float ag = 0.0f, ab = 0.0f;
+  if (c < cols) {
+    for (int r = r_begin + threadIdx.y; r < r_end; r += 8) {
+      const float d = Num<GT>::load(dy + static_cast<int64_t>(r) * cols + c);
+      const float xv = Num<XT>::load(x + static_cast<int64_t>(r) * cols + c);
+      const float xhat = (xv - (kRms ? 0.0f : mean[r])) * rstd[r];
+      ag += d * xhat;
+      ab += d;
+    }
+  }
+  sg[threadIdx.y][threadIdx.x] = ag;
+  sb[threadIdx.y][threadIdx.x] = ab;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+    float tg = 0.0f, tb = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      tg += sg[k][threadIdx.x];
+      tb += sb[k][threadIdx.x];
+    }
+    partial[(static_cast<int64_t>(chunk) * 2 + 0) * cols + c] = tg;
+    partial[(static_cast<int64_t>(chunk) * 2 + 1) * cols + c] = tb;
+  }
+}
+
+__global__ void norm_bwd_param_final_kernel(const float* __restrict__ partial, float* __restrict__ dgamma,
+                                            float* __restrict__ dbeta, int cols, int chunks, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  float tg = 0.0f, tb = 0.0f;
+  for (int k = 0; k < chunks; ++k) {
+    tg += partial[(static_cast<int64_t>(k) * 2 + 0) * cols + c];
+    tb += partial[(static_cast<int64_t>(k) * 2 + 1) * cols + c];
+  }
+  if (dgamma) dgamma[c] = accumulate ? dgamma[c] + tg : tg;
+  if (dbeta) dbeta[c] = accumulate ? dbeta[c] + tb : tb;
+}
+
+template <typename XT, typename PT, typename YT>
+int launch_fwd(bool rms, const void* x, const void* res, void* sum_out, const void* gamma, const void* beta, void* y,
+               float* mean, float* rstd, int rows, int cols, float eps, cudaStream_t st) {
+  const int threads = 256, wpb = threads / 32;
+  const int blocks = std::min((rows + wpb - 1) / wpb, kNumSmsB200 * 8);
+  if (rms)
+    norm_fwd_kernel<XT, PT, YT, true><<<blocks, threads, 0, st>>>(
+        (const XT*)x, (const XT*)res, (XT*)sum_out, (const PT*)gamma, (const PT*)beta, (YT*)y, mean, rstd, rows, cols,
+        eps);
+  else
+    norm_fwd_kernel<XT, PT, YT, false><<<blocks, threads, 0, st>>>(
+        (const XT*)x, (const XT*)res, (XT*)sum_out, (const PT*)gamma, (const PT*)beta, (YT*)y, mean, rstd, rows, cols,
+        eps);
+  return launch_status();
+}
+
+template <typename XT, typename PT, typename GT, typename DT>
+int launch_bwd_dx(bool rms, const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                  const void* add, void* dx, int rows, int cols, cudaStream_t st) {
+  const int threads = 256, wpb = threads / 32;
+  const int blocks = std::min((rows + wpb - 1) / wpb, kNumSmsB200 * 8);
+  if (rms)
+    norm_bwd_dx_kernel<XT, PT, GT, DT, true><<<blocks, threads, 0, st>>>(
+        (const GT*)dy, (const XT*)x, (const PT*)gamma, mean, rstd, (const DT*)add, (DT*)dx, rows, cols);
+  else
+    norm_bwd_dx_kernel<XT, PT, GT, DT, false><<<blocks, threads, 0, st>>>(
+        (const GT*)dy, (const XT*)x, (const PT*)gamma, mean, rstd, (const DT*)add, (DT*)dx, rows, cols);
+  return launch_status();
+}
+
+}  // namespace
+
+#include <algorithm>
+
+extern "C" int nx_norm_fwd(int rms, const void* x, int x_dtype, const void* residual, void* sum_out,
+                           const void* gamma, const void* beta, int param_dtype, void* y, int y_dtype, float* mean,
+                           float* rstd, int rows, int cols, float eps, nx_stream_t stream) {
+  if (rows <= 0 || cols <= 0 || (cols & 3)) return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool r = rms != 0;
+#define NX_FWD(XT, PT, YT) \
+  return launch_fwd<XT, PT, YT>(r, x, residual, sum_out, gamma, beta, y, mean, rstd, rows, cols, eps, st)
+  if (x_dtype == NX_F32 && param_dtype == NX_F32 && y_dtype == NX_BF16) NX_FWD(float, float, __nv_bfloat16);
+  if (x_dtype == NX_F32 && param_dtype == NX_F32 && y_dtype == NX_F32) NX_FWD(float, float, float);
+  if (x_dtype == NX_BF16 && param_dtype == NX_F32 && y_dtype == NX_BF16) NX_FWD(__nv_bfloat16, float, __nv_bfloat16);
+  if (x_dtype == NX_BF16 && param_dtype == NX_BF16 && y_dtype == NX_BF16)
+    NX_FWD(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+  if (x_dtype == NX_F32 && param_dtype == NX_BF16 && y_dtype == NX_BF16) NX_FWD(float, __nv_bfloat16, __nv_bfloat16);
+#undef NX_FWD
+  return -1;
+}
+
+size_t nx_norm_bwd_partial_floats(int rows, int cols) {
+  const int chunks = std::max(1, std::min(64, (rows + 255) / 256));
+  return static_cast<size_t>(chunks) * 2 * cols;
+}
+
+extern "C" size_t nx_norm_bwd_scratch_bytes(int rows, int cols) {
+  return nx_norm_bwd_partial_floats(rows, cols) * sizeof(float);
+}
+
+extern "C" int nx_norm_bwd(int rms, const void* dy, int dy_dtype, const void* x, int x_dtype, const void* gamma,
+                           int param_dtype, const float* mean, const float* rstd, const void* add, void* dx,
+                           int dx_dtype, float* dgamma, float* dbeta, int accumulate_params, float* scratch, int rows,
+                           int cols, nx_stream_t stream) {
+  if (rows <= 0 || cols <= 0 || (cols & 3)) return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool r = rms != 0;
+  int rc = -1;
+#define NX_BWD(XT, PT, GT, DT) rc = launch_bwd_dx<XT, PT, GT, DT>(r, dy, x, gamma, mean, rstd, add, dx, rows, cols, st)
+  if (dx != nullptr) {
+    if (x_dtype == NX_F32 && param_dtype == NX_F32 && dy_dtype == NX_BF16 && dx_dtype == NX_F32)
+      NX_BWD(float, float, __nv_bfloat16, float);
+    else if (x_dtype == NX_F32 && param_dtype == NX_F32 && dy_dtype == NX_F32 && dx_dtype == NX_F32)
+      NX_BWD(float, float, float, float);
+    else if (x_dtype == NX_BF16 && param_dtype == NX_F32 && dy_dtype == NX_BF16 && dx_dtype == NX_BF16)
+      NX_BWD(__nv_bfloat16, float, __nv_bfloat16, __nv_bfloat16);
+    else if (x_dtype == NX_BF16 && param_dtype == NX_BF16 && dy_dtype == NX_BF16 && dx_dtype == NX_BF16)
+      NX_BWD(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    else if (x_dtype == NX_F32 && param_dtype == NX_BF16 && dy_dtype == NX_BF16 && dx_dtype == NX_F32)
+      NX_BWD(float, __nv_bfloat16, __nv_bfloat16, float);
+    else
+      return -1;
+    if (rc != 0) return rc;
+  }
+#undef NX_BWD
+  if (dgamma == nullptr && dbeta == nullptr) return 0;
+  if (scratch == nullptr) return -1;
+  const int chunks = std::max(1, std::min(64, (rows + 255) / 256));
+  const int rows_per_chunk = (rows + chunks - 1) / chunks;
+  dim3 grid((cols + 31) / 32, chunks), block(32, 8);
+#define NX_PP(XT, GT)                                                                                     \
+  do {                                                                                                    \
+    if (r)                                                                                                \
+      norm_bwd_param_partial_kernel<XT, GT, true><<<grid, block, 0, st>>>((const GT*)dy, (const XT*)x, mean, rstd, \
+                                                                         scratch, rows, cols, rows_per_chunk);     \
+    else                                                                                                  \
+      norm_bwd_param_partial_kernel<XT, GT, false><<<grid, block, 0, st>>>((const GT*)dy, (const XT*)x, mean, rstd, \
+                                                                          scratch, rows, cols, rows_per_chunk);    \
+  } while (0)
+  if (x_dtype == NX_F32 && dy_dtype == NX_BF16) NX_PP(float, __nv_bfloat16);
+  else if (x_dtype == NX_F32 && dy_dtype == NX_F32) NX_PP(float, float);
+  else if (x_dtype == NX_BF16 && dy_dtype == NX_BF16) NX_PP(__nv_bfloat16, __nv_bfloat16);
+  else return -1;
+#undef NX_PP
+  if (launch_status() != 0) return -2;
+  norm_bwd_param_final_kernel<<<(cols + 255) / 256, 256, 0, st>>>(scratch, dgamma, dbeta, cols, chunks,
+                                                                  accumulate_params);
+  return launch_status();
+}
