@@ -7,6 +7,8 @@
 #include "common.cuh"
 #include "nx_api_kernels.h"
 
+#include <algorithm>
+
 namespace {
 using namespace nx;
 
@@ -126,7 +128,7 @@ template <typename XT, typename PT, typename GT, typename DT, bool kRms>
 __global__ void norm_bwd_dx_kernel(const GT* __restrict__ dy, const XT* __restrict__ x,
                                    const PT* __restrict__ gamma, const float* __restrict__ mean,
                                    const float* __restrict__ rstd, const DT* __restrict__ add, DT* __restrict__ dx,
-                                   int rows, int cols) {
+                                   __nv_bfloat16* __restrict__ dx_lp, int rows, int cols) {
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nvec = cols >> 2;
@@ -167,6 +169,7 @@ __global__ void norm_bwd_dx_kernel(const GT* __restrict__ dy, const XT* __restri
         for (int j = 0; j < 4; ++j) o[j] += a[j];
       }
       Vec4<DT>::store(dxr + 4 * i, o);
+      if (dx_lp) Vec4<__nv_bfloat16>::store(dx_lp + static_cast<int64_t>(row) * cols + 4 * i, o);
     }
   }
 }
@@ -240,15 +243,17 @@ int launch_fwd(bool rms, const void* x, const void* res, void* sum_out, const vo
 
 template <typename XT, typename PT, typename GT, typename DT>
 int launch_bwd_dx(bool rms, const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
-                  const void* add, void* dx, int rows, int cols, cudaStream_t st) {
+                  const void* add, void* dx, void* dx_lp, int rows, int cols, cudaStream_t st) {
   const int threads = 256, wpb = threads / 32;
   const int blocks = std::min((rows + wpb - 1) / wpb, kNumSmsB200 * 8);
   if (rms)
     norm_bwd_dx_kernel<XT, PT, GT, DT, true><<<blocks, threads, 0, st>>>(
-        (const GT*)dy, (const XT*)x, (const PT*)gamma, mean, rstd, (const DT*)add, (DT*)dx, rows, cols);
+        (const GT*)dy, (const XT*)x, (const PT*)gamma, mean, rstd, (const DT*)add, (DT*)dx, (__nv_bfloat16*)dx_lp, rows,
+        cols);
   else
     norm_bwd_dx_kernel<XT, PT, GT, DT, false><<<blocks, threads, 0, st>>>(
-        (const GT*)dy, (const XT*)x, (const PT*)gamma, mean, rstd, (const DT*)add, (DT*)dx, rows, cols);
+        (const GT*)dy, (const XT*)x, (const PT*)gamma, mean, rstd, (const DT*)add, (DT*)dx, (__nv_bfloat16*)dx_lp, rows,
+        cols);
   return launch_status();
 }
 
@@ -274,7 +279,7 @@ extern "C" int nx_norm_fwd(int rms, const void* x, int x_dtype, const void* resi
   return -1;
 }
 
-size_t nx_norm_bwd_partial_floats(int rows, int cols) {
+static size_t nx_norm_bwd_partial_floats(int rows, int cols) {
   const int chunks = std::max(1, std::min(64, (rows + 255) / 256));
   return static_cast<size_t>(chunks) * 2 * cols;
 }
@@ -285,13 +290,13 @@ extern "C" size_t nx_norm_bwd_scratch_bytes(int rows, int cols) {
 
 extern "C" int nx_norm_bwd(int rms, const void* dy, int dy_dtype, const void* x, int x_dtype, const void* gamma,
                            int param_dtype, const float* mean, const float* rstd, const void* add, void* dx,
-                           int dx_dtype, float* dgamma, float* dbeta, int accumulate_params, float* scratch, int rows,
-                           int cols, nx_stream_t stream) {
+                           int dx_dtype, void* dx_lp, float* dgamma, float* dbeta, int accumulate_params,
+                           float* scratch, int rows, int cols, nx_stream_t stream) {
   if (rows <= 0 || cols <= 0 || (cols & 3)) return -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool r = rms != 0;
   int rc = -1;
-#define NX_BWD(XT, PT, GT, DT) rc = launch_bwd_dx<XT, PT, GT, DT>(r, dy, x, gamma, mean, rstd, add, dx, rows, cols, st)
+#define NX_BWD(XT, PT, GT, DT) rc = launch_bwd_dx<XT, PT, GT, DT>(r, dy, x, gamma, mean, rstd, add, dx, dx_lp, rows, cols, st)
   if (dx != nullptr) {
     if (x_dtype == NX_F32 && param_dtype == NX_F32 && dy_dtype == NX_BF16 && dx_dtype == NX_F32)
       NX_BWD(float, float, __nv_bfloat16, float);

@@ -42,8 +42,8 @@ int nx_norm_fwd(int rms, const void* x, int x_dtype, const void* residual, void*
 size_t nx_norm_bwd_scratch_bytes(int rows, int cols);
 int nx_norm_bwd(int rms, const void* dy, int dy_dtype, const void* x, int x_dtype, const void* gamma,
                 int param_dtype, const float* mean, const float* rstd, const void* add, void* dx, int dx_dtype,
-                float* dgamma, float* dbeta, int accumulate_params, float* scratch, int rows, int cols,
-                nx_stream_t stream);
+                void* dx_lp /* optional BF16 copy of dx */, float* dgamma, float* dbeta, int accumulate_params,
+                float* scratch, int rows, int cols, nx_stream_t stream);
 
 // ---- embedding ---------------------------------------------------------------------------------
 int nx_embedding_pos_fwd(const int32_t* tokens, const int32_t* positions, const void* wte, const void* wpe,

@@ -225,9 +225,10 @@ def norm_fwd(x, gamma, beta=None, *, rms=False, eps=1e-5, residual=None, sum_out
 
 
 def norm_bwd(dy, x, gamma, mean, rstd, *, rms=False, add=None, dx_dtype=None, dgamma=None, dbeta=None,
-             accumulate_params=False, want_dx=True):
+             accumulate_params=False, want_dx=True, dx=None, dx_lp=None):
     rows, cols = x.numel() // x.shape[-1], x.shape[-1]
-    dx = torch.empty(x.shape, dtype=dx_dtype or x.dtype, device=x.device) if want_dx else None
+    if dx is None and want_dx:
+        dx = torch.empty(x.shape, dtype=dx_dtype or x.dtype, device=x.device)
     need_params = dgamma is not None or dbeta is not None
     L = lib()
     sc = None
@@ -235,7 +236,7 @@ def norm_bwd(dy, x, gamma, mean, rstd, *, rms=False, add=None, dx_dtype=None, dg
         sc = scratch(L.nx_norm_bwd_scratch_bytes(C.c_int(rows), C.c_int(cols)), "norm_bwd", x.device)
     _check(L.nx_norm_bwd(C.c_int(int(rms)), _p(dy), C.c_int(_DT[dy.dtype]), _p(x), C.c_int(_DT[x.dtype]), _p(gamma),
                          C.c_int(_DT[gamma.dtype]), _p(mean), _p(rstd), _p(add), _p(dx),
-                         C.c_int(_DT[dx.dtype] if dx is not None else F32), _p(dgamma), _p(dbeta),
+                         C.c_int(_DT[dx.dtype] if dx is not None else F32), _p(dx_lp), _p(dgamma), _p(dbeta),
                          C.c_int(int(accumulate_params)), _p(sc), C.c_int(rows), C.c_int(cols), _stream()),
            "nx_norm_bwd")
     return dx

@@ -1,0 +1,259 @@
+"""`GptModel` behind the `LmBackend` interface: pinned double-buffered token upload, one device
+sync per optimizer step, optional whole-step CUDA graph (inputs, every micro-step, optimizer and
+the result tail are captured once and replayed; learning rate and micro-step weights are refreshed
+from pinned host memory), data-parallel gradient all-reduce over NCCL.
+
+Parity: include/nexus/cuda/lm_backend.hpp:52-141 and src/cuda/lm_backend.cpp:211-700 of the
+reference (`GptLmBackend`).  The reference moves DDP gradients through the host; here they stay
+on the device (NCCL / NVLink).
+"""
+from __future__ import annotations
+
+import io
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from ..lm.config import LmConfig
+from ..models.gpt import PARAM_ORDER, AdamWConfig, GptModel
+from ..ops import _cuda as K
+from .lm_trainer import AdamW, LmBackend, LmNonFinite, LmParamInfo, LmStepResult
+
+# Dense BF16 tensor peak per device, FLOP/s, keyed by compute capability major (MFU denominator).
+PEAK_BF16_FLOPS = {10: 2.25e15, 9: 0.989e15, 8: 0.312e15}
+
+
+class GptLmBackend(LmBackend):
+    def __init__(self, config: LmConfig, micro_batch: int, seq_len: int, device="cuda", seed: int = 1234,
+                 deterministic: bool = False):
+        self.dev = torch.device(device)
+        torch.cuda.set_device(self.dev)
+        self.model = GptModel(config, device=self.dev, seed=seed)
+        self.model.deterministic_embedding = deterministic
+        self.B, self.T = micro_batch, seq_len
+        self._host_tokens = [torch.empty((micro_batch, seq_len), dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._dev_tokens: List[torch.Tensor] = []
+        self._copy_events = [None, None]
+        self._slot = 0
+        self._losses_dev = None
+        self._result_host = torch.zeros(8, dtype=torch.float32).pin_memory()
+        self._opt_cfg: Optional[AdamWConfig] = None
+        self._pg = None
+        self._graph = None
+        self._graph_enabled = False
+        self._graph_key = None
+        self._pending: List[tuple] = []
+        self._loss_total = torch.zeros(1, dtype=torch.float32, device=self.dev)
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    # -------------------------------------------------------------------------------- interface
+    def device(self) -> str: return str(self.dev)
+    def micro_batch(self) -> int: return self.B
+    def seq_len(self) -> int: return self.T
+    def vocab(self) -> int: return self.model.V
+
+    def parameters(self) -> List[LmParamInfo]:
+        m = self.model
+        return [LmParamInfo(n, int(np.prod(m.shapes[n])), 2 if n.endswith("_w") and not n.startswith("ln") or n in ("wte", "wpe") else 1,
+                            n in ("wte", "wpe")) for n in PARAM_ORDER]
+
+    def set_param_scales(self, weight_decay, lr) -> None:
+        m = self.model
+        segs = [(m.offsets[n], int(np.prod(m.shapes[n])), float(weight_decay[i]), float(lr[i]))
+                for i, n in enumerate(PARAM_ORDER)]
+        m.chunks = K.make_chunks(segs, device=self.dev)
+
+    def reshape(self, micro_batch: int, seq_len: int) -> None:
+        if (micro_batch, seq_len) != (self.B, self.T):
+            self.__init_buffers(micro_batch, seq_len)
+
+    def __init_buffers(self, B, T):
+        self.B, self.T = B, T
+        self._host_tokens = [torch.empty((B, T), dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._dev_tokens = []
+        self._graph = None
+
+    def _upload(self, tokens: np.ndarray, index: int) -> torch.Tensor:
+        """Pinned host buffer (double-buffered) -> device, on the compute stream."""
+        while len(self._dev_tokens) <= index:
+            self._dev_tokens.append(torch.empty((self.B, self.T), dtype=torch.int32, device=self.dev))
+        slot = self._slot
+        self._slot ^= 1
+        ev = self._copy_events[slot]
+        if ev is not None:
+            ev.synchronize()  # the previous copy out of this pinned buffer has finished
+        host = self._host_tokens[slot]
+        host.copy_(torch.from_numpy(np.ascontiguousarray(tokens, dtype=np.int32)))
+        self._dev_tokens[index].copy_(host, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._copy_events[slot] = ev
+        self.h2d_bytes += host.numel() * 4
+        return self._dev_tokens[index]
+
+    def micro_step(self, tokens: np.ndarray, grad_weight: float, index: int, count: int) -> None:
+        dev_tokens = self._upload(tokens, index)
+        if self._graph_enabled:
+            self._pending.append((index, grad_weight))
+            if index == count - 1:
+                self._count = count
+            return
+        self.model.forward_backward(dev_tokens, grad_scale=grad_weight, accumulate_loss=index > 0,
+                                    loss_weight=grad_weight)
+        if index == count - 1 and self._pg is not None:
+            self._pg.all_reduce_tensor(self.model.grads, "sum")
+
+    def optimizer_step(self, optimizer: AdamW, lr: float, clip: float) -> None:
+        cfg = AdamWConfig(lr=lr, beta1=optimizer.beta1, beta2=optimizer.beta2, eps=optimizer.eps,
+                          weight_decay=optimizer.weight_decay, grad_clip=clip)
+        m = self.model
+        if self._opt_cfg is None or (cfg.beta1, cfg.beta2, cfg.eps, cfg.weight_decay, cfg.grad_clip) != \
+                (self._opt_cfg.beta1, self._opt_cfg.beta2, self._opt_cfg.eps, self._opt_cfg.weight_decay,
+                 self._opt_cfg.grad_clip):
+            m.set_optimizer(cfg)
+            self._opt_cfg = cfg
+        m.set_lr(lr)
+        if self._graph_enabled:
+            self._run_graph()
+            return
+        m.optimizer_step()
+
+    def finish_step(self) -> LmStepResult:
+        """One small D2H copy (loss, grad norm, found_inf) + one synchronisation."""
+        m = self.model
+        st = m.opt_state
+        gn_off, fi_off = K.OptState.grad_norm.offset, K.OptState.found_inf.offset
+        self._result_host[0:1].copy_(m.loss_buf, non_blocking=True)
+        self._result_host[1:2].copy_(st[gn_off: gn_off + 4].view(torch.float32), non_blocking=True)
+        self._result_host[2:3].copy_(st[fi_off: fi_off + 4].view(torch.int32).to(torch.float32), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        self.d2h_bytes += 12
+        K.check_status(self.dev)
+        loss, gn, fi = (float(x) for x in self._result_host[:3])
+        return LmStepResult(loss=loss, grad_norm=gn, skipped=fi != 0.0)
+
+    def device_step(self, tokens_dev: torch.Tensor, lr: float) -> None:
+        """One full optimizer step on tokens that already live on the device (no host traffic, no sync)."""
+        m = self.model
+        if self._opt_cfg is None:
+            self._opt_cfg = AdamWConfig(lr=lr)
+            m.set_optimizer(self._opt_cfg)
+        m.forward_backward(tokens_dev, grad_scale=1.0)
+        if self._pg is not None:
+            self._pg.all_reduce_tensor(m.grads, "sum")
+        m.optimizer_step()
+
+    # ------------------------------------------------------------------------------- CUDA graph
+    def compile(self, enabled: bool, mode: str = "default") -> None:
+        self._graph_enabled = enabled
+        self._graph = None
+
+    def _run_graph(self) -> None:
+        m = self.model
+        count = self._count
+        weights = [w for _, w in sorted(self._pending)]
+        self._pending = []
+        key = (count, tuple(weights))
+        if self._graph is None or self._graph_key != key:
+            # warm-up on a side stream (allocations, lazy module loading), then capture
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._graph_body(count, weights)
+                K.scratch(1, "gemm_splitk", self.dev)
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            # undo the warm-up's optimizer update: restore from a snapshot
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._graph_body(count, weights)
+            self._graph, self._graph_key = g, key
+            return  # the warm-up run already performed this step
+        self._graph.replay()
+
+    def _graph_body(self, count: int, weights) -> None:
+        m = self.model
+        for i in range(count):
+            m.forward_backward(self._dev_tokens[i], grad_scale=weights[i], accumulate_loss=i > 0,
+                               loss_weight=weights[i])
+        if self._pg is not None:
+            self._pg.all_reduce_tensor(m.grads, "sum")
+        m.optimizer_step()
+
+    # ------------------------------------------------------------------------------- evaluation
+    def eval_loss(self, tokens: np.ndarray) -> float:
+        t = torch.from_numpy(np.ascontiguousarray(tokens, dtype=np.int32)).to(self.dev)
+        return self.model.loss(t)
+
+    def token_losses(self, tokens: np.ndarray) -> np.ndarray:
+        t = torch.from_numpy(np.ascontiguousarray(tokens, dtype=np.int32)).to(self.dev)
+        logits = self.model.forward(t)[:, : self.model.V].float()
+        tgt = torch.roll(t.long(), -1, dims=1).reshape(-1)
+        l = torch.nn.functional.cross_entropy(logits, tgt, reduction="none").reshape(t.shape)
+        l[:, -1] = 0.0
+        return l.reshape(-1).cpu().numpy()
+
+    def diagnose(self, tokens: np.ndarray) -> LmNonFinite:
+        m = self.model
+        for n in PARAM_ORDER:
+            if int(K.count_nonfinite(m.p[n].reshape(-1)).item()):
+                return LmNonFinite(True, f"param:{n}")
+        for n in PARAM_ORDER:
+            if int(K.count_nonfinite(m.g[n].reshape(-1)).item()):
+                return LmNonFinite(True, f"grad:{n}")
+        t = torch.from_numpy(np.ascontiguousarray(tokens, dtype=np.int32)).to(self.dev)
+        m.forward(t)
+        a = m._acts
+        for l in range(m.L):
+            for key in ("ln1", "qkv", "atty", "ln2", "fch"):
+                if int(K.count_nonfinite(a[key][l].reshape(-1)).item()):
+                    return LmNonFinite(True, f"activation:h{l}.{key}")
+        return LmNonFinite(False, "")
+
+    def layer_norms(self):
+        m = self.model
+        return [(n, float(m.p[n].norm()), float(m.g[n].norm())) for n in PARAM_ORDER]
+
+    # ------------------------------------------------------------------------------------ state
+    def save_state(self) -> bytes:
+        m = self.model
+        buf = io.BytesIO()
+        torch.save({"params": m.params.cpu(), "m": m.m.cpu(), "v": m.v.cpu(), "opt": m.opt_state.cpu(),
+                    "step_count": m.step_count}, buf)
+        return buf.getvalue()
+
+    def load_state(self, blob: bytes) -> None:
+        m = self.model
+        d = torch.load(io.BytesIO(blob), map_location="cpu")
+        m.params.copy_(d["params"])
+        m.m.copy_(d["m"])
+        m.v.copy_(d["v"])
+        m.opt_state.copy_(d["opt"])
+        m.step_count = d["step_count"]
+        m.refresh_shadow()
+        m.grads.zero_()
+
+    def load_resharded_state(self, blobs) -> None:
+        self.load_state(blobs[0])  # replicated layout: every old rank holds the full state
+
+    def peak_memory_bytes(self) -> int: return int(torch.cuda.max_memory_allocated(self.dev))
+    def reset_peak_memory(self) -> None: torch.cuda.reset_peak_memory_stats(self.dev)
+
+    def peak_flops(self) -> float:
+        major = torch.cuda.get_device_capability(self.dev)[0]
+        return PEAK_BF16_FLOPS.get(major, 0.0)
+
+    def flops_per_token(self, seq_len: int) -> float: return self.model.flops_per_token(seq_len)
+
+    # ------------------------------------------------------------------------------ data parallel
+    def attach_process_group(self, group, options=None) -> None:
+        self._pg = group
+
+    def broadcast_parameters(self) -> None:
+        if self._pg is not None:
+            self._pg.broadcast_tensor(self.model.params, 0)
+            self.model.refresh_shadow()
+
+    def data_parallel_group(self): return self._pg
