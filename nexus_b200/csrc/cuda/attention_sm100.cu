@@ -19,6 +19,7 @@
 #include "sm100_ptx.cuh"
 #include "tensor_map.h"
 #include <algorithm>
+#include <type_traits>
 
 namespace {
 using namespace nx;
@@ -71,12 +72,72 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_addr, int k_rows,
   return make_smem_desc_sw128(a, static_cast<uint32_t>(k_rows * 128), 1024);
 }
 
-__device__ __forceinline__ bool masked(const AttnDev& p, int q, int k) {
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Per-row visible key range [lo, hi] (inclusive) under the causal / window / length masks.
+__device__ __forceinline__ void row_limits(const AttnDev& p, int q, int& lo, int& hi) {
   const int off = p.Tk - p.Tq;
-  if (k >= p.Tk) return true;
-  if (p.causal && k > q + off) return true;
-  if (p.window > 0 && k < q + off - p.window + 1) return true;
-  return false;
+  hi = p.Tk - 1;
+  lo = 0;
+  if (p.causal) hi = min(hi, q + off);
+  if (p.window > 0) lo = max(lo, q + off - p.window + 1);
+}
+
+// Row maximum of a [128 x 32*kChunks] fp32 score tile held in TMEM (this thread's lane).
+template <bool kMask, int kChunks>
+__device__ __forceinline__ float tile_row_max(uint32_t taddr, int k0, int lo, int hi) {
+  float mx = -INFINITY;
+#pragma unroll 1
+  for (int cc = 0; cc < kChunks; ++cc) {
+    uint32_t v[32];
+    tmem_ld_32x32b_x32(taddr + cc * 32, v);
+    tmem_ld_wait();
+    const int clo = lo - k0 - cc * 32, chi = hi - k0 - cc * 32;  // valid iff clo <= c <= chi
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      float s = __uint_as_float(v[c]);
+      if (kMask && (c < clo || c > chi)) s = -INFINITY;
+      mx = fmaxf(mx, s);
+    }
+  }
+  return mx;
+}
+
+// P = exp2(S*sc - m) for the 128 keys of the tile -> BF16, swizzled [128][128] shared tile (2 slabs).
+template <bool kMask>
+__device__ __forceinline__ float tile_softmax_store(uint32_t taddr, uint8_t* sP, int r, int k0, int lo, int hi,
+                                                    float sc, float m_use) {
+  float rs = 0.0f;
+#pragma unroll 1
+  for (int cc = 0; cc < 4; ++cc) {
+    uint32_t v[32];
+    tmem_ld_32x32b_x32(taddr + cc * 32, v);
+    tmem_ld_wait();
+    const int clo = lo - k0 - cc * 32, chi = hi - k0 - cc * 32;
+    float pr[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) {
+      float e = ex2f(fmaf(__uint_as_float(v[c]), sc, -m_use));
+      if (kMask && (c < clo || c > chi)) e = 0.0f;
+      pr[c] = e;
+      rs += e;
+    }
+    uint8_t* slab = sP + (cc >> 1) * (128 * 128);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint4 w;
+      w.x = pack_bf16x2(pr[8 * g + 0], pr[8 * g + 1]);
+      w.y = pack_bf16x2(pr[8 * g + 2], pr[8 * g + 3]);
+      w.z = pack_bf16x2(pr[8 * g + 4], pr[8 * g + 5]);
+      w.w = pack_bf16x2(pr[8 * g + 6], pr[8 * g + 7]);
+      *reinterpret_cast<uint4*>(slab + sw128_off(r, (cc & 1) * 4 + g)) = w;
+    }
+  }
+  return rs;
 }
 
 // first/last (exclusive) kv index that any row in [q0, q0+nq) can see
@@ -213,6 +274,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const float sc = p.scale * kLog2e;
     float m_run = -INFINITY, l_run = 0.0f;
+    int row_lo, row_hi;
+    row_limits(p, q, row_lo, row_hi);
     float o_acc[HD];
 #pragma unroll
     for (int c = 0; c < HD; ++c) o_acc[c] = 0.0f;
@@ -230,50 +293,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int off = p.Tk - p.Tq;
       const bool need_mask = (k0 + 128 > p.Tk) || (p.causal && (k0 + 127 > q0 + off)) ||
                              (p.window > 0 && (k0 < q0 + 127 + off - p.window + 1));
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_s + lane_addr + cc * 32, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          float s = __uint_as_float(v[c]);
-          if (need_mask && masked(p, q, k0 + cc * 32 + c)) s = -INFINITY;
-          mx = fmaxf(mx, s);
-        }
-      }
+      float mx, rs;
+      if (need_mask) mx = tile_row_max<true, 4>(tmem_s + lane_addr, k0, row_lo, row_hi);
+      else mx = tile_row_max<false, 4>(tmem_s + lane_addr, k0, row_lo, row_hi);
       const float m_new = fmaxf(m_run, mx * sc);
       const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
-      const float alpha = exp2f(m_run - m_use);  // m_run == -inf -> 0
-      float rs = 0.0f;
-      // pass 2: probabilities -> swizzled shared memory (A operand of P V)
-#pragma unroll 1
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_s + lane_addr + cc * 32, v);
-        tmem_ld_wait();
-        float pr[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          float s = __uint_as_float(v[c]);
-          float e = exp2f(s * sc - m_use);
-          if (need_mask && masked(p, q, k0 + cc * 32 + c)) e = 0.0f;
-          pr[c] = e;
-          rs += e;
-        }
-        uint8_t* slab = sP + (cc >> 1) * (128 * 128);
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 w;
-          w.x = pack_bf16x2(pr[8 * g + 0], pr[8 * g + 1]);
-          w.y = pack_bf16x2(pr[8 * g + 2], pr[8 * g + 3]);
-          w.z = pack_bf16x2(pr[8 * g + 4], pr[8 * g + 5]);
-          w.w = pack_bf16x2(pr[8 * g + 6], pr[8 * g + 7]);
-          *reinterpret_cast<uint4*>(slab + sw128_off(r, (cc & 1) * 4 + g)) = w;
-        }
-      }
+      const float alpha = ex2f(m_run - m_use);  // m_run == -inf -> 0
+      if (need_mask) rs = tile_softmax_store<true>(tmem_s + lane_addr, sP, r, k0, row_lo, row_hi, sc, m_use);
+      else rs = tile_softmax_store<false>(tmem_s + lane_addr, sP, r, k0, row_lo, row_hi, sc, m_use);
       l_run = l_run * alpha + rs;
       m_run = m_new;
       fence_proxy_async_smem();  // generic-proxy writes of P -> visible to the tensor core's async proxy
@@ -504,6 +531,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const int k = k0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const float sc = p.scale * kLog2e;
+    // queries that may attend to key k:  k - off <= q (causal),  q <= k - off + window - 1 (window)
+    int q_row_lo = p.causal ? k - off : 0;
+    int q_row_hi = p.Tq - 1;
+    if (p.window > 0) q_row_hi = min(q_row_hi, k - off + p.window - 1);
+    if (k >= p.Tk) q_row_lo = 0x3fffffff;  // key out of range: nothing valid
     bool ok = true;
     for (int it = 0; it < iters; ++it) {
       const int hq = hk * group + it / nchunk;
@@ -530,37 +562,43 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tc_fence_after_sync();
       const bool need_mask = (k0 + 128 > p.Tk) || (c0 + 64 > p.Tq) || (p.causal && (k0 + 127 > c0 + off)) ||
                              (p.window > 0 && (k0 < c0 + 63 + off - p.window + 1));
+      auto body = [&](auto mask_tag) {
+        constexpr bool kMask = decltype(mask_tag)::value;
 #pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tmem_st + lane_addr + cc * 32, sv);
-        tmem_ld_32x32b_x32(tmem_dpt + lane_addr + cc * 32, dv);
-        tmem_ld_wait();
-        float pr[32], dsv[32];
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t sv[32], dv[32];
+          tmem_ld_32x32b_x32(tmem_st + lane_addr + cc * 32, sv);
+          tmem_ld_32x32b_x32(tmem_dpt + lane_addr + cc * 32, dv);
+          tmem_ld_wait();
+          const int clo = q_row_lo - c0 - cc * 32, chi = q_row_hi - c0 - cc * 32;  // valid iff clo <= c <= chi
+          float pr[32], dsv[32];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int qi = cc * 32 + c;
-          float e = exp2f(__uint_as_float(sv[c]) * sc - lse_s[qi]);
-          if (need_mask && (c0 + qi >= p.Tq || masked(p, c0 + qi, k))) e = 0.0f;
-          pr[c] = e;
-          dsv[c] = e * (__uint_as_float(dv[c]) - ds_s[qi]) * p.scale;
-        }
+          for (int c = 0; c < 32; ++c) {
+            const int qi = cc * 32 + c;
+            float e = ex2f(fmaf(__uint_as_float(sv[c]), sc, -lse_s[qi]));
+            if (kMask && (c < clo || c > chi)) e = 0.0f;
+            pr[c] = e;
+            dsv[c] = e * (__uint_as_float(dv[c]) - ds_s[qi]) * p.scale;
+          }
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 w, z;
-          w.x = pack_bf16x2(pr[8 * g + 0], pr[8 * g + 1]);
-          w.y = pack_bf16x2(pr[8 * g + 2], pr[8 * g + 3]);
-          w.z = pack_bf16x2(pr[8 * g + 4], pr[8 * g + 5]);
-          w.w = pack_bf16x2(pr[8 * g + 6], pr[8 * g + 7]);
-          z.x = pack_bf16x2(dsv[8 * g + 0], dsv[8 * g + 1]);
-          z.y = pack_bf16x2(dsv[8 * g + 2], dsv[8 * g + 3]);
-          z.z = pack_bf16x2(dsv[8 * g + 4], dsv[8 * g + 5]);
-          z.w = pack_bf16x2(dsv[8 * g + 6], dsv[8 * g + 7]);
-          const uint32_t o = sw128_off(r, cc * 4 + g);
-          *reinterpret_cast<uint4*>(sPT + o) = w;
-          *reinterpret_cast<uint4*>(sDST + o) = z;
+          for (int g = 0; g < 4; ++g) {
+            uint4 w, z;
+            w.x = pack_bf16x2(pr[8 * g + 0], pr[8 * g + 1]);
+            w.y = pack_bf16x2(pr[8 * g + 2], pr[8 * g + 3]);
+            w.z = pack_bf16x2(pr[8 * g + 4], pr[8 * g + 5]);
+            w.w = pack_bf16x2(pr[8 * g + 6], pr[8 * g + 7]);
+            z.x = pack_bf16x2(dsv[8 * g + 0], dsv[8 * g + 1]);
+            z.y = pack_bf16x2(dsv[8 * g + 2], dsv[8 * g + 3]);
+            z.z = pack_bf16x2(dsv[8 * g + 4], dsv[8 * g + 5]);
+            z.w = pack_bf16x2(dsv[8 * g + 6], dsv[8 * g + 7]);
+            const uint32_t o = sw128_off(r, cc * 4 + g);
+            *reinterpret_cast<uint4*>(sPT + o) = w;
+            *reinterpret_cast<uint4*>(sDST + o) = z;
+          }
         }
-      }
+      };
+      if (need_mask) body(std::true_type{});
+      else body(std::false_type{});
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(p_full);
@@ -759,6 +797,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     if (lse_n == -INFINITY) lse_n = INFINITY;  // row that saw no key: probabilities are zero
     const float lse2 = lse_n * kLog2e;
     const float dsum = q < p.Tq ? p.dsum[sidx] : 0.0f;
+    int row_lo, row_hi;
+    row_limits(p, q, row_lo, row_hi);
+    if (q >= p.Tq) row_lo = 0x3fffffff;
     bool ok = true;
     for (int it = 0; it < iters; ++it) {
       const int k0 = (jb + it) * 64;
@@ -771,29 +812,35 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tc_fence_after_sync();
       const bool need_mask = (k0 + 64 > p.Tk) || (q0 + 128 > p.Tq) || (p.causal && (k0 + 63 > q0 + off)) ||
                              (p.window > 0 && (k0 < q0 + 127 + off - p.window + 1));
+      auto body = [&](auto mask_tag) {
+        constexpr bool kMask = decltype(mask_tag)::value;
 #pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32b_x32(tmem_s + lane_addr + cc * 32, sv);
-        tmem_ld_32x32b_x32(tmem_dp + lane_addr + cc * 32, dv);
-        tmem_ld_wait();
-        float dsv[32];
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t sv[32], dv[32];
+          tmem_ld_32x32b_x32(tmem_s + lane_addr + cc * 32, sv);
+          tmem_ld_32x32b_x32(tmem_dp + lane_addr + cc * 32, dv);
+          tmem_ld_wait();
+          const int clo = row_lo - k0 - cc * 32, chi = row_hi - k0 - cc * 32;
+          float dsv[32];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          float e = exp2f(__uint_as_float(sv[c]) * sc - lse2);
-          if (need_mask && (q >= p.Tq || masked(p, q, k0 + cc * 32 + c))) e = 0.0f;
-          dsv[c] = e * (__uint_as_float(dv[c]) - dsum) * p.scale;
-        }
+          for (int c = 0; c < 32; ++c) {
+            float e = ex2f(fmaf(__uint_as_float(sv[c]), sc, -lse2));
+            if (kMask && (c < clo || c > chi)) e = 0.0f;
+            dsv[c] = e * (__uint_as_float(dv[c]) - dsum) * p.scale;
+          }
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 z;
-          z.x = pack_bf16x2(dsv[8 * g + 0], dsv[8 * g + 1]);
-          z.y = pack_bf16x2(dsv[8 * g + 2], dsv[8 * g + 3]);
-          z.z = pack_bf16x2(dsv[8 * g + 4], dsv[8 * g + 5]);
-          z.w = pack_bf16x2(dsv[8 * g + 6], dsv[8 * g + 7]);
-          *reinterpret_cast<uint4*>(sDS + sw128_off(r, cc * 4 + g)) = z;
+          for (int g = 0; g < 4; ++g) {
+            uint4 z;
+            z.x = pack_bf16x2(dsv[8 * g + 0], dsv[8 * g + 1]);
+            z.y = pack_bf16x2(dsv[8 * g + 2], dsv[8 * g + 3]);
+            z.z = pack_bf16x2(dsv[8 * g + 4], dsv[8 * g + 5]);
+            z.w = pack_bf16x2(dsv[8 * g + 6], dsv[8 * g + 7]);
+            *reinterpret_cast<uint4*>(sDS + sw128_off(r, cc * 4 + g)) = z;
+          }
         }
-      }
+      };
+      if (need_mask) body(std::true_type{});
+      else body(std::false_type{});
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(p_full);

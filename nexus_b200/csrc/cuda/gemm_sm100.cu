@@ -2,7 +2,8 @@
 //
 //   warp 0      : TMA producer  (cp.async.bulk.tensor into 128B-swizzled shared-memory stages)
 //   warp 1      : TMEM owner + UMMA issuer (tcgen05.mma, one elected lane; accumulators in TMEM)
-//   warps 2..5  : epilogue (tcgen05.ld -> registers -> bias / GELU / dGELU / residual / accumulate -> global)
+//   warps 2..9  : epilogue (tcgen05.ld -> registers -> bias / GELU / dGELU / residual / accumulate -> global);
+//                 two warps share each TMEM lane quarter and split the tile's columns
 //
 // One CTA per SM walks over (tile, k-slice) work units; two TMEM accumulator buffers let the
 // epilogue of unit i overlap the main loop of unit i+1.  Operands may be K-major or MN-major, so
@@ -21,7 +22,7 @@ using namespace nx;
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;  // 64 bf16 = one 128-byte swizzle row
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // warp 0: TMA, warp 1: MMA, warps 2..9: epilogue (two per TMEM lane quarter)
 constexpr int kSmemBudget = 200 * 1024;
 
 template <int BN>
@@ -174,7 +175,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+      mbar_init(&tempty_bar[a], 8);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -281,8 +282,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    // ------------------------------------------------------------------ epilogue (warps 2..9)
+    const int quarter = warp & 3;         // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;     // which half of the tile's columns this warp handles
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int u = blockIdx.x; u < p.num_units; u += gridDim.x) {
@@ -298,7 +300,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const bool row_ok = row < p.m;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.n) break;  // warp-uniform
         uint32_t r[32];
@@ -311,6 +313,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
 
         if (p.split_k > 1) {
+          if (p.accumulate == 2) {
+            // split-K slices add straight into the FP32 output (vector reductions in L2)
+            float* op = reinterpret_cast<float*>(p.out) + static_cast<int64_t>(row) * p.ldo + col0;
+            if ((valid == 32) && ((p.ldo & 3) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(op + j), "f"(v[j]), "f"(v[j + 1]),
+                             "f"(v[j + 2]), "f"(v[j + 3])
+                             : "memory");
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < valid) atomicAdd(op + j, v[j]);
+            }
+            continue;
+          }
           float* wp = p.workspace + (static_cast<int64_t>(w.slice) * p.m + row) * p.n + col0;
           const bool vec = (valid == 32) && ((p.n & 3) == 0);
           store_row32_f32(wp, vec, valid, v);
@@ -461,7 +479,9 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
   if ((a->lda & 7) || (a->ldb & 7)) return -1;
   if (a->batch > 1 && ((a->stride_a & 7) || (a->stride_b & 7))) return -1;
   int split = a->split_k < 1 ? 1 : a->split_k;
-  if (split > 1 && (a->batch != 1 || a->workspace == nullptr)) return -1;
+  if (split > 1 && a->batch != 1) return -1;
+  if (split > 1 && a->accumulate == 2 && a->out_dtype != NX_F32) return -1;
+  if (split > 1 && a->accumulate != 2 && a->workspace == nullptr) return -1;
 
   int bn = a->block_n;
   if (bn != 128 && bn != 256) bn = (a->n >= 256) ? 256 : 128;

@@ -40,7 +40,7 @@ typedef struct NxGemmArgs {
   int32_t out_dtype;  // NX_BF16 or NX_F32
   int32_t bias_dtype, res_dtype;
   int32_t act;
-  int32_t accumulate;
+  int32_t accumulate;  // 0 overwrite, 1 out += v, 2 (split_k > 1, FP32 out) slices add with vector reductions
   int32_t split_k;  // 1 = none
   int32_t block_n;  // 0 = choose; else 128 or 256
   float alpha;

@@ -247,16 +247,21 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t a_fmt, uint32_t b_fmt
 // ----------------------------------------------------------------------------------------------
 // small math helpers shared by epilogues
 // ----------------------------------------------------------------------------------------------
+__device__ __forceinline__ float tanh_approx_f(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float gelu_tanh_f(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   float u = k0 * (x + k1 * x * x * x);
-  return 0.5f * x * (1.0f + tanhf(u));
+  return 0.5f * x * (1.0f + tanh_approx_f(u));
 }
 __device__ __forceinline__ float dgelu_tanh_f(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   float x2 = x * x;
   float u = k0 * (x + k1 * x * x2);
-  float t = tanhf(u);
+  float t = tanh_approx_f(u);
   float du = k0 * (1.0f + 3.0f * k1 * x2);
   return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
 }

@@ -160,6 +160,126 @@ __global__ void ce_row_kernel(LT* __restrict__ logits, const int32_t* __restrict
   for (int64_t c = vocab + threadIdx.x; c < ld; c += blockDim.x) Num<LT>::store(lr + c, 0.0f);
 }
 
+// 16-byte vector access to a logits row: 8 bf16 or 4 fp32 per load.
+template <typename LT>
+struct RowVec;
+template <>
+struct RowVec<__nv_bfloat16> {
+  static constexpr int kN = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+      v[2 * i] = __low2float(h);
+      v[2 * i + 1] = __high2float(h);
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+template <>
+struct RowVec<float> {
+  static constexpr int kN = 4;
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 q = *reinterpret_cast<const float4*>(p);
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+
+// Vectorised variant of ce_row_kernel: rows are 16-byte aligned (ld a multiple of the vector width).
+// Pass 1 streams the row from HBM (online max / sum-exp in the log2 domain); pass 2 re-reads it
+// (L2 resident: one row is ~100 KB) and writes the gradient in place.
+template <typename LT>
+__global__ void __launch_bounds__(512) ce_row_vec_kernel(LT* __restrict__ logits, const int32_t* __restrict__ tokens,
+                                  const int32_t* __restrict__ targets, float* __restrict__ row_loss, int64_t rows,
+                                  int seq_len, int vocab, int64_t ld, int ignore_index, float smoothing,
+                                  float z_loss, float grad_scale, const CeState* __restrict__ st, int write_grad) {
+  constexpr int VN = RowVec<LT>::kN;
+  constexpr float kL2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
+  __shared__ float s_scratch[32];
+  const int64_t row = blockIdx.x;
+  LT* lr = logits + row * ld;
+  const int tg = ce_target(tokens, targets, row, seq_len);
+  const bool valid = !(tg == ignore_index || (targets == nullptr && tg == -100)) && tg >= 0 && tg < vocab;
+  const int nvec = static_cast<int>(ld / VN);
+  if (!valid) {
+    if (threadIdx.x == 0) row_loss[row] = 0.0f;
+    if (write_grad) {
+      float z[VN];
+#pragma unroll
+      for (int j = 0; j < VN; ++j) z[j] = 0.0f;
+      for (int i = threadIdx.x; i < nvec; i += blockDim.x) RowVec<LT>::store(lr + i * VN, z);
+    }
+    return;
+  }
+  const int full = vocab / VN;  // vectors entirely inside the vocabulary
+  float mx = -INFINITY, se = 0.0f, sl = 0.0f;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    if (i * VN >= vocab) break;
+    float v[VN];
+    RowVec<LT>::load(lr + i * VN, v);
+    float vm = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < VN; ++j) {
+      if (i >= full && i * VN + j >= vocab) v[j] = -INFINITY;
+      vm = fmaxf(vm, v[j]);
+    }
+    if (vm > mx) {
+      se *= exp2f((mx - vm) * kL2e);
+      mx = vm;
+    }
+#pragma unroll
+    for (int j = 0; j < VN; ++j) {
+      se += exp2f((v[j] - mx) * kL2e);
+      sl += (v[j] == -INFINITY) ? 0.0f : v[j];
+    }
+  }
+  const float bmx = block_max(mx, s_scratch);
+  se = (mx == -INFINITY) ? 0.0f : se * exp2f((mx - bmx) * kL2e);
+  se = block_sum<float>(se, s_scratch);
+  sl = block_sum<float>(sl, s_scratch);
+  const float lse = bmx + log2f(se) * kLn2;
+  const float tlogit = Num<LT>::load(lr + tg);
+  const float loss = (1.0f - smoothing) * (lse - tlogit) + smoothing * (lse - sl / vocab) + z_loss * lse * lse;
+  if (threadIdx.x == 0) row_loss[row] = loss;
+  if (!write_grad) return;
+  __syncthreads();  // every thread has read lr[tg] before anyone overwrites it
+  const float k = grad_scale * st->inv_valid;
+  const float pz = (1.0f + 2.0f * z_loss * lse) * k;
+  const float sv = smoothing / vocab * k;
+  const float onehot = (1.0f - smoothing) * k;
+  const float lse2 = lse * kL2e;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    float v[VN];
+    if (i * VN < vocab) {
+      RowVec<LT>::load(lr + i * VN, v);
+#pragma unroll
+      for (int j = 0; j < VN; ++j) {
+        const int c = i * VN + j;
+        float g = exp2f(fmaf(v[j], kL2e, -lse2)) * pz - sv;
+        if (c == tg) g -= onehot;
+        v[j] = (c < vocab) ? g : 0.0f;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < VN; ++j) v[j] = 0.0f;
+    }
+    RowVec<LT>::store(lr + i * VN, v);
+  }
+}
+
 __global__ void ce_reduce_kernel(const float* __restrict__ row_loss, int64_t rows, CeState* st,
                                  float* __restrict__ loss_out, float loss_weight, int accumulate) {
   __shared__ double s_scratch[32];
@@ -363,6 +483,37 @@ __global__ void colsum_partial_kernel(const GT* __restrict__ dy, float* __restri
     partial[static_cast<int64_t>(blockIdx.y) * cols + c] = t;
   }
 }
+// BF16 fast path: each thread owns 8 adjacent columns (one 16-byte load per row); block = 32 column
+// groups x 8 row lanes = a 256-column strip of one row chunk.  Same partial layout as above.
+__global__ void colsum_partial_vec_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ partial,
+                                          int rows, int cols, int64_t ld, int rows_per_chunk) {
+  __shared__ float s[8][32][9];
+  const int c0 = (blockIdx.x * 32 + threadIdx.x) * 8;
+  const int r_begin = blockIdx.y * rows_per_chunk, r_end = min(rows, r_begin + rows_per_chunk);
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+  if (c0 < cols) {
+    for (int r = r_begin + threadIdx.y; r < r_end; r += 8) {
+      float v[8];
+      RowVec<__nv_bfloat16>::load(dy + static_cast<int64_t>(r) * ld + c0, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s[threadIdx.y][threadIdx.x][j] = acc[j];
+  __syncthreads();
+  if (threadIdx.y == 0 && c0 < cols) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float t = 0.0f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) t += s[k][threadIdx.x][j];
+      partial[static_cast<int64_t>(blockIdx.y) * cols + c0 + j] = t;
+    }
+  }
+}
 __global__ void colsum_final_kernel(const float* __restrict__ partial, float* __restrict__ out, int cols, int chunks,
                                     int accumulate) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -438,7 +589,12 @@ extern "C" int nx_cross_entropy_shifted(void* logits, int logits_dtype, const in
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CeState* cs = static_cast<CeState*>(ce_state);
   ce_count_kernel<<<1, 1024, 0, st>>>(tokens, targets, rows, seq_len, vocab, ignore_index, cs);
-  if (logits_dtype == NX_F32)
+  const bool aligned = (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
+  if (logits_dtype == NX_F32 && aligned && (ld % 4) == 0)
+    ce_row_vec_kernel<float><<<static_cast<unsigned>(rows), 512, 0, st>>>((float*)logits, tokens, targets, row_loss, rows, seq_len, vocab, ld, ignore_index, smoothing, z_loss, grad_scale, cs, write_grad);
+  else if (logits_dtype == NX_BF16 && aligned && (ld % 8) == 0)
+    ce_row_vec_kernel<__nv_bfloat16><<<static_cast<unsigned>(rows), 512, 0, st>>>((__nv_bfloat16*)logits, tokens, targets, row_loss, rows, seq_len, vocab, ld, ignore_index, smoothing, z_loss, grad_scale, cs, write_grad);
+  else if (logits_dtype == NX_F32)
     ce_row_kernel<float><<<static_cast<unsigned>(rows), 512, 0, st>>>((float*)logits, tokens, targets, row_loss, rows, seq_len, vocab, ld, ignore_index, smoothing, z_loss, grad_scale, cs, write_grad);
   else if (logits_dtype == NX_BF16)
     ce_row_kernel<__nv_bfloat16><<<static_cast<unsigned>(rows), 512, 0, st>>>((__nv_bfloat16*)logits, tokens, targets, row_loss, rows, seq_len, vocab, ld, ignore_index, smoothing, z_loss, grad_scale, cs, write_grad);
@@ -532,7 +688,10 @@ extern "C" int nx_colsum(const void* dy, int dtype, float* out, float* scratch, 
   const int chunks = std::max(1, std::min(64, (rows + 255) / 256));
   const int rpc = (rows + chunks - 1) / chunks;
   dim3 grid((cols + 31) / 32, chunks), block(32, 8);
-  if (dtype == NX_F32) colsum_partial_kernel<float><<<grid, block, 0, st>>>((const float*)dy, scratch, rows, cols, ld, rpc);
+  if (dtype == NX_BF16 && (cols % 8) == 0 && (ld % 8) == 0 && (reinterpret_cast<uintptr_t>(dy) & 15) == 0) {
+    dim3 vgrid((cols + 255) / 256, chunks);
+    colsum_partial_vec_kernel<<<vgrid, block, 0, st>>>((const __nv_bfloat16*)dy, scratch, rows, cols, ld, rpc);
+  } else if (dtype == NX_F32) colsum_partial_kernel<float><<<grid, block, 0, st>>>((const float*)dy, scratch, rows, cols, ld, rpc);
   else if (dtype == NX_BF16) colsum_partial_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)dy, scratch, rows, cols, ld, rpc);
   else return -1;
   colsum_final_kernel<<<(cols + 255) / 256, 256, 0, st>>>(scratch, out, cols, chunks, accumulate);

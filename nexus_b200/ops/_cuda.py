@@ -143,7 +143,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          aux_in: Optional[torch.Tensor] = None, aux_out: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
          out_dtype: Optional[torch.dtype] = None, accumulate: bool = False, alpha: float = 1.0,
-         split_k: int = 1, block_n: int = 0, max_ctas: int = 0) -> torch.Tensor:
+         split_k: int = 1, block_n: int = 0, max_ctas: int = 0, deterministic: bool = False) -> torch.Tensor:
     """``out = epilogue(alpha * A @ B^T)`` with A logical [M, K], B logical [N, K].
 
     ``a_mn`` / ``b_mn``: the operand is stored transposed ([K, M] / [K, N], i.e. reduction-major).
@@ -197,7 +197,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         split_k = min(split_k, kb_total)
         per = (kb_total + split_k - 1) // split_k
         split_k = (kb_total + per - 1) // per
-    if split_k > 1 and not batched:
+    if split_k > 1 and not batched and accumulate and out.dtype == torch.float32 and not deterministic:
+        # slices add into the FP32 output with vector reductions (summation order not fixed)
+        g.split_k = split_k
+        g.accumulate = 2
+        _check(L.nx_gemm(C.byref(g), _stream()), "nx_gemm")
+    elif split_k > 1 and not batched:
         ws = scratch(split_k * m * n * 4, "gemm_splitk", a.device)
         g.workspace = ws.data_ptr()
         g.split_k = split_k
