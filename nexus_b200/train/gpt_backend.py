@@ -28,6 +28,8 @@ class GptLmBackend(LmBackend):
     def __init__(self, config: LmConfig, micro_batch: int, seq_len: int, device="cuda", seed: int = 1234,
                  deterministic: bool = False):
         self.dev = torch.device(device)
+        if self.dev.index is None:
+            self.dev = torch.device("cuda", torch.cuda.current_device())
         torch.cuda.set_device(self.dev)
         self.model = GptModel(config, device=self.dev, seed=seed)
         self.model.deterministic_embedding = deterministic

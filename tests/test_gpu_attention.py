@@ -1,0 +1,63 @@
+"""tcgen05 flash attention forward/backward vs an FP32 PyTorch reference (causal, window, GQA,
+Tq != Tk, packed QKV, head_dim 64 and 128, ragged lengths)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(q, k, v, causal, window, scale):
+    B, Tq, H, D = q.shape
+    Tk, Hkv = k.shape[1], k.shape[2]
+    qf, kf, vf = [t.permute(0, 2, 1, 3) for t in (q, k, v)]
+    if Hkv != H:
+        kf = kf.repeat_interleave(H // Hkv, 1)
+        vf = vf.repeat_interleave(H // Hkv, 1)
+    s = qf @ kf.transpose(-1, -2) * scale
+    qi = torch.arange(Tq, device=q.device)[:, None] + (Tk - Tq)
+    ki = torch.arange(Tk, device=q.device)[None]
+    mask = torch.zeros(Tq, Tk, dtype=torch.bool, device=q.device)
+    if causal:
+        mask |= ki > qi
+    if window > 0:
+        mask |= ki < qi - window + 1
+    s = s.masked_fill(mask, float("-inf"))
+    return (torch.softmax(s, -1) @ vf).permute(0, 2, 1, 3), torch.logsumexp(s, -1)
+
+
+CASES = [
+    (1, 128, 128, 1, 1, 64, False, 0, False),
+    (2, 256, 256, 3, 3, 64, True, 0, False),
+    (2, 1024, 1024, 4, 4, 64, True, 0, True),
+    (1, 200, 200, 2, 2, 64, True, 0, False),
+    (1, 100, 300, 4, 2, 64, True, 0, False),
+    (1, 512, 512, 2, 2, 64, True, 100, False),
+    (1, 256, 256, 2, 1, 128, True, 0, False),
+    (1, 384, 384, 2, 2, 128, False, 0, False),
+]
+
+
+@pytest.mark.parametrize("B,Tq,Tk,H,Hkv,D,causal,window,packed", CASES)
+def test_attention_fwd_bwd(B, Tq, Tk, H, Hkv, D, causal, window, packed):
+    from nexus_b200.ops import _cuda as K
+    torch.manual_seed(0)
+    dev = "cuda"
+    if packed:
+        qkv = torch.randn(B, Tq, 3, H, D, device=dev).bfloat16()
+        q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
+    else:
+        q = torch.randn(B, Tq, H, D, device=dev).bfloat16()
+        k = torch.randn(B, Tk, Hkv, D, device=dev).bfloat16()
+        v = torch.randn(B, Tk, Hkv, D, device=dev).bfloat16()
+    o, lse = K.attention_fwd(q, k, v, causal=causal, window=window)
+    K.check_status()
+    qr, kr, vr = [t.float().detach().requires_grad_(True) for t in (q, k, v)]
+    oref, lref = _ref(qr, kr, vr, causal, window, D ** -0.5)
+    assert (o.float() - oref).abs().max() < 2e-2
+    assert (lse - lref).abs().max() < 2e-2
+    do = torch.randn_like(o)
+    dq, dk, dv = K.attention_bwd(q, k, v, o, lse, do, causal=causal, window=window)
+    K.check_status()
+    oref.backward(do.float())
+    for got, want in ((dq, qr.grad), (dk, kr.grad), (dv, vr.grad)):
+        assert (got.float() - want).abs().max() <= 3e-2 * want.abs().max()

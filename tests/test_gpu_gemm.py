@@ -1,0 +1,112 @@
+"""tcgen05 GEMM vs an FP32 PyTorch reference: every operand layout, both tile widths, tails,
+fused epilogues, split-K (deterministic and reduction-based) and the strided batch."""
+import itertools
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _K():
+    from nexus_b200.ops import _cuda as K
+    return K
+
+
+def _operands(M, N, Kd, a_mn, b_mn):
+    A = torch.randn(M, Kd, device="cuda").bfloat16()
+    B = torch.randn(N, Kd, device="cuda").bfloat16()
+    a = A.t().contiguous() if a_mn else A
+    b = B.t().contiguous() if b_mn else B
+    return A, B, a, b
+
+
+@pytest.mark.parametrize("a_mn,b_mn", list(itertools.product((False, True), repeat=2)))
+@pytest.mark.parametrize("bn", (128, 256))
+@pytest.mark.parametrize("shape", ((128, 128, 64), (256, 512, 320), (304, 200, 136)))
+def test_gemm_layouts(a_mn, b_mn, bn, shape):
+    K = _K()
+    torch.manual_seed(1)
+    M, N, Kd = shape
+    A, B, a, b = _operands(M, N, Kd, a_mn, b_mn)
+    out = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, block_n=bn)
+    K.check_status()
+    ref = A.float() @ B.float().t()
+    assert (out.float() - ref).abs().max() <= 1.5e-2 * ref.abs().max()
+
+
+def test_gemm_bias_gelu_aux():
+    K = _K()
+    torch.manual_seed(2)
+    M, N, Kd = 1024, 3072, 768
+    A, B, a, b = _operands(M, N, Kd, False, False)
+    bias = torch.randn(N, device="cuda")
+    aux = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    out = K.gemm(a, b, bias=bias, act="gelu", aux_out=aux)
+    K.check_status()
+    pre = A.float() @ B.float().t() + bias
+    ref = torch.nn.functional.gelu(pre, approximate="tanh")
+    assert (aux.float() - pre).abs().max() <= 1.5e-2 * pre.abs().max()
+    assert (out.float() - ref).abs().max() <= 1.5e-2 * ref.abs().max()
+
+
+def test_gemm_dgelu_residual_accumulate():
+    K = _K()
+    torch.manual_seed(3)
+    M, N, Kd = 512, 768, 1024
+    A, B, a, b = _operands(M, N, Kd, False, True)
+    pre = torch.randn(M, N, device="cuda").bfloat16()
+    out = K.gemm(a, b, b_mn=True, act="dgelu", aux_in=pre)
+    K.check_status()
+    x = pre.float().requires_grad_(True)
+    torch.nn.functional.gelu(x, approximate="tanh").sum().backward()
+    ref = (A.float() @ B.float().t()) * x.grad
+    assert (out.float() - ref).abs().max() <= 2e-2 * ref.abs().max()
+    res = torch.randn(M, N, device="cuda")
+    bias = torch.randn(N, device="cuda").bfloat16()
+    out = K.gemm(a, b, b_mn=True, bias=bias, residual=res, out_dtype=torch.float32)
+    ref = A.float() @ B.float().t() + bias.float() + res
+    assert (out - ref).abs().max() <= 1e-3 * ref.abs().max()
+    acc = torch.randn(M, N, device="cuda")
+    ref = acc + A.float() @ B.float().t()
+    K.gemm(a, b, b_mn=True, out=acc, accumulate=True)
+    K.check_status()
+    assert (acc - ref).abs().max() <= 1e-3 * ref.abs().max()
+
+
+@pytest.mark.parametrize("deterministic", (True, False))
+def test_gemm_split_k(deterministic):
+    K = _K()
+    torch.manual_seed(4)
+    M, N, Kd = 768, 768, 4096
+    A, B, a, b = _operands(M, N, Kd, True, True)
+    acc0 = torch.randn(M, N, device="cuda")
+    ref = acc0 + A.float() @ B.float().t()
+    outs = []
+    for _ in range(2):
+        acc = acc0.clone()
+        K.gemm(a, b, a_mn=True, b_mn=True, out=acc, accumulate=True, split_k=4, deterministic=deterministic)
+        K.check_status()
+        assert (acc - ref).abs().max() <= 1e-3 * ref.abs().max()
+        outs.append(acc)
+    if deterministic:
+        assert torch.equal(outs[0], outs[1])
+
+
+def test_gemm_batched():
+    K = _K()
+    torch.manual_seed(5)
+    A = torch.randn(5, 200, 72, device="cuda").bfloat16()
+    B = torch.randn(5, 136, 72, device="cuda").bfloat16()
+    out = K.gemm(A, B)
+    K.check_status()
+    ref = torch.einsum("bmk,bnk->bmn", A.float(), B.float())
+    assert (out.float() - ref).abs().max() <= 1.5e-2 * ref.abs().max()
+
+
+def test_gemm_rejects_unaligned_pitch():
+    K = _K()
+    a = torch.randn(64, 36, device="cuda").bfloat16()  # pitch 36: not a multiple of 8 elements
+    b = torch.randn(64, 36, device="cuda").bfloat16()
+    with pytest.raises(RuntimeError):
+        K.gemm(a, b)
