@@ -84,6 +84,26 @@ size_t nx_colsum_scratch_bytes(int rows, int cols);
 int nx_colsum(const void* dy, int dtype, float* out, float* scratch, int rows, int cols, int64_t ld, int accumulate,
               nx_stream_t stream);
 
+// ---- column sums for callers that cannot allocate -----------------------------------------------
+// (This entry point has no counterpart in the reference; it exists for embedders of this library.)
+//
+// Same result as nx_colsum, but the partial-sum scratch is a fixed 2 MiB array inside the library
+// image instead of a caller buffer, and the call performs no device allocation of any kind.  It is
+// meant for hosts that must not call cudaMalloc while running: a server that handed all free HBM
+// to its own arena (a KV cache, say) at start-up and has nothing left for the driver to give, or a
+// latency-critical loop that cannot afford the device-wide synchronisation an allocation implies.
+//
+//   * cols <= nx_colsum_static_max_cols() (8192); larger inputs return -5 with a message on stderr.
+//   * The first call on each device looks the array's device address up (cudaGetSymbolAddress, with
+//     that device current) and caches it; make that first call during set-up, before any stream
+//     capture begins.  Every GPU that loads the library keeps the 2 MiB until the process exits.
+//   * All calls on a device share the one array and it keeps the previous call's partials.  Each
+//     call overwrites every entry it later reads, so nothing needs clearing, but two calls that
+//     overlap on the GPU (different streams) race on it: keep them on one stream or order them.
+int nx_colsum_static_max_cols(void);
+int nx_colsum_static(const void* dy, int dtype, float* out, int rows, int cols, int64_t ld, int accumulate,
+                     nx_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -7,6 +7,7 @@
 #include "nx_api_kernels.h"
 
 #include <algorithm>
+#include <cstdio>
 
 namespace {
 using namespace nx;
@@ -694,6 +695,75 @@ extern "C" int nx_colsum(const void* dy, int dtype, float* out, float* scratch, 
   } else if (dtype == NX_F32) colsum_partial_kernel<float><<<grid, block, 0, st>>>((const float*)dy, scratch, rows, cols, ld, rpc);
   else if (dtype == NX_BF16) colsum_partial_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)dy, scratch, rows, cols, ld, rpc);
   else return -1;
+  colsum_final_kernel<<<(cols + 255) / 256, 256, 0, st>>>(scratch, out, cols, chunks, accumulate);
+  return launch_status();
+}
+
+// ================================================================================================
+// Column sums without caller-provided scratch (see nx_colsum_static in nx_api_kernels.h).
+// ================================================================================================
+namespace {
+
+constexpr int kStaticColsumMaxCols = 8192;
+constexpr int kStaticColsumMaxChunks = 64;
+
+// Partial sums [chunk][col] of one call.  Lives in the module image: every GPU that loads this
+// library holds these 2 MiB from load until the process exits.
+static __device__ __align__(256) float g_colsum_static_scratch[kStaticColsumMaxChunks * kStaticColsumMaxCols];
+
+constexpr int kMaxDevices = 64;
+float* g_colsum_static_ptr[kMaxDevices] = {};  // device address of the array, per device ordinal
+
+// In host code `g_colsum_static_scratch` is only a handle for the symbol, not a device address, so
+// the address a kernel can use is asked for once per device (with that device current).
+int colsum_static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -2;
+  if (g_colsum_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_colsum_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      fprintf(stderr, "nx_colsum_static: cudaGetSymbolAddress failed on device %d: %s\n", dev,
+              cudaGetErrorString(e));
+      return -2;
+    }
+    g_colsum_static_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_colsum_static_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int nx_colsum_static_max_cols(void) { return kStaticColsumMaxCols; }
+
+extern "C" int nx_colsum_static(const void* dy, int dtype, float* out, int rows, int cols, int64_t ld, int accumulate,
+                                nx_stream_t stream) {
+  if (dy == nullptr || out == nullptr || rows <= 0 || cols <= 0 || ld < cols) return -1;
+  if (cols > kStaticColsumMaxCols) {
+    fprintf(stderr, "nx_colsum_static: %d columns exceed the built-in scratch (max %d); use nx_colsum with "
+                    "caller-provided scratch instead\n", cols, kStaticColsumMaxCols);
+    return -5;
+  }
+  float* scratch = nullptr;
+  const int rc = colsum_static_scratch_for_current_device(&scratch);
+  if (rc != 0) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int chunks = std::max(1, std::min(kStaticColsumMaxChunks, (rows + 255) / 256));
+  const int rpc = (rows + chunks - 1) / chunks;
+  dim3 grid((cols + 31) / 32, chunks), block(32, 8);
+  // every (chunk, column) partial that the final pass reads is written by the first pass of this
+  // same call, so nothing in the shared array has to be cleared between calls
+  if (dtype == NX_BF16 && (cols % 8) == 0 && (ld % 8) == 0 && (reinterpret_cast<uintptr_t>(dy) & 15) == 0) {
+    dim3 vgrid((cols + 255) / 256, chunks);
+    colsum_partial_vec_kernel<<<vgrid, block, 0, st>>>((const __nv_bfloat16*)dy, scratch, rows, cols, ld, rpc);
+  } else if (dtype == NX_F32) {
+    colsum_partial_kernel<float><<<grid, block, 0, st>>>((const float*)dy, scratch, rows, cols, ld, rpc);
+  } else if (dtype == NX_BF16) {
+    colsum_partial_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)dy, scratch, rows, cols, ld, rpc);
+  } else {
+    return -1;
+  }
   colsum_final_kernel<<<(cols + 255) / 256, 256, 0, st>>>(scratch, out, cols, chunks, accumulate);
   return launch_status();
 }
