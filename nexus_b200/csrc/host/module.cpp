@@ -1,0 +1,20 @@
+// `nexus_b200._native`: the host-side native runtime (archive codecs, checksums, allocator and
+// planner, profiler, CPU oracles, environments).  Each translation unit registers its own bindings.
+#include <pybind11/pybind11.h>
+
+namespace py = pybind11;
+
+void bind_nxs2(py::module_& m);
+void bind_nxs3(py::module_& m);
+void bind_runtime(py::module_& m);
+void bind_cpu_kernels(py::module_& m);
+void bind_envs(py::module_& m);
+
+PYBIND11_MODULE(_native, m) {
+  m.doc() = "nexus_b200 native host runtime";
+  bind_nxs2(m);
+  bind_nxs3(m);
+  bind_runtime(m);
+  bind_cpu_kernels(m);
+  bind_envs(m);
+}
