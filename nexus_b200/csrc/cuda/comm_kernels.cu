@@ -1,0 +1,340 @@
+// Kernels that fuse computation with NVLink / NVSwitch communication through peer-mapped
+// (symmetric) memory: every rank passes a table of device pointers, one per rank, to buffers of
+// identical layout; loads and stores through a peer's pointer travel over NVLink.
+//
+//   * cross-GPU barrier and flag signalling with BOUNDED waits (a wait that runs out records
+//     kStatusTimeoutPeer in the status word and the kernel returns; nothing spins for ever);
+//   * gradient reduce-scatter by owner-pull: the owner of a shard sums the shard over all ranks in a
+//     fixed order (deterministic), fused with the FP64 square sum for the global norm;
+//   * global-norm exchange (each rank publishes its square sum into every peer's slot) fused with
+//     the clip coefficient / bias-correction computation of the optimizer state;
+//   * AdamW on the owned shard fused with the all-gather of the updated BF16 weights: the narrow
+//     copy is stored straight into every rank's parameter buffer;
+//   * MoE dispatch (rows stored into the expert owner's capacity buffer) and combine (rows pulled
+//     back from the owners, gate-weighted) for expert parallelism;
+//   * vocabulary-parallel cross-entropy statistics exchange.
+//
+// No kernel here uses TMA multicast or multimem; plain peer loads/stores only, so a rank that
+// exits between steps cannot fault its peers.
+// Replaces (reference, CPU only): FsdpEngine::launch_reduce + step (src/dist/fsdp.cpp:387-568),
+// MoeExpertParallel (src/dist/moe_ep.cpp:45-90), vocab-parallel CE (src/dist/parallel_lm.cpp:611-665).
+#include "common.cuh"
+#include "nx_api_comm.h"
+#include "sm100_ptx.cuh"
+
+namespace {
+using namespace nx;
+
+constexpr uint64_t kPeerWaitNs = 2000000000ull;
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Thread t < n: tell rank t that `rank` reached `epoch`, then wait until rank t told us the same.
+// flags.ptr[q] is rank q's flag array (n ints), as mapped into this process.
+__device__ __forceinline__ bool signal_and_wait(const NxPeerTable& flags, int rank, int n, int epoch, int* status) {
+  const int t = threadIdx.x;
+  bool ok = true;
+  if (t < n) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<int*>(flags.ptr[t]) + rank, epoch);
+    const int* mine = reinterpret_cast<const int*>(flags.ptr[rank]) + t;
+    const uint64_t t0 = globaltimer_ns();
+    while (ld_acquire_sys(mine) < epoch) {
+      if (globaltimer_ns() - t0 > kPeerWaitNs) {
+        atomicCAS(status, 0, kStatusTimeoutPeer);
+        ok = false;
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  return ok;
+}
+
+__global__ void barrier_kernel(NxPeerTable flags, int rank, int n, int epoch, int* status) {
+  signal_and_wait(flags, rank, n, epoch, status);
+}
+
+// ------------------------------------------------------------------------------------------------
+// owner-pull reduce-scatter + square sum
+// ------------------------------------------------------------------------------------------------
+constexpr int kReduceChunk = 16384;  // elements per block
+
+__global__ void __launch_bounds__(256)
+reduce_shard_kernel(NxPeerTable grads, int n, int64_t shard_off, int64_t count, float scale,
+                    float* __restrict__ out, double* __restrict__ partial) {
+  __shared__ double s_scratch[32];
+  const int64_t begin = static_cast<int64_t>(blockIdx.x) * kReduceChunk;
+  const int64_t end = min(count, begin + kReduceChunk);
+  double sq = 0.0;
+  // shard_off and every chunk start are multiples of 4 elements: 16-byte vector loads
+  for (int64_t i = begin + threadIdx.x * 4; i < end; i += blockDim.x * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i + 4 <= end) {
+#pragma unroll 1
+      for (int p = 0; p < n; ++p) {
+        const float4 v = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.ptr[p]) + shard_off + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+      *reinterpret_cast<float4*>(out + i) = acc;
+      sq += static_cast<double>(acc.x) * acc.x + static_cast<double>(acc.y) * acc.y +
+            static_cast<double>(acc.z) * acc.z + static_cast<double>(acc.w) * acc.w;
+    } else {
+      for (int64_t j = i; j < end; ++j) {
+        float a = 0.f;
+        for (int p = 0; p < n; ++p) a += reinterpret_cast<const float*>(grads.ptr[p])[shard_off + j];
+        a *= scale;
+        out[j] = a;
+        sq += static_cast<double>(a) * a;
+      }
+    }
+  }
+  sq = block_sum<double>(sq, s_scratch);
+  if (threadIdx.x == 0) partial[blockIdx.x] = sq;
+}
+
+// One block.  Local square sum -> every peer's slot -> wait for all -> global norm -> optimizer state.
+__global__ void norm_exchange_kernel(const double* __restrict__ partial, int nparts, NxPeerTable slots,
+                                     NxPeerTable flags, int rank, int n, int epoch, NxOptState* st, int* status) {
+  __shared__ double s_scratch[32];
+  __shared__ int s_ok;
+  double acc = 0.0;
+  for (int i = threadIdx.x; i < nparts; i += blockDim.x) acc += partial[i];
+  acc = block_sum<double>(acc, s_scratch);
+  if (threadIdx.x == 0) {
+    st->local_sq = acc;
+    s_ok = 1;
+  }
+  if (threadIdx.x < n) reinterpret_cast<double*>(slots.ptr[threadIdx.x])[rank] = acc;
+  __syncthreads();
+  const bool ok = signal_and_wait(flags, rank, n, epoch, status);
+  if (!ok) s_ok = 0;
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  if (!s_ok) {
+    st->found_inf = 1;  // no update on a step whose exchange failed
+    return;
+  }
+  double total = 0.0;
+  const volatile double* mine = reinterpret_cast<const volatile double*>(slots.ptr[rank]);
+  for (int q = 0; q < n; ++q) total += mine[q];
+  const double inv_scale = st->loss_scale > 0.0f ? 1.0 / st->loss_scale : 1.0;
+  const double norm = sqrt(total) * inv_scale;
+  const bool finite = isfinite(norm);
+  st->grad_norm = static_cast<float>(norm);
+  st->found_inf = finite ? 0 : 1;
+  double coef = 1.0;
+  if (st->max_grad_norm > 0.0f) coef = fmin(1.0, static_cast<double>(st->max_grad_norm) / (norm + 1e-6));
+  st->clip_coef = static_cast<float>(coef * inv_scale);
+  if (finite) {
+    st->step += 1;
+    const double t = static_cast<double>(st->step);
+    st->inv_bias1 = static_cast<float>(1.0 / (1.0 - pow(static_cast<double>(st->beta1), t)));
+    st->inv_bias2 = static_cast<float>(1.0 / (1.0 - pow(static_cast<double>(st->beta2), t)));
+  } else {
+    st->skipped += 1;
+  }
+}
+
+// AdamW on the owned shard; chunk descriptors use GLOBAL element offsets clipped to the shard, the
+// FP32 state arrays (master/grad/m/v) are shard-local (index = global - shard_off); the BF16 result
+// goes to every rank's full shadow buffer at the global index.  Same op order as adamw_kernel.
+__global__ void __launch_bounds__(256)
+adamw_shard_allgather_kernel(float* __restrict__ master, const float* __restrict__ grad, float* __restrict__ m,
+                             float* __restrict__ v, NxPeerTable shadows, int n, int64_t shard_off,
+                             const NxAdamChunk* __restrict__ chunks, const NxOptState* __restrict__ st) {
+  if (st->found_inf) return;
+  const NxAdamChunk ch = chunks[blockIdx.x];
+  const float lr = __fmul_rn(st->lr, ch.lr_scale);
+  const float wd = __fmul_rn(st->weight_decay, ch.wd_scale);
+  const float b1 = st->beta1, b2 = st->beta2, omb1 = __fsub_rn(1.0f, b1), omb2 = __fsub_rn(1.0f, b2);
+  const float i1 = st->inv_bias1, i2 = st->inv_bias2, eps = st->eps, clip = st->clip_coef;
+  const float lrwd = __fmul_rn(lr, wd);
+  for (int64_t gi = ch.offset + threadIdx.x; gi < ch.offset + ch.count; gi += blockDim.x) {
+    const int64_t i = gi - shard_off;
+    const float g = __fmul_rn(grad[i], clip);
+    float p = master[i];
+    p = __fsub_rn(p, __fmul_rn(lrwd, p));
+    const float mi = __fadd_rn(__fmul_rn(b1, m[i]), __fmul_rn(omb1, g));
+    const float vi = __fadd_rn(__fmul_rn(b2, v[i]), __fmul_rn(omb2, __fmul_rn(g, g)));
+    p = __fsub_rn(p, __fdiv_rn(__fmul_rn(lr, __fmul_rn(mi, i1)), __fadd_rn(__fsqrt_rn(__fmul_rn(vi, i2)), eps)));
+    master[i] = p;
+    m[i] = mi;
+    v[i] = vi;
+    const __nv_bfloat16 lp = __float2bfloat16_rn(p);
+#pragma unroll 1
+    for (int q = 0; q < n; ++q) reinterpret_cast<__nv_bfloat16*>(shadows.ptr[q])[gi] = lp;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// MoE expert-parallel dispatch / combine over peer memory
+// ------------------------------------------------------------------------------------------------
+// Row r of the permuted token matrix belongs to global expert e = expert_of[r] at slot slot_of[r]
+// (< capacity) of that expert; it is stored into the owner's buffer [local_experts, capacity, d].
+__global__ void moe_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ token_of,
+                                    const int32_t* __restrict__ expert_of, const int32_t* __restrict__ slot_of,
+                                    NxPeerTable bufs, int rows, int d, int local_experts, int capacity,
+                                    int src_rank, int n_ranks) {
+  const int vec = d >> 3;  // 16-byte vectors
+  for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    const int e = expert_of[r];
+    const int owner = e / local_experts, le = e % local_experts;
+    // each source rank owns a disjoint slice of the capacity: slot indices are global per expert
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(bufs.ptr[owner]) +
+                         (static_cast<int64_t>(le) * capacity + slot_of[r]) * d;
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(token_of[r]) * d);
+    for (int i = threadIdx.x; i < vec; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = src[i];
+  }
+  (void)src_rank;
+  (void)n_ranks;
+}
+
+// y[t] = sum_j gate[t,j] * out_buf[owner(e_tj)][le][slot_tj]   (slot < 0: dropped assignment)
+__global__ void moe_combine_kernel(NxPeerTable bufs, const int32_t* __restrict__ expert, const int32_t* __restrict__ slot,
+                                   const float* __restrict__ gate, __nv_bfloat16* __restrict__ y, int tokens, int top_k,
+                                   int d, int local_experts, int capacity) {
+  for (int t = blockIdx.x; t < tokens; t += gridDim.x) {
+    for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+      for (int k = 0; k < top_k; ++k) {
+        const int s = slot[t * top_k + k];
+        if (s < 0) continue;
+        const int e = expert[t * top_k + k];
+        const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(bufs.ptr[e / local_experts]) +
+                                   (static_cast<int64_t>(e % local_experts) * capacity + s) * d + c;
+        const uint4 q = *reinterpret_cast<const uint4*>(src);
+        const float g = gate[t * top_k + k];
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float lo, hi;
+          unpack_bf16x2(w[j], lo, hi);
+          acc[2 * j] += g * lo;
+          acc[2 * j + 1] += g * hi;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(y + static_cast<int64_t>(t) * d + c) = o;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// vocabulary-parallel cross-entropy: exchange of per-row statistics
+// ------------------------------------------------------------------------------------------------
+// stats[rank] holds [rows][3] = (local max, local sum-exp relative to the local max, target logit or 0).
+// Every rank publishes its rows into every peer's table, waits, then merges in rank order:
+//   gmax = max_q max_q;  sumexp = sum_q se_q * exp(max_q - gmax);  tlogit = sum_q t_q.
+__global__ void vocab_ce_exchange_kernel(const float* __restrict__ local_stats, NxPeerTable tables, NxPeerTable flags,
+                                         int rank, int n, int rows, int epoch, float* __restrict__ merged, int* status) {
+  __shared__ int s_ok;
+  for (int i = threadIdx.x; i < rows * 3; i += blockDim.x) {
+    const float v = local_stats[i];
+    for (int q = 0; q < n; ++q) reinterpret_cast<float*>(tables.ptr[q])[static_cast<int64_t>(rank) * rows * 3 + i] = v;
+  }
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  const bool ok = signal_and_wait(flags, rank, n, epoch, status);
+  if (!ok) s_ok = 0;
+  __syncthreads();
+  if (!s_ok) return;
+  const volatile float* mine = reinterpret_cast<const volatile float*>(tables.ptr[rank]);
+  for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+    float gmax = -INFINITY;
+    for (int q = 0; q < n; ++q) gmax = fmaxf(gmax, mine[(static_cast<int64_t>(q) * rows + r) * 3]);
+    float se = 0.0f, tl = 0.0f;
+    for (int q = 0; q < n; ++q) {
+      const int64_t b = (static_cast<int64_t>(q) * rows + r) * 3;
+      se += mine[b + 1] * __expf(mine[b] - gmax);
+      tl += mine[b + 2];
+    }
+    merged[r * 3] = gmax;
+    merged[r * 3 + 1] = se;
+    merged[r * 3 + 2] = tl;
+  }
+}
+
+}  // namespace
+
+// ================================================================================================
+extern "C" int nx_comm_barrier(const NxPeerTable* flags, int rank, int n, int epoch, int* status, nx_stream_t stream) {
+  if (flags == nullptr || n < 1 || n > NX_MAX_PEERS || rank < 0 || rank >= n || status == nullptr) return -1;
+  barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(*flags, rank, n, epoch, status);
+  return launch_status();
+}
+
+extern "C" int64_t nx_comm_reduce_partials(int64_t count) { return (count + kReduceChunk - 1) / kReduceChunk; }
+
+extern "C" int nx_comm_reduce_shard(const NxPeerTable* grads, int n, int64_t shard_off, int64_t count, float scale,
+                                    float* out, double* partial, nx_stream_t stream) {
+  if (grads == nullptr || n < 1 || n > NX_MAX_PEERS || count <= 0 || (shard_off & 3)) return -1;
+  const int blocks = static_cast<int>((count + kReduceChunk - 1) / kReduceChunk);
+  reduce_shard_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(*grads, n, shard_off, count, scale, out,
+                                                                              partial);
+  return launch_status();
+}
+
+extern "C" int nx_comm_norm_exchange(const double* partial, int nparts, const NxPeerTable* slots,
+                                     const NxPeerTable* flags, int rank, int n, int epoch, NxOptState* state,
+                                     int* status, nx_stream_t stream) {
+  if (slots == nullptr || flags == nullptr || n < 1 || n > NX_MAX_PEERS || status == nullptr) return -1;
+  norm_exchange_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(partial, nparts, *slots, *flags, rank, n, epoch,
+                                                                         state, status);
+  return launch_status();
+}
+
+extern "C" int nx_comm_adamw_allgather(float* master, const float* grad, float* m, float* v,
+                                       const NxPeerTable* shadows, int n, int64_t shard_off,
+                                       const NxAdamChunk* chunks, int nchunks, const NxOptState* state,
+                                       nx_stream_t stream) {
+  if (shadows == nullptr || n < 1 || n > NX_MAX_PEERS || nchunks <= 0) return -1;
+  adamw_shard_allgather_kernel<<<nchunks, 256, 0, static_cast<cudaStream_t>(stream)>>>(master, grad, m, v, *shadows, n,
+                                                                                       shard_off, chunks, state);
+  return launch_status();
+}
+
+extern "C" int nx_moe_dispatch(const void* x, const int32_t* token_of, const int32_t* expert_of, const int32_t* slot_of,
+                               const NxPeerTable* bufs, int rows, int d, int local_experts, int capacity, int src_rank,
+                               int n_ranks, nx_stream_t stream) {
+  if (bufs == nullptr || rows < 0 || d <= 0 || (d & 7)) return -1;
+  if (rows == 0) return 0;
+  const int blocks = rows < 148 * 8 ? rows : 148 * 8;
+  moe_dispatch_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), token_of, expert_of, slot_of, *bufs, rows, d, local_experts, capacity,
+      src_rank, n_ranks);
+  return launch_status();
+}
+
+extern "C" int nx_moe_combine(const NxPeerTable* bufs, const int32_t* expert, const int32_t* slot, const float* gate,
+                              void* y, int tokens, int top_k, int d, int local_experts, int capacity,
+                              nx_stream_t stream) {
+  if (bufs == nullptr || tokens <= 0 || d <= 0 || (d & 7)) return -1;
+  const int blocks = tokens < 148 * 8 ? tokens : 148 * 8;
+  moe_combine_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      *bufs, expert, slot, gate, static_cast<__nv_bfloat16*>(y), tokens, top_k, d, local_experts, capacity);
+  return launch_status();
+}
+
+extern "C" int nx_vocab_ce_exchange(const float* local_stats, const NxPeerTable* tables, const NxPeerTable* flags,
+                                    int rank, int n, int rows, int epoch, float* merged, int* status,
+                                    nx_stream_t stream) {
+  if (tables == nullptr || flags == nullptr || n < 1 || n > NX_MAX_PEERS || rows <= 0) return -1;
+  vocab_ce_exchange_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(local_stats, *tables, *flags, rank, n,
+                                                                              rows, epoch, merged, status);
+  return launch_status();
+}

@@ -11,7 +11,7 @@
 //
 // Replaces the reference's cuBLASLt layer and its epilogues Bias / BiasGelu(+aux) / DGelu /
 // beta=1 accumulate (include/nexus/cuda/gemm.hpp:38-121, src/cuda/gemm_lt.cpp:260-360).
-#include "nx_api.h"
+#include "nx_api_comm.h"
 #include "sm100_ptx.cuh"
 #include "tensor_map.h"
 #include <algorithm>
@@ -53,6 +53,21 @@ struct DevParams {
 
 struct Unit {
   int m0, n0, batch, slice, kb_begin, kb_end;
+};
+
+// Operands / output spread over the ranks of a group (peer-mapped memory).  Tiles never straddle a
+// rank boundary (rows per rank are multiples of the tile height).
+template <bool DIST>
+struct DistParam {
+  char unused;
+};
+template <>
+struct alignas(64) DistParam<true> {
+  CUtensorMap a[NX_MAX_PEERS];
+  CUtensorMap b[NX_MAX_PEERS];
+  float* out[NX_MAX_PEERS];
+  int a_rows, b_rows, out_rows;  // rows per rank
+  int a_sharded, b_sharded, out_scatter;
 };
 
 __device__ __forceinline__ Unit decode_unit(const DevParams& p, int u) {
@@ -148,10 +163,10 @@ __device__ __forceinline__ void load_any32(const void* base, int dtype, int64_t 
     load_row32<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(base) + elem_off, vec_ok, valid, v);
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool DIST>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            const DevParams p, const uint32_t idesc) {
+            const DevParams p, const uint32_t idesc, const __grid_constant__ DistParam<DIST> dist) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128B swizzle pattern (descriptor base_offset = 0).
@@ -212,19 +227,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           uint8_t* sb = sa + C::kABytes;
           mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
           const int k0 = kb * kBK;
+          const CUtensorMap* ma = &tmap_a;
+          const CUtensorMap* mb = &tmap_b;
+          int am0 = w.m0, bn0 = n0;
+          if constexpr (DIST) {
+            // the tile's rows live in the memory of the rank that owns them: plain (non-multicast) TMA
+            if (dist.a_sharded) {
+              const int q = w.m0 / dist.a_rows;
+              ma = &dist.a[q];
+              am0 = w.m0 - q * dist.a_rows;
+            }
+            if (dist.b_sharded) {
+              const int q = n0 / dist.b_rows;
+              mb = &dist.b[q];
+              bn0 = n0 - q * dist.b_rows;
+            }
+          }
           if (!A_MN) {
-            tma_load_3d(sa, &tmap_a, &full_bar[stage], k0, w.m0, w.batch);
+            tma_load_3d(sa, ma, &full_bar[stage], k0, am0, w.batch);
           } else {
 #pragma unroll
             for (int j = 0; j < kBM / 64; ++j)
-              tma_load_3d(sa + j * (64 * kBK * 2), &tmap_a, &full_bar[stage], w.m0 + 64 * j, k0, w.batch);
+              tma_load_3d(sa + j * (64 * kBK * 2), ma, &full_bar[stage], am0 + 64 * j, k0, w.batch);
           }
           if (!B_MN) {
-            tma_load_3d(sb, &tmap_b, &full_bar[stage], k0, n0, w.batch);
+            tma_load_3d(sb, mb, &full_bar[stage], k0, bn0, w.batch);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_3d(sb + j * (64 * kBK * 2), &tmap_b, &full_bar[stage], n0 + 64 * j, k0, w.batch);
+              tma_load_3d(sb + j * (64 * kBK * 2), mb, &full_bar[stage], bn0 + 64 * j, k0, w.batch);
           }
           if (++stage == C::kStages) {
             stage = 0;
@@ -312,6 +343,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
 
+        if constexpr (DIST) {
+          if (dist.out_scatter) {
+            // GEMM -> reduce-scatter: add the tile into the FP32 buffer of the rank that owns these rows
+            const int owner = row / dist.out_rows;
+            float* op = dist.out[owner] + static_cast<int64_t>(row - owner * dist.out_rows) * p.ldo + col0;
+            if ((valid == 32) && ((p.ldo & 3) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(op + j), "f"(v[j]), "f"(v[j + 1]),
+                             "f"(v[j + 2]), "f"(v[j + 3])
+                             : "memory");
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < valid) atomicAdd(op + j, v[j]);
+            }
+            continue;
+          }
+        }
         if (p.split_k > 1) {
           if (p.accumulate == 2) {
             // split-K slices add straight into the FP32 output (vector reductions in L2)
@@ -407,19 +457,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   }
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool DIST = false>
 int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const DevParams& p, uint32_t in_fmt, int grid,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, const DistParam<DIST>& dist = DistParam<DIST>{}) {
   using C = Cfg<BN>;
   static bool attr_set = false;
-  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, DIST>;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
       return -2;
     attr_set = true;
   }
   const uint32_t idesc = make_idesc(in_fmt, in_fmt, A_MN, B_MN, kBM, BN);
-  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, p, idesc);
+  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, p, idesc, dist);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -557,4 +607,81 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
   }
 #undef NX_LAUNCH
   return rc;
+}
+
+// K-major operands only; batch 1; no split-K.  Rows per rank must be multiples of the tile size.
+extern "C" int nx_gemm_dist(const NxGemmArgs* a, const NxGemmDist* d, nx_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a == nullptr || d == nullptr || a->m <= 0 || a->n <= 0 || a->k <= 0 || a->status == nullptr) return -1;
+  if (a->batch != 1 || a->a_mn_major || a->b_mn_major || a->in_dtype != NX_BF16) return -1;
+  const int n = d->n_ranks;
+  if (n < 1 || n > NX_MAX_PEERS || (a->lda & 7) || (a->ldb & 7)) return -1;
+  if (d->a_sharded && (a->m % n || (a->m / n) % kBM)) return -1;
+  int bn = (a->n >= 256) ? 256 : 128;
+  if (d->b_sharded) {
+    if (a->n % n) return -1;
+    const int per = a->n / n;
+    if (per % 256 == 0) bn = 256;
+    else if (per % 128 == 0) bn = 128;
+    else return -1;
+  }
+  if (d->out_scatter && (a->m % n || (a->m / n) % kBM || a->out_dtype != NX_F32)) return -1;
+
+  DevParams p{};
+  p.out = a->out;
+  p.bias = a->bias;
+  p.aux_in = a->aux_in;
+  p.aux_out = a->aux_out;
+  p.residual = a->residual;
+  p.status = a->status;
+  p.ldo = a->ldo;
+  p.ld_aux = a->ld_aux;
+  p.ld_res = a->ld_res;
+  p.m = a->m;
+  p.n = a->n;
+  p.k = a->k;
+  p.batch = 1;
+  p.out_dtype = a->out_dtype;
+  p.bias_dtype = a->bias_dtype;
+  p.res_dtype = a->res_dtype;
+  p.act = a->act;
+  p.accumulate = a->accumulate;
+  p.split_k = 1;
+  p.tiles_m = (a->m + kBM - 1) / kBM;
+  p.tiles_n = (a->n + bn - 1) / bn;
+  p.kb_total = (a->k + kBK - 1) / kBK;
+  p.kb_per_slice = p.kb_total;
+  p.num_units = p.tiles_m * p.tiles_n;
+  p.alpha = a->alpha;
+
+  const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  DistParam<true> dist{};
+  dist.a_sharded = d->a_sharded;
+  dist.b_sharded = d->b_sharded;
+  dist.out_scatter = d->out_scatter;
+  dist.a_rows = d->a_sharded ? a->m / n : a->m;
+  dist.b_rows = d->b_sharded ? a->n / n : a->n;
+  dist.out_rows = d->out_scatter ? a->m / n : a->m;
+  CUtensorMap ta, tb;
+  int rc;
+  for (int q = 0; q < n; ++q) {
+    if (d->a_sharded) {
+      if (reinterpret_cast<uintptr_t>(d->a_ptrs[q]) & 15) return -1;
+      if ((rc = nx::make_tensor_map_3d(&dist.a[q], dt, 2, d->a_ptrs[q], a->k, dist.a_rows, 1, a->lda, 0, kBK, kBM))) return rc;
+    }
+    if (d->b_sharded) {
+      if (reinterpret_cast<uintptr_t>(d->b_ptrs[q]) & 15) return -1;
+      if ((rc = nx::make_tensor_map_3d(&dist.b[q], dt, 2, d->b_ptrs[q], a->k, dist.b_rows, 1, a->ldb, 0, kBK, bn))) return rc;
+    }
+    dist.out[q] = static_cast<float*>(d->out_ptrs[q]);
+  }
+  const void* a0 = d->a_sharded ? d->a_ptrs[d->rank] : a->a;
+  const void* b0 = d->b_sharded ? d->b_ptrs[d->rank] : a->b;
+  if ((rc = nx::make_tensor_map_3d(&ta, dt, 2, a0, a->k, d->a_sharded ? dist.a_rows : a->m, 1, a->lda, 0, kBK, kBM))) return rc;
+  if ((rc = nx::make_tensor_map_3d(&tb, dt, 2, b0, a->k, d->b_sharded ? dist.b_rows : a->n, 1, a->ldb, 0, kBK, bn))) return rc;
+  int sms = nx_sm_count();
+  if (sms <= 0) return -2;
+  const int grid = p.num_units < sms ? p.num_units : sms;
+  if (bn == 256) return launch_variant<256, false, false, true>(ta, tb, p, kFmtBF16, grid, stream, dist);
+  return launch_variant<128, false, false, true>(ta, tb, p, kFmtBF16, grid, stream, dist);
 }

@@ -1,0 +1,61 @@
+// C ABI of the kernels that combine computation with NVLink communication over peer-mapped memory.
+// A peer table holds, for every rank of the group, the device pointer (as mapped in THIS process) of
+// that rank's copy of a symmetric buffer.  All waits inside these kernels are bounded (2 s); a wait
+// that runs out writes nx::kStatusTimeoutPeer into the status word.
+#pragma once
+#include "nx_api_kernels.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NX_MAX_PEERS 8
+
+typedef struct NxPeerTable {
+  void* ptr[NX_MAX_PEERS];
+} NxPeerTable;
+
+// flags: per rank an int[n] array (zero-initialised); `epoch` must grow by one per call on every rank.
+int nx_comm_barrier(const NxPeerTable* flags, int rank, int n, int epoch, int* status, nx_stream_t stream);
+
+// out[i] = scale * sum_p grads[p][shard_off + i] (p = 0..n-1 in order), i < count; partial[] receives
+// per-block FP64 square sums (nx_comm_reduce_partials(count) entries).  shard_off % 4 == 0.
+int64_t nx_comm_reduce_partials(int64_t count);
+int nx_comm_reduce_shard(const NxPeerTable* grads, int n, int64_t shard_off, int64_t count, float scale, float* out,
+                         double* partial, nx_stream_t stream);
+// slots: per rank a double[n] array.  Publishes this rank's square sum to every rank, waits for all,
+// then fills grad_norm / clip_coef / found_inf / step / bias corrections of `state`.
+int nx_comm_norm_exchange(const double* partial, int nparts, const NxPeerTable* slots, const NxPeerTable* flags,
+                          int rank, int n, int epoch, NxOptState* state, int* status, nx_stream_t stream);
+// AdamW on shard-local FP32 state; chunks carry GLOBAL offsets inside [shard_off, shard_off + shard);
+// the BF16 weights are written into every rank's full shadow buffer (the all-gather).
+int nx_comm_adamw_allgather(float* master, const float* grad, float* m, float* v, const NxPeerTable* shadows, int n,
+                            int64_t shard_off, const NxAdamChunk* chunks, int nchunks, const NxOptState* state,
+                            nx_stream_t stream);
+
+// Expert parallelism.  bufs[q]: rank q's [local_experts, capacity, d] BF16 buffer.
+int nx_moe_dispatch(const void* x, const int32_t* token_of, const int32_t* expert_of, const int32_t* slot_of,
+                    const NxPeerTable* bufs, int rows, int d, int local_experts, int capacity, int src_rank,
+                    int n_ranks, nx_stream_t stream);
+int nx_moe_combine(const NxPeerTable* bufs, const int32_t* expert, const int32_t* slot, const float* gate, void* y,
+                   int tokens, int top_k, int d, int local_experts, int capacity, nx_stream_t stream);
+
+// Vocabulary-parallel CE: local_stats [rows][3]; tables[q]: float[n][rows][3]; merged [rows][3].
+int nx_vocab_ce_exchange(const float* local_stats, const NxPeerTable* tables, const NxPeerTable* flags, int rank, int n,
+                         int rows, int epoch, float* merged, int* status, nx_stream_t stream);
+
+// Distributed GEMM (see nx_gemm): operand A and/or B is row-sharded over the ranks and its tiles are
+// fetched by (non-multicast) TMA straight from the owning rank's memory; the output can be
+// reduce-scattered by adding each tile into the owning rank's FP32 buffer.
+typedef struct NxGemmDist {
+  const void* a_ptrs[NX_MAX_PEERS];  // when a_sharded: rank q holds rows [q*M/n, (q+1)*M/n) of A (K-major)
+  const void* b_ptrs[NX_MAX_PEERS];  // when b_sharded: rank q holds rows [q*N/n, (q+1)*N/n) of B (K-major)
+  void* out_ptrs[NX_MAX_PEERS];      // when out_scatter: rank q owns output rows [q*M/n, (q+1)*M/n), FP32
+  int32_t n_ranks, rank;
+  int32_t a_sharded, b_sharded, out_scatter;
+} NxGemmDist;
+int nx_gemm_dist(const NxGemmArgs* args, const NxGemmDist* dist, nx_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

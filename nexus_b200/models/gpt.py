@@ -116,6 +116,16 @@ class GptModel:
             self.p[name].fill_(1.0)
         self.refresh_shadow()
 
+    def rebind_buffers(self, params_lp: Optional[torch.Tensor] = None, grads: Optional[torch.Tensor] = None) -> None:
+        """Re-points the BF16 shadow and/or the gradient buffer at caller-provided storage (e.g. symmetric
+        memory that peers can reach) and rebuilds the per-tensor views."""
+        if params_lp is not None:
+            self.params_lp = params_lp
+            self.w = {n: self._view(self.params_lp, n) for n in PARAM_ORDER}
+        if grads is not None:
+            self.grads = grads
+            self.g = {n: self._view(self.grads, n) for n in PARAM_ORDER}
+
     def refresh_shadow(self) -> None:
         self.params_lp.copy_(self.params)
 

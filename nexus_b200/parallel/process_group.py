@@ -510,7 +510,8 @@ class ThreadWorld:
             t.start()
         for t in threads:
             t.join()
-        real = [e for e in errors if e is not None and not (isinstance(e, DistError) and "broken" in str(e))]
+        # a rank's own failure outranks the DistErrors it caused on the ranks that waited for it
+        real = [e for e in errors if e is not None and not isinstance(e, DistError)]
         first = real[0] if real else next((e for e in errors if e is not None), None)
         if first is not None:
             raise first

@@ -1,0 +1,212 @@
+"""Symmetric (peer-mapped) device memory and the fused compute+communication paths built on it.
+
+Every rank allocates buffers of identical layout through ``torch.distributed._symmetric_memory``
+(the allocation / handle exchange plumbing) and maps all peers' copies; the kernels of
+``csrc/cuda/comm_kernels.cu`` and the distributed GEMM then read and write peers directly over
+NVLink 5 / NVSwitch.  Cross-GPU ordering uses flag arrays with bounded device-side waits.
+
+`FusedShardedOptimizer` is the FSDP/ZeRO path of the flat GPT model: gradient reduce-scatter by
+owner-pull in a fixed order, global-norm exchange, AdamW on the owned shard and the all-gather of
+the updated BF16 weights, as four kernels and no NCCL call.
+
+Parity (behaviour): FsdpEngine::step of src/dist/fsdp.cpp:474-568 in the reference (norm ->
+all-reduce -> clip -> AdamW on the shard -> all-gather), which runs on CPU ranks there.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import List, Optional
+
+import numpy as np
+import torch
+
+from ..ops import _cuda as K
+
+MAX_PEERS = 8
+
+
+class PeerTable(C.Structure):
+    _fields_ = [("ptr", C.c_void_p * MAX_PEERS)]
+
+
+class GemmDist(C.Structure):
+    _fields_ = [("a_ptrs", C.c_void_p * MAX_PEERS), ("b_ptrs", C.c_void_p * MAX_PEERS),
+                ("out_ptrs", C.c_void_p * MAX_PEERS), ("n_ranks", C.c_int32), ("rank", C.c_int32),
+                ("a_sharded", C.c_int32), ("b_sharded", C.c_int32), ("out_scatter", C.c_int32)]
+
+
+def _table(ptrs: List[int]) -> PeerTable:
+    t = PeerTable()
+    for i, p in enumerate(ptrs):
+        t.ptr[i] = p
+    return t
+
+
+class SymmetricBuffer:
+    """One symmetric allocation: ``local`` is this rank's tensor, ``ptrs[q]`` rank q's device address."""
+
+    def __init__(self, local: torch.Tensor, ptrs: List[int]):
+        self.local, self.ptrs = local, ptrs
+        self.table = _table(ptrs)
+
+    def offset_table(self, byte_offset: int) -> PeerTable:
+        return _table([p + byte_offset for p in self.ptrs])
+
+
+class SymmetricWorkspace:
+    """Allocator of symmetric buffers for one process group + the group's flag array and barrier."""
+
+    def __init__(self, pg):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self.pg, self.symm_mem = pg, symm_mem
+        self.rank, self.n = pg.rank(), pg.size()
+        if self.n > MAX_PEERS:
+            raise ValueError(f"at most {MAX_PEERS} ranks per symmetric group")
+        self.group = pg.group if pg.group is not None else dist.group.WORLD
+        self.device = pg.device
+        try:
+            symm_mem.enable_symm_mem_for_group(self.group.group_name)
+        except Exception:
+            pass
+        self.epoch = 0
+        self.flags = self.alloc(MAX_PEERS, torch.int32)
+        self.flags.local.zero_()
+        self.slots = self.alloc(MAX_PEERS, torch.float64)
+        self.slots.local.zero_()
+        torch.cuda.synchronize()
+        pg.barrier()
+
+    def alloc(self, numel: int, dtype: torch.dtype) -> SymmetricBuffer:
+        t = self.symm_mem.empty(int(numel), dtype=dtype, device=self.device)
+        hdl = self.symm_mem.rendezvous(t, self.group)
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        return SymmetricBuffer(t, ptrs)
+
+    def barrier(self) -> None:
+        """Device-side barrier over the group on the current stream (bounded wait)."""
+        self.epoch += 1
+        K._check(K.lib().nx_comm_barrier(C.byref(self.flags.table), C.c_int(self.rank), C.c_int(self.n),
+                                         C.c_int(self.epoch), K._p(K.status_word(self.device)), K._stream()),
+                 "nx_comm_barrier")
+
+
+class FusedShardedOptimizer:
+    """ZeRO-style sharded AdamW for a `GptModel` over symmetric memory (no NCCL in the step)."""
+
+    def __init__(self, model, ws: SymmetricWorkspace):
+        self.model, self.ws = model, ws
+        n, r = ws.n, ws.rank
+        N = model.num_params
+        self.S = (math.ceil(N / n) + 63) // 64 * 64
+        self.off = min(N, r * self.S)
+        self.count = max(0, min(self.S, N - self.off))
+        dev = model.device
+        # gradients and the BF16 shadow move into symmetric memory so that peers can reach them
+        self.grads = ws.alloc(N, torch.float32)
+        self.shadow = ws.alloc(N, torch.bfloat16)
+        self.grads.local.zero_()
+        self.shadow.local.copy_(model.params_lp)
+        model.rebind_buffers(params_lp=self.shadow.local, grads=self.grads.local)
+        sl = slice(self.off, self.off + self.count)
+        self.master = model.params[sl].clone()
+        self.m = torch.zeros(self.count, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(self.count, dtype=torch.float32, device=dev)
+        self.gshard = torch.empty(max(self.count, 4), dtype=torch.float32, device=dev)
+        nparts = int(K.lib().nx_comm_reduce_partials(C.c_int64(max(self.count, 1))))
+        self.partials = torch.zeros(max(nparts, 1), dtype=torch.float64, device=dev)
+        self.nparts = nparts
+        self.chunks = None
+        self.set_param_scales(None, None)
+        torch.cuda.synchronize()
+        ws.pg.barrier()
+
+    def set_param_scales(self, weight_decay, lr) -> None:
+        from ..models.gpt import DECAY, PARAM_ORDER
+        m = self.model
+        segs = []
+        for i, name in enumerate(PARAM_ORDER):
+            a, cnt = m.offsets[name], math.prod(m.shapes[name])
+            lo, hi = max(a, self.off), min(a + cnt, self.off + self.count)
+            if lo < hi:
+                wd = (1.0 if name in DECAY else 0.0) if weight_decay is None else float(weight_decay[i])
+                segs.append((lo, hi - lo, wd, 1.0 if lr is None else float(lr[i])))
+        self.chunks = K.make_chunks(segs, device=m.device) if segs else None
+
+    def step(self) -> None:
+        ws, m, L = self.ws, self.model, K.lib()
+        n, r = ws.n, ws.rank
+        st = K._stream()
+        status = K._p(K.status_word(m.device))
+        ws.barrier()  # every rank has finished its backward pass
+        if self.count > 0:
+            K._check(L.nx_comm_reduce_shard(C.byref(self.grads.table), C.c_int(n), C.c_int64(self.off),
+                                            C.c_int64(self.count), C.c_float(1.0), K._p(self.gshard),
+                                            K._p(self.partials), st), "nx_comm_reduce_shard")
+        ws.epoch += 1
+        K._check(L.nx_comm_norm_exchange(K._p(self.partials), C.c_int(self.nparts if self.count > 0 else 0),
+                                         C.byref(ws.slots.table), C.byref(ws.flags.table), C.c_int(r), C.c_int(n),
+                                         C.c_int(ws.epoch), K._p(m.opt_state), status, st), "nx_comm_norm_exchange")
+        m.grads.zero_()  # every peer has finished reading this rank's gradients
+        if self.count > 0 and self.chunks is not None:
+            K._check(L.nx_comm_adamw_allgather(K._p(self.master), K._p(self.gshard), K._p(self.m), K._p(self.v),
+                                               C.byref(self.shadow.table), C.c_int(n), C.c_int64(self.off),
+                                               K._p(self.chunks), C.c_int(self.chunks.nchunks), K._p(m.opt_state),
+                                               st), "nx_comm_adamw_allgather")
+        ws.barrier()  # updated weights are visible on every rank
+        m.step_count += 1
+
+    def gather_master(self) -> torch.Tensor:
+        """Full FP32 master vector (for checkpoints / tests) through NCCL."""
+        out = torch.zeros(self.S * self.ws.n, dtype=torch.float32, device=self.model.device)
+        pad = torch.zeros(self.S, dtype=torch.float32, device=self.model.device)
+        pad[: self.count] = self.master
+        self.ws.pg.all_gather_tensor(out, pad)
+        return out[: self.model.num_params]
+
+
+def gemm_dist(ws: SymmetricWorkspace, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *,
+              a_peers: Optional[SymmetricBuffer] = None, b_peers: Optional[SymmetricBuffer] = None,
+              out_peers: Optional[SymmetricBuffer] = None, bias=None, act=None, m: Optional[int] = None,
+              n: Optional[int] = None) -> torch.Tensor:
+    """out = epilogue(A @ B^T) where A and/or B is row-sharded over the group and read tile by tile from
+    its owners (all-gather fused into the GEMM), and/or the FP32 output is added into the owner of each
+    row block (GEMM fused with reduce-scatter).  ``a`` / ``b`` are this rank's (local) operands."""
+    g = K.GemmArgs()
+    k = a.shape[1]
+    M = m if m is not None else (a.shape[0] * ws.n if a_peers is not None else a.shape[0])
+    N = n if n is not None else (b.shape[0] * ws.n if b_peers is not None else b.shape[0])
+    g.a, g.b, g.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    g.lda, g.ldb, g.ldo = a.stride(0), b.stride(0), out.stride(0)
+    g.m, g.n, g.k, g.batch = M, N, k, 1
+    g.in_dtype, g.out_dtype = K._DT[a.dtype], K._DT[out.dtype]
+    if bias is not None:
+        g.bias, g.bias_dtype = bias.data_ptr(), K._DT[bias.dtype]
+    g.act, g.alpha, g.split_k = K.ACT[act], 1.0, 1
+    g.status = K.status_word(a.device).data_ptr()
+    d = GemmDist()
+    d.n_ranks, d.rank = ws.n, ws.rank
+    for q in range(ws.n):
+        if a_peers is not None:
+            d.a_ptrs[q] = a_peers.ptrs[q]
+        if b_peers is not None:
+            d.b_ptrs[q] = b_peers.ptrs[q]
+        if out_peers is not None:
+            d.out_ptrs[q] = out_peers.ptrs[q]
+    d.a_sharded, d.b_sharded, d.out_scatter = int(a_peers is not None), int(b_peers is not None), int(out_peers is not None)
+    K._check(K.lib().nx_gemm_dist(C.byref(g), C.byref(d), K._stream()), "nx_gemm_dist")
+    return out
+
+
+def moe_dispatch(ws, x, token_of, expert_of, slot_of, bufs: SymmetricBuffer, local_experts: int, capacity: int):
+    K._check(K.lib().nx_moe_dispatch(K._p(x), K._p(token_of), K._p(expert_of), K._p(slot_of), C.byref(bufs.table),
+                                     C.c_int(token_of.numel()), C.c_int(x.shape[1]), C.c_int(local_experts),
+                                     C.c_int(capacity), C.c_int(ws.rank), C.c_int(ws.n), K._stream()), "nx_moe_dispatch")
+
+
+def moe_combine(ws, bufs: SymmetricBuffer, expert, slot, gate, y, local_experts: int, capacity: int):
+    tokens, top_k = expert.shape
+    K._check(K.lib().nx_moe_combine(C.byref(bufs.table), K._p(expert), K._p(slot), K._p(gate), K._p(y),
+                                    C.c_int(tokens), C.c_int(top_k), C.c_int(y.shape[1]), C.c_int(local_experts),
+                                    C.c_int(capacity), K._stream()), "nx_moe_combine")

@@ -42,6 +42,8 @@ class GptLmBackend(LmBackend):
         self._result_host = torch.zeros(8, dtype=torch.float32).pin_memory()
         self._opt_cfg: Optional[AdamWConfig] = None
         self._pg = None
+        self._sharded = None
+        self._scales = None
         self._graph = None
         self._graph_enabled = False
         self._graph_key = None
@@ -62,6 +64,9 @@ class GptLmBackend(LmBackend):
                             n in ("wte", "wpe")) for n in PARAM_ORDER]
 
     def set_param_scales(self, weight_decay, lr) -> None:
+        self._scales = (list(weight_decay), list(lr))
+        if self._sharded is not None:
+            self._sharded.set_param_scales(weight_decay, lr)
         m = self.model
         segs = [(m.offsets[n], int(np.prod(m.shapes[n])), float(weight_decay[i]), float(lr[i]))
                 for i, n in enumerate(PARAM_ORDER)]
@@ -104,7 +109,7 @@ class GptLmBackend(LmBackend):
             return
         self.model.forward_backward(dev_tokens, grad_scale=grad_weight, accumulate_loss=index > 0,
                                     loss_weight=grad_weight)
-        if index == count - 1 and self._pg is not None:
+        if index == count - 1 and self._pg is not None and self._sharded is None:
             self._pg.all_reduce_tensor(self.model.grads, "sum")
 
     def optimizer_step(self, optimizer: AdamW, lr: float, clip: float) -> None:
@@ -120,7 +125,28 @@ class GptLmBackend(LmBackend):
         if self._graph_enabled:
             self._run_graph()
             return
-        m.optimizer_step()
+        self._opt_step()
+
+    def _opt_step(self) -> None:
+        if self._sharded is not None:
+            self._sharded.step()
+        else:
+            self.model.optimizer_step()
+
+    def attach_fsdp(self, group, options=None) -> None:
+        """Shards master weights, moments and the gradient reduction over ``group`` using the fused
+        peer-memory kernels (reduce-scatter + norm exchange + AdamW + all-gather, no NCCL in the step)."""
+        from ..parallel.symm import FusedShardedOptimizer, SymmetricWorkspace
+        self._pg_fsdp = group
+        group.broadcast_tensor(self.model.params, 0)
+        self.model.refresh_shadow()
+        self._ws = SymmetricWorkspace(group)
+        self._sharded = FusedShardedOptimizer(self.model, self._ws)
+        if self._scales is not None:
+            self._sharded.set_param_scales(*self._scales)
+
+    def state_layout(self) -> str:
+        return f"fsdp:2:{self._ws.n}" if self._sharded is not None else "replicated"
 
     def finish_step(self) -> LmStepResult:
         """One small D2H copy (loss, grad norm, found_inf) + one synchronisation."""
@@ -142,10 +168,11 @@ class GptLmBackend(LmBackend):
         if self._opt_cfg is None:
             self._opt_cfg = AdamWConfig(lr=lr)
             m.set_optimizer(self._opt_cfg)
-        m.forward_backward(tokens_dev, grad_scale=1.0)
-        if self._pg is not None:
+        world = self._ws.n if self._sharded is not None else (self._pg.size() if self._pg is not None else 1)
+        m.forward_backward(tokens_dev, grad_scale=1.0 / world)
+        if self._pg is not None and self._sharded is None:
             self._pg.all_reduce_tensor(m.grads, "sum")
-        m.optimizer_step()
+        self._opt_step()
 
     # ------------------------------------------------------------------------------- CUDA graph
     def compile(self, enabled: bool, mode: str = "default") -> None:
@@ -180,9 +207,9 @@ class GptLmBackend(LmBackend):
         for i in range(count):
             m.forward_backward(self._dev_tokens[i], grad_scale=weights[i], accumulate_loss=i > 0,
                                loss_weight=weights[i])
-        if self._pg is not None:
+        if self._pg is not None and self._sharded is None:
             self._pg.all_reduce_tensor(m.grads, "sum")
-        m.optimizer_step()
+        self._opt_step()
 
     # ------------------------------------------------------------------------------- evaluation
     def eval_loss(self, tokens: np.ndarray) -> float:

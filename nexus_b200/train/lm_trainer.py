@@ -553,8 +553,11 @@ class LanguageModelTrainer:
 
     # ------------------------------------------------------------------------------ persistence
     def trainer_state(self) -> dict:
+        cursor = self.source.global_cursor()
+        if self._prefetched is not None:  # the prefetched batch already advanced the source: rewind one step
+            cursor -= self.accum * self.micro * self.dp
         return {"step": self.step, "lr_factor": self.lr_factor, "rng_seed": self.b._seed,
-                "rng_offset": self.rng_offset, "train_cursor": self.source.global_cursor(),
+                "rng_offset": self.rng_offset, "train_cursor": cursor,
                 "val_cursor": self.val.global_cursor() if self.val is not None else 0,
                 "world": self.dp, "rank": self.rank, "tokens_seen": self.tokens_seen,
                 "schedule_step": self.step}
@@ -572,10 +575,7 @@ class LanguageModelTrainer:
     def save_checkpoint(self) -> None:
         if self.ckpt is None:
             raise RuntimeError("checkpointing(options) was not configured")
-        # the prefetched batch has already advanced the source: rewind the cursor by one step
         st = self.trainer_state()
-        if self._prefetched is not None:
-            st["train_cursor"] -= self.accum * self.micro * self.dp
         self.ckpt.save(self.step, st, self.backend.save_state(), layout=self.backend.state_layout())
 
     def resume_latest(self) -> bool:

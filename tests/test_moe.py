@@ -1,0 +1,53 @@
+import pytest
+import torch
+
+from nexus_b200.moe import MoEFFN, Spec, reference, route
+from nexus_b200.moe.moe import capacity_of, dequantize_experts, quantize_experts
+
+
+def test_matches_fp64_oracle_and_has_router_gradients():
+    torch.manual_seed(0)
+    s = Spec(experts=4, top_k=2, d_model=16, d_ff=8, capacity_factor=1.0, min_capacity=1)
+    m = MoEFFN(s)
+    x = torch.randn(32, 16)
+    y = m(x)
+    yr, aux, z = reference(x, m.router.detach(), m.up.detach(), m.down.detach(), s)
+    assert (y.double() - yr).abs().max() < 1e-6
+    assert float(m.last_routing.aux) == pytest.approx(aux, rel=1e-6) and float(m.last_routing.z) == pytest.approx(z, rel=1e-6)
+    (y.sum() + m.losses()).backward()
+    assert m.router.grad.abs().sum() > 0 and m.up.grad.abs().sum() > 0
+
+
+def test_capacity_priority_drop_and_reroute():
+    assert capacity_of(Spec(experts=8, top_k=2, d_model=1, d_ff=1, capacity_factor=1.25, min_capacity=4), 64) == 20
+    torch.manual_seed(1)
+    x = torch.randn(16, 8)
+    w = torch.zeros(8, 4)
+    w[:, 0] = 5.0                     # every token prefers expert 0
+    s = Spec(experts=4, top_k=1, d_model=8, d_ff=4, capacity_factor=1.0, min_capacity=1)
+    r = route(x.abs(), w, None, s)
+    assert r.capacity == 4 and r.dropped == 12
+    assert (r.row[:4, 0] >= 0).all() and (r.row[4:, 0] < 0).all()     # earliest tokens win
+    s2 = Spec(experts=4, top_k=1, d_model=8, d_ff=4, capacity_factor=1.0, min_capacity=1, overflow="reroute")
+    r2 = route(x.abs(), w, None, s2)
+    assert r2.dropped == 0 and r2.rerouted == 12
+    counts = (r2.offsets[1:] - r2.offsets[:-1]).tolist()
+    assert counts == [4, 4, 4, 4]
+    with pytest.raises(ValueError):
+        route(x[:15], w, None, Spec(experts=4, top_k=1, d_model=8, d_ff=4, groups=2))
+
+
+def test_groups_and_gate_normalisation():
+    torch.manual_seed(2)
+    s = Spec(experts=4, top_k=2, d_model=8, d_ff=4, groups=2, capacity_factor=2.0)
+    r = route(torch.randn(16, 8), torch.randn(8, 4), None, s)
+    assert torch.allclose(r.gate.sum(-1), torch.ones(16))
+    assert int(r.offsets[-1]) == int((r.row >= 0).sum())
+
+
+def test_expert_quantisation():
+    w = torch.randn(4, 8, 16)
+    q, sc = quantize_experts(w, "fp8")
+    assert (dequantize_experts(q, sc) - w).abs().max() < 0.07 * w.abs().max()
+    q, sc = quantize_experts(w, "bf16")
+    assert sc is None and (q.float() - w).abs().max() < 0.01 * w.abs().max()

@@ -1,0 +1,138 @@
+"""2+ GPU worker (one rank per GPU, launched by torch.distributed.run): checks the fused
+peer-memory paths against single-GPU / PyTorch references.  Prints 'WORKER_OK' on rank 0."""
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from nexus_b200.lm.config import preset  # noqa: E402
+from nexus_b200.models.gpt import AdamWConfig, GptModel  # noqa: E402
+from nexus_b200.ops import _cuda as K  # noqa: E402
+from nexus_b200.parallel.process_group import init_process_group  # noqa: E402
+from nexus_b200.parallel.symm import (FusedShardedOptimizer, SymmetricWorkspace, gemm_dist, moe_combine,  # noqa: E402
+                                      moe_dispatch)
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    pg = init_process_group("nccl", dev)
+    ws = SymmetricWorkspace(pg)
+    ok = True
+
+    def check(name, cond):
+        nonlocal ok
+        ok &= bool(cond)
+        if rank == 0:
+            print(("OK  " if cond else "BAD ") + name, flush=True)
+
+    # ---- barrier
+    for _ in range(3):
+        ws.barrier()
+    torch.cuda.synchronize()
+    K.check_status()
+    check("barrier", True)
+
+    # ---- fused sharded optimizer vs single-GPU run of the same global batch
+    cfg = preset("gpt2-124m")
+    cfg.n_layer, cfg.d_model, cfg.n_head, cfg.d_ff, cfg.vocab_size, cfg.max_position = 2, 128, 2, 512, 500, 128
+    g = torch.Generator().manual_seed(3)
+    tokens = torch.randint(0, cfg.vocab_size, (world, 2, 128), generator=g, dtype=torch.int32).to(dev)
+    ref = GptModel(cfg, device=dev, seed=11)
+    ref.set_optimizer(AdamWConfig(lr=1e-3))
+    model = GptModel(cfg, device=dev, seed=11)
+    model.set_optimizer(AdamWConfig(lr=1e-3))
+    opt = FusedShardedOptimizer(model, ws)
+    for step in range(3):
+        for r in range(world):
+            ref.forward_backward(tokens[r], grad_scale=1.0 / world, accumulate_loss=r > 0, loss_weight=1.0 / world)
+        ref.optimizer_step()
+        model.forward_backward(tokens[rank], grad_scale=1.0 / world, loss_weight=1.0 / world)
+        opt.step()
+    torch.cuda.synchronize()
+    K.check_status()
+    full = opt.gather_master()
+    err = (full - ref.params).abs().max().item()
+    err_lp = (model.params_lp.float() - ref.params_lp.float()).abs().max().item()
+    s1, s2 = model.read_opt_state(), ref.read_opt_state()
+    check(f"sharded optimizer master err {err:.2e} shadow err {err_lp:.2e}", err < 2e-4 and err_lp < 1e-2)
+    check(f"grad norm {s1.grad_norm:.5f} vs {s2.grad_norm:.5f}", abs(s1.grad_norm - s2.grad_norm) < 1e-3 * s2.grad_norm)
+
+    # ---- distributed GEMM: all-gather fused into the GEMM (A sharded / B sharded) and GEMM -> reduce-scatter
+    torch.manual_seed(5)
+    M, N, Kd = 256 * world, 256 * world, 320
+    A = torch.randn(M, Kd, device=dev).bfloat16()
+    B = torch.randn(N, Kd, device=dev).bfloat16()
+    pg.broadcast_tensor(A, 0)
+    pg.broadcast_tensor(B, 0)
+    ref_out = A.float() @ B.float().t()
+    a_sym = ws.alloc(M // world * Kd, torch.bfloat16)
+    a_loc = a_sym.local.view(M // world, Kd)
+    a_loc.copy_(A[rank * (M // world): (rank + 1) * (M // world)])
+    b_sym = ws.alloc(N // world * Kd, torch.bfloat16)
+    b_loc = b_sym.local.view(N // world, Kd)
+    b_loc.copy_(B[rank * (N // world): (rank + 1) * (N // world)])
+    torch.cuda.synchronize()
+    ws.barrier()
+    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    gemm_dist(ws, a_loc, B, out, a_peers=a_sym)
+    torch.cuda.synchronize(); K.check_status()
+    check("AG(A)->GEMM", (out.float() - ref_out).abs().max() <= 1.5e-2 * ref_out.abs().max())
+    gemm_dist(ws, A, b_loc, out, b_peers=b_sym)
+    torch.cuda.synchronize(); K.check_status()
+    check("AG(B)->GEMM", (out.float() - ref_out).abs().max() <= 1.5e-2 * ref_out.abs().max())
+    # row-parallel: each rank holds a K slice; out rows reduce-scattered
+    Ks = Kd // world // 8 * 8
+    Ak = A[:, rank * Ks: (rank + 1) * Ks].contiguous()
+    Bk = B[:, rank * Ks: (rank + 1) * Ks].contiguous()
+    o_sym = ws.alloc(M // world * N, torch.float32)
+    o_sym.local.zero_()
+    torch.cuda.synchronize()
+    ws.barrier()
+    gemm_dist(ws, Ak, Bk, o_sym.local.view(M // world, N), out_peers=o_sym, m=M, n=N)
+    ws.barrier()
+    torch.cuda.synchronize(); K.check_status()
+    ref_rs = A[:, : Ks * world].float() @ B[:, : Ks * world].float().t()
+    mine = ref_rs[rank * (M // world): (rank + 1) * (M // world)]
+    check("GEMM->RS", (o_sym.local.view(M // world, N) - mine).abs().max() <= 1e-2 * ref_rs.abs().max())
+
+    # ---- MoE dispatch / combine over peer memory (identity experts)
+    E, k, d, T, cap = 2 * world, 2, 64, 32, 64
+    le = E // world
+    x = torch.randn(T, d, device=dev).bfloat16()
+    expert = torch.stack([torch.randperm(E, device=dev)[:k] for _ in range(T)]).to(torch.int32)
+    gate = torch.softmax(torch.randn(T, k, device=dev), -1)
+    # global slot of an assignment inside its expert: rank-major, then token order (counts exchanged through NCCL)
+    onehot = torch.nn.functional.one_hot(expert.long().reshape(-1), E)
+    counts = onehot.sum(0)
+    allc = torch.empty(world * E, dtype=counts.dtype, device=dev)
+    pg.all_gather_tensor(allc, counts)
+    base = allc.view(world, E)[:rank].sum(0)
+    within = (onehot.cumsum(0) - 1).gather(1, expert.long().reshape(-1, 1))[:, 0]
+    slot = (base[expert.long().reshape(-1)] + within).to(torch.int32)
+    bufs = ws.alloc(le * cap * d, torch.bfloat16)
+    bufs.local.zero_()
+    torch.cuda.synchronize()
+    ws.barrier()
+    token_of = (torch.arange(T * k, device=dev) // k).to(torch.int32)
+    moe_dispatch(ws, x, token_of, expert.reshape(-1).contiguous(), slot, bufs, le, cap)
+    ws.barrier()
+    y = torch.empty(T, d, device=dev, dtype=torch.bfloat16)
+    moe_combine(ws, bufs, expert.contiguous(), slot.view(T, k).contiguous(), gate.contiguous(), y, le, cap)
+    ws.barrier()
+    torch.cuda.synchronize(); K.check_status()
+    check("MoE dispatch+combine", (y.float() - x.float() * gate.sum(-1, keepdim=True)).abs().max() < 3e-2)
+
+    flag = torch.tensor([1.0 if ok else 0.0], device=dev)
+    pg.all_reduce_tensor(flag, "min")
+    if rank == 0:
+        print("WORKER_OK" if flag.item() == 1.0 else "WORKER_FAILED", flush=True)
+    pg.destroy()
+    return 0 if ok else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
