@@ -149,8 +149,9 @@ __global__ void norm_exchange_kernel(const double* __restrict__ partial, int npa
 // goes to every rank's full shadow buffer at the global index.  Same op order as adamw_kernel.
 __global__ void __launch_bounds__(256)
 adamw_shard_allgather_kernel(float* __restrict__ master, const float* __restrict__ grad, float* __restrict__ m,
-                             float* __restrict__ v, NxPeerTable shadows, int n, int64_t shard_off,
-                             const NxAdamChunk* __restrict__ chunks, const NxOptState* __restrict__ st) {
+                             float* __restrict__ v, NxPeerTable shadows, NxPeerTable tails, int64_t tail_off,
+                             int n, int64_t shard_off, const NxAdamChunk* __restrict__ chunks,
+                             const NxOptState* __restrict__ st) {
   if (st->found_inf) return;
   const NxAdamChunk ch = chunks[blockIdx.x];
   const float lr = __fmul_rn(st->lr, ch.lr_scale);
@@ -172,6 +173,10 @@ adamw_shard_allgather_kernel(float* __restrict__ master, const float* __restrict
     const __nv_bfloat16 lp = __float2bfloat16_rn(p);
 #pragma unroll 1
     for (int q = 0; q < n; ++q) reinterpret_cast<__nv_bfloat16*>(shadows.ptr[q])[gi] = lp;
+    if (tail_off >= 0 && gi >= tail_off) {  // parameters that the model reads in FP32 (norm scales, biases)
+#pragma unroll 1
+      for (int q = 0; q < n; ++q) reinterpret_cast<float*>(tails.ptr[q])[gi - tail_off] = p;
+    }
   }
 }
 
@@ -299,12 +304,14 @@ extern "C" int nx_comm_norm_exchange(const double* partial, int nparts, const Nx
 }
 
 extern "C" int nx_comm_adamw_allgather(float* master, const float* grad, float* m, float* v,
-                                       const NxPeerTable* shadows, int n, int64_t shard_off,
-                                       const NxAdamChunk* chunks, int nchunks, const NxOptState* state,
-                                       nx_stream_t stream) {
+                                       const NxPeerTable* shadows, const NxPeerTable* fp32_tails,
+                                       int64_t tail_off, int n, int64_t shard_off, const NxAdamChunk* chunks,
+                                       int nchunks, const NxOptState* state, nx_stream_t stream) {
   if (shadows == nullptr || n < 1 || n > NX_MAX_PEERS || nchunks <= 0) return -1;
-  adamw_shard_allgather_kernel<<<nchunks, 256, 0, static_cast<cudaStream_t>(stream)>>>(master, grad, m, v, *shadows, n,
-                                                                                       shard_off, chunks, state);
+  NxPeerTable none = {};
+  adamw_shard_allgather_kernel<<<nchunks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      master, grad, m, v, *shadows, fp32_tails ? *fp32_tails : none, fp32_tails ? tail_off : -1, n, shard_off, chunks,
+      state);
   return launch_status();
 }
 

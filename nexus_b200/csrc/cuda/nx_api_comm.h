@@ -28,10 +28,12 @@ int nx_comm_reduce_shard(const NxPeerTable* grads, int n, int64_t shard_off, int
 int nx_comm_norm_exchange(const double* partial, int nparts, const NxPeerTable* slots, const NxPeerTable* flags,
                           int rank, int n, int epoch, NxOptState* state, int* status, nx_stream_t stream);
 // AdamW on shard-local FP32 state; chunks carry GLOBAL offsets inside [shard_off, shard_off + shard);
-// the BF16 weights are written into every rank's full shadow buffer (the all-gather).
-int nx_comm_adamw_allgather(float* master, const float* grad, float* m, float* v, const NxPeerTable* shadows, int n,
-                            int64_t shard_off, const NxAdamChunk* chunks, int nchunks, const NxOptState* state,
-                            nx_stream_t stream);
+// the BF16 weights are written into every rank's full shadow buffer (the all-gather).  fp32_tails
+// (optional): per rank an FP32 buffer holding the parameters at global offsets >= tail_off, which
+// receive the FP32 values too (norm scales and biases that the model reads in full precision).
+int nx_comm_adamw_allgather(float* master, const float* grad, float* m, float* v, const NxPeerTable* shadows,
+                            const NxPeerTable* fp32_tails, int64_t tail_off, int n, int64_t shard_off,
+                            const NxAdamChunk* chunks, int nchunks, const NxOptState* state, nx_stream_t stream);
 
 // Expert parallelism.  bufs[q]: rank q's [local_experts, capacity, d] BF16 buffer.
 int nx_moe_dispatch(const void* x, const int32_t* token_of, const int32_t* expert_of, const int32_t* slot_of,

@@ -126,6 +126,20 @@ class GptModel:
             self.grads = grads
             self.g = {n: self._view(self.grads, n) for n in PARAM_ORDER}
 
+    def fp32_tail_offset(self) -> int:
+        """Offset of the first 1-D parameter (norm scales and biases follow the matrices in the flat
+        buffer); everything from here on is read by the kernels in FP32."""
+        return self.offsets["ln1_w"]
+
+    def rebind_fp32_tail(self, tail: torch.Tensor) -> None:
+        """Re-points the FP32 views of the 1-D parameters at ``tail`` (same layout as
+        ``params[fp32_tail_offset():]``), e.g. symmetric memory filled by a sharded optimizer."""
+        base = self.fp32_tail_offset()
+        for n in PARAM_ORDER:
+            if self.offsets[n] >= base:
+                o, cnt = self.offsets[n] - base, math.prod(self.shapes[n])
+                self.p[n] = tail[o: o + cnt].view(self.shapes[n])
+
     def refresh_shadow(self) -> None:
         self.params_lp.copy_(self.params)
 

@@ -109,6 +109,12 @@ class FusedShardedOptimizer:
         self.grads.local.zero_()
         self.shadow.local.copy_(model.params_lp)
         model.rebind_buffers(params_lp=self.shadow.local, grads=self.grads.local)
+        # the 1-D parameters (norm scales, biases) are read by the model in FP32: they live in a
+        # symmetric FP32 buffer that the optimizer kernel of their owner fills on every rank
+        self.tail_off = model.fp32_tail_offset()
+        self.tail = ws.alloc(max(N - self.tail_off, 4), torch.float32)
+        self.tail.local[: N - self.tail_off].copy_(model.params[self.tail_off:])
+        model.rebind_fp32_tail(self.tail.local[: N - self.tail_off])
         sl = slice(self.off, self.off + self.count)
         self.master = model.params[sl].clone()
         self.m = torch.zeros(self.count, dtype=torch.float32, device=dev)
@@ -151,7 +157,8 @@ class FusedShardedOptimizer:
         m.grads.zero_()  # every peer has finished reading this rank's gradients
         if self.count > 0 and self.chunks is not None:
             K._check(L.nx_comm_adamw_allgather(K._p(self.master), K._p(self.gshard), K._p(self.m), K._p(self.v),
-                                               C.byref(self.shadow.table), C.c_int(n), C.c_int64(self.off),
+                                               C.byref(self.shadow.table), C.byref(self.tail.table),
+                                               C.c_int64(self.tail_off), C.c_int(n), C.c_int64(self.off),
                                                K._p(self.chunks), C.c_int(self.chunks.nchunks), K._p(m.opt_state),
                                                st), "nx_comm_adamw_allgather")
         ws.barrier()  # updated weights are visible on every rank

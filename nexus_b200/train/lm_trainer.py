@@ -328,7 +328,7 @@ def _make_backend(b: LanguageTrainerBuilder) -> LmBackend:
     if isinstance(model, LmConfig):
         cfg = model
         if use_gpu and cfg.norm == "layernorm" and cfg.mlp == "gelu" and cfg.pos == "learned" and cfg.tie_embeddings \
-                and cfg.bias and b._precision == "bf16" and b._fsdp_pg is None:
+                and cfg.bias and b._precision == "bf16":
             from .gpt_backend import GptLmBackend
             return GptLmBackend(cfg, b._micro_batch, b._seq_len, device=b._device, seed=b._seed,
                                 deterministic=b._deterministic)

@@ -43,6 +43,7 @@ def main():
     tokens = torch.randint(0, cfg.vocab_size, (world, 2, 128), generator=g, dtype=torch.int32).to(dev)
     ref = GptModel(cfg, device=dev, seed=11)
     ref.set_optimizer(AdamWConfig(lr=1e-3))
+    init = ref.params.clone()
     model = GptModel(cfg, device=dev, seed=11)
     model.set_optimizer(AdamWConfig(lr=1e-3))
     opt = FusedShardedOptimizer(model, ws)
@@ -55,10 +56,15 @@ def main():
     torch.cuda.synchronize()
     K.check_status()
     full = opt.gather_master()
-    err = (full - ref.params).abs().max().item()
-    err_lp = (model.params_lp.float() - ref.params_lp.float()).abs().max().item()
+    # Adam's first updates are +-lr whatever the gradient's size, so an element whose tiny gradient
+    # rounds differently (atomic split-K order) moves by 2*lr: compare in L2 relative to the update
+    upd = (ref.params - init).norm().item()
+    err = (full - ref.params).norm().item() / upd
+    err_lp = (model.params_lp.float() - ref.params_lp.float()).norm().item() / upd
+    frac = ((full - ref.params).abs() > 2e-4).float().mean().item()
     s1, s2 = model.read_opt_state(), ref.read_opt_state()
-    check(f"sharded optimizer master err {err:.2e} shadow err {err_lp:.2e}", err < 2e-4 and err_lp < 1e-2)
+    check(f"sharded optimizer rel-L2 master {err:.2e} shadow {err_lp:.2e} outliers {frac:.2e}",
+          err < 0.05 and err_lp < 0.08 and frac < 0.01)
     check(f"grad norm {s1.grad_norm:.5f} vs {s2.grad_norm:.5f}", abs(s1.grad_norm - s2.grad_norm) < 1e-3 * s2.grad_norm)
 
     # ---- distributed GEMM: all-gather fused into the GEMM (A sharded / B sharded) and GEMM -> reduce-scatter
