@@ -497,8 +497,13 @@ class Engine:
         od = torch.float32 if residual is not None else (out_dtype or torch.bfloat16)
         if lin.quant == "w8a8":
             _, x, _ = I.quant_rows(x, lin.inv_smooth, want_codes=False, want_fake=True)
-        if lin.quant != "bf16" and n <= self._skinny and residual is None and act is None and od == torch.bfloat16:
-            return I.wq_gemv(x, lin.wq, lin.scales, bits=8 if lin.quant == "w8a8" else 4, group=lin.group, bias=lin.bias)
+        if lin.quant != "bf16" and n <= self._skinny:   # weights stay packed: the GEMV dequantises on the fly
+            y = I.wq_gemv(x, lin.wq, lin.scales, bits=8 if lin.quant == "w8a8" else 4, group=lin.group, bias=lin.bias)
+            if act == "gelu":
+                y = torch.nn.functional.gelu(y, approximate="tanh")
+            if residual is not None:
+                return residual.add_(y)
+            return y if od == torch.bfloat16 else y.to(od)
         w = lin.dense()
         if n <= self._skinny:
             return I.skinny_gemm(x, w, lin.bias, act=act, residual=residual, out=residual, out_dtype=od)
@@ -615,6 +620,12 @@ class Engine:
         dl = Hl * D
         for l in range(nl):
             lw = self.layers[l]
+            if Hl == 0:   # more ranks than heads: this rank only takes part in the all-reduce
+                x = x + self._all_reduce(torch.zeros_like(x))
+                h2 = self._norm(x, lw["ln2_w"], lw["ln2_b"])
+                f = self._linear(h2, lw["fc"], act="gelu")
+                x = x + self._all_reduce(self._linear(f, lw["fc2"], out_dtype=torch.float32).float())
+                continue
             h = self._norm(x, lw["ln1_w"], lw["ln1_b"])
             qkv = self._linear(h, lw["qkv"])                         # [N, 3 * dl]
             q = qkv[:, :dl].view(N, Hl, D)
