@@ -361,24 +361,37 @@ __global__ void attn_bwd_dsum_kernel(const __nv_bfloat16* __restrict__ o, const 
                                      float* __restrict__ dsum, int B, int T, int H, int HD, int64_t o_row,
                                      int64_t o_head, int64_t o_batch, int64_t do_row, int64_t do_head,
                                      int64_t do_batch) {
-  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  // HD/8 adjacent lanes share one row: 16-byte loads, shuffle reduction inside the lane group
+  const int lpr = HD >> 3;
   const int64_t total = static_cast<int64_t>(B) * H * T;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * warps + (threadIdx.x >> 5); i < total;
-       i += static_cast<int64_t>(gridDim.x) * warps) {
-    const int t = static_cast<int>(i % T);
-    const int h = static_cast<int>((i / T) % H);
-    const int b = static_cast<int>(i / (static_cast<int64_t>(T) * H));
-    const __nv_bfloat16* po = o + b * o_batch + t * o_row + h * o_head;
-    const __nv_bfloat16* pd = d_o + b * do_batch + t * do_row + h * do_head;
+  const int64_t gthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t rows_per_pass = gthreads / lpr;
+  const int sub = threadIdx.x % lpr;
+  for (int64_t base = 0; base < total; base += rows_per_pass) {  // trip count is grid-uniform (shuffles below)
+    const int64_t i = base + (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / lpr;
     float acc = 0.0f;
-    for (int d = lane * 2; d < HD; d += 64) {
-      __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(po + d);
-      __nv_bfloat162 g = *reinterpret_cast<const __nv_bfloat162*>(pd + d);
-      acc += __low2float(a) * __low2float(g) + __high2float(a) * __high2float(g);
-    }
+    if (i < total) {
+      const int h = static_cast<int>(i % H);
+      const int t = static_cast<int>((i / H) % T);
+      const int b = static_cast<int>(i / (static_cast<int64_t>(T) * H));
+      const uint4 a = *reinterpret_cast<const uint4*>(o + b * o_batch + t * o_row + h * o_head + sub * 8);
+      const uint4 g = *reinterpret_cast<const uint4*>(d_o + b * do_batch + t * do_row + h * do_head + sub * 8);
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
 #pragma unroll
-    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-    if (lane == 0) dsum[i] = acc;
+      for (int j = 0; j < 4; ++j) {
+        float a0, a1, g0, g1;
+        unpack_bf16x2(aw[j], a0, a1);
+        unpack_bf16x2(gw[j], g0, g1);
+        acc += a0 * g0 + a1 * g1;
+      }
+    }
+    for (int sft = lpr >> 1; sft > 0; sft >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sft);
+    if (sub == 0 && i < total) {
+      const int h = static_cast<int>(i % H);
+      const int t = static_cast<int>((i / H) % T);
+      const int b = static_cast<int>(i / (static_cast<int64_t>(T) * H));
+      dsum[(static_cast<int64_t>(b) * H + h) * T + t] = acc;
+    }
   }
 }
 
@@ -989,7 +1002,8 @@ extern "C" int nx_attention_bwd(const NxAttnArgs* a, nx_stream_t stream_) {
   // part 0
   {
     const int64_t total = static_cast<int64_t>(a->batch) * a->heads * a->tq;
-    const int blocks = static_cast<int>(std::min<int64_t>((total + 7) / 8, 148 * 16));
+    const int rows_per_block = 256 / (HD / 8);
+    const int blocks = static_cast<int>(std::min<int64_t>((total + rows_per_block - 1) / rows_per_block, 148 * 16));
     attn_bwd_dsum_kernel<<<blocks, 256, 0, st>>>(
         static_cast<const __nv_bfloat16*>(a->o.ptr), static_cast<const __nv_bfloat16*>(a->d_o.ptr), a->dsum, a->batch,
         a->tq, a->heads, HD, a->o.row_stride, a->o.head_stride, a->o.batch_stride, a->d_o.row_stride,

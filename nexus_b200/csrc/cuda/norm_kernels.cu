@@ -257,6 +257,151 @@ int launch_bwd_dx(bool rms, const void* dy, const void* x, const void* gamma, co
   return launch_status();
 }
 
+
+// Fused backward for rows of 128*VPL columns: one pass over dy and x.  A warp keeps its row in
+// registers (VPL float4 per lane), writes dx, and accumulates the column sums of dy*xhat and dy for its
+// own columns over every row it owns; the block then folds its warps through shared memory (fixed
+// order) into partial[block][2][cols].  Rows are assigned round-robin, so the result is deterministic.
+template <typename XT, typename PT, typename GT, typename DT, bool kRms, int VPL>
+__global__ void __launch_bounds__(256)
+norm_bwd_fused_kernel(const GT* __restrict__ dy, const XT* __restrict__ x, const PT* __restrict__ gamma,
+                      const float* __restrict__ mean, const float* __restrict__ rstd, const DT* __restrict__ add,
+                      DT* __restrict__ dx, __nv_bfloat16* __restrict__ dx_lp, float* __restrict__ partial, int rows) {
+  constexpr int kCols = 128 * VPL;
+  __shared__ float s_red[8][128];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float g[VPL][4], ag[VPL][4], ab[VPL][4];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    Vec4<PT>::load(gamma + 4 * (lane + 32 * i), g[i]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ag[i][j] = ab[i][j] = 0.0f;
+  }
+  for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
+    const XT* xr = x + static_cast<int64_t>(row) * kCols;
+    const GT* gr = dy + static_cast<int64_t>(row) * kCols;
+    const float mu = kRms ? 0.0f : mean[row];
+    const float rs = rstd[row];
+    float xh[VPL][4], d[VPL][4];
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      Vec4<XT>::load(xr + 4 * (lane + 32 * i), xh[i]);
+      Vec4<GT>::load(gr + 4 * (lane + 32 * i), d[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        xh[i][j] = (xh[i][j] - mu) * rs;
+        const float gd = g[i][j] * d[i][j];
+        s1 += gd;
+        s2 += gd * xh[i][j];
+        ag[i][j] += d[i][j] * xh[i][j];
+        ab[i][j] += d[i][j];
+      }
+    }
+    s1 = warp_sum(s1) / kCols;
+    s2 = warp_sum(s2) / kCols;
+    if (kRms) s1 = 0.0f;
+    if (dx != nullptr) {
+      DT* dxr = dx + static_cast<int64_t>(row) * kCols;
+      const DT* ar = add ? add + static_cast<int64_t>(row) * kCols : nullptr;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        float o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = rs * (g[i][j] * d[i][j] - s1 - xh[i][j] * s2);
+        if (ar) {
+          float a[4];
+          Vec4<DT>::load(ar + 4 * (lane + 32 * i), a);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o[j] += a[j];
+        }
+        Vec4<DT>::store(dxr + 4 * (lane + 32 * i), o);
+        if (dx_lp) Vec4<__nv_bfloat16>::store(dx_lp + static_cast<int64_t>(row) * kCols + 4 * (lane + 32 * i), o);
+      }
+    }
+  }
+  if (partial == nullptr) return;
+  float* out = partial + static_cast<int64_t>(blockIdx.x) * 2 * kCols;
+#pragma unroll 1
+  for (int which = 0; which < 2; ++which) {
+#pragma unroll 1
+    for (int i = 0; i < VPL; ++i) {
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s_red[warp][lane * 4 + j] = which == 0 ? ag[i][j] : ab[i][j];
+      __syncthreads();
+      if (threadIdx.x < 128) {
+        float t = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) t += s_red[w][threadIdx.x];
+        out[which * kCols + 128 * i + threadIdx.x] = t;
+      }
+    }
+  }
+}
+
+// dgamma / dbeta = sum over chunks of partial[chunk][0/1][c]; block (32 columns x 8 chunk lanes).
+__global__ void norm_bwd_param_final2_kernel(const float* __restrict__ partial, float* __restrict__ dgamma,
+                                             float* __restrict__ dbeta, int cols, int chunks, int accumulate) {
+  __shared__ float sg[8][33];
+  __shared__ float sb[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  float tg = 0.0f, tb = 0.0f;
+  if (c < cols) {
+    for (int k = threadIdx.y; k < chunks; k += 8) {
+      tg += partial[(static_cast<int64_t>(k) * 2 + 0) * cols + c];
+      tb += partial[(static_cast<int64_t>(k) * 2 + 1) * cols + c];
+    }
+  }
+  sg[threadIdx.y][threadIdx.x] = tg;
+  sb[threadIdx.y][threadIdx.x] = tb;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+    tg = tb = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      tg += sg[k][threadIdx.x];
+      tb += sb[k][threadIdx.x];
+    }
+    if (dgamma) dgamma[c] = accumulate ? dgamma[c] + tg : tg;
+    if (dbeta) dbeta[c] = accumulate ? dbeta[c] + tb : tb;
+  }
+}
+
+constexpr int kFusedBwdBlocks = kNumSmsB200 * 2;
+
+template <typename XT, typename PT, typename GT, typename DT, int VPL>
+int launch_bwd_fused_v(bool rms, const void* dy, const void* x, const void* gamma, const float* mean,
+                       const float* rstd, const void* add, void* dx, void* dx_lp, float* partial, int rows,
+                       cudaStream_t st) {
+  const int blocks = std::min(kFusedBwdBlocks, (rows + 7) / 8);
+  if (rms)
+    norm_bwd_fused_kernel<XT, PT, GT, DT, true, VPL><<<blocks, 256, 0, st>>>(
+        (const GT*)dy, (const XT*)x, (const PT*)gamma, mean, rstd, (const DT*)add, (DT*)dx, (__nv_bfloat16*)dx_lp,
+        partial, rows);
+  else
+    norm_bwd_fused_kernel<XT, PT, GT, DT, false, VPL><<<blocks, 256, 0, st>>>(
+        (const GT*)dy, (const XT*)x, (const PT*)gamma, mean, rstd, (const DT*)add, (DT*)dx, (__nv_bfloat16*)dx_lp,
+        partial, rows);
+  return launch_status() != 0 ? -2 : blocks;
+}
+
+// Returns the number of partial chunks written (> 0), 0 when the shape has no fused instance, < 0 on error.
+template <typename XT, typename PT, typename GT, typename DT>
+int launch_bwd_fused(bool rms, const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+                     const void* add, void* dx, void* dx_lp, float* partial, int rows, int cols, cudaStream_t st) {
+#define NX_V(V) case V: return launch_bwd_fused_v<XT, PT, GT, DT, V>(rms, dy, x, gamma, mean, rstd, add, dx, dx_lp, partial, rows, st)
+  if (cols % 128) return 0;
+  switch (cols / 128) {
+    NX_V(2); NX_V(4); NX_V(6); NX_V(8);
+    default: return 0;
+  }
+#undef NX_V
+}
+
 }  // namespace
 
 #include <algorithm>
@@ -280,7 +425,7 @@ extern "C" int nx_norm_fwd(int rms, const void* x, int x_dtype, const void* resi
 }
 
 static size_t nx_norm_bwd_partial_floats(int rows, int cols) {
-  const int chunks = std::max(1, std::min(64, (rows + 255) / 256));
+  const int chunks = std::max(kFusedBwdBlocks, std::max(1, std::min(64, (rows + 255) / 256)));
   return static_cast<size_t>(chunks) * 2 * cols;
 }
 
@@ -296,6 +441,25 @@ extern "C" int nx_norm_bwd(int rms, const void* dy, int dy_dtype, const void* x,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool r = rms != 0;
   int rc = -1;
+  const bool want_params = dgamma != nullptr || dbeta != nullptr;
+  if (want_params && scratch == nullptr) return -1;
+  {  // single-pass path (dx and the parameter partials from one read of dy and x)
+    int chunks = 0;
+#define NX_FUSED(XT, PT, GT, DT) \
+  chunks = launch_bwd_fused<XT, PT, GT, DT>(r, dy, x, gamma, mean, rstd, add, dx, dx_lp, want_params ? scratch : nullptr, rows, cols, st)
+    if (x_dtype == NX_F32 && param_dtype == NX_F32 && dy_dtype == NX_BF16 && (dx == nullptr || dx_dtype == NX_F32))
+      NX_FUSED(float, float, __nv_bfloat16, float);
+    else if (x_dtype == NX_BF16 && param_dtype == NX_F32 && dy_dtype == NX_BF16 && (dx == nullptr || dx_dtype == NX_BF16))
+      NX_FUSED(__nv_bfloat16, float, __nv_bfloat16, __nv_bfloat16);
+#undef NX_FUSED
+    if (chunks < 0) return chunks;
+    if (chunks > 0) {
+      if (!want_params) return 0;
+      dim3 grid2((cols + 31) / 32), block2(32, 8);
+      norm_bwd_param_final2_kernel<<<grid2, block2, 0, st>>>(scratch, dgamma, dbeta, cols, chunks, accumulate_params);
+      return launch_status();
+    }
+  }
 #define NX_BWD(XT, PT, GT, DT) rc = launch_bwd_dx<XT, PT, GT, DT>(r, dy, x, gamma, mean, rstd, add, dx, dx_lp, rows, cols, st)
   if (dx != nullptr) {
     if (x_dtype == NX_F32 && param_dtype == NX_F32 && dy_dtype == NX_BF16 && dx_dtype == NX_F32)

@@ -406,6 +406,41 @@ __global__ void adamw_kernel(float* __restrict__ master, const GT* __restrict__ 
   const float b1 = st->beta1, b2 = st->beta2, omb1 = __fsub_rn(1.0f, b1), omb2 = __fsub_rn(1.0f, b2);
   const float i1 = st->inv_bias1, i2 = st->inv_bias2, eps = st->eps, clip = st->clip_coef;
   const float lrwd = __fmul_rn(lr, wd);
+  if (sizeof(GT) == 4 && sizeof(ST) == 2 && sr_seed == 0 && shadow != nullptr && (ch.offset & 3) == 0 &&
+      (ch.count & 3) == 0) {
+    // 16-byte path (same per-element op order): one pass updates p/m/v, the shadow and clears the gradient
+    float4* g4 = reinterpret_cast<float4*>(const_cast<GT*>(grad) + ch.offset);
+    float4* p4 = reinterpret_cast<float4*>(master + ch.offset);
+    float4* m4 = reinterpret_cast<float4*>(m + ch.offset);
+    float4* v4 = reinterpret_cast<float4*>(v + ch.offset);
+    uint2* s2 = reinterpret_cast<uint2*>(shadow + ch.offset);
+    const int n4 = static_cast<int>(ch.count >> 2);
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 gq = g4[i];
+      float4 pq = p4[i], mq = m4[i], vq = v4[i];
+      float gg[4] = {gq.x, gq.y, gq.z, gq.w}, pp[4] = {pq.x, pq.y, pq.z, pq.w}, mm[4] = {mq.x, mq.y, mq.z, mq.w},
+            vv[4] = {vq.x, vq.y, vq.z, vq.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float g = __fmul_rn(gg[j], clip);
+        float p = pp[j];
+        p = __fsub_rn(p, __fmul_rn(lrwd, p));
+        const float mi = __fadd_rn(__fmul_rn(b1, mm[j]), __fmul_rn(omb1, g));
+        const float vi = __fadd_rn(__fmul_rn(b2, vv[j]), __fmul_rn(omb2, __fmul_rn(g, g)));
+        p = __fsub_rn(p, __fdiv_rn(__fmul_rn(lr, __fmul_rn(mi, i1)), __fadd_rn(__fsqrt_rn(__fmul_rn(vi, i2)), eps)));
+        pp[j] = p;
+        mm[j] = mi;
+        vv[j] = vi;
+      }
+      p4[i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
+      m4[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+      v4[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(pp[0], pp[1]), hi = __floats2bfloat162_rn(pp[2], pp[3]);
+      s2[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+      if (zero_grad) g4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    return;
+  }
   for (int64_t i = ch.offset + threadIdx.x; i < ch.offset + ch.count; i += blockDim.x) {
     const float g = __fmul_rn(Num<GT>::load(grad + i), clip);
     float p = master[i];
