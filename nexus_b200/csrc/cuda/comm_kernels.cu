@@ -181,6 +181,61 @@ adamw_shard_allgather_kernel(float* __restrict__ master, const float* __restrict
 }
 
 // ------------------------------------------------------------------------------------------------
+// all-reduce over peer memory with the cast fused in: the owner of [shard_off, shard_off + count) pulls
+// that range from every rank's input buffer (FP32 or BF16), sums in rank order in FP32, scales, and
+// stores the result (FP32 or BF16) into the output buffer of n_out ranks (n_out = n: two-shot
+// all-reduce; n_out = 1: only this rank's copy, i.e. a one-shot all-reduce when the range is the whole
+// buffer).  16-byte accesses: offsets and counts are multiples of 8 elements.
+// ------------------------------------------------------------------------------------------------
+template <typename IT, typename OT>
+__global__ void __launch_bounds__(256)
+allreduce_shard_kernel(NxPeerTable in, int n_in, NxPeerTable out, int n_out, int64_t shard_off, int64_t count,
+                       float scale) {
+  constexpr int V = 8;
+  const int64_t nvec = count / V;
+  NX_GRID_STRIDE(i, nvec) {
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0.0f;
+#pragma unroll 1
+    for (int p = 0; p < n_in; ++p) {
+      const IT* src = reinterpret_cast<const IT*>(in.ptr[p]) + shard_off + i * V;
+      if (sizeof(IT) == 4) {
+        const float4 a = reinterpret_cast<const float4*>(src)[0], b = reinterpret_cast<const float4*>(src)[1];
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+        acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+      } else {
+        const uint4 q = *reinterpret_cast<const uint4*>(src);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[j]);
+          acc[2 * j] += __low2float(h);
+          acc[2 * j + 1] += __high2float(h);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] *= scale;
+#pragma unroll 1
+    for (int q = 0; q < n_out; ++q) {
+      OT* dst = reinterpret_cast<OT*>(out.ptr[q]) + shard_off + i * V;
+      if (sizeof(OT) == 4) {
+        reinterpret_cast<float4*>(dst)[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        reinterpret_cast<float4*>(dst)[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      } else {
+        uint4 w;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(acc[0], acc[1]), h1 = __floats2bfloat162_rn(acc[2], acc[3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[4], acc[5]), h3 = __floats2bfloat162_rn(acc[6], acc[7]);
+        w.x = *reinterpret_cast<uint32_t*>(&h0); w.y = *reinterpret_cast<uint32_t*>(&h1);
+        w.z = *reinterpret_cast<uint32_t*>(&h2); w.w = *reinterpret_cast<uint32_t*>(&h3);
+        *reinterpret_cast<uint4*>(dst) = w;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // MoE expert-parallel dispatch / combine over peer memory
 // ------------------------------------------------------------------------------------------------
 // Row r of the permuted token matrix belongs to global expert e = expert_of[r] at slot slot_of[r]
@@ -188,16 +243,33 @@ adamw_shard_allgather_kernel(float* __restrict__ master, const float* __restrict
 __global__ void moe_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ token_of,
                                     const int32_t* __restrict__ expert_of, const int32_t* __restrict__ slot_of,
                                     NxPeerTable bufs, int rows, int d, int local_experts, int capacity,
-                                    int src_rank, int n_ranks) {
+                                    int src_rank, int n_ranks, const float* __restrict__ row_scale, int rows_per_token) {
   const int vec = d >> 3;  // 16-byte vectors
   for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    if (slot_of[r] < 0) continue;  // dropped by the capacity limit
     const int e = expert_of[r];
     const int owner = e / local_experts, le = e % local_experts;
     // each source rank owns a disjoint slice of the capacity: slot indices are global per expert
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(bufs.ptr[owner]) +
                          (static_cast<int64_t>(le) * capacity + slot_of[r]) * d;
-    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(token_of[r]) * d);
-    for (int i = threadIdx.x; i < vec; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = src[i];
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(token_of ? token_of[r] : r / rows_per_token) * d);
+    if (row_scale == nullptr) {
+      for (int i = threadIdx.x; i < vec; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = src[i];
+    } else {  // scaled copy (backward of the gate-weighted combine)
+      const float sc = row_scale[r];
+      for (int i = threadIdx.x; i < vec; i += blockDim.x) {
+        const uint4 q = src[i];
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float lo, hi;
+          unpack_bf16x2(w[j], lo, hi);
+          o[j] = pack_bf16x2(lo * sc, hi * sc);
+        }
+        reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
   }
   (void)src_rank;
   (void)n_ranks;
@@ -315,15 +387,33 @@ extern "C" int nx_comm_adamw_allgather(float* master, const float* grad, float* 
   return launch_status();
 }
 
+extern "C" int nx_comm_allreduce_shard(const NxPeerTable* in, int in_dtype, int n_in, const NxPeerTable* out,
+                                       int out_dtype, int n_out, int64_t shard_off, int64_t count, float scale,
+                                       nx_stream_t stream) {
+  if (in == nullptr || out == nullptr || n_in < 1 || n_in > NX_MAX_PEERS || n_out < 1 || n_out > NX_MAX_PEERS) return -1;
+  if (count <= 0) return 0;
+  if ((shard_off & 7) || (count & 7)) return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int blocks = blocks_for(count / 8, 256, 148 * 8);
+#define NX_AR(IT, OT) allreduce_shard_kernel<IT, OT><<<blocks, 256, 0, st>>>(*in, n_in, *out, n_out, shard_off, count, scale)
+  if (in_dtype == NX_F32 && out_dtype == NX_F32) NX_AR(float, float);
+  else if (in_dtype == NX_BF16 && out_dtype == NX_F32) NX_AR(__nv_bfloat16, float);
+  else if (in_dtype == NX_BF16 && out_dtype == NX_BF16) NX_AR(__nv_bfloat16, __nv_bfloat16);
+  else if (in_dtype == NX_F32 && out_dtype == NX_BF16) NX_AR(float, __nv_bfloat16);
+  else return -1;
+#undef NX_AR
+  return launch_status();
+}
+
 extern "C" int nx_moe_dispatch(const void* x, const int32_t* token_of, const int32_t* expert_of, const int32_t* slot_of,
                                const NxPeerTable* bufs, int rows, int d, int local_experts, int capacity, int src_rank,
-                               int n_ranks, nx_stream_t stream) {
+                               int n_ranks, const float* row_scale, int rows_per_token, nx_stream_t stream) {
   if (bufs == nullptr || rows < 0 || d <= 0 || (d & 7)) return -1;
   if (rows == 0) return 0;
   const int blocks = rows < 148 * 8 ? rows : 148 * 8;
   moe_dispatch_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), token_of, expert_of, slot_of, *bufs, rows, d, local_experts, capacity,
-      src_rank, n_ranks);
+      src_rank, n_ranks, row_scale, rows_per_token < 1 ? 1 : rows_per_token);
   return launch_status();
 }
 

@@ -49,6 +49,11 @@ struct DevParams {
   int tiles_m, tiles_n, kb_total, kb_per_slice;
   int num_units;
   float alpha;
+  // 8-bit float inputs: 128 elements per 128-byte swizzle row, kind::f8f6f4 MMA (K = 32 per instruction)
+  int fp8, bk_elems;
+  const float* scale_a;   // [m] per-row scale of A (may be null)
+  const float* scale_b;   // [n] per-row scale of B (may be null)
+  unsigned int* amax_out;  // max |out| as float bits (may be null)
 };
 
 struct Unit {
@@ -226,7 +231,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           uint8_t* sa = stage_base + stage * C::kStageBytes;
           uint8_t* sb = sa + C::kABytes;
           mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
-          const int k0 = kb * kBK;
+          const int k0 = kb * p.bk_elems;
           const CUtensorMap* ma = &tmap_a;
           const CUtensorMap* mb = &tmap_b;
           int am0 = w.m0, bn0 = n0;
@@ -296,7 +301,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             const uint32_t b_addr = B_MN ? sb + ks * 2048 : sb + ks * 32;
             const uint64_t da = make_smem_desc_sw128(a_addr, A_MN ? 64 * kBK * 2 : 16, 1024);
             const uint64_t db = make_smem_desc_sw128(b_addr, B_MN ? 64 * kBK * 2 : 16, 1024);
-            umma_f16_ss(tmem_d, da, db, idesc, (kb > w.kb_begin || ks > 0) ? 1u : 0u);
+            if (p.fp8)
+              umma_f8_ss(tmem_d, da, db, idesc, (kb > w.kb_begin || ks > 0) ? 1u : 0u);
+            else
+              umma_f16_ss(tmem_d, da, db, idesc, (kb > w.kb_begin || ks > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == C::kStages) {
@@ -342,6 +350,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        if (p.scale_a != nullptr) {
+          const float sa_row = p.scale_a[row];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] *= sa_row;
+        }
+        if (p.scale_b != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] *= (j < valid) ? p.scale_b[col0 + j] : 0.0f;
+        }
 
         if constexpr (DIST) {
           if (dist.out_scatter) {
@@ -426,6 +443,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] += q[j];
         }
+        if (p.amax_out != nullptr) {  // non-negative floats order like their bit patterns
+          float am = 0.0f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < valid) am = fmaxf(am, fabsf(v[j]));
+          if (am > 0.0f) atomicMax(p.amax_out, __float_as_uint(am));
+        }
         if (p.out_dtype == NX_F32)
           store_row32_f32(reinterpret_cast<float*>(p.out) + out_off, out_vec, valid, v);
         else
@@ -459,7 +483,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
 template <int BN, bool A_MN, bool B_MN, bool DIST = false>
 int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const DevParams& p, uint32_t in_fmt, int grid,
-                   cudaStream_t stream, const DistParam<DIST>& dist = DistParam<DIST>{}) {
+                   cudaStream_t stream, const DistParam<DIST>& dist = DistParam<DIST>{}, int fmt_b = -1) {
   using C = Cfg<BN>;
   static bool attr_set = false;
   auto kern = gemm_kernel<BN, A_MN, B_MN, DIST>;
@@ -468,7 +492,7 @@ int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const DevParams
       return -2;
     attr_set = true;
   }
-  const uint32_t idesc = make_idesc(in_fmt, in_fmt, A_MN, B_MN, kBM, BN);
+  const uint32_t idesc = make_idesc(in_fmt, fmt_b < 0 ? in_fmt : static_cast<uint32_t>(fmt_b), A_MN, B_MN, kBM, BN);
   kern<<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, p, idesc, dist);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -521,13 +545,18 @@ extern "C" int nx_splitk_reduce(const float* workspace, void* out, int out_dtype
 extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (a == nullptr || a->m <= 0 || a->n <= 0 || a->k <= 0 || a->batch <= 0) return -1;
-  if (a->in_dtype != NX_BF16 && a->in_dtype != NX_F16) return -1;
+  const bool fp8 = a->in_dtype == NX_E4M3 || a->in_dtype == NX_E5M2;
+  if (a->in_dtype != NX_BF16 && a->in_dtype != NX_F16 && !fp8) return -1;
   if (a->out_dtype != NX_BF16 && a->out_dtype != NX_F32) return -1;
   if (a->status == nullptr) return -1;
+  const int b_dtype = a->b_dtype_plus1 > 0 ? a->b_dtype_plus1 - 1 : a->in_dtype;
+  if (fp8 && (a->a_mn_major || a->b_mn_major || (b_dtype != NX_E4M3 && b_dtype != NX_E5M2))) return -1;
+  if (!fp8 && b_dtype != a->in_dtype) return -1;
   // TMA: base 16-byte aligned, every non-innermost stride a multiple of 16 bytes.
+  const int pitch_mask = fp8 ? 15 : 7;
   if ((reinterpret_cast<uintptr_t>(a->a) & 15) || (reinterpret_cast<uintptr_t>(a->b) & 15)) return -1;
-  if ((a->lda & 7) || (a->ldb & 7)) return -1;
-  if (a->batch > 1 && ((a->stride_a & 7) || (a->stride_b & 7))) return -1;
+  if ((a->lda & pitch_mask) || (a->ldb & pitch_mask)) return -1;
+  if (a->batch > 1 && ((a->stride_a & pitch_mask) || (a->stride_b & pitch_mask))) return -1;
   int split = a->split_k < 1 ? 1 : a->split_k;
   if (split > 1 && a->batch != 1) return -1;
   if (split > 1 && a->accumulate == 2 && a->out_dtype != NX_F32) return -1;
@@ -536,7 +565,8 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
   int bn = a->block_n;
   if (bn != 128 && bn != 256) bn = (a->n >= 256) ? 256 : 128;
 
-  const int kb_total = (a->k + kBK - 1) / kBK;
+  const int bk = fp8 ? 2 * kBK : kBK;  // elements per 128-byte swizzle row
+  const int kb_total = (a->k + bk - 1) / bk;
   if (split > kb_total) split = kb_total;
   int kb_per = (kb_total + split - 1) / split;
   split = (kb_total + kb_per - 1) / kb_per;
@@ -569,20 +599,27 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
   p.kb_per_slice = kb_per;
   p.num_units = p.tiles_m * p.tiles_n * split * a->batch;
   p.alpha = a->alpha;
+  p.fp8 = fp8 ? 1 : 0;
+  p.bk_elems = bk;
+  p.scale_a = a->scale_a;
+  p.scale_b = a->scale_b;
+  p.amax_out = reinterpret_cast<unsigned int*>(a->amax_out);
 
-  const CUtensorMapDataType dt =
-      a->in_dtype == NX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                     : (a->in_dtype == NX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  const int eb = fp8 ? 1 : 2;
   CUtensorMap ta, tb;
   const uint64_t sa = a->batch > 1 ? static_cast<uint64_t>(a->stride_a) : 0;
   const uint64_t sb = a->batch > 1 ? static_cast<uint64_t>(a->stride_b) : 0;
   int rc;
   if (!a->a_mn_major)
-    rc = nx::make_tensor_map_3d(&ta, dt, 2, a->a, a->k, a->m, a->batch, a->lda, sa, kBK, kBM);
+    rc = nx::make_tensor_map_3d(&ta, dt, eb, a->a, a->k, a->m, a->batch, a->lda, sa, bk, kBM);
   else
     rc = nx::make_tensor_map_3d(&ta, dt, 2, a->a, a->m, a->k, a->batch, a->lda, sa, 64, kBK);
   if (rc != 0) return rc;
   if (!a->b_mn_major)
-    rc = nx::make_tensor_map_3d(&tb, dt, 2, a->b, a->k, a->n, a->batch, a->ldb, sb, kBK, bn);
+    rc = nx::make_tensor_map_3d(&tb, dt, eb, a->b, a->k, a->n, a->batch, a->ldb, sb, bk, bn);
   else
     rc = nx::make_tensor_map_3d(&tb, dt, 2, a->b, a->n, a->k, a->batch, a->ldb, sb, 64, kBK);
   if (rc != 0) return rc;
@@ -591,9 +628,11 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
   if (sms <= 0) return -2;
   if (a->max_ctas > 0 && a->max_ctas < sms) sms = a->max_ctas;
   const int grid = p.num_units < sms ? p.num_units : sms;
-  const uint32_t fmt = a->in_dtype == NX_BF16 ? kFmtBF16 : kFmtF16;
+  const uint32_t fmt = fp8 ? (a->in_dtype == NX_E4M3 ? kFmtE4M3 : kFmtE5M2) : (a->in_dtype == NX_BF16 ? kFmtBF16 : kFmtF16);
+  const int fmt_b = fp8 ? static_cast<int>(b_dtype == NX_E4M3 ? kFmtE4M3 : kFmtE5M2) : -1;
 
-#define NX_LAUNCH(BN_, AM_, BM_) rc = launch_variant<BN_, AM_, BM_>(ta, tb, p, fmt, grid, stream)
+#define NX_LAUNCH(BN_, AM_, BM_) \
+  rc = launch_variant<BN_, AM_, BM_>(ta, tb, p, fmt, grid, stream, DistParam<false>{}, fmt_b)
   if (bn == 256) {
     if (!a->a_mn_major && !a->b_mn_major) NX_LAUNCH(256, false, false);
     else if (!a->a_mn_major && a->b_mn_major) NX_LAUNCH(256, false, true);

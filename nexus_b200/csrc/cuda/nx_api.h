@@ -36,7 +36,7 @@ typedef struct NxGemmArgs {
   int64_t stride_a, stride_b, stride_o;  // batch strides in elements
   int32_t m, n, k, batch;
   int32_t a_mn_major, b_mn_major;
-  int32_t in_dtype;   // NX_BF16 or NX_F16
+  int32_t in_dtype;   // NX_BF16, NX_F16, or NX_E4M3 / NX_E5M2 (8-bit: K-major operands, pitches % 16 == 0)
   int32_t out_dtype;  // NX_BF16 or NX_F32
   int32_t bias_dtype, res_dtype;
   int32_t act;
@@ -45,6 +45,10 @@ typedef struct NxGemmArgs {
   int32_t block_n;  // 0 = choose; else 128 or 256
   float alpha;
   int32_t max_ctas;  // 0 = one per SM
+  int32_t b_dtype_plus1;  // 8-bit inputs: dtype of B plus one (0: same as A), e.g. E5M2 grads x E4M3 weights
+  const float* scale_a;   // [M] per-row dequantisation scale of A, may be null
+  const float* scale_b;   // [N] per-row dequantisation scale of B, may be null
+  float* amax_out;        // receives max |out| (must be zeroed by the caller), may be null
 } NxGemmArgs;
 
 int nx_gemm(const NxGemmArgs* args, nx_stream_t stream);

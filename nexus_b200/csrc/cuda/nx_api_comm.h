@@ -35,10 +35,18 @@ int nx_comm_adamw_allgather(float* master, const float* grad, float* m, float* v
                             const NxPeerTable* fp32_tails, int64_t tail_off, int n, int64_t shard_off,
                             const NxAdamChunk* chunks, int nchunks, const NxOptState* state, nx_stream_t stream);
 
-// Expert parallelism.  bufs[q]: rank q's [local_experts, capacity, d] BF16 buffer.
+// All-reduce with the cast fused in.  The caller owns [shard_off, shard_off + count) (multiples of 8
+// elements): it sums that range over the n_in input buffers (FP32 or BF16, rank order, FP32 math),
+// scales, and stores into the first n_out output buffers (FP32 or BF16).  Bracket with nx_comm_barrier.
+int nx_comm_allreduce_shard(const NxPeerTable* in, int in_dtype, int n_in, const NxPeerTable* out, int out_dtype,
+                            int n_out, int64_t shard_off, int64_t count, float scale, nx_stream_t stream);
+
+// Expert parallelism.  bufs[q]: rank q's [local_experts, capacity, d] BF16 buffer.  Row r of the
+// assignment list goes to expert expert_of[r], slot slot_of[r] (negative: dropped, skipped); its source
+// row is x[token_of[r]] (token_of null: x[r / rows_per_token]); row_scale (optional) multiplies the copy.
 int nx_moe_dispatch(const void* x, const int32_t* token_of, const int32_t* expert_of, const int32_t* slot_of,
                     const NxPeerTable* bufs, int rows, int d, int local_experts, int capacity, int src_rank,
-                    int n_ranks, nx_stream_t stream);
+                    int n_ranks, const float* row_scale, int rows_per_token, nx_stream_t stream);
 int nx_moe_combine(const NxPeerTable* bufs, const int32_t* expert, const int32_t* slot, const float* gate, void* y,
                    int tokens, int top_k, int d, int local_experts, int capacity, nx_stream_t stream);
 

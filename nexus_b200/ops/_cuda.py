@@ -25,6 +25,7 @@ _DT = {torch.bfloat16: BF16, torch.float32: F32, torch.float16: F16}
 if hasattr(torch, "float8_e4m3fn"):
     _DT[torch.float8_e4m3fn] = E4M3
     _DT[torch.float8_e5m2] = E5M2
+_FP8 = tuple(t for t in (getattr(torch, "float8_e4m3fn", None), getattr(torch, "float8_e5m2", None)) if t is not None)
 
 
 class GemmArgs(C.Structure):
@@ -38,7 +39,8 @@ class GemmArgs(C.Structure):
         ("a_mn_major", C.c_int32), ("b_mn_major", C.c_int32),
         ("in_dtype", C.c_int32), ("out_dtype", C.c_int32), ("bias_dtype", C.c_int32), ("res_dtype", C.c_int32),
         ("act", C.c_int32), ("accumulate", C.c_int32), ("split_k", C.c_int32), ("block_n", C.c_int32),
-        ("alpha", C.c_float), ("max_ctas", C.c_int32),
+        ("alpha", C.c_float), ("max_ctas", C.c_int32), ("b_dtype_plus1", C.c_int32),
+        ("scale_a", C.c_void_p), ("scale_b", C.c_void_p), ("amax_out", C.c_void_p),
     ]
 
 
@@ -143,7 +145,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
          aux_in: Optional[torch.Tensor] = None, aux_out: Optional[torch.Tensor] = None,
          residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
          out_dtype: Optional[torch.dtype] = None, accumulate: bool = False, alpha: float = 1.0,
-         split_k: int = 1, block_n: int = 0, max_ctas: int = 0, deterministic: bool = False) -> torch.Tensor:
+         split_k: int = 1, block_n: int = 0, max_ctas: int = 0, deterministic: bool = False,
+         scale_a: Optional[torch.Tensor] = None, scale_b: Optional[torch.Tensor] = None,
+         amax_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out = epilogue(alpha * A @ B^T)`` with A logical [M, K], B logical [N, K].
 
     ``a_mn`` / ``b_mn``: the operand is stored transposed ([K, M] / [K, N], i.e. reduction-major).
@@ -164,10 +168,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         raise ValueError(f"gemm: reduction sizes differ ({k} vs {kb})")
     if a.stride(-1) != 1 or b.stride(-1) != 1:
         raise ValueError("gemm: innermost stride must be 1")
-    if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16):
-        raise ValueError("gemm: operands must both be bf16 or fp16")
+    fp8 = a.dtype in _FP8
+    if fp8:
+        if b.dtype not in _FP8 or a_mn or b_mn:
+            raise ValueError("gemm: 8-bit operands must both be FP8 and K-major")
+    elif a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16):
+        raise ValueError("gemm: operands must both be bf16 or fp16 (or both FP8)")
     if out is None:
-        od = out_dtype or a.dtype
+        od = out_dtype or (torch.bfloat16 if fp8 else a.dtype)
         out = torch.empty((batch, m, n) if batched else (m, n), dtype=od, device=a.device)
     g = GemmArgs()
     g.a, g.b, g.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
@@ -177,6 +185,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     g.m, g.n, g.k, g.batch = m, n, k, batch
     g.a_mn_major, g.b_mn_major = int(a_mn), int(b_mn)
     g.in_dtype, g.out_dtype = _DT[a.dtype], _DT[out.dtype]
+    if fp8:
+        g.b_dtype_plus1 = _DT[b.dtype] + 1
+    if scale_a is not None:
+        g.scale_a = scale_a.data_ptr()
+    if scale_b is not None:
+        g.scale_b = scale_b.data_ptr()
+    if amax_out is not None:
+        g.amax_out = amax_out.data_ptr()
     if bias is not None:
         g.bias, g.bias_dtype = bias.data_ptr(), _DT[bias.dtype]
     if aux_in is not None:

@@ -173,6 +173,36 @@ class FusedShardedOptimizer:
         return out[: self.model.num_params]
 
 
+def fused_all_reduce(ws: SymmetricWorkspace, src: SymmetricBuffer, dst: SymmetricBuffer, count: int, *,
+                     scale: float = 1.0, one_shot: Optional[bool] = None) -> None:
+    """All-reduce (sum * scale) of ``src`` over the group into ``dst`` on every rank, with the dtype
+    conversion fused into the reduction (e.g. BF16-compressed gradients in, FP32 out).  Two-shot
+    (each rank reduces one slice and stores it to every rank) for large buffers, one-shot (each rank
+    reduces the whole buffer for itself) for small ones.  ``count`` must be a multiple of 8."""
+    n, r = ws.n, ws.rank
+    if count % 8:
+        raise ValueError("fused_all_reduce: count must be a multiple of 8 elements")
+    if one_shot is None:
+        one_shot = count * src.local.element_size() <= (256 << 10)
+    dt_in, dt_out = K._DT[src.local.dtype], K._DT[dst.local.dtype]
+    L = K.lib()
+    ws.barrier()
+    if one_shot:
+        own = _table([dst.ptrs[r]])
+        K._check(L.nx_comm_allreduce_shard(C.byref(src.table), C.c_int(dt_in), C.c_int(n), C.byref(own), C.c_int(dt_out),
+                                           C.c_int(1), C.c_int64(0), C.c_int64(count), C.c_float(scale), K._stream()),
+                 "nx_comm_allreduce_shard")
+    else:
+        per = (-(-count // n) + 7) // 8 * 8
+        off = min(count, r * per)
+        cnt = max(0, min(per, count - off))
+        if cnt > 0:
+            K._check(L.nx_comm_allreduce_shard(C.byref(src.table), C.c_int(dt_in), C.c_int(n), C.byref(dst.table),
+                                               C.c_int(dt_out), C.c_int(n), C.c_int64(off), C.c_int64(cnt),
+                                               C.c_float(scale), K._stream()), "nx_comm_allreduce_shard")
+    ws.barrier()
+
+
 def gemm_dist(ws: SymmetricWorkspace, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *,
               a_peers: Optional[SymmetricBuffer] = None, b_peers: Optional[SymmetricBuffer] = None,
               out_peers: Optional[SymmetricBuffer] = None, bias=None, act=None, m: Optional[int] = None,
@@ -206,10 +236,13 @@ def gemm_dist(ws: SymmetricWorkspace, a: torch.Tensor, b: torch.Tensor, out: tor
     return out
 
 
-def moe_dispatch(ws, x, token_of, expert_of, slot_of, bufs: SymmetricBuffer, local_experts: int, capacity: int):
+def moe_dispatch(ws, x, token_of, expert_of, slot_of, bufs: SymmetricBuffer, local_experts: int, capacity: int,
+                 row_scale=None, rows_per_token: int = 1):
+    rows = expert_of.numel()
     K._check(K.lib().nx_moe_dispatch(K._p(x), K._p(token_of), K._p(expert_of), K._p(slot_of), C.byref(bufs.table),
-                                     C.c_int(token_of.numel()), C.c_int(x.shape[1]), C.c_int(local_experts),
-                                     C.c_int(capacity), C.c_int(ws.rank), C.c_int(ws.n), K._stream()), "nx_moe_dispatch")
+                                     C.c_int(rows), C.c_int(x.shape[1]), C.c_int(local_experts),
+                                     C.c_int(capacity), C.c_int(ws.rank), C.c_int(ws.n), K._p(row_scale),
+                                     C.c_int(rows_per_token), K._stream()), "nx_moe_dispatch")
 
 
 def moe_combine(ws, bufs: SymmetricBuffer, expert, slot, gate, y, local_experts: int, capacity: int):

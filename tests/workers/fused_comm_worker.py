@@ -11,8 +11,8 @@ from nexus_b200.lm.config import preset  # noqa: E402
 from nexus_b200.models.gpt import AdamWConfig, GptModel  # noqa: E402
 from nexus_b200.ops import _cuda as K  # noqa: E402
 from nexus_b200.parallel.process_group import init_process_group  # noqa: E402
-from nexus_b200.parallel.symm import (FusedShardedOptimizer, SymmetricWorkspace, gemm_dist, moe_combine,  # noqa: E402
-                                      moe_dispatch)
+from nexus_b200.parallel.symm import (FusedShardedOptimizer, SymmetricWorkspace, fused_all_reduce, gemm_dist,  # noqa: E402
+                                      moe_combine, moe_dispatch)
 
 
 def main():
@@ -66,6 +66,19 @@ def main():
     check(f"sharded optimizer rel-L2 master {err:.2e} shadow {err_lp:.2e} outliers {frac:.2e}",
           err < 0.05 and err_lp < 0.08 and frac < 0.01)
     check(f"grad norm {s1.grad_norm:.5f} vs {s2.grad_norm:.5f}", abs(s1.grad_norm - s2.grad_norm) < 1e-3 * s2.grad_norm)
+
+    # ---- all-reduce with the cast fused in (BF16 in -> FP32 out), two-shot and one-shot
+    for count, one_shot in ((1 << 20, False), (4096, True), (1000 * 8, False)):
+        src = ws.alloc(count, torch.bfloat16)
+        dst = ws.alloc(count, torch.float32)
+        gen = torch.Generator(device=dev).manual_seed(100 + rank)
+        src.local.copy_(torch.randn(count, device=dev, generator=gen).bfloat16())
+        want = src.local.float().clone()
+        pg.all_reduce_tensor(want)
+        fused_all_reduce(ws, src, dst, count, scale=0.5, one_shot=one_shot)
+        torch.cuda.synchronize()
+        check(f"fused all-reduce bf16->fp32 n={count} one_shot={one_shot}",
+              (dst.local - 0.5 * want).abs().max().item() < 1e-5)
 
     # ---- distributed GEMM: all-gather fused into the GEMM (A sharded / B sharded) and GEMM -> reduce-scatter
     torch.manual_seed(5)
