@@ -39,6 +39,8 @@ struct AttnDev {
   int causal, window;  // window <= 0: unlimited
   int hfirst;          // TMA coordinate order, see load_tile
   float scale;
+  float* merge_o;      // fwd: FP32 [B,Tq,H,D] running output of earlier key/value chunks (in/out), or null
+  float* merge_lse;    // fwd: FP32 [B,H,Tq] running log-sum-exp (in/out)
 };
 
 // byte offset of the 16-byte chunk (8 bf16) `chunk` (0..7) of row `r` inside a [rows][64] swizzled slab
@@ -321,6 +323,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int c = 0; c < 32; ++c) o_acc[cc * 32 + c] = o_acc[cc * 32 + c] * alpha + __uint_as_float(v[c]);
       }
       tc_fence_before_sync();
+    }
+    if (ok && q < p.Tq && p.merge_o != nullptr) {
+      // merge with the result of earlier key/value chunks: softmax over the union of the key sets
+      const int64_t li = (static_cast<int64_t>(b) * p.H + h) * p.Tq + q;
+      float* mo = p.merge_o + ((static_cast<int64_t>(b) * p.Tq + q) * p.H + h) * HD;
+      const float lse_new = l_run > 0.0f ? (m_run / kLog2e + logf(l_run)) : -INFINITY;
+      const float lse_old = p.merge_lse[li];
+      const float mm = fmaxf(lse_new, lse_old);
+      const float w_new = (lse_new == -INFINITY) ? 0.0f : __expf(lse_new - mm);
+      const float w_old = (lse_old == -INFINITY) ? 0.0f : __expf(lse_old - mm);
+      const float den = w_new + w_old;
+      const float c_new = den > 0.0f ? w_new / den / (l_run > 0.0f ? l_run : 1.0f) : 0.0f;
+      const float c_old = den > 0.0f ? w_old / den : 0.0f;
+#pragma unroll
+      for (int g = 0; g < HD / 4; ++g) {
+        float4 prev = reinterpret_cast<const float4*>(mo)[g];
+        prev.x = prev.x * c_old + o_acc[4 * g + 0] * c_new;
+        prev.y = prev.y * c_old + o_acc[4 * g + 1] * c_new;
+        prev.z = prev.z * c_old + o_acc[4 * g + 2] * c_new;
+        prev.w = prev.w * c_old + o_acc[4 * g + 3] * c_new;
+        reinterpret_cast<float4*>(mo)[g] = prev;
+        o_acc[4 * g + 0] = prev.x;
+        o_acc[4 * g + 1] = prev.y;
+        o_acc[4 * g + 2] = prev.z;
+        o_acc[4 * g + 3] = prev.w;
+      }
+      p.merge_lse[li] = den > 0.0f ? mm + logf(den) : -INFINITY;
+      l_run = 1.0f;                       // o_acc now holds the normalised merged output
+      m_run = (den > 0.0f ? mm + logf(den) : -INFINITY) * kLog2e;
+      if (den <= 0.0f) l_run = 0.0f;
     }
     if (ok && q < p.Tq) {
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
@@ -931,6 +963,8 @@ int set_smem(K kern, int bytes) {
 AttnDev base_params(const NxAttnArgs* a) {
   AttnDev p{};
   p.lse = a->lse;
+  p.merge_o = a->merge_o;
+  p.merge_lse = a->merge_lse;
   p.dsum = a->dsum;
   p.status = a->status;
   p.B = a->batch;

@@ -236,6 +236,38 @@ allreduce_shard_kernel(NxPeerTable in, int n_in, NxPeerTable out, int n_out, int
 }
 
 // ------------------------------------------------------------------------------------------------
+// Ulysses all-to-all by peer stores.  mode 0 (sequence -> heads): x is this rank's [B, Tl, H, D];
+// head h goes to rank h / Hl as out[q][b, rank * Tl + t, h % Hl, :] with out [B, n * Tl, Hl, D].
+// mode 1 (heads -> sequence): x is [B, n * Tl, Hl, D]; row t goes to rank t / Tl as
+// out[q][b, t % Tl, rank * Hl + h, :] with out [B, Tl, H, D].  16-byte vectors (D % 8 == 0).
+// ------------------------------------------------------------------------------------------------
+__global__ void a2a_heads_kernel(const __nv_bfloat16* __restrict__ x, NxPeerTable out, int B, int Tl, int H, int D,
+                                 int rank, int n, int mode) {
+  const int Hl = H / n, vec = D >> 3;
+  const int64_t total = static_cast<int64_t>(B) * Tl * H * vec;  // same element count in both modes
+  NX_GRID_STRIDE(i, total) {
+    const int dv = static_cast<int>(i % vec);
+    int64_t r = i / vec;
+    int64_t dst;
+    int q;
+    if (mode == 0) {
+      const int h = static_cast<int>(r % H);
+      const int t = static_cast<int>((r / H) % Tl);
+      const int b = static_cast<int>(r / (static_cast<int64_t>(H) * Tl));
+      q = h / Hl;
+      dst = ((static_cast<int64_t>(b) * n * Tl + rank * Tl + t) * Hl + h % Hl) * vec + dv;
+    } else {
+      const int h = static_cast<int>(r % Hl);
+      const int t = static_cast<int>((r / Hl) % (n * Tl));
+      const int b = static_cast<int>(r / (static_cast<int64_t>(Hl) * n * Tl));
+      q = t / Tl;
+      dst = ((static_cast<int64_t>(b) * Tl + t % Tl) * H + rank * Hl + h) * vec + dv;
+    }
+    reinterpret_cast<uint4*>(out.ptr[q])[dst] = reinterpret_cast<const uint4*>(x)[i];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // MoE expert-parallel dispatch / combine over peer memory
 // ------------------------------------------------------------------------------------------------
 // Row r of the permuted token matrix belongs to global expert e = expert_of[r] at slot slot_of[r]
@@ -402,6 +434,16 @@ extern "C" int nx_comm_allreduce_shard(const NxPeerTable* in, int in_dtype, int 
   else if (in_dtype == NX_F32 && out_dtype == NX_BF16) NX_AR(float, __nv_bfloat16);
   else return -1;
 #undef NX_AR
+  return launch_status();
+}
+
+extern "C" int nx_comm_a2a_heads(const void* x, const NxPeerTable* out, int B, int Tl, int H, int D, int rank, int n,
+                                 int mode, nx_stream_t stream) {
+  if (out == nullptr || n < 1 || n > NX_MAX_PEERS || H % n || (D & 7) || mode < 0 || mode > 1) return -1;
+  const int64_t total = static_cast<int64_t>(B) * Tl * H * (D / 8);
+  if (total <= 0) return 0;
+  a2a_heads_kernel<<<blocks_for(total, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), *out, B, Tl, H, D, rank, n, mode);
   return launch_status();
 }
 

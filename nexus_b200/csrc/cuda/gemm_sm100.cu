@@ -690,6 +690,11 @@ extern "C" int nx_gemm_dist(const NxGemmArgs* a, const NxGemmDist* d, nx_stream_
   p.tiles_n = (a->n + bn - 1) / bn;
   p.kb_total = (a->k + kBK - 1) / kBK;
   p.kb_per_slice = p.kb_total;
+  p.fp8 = 0;
+  p.bk_elems = kBK;
+  p.scale_a = nullptr;
+  p.scale_b = nullptr;
+  p.amax_out = nullptr;
   p.num_units = p.tiles_m * p.tiles_n;
   p.alpha = a->alpha;
 

@@ -23,6 +23,11 @@ typedef struct NxAttnArgs {
   int32_t causal;               // bottom-right aligned when tq != tk
   int32_t window;               // <= 0: unlimited; else each query sees the last `window` keys
   float scale;                  // softmax scale (1/sqrt(head_dim) by convention)
+  // Forward only, optional: running FP32 output [B, Tq, H, D] and log-sum-exp [B, H, Tq] of earlier
+  // key/value chunks (start: zeros / -inf).  The kernel merges this chunk into them (softmax over the
+  // union of the key sets) and writes the merged result to `o` and `lse` as well: one launch per ring step.
+  float* merge_o;
+  float* merge_lse;
 } NxAttnArgs;
 
 int nx_attention_fwd(const NxAttnArgs* args, nx_stream_t stream);

@@ -41,6 +41,11 @@ int nx_comm_adamw_allgather(float* master, const float* grad, float* m, float* v
 int nx_comm_allreduce_shard(const NxPeerTable* in, int in_dtype, int n_in, const NxPeerTable* out, int out_dtype,
                             int n_out, int64_t shard_off, int64_t count, float scale, nx_stream_t stream);
 
+// Ulysses all-to-all by peer stores (BF16, D % 8 == 0, H % n == 0).  mode 0: x [B, Tl, H, D] ->
+// out[q] [B, n*Tl, H/n, D] (heads scattered, sequence gathered); mode 1: the inverse.  Bracket with barriers.
+int nx_comm_a2a_heads(const void* x, const NxPeerTable* out, int B, int Tl, int H, int D, int rank, int n, int mode,
+                      nx_stream_t stream);
+
 // Expert parallelism.  bufs[q]: rank q's [local_experts, capacity, d] BF16 buffer.  Row r of the
 // assignment list goes to expert expert_of[r], slot slot_of[r] (negative: dropped, skipped); its source
 // row is x[token_of[r]] (token_of null: x[r / rows_per_token]); row_scale (optional) multiplies the copy.

@@ -84,18 +84,18 @@ class Gpt2Weights:
     @staticmethod
     def from_language_model(model) -> "Gpt2Weights":
         """From ``lm.LanguageModel`` (GPT-2 family: LayerNorm, GELU, learned positions, biases)."""
-        cfg = model.cfg
+        cfg = model.config
         sd = {k: v.detach().float().cpu() for k, v in model.state_dict().items()}
         w = Gpt2Weights(cfg.n_layer, cfg.n_head, cfg.d_model, cfg.vocab_size, cfg.max_position, sd["wte"], sd["wpe"],
                         sd["norm_f.weight"], sd["norm_f.bias"])
         for l in range(cfg.n_layer):
-            p = f"h{l}."
+            p = f"h.{l}."
             w.h.append({"ln1_w": sd[p + "norm1.weight"], "ln1_b": sd[p + "norm1.bias"],
-                        "attn_w": sd[p + "attn.qkv.weight"].t().contiguous(), "attn_b": sd[p + "attn.qkv.bias"],
-                        "proj_w": sd[p + "attn.o.weight"].t().contiguous(), "proj_b": sd[p + "attn.o.bias"],
+                        "attn_w": sd[p + "attn.qkv.weight"], "attn_b": sd[p + "attn.qkv.bias"],
+                        "proj_w": sd[p + "attn.o.weight"], "proj_b": sd[p + "attn.o.bias"],
                         "ln2_w": sd[p + "norm2.weight"], "ln2_b": sd[p + "norm2.bias"],
-                        "fc_w": sd[p + "mlp.up.weight"].t().contiguous(), "fc_b": sd[p + "mlp.up.bias"],
-                        "fc2_w": sd[p + "mlp.down.weight"].t().contiguous(), "fc2_b": sd[p + "mlp.down.bias"]})
+                        "fc_w": sd[p + "mlp.up.weight"], "fc_b": sd[p + "mlp.up.bias"],
+                        "fc2_w": sd[p + "mlp.down.weight"], "fc2_b": sd[p + "mlp.down.bias"]})
         return w
 
 

@@ -56,6 +56,7 @@ class AttnArgs(C.Structure):
         ("lse", C.c_void_p), ("dsum", C.c_void_p), ("status", C.c_void_p),
         ("batch", C.c_int32), ("heads", C.c_int32), ("kv_heads", C.c_int32), ("tq", C.c_int32), ("tk", C.c_int32),
         ("head_dim", C.c_int32), ("causal", C.c_int32), ("window", C.c_int32), ("scale", C.c_float),
+        ("merge_o", C.c_void_p), ("merge_lse", C.c_void_p),
     ]
 
 
@@ -402,8 +403,10 @@ def _view(t: torch.Tensor) -> AttnView:
     return AttnView(t.data_ptr(), t.stride(1), t.stride(2), t.stride(0))
 
 
-def attention_fwd(q, k, v, *, causal=True, window=0, scale=None, out=None):
-    """q [B,Tq,H,D], k/v [B,Tk,Hkv,D] bf16 (strided views allowed).  Returns (o, lse[B,H,Tq])."""
+def attention_fwd(q, k, v, *, causal=True, window=0, scale=None, out=None, merge_o=None, merge_lse=None):
+    """q [B,Tq,H,D], k/v [B,Tk,Hkv,D] bf16 (strided views allowed).  Returns (o, lse[B,H,Tq]).
+    ``merge_o`` (FP32 [B,Tq,H,D]) / ``merge_lse`` (FP32 [B,H,Tq]): running result of earlier key/value
+    chunks; this chunk is merged into them in the kernel's epilogue (ring / chunked attention)."""
     B, Tq, H, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
     o = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device) if out is None else out
@@ -415,6 +418,10 @@ def attention_fwd(q, k, v, *, causal=True, window=0, scale=None, out=None):
     a.batch, a.heads, a.kv_heads, a.tq, a.tk, a.head_dim = B, H, Hkv, Tq, Tk, D
     a.causal, a.window = int(causal), int(window)
     a.scale = scale if scale is not None else D ** -0.5
+    if merge_o is not None:
+        if not (merge_o.is_contiguous() and merge_lse.is_contiguous() and merge_o.dtype == torch.float32):
+            raise ValueError("attention_fwd: merge buffers must be contiguous FP32")
+        a.merge_o, a.merge_lse = merge_o.data_ptr(), merge_lse.data_ptr()
     _check(lib().nx_attention_fwd(C.byref(a), _stream()), "nx_attention_fwd")
     return o, lse
 

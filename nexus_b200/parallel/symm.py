@@ -250,3 +250,92 @@ def moe_combine(ws, bufs: SymmetricBuffer, expert, slot, gate, y, local_experts:
     K._check(K.lib().nx_moe_combine(C.byref(bufs.table), K._p(expert), K._p(slot), K._p(gate), K._p(y),
                                     C.c_int(tokens), C.c_int(top_k), C.c_int(y.shape[1]), C.c_int(local_experts),
                                     C.c_int(capacity), K._stream()), "nx_moe_combine")
+
+
+# ---------------------------------------------------------------------------------------------- context parallel
+class RingAttention:
+    """Forward ring attention over symmetric memory: every rank publishes its K/V chunk once; each step
+    runs ONE attention kernel whose TMA loads read the owner's K/V straight from peer memory (plain,
+    non-multicast loads) and whose epilogue merges the chunk into the running FP32 output / LSE.
+    Layouts: ``contiguous`` (rank r holds tokens [r*Tl, (r+1)*Tl)) or ``zigzag`` (rank r holds chunks
+    r and 2n-1-r of 2n, which balances the causal work).  Parity: src/dist/context_parallel.cpp
+    (ring_attention_forward) of the reference, which exchanges blocks with send_recv on CPU ranks."""
+
+    def __init__(self, ws: SymmetricWorkspace, B: int, Tl: int, Hkv: int, D: int, layout: str = "contiguous"):
+        if layout not in ("contiguous", "zigzag"):
+            raise ValueError("layout must be 'contiguous' or 'zigzag'")
+        if layout == "zigzag" and Tl % 2:
+            raise ValueError("zigzag needs an even local length")
+        self.ws, self.layout, self.shape = ws, layout, (B, Tl, Hkv, D)
+        n = B * Tl * Hkv * D
+        self.k_sym = ws.alloc(n, torch.bfloat16)
+        self.v_sym = ws.alloc(n, torch.bfloat16)
+        hdl_k = ws.symm_mem.rendezvous(self.k_sym.local, ws.group)
+        hdl_v = ws.symm_mem.rendezvous(self.v_sym.local, ws.group)
+        self.k_peer = [hdl_k.get_buffer(q, (B, Tl, Hkv, D), torch.bfloat16) for q in range(ws.n)]
+        self.v_peer = [hdl_v.get_buffer(q, (B, Tl, Hkv, D), torch.bfloat16) for q in range(ws.n)]
+
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True):
+        """q [B, Tl, H, D], k/v [B, Tl, Hkv, D] (this rank's tokens).  Returns (o BF16, lse FP32 [B, H, Tl])."""
+        ws, n, r = self.ws, self.ws.n, self.ws.rank
+        B, Tl, H, D = q.shape
+        self.k_sym.local.view(self.shape).copy_(k)
+        self.v_sym.local.view(self.shape).copy_(v)
+        ws.barrier()                                   # every rank's K/V chunk is published
+        dev = q.device
+        if not causal or self.layout == "contiguous":
+            acc_o = torch.zeros((B, Tl, H, D), dtype=torch.float32, device=dev)
+            acc_l = torch.full((B, H, Tl), float("-inf"), dtype=torch.float32, device=dev)
+            out = torch.empty_like(q)
+            for s in range(n):
+                src = (r - s) % n                      # own chunk first, then around the ring
+                if causal and src > r:
+                    continue                           # entirely in the future
+                K.attention_fwd(q, self.k_peer[src], self.v_peer[src], causal=causal and src == r, out=out,
+                                merge_o=acc_o, merge_lse=acc_l)
+            ws.barrier()                               # nobody reads this rank's K/V any more
+            return out, acc_l
+        # zigzag: rank x holds chunk x (first half of its tokens) and chunk 2n-1-x (second half)
+        half = Tl // 2
+        acc = [(torch.zeros((B, half, H, D), dtype=torch.float32, device=dev),
+                torch.full((B, H, half), float("-inf"), dtype=torch.float32, device=dev)) for _ in range(2)]
+        o_half = [torch.empty((B, half, H, D), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        for s in range(n):
+            src = (r - s) % n
+            kk, vv = self.k_peer[src], self.v_peer[src]
+            for qi, qc in enumerate((r, 2 * n - 1 - r)):
+                for ki, kc in enumerate((src, 2 * n - 1 - src)):
+                    if kc > qc:
+                        continue
+                    K.attention_fwd(q[:, qi * half: (qi + 1) * half], kk[:, ki * half: (ki + 1) * half],
+                                    vv[:, ki * half: (ki + 1) * half], causal=(kc == qc), out=o_half[qi],
+                                    merge_o=acc[qi][0], merge_lse=acc[qi][1])
+        ws.barrier()
+        return torch.cat(o_half, dim=1), torch.cat([acc[0][1], acc[1][1]], dim=2)
+
+
+def ulysses_attention(ws: SymmetricWorkspace, q, k, v, causal: bool = True):
+    """DeepSpeed-Ulysses attention over symmetric memory: heads <-> sequence all-to-all by peer stores,
+    local causal flash attention over the full sequence on H/n heads, all-to-all back.
+    q/k/v: [B, Tl, H, D] BF16 with H % n == 0.  Returns o [B, Tl, H, D]."""
+    n, r = ws.n, ws.rank
+    B, Tl, H, D = q.shape
+    Hl = H // n
+    numel = B * Tl * H * D
+    cache = ws.__dict__.setdefault("_ulysses", {})
+    if cache.get("numel") != numel:
+        cache["numel"] = numel
+        cache["bufs"] = [ws.alloc(numel, torch.bfloat16) for _ in range(4)]
+    gq, gk, gv, back = cache["bufs"]
+    L = K.lib()
+    ws.barrier()                                       # the previous call's readers are done
+    for src, dst in ((q, gq), (k, gk), (v, gv)):
+        K._check(L.nx_comm_a2a_heads(K._p(src.contiguous()), C.byref(dst.table), C.c_int(B), C.c_int(Tl), C.c_int(H),
+                                     C.c_int(D), C.c_int(r), C.c_int(n), C.c_int(0), K._stream()), "nx_comm_a2a_heads")
+    ws.barrier()
+    shp = (B, n * Tl, Hl, D)
+    o, _ = K.attention_fwd(gq.local.view(shp), gk.local.view(shp), gv.local.view(shp), causal=causal)
+    K._check(L.nx_comm_a2a_heads(K._p(o), C.byref(back.table), C.c_int(B), C.c_int(Tl), C.c_int(H), C.c_int(D),
+                                 C.c_int(r), C.c_int(n), C.c_int(1), K._stream()), "nx_comm_a2a_heads")
+    ws.barrier()
+    return back.local.view(B, Tl, H, D).clone()

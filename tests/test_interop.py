@@ -1,0 +1,123 @@
+import json
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+from nexus_b200.interop import SafetensorsError, SafetensorsFile, dlpack, gguf, hf, load_file, save_file
+from nexus_b200.lm import LanguageModel
+from nexus_b200.lm.config import LmConfig
+
+
+def small_llama(tie=False, qkv_bias=False, kv=2):
+    cfg = LmConfig(vocab_size=96, d_model=64, n_layer=2, n_head=4, n_kv_head=kv, d_ff=128, max_position=64,
+                   norm="rmsnorm", mlp="swiglu", pos="rope", bias=False, qkv_bias=qkv_bias, tie_embeddings=tie)
+    return LanguageModel(cfg)
+
+
+def test_safetensors_round_trip_and_mmap(tmp_path):
+    t = {"a": torch.randn(3, 5), "b": torch.arange(7, dtype=torch.int64), "c.h": torch.randn(4).bfloat16(),
+         "e": torch.zeros(0, 3), "f8": torch.randn(8).to(torch.float8_e4m3fn)}
+    p = str(tmp_path / "x.safetensors")
+    save_file(t, p, {"who": "test"})
+    f = SafetensorsFile(p)
+    assert f.metadata == {"who": "test"} and sorted(f.keys()) == sorted(t)
+    for k in t:
+        assert torch.equal(f.tensor(k).view(torch.uint8) if k == "f8" else f.tensor(k), t[k].view(torch.uint8) if k == "f8" else t[k])
+    back = load_file(p)
+    assert torch.equal(back["c.h"], t["c.h"])
+    # readable by the same layout rules as the reference implementation of the format
+    raw = open(p, "rb").read()
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    hdr = json.loads(raw[8: 8 + hlen])
+    assert hdr["a"]["dtype"] == "F32" and hdr["a"]["shape"] == [3, 5]
+
+
+def _write(path, header: dict, data: bytes, raw_header: bytes = None):
+    hj = raw_header if raw_header is not None else json.dumps(header).encode()
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hj)) + hj + data)
+
+
+def test_safetensors_strict_validation(tmp_path):
+    p = str(tmp_path / "bad.safetensors")
+    ok = {"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]}}
+    _write(p, ok, b"\0" * 8)
+    SafetensorsFile(p)
+    cases = [
+        ({"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 12]}}, b"\0" * 12),                      # size mismatch
+        ({"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]}}, b"\0" * 12),                       # trailing bytes
+        ({"a": {"dtype": "F33", "shape": [2], "data_offsets": [0, 8]}}, b"\0" * 8),                        # dtype
+        ({"a": {"dtype": "F32", "shape": [-2], "data_offsets": [0, 8]}}, b"\0" * 8),                       # shape
+        ({"a": {"dtype": "F32", "shape": [2], "data_offsets": [4, 12]}}, b"\0" * 12),                      # hole
+        ({"a": {"dtype": "F32", "shape": [1], "data_offsets": [0, 4]},
+          "b": {"dtype": "F32", "shape": [1], "data_offsets": [2, 6]}}, b"\0" * 6),                        # overlap
+        ({"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8], "x": 1}}, b"\0" * 8),                # extra key
+        ({"a": {"dtype": "F32", "shape": [4], "data_offsets": [0, 16]}}, b"\0" * 8),                       # out of range
+    ]
+    for hdr, data in cases:
+        _write(p, hdr, data)
+        with pytest.raises(SafetensorsError):
+            SafetensorsFile(p)
+    _write(p, None, b"", raw_header=b'{"a": {"dtype":"F32","shape":[0],"data_offsets":[0,0]}, "a": {"dtype":"F32","shape":[0],"data_offsets":[0,0]}}')
+    with pytest.raises(SafetensorsError, match="duplicate"):
+        SafetensorsFile(p)
+    _write(p, None, b"", raw_header=b"{not json")
+    with pytest.raises(SafetensorsError):
+        SafetensorsFile(p)
+    with open(p, "wb") as f:
+        f.write(struct.pack("<Q", 1 << 40))
+    with pytest.raises(SafetensorsError):
+        SafetensorsFile(p)
+
+
+@pytest.mark.parametrize("mt,tie,bias,kv", [("llama", False, False, 2), ("qwen2", True, True, 4), ("mistral", False, False, 1)])
+def test_hf_round_trip_preserves_logits(tmp_path, mt, tie, bias, kv):
+    m = small_llama(tie, bias, kv)
+    d = str(tmp_path / mt)
+    hf.export_hf(m, d, mt)
+    cfgj = json.load(open(d + "/config.json"))
+    assert cfgj["model_type"] == mt and cfgj["num_key_value_heads"] == kv
+    m2 = hf.import_hf(d)
+    toks = torch.randint(0, 96, (2, 10))
+    assert torch.allclose(m.logits(toks), m2.logits(toks), atol=1e-6)
+    names = set(hf.to_hf_state(m))
+    assert "model.layers.1.self_attn.k_proj.weight" in names and ("lm_head.weight" in names) == (not tie)
+    assert ("model.layers.0.self_attn.q_proj.bias" in names) == bias
+    with pytest.raises(ValueError):
+        hf.config_from_hf({"model_type": "gpt_neox"})
+
+
+def test_gguf_quant_blocks_and_llama_round_trip(tmp_path):
+    x = np.random.default_rng(0).normal(size=256).astype(np.float32)
+    q8 = gguf.dequantize_q8_0(gguf.quantize_q8_0(x), 256)
+    assert np.abs(q8 - x).max() < np.abs(x).max() / 127 + 1e-3
+    q4 = gguf.dequantize_q4_0(gguf.quantize_q4_0(x), 256)
+    assert np.abs(q4 - x).max() < np.abs(x).max() / 7 + 1e-3
+    assert len(gguf.quantize_q8_0(x)) == 8 * 34 and len(gguf.quantize_q4_0(x)) == 8 * 18
+    w = torch.randn(4 * 16, 32)
+    assert torch.equal(gguf.permute_qk(gguf.permute_qk(w, 4), 4, inverse=True), w)
+    assert torch.equal(gguf.permute_qk(w, 4)[1], w[8])     # pair (0, D/2) becomes adjacent
+    m = small_llama()
+    toks = torch.randint(0, 96, (1, 12))
+    for ty, tol in ((gguf.T_F32, 1e-6), (gguf.T_F16, 5e-3), (gguf.T_Q8_0, 5e-2)):
+        p = str(tmp_path / f"m{ty}.gguf")
+        gguf.export_llama(m, p, ty)
+        meta, tensors, types = gguf.read_gguf(p)
+        assert meta["general.architecture"] == "llama" and meta["llama.block_count"] == 2
+        assert types["blk.0.attn_q.weight"] == ty and types["blk.0.attn_norm.weight"] == gguf.T_F32
+        m2 = gguf.import_llama(p)
+        err = (m.logits(toks) - m2.logits(toks)).abs().max().item()
+        assert err < tol * max(1.0, m.logits(toks).abs().max().item()), (ty, err)
+    raw = open(p, "rb").read()
+    assert raw[:4] == b"GGUF" and struct.unpack("<I", raw[4:8])[0] == 3
+
+
+def test_dlpack_zero_copy():
+    t = torch.randn(4, 4)
+    u = dlpack.from_dlpack(dlpack.to_dlpack(t))
+    u[0, 0] = 42.0
+    assert t[0, 0] == 42.0 and dlpack.device_type(t) == dlpack.K_CPU
+    with pytest.raises(TypeError):
+        dlpack.to_dlpack(t.half())

@@ -11,8 +11,8 @@ from nexus_b200.lm.config import preset  # noqa: E402
 from nexus_b200.models.gpt import AdamWConfig, GptModel  # noqa: E402
 from nexus_b200.ops import _cuda as K  # noqa: E402
 from nexus_b200.parallel.process_group import init_process_group  # noqa: E402
-from nexus_b200.parallel.symm import (FusedShardedOptimizer, SymmetricWorkspace, fused_all_reduce, gemm_dist,  # noqa: E402
-                                      moe_combine, moe_dispatch)
+from nexus_b200.parallel.symm import (FusedShardedOptimizer, RingAttention, SymmetricWorkspace,  # noqa: E402
+                                      fused_all_reduce, gemm_dist, moe_combine, moe_dispatch, ulysses_attention)
 
 
 def main():
@@ -79,6 +79,31 @@ def main():
         torch.cuda.synchronize()
         check(f"fused all-reduce bf16->fp32 n={count} one_shot={one_shot}",
               (dst.local - 0.5 * want).abs().max().item() < 1e-5)
+
+    # ---- context parallelism: ring attention (contiguous + zigzag) and Ulysses vs full attention
+    Bc, Tl, Hc, Dc = 2, 256, 4, 64
+    Tfull = Tl * world
+    gen = torch.Generator(device=dev).manual_seed(77)
+    qf, kf, vf = (torch.randn(Bc, Tfull, Hc, Dc, device=dev, generator=gen).bfloat16() for _ in range(3))
+    for t in (qf, kf, vf):
+        pg.broadcast_tensor(t, 0)
+    ref_o, _ = K.attention_fwd(qf, kf, vf, causal=True)
+    sl = slice(rank * Tl, (rank + 1) * Tl)
+    ring = RingAttention(ws, Bc, Tl, Hc, Dc, "contiguous")
+    o, _ = ring.forward(qf[:, sl].contiguous(), kf[:, sl].contiguous(), vf[:, sl].contiguous(), causal=True)
+    torch.cuda.synchronize()
+    check("ring attention (contiguous)", (o.float() - ref_o[:, sl].float()).abs().max().item() < 3e-2)
+    half = Tl // 2
+    idx = torch.cat([torch.arange(rank * half, (rank + 1) * half),
+                     torch.arange((2 * world - 1 - rank) * half, (2 * world - rank) * half)]).to(dev)
+    zz = RingAttention(ws, Bc, Tl, Hc, Dc, "zigzag")
+    o, _ = zz.forward(qf[:, idx].contiguous(), kf[:, idx].contiguous(), vf[:, idx].contiguous(), causal=True)
+    torch.cuda.synchronize()
+    check("ring attention (zigzag)", (o.float() - ref_o[:, idx].float()).abs().max().item() < 3e-2)
+    o = ulysses_attention(ws, qf[:, sl].contiguous(), kf[:, sl].contiguous(), vf[:, sl].contiguous(), causal=True)
+    torch.cuda.synchronize()
+    check("ulysses attention", (o.float() - ref_o[:, sl].float()).abs().max().item() < 3e-2)
+    K.check_status()
 
     # ---- distributed GEMM: all-gather fused into the GEMM (A sharded / B sharded) and GEMM -> reduce-scatter
     torch.manual_seed(5)
