@@ -121,3 +121,35 @@ def test_dlpack_zero_copy():
     assert t[0, 0] == 42.0 and dlpack.device_type(t) == dlpack.K_CPU
     with pytest.raises(TypeError):
         dlpack.to_dlpack(t.half())
+
+
+def test_onnx_export_structure(tmp_path):
+    from nexus_b200.interop import onnx as O
+    from nexus_b200.lm.config import preset
+    m = LanguageModel(preset("nano"))
+    p = str(tmp_path / "m.onnx")
+    st = O.export_onnx(m, p, opset=17, external_data_threshold=64 * 1024)
+    assert st["external_bytes"] > 0 and (tmp_path / "m.onnx.data").exists()
+    top = O.parse(open(p, "rb").read())
+    fields = {f for f, _, _ in top}
+    assert {1, 7, 8} <= fields
+    opsets = [O.parse(v) for f, _, v in top if f == 8]
+    assert any(dict((a, c) for a, _, c in o).get(2) == 17 for o in opsets)
+    graph = O.parse([v for f, _, v in top if f == 7][0])
+    ops = [dict((a, c) for a, _, c in O.parse(v))[4].decode() for f, _, v in graph if f == 1]
+    assert ops.count("LayerNormalization") == 9 and "Gather" in ops and "MatMul" in ops and "Attention" in ops
+    inits = [O.parse(v) for f, _, v in graph if f == 5]
+    names = [dict((a, c) for a, _, c in t if a == 8)[8].decode() for t in inits]
+    assert "wte" in names and "h.0.attn.qkv.weight" in names
+    ext = [t for t in inits if any(a == 14 for a, _, _ in t)]
+    small = [t for t in inits if any(a == 9 for a, _, _ in t)]
+    assert ext and small
+    wte = [t for t in inits if dict((a, c) for a, _, c in t if a == 8)[8] == b"wte"][0]
+    kv = dict((O.parse(c)[0][2].decode(), O.parse(c)[1][2].decode()) for a, _, c in wte if a == 13)
+    data = open(p + ".data", "rb").read()
+    got = np.frombuffer(data[int(kv["offset"]): int(kv["offset"]) + int(kv["length"])], dtype=np.float32)
+    assert np.array_equal(got, m.state_dict()["wte"].numpy().reshape(-1))
+    ins = [O.parse(v) for f, _, v in graph if f == 11]
+    assert [dict((a, c) for a, _, c in i)[1] for i in ins] == [b"tokens", b"positions"]
+    with pytest.raises(ValueError):
+        O.export_onnx(m, p, opset=11)
