@@ -1,0 +1,70 @@
+import json
+
+import numpy as np
+import pytest
+
+from nexus_b200.lm.config import count_parameters, preset
+from nexus_b200.tools import estimate as E
+from nexus_b200.tools import tokenize as T
+
+
+def test_parameter_counts_match_known_models():
+    gpt2 = E.ModelShape.from_config(preset("gpt2-124m"))
+    assert E.param_breakdown(gpt2)["total"] == 124_439_808 == count_parameters(preset("gpt2-124m"))
+    llama = E.ModelShape(n_layer=32, d_model=4096, n_head=32, n_kv_head=32, d_ff=11008, vocab=32000, seq_len=4096,
+                         learned_pos=0, tie_head=False, ffn_swiglu=True, bias=False, rmsnorm=True)
+    assert E.param_breakdown(llama)["total"] == 6_738_415_616
+    f = E.flops_per_token(gpt2)
+    assert 6 * 85e6 < f < 6 * 124.4e6 + 12 * 12 * 768 * 1024
+
+
+def test_memory_model_zero_stages_and_recompute():
+    m = E.ModelShape.from_config(preset("gpt2-124m"), 1024, 16)
+    dt = E.DTypePlan()
+    base = E.memory_bytes(m, dt, E.Plan())
+    n = 124_439_808
+    assert base["static"] == n * (2 + 4 + 8 + 4)
+    z = [E.memory_bytes(m, dt, E.Plan(dp=8, zero_stage=s))["static"] for s in range(4)]
+    assert z[0] > z[1] > z[2] > z[3] and abs(z[3] - z[0] / 8) < 1
+    assert E.memory_bytes(m, dt, E.Plan(full_recompute=True))["activations"] < 0.1 * base["activations"]
+    assert E.memory_bytes(m, dt, E.Plan(flash_attention=False))["activations"] > base["activations"]
+    assert E.memory_bytes(m, dt, E.Plan(tp=2))["activations"] == base["activations"] / 2
+
+
+def test_step_time_and_auto_parallel():
+    cl = E.Cluster()
+    m = E.ModelShape.from_config(preset("gpt2-124m"), 1024, 16)
+    t = E.step_time(m, E.Plan(), cl)
+    assert 5e-3 < t["step_s"] < 50e-3 and t["tp_comm_s"] == 0 and abs(t["mfu"] - cl.mfu) < 1e-6
+    assert E.step_time(m, E.Plan(tp=2), cl)["tp_comm_s"] > 0
+    llama = E.ModelShape(n_layer=32, d_model=4096, n_head=32, n_kv_head=32, d_ff=11008, vocab=32000, seq_len=4096,
+                         tie_head=False, ffn_swiglu=True, bias=False, rmsnorm=True)
+    r = E.auto_parallel(llama, cl, E.AutoOptions(global_batch=64))
+    assert r["feasible"] > 0 and len(r["best"]) == 3
+    best = r["best"][0]
+    assert best["dp"] * best["tp"] * best["pp"] * best["cp"] == 8 and best["memory_gib"] + cl.reserve_gib <= cl.mem_gib
+    assert best["step_s"] <= r["best"][1]["step_s"]
+    tight = E.auto_parallel(llama, E.Cluster(mem_gib=24.0), E.AutoOptions(global_batch=64))
+    assert all(c["tp"] * c["pp"] > 1 or c["zero"] >= 1 for c in tight["best"])
+    assert E.main(["--preset", "gpt2-124m", "--batch", "16", "--seq", "1024"]) == 0
+    assert E.main(["--preset", "gpt2-124m", "--auto-parallel", "--global-batch", "64", "--json"]) == 0
+
+
+def test_byte_bpe_and_shards(tmp_path):
+    text = (b"the quick brown fox jumps over the lazy dog. " * 40) + "çığ öğe".encode()
+    tok = T.ByteBpe.train(text, 300)
+    assert 256 < tok.vocab_size <= 300
+    ids = tok.encode(text)
+    assert len(ids) < len(text) / 2 and tok.decode(ids) == text
+    tok.save(str(tmp_path / "t.json"))
+    again = T.ByteBpe.load(str(tmp_path / "t.json"))
+    assert again.encode(b"the lazy fox") == tok.encode(b"the lazy fox")
+    T.write_shard(str(tmp_path / "s.nxtk"), ids, tok.vocab_size)
+    data, vocab = T.read_shard(str(tmp_path / "s.nxtk"))
+    assert vocab == tok.vocab_size and data.dtype == np.uint16 and data.tolist() == ids
+    (tmp_path / "c.txt").write_bytes(text)
+    assert T.main(["train", "--vocab", "280", "--out", str(tmp_path / "t2.json"), str(tmp_path / "c.txt")]) == 0
+    assert T.main(["encode", "--tokenizer", str(tmp_path / "t2.json"), "--out", str(tmp_path / "o.nxtk"), str(tmp_path / "c.txt")]) == 0
+    with pytest.raises(ValueError):
+        (tmp_path / "bad").write_bytes(b"XXXX" + b"\0" * 16)
+        T.read_shard(str(tmp_path / "bad"))
