@@ -9,6 +9,7 @@ void bind_nxs3(py::module_& m);
 void bind_runtime(py::module_& m);
 void bind_cpu_kernels(py::module_& m);
 void bind_envs(py::module_& m);
+void bind_device_allocator(py::module_& m);
 
 PYBIND11_MODULE(_native, m) {
   m.doc() = "nexus_b200 native host runtime";
@@ -17,4 +18,5 @@ PYBIND11_MODULE(_native, m) {
   bind_runtime(m);
   bind_cpu_kernels(m);
   bind_envs(m);
+  bind_device_allocator(m);
 }
