@@ -268,3 +268,15 @@ to_device = lambda a, device: _wrap(_t(a).to(device))
 def dropout(a, p: float, seed: int = 0, offset: int = 0, training: bool = True):
     from ..fused.ops import dropout_philox
     return _wrap(dropout_philox(_t(a), p, seed, offset, training))
+
+
+def module_function(module) -> Callable:
+    """Wraps a classic module with explicit ``forward(x)`` / ``backward(grad_out) -> grad_in`` (parameter
+    gradients accumulate inside the module) as ONE autograd node, so that it can sit inside a tape-based
+    model.  Parity: include/nexus/autograd/module_function.hpp:57-69 of the reference."""
+    def fwd(ctx, x):
+        return module.forward(x)
+
+    def bwd(ctx, grad_out):
+        return module.backward(grad_out)
+    return custom_function(fwd, bwd, name=type(module).__name__)

@@ -81,7 +81,7 @@ class Executor:
         if op in ("Relu", "Tanh", "Sigmoid"):
             return [getattr(torch, op.lower())(x[0])]
         if op == "Const":
-            return [torch.tensor(float(a["value"]), device=self._dev)]
+            return [torch.full((), float(a["value"]), device=self._dev)]   # a fill kernel: safe under graph capture
         if op == "LayerNorm":
             return [F.layer_norm(x[0], x[0].shape[-1:], x[1], x[2], float(a["eps"]))]
         if op == "RmsNorm":

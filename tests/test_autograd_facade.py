@@ -85,3 +85,25 @@ def test_checkpoint_matches_plain_backward_and_saves_less():
         checkpoint(lambda t: checkpoint(f, t), x).sum().backward()   # nested
     assert torch.equal(x.grad, g0[0]) and torch.equal(lin1.weight.grad, g0[1])
     assert ck.bytes < plain.bytes
+
+
+def test_module_function_wraps_explicit_backward():
+    import torch
+    from nexus_b200 import autograd as A
+
+    class Scale:
+        def __init__(self):
+            self.w, self.gw = torch.tensor(3.0), torch.tensor(0.0)
+
+        def forward(self, x):
+            self.x = x
+            return x * self.w
+
+        def backward(self, g):
+            self.gw = self.gw + (g * self.x).sum()
+            return g * self.w
+    mod = Scale()
+    f = A.module_function(mod)
+    x = A.Variable(torch.tensor([1.0, 2.0]), requires_grad=True)
+    A.sum(f(x)).backward()
+    assert float(mod.gw) == 3.0 and x.grad.tensor.tolist() == [3.0, 3.0]

@@ -382,3 +382,35 @@ def test_gloo_processes_all_reduce():
 def test_rank_failure_is_a_clean_error_for_the_others():
     codes = _launch(3, 29741, {"FAIL_RANK": "1"})
     assert codes[1] == 3 and codes[0] == 4 and codes[2] == 4
+
+
+def test_tcp_store_set_get_add_wait_barrier():
+    import threading
+    from nexus_b200.parallel.store import TcpStore
+    server = TcpStore(port=0, is_server=True, world_size=3, timeout_s=5.0)
+    clients = [server] + [TcpStore(port=server.port, world_size=3, timeout_s=5.0) for _ in range(2)]
+    clients[1].set("a", b"hello")
+    assert clients[2].get("a") == b"hello" and clients[0].check(["a"]) and not clients[0].check(["a", "zz"])
+    assert [c.add("n", 2) for c in clients] == [2, 4, 6]
+    got = []
+    t = threading.Thread(target=lambda: got.append(clients[2].get("late", 5.0)))
+    t.start()
+    clients[0].set("late", b"x")
+    t.join(5)
+    assert got == [b"x"]
+    with pytest.raises(TimeoutError):
+        clients[1].get("never", 0.1)
+    order = []
+    ts = [threading.Thread(target=lambda i=i: (clients[i].barrier(), order.append(i))) for i in range(3)]
+    for x in ts[:2]:
+        x.start()
+    import time
+    time.sleep(0.1)
+    assert order == []             # nobody passes before the third arrives
+    ts[2].start()
+    for x in ts:
+        x.join(5)
+    assert sorted(order) == [0, 1, 2]
+    for c in clients[1:]:
+        c.close()
+    server.close()
