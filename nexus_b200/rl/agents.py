@@ -329,7 +329,7 @@ class ActorCritic:
         with torch.no_grad():
             target = rew + (0.0 if done else c.gamma * float(self.v(no)))
         v = self.v(o)[0, 0]
-        adv = target - float(v)
+        adv = target - float(v.detach())
         self.v.step((v - target) ** 2)
         lp = torch.log_softmax(self.pi(o)[0], -1)
         ent = -(lp.exp() * lp).sum()
@@ -370,7 +370,7 @@ class ContinuousActorCritic(ActorCritic):
         with torch.no_grad():
             target = rew + (0.0 if done else c.gamma * float(self.v(no)))
         v = self.v(o)[0, 0]
-        adv = target - float(v)
+        adv = target - float(v.detach())
         self.v.step((v - target) ** 2)
         mu = self.pi(o)[0]
         a = _t(act)

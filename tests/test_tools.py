@@ -68,3 +68,27 @@ def test_byte_bpe_and_shards(tmp_path):
     with pytest.raises(ValueError):
         (tmp_path / "bad").write_bytes(b"XXXX" + b"\0" * 16)
         T.read_shard(str(tmp_path / "bad"))
+
+
+def test_bench_evidence_rules(tmp_path):
+    import sys
+    from nexus_b200.bench import evidence as V
+    ok = V.summarise([100, 101, 99, 100, 102], True, 100.0)
+    assert ok["verdict"] == "ok" and ok["median"] == 100
+    assert V.summarise([100, 150, 60, 100, 130], True, None)["verdict"].startswith("no-verdict")
+    assert V.summarise([95, 96, 95, 96, 95], True, 100.0)["verdict"].startswith("regression")
+    assert V.summarise([1.05, 1.05, 1.06], False, 1.0)["verdict"].startswith("regression")
+    assert V.summarise([1.02, 1.02, 1.01], False, 1.0)["verdict"] == "ok"
+    worker = tmp_path / "w.py"
+    worker.write_text("import json, os; print('noise'); print(json.dumps({'value': [10.0, 10.1, 9.9]}))")
+    r = V.sample_case("fake", [sys.executable, str(worker)], "value", 3, True, 10.0)
+    assert r["samples"] == 9 and r["verdict"] == "ok"
+    d = V.digests()
+    assert any(k.endswith("gemm_sm100.cu") for k in d) and all(len(v) == 64 for v in d.values())
+    ev = {"when": "t", "matrix": "kernels", "processes": 3, "warmup": 2, "samples": 3, "digests": d, "results": [r]}
+    txt = V.report(ev)
+    assert "| fake |" in txt and "verdict" in txt
+    bad = tmp_path / "bad.py"
+    bad.write_text("import sys; sys.exit(3)")
+    with pytest.raises(RuntimeError):
+        V.run_worker([sys.executable, str(bad)])
