@@ -39,6 +39,7 @@ struct AttnDev {
   int causal, window;  // window <= 0: unlimited
   int hfirst;          // TMA coordinate order, see load_tile
   float scale;
+  int items, nqb;      // fwd (persistent): number of work items = nqb * H * B, q blocks per (head, batch)
   float* merge_o;      // fwd: FP32 [B,Tq,H,D] running output of earlier key/value chunks (in/out), or null
   float* merge_lse;    // fwd: FP32 [B,H,Tq] running log-sum-exp (in/out)
 };
@@ -89,58 +90,75 @@ __device__ __forceinline__ void row_limits(const AttnDev& p, int q, int& lo, int
   if (p.window > 0) lo = max(lo, q + off - p.window + 1);
 }
 
-// Row maximum of a [128 x 32*kChunks] fp32 score tile held in TMEM (this thread's lane).
-template <bool kMask, int kChunks>
-__device__ __forceinline__ float tile_row_max(uint32_t taddr, int k0, int lo, int hi) {
-  float mx = -INFINITY;
-#pragma unroll 1
-  for (int cc = 0; cc < kChunks; ++cc) {
-    uint32_t v[32];
-    tmem_ld_32x32b_x32(taddr + cc * 32, v);
-    tmem_ld_wait();
-    const int clo = lo - k0 - cc * 32, chi = hi - k0 - cc * 32;  // valid iff clo <= c <= chi
+// Forward softmax helpers.  A score row (128 keys) is shared by two threads of different warps: `c0` is
+// the first of the 64 columns this thread owns (0 or 64).
+template <bool kMask>
+__device__ __forceinline__ float half_row_max(uint32_t taddr, int c0, int k0, int lo, int hi) {
+  float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-    for (int c = 0; c < 32; ++c) {
-      float s = __uint_as_float(v[c]);
-      if (kMask && (c < clo || c > chi)) s = -INFINITY;
-      mx = fmaxf(mx, s);
+  for (int cc = 0; cc < 2; ++cc) {
+    uint32_t v[32];
+    tmem_ld_32x32b_x32(taddr + c0 + cc * 32, v);
+    tmem_ld_wait();
+    const int clo = lo - k0 - c0 - cc * 32, chi = hi - k0 - c0 - cc * 32;  // valid iff clo <= c <= chi
+#pragma unroll
+    for (int c = 0; c < 32; c += 4) {
+      float s0 = __uint_as_float(v[c]), s1 = __uint_as_float(v[c + 1]), s2 = __uint_as_float(v[c + 2]),
+            s3 = __uint_as_float(v[c + 3]);
+      if (kMask) {
+        if (c < clo || c > chi) s0 = -INFINITY;
+        if (c + 1 < clo || c + 1 > chi) s1 = -INFINITY;
+        if (c + 2 < clo || c + 2 > chi) s2 = -INFINITY;
+        if (c + 3 < clo || c + 3 > chi) s3 = -INFINITY;
+      }
+      m0 = fmaxf(m0, s0);
+      m1 = fmaxf(m1, s1);
+      m2 = fmaxf(m2, s2);
+      m3 = fmaxf(m3, s3);
     }
   }
-  return mx;
+  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
 }
 
-// P = exp2(S*sc - m) for the 128 keys of the tile -> BF16, swizzled [128][128] shared tile (2 slabs).
+// P = exp2(S*sc - m) for this thread's 64 keys -> BF16 into slab `c0 / 64` of the swizzled [128][128] tile.
 template <bool kMask>
-__device__ __forceinline__ float tile_softmax_store(uint32_t taddr, uint8_t* sP, int r, int k0, int lo, int hi,
+__device__ __forceinline__ float half_softmax_store(uint32_t taddr, uint8_t* sP, int r, int c0, int k0, int lo, int hi,
                                                     float sc, float m_use) {
-  float rs = 0.0f;
-#pragma unroll 1
-  for (int cc = 0; cc < 4; ++cc) {
-    uint32_t v[32];
-    tmem_ld_32x32b_x32(taddr + cc * 32, v);
-    tmem_ld_wait();
-    const int clo = lo - k0 - cc * 32, chi = hi - k0 - cc * 32;
-    float pr[32];
+  float r0 = 0.0f, r1 = 0.0f, r2 = 0.0f, r3 = 0.0f;
+  uint8_t* slab = sP + (c0 >> 6) * (128 * 128);
 #pragma unroll
-    for (int c = 0; c < 32; ++c) {
-      float e = ex2f(fmaf(__uint_as_float(v[c]), sc, -m_use));
-      if (kMask && (c < clo || c > chi)) e = 0.0f;
-      pr[c] = e;
-      rs += e;
-    }
-    uint8_t* slab = sP + (cc >> 1) * (128 * 128);
+  for (int cc = 0; cc < 2; ++cc) {
+    uint32_t v[32];
+    tmem_ld_32x32b_x32(taddr + c0 + cc * 32, v);
+    tmem_ld_wait();
+    const int clo = lo - k0 - c0 - cc * 32, chi = hi - k0 - c0 - cc * 32;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
+      float e[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c = 8 * g + j;
+        float x = ex2f(fmaf(__uint_as_float(v[c]), sc, -m_use));
+        if (kMask && (c < clo || c > chi)) x = 0.0f;
+        e[j] = x;
+      }
+      r0 += e[0] + e[4];
+      r1 += e[1] + e[5];
+      r2 += e[2] + e[6];
+      r3 += e[3] + e[7];
       uint4 w;
-      w.x = pack_bf16x2(pr[8 * g + 0], pr[8 * g + 1]);
-      w.y = pack_bf16x2(pr[8 * g + 2], pr[8 * g + 3]);
-      w.z = pack_bf16x2(pr[8 * g + 4], pr[8 * g + 5]);
-      w.w = pack_bf16x2(pr[8 * g + 6], pr[8 * g + 7]);
-      *reinterpret_cast<uint4*>(slab + sw128_off(r, (cc & 1) * 4 + g)) = w;
+      w.x = pack_bf16x2(e[0], e[1]);
+      w.y = pack_bf16x2(e[2], e[3]);
+      w.z = pack_bf16x2(e[4], e[5]);
+      w.w = pack_bf16x2(e[6], e[7]);
+      *reinterpret_cast<uint4*>(slab + sw128_off(r, cc * 4 + g)) = w;
     }
   }
-  return rs;
+  return (r0 + r1) + (r2 + r3);
 }
+
+// barrier among the 256 softmax threads only (the TMA and MMA warps never join it)
+__device__ __forceinline__ void softmax_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // first/last (exclusive) kv index that any row in [q0, q0+nq) can see
 __device__ __forceinline__ void kv_range(const AttnDev& p, int q0, int nq, int& lo, int& hi) {
@@ -160,15 +178,31 @@ struct FwdCfg {
   static constexpr int kQBytes = 128 * HD * 2;
   static constexpr int kKVBytes = 128 * HD * 2;
   static constexpr int kPBytes = 128 * 128 * 2;
-  static constexpr int kSmem = kQBytes + 4 * kKVBytes + kPBytes + 128;
+  static constexpr int kXchgBytes = 128 * 4;  // row statistics exchanged between the two column halves (two CTAs
+                                              // per SM leave no room for a second array)
+  static constexpr int kSmem = kQBytes + 4 * kKVBytes + kPBytes + kXchgBytes + 128;
   static constexpr int kTmemCols = 256;  // S: 128, PV: HD
 };
 
+constexpr int kFwdThreads = 320;  // warps 0-7: softmax (row quarter = warp & 3, column half = warp >> 2), 8: TMA, 9: MMA
+
+// Work item i of the persistent forward kernel -> (q block, head, batch).  Items are ordered by cost: under
+// a causal mask the late q blocks see the most keys, so they come first and the CTAs (which take items
+// i, i + grid, i + 2 grid, ...) finish together.
+__device__ __forceinline__ void fwd_item(const AttnDev& p, int item, int& qb, int& h, int& b) {
+  const int per = p.H * p.B;
+  qb = p.nqb - 1 - item / per;
+  const int rem = item % per;
+  h = rem % p.H;
+  b = rem / p.H;
+}
+
 template <int HD>
-__global__ void __launch_bounds__(kThreads, (HD == 64 ? 2 : 1))
+__global__ void __launch_bounds__(kFwdThreads, (HD == 64 ? 2 : 1))
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnDev p) {
   using C = FwdCfg<HD>;
+  constexpr int HH = HD / 2;  // output columns per softmax thread
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (smem_u32(smem) & 1023u) {  // the swizzled tiles need a 1 KiB aligned base; uniform early exit
@@ -179,35 +213,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* sK = sQ + C::kQBytes;               // 2 stages
   uint8_t* sV = sK + 2 * C::kKVBytes;          // 2 stages
   uint8_t* sP = sV + 2 * C::kKVBytes;          // [128][128] bf16 as 2 slabs
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + C::kPBytes);
+  float* sX = reinterpret_cast<float*>(sP + C::kPBytes);  // [128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sX + 128);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;   // [2]
   uint64_t* kv_empty = bars + 3;  // [2]
   uint64_t* s_full = bars + 5;
   uint64_t* p_full = bars + 6;
   uint64_t* o_full = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* q_empty = bars + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = gridDim.x - 1 - blockIdx.x;  // heavy (late) q blocks first under a causal mask
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int hk = h / (p.H / p.Hkv);
-  const int q0 = qb * 128;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 8);  // one arrival per softmax warp
     mbar_init(o_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, C::kTmemCols);
     tmem_relinquish();
   }
@@ -218,158 +251,221 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem_s = tmem_base;
   const uint32_t tmem_o = tmem_base + 128;
 
-  int kv_lo, kv_hi;
-  kv_range(p, q0, min(128, p.Tq - q0), kv_lo, kv_hi);
-  const int jb = kv_lo / 128;
-  const int je = (kv_hi + 127) / 128;  // exclusive; may equal jb when the block sees nothing
-
-  if (warp == 4) {
+  // every role walks the same item list and keeps its own running counters of items and key tiles
+  if (warp == 8) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, C::kQBytes);
-      load_tile<HD>(sQ, &tm_q, q_full, 128, q0, h, b, p.hfirst);
-      for (int j = jb; j < je; ++j) {
-        const int it = j - jb, s = it & 1;
-        if (!mbar_wait_bounded(&kv_empty[s], ((it >> 1) & 1) ^ 1u, abort_flag)) {
+      int n_item = 0, n_kv = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x, ++n_item) {
+        int qb, h, b;
+        fwd_item(p, item, qb, h, b);
+        const int hk = h / (p.H / p.Hkv);
+        const int q0 = qb * 128;
+        int kv_lo, kv_hi;
+        kv_range(p, q0, min(128, p.Tq - q0), kv_lo, kv_hi);
+        const int jb = kv_lo / 128, je = (kv_hi + 127) / 128;
+        if (!mbar_wait_bounded(q_empty, (n_item & 1) ^ 1u, abort_flag)) {  // the previous item's QK^T are done
           atomicCAS(p.status, 0, kStatusTimeoutProducer);
           break;
         }
-        mbar_arrive_expect_tx(&kv_full[s], 2 * C::kKVBytes);
-        load_tile<HD>(sK + s * C::kKVBytes, &tm_k, &kv_full[s], 128, j * 128, hk, b, p.hfirst);
-        load_tile<HD>(sV + s * C::kKVBytes, &tm_v, &kv_full[s], 128, j * 128, hk, b, p.hfirst);
+        mbar_arrive_expect_tx(q_full, C::kQBytes);
+        load_tile<HD>(sQ, &tm_q, q_full, 128, q0, h, b, p.hfirst);
+        for (int j = jb; j < je; ++j, ++n_kv) {
+          const int s = n_kv & 1;
+          if (!mbar_wait_bounded(&kv_empty[s], ((n_kv >> 1) & 1) ^ 1u, abort_flag)) {
+            atomicCAS(p.status, 0, kStatusTimeoutProducer);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&kv_full[s], 2 * C::kKVBytes);
+          load_tile<HD>(sK + s * C::kKVBytes, &tm_k, &kv_full[s], 128, j * 128, hk, b, p.hfirst);
+          load_tile<HD>(sV + s * C::kKVBytes, &tm_v, &kv_full[s], 128, j * 128, hk, b, p.hfirst);
+        }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, false, false, 128, 128);
       const uint32_t idesc_o = make_idesc(kFmtBF16, kFmtBF16, false, true, 128, HD);
-      bool ok = mbar_wait_bounded(q_full, 0, abort_flag);
-      if (!ok) atomicCAS(p.status, 0, kStatusTimeoutMma);
-      for (int j = jb; j < je && ok; ++j) {
-        const int it = j - jb, s = it & 1;
-        if (!mbar_wait_bounded(&kv_full[s], (it >> 1) & 1, abort_flag)) {
+      int n_item = 0, n_kv = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x, ++n_item) {
+        int qb, h, b;
+        fwd_item(p, item, qb, h, b);
+        const int q0 = qb * 128;
+        int kv_lo, kv_hi;
+        kv_range(p, q0, min(128, p.Tq - q0), kv_lo, kv_hi);
+        const int jb = kv_lo / 128, je = (kv_hi + 127) / 128;
+        if (!mbar_wait_bounded(q_full, n_item & 1, abort_flag)) {
           atomicCAS(p.status, 0, kStatusTimeoutMma);
           break;
         }
-        tc_fence_after_sync();
-        const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK + s * C::kKVBytes), aV = smem_u32(sV + s * C::kKVBytes);
+        for (int j = jb; j < je; ++j, ++n_kv) {
+          const int s = n_kv & 1;
+          if (!mbar_wait_bounded(&kv_full[s], (n_kv >> 1) & 1, abort_flag)) {
+            atomicCAS(p.status, 0, kStatusTimeoutMma);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK + s * C::kKVBytes), aV = smem_u32(sV + s * C::kKVBytes);
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks)
-          umma_f16_ss(tmem_s, desc_kmajor(aQ, 128, ks), desc_kmajor(aK, 128, ks), idesc_s, ks > 0 ? 1u : 0u);
-        umma_commit(s_full);
-        if (!mbar_wait_bounded(p_full, it & 1, abort_flag)) {
-          atomicCAS(p.status, 0, kStatusTimeoutMma);
-          break;
+          for (int ks = 0; ks < HD / 16; ++ks)
+            umma_f16_ss(tmem_s, desc_kmajor(aQ, 128, ks), desc_kmajor(aK, 128, ks), idesc_s, ks > 0 ? 1u : 0u);
+          umma_commit(s_full);
+          if (j + 1 == je) umma_commit(q_empty);  // the Q tile may be replaced once these MMAs have read it
+          if (!mbar_wait_bounded(p_full, n_kv & 1, abort_flag)) {
+            atomicCAS(p.status, 0, kStatusTimeoutMma);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t aP = smem_u32(sP);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma_f16_ss(tmem_o, desc_kmajor(aP, 128, ks), desc_mnmajor(aV, 128, ks), idesc_o, ks > 0 ? 1u : 0u);
+          umma_commit(o_full);
+          umma_commit(&kv_empty[s]);
         }
-        tc_fence_after_sync();
-        const uint32_t aP = smem_u32(sP);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_f16_ss(tmem_o, desc_kmajor(aP, 128, ks), desc_mnmajor(aV, 128, ks), idesc_o, ks > 0 ? 1u : 0u);
-        umma_commit(o_full);
-        umma_commit(&kv_empty[s]);
+        if (jb >= je) umma_commit(q_empty);  // nothing visible: release Q at once
       }
     }
   } else {
     // ------------------------------------------------------------------ softmax + output rows
-    const int r = warp * 32 + lane;  // row inside the q block == TMEM lane
-    const int q = q0 + r;
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    // Two threads (warps w and w + 4) share a row: each owns 64 of the 128 score columns and half of the
+    // output columns; they exchange the row maximum through shared memory once per key tile.
+    const int quarter = warp & 3, half = warp >> 2;
+    const int r = quarter * 32 + lane;  // row inside the q block == TMEM lane
+    const int c0 = half * 64;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float sc = p.scale * kLog2e;
-    float m_run = -INFINITY, l_run = 0.0f;
-    int row_lo, row_hi;
-    row_limits(p, q, row_lo, row_hi);
-    float o_acc[HD];
-#pragma unroll
-    for (int c = 0; c < HD; ++c) o_acc[c] = 0.0f;
+    int n_kv = 0;
     bool ok = true;
-    for (int j = jb; j < je; ++j) {
-      const int it = j - jb;
-      const int k0 = j * 128;
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(s_full, it & 1, abort_flag));
-      if (!ok) {
-        if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
-        break;
-      }
-      tc_fence_after_sync();
-      // does this tile need per-element masking?  (warp-uniform by construction of the bounds)
-      const int off = p.Tk - p.Tq;
-      const bool need_mask = (k0 + 128 > p.Tk) || (p.causal && (k0 + 127 > q0 + off)) ||
-                             (p.window > 0 && (k0 < q0 + 127 + off - p.window + 1));
-      float mx, rs;
-      if (need_mask) mx = tile_row_max<true, 4>(tmem_s + lane_addr, k0, row_lo, row_hi);
-      else mx = tile_row_max<false, 4>(tmem_s + lane_addr, k0, row_lo, row_hi);
-      const float m_new = fmaxf(m_run, mx * sc);
-      const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
-      const float alpha = ex2f(m_run - m_use);  // m_run == -inf -> 0
-      if (need_mask) rs = tile_softmax_store<true>(tmem_s + lane_addr, sP, r, k0, row_lo, row_hi, sc, m_use);
-      else rs = tile_softmax_store<false>(tmem_s + lane_addr, sP, r, k0, row_lo, row_hi, sc, m_use);
-      l_run = l_run * alpha + rs;
-      m_run = m_new;
-      fence_proxy_async_smem();  // generic-proxy writes of P -> visible to the tensor core's async proxy
-      tc_fence_before_sync();
-      mbar_arrive(p_full);
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(o_full, it & 1, abort_flag));
-      if (!ok) {
-        if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
-        break;
-      }
-      tc_fence_after_sync();
+    for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
+      int qb, h, b;
+      fwd_item(p, item, qb, h, b);
+      const int q0 = qb * 128;
+      const int q = q0 + r;
+      int kv_lo, kv_hi;
+      kv_range(p, q0, min(128, p.Tq - q0), kv_lo, kv_hi);
+      const int jb = kv_lo / 128, je = (kv_hi + 127) / 128;
+      float m_run = -INFINITY, l_run = 0.0f;  // l_run: partial sum over this thread's columns
+      int row_lo, row_hi;
+      row_limits(p, q, row_lo, row_hi);
+      float o_acc[HH];
 #pragma unroll
-      for (int cc = 0; cc < HD / 32; ++cc) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_o + lane_addr + cc * 32, v);
-        tmem_ld_wait();
+      for (int c = 0; c < HH; ++c) o_acc[c] = 0.0f;
+      for (int j = jb; j < je; ++j, ++n_kv) {
+        const int k0 = j * 128;
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(s_full, n_kv & 1, abort_flag));
+        if (!ok) {
+          if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+          break;
+        }
+        tc_fence_after_sync();
+        // does this tile need per-element masking?  (uniform over the CTA by construction of the bounds)
+        const int off = p.Tk - p.Tq;
+        const bool need_mask = (k0 + 128 > p.Tk) || (p.causal && (k0 + 127 > q0 + off)) ||
+                               (p.window > 0 && (k0 < q0 + 127 + off - p.window + 1));
+        float mx, rs;
+        if (need_mask) mx = half_row_max<true>(tmem_s + lane_addr, c0, k0, row_lo, row_hi);
+        else mx = half_row_max<false>(tmem_s + lane_addr, c0, k0, row_lo, row_hi);
+        // second half publishes, first half combines and publishes the row maximum
+        if (half == 1) sX[r] = mx;
+        softmax_bar();
+        if (half == 0) {
+          mx = fmaxf(mx, sX[r]);
+          sX[r] = mx;
+        }
+        softmax_bar();
+        if (half == 1) mx = sX[r];
+        const float m_new = fmaxf(m_run, mx * sc);
+        const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+        const float alpha = ex2f(m_run - m_use);  // m_run == -inf -> 0
+        if (need_mask) rs = half_softmax_store<true>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use);
+        else rs = half_softmax_store<false>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use);
+        l_run = l_run * alpha + rs;
+        m_run = m_new;
+        fence_proxy_async_smem();  // generic-proxy writes of P -> visible to the tensor core's async proxy
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full);
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(o_full, n_kv & 1, abort_flag));
+        if (!ok) {
+          if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+          break;
+        }
+        tc_fence_after_sync();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) o_acc[cc * 32 + c] = o_acc[cc * 32 + c] * alpha + __uint_as_float(v[c]);
-      }
-      tc_fence_before_sync();
-    }
-    if (ok && q < p.Tq && p.merge_o != nullptr) {
-      // merge with the result of earlier key/value chunks: softmax over the union of the key sets
-      const int64_t li = (static_cast<int64_t>(b) * p.H + h) * p.Tq + q;
-      float* mo = p.merge_o + ((static_cast<int64_t>(b) * p.Tq + q) * p.H + h) * HD;
-      const float lse_new = l_run > 0.0f ? (m_run / kLog2e + logf(l_run)) : -INFINITY;
-      const float lse_old = p.merge_lse[li];
-      const float mm = fmaxf(lse_new, lse_old);
-      const float w_new = (lse_new == -INFINITY) ? 0.0f : __expf(lse_new - mm);
-      const float w_old = (lse_old == -INFINITY) ? 0.0f : __expf(lse_old - mm);
-      const float den = w_new + w_old;
-      const float c_new = den > 0.0f ? w_new / den / (l_run > 0.0f ? l_run : 1.0f) : 0.0f;
-      const float c_old = den > 0.0f ? w_old / den : 0.0f;
+        for (int cc = 0; cc < HH / 32; ++cc) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(tmem_o + lane_addr + half * HH + cc * 32, v);
+          tmem_ld_wait();
 #pragma unroll
-      for (int g = 0; g < HD / 4; ++g) {
-        float4 prev = reinterpret_cast<const float4*>(mo)[g];
-        prev.x = prev.x * c_old + o_acc[4 * g + 0] * c_new;
-        prev.y = prev.y * c_old + o_acc[4 * g + 1] * c_new;
-        prev.z = prev.z * c_old + o_acc[4 * g + 2] * c_new;
-        prev.w = prev.w * c_old + o_acc[4 * g + 3] * c_new;
-        reinterpret_cast<float4*>(mo)[g] = prev;
-        o_acc[4 * g + 0] = prev.x;
-        o_acc[4 * g + 1] = prev.y;
-        o_acc[4 * g + 2] = prev.z;
-        o_acc[4 * g + 3] = prev.w;
+          for (int c = 0; c < 32; ++c) o_acc[cc * 32 + c] = o_acc[cc * 32 + c] * alpha + __uint_as_float(v[c]);
+        }
+        tc_fence_before_sync();
+        softmax_bar();  // the exchanged maxima have been read before the next tile overwrites them
       }
-      p.merge_lse[li] = den > 0.0f ? mm + logf(den) : -INFINITY;
-      l_run = 1.0f;                       // o_acc now holds the normalised merged output
-      m_run = (den > 0.0f ? mm + logf(den) : -INFINITY) * kLog2e;
-      if (den <= 0.0f) l_run = 0.0f;
-    }
-    if (ok && q < p.Tq) {
-      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-      __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(b) * p.o_batch +
-                            static_cast<int64_t>(q) * p.o_row + static_cast<int64_t>(h) * p.o_head;
+      // the two halves of a row add their partial sums
+      if (!ok) l_run = 0.0f;
+      if (half == 1) sX[r] = l_run;
+      softmax_bar();
+      if (half == 0) {
+        l_run += sX[r];
+        sX[r] = l_run;
+      }
+      softmax_bar();
+      if (half == 1) l_run = sX[r];
+      if (ok && q < p.Tq && p.merge_o != nullptr) {
+        // merge with the result of earlier key/value chunks: softmax over the union of the key sets
+        const int64_t li = (static_cast<int64_t>(b) * p.H + h) * p.Tq + q;
+        float* mo = p.merge_o + ((static_cast<int64_t>(b) * p.Tq + q) * p.H + h) * HD + half * HH;
+        const float lse_new = l_run > 0.0f ? (m_run / kLog2e + logf(l_run)) : -INFINITY;
+        const float lse_old = p.merge_lse[li];
+        const float mm = fmaxf(lse_new, lse_old);
+        const float w_new = (lse_new == -INFINITY) ? 0.0f : __expf(lse_new - mm);
+        const float w_old = (lse_old == -INFINITY) ? 0.0f : __expf(lse_old - mm);
+        const float den = w_new + w_old;
+        const float c_new = den > 0.0f ? w_new / den / (l_run > 0.0f ? l_run : 1.0f) : 0.0f;
+        const float c_old = den > 0.0f ? w_old / den : 0.0f;
 #pragma unroll
-      for (int g = 0; g < HD / 8; ++g) {
-        uint4 w;
-        w.x = pack_bf16x2(o_acc[8 * g + 0] * inv, o_acc[8 * g + 1] * inv);
-        w.y = pack_bf16x2(o_acc[8 * g + 2] * inv, o_acc[8 * g + 3] * inv);
-        w.z = pack_bf16x2(o_acc[8 * g + 4] * inv, o_acc[8 * g + 5] * inv);
-        w.w = pack_bf16x2(o_acc[8 * g + 6] * inv, o_acc[8 * g + 7] * inv);
-        reinterpret_cast<uint4*>(orow)[g] = w;
+        for (int g = 0; g < HH / 4; ++g) {
+          float4 prev = reinterpret_cast<const float4*>(mo)[g];
+          prev.x = prev.x * c_old + o_acc[4 * g + 0] * c_new;
+          prev.y = prev.y * c_old + o_acc[4 * g + 1] * c_new;
+          prev.z = prev.z * c_old + o_acc[4 * g + 2] * c_new;
+          prev.w = prev.w * c_old + o_acc[4 * g + 3] * c_new;
+          reinterpret_cast<float4*>(mo)[g] = prev;
+          o_acc[4 * g + 0] = prev.x;
+          o_acc[4 * g + 1] = prev.y;
+          o_acc[4 * g + 2] = prev.z;
+          o_acc[4 * g + 3] = prev.w;
+        }
+        l_run = den > 0.0f ? 1.0f : 0.0f;  // o_acc now holds the normalised merged output
+        m_run = (den > 0.0f ? mm + logf(den) : -INFINITY) * kLog2e;
       }
-      if (p.lse)
-        p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Tq + q] =
-            l_run > 0.0f ? (m_run / kLog2e + logf(l_run)) : -INFINITY;
+      softmax_bar();  // every thread has read merge_lse / sX before they are written again
+      if (ok && q < p.Tq) {
+        const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(b) * p.o_batch +
+                              static_cast<int64_t>(q) * p.o_row + static_cast<int64_t>(h) * p.o_head + half * HH;
+#pragma unroll
+        for (int g = 0; g < HH / 8; ++g) {
+          uint4 w;
+          w.x = pack_bf16x2(o_acc[8 * g + 0] * inv, o_acc[8 * g + 1] * inv);
+          w.y = pack_bf16x2(o_acc[8 * g + 2] * inv, o_acc[8 * g + 3] * inv);
+          w.z = pack_bf16x2(o_acc[8 * g + 4] * inv, o_acc[8 * g + 5] * inv);
+          w.w = pack_bf16x2(o_acc[8 * g + 6] * inv, o_acc[8 * g + 7] * inv);
+          reinterpret_cast<uint4*>(orow)[g] = w;
+        }
+        if (half == 0) {
+          const int64_t li = (static_cast<int64_t>(b) * p.H + h) * p.Tq + q;
+          const float lse = l_run > 0.0f ? (m_run / kLog2e + logf(l_run)) : -INFINITY;
+          if (p.lse) p.lse[li] = lse;
+          if (p.merge_lse) p.merge_lse[li] = lse;
+        }
+      }
     }
   }
 
@@ -380,7 +476,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(2000);
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, C::kTmemCols);
   }
@@ -473,7 +569,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  // 1-D grid in cost order: under a causal mask the early kv blocks are seen by the most queries, and
+  // CTAs are handed out in block-index order, so the long ones start first
+  const int per_blk = p.Hkv * p.B;
+  const int kb = blockIdx.x / per_blk, hk = (blockIdx.x % per_blk) % p.Hkv, b = (blockIdx.x % per_blk) / p.Hkv;
   const int k0 = kb * 128;
   const int group = p.H / p.Hkv;
   const int off = p.Tk - p.Tq;
@@ -745,8 +844,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = gridDim.x - 1 - blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  // 1-D grid in cost order (late q blocks see the most keys under a causal mask)
+  const int per_blk = p.H * p.B;
+  const int qb = p.nqb - 1 - blockIdx.x / per_blk;
+  const int h = (blockIdx.x % per_blk) % p.H, b = (blockIdx.x % per_blk) / p.H;
   const int hk = h / (p.H / p.Hkv);
   const int q0 = qb * 128;
 
@@ -1007,21 +1108,27 @@ extern "C" int nx_attention_fwd(const NxAttnArgs* a, nx_stream_t stream_) {
   p.o_row = a->o.row_stride;
   p.o_head = a->o.head_stride;
   p.o_batch = a->o.batch_stride;
-  dim3 grid((a->tq + 127) / 128, a->heads, a->batch);
+  p.nqb = (a->tq + 127) / 128;
+  p.items = p.nqb * a->heads * a->batch;
+  int sms = 0, dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return -2;
+  // one persistent CTA per slot: two per SM for head_dim 64 (registers / shared memory allow it), one otherwise
+  const int grid = std::min(p.items, sms * (HD == 64 ? 2 : 1));
   if (HD == 64) {
     static bool once = false;
     if (!once) {
       if (set_smem(attn_fwd_kernel<64>, FwdCfg<64>::kSmem)) return -2;
       once = true;
     }
-    attn_fwd_kernel<64><<<grid, kThreads, FwdCfg<64>::kSmem, st>>>(tq, tk, tv, p);
+    attn_fwd_kernel<64><<<grid, kFwdThreads, FwdCfg<64>::kSmem, st>>>(tq, tk, tv, p);
   } else {
     static bool once = false;
     if (!once) {
       if (set_smem(attn_fwd_kernel<128>, FwdCfg<128>::kSmem)) return -2;
       once = true;
     }
-    attn_fwd_kernel<128><<<grid, kThreads, FwdCfg<128>::kSmem, st>>>(tq, tk, tv, p);
+    attn_fwd_kernel<128><<<grid, kFwdThreads, FwdCfg<128>::kSmem, st>>>(tq, tk, tv, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -1061,7 +1168,7 @@ extern "C" int nx_attention_bwd(const NxAttnArgs* a, nx_stream_t stream_) {
     p.o2_row = a->dv.row_stride;
     p.o2_head = a->dv.head_stride;
     p.o2_batch = a->dv.batch_stride;
-    dim3 grid((a->tk + 127) / 128, a->kv_heads, a->batch);
+    const unsigned grid = static_cast<unsigned>(((a->tk + 127) / 128) * a->kv_heads * a->batch);
     if (HD == 64) {
       static bool once = false;
       if (!once) {
@@ -1091,7 +1198,8 @@ extern "C" int nx_attention_bwd(const NxAttnArgs* a, nx_stream_t stream_) {
     p.o_row = a->dq.row_stride;
     p.o_head = a->dq.head_stride;
     p.o_batch = a->dq.batch_stride;
-    dim3 grid((a->tq + 127) / 128, a->heads, a->batch);
+    p.nqb = (a->tq + 127) / 128;
+    const unsigned grid = static_cast<unsigned>(p.nqb * a->heads * a->batch);
     if (HD == 64) {
       static bool once = false;
       if (!once) {
