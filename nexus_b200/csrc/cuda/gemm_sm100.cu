@@ -15,6 +15,7 @@
 #include "sm100_ptx.cuh"
 #include "tensor_map.h"
 #include <algorithm>
+#include <cstdlib>
 
 namespace {
 
@@ -32,7 +33,8 @@ struct Cfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = kSmemBudget / kStageBytes;  // 4 for BN=256, 6 for BN=128
   static constexpr int kTmemCols = 2 * BN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kStoreBytes = 8 * 2 * 2048;  // per epilogue warp: [32 rows][32 bf16] for out and for aux_out
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
 struct DevParams {
@@ -54,6 +56,7 @@ struct DevParams {
   const float* scale_a;   // [m] per-row scale of A (may be null)
   const float* scale_b;   // [n] per-row scale of B (may be null)
   unsigned int* amax_out;  // max |out| as float bits (may be null)
+  int tma_store;           // BF16 out (and aux_out) leave through shared memory and tiled TMA stores
 };
 
 struct Unit {
@@ -160,6 +163,20 @@ __device__ __forceinline__ void store_row32_f32(float* ptr, bool vec_ok, int val
   }
 }
 
+// One row (32 BF16 = 64 bytes) of a [32 rows][32 cols] staging tile in the 64-byte swizzle of its tensor map:
+// 16-byte chunk c of row r lives at chunk c ^ ((r >> 1) & 3).
+__device__ __forceinline__ void stage_row32_bf16(uint8_t* buf, int r, const float (&v)[32]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 q;
+    q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+    q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+    q.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+    q.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+    *reinterpret_cast<uint4*>(buf + r * 64 + ((i ^ ((r >> 1) & 3)) << 4)) = q;
+  }
+}
+
 __device__ __forceinline__ void load_any32(const void* base, int dtype, int64_t elem_off, bool vec_ok, int valid,
                                            float (&v)[32]) {
   if (dtype == NX_F32)
@@ -171,13 +188,15 @@ __device__ __forceinline__ void load_any32(const void* base, int dtype, int64_t 
 template <int BN, bool A_MN, bool B_MN, bool DIST>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            const DevParams p, const uint32_t idesc, const __grid_constant__ DistParam<DIST> dist) {
+            const DevParams p, const uint32_t idesc, const __grid_constant__ DistParam<DIST> dist,
+            const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_aux) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: required by the 128B swizzle pattern (descriptor base_offset = 0).
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint8_t* store_base = smem + C::kStages * C::kStageBytes;  // 1 KiB aligned (stage sizes are multiples of it)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(store_base + C::kStoreBytes);
   uint64_t* full_bar = bars;                    // [kStages]
   uint64_t* empty_bar = bars + C::kStages;      // [kStages]
   uint64_t* tfull_bar = bars + 2 * C::kStages;  // [2]
@@ -345,12 +364,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c * 32, r);
         tmem_ld_wait();
-        if (!row_ok) continue;
+        if (p.tma_store) {
+          // the staging tiles may be rewritten once the previous stores have read them; every lane stays in the
+          // loop (rows past M carry garbage that the tiled store clips)
+          if (lane == 0) tma_store_wait_read();
+          __syncwarp();
+        } else if (!row_ok) {
+          continue;
+        }
         const int valid = min(32, p.n - col0);
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-        if (p.scale_a != nullptr) {
+        if (p.scale_a != nullptr && row_ok) {
           const float sa_row = p.scale_a[row];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] *= sa_row;
@@ -410,14 +436,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         const int64_t aux_off = static_cast<int64_t>(row) * p.ld_aux + col0;
         const bool aux_vec = (valid == 32) && ((p.ld_aux & 7) == 0);
-        if (p.act == NX_ACT_DGELU && p.aux_in != nullptr) {
+        if (p.act == NX_ACT_DGELU && p.aux_in != nullptr && row_ok) {
           float a[32];
           load_row32<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + aux_off, aux_vec, valid, a);
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] *= dgelu_tanh_f(a[j]);
         }
-        if (p.aux_out != nullptr)
-          store_row32_bf16(reinterpret_cast<__nv_bfloat16*>(p.aux_out) + aux_off, aux_vec, valid, v);
+        uint8_t* st_out = store_base + (warp - 2) * 4096;
+        if (p.aux_out != nullptr) {
+          if (p.tma_store) stage_row32_bf16(st_out + 2048, lane, v);
+          else store_row32_bf16(reinterpret_cast<__nv_bfloat16*>(p.aux_out) + aux_off, aux_vec, valid, v);
+        }
         if (p.act == NX_ACT_GELU) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_f(v[j]);
@@ -428,7 +457,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = silu_f(v[j]);
         }
-        if (p.residual != nullptr) {
+        if (p.residual != nullptr && row_ok) {
           float q[32];
           const bool vec = (valid == 32) && ((p.ld_res & 7) == 0);
           load_any32(p.residual, p.res_dtype, static_cast<int64_t>(row) * p.ld_res + col0, vec, valid, q);
@@ -443,17 +472,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] += q[j];
         }
-        if (p.amax_out != nullptr) {  // non-negative floats order like their bit patterns
+        if (p.amax_out != nullptr && row_ok) {  // non-negative floats order like their bit patterns
           float am = 0.0f;
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             if (j < valid) am = fmaxf(am, fabsf(v[j]));
           if (am > 0.0f) atomicMax(p.amax_out, __float_as_uint(am));
         }
-        if (p.out_dtype == NX_F32)
+        if (p.tma_store) {
+          stage_row32_bf16(st_out, lane, v);
+          fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA engine
+          __syncwarp();
+          const int row0 = w.m0 + quarter * 32;
+          if (lane == 0 && row0 < p.m) {
+            if (p.aux_out != nullptr) tma_store_3d(&tmap_aux, st_out + 2048, col0, row0, w.batch);
+            tma_store_3d(&tmap_out, st_out, col0, row0, w.batch);
+            tma_store_commit();
+          }
+        } else if (p.out_dtype == NX_F32) {
           store_row32_f32(reinterpret_cast<float*>(p.out) + out_off, out_vec, valid, v);
-        else
+        } else {
           store_row32_bf16(reinterpret_cast<__nv_bfloat16*>(p.out) + out_off, out_vec, valid, v);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -463,6 +503,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         acc_phase ^= 1u;
       }
     }
+    if (p.tma_store && lane == 0) tma_store_wait_all();  // the staging tiles die with the CTA
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -483,7 +524,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
 template <int BN, bool A_MN, bool B_MN, bool DIST = false>
 int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const DevParams& p, uint32_t in_fmt, int grid,
-                   cudaStream_t stream, const DistParam<DIST>& dist = DistParam<DIST>{}, int fmt_b = -1) {
+                   cudaStream_t stream, const DistParam<DIST>& dist = DistParam<DIST>{}, int fmt_b = -1,
+                   const CUtensorMap* t_out = nullptr, const CUtensorMap* t_aux = nullptr) {
   using C = Cfg<BN>;
   static bool attr_set = false;
   auto kern = gemm_kernel<BN, A_MN, B_MN, DIST>;
@@ -493,7 +535,8 @@ int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const DevParams
     attr_set = true;
   }
   const uint32_t idesc = make_idesc(in_fmt, fmt_b < 0 ? in_fmt : static_cast<uint32_t>(fmt_b), A_MN, B_MN, kBM, BN);
-  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, p, idesc, dist);
+  // unused store maps are passed as copies of an operand map: never dereferenced unless p.tma_store is set
+  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(ta, tb, p, idesc, dist, t_out ? *t_out : ta, t_aux ? *t_aux : ta);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -624,6 +667,24 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
     rc = nx::make_tensor_map_3d(&tb, dt, 2, a->b, a->n, a->k, a->batch, a->ldb, sb, 64, kBK);
   if (rc != 0) return rc;
 
+  // BF16 results leave through shared memory and tiled stores (full-line writes) when the layout allows a map
+  CUtensorMap to, tx;
+  const bool can_tma_out = a->out_dtype == NX_BF16 && split == 1 && a->accumulate == 0 && (a->ldo & 7) == 0 &&
+                           (reinterpret_cast<uintptr_t>(a->out) & 15) == 0 && (a->batch == 1 || (a->stride_o & 7) == 0) &&
+                           (a->aux_out == nullptr || ((a->ld_aux & 7) == 0 && (reinterpret_cast<uintptr_t>(a->aux_out) & 15) == 0 &&
+                                                      a->batch == 1));
+  p.tma_store = 0;
+  static const bool direct_only = std::getenv("NX_GEMM_DIRECT_STORE") != nullptr;  // measurement switch
+  if (can_tma_out && !direct_only) {
+    const uint64_t so = a->batch > 1 ? static_cast<uint64_t>(a->stride_o) : 0;
+    rc = nx::make_tensor_map_3d(&to, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->out, a->n, a->m, a->batch, a->ldo, so, 32, 32,
+                                CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc == 0 && a->aux_out != nullptr)
+      rc = nx::make_tensor_map_3d(&tx, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->aux_out, a->n, a->m, 1, a->ld_aux, 0, 32, 32,
+                                  CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc == 0) p.tma_store = 1;
+  }
+
   int sms = nx_sm_count();
   if (sms <= 0) return -2;
   if (a->max_ctas > 0 && a->max_ctas < sms) sms = a->max_ctas;
@@ -632,7 +693,8 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
   const int fmt_b = fp8 ? static_cast<int>(b_dtype == NX_E4M3 ? kFmtE4M3 : kFmtE5M2) : -1;
 
 #define NX_LAUNCH(BN_, AM_, BM_) \
-  rc = launch_variant<BN_, AM_, BM_>(ta, tb, p, fmt, grid, stream, DistParam<false>{}, fmt_b)
+  rc = launch_variant<BN_, AM_, BM_>(ta, tb, p, fmt, grid, stream, DistParam<false>{}, fmt_b, p.tma_store ? &to : nullptr, \
+                                     (p.tma_store && a->aux_out) ? &tx : nullptr)
   if (bn == 256) {
     if (!a->a_mn_major && !a->b_mn_major) NX_LAUNCH(256, false, false);
     else if (!a->a_mn_major && a->b_mn_major) NX_LAUNCH(256, false, true);
