@@ -93,6 +93,18 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
     return CUDA_LIB
 
 
+def build_gemm_profile(verbose: bool = False) -> Path:
+    """Instrumented GEMM library (`-DNX_PROFILE_MMA`) for `python -m nexus_b200.bench.mma_profile`."""
+    out = CUDA_LIB.parent / "libnexus_b200_gemm_prof.so"
+    src = CSRC / "cuda" / "gemm_sm100.cu"
+    if not out.exists() or out.stat().st_mtime < max(src.stat().st_mtime, _newest_header([CSRC / "cuda"])):
+        _run([_nvcc(), *NVCC_FLAGS, "-DNX_PROFILE_MMA", "-I", str(CSRC / "cuda"), "-shared", "-Xcompiler", "-fPIC",
+              str(src), "-o", str(out), "-cudart", "static", "-lcuda"])
+        if verbose:
+            print("linked", out)
+    return out
+
+
 def build_host(force: bool = False, verbose: bool = False) -> Path:
     import pybind11
 
@@ -134,7 +146,7 @@ def build_tools(force: bool = False, verbose: bool = False):
 
 
 def build_all(force: bool = False, verbose: bool = False):
-    return build_cuda(force, verbose), build_host(force, verbose), build_tools(force, verbose)
+    return build_cuda(force, verbose), build_host(force, verbose), build_tools(force, verbose), build_gemm_profile(verbose)
 
 
 if __name__ == "__main__":

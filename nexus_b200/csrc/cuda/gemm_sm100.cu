@@ -185,6 +185,16 @@ __device__ __forceinline__ void load_any32(const void* base, int dtype, int64_t 
     load_row32<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(base) + elem_off, vec_ok, valid, v);
 }
 
+#ifdef NX_PROFILE_MMA
+// Profiling build only (-DNX_PROFILE_MMA): per CTA, cycles the MMA-issuing thread spent in total, waiting for a
+// free accumulator, waiting for TMA data, and between a stage's arrival and the commit of its MMAs (which blocks
+// while the tensor-core queue is full), plus k-block and tile counts.  Read back with nx_gemm_prof_read.
+__device__ long long g_mma_prof[148 * 8];
+#define NX_PROF(x) x
+#else
+#define NX_PROF(x)
+#endif
+
 template <int BN, bool A_MN, bool B_MN, bool DIST>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -296,20 +306,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      NX_PROF(long long t_acc = 0; long long t_tma = 0; long long t_issue = 0; long long n_kb = 0; long long n_tiles = 0;
+              const long long t_begin = clock64();)
       for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
         Unit w = decode_unit(p, u);
+        NX_PROF(const long long c0 = clock64();)
         if (!mbar_wait_bounded(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) {
           atomicCAS(p.status, 0, kStatusTimeoutMma);
           break;
         }
+        NX_PROF(t_acc += clock64() - c0; ++n_tiles;)
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = w.kb_begin; kb < w.kb_end; ++kb) {
+          NX_PROF(const long long c1 = clock64();)
           if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
             ok = false;
             atomicCAS(p.status, 0, kStatusTimeoutMma);
             break;
           }
+          NX_PROF(const long long c2 = clock64(); t_tma += c2 - c1; ++n_kb;)
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(stage_base + stage * C::kStageBytes);
           const uint32_t sb = sa + C::kABytes;
@@ -326,6 +342,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               umma_f16_ss(tmem_d, da, db, idesc, (kb > w.kb_begin || ks > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+          NX_PROF(t_issue += clock64() - c2;)
           if (++stage == C::kStages) {
             stage = 0;
             phase ^= 1u;
@@ -338,6 +355,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           acc_phase ^= 1u;
         }
       }
+      NX_PROF(if (blockIdx.x < 148) {
+        long long* o = g_mma_prof + blockIdx.x * 8;
+        o[0] = clock64() - t_begin; o[1] = t_acc; o[2] = t_tma; o[3] = t_issue; o[4] = n_kb; o[5] = n_tiles;
+      })
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..9)
@@ -791,3 +812,9 @@ extern "C" int nx_gemm_dist(const NxGemmArgs* a, const NxGemmDist* d, nx_stream_
   if (bn == 256) return launch_variant<256, false, false, true>(ta, tb, p, kFmtBF16, grid, stream, dist);
   return launch_variant<128, false, false, true>(ta, tb, p, kFmtBF16, grid, stream, dist);
 }
+
+#ifdef NX_PROFILE_MMA
+extern "C" int nx_gemm_prof_read(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_mma_prof, sizeof(long long) * 148 * 8) == cudaSuccess ? 0 : -1;
+}
+#endif

@@ -104,9 +104,13 @@ def _p(t: Optional[torch.Tensor]) -> C.c_void_p:
     return C.c_void_p(0 if t is None else t.data_ptr())
 
 
+_KERNELS_PER_CALL = {"nx_norm_bwd": 2, "nx_embedding_bwd": 2, "nx_cross_entropy_shifted": 3, "nx_grad_norm": 2,
+                     "nx_colsum": 2, "nx_attention_bwd": 3}
+
+
 def _check(rc: int, what: str) -> None:
     global launch_count
-    launch_count += 1
+    launch_count += _KERNELS_PER_CALL.get(what, 1)
     if rc != 0:
         raise RuntimeError(f"{what} failed with code {rc}")
 
