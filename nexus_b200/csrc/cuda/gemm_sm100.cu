@@ -26,15 +26,25 @@ constexpr int kBK = 64;  // 64 bf16 = one 128-byte swizzle row
 constexpr int kThreads = 320;  // warp 0: TMA, warp 1: MMA, warps 2..9: epilogue (two per TMEM lane quarter)
 constexpr int kSmemBudget = 200 * 1024;
 
-template <int BN>
+// PAIR: two CTAs of a cluster share one 256 x BN tile (tcgen05 cta_group::2); each stages its own 128 A rows
+// and half of the B rows, so a k-block costs each SM 32 KiB of shared-memory traffic instead of 48 KiB.
+template <int BN, bool PAIR = false>
 struct Cfg {
   static constexpr int kABytes = kBM * kBK * 2;
-  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kBRows = PAIR ? BN / 2 : BN;  // B rows staged by one CTA
+  static constexpr int kBBytes = kBRows * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = kSmemBudget / kStageBytes;  // 4 for BN=256, 6 for BN=128
+  // per epilogue warp: a ring of [32 rows][32 bf16] staging tiles for the tiled stores (the pair's smaller stages
+  // leave room for four, so stores of out AND aux_out are double-buffered)
+  static constexpr int kStoreSlots = PAIR ? 4 : 2;
+  static constexpr int kStoreBytes = 8 * kStoreSlots * 2048;
+  static constexpr int kStages = (PAIR ? kSmemBudget - 32 * 1024 : kSmemBudget) / kStageBytes;  // 4 (BN=256), 6 (BN=128), 5 (pair)
   static constexpr int kTmemCols = 2 * BN;
-  static constexpr int kStoreBytes = 8 * 2 * 2048;  // per epilogue warp: [32 rows][32 bf16] for out and for aux_out
-  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  // the pair's bias strips: [tile parity][column half][128 floats]; its buffer is declared 1 KiB-aligned, the
+  // single-CTA kernel rounds its base up inside a 1 KiB slack
+  static constexpr int kBiasBytes = PAIR ? 2 * 2 * 128 * 4 : 0;
+  static constexpr int kSlackBytes = PAIR ? 0 : 1024;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kBiasBytes + kSlackBytes + 256 /*barriers*/;
 };
 
 struct DevParams {
@@ -57,6 +67,7 @@ struct DevParams {
   const float* scale_b;   // [n] per-row scale of B (may be null)
   unsigned int* amax_out;  // max |out| as float bits (may be null)
   int tma_store;           // BF16 out (and aux_out) leave through shared memory and tiled TMA stores
+  int n_fastest;           // consecutive work units walk along N (A tile reused from L2) instead of along M
 };
 
 struct Unit {
@@ -78,15 +89,26 @@ struct alignas(64) DistParam<true> {
   int a_sharded, b_sharded, out_scatter;
 };
 
+template <int TILE_M = kBM>
 __device__ __forceinline__ Unit decode_unit(const DevParams& p, int u) {
   Unit w;
-  int tm = u % p.tiles_m;
-  u /= p.tiles_m;
-  w.slice = u % p.split_k;
-  u /= p.split_k;
-  int tn = u % p.tiles_n;
-  w.batch = u / p.tiles_n;
-  w.m0 = tm * kBM;
+  int tm, tn;
+  if (p.n_fastest) {
+    tn = u % p.tiles_n;
+    u /= p.tiles_n;
+    w.slice = u % p.split_k;
+    u /= p.split_k;
+    tm = u % p.tiles_m;
+    w.batch = u / p.tiles_m;
+  } else {
+    tm = u % p.tiles_m;
+    u /= p.tiles_m;
+    w.slice = u % p.split_k;
+    u /= p.split_k;
+    tn = u % p.tiles_n;
+    w.batch = u / p.tiles_n;
+  }
+  w.m0 = tm * TILE_M;
   w.n0 = tn;  // multiplied by BN by the caller
   w.kb_begin = w.slice * p.kb_per_slice;
   w.kb_end = min(p.kb_total, w.kb_begin + p.kb_per_slice);
@@ -190,23 +212,37 @@ __device__ __forceinline__ void load_any32(const void* base, int dtype, int64_t 
 // free accumulator, waiting for TMA data, and between a stage's arrival and the commit of its MMAs (which blocks
 // while the tensor-core queue is full), plus k-block and tile counts.  Read back with nx_gemm_prof_read.
 __device__ long long g_mma_prof[148 * 8];
+__device__ long long g_epi_prof[148 * 8];  // first epilogue warp: busy cycles per tile, TMEM-load wait, store-slot wait, tiles
 #define NX_PROF(x) x
 #else
 #define NX_PROF(x)
 #endif
 
-template <int BN, bool A_MN, bool B_MN, bool DIST>
+// FAST (pair only): the epilogue of the training GEMMs and nothing else - BF16 result through tiled stores,
+// optional bias, GELU with saved pre-activation, or dGELU of a saved pre-activation - with the bias staged once
+// per tile in shared memory and one proxy fence / store group per tile (two with aux_out).
+template <int BN, bool A_MN, bool B_MN, bool DIST, bool PAIR = false, bool FAST = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const DevParams p, const uint32_t idesc, const __grid_constant__ DistParam<DIST> dist,
             const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_aux) {
-  using C = Cfg<BN>;
-  extern __shared__ uint8_t smem_raw[];
+  using C = Cfg<BN, PAIR>;
+  static_assert(!(PAIR && DIST), "the CTA-pair tile is for single-GPU operands");
+  static_assert(!FAST || PAIR, "the lean epilogue is built for the pair kernel");
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  if constexpr (PAIR) {
+    // no slack to round the base up in: refuse to run on a base that is not 1 KiB-aligned (same in every CTA)
+    if ((smem_u32(smem_raw) & 1023u) != 0u) {
+      if (threadIdx.x == 0) atomicCAS(p.status, 0, kStatusBadArgument);
+      return;
+    }
+  }
   // 1024-byte alignment: required by the 128B swizzle pattern (descriptor base_offset = 0).
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* stage_base = smem;
   uint8_t* store_base = smem + C::kStages * C::kStageBytes;  // 1 KiB aligned (stage sizes are multiples of it)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(store_base + C::kStoreBytes);
+  float* bias_strip = reinterpret_cast<float*>(store_base + C::kStoreBytes);  // pair only
+  uint64_t* bars = reinterpret_cast<uint64_t*>(store_base + C::kStoreBytes + C::kBiasBytes);
   uint64_t* full_bar = bars;                    // [kStages]
   uint64_t* empty_bar = bars + C::kStages;      // [kStages]
   uint64_t* tfull_bar = bars + 2 * C::kStages;  // [2]
@@ -216,6 +252,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // pair: consecutive CTAs form a cluster; the even one issues the MMAs and owns the barriers both wait on
+  const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
+  const int unit_first = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int unit_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  constexpr int kTileM = PAIR ? 2 * kBM : kBM;
+  const int m_off = static_cast<int>(cta_rank) * kBM;  // this CTA's rows inside the pair's tile
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
@@ -224,14 +266,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 8);
+      mbar_init(&tempty_bar[a], PAIR ? 16 : 8);
     }
     *abort_flag = 0;
     fence_mbar_init();
   }
+  if constexpr (PAIR) cluster_sync_all();  // both CTAs' barriers exist before anything may signal them
   if (warp == 1) {
-    tmem_alloc(tmem_slot, C::kTmemCols);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(tmem_slot, C::kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, C::kTmemCols);
+      tmem_relinquish();
+    }
   }
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmap_a);
@@ -248,8 +296,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
-        Unit w = decode_unit(p, u);
+      for (int u = unit_first; u < p.num_units && ok; u += unit_step) {
+        Unit w = decode_unit<kTileM>(p, u);
+        w.m0 += m_off;
         const int n0 = w.n0 * BN;
         for (int kb = w.kb_begin; kb < w.kb_end; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) {
@@ -259,8 +308,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
           uint8_t* sa = stage_base + stage * C::kStageBytes;
           uint8_t* sb = sa + C::kABytes;
-          mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
           const int k0 = kb * p.bk_elems;
+          if constexpr (PAIR) {
+            // both CTAs' bytes are counted on the even CTA's barrier, which that CTA arms for the pair
+            if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * C::kStageBytes);
+            const uint32_t bar = mapa_shared(smem_u32(&full_bar[stage]), 0);
+            const int bn0 = n0 + static_cast<int>(cta_rank) * C::kBRows;
+            if (!A_MN) {
+              tma_load_3d_pair(sa, &tmap_a, bar, k0, w.m0, w.batch);
+            } else {
+#pragma unroll
+              for (int j = 0; j < kBM / 64; ++j)
+                tma_load_3d_pair(sa + j * (64 * kBK * 2), &tmap_a, bar, w.m0 + 64 * j, k0, w.batch);
+            }
+            if (!B_MN) {
+              tma_load_3d_pair(sb, &tmap_b, bar, k0, bn0, w.batch);
+            } else {
+#pragma unroll
+              for (int j = 0; j < C::kBRows / 64; ++j)
+                tma_load_3d_pair(sb + j * (64 * kBK * 2), &tmap_b, bar, bn0 + 64 * j, k0, w.batch);
+            }
+            if (++stage == C::kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            continue;
+          }
+          mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
           const CUtensorMap* ma = &tmap_a;
           const CUtensorMap* mb = &tmap_b;
           int am0 = w.m0, bn0 = n0;
@@ -297,10 +371,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
         }
       }
+      if constexpr (PAIR) {
+        // The even CTA's commits also arrive on this CTA's barriers: wait until every stage filled here has been
+        // released, so that no arrival is still on its way when the CTA leaves.
+        for (int s = 0; s < C::kStages && ok; ++s) {
+          ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag);
+          if (++stage == C::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer
-    if (lane == 0) {
+    if (lane == 0 && cta_rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -308,8 +393,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       bool ok = true;
       NX_PROF(long long t_acc = 0; long long t_tma = 0; long long t_issue = 0; long long n_kb = 0; long long n_tiles = 0;
               const long long t_begin = clock64();)
-      for (int u = blockIdx.x; u < p.num_units && ok; u += gridDim.x) {
-        Unit w = decode_unit(p, u);
+      for (int u = unit_first; u < p.num_units && ok; u += unit_step) {
+        Unit w = decode_unit<kTileM>(p, u);
         NX_PROF(const long long c0 = clock64();)
         if (!mbar_wait_bounded(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) {
           atomicCAS(p.status, 0, kStatusTimeoutMma);
@@ -336,12 +421,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             const uint32_t b_addr = B_MN ? sb + ks * 2048 : sb + ks * 32;
             const uint64_t da = make_smem_desc_sw128(a_addr, A_MN ? 64 * kBK * 2 : 16, 1024);
             const uint64_t db = make_smem_desc_sw128(b_addr, B_MN ? 64 * kBK * 2 : 16, 1024);
-            if (p.fp8)
+            if constexpr (PAIR)
+              umma_f16_ss_pair(tmem_d, da, db, idesc, (kb > w.kb_begin || ks > 0) ? 1u : 0u);
+            else if (p.fp8)
               umma_f8_ss(tmem_d, da, db, idesc, (kb > w.kb_begin || ks > 0) ? 1u : 0u);
             else
               umma_f16_ss(tmem_d, da, db, idesc, (kb > w.kb_begin || ks > 0) ? 1u : 0u);
           }
-          umma_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+          // frees the stage (in both CTAs of a pair) once these MMAs have read it
+          if constexpr (PAIR) umma_commit_pair(&empty_bar[stage], 3);
+          else umma_commit(&empty_bar[stage]);
           NX_PROF(t_issue += clock64() - c2;)
           if (++stage == C::kStages) {
             stage = 0;
@@ -349,14 +438,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
         }
         if (!ok) break;
-        umma_commit(&tfull_bar[acc]);  // accumulator complete
+        // accumulator complete (each CTA of a pair holds its 128 rows)
+        if constexpr (PAIR) umma_commit_pair(&tfull_bar[acc], 3);
+        else umma_commit(&tfull_bar[acc]);
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1u;
         }
       }
       NX_PROF(if (blockIdx.x < 148) {
-        long long* o = g_mma_prof + blockIdx.x * 8;
+        long long* o = g_mma_prof + (PAIR ? blockIdx.x >> 1 : blockIdx.x) * 8;
         o[0] = clock64() - t_begin; o[1] = t_acc; o[2] = t_tma; o[3] = t_issue; o[4] = n_kb; o[5] = n_tiles;
       })
     }
@@ -366,37 +457,239 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int half = (warp - 2) >> 2;     // which half of the tile's columns this warp handles
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int u = blockIdx.x; u < p.num_units; u += gridDim.x) {
-      Unit w = decode_unit(p, u);
+    int ring = 0;  // next staging tile of this warp
+    (void)ring;
+
+    if constexpr (FAST) {
+      uint8_t* const st_base = store_base + (warp - 2) * (C::kStoreSlots * 2048);
+      const int per = p.aux_out != nullptr ? 2 : 1;
+      const int group = C::kStoreSlots / per;  // chunks per proxy fence and committed store group
+      const int c_begin = half * (BN / 64), c_end = (half + 1) * (BN / 64);
+      int tile_parity = 0;
+      for (int u = unit_first; u < p.num_units; u += unit_step, tile_parity ^= 1) {
+        Unit w = decode_unit<kTileM>(p, u);
+        w.m0 += m_off;
+        const int n0 = w.n0 * BN;
+        const int row = w.m0 + quarter * 32 + lane;
+        const bool row_ok = row < p.m;
+        // While the tile's MMAs still run: the first warp of each column half puts the half's 128 bias values in
+        // shared memory (zeros past N); the four warps of the half meet on a named barrier.  Two strips alternate,
+        // so a warp that is a tile ahead does not overwrite what a slower one still reads.
+        const float* strip = bias_strip + (tile_parity * 2 + half) * 128;
+        if (p.bias != nullptr) {
+          if (quarter == 0) {
+            const int col = n0 + half * 128 + lane * 4;
+            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (col + 3 < p.n && (p.bias_dtype == NX_F32 || (col & 3) == 0)) {
+              if (p.bias_dtype == NX_F32) {
+                const float* bp = reinterpret_cast<const float*>(p.bias) + col;
+                b4 = make_float4(bp[0], bp[1], bp[2], bp[3]);
+              } else {
+                const uint2 q = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(p.bias) + col);
+                unpack_bf16x2(q.x, b4.x, b4.y);
+                unpack_bf16x2(q.y, b4.z, b4.w);
+              }
+            } else {
+              float t[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                t[j] = 0.0f;
+                if (col + j < p.n)
+                  t[j] = p.bias_dtype == NX_F32 ? reinterpret_cast<const float*>(p.bias)[col + j]
+                                                : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[col + j]);
+              }
+              b4 = make_float4(t[0], t[1], t[2], t[3]);
+            }
+            *reinterpret_cast<float4*>(const_cast<float*>(strip) + lane * 4) = b4;
+          }
+          asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+        }
+        const __nv_bfloat16* aux_row = reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + static_cast<int64_t>(row) * p.ld_aux;
+        const bool dgelu = p.act == NX_ACT_DGELU && p.aux_in != nullptr;
+        if (dgelu && row_ok && n0 + c_begin * 32 < p.n) prefetch_l1(aux_row + n0 + c_begin * 32);
+        const bool got = mbar_wait_bounded(&tfull_bar[acc], acc_phase, abort_flag);
+        if (!__all_sync(0xffffffffu, got)) {  // warp-uniform exit: the TMEM loads below need the whole warp
+          if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
+        const int row0 = w.m0 + quarter * 32;
+        int gpos = 0, gcol0 = 0;
+        bool released = false;
+        uint32_t r[32];
+        if (n0 + c_begin * 32 < p.n) tmem_ld_32x32b_x32(taddr + c_begin * 32, r);
+#pragma unroll 1
+        for (int c = c_begin; c < c_end; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.n) break;  // warp-uniform
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          const bool last_chunk = (c + 1 == c_end) || (col0 + 32 >= p.n);
+          if (!last_chunk) {
+            tmem_ld_32x32b_x32(taddr + (c + 1) * 32, r);  // runs under this chunk's arithmetic
+            if (dgelu && row_ok) prefetch_l1(aux_row + col0 + 32);
+          } else {
+            // everything this warp needs from the accumulator is in registers: the MMA warp may overwrite it
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0));
+            released = true;
+          }
+          if (gpos == 0) {
+            // the staging tiles are free once the previous group's stores have read them (long ago, as a rule)
+            if (lane == 0) tma_store_wait_read<0>();
+            __syncwarp();
+            gcol0 = col0;
+          }
+          if (p.alpha != 1.0f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+          }
+          if (p.bias != nullptr) {
+            const float4* b4 = reinterpret_cast<const float4*>(strip + (c - c_begin) * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float4 b = b4[i];  // same address in every lane: one broadcast read
+              v[4 * i + 0] += b.x;
+              v[4 * i + 1] += b.y;
+              v[4 * i + 2] += b.z;
+              v[4 * i + 3] += b.w;
+            }
+          }
+          uint8_t* st_out = st_base + gpos * per * 2048;
+          if (dgelu && row_ok) {
+            const int valid = min(32, p.n - col0);
+            float a[32];
+            load_row32<__nv_bfloat16>(aux_row + col0, (valid == 32) && ((p.ld_aux & 7) == 0), valid, a);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= dgelu_tanh_f(a[j]);
+          }
+          if (p.aux_out != nullptr) stage_row32_bf16(st_out + 2048, lane, v);
+          if (p.act == NX_ACT_GELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_f(v[j]);
+          }
+          stage_row32_bf16(st_out, lane, v);
+          if (++gpos == group || last_chunk) {
+            fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA engine
+            __syncwarp();
+            if (lane == 0 && row0 < p.m) {
+              for (int g = 0; g < gpos; ++g) {
+                const uint8_t* sg = st_base + g * per * 2048;
+                if (p.aux_out != nullptr) tma_store_3d(&tmap_aux, sg + 2048, gcol0 + 32 * g, row0, w.batch);
+                tma_store_3d(&tmap_out, sg, gcol0 + 32 * g, row0, w.batch);
+              }
+              tma_store_commit();
+            }
+            gpos = 0;
+          }
+        }
+        if (!released) {  // no column of this warp's half lies inside the matrix
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0));
+        }
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+      if (lane == 0) tma_store_wait_all();  // the staging tiles die with the CTA
+    } else {
+    NX_PROF(long long e_busy = 0; long long e_ld = 0; long long e_slot = 0; long long e_tiles = 0;
+            long long e_bias = 0; long long e_stage = 0; long long e_fence = 0; long long e_issue = 0;)
+    for (int u = unit_first; u < p.num_units; u += unit_step) {
+      Unit w = decode_unit<kTileM>(p, u);
+      w.m0 += m_off;
       const int n0 = w.n0 * BN;
+      const int row = w.m0 + quarter * 32 + lane;
+      const bool row_ok = row < p.m;
+      const int c_begin = half * (BN / 64), c_end = (half + 1) * (BN / 64);
+      // While the tile's MMAs still run: pull what the epilogue will read (this warp's bias columns, the first
+      // chunk of this lane's aux_in / residual row) into L1, so that the loads below do not wait on L2.
+      auto prefetch_row_inputs = [&](int col) {
+        if (!row_ok || col >= p.n) return;
+        if (p.act == NX_ACT_DGELU && p.aux_in != nullptr)
+          prefetch_l1(reinterpret_cast<const __nv_bfloat16*>(p.aux_in) + static_cast<int64_t>(row) * p.ld_aux + col);
+        if (p.residual != nullptr)
+          prefetch_l1(reinterpret_cast<const uint8_t*>(p.residual) +
+                      (static_cast<int64_t>(row) * p.ld_res + col) * (p.res_dtype == NX_F32 ? 4 : 2));
+      };
+      if (p.bias != nullptr && lane < 4) {
+        const int eb = p.bias_dtype == NX_F32 ? 4 : 2;
+        const int col = n0 + c_begin * 32 + lane * (128 / eb);
+        if (col < p.n) prefetch_l1(reinterpret_cast<const uint8_t*>(p.bias) + static_cast<int64_t>(col) * eb);
+      }
+      prefetch_row_inputs(n0 + c_begin * 32);
       const bool got = mbar_wait_bounded(&tfull_bar[acc], acc_phase, abort_flag);
       if (!__all_sync(0xffffffffu, got)) {  // warp-uniform exit: the TMEM loads below need the whole warp
         if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
         break;
       }
       tc_fence_after_sync();
-      const int row = w.m0 + quarter * 32 + lane;
-      const bool row_ok = row < p.m;
+      NX_PROF(const long long e0 = clock64();)
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * BN);
+      // Tiled stores: `per` staging tiles per chunk (out, aux_out); `group` chunks share one proxy fence and one
+      // committed store group; the ring holds kStoreSlots / (per * group) groups.
+      const int per = p.aux_out != nullptr ? 2 : 1;
+      const int group = (C::kStoreSlots / per >= 4) ? 2 : 1;
+      int gpos = 0, gcol0 = 0;
+      bool released = false;  // accumulator handed back to the MMA warp
+      uint32_t r[32];
+      if (n0 + c_begin * 32 < p.n) tmem_ld_32x32b_x32(taddr + c_begin * 32, r);
 #pragma unroll 1
-      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
+      for (int c = c_begin; c < c_end; ++c) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.n) break;  // warp-uniform
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        NX_PROF(const long long e1 = clock64();)
         tmem_ld_wait();
-        if (p.tma_store) {
-          // the staging tiles may be rewritten once the previous stores have read them; every lane stays in the
-          // loop (rows past M carry garbage that the tiled store clips)
-          if (lane == 0) tma_store_wait_read();
+        NX_PROF(e_ld += clock64() - e1;)
+        float v[32];
+        if (p.alpha != 1.0f) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        }
+        const bool last_chunk = (c + 1 == c_end) || (col0 + 32 >= p.n);
+        if (!last_chunk) {
+          // the next chunk's TMEM read and row inputs run under this chunk's arithmetic and stores
+          tmem_ld_32x32b_x32(taddr + (c + 1) * 32, r);
+          prefetch_row_inputs(col0 + 32);
+        } else {
+          // everything this warp needs from the accumulator is in registers: the MMA warp may overwrite it
+          tc_fence_before_sync();
           __syncwarp();
+          if (lane == 0) {
+            if constexpr (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0));
+            else mbar_arrive(&tempty_bar[acc]);
+          }
+          released = true;
+        }
+        uint8_t* const st_base = store_base + (warp - 2) * (C::kStoreSlots * 2048);
+        uint8_t* st_out = st_base;
+        if (p.tma_store) {
+          // A staging tile may be rewritten once the store group that last used it has read it.  Every lane stays
+          // in the loop (rows past M carry garbage that the tiled store clips).
+          if (gpos == 0) {
+            NX_PROF(const long long e2 = clock64();)
+            if (lane == 0) {
+              if (C::kStoreSlots / (per * group) >= 2) tma_store_wait_read<1>();
+              else tma_store_wait_read<0>();
+            }
+            __syncwarp();
+            NX_PROF(e_slot += clock64() - e2;)
+            gcol0 = col0;
+          }
+          st_out += (ring + gpos * per) * 2048;  // the ring runs on across tiles, in step with the committed groups
         } else if (!row_ok) {
           continue;
         }
         const int valid = min(32, p.n - col0);
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
         if (p.scale_a != nullptr && row_ok) {
           const float sa_row = p.scale_a[row];
 #pragma unroll
@@ -448,6 +741,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           store_row32_f32(wp, vec, valid, v);
           continue;
         }
+        NX_PROF(const long long e3 = clock64();)
         if (p.bias != nullptr) {
           float b[32];
           const bool vec = (valid == 32) && ((col0 & 7) == 0);
@@ -455,6 +749,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] += b[j];
         }
+        NX_PROF(e_bias += clock64() - e3;)
         const int64_t aux_off = static_cast<int64_t>(row) * p.ld_aux + col0;
         const bool aux_vec = (valid == 32) && ((p.ld_aux & 7) == 0);
         if (p.act == NX_ACT_DGELU && p.aux_in != nullptr && row_ok) {
@@ -463,7 +758,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] *= dgelu_tanh_f(a[j]);
         }
-        uint8_t* st_out = store_base + (warp - 2) * 4096;
         if (p.aux_out != nullptr) {
           if (p.tma_store) stage_row32_bf16(st_out + 2048, lane, v);
           else store_row32_bf16(reinterpret_cast<__nv_bfloat16*>(p.aux_out) + aux_off, aux_vec, valid, v);
@@ -501,14 +795,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if (am > 0.0f) atomicMax(p.amax_out, __float_as_uint(am));
         }
         if (p.tma_store) {
+          NX_PROF(const long long e4 = clock64();)
           stage_row32_bf16(st_out, lane, v);
-          fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA engine
-          __syncwarp();
-          const int row0 = w.m0 + quarter * 32;
-          if (lane == 0 && row0 < p.m) {
-            if (p.aux_out != nullptr) tma_store_3d(&tmap_aux, st_out + 2048, col0, row0, w.batch);
-            tma_store_3d(&tmap_out, st_out, col0, row0, w.batch);
-            tma_store_commit();
+          NX_PROF(const long long e5 = clock64(); e_stage += e5 - e4;)
+          if (++gpos == group || last_chunk) {
+            fence_proxy_async_smem();  // generic-proxy writes -> visible to the TMA engine
+            __syncwarp();
+            NX_PROF(const long long e6 = clock64(); e_fence += e6 - e5;)
+            const int row0 = w.m0 + quarter * 32;
+            if (lane == 0 && row0 < p.m) {
+              for (int g = 0; g < gpos; ++g) {
+                const uint8_t* sg = st_base + (ring + g * per) * 2048;
+                if (p.aux_out != nullptr) tma_store_3d(&tmap_aux, sg + 2048, gcol0 + 32 * g, row0, w.batch);
+                tma_store_3d(&tmap_out, sg, gcol0 + 32 * g, row0, w.batch);
+              }
+              tma_store_commit();
+            }
+            ring = (ring + per * group) % C::kStoreSlots;
+            gpos = 0;
+            NX_PROF(e_issue += clock64() - e6;)
           }
         } else if (p.out_dtype == NX_F32) {
           store_row32_f32(reinterpret_cast<float*>(p.out) + out_off, out_vec, valid, v);
@@ -516,15 +821,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           store_row32_bf16(reinterpret_cast<__nv_bfloat16*>(p.out) + out_off, out_vec, valid, v);
         }
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      NX_PROF(e_busy += clock64() - e0; ++e_tiles;)
+      if (!released) {  // no column of this warp's half lies inside the matrix
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0));
+          else mbar_arrive(&tempty_bar[acc]);
+        }
+      }
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1u;
       }
     }
+    NX_PROF(if (warp == 2 && lane == 0 && blockIdx.x < 148) {
+      long long* o = g_epi_prof + blockIdx.x * 8;
+      o[0] = e_busy; o[1] = e_ld; o[2] = e_slot; o[3] = e_tiles;
+      o[4] = e_bias; o[5] = e_stage; o[6] = e_fence; o[7] = e_issue;
+    })
     if (p.tma_store && lane == 0) tma_store_wait_all();  // the staging tiles die with the CTA
+    }  // generic epilogue
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -537,10 +854,54 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(2000);
     __syncthreads();
   }
+  if constexpr (PAIR) cluster_sync_all();  // neither CTA frees TMEM or leaves while the other may still use the pair
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, C::kTmemCols);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, C::kTmemCols);
+    else tmem_dealloc(tmem_base, C::kTmemCols);
   }
+}
+
+// CTA-pair variant: clusters of two CTAs, one 256 x 256 tile per cluster.  `max_ctas` caps the grid.
+template <bool A_MN, bool B_MN, bool FAST>
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const DevParams& p, uint32_t in_fmt, int max_ctas,
+                cudaStream_t stream, const CUtensorMap* t_out, const CUtensorMap* t_aux) {
+  using C = Cfg<256, true>;
+  static int max_clusters = 0;  // 0: not asked yet, < 0: clusters of two cannot be placed
+  auto kern = gemm_kernel<256, A_MN, B_MN, false, true, FAST>;
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = C::kSmemBytes;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (max_clusters == 0) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess) return -2;
+    cfg.gridDim = dim3(2 * 74);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
+      (void)cudaGetLastError();
+      max_clusters = -1;
+    } else {
+      max_clusters = n;
+    }
+  }
+  if (max_clusters < 0) return -3;
+  int clusters = std::min(p.num_units, max_clusters);
+  if (max_ctas > 1) clusters = std::min(clusters, max_ctas / 2);
+  cfg.gridDim = dim3(2 * clusters);
+  const uint32_t idesc = make_idesc(in_fmt, in_fmt, A_MN, B_MN, 2 * kBM, 256);
+  DistParam<false> dist{};
+  if (cudaLaunchKernelEx(&cfg, kern, ta, tb, p, idesc, dist, t_out ? *t_out : ta, t_aux ? *t_aux : ta) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return -2;
+  }
+  return 0;
 }
 
 template <int BN, bool A_MN, bool B_MN, bool DIST = false>
@@ -629,6 +990,12 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
   int bn = a->block_n;
   if (bn != 128 && bn != 256) bn = (a->n >= 256) ? 256 : 128;
 
+  // Two-CTA tiles (256 x 256 over a cluster of two) whenever the problem has at least one such tile of BF16/FP16.
+  static const bool single_only = std::getenv("NX_GEMM_SINGLE_CTA") != nullptr;  // measurement switch
+  static bool pair_ok = true;  // cleared when the device cannot place clusters of two
+  const bool pair = bn == 256 && !fp8 && a->m >= 2 * kBM && pair_ok && !single_only && (a->max_ctas <= 0 || a->max_ctas >= 2);
+  const int tile_m = pair ? 2 * kBM : kBM;
+
   const int bk = fp8 ? 2 * kBK : kBK;  // elements per 128-byte swizzle row
   const int kb_total = (a->k + bk - 1) / bk;
   if (split > kb_total) split = kb_total;
@@ -657,7 +1024,7 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
   p.act = a->act;
   p.accumulate = a->accumulate;
   p.split_k = split;
-  p.tiles_m = (a->m + kBM - 1) / kBM;
+  p.tiles_m = (a->m + tile_m - 1) / tile_m;
   p.tiles_n = (a->n + bn - 1) / bn;
   p.kb_total = kb_total;
   p.kb_per_slice = kb_per;
@@ -668,6 +1035,10 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
   p.scale_a = a->scale_a;
   p.scale_b = a->scale_b;
   p.amax_out = reinterpret_cast<unsigned int*>(a->amax_out);
+  // Units that run at the same time should share the larger operand's tile: walk along N when B is the smaller
+  // matrix (its whole K-panel set stays in L2 while each A tile is fetched from DRAM once), else along M.
+  static const char* order_env = std::getenv("NX_GEMM_ORDER");  // measurement switch: "m" or "n"
+  p.n_fastest = order_env ? (order_env[0] == 'n') : (a->n < a->m);
 
   const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                      : (a->in_dtype == NX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -683,7 +1054,7 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
     rc = nx::make_tensor_map_3d(&ta, dt, 2, a->a, a->m, a->k, a->batch, a->lda, sa, 64, kBK);
   if (rc != 0) return rc;
   if (!a->b_mn_major)
-    rc = nx::make_tensor_map_3d(&tb, dt, eb, a->b, a->k, a->n, a->batch, a->ldb, sb, bk, bn);
+    rc = nx::make_tensor_map_3d(&tb, dt, eb, a->b, a->k, a->n, a->batch, a->ldb, sb, bk, pair ? bn / 2 : bn);
   else
     rc = nx::make_tensor_map_3d(&tb, dt, 2, a->b, a->n, a->k, a->batch, a->ldb, sb, 64, kBK);
   if (rc != 0) return rc;
@@ -712,6 +1083,29 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
   const int grid = p.num_units < sms ? p.num_units : sms;
   const uint32_t fmt = fp8 ? (a->in_dtype == NX_E4M3 ? kFmtE4M3 : kFmtE5M2) : (a->in_dtype == NX_BF16 ? kFmtBF16 : kFmtF16);
   const int fmt_b = fp8 ? static_cast<int>(b_dtype == NX_E4M3 ? kFmtE4M3 : kFmtE5M2) : -1;
+
+  if (pair) {
+    const CUtensorMap* po = p.tma_store ? &to : nullptr;
+    const CUtensorMap* px = (p.tma_store && a->aux_out) ? &tx : nullptr;
+    // the lean epilogue covers what the training step's BF16-output GEMMs ask for
+    static const bool generic_only = std::getenv("NX_GEMM_GENERIC_EPILOGUE") != nullptr;  // measurement switch
+    const bool fast = p.tma_store && !generic_only && a->residual == nullptr && a->scale_a == nullptr && a->scale_b == nullptr &&
+                      a->amax_out == nullptr && (reinterpret_cast<uintptr_t>(a->bias) & 15) == 0 &&
+                      (a->aux_in == nullptr || (reinterpret_cast<uintptr_t>(a->aux_in) & 15) == 0) &&
+                      (a->act == NX_ACT_NONE || a->act == NX_ACT_GELU || (a->act == NX_ACT_DGELU && a->aux_in != nullptr));
+#define NX_PAIR(AM_, BM_) \
+  rc = fast ? launch_pair<AM_, BM_, true>(ta, tb, p, fmt, sms, stream, po, px) \
+            : launch_pair<AM_, BM_, false>(ta, tb, p, fmt, sms, stream, po, px)
+    if (!a->a_mn_major && !a->b_mn_major) NX_PAIR(false, false);
+    else if (!a->a_mn_major && a->b_mn_major) NX_PAIR(false, true);
+    else if (a->a_mn_major && !a->b_mn_major) NX_PAIR(true, false);
+    else NX_PAIR(true, true);
+#undef NX_PAIR
+    if (rc != -3) return rc;
+    // no room for clusters of two on this device: rebuild the launch for single-CTA tiles
+    pair_ok = false;
+    return nx_gemm(a, stream_);
+  }
 
 #define NX_LAUNCH(BN_, AM_, BM_) \
   rc = launch_variant<BN_, AM_, BM_>(ta, tb, p, fmt, grid, stream, DistParam<false>{}, fmt_b, p.tma_store ? &to : nullptr, \
@@ -816,5 +1210,8 @@ extern "C" int nx_gemm_dist(const NxGemmArgs* a, const NxGemmDist* d, nx_stream_
 #ifdef NX_PROFILE_MMA
 extern "C" int nx_gemm_prof_read(long long* out) {
   return cudaMemcpyFromSymbol(out, g_mma_prof, sizeof(long long) * 148 * 8) == cudaSuccess ? 0 : -1;
+}
+extern "C" int nx_gemm_prof_read_epilogue(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_epi_prof, sizeof(long long) * 148 * 8) == cudaSuccess ? 0 : -1;
 }
 #endif

@@ -35,6 +35,22 @@ def test_gemm_layouts(a_mn, b_mn, bn, shape):
     assert (out.float() - ref).abs().max() <= 1.5e-2 * ref.abs().max()
 
 
+@pytest.mark.parametrize("a_mn,b_mn", list(itertools.product((False, True), repeat=2)))
+def test_gemm_cta_pair_many_tiles(a_mn, b_mn):
+    """256 x 256 tiles over CTA pairs: more tiles than clusters, more k-blocks than stages, ragged M and N."""
+    K = _K()
+    torch.manual_seed(7)
+    M, N, Kd = 5000, 1096, 1096
+    A, B, a, b = _operands(M, N, Kd, a_mn, b_mn)
+    out = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    K.check_status()
+    ref = A.float() @ B.float().t()
+    assert (out.float() - ref).abs().max() <= 1.5e-2 * ref.abs().max()
+    if not a_mn and not b_mn:   # the same product from single-CTA tiles (128-wide) agrees to rounding
+        out1 = K.gemm(a, b, block_n=128)
+        assert (out.float() - out1.float()).abs().max() <= 4e-3 * ref.abs().max()
+
+
 def test_gemm_bias_gelu_aux():
     K = _K()
     torch.manual_seed(2)
