@@ -262,20 +262,26 @@ int launch_bwd_dx(bool rms, const void* dy, const void* x, const void* gamma, co
 // registers (VPL float4 per lane), writes dx, and accumulates the column sums of dy*xhat and dy for its
 // own columns over every row it owns; the block then folds its warps through shared memory (fixed
 // order) into partial[block][2][cols].  Rows are assigned round-robin, so the result is deterministic.
-template <typename XT, typename PT, typename GT, typename DT, bool kRms, int VPL>
+// kSum: also accumulate the column sums of the BF16 copy of dx (partial[block][2][cols]): the bias gradient of the
+// linear layer whose output gradient that copy is, without another pass over it.
+template <typename XT, typename PT, typename GT, typename DT, bool kRms, int VPL, bool kSum>
 __global__ void __launch_bounds__(256)
 norm_bwd_fused_kernel(const GT* __restrict__ dy, const XT* __restrict__ x, const PT* __restrict__ gamma,
                       const float* __restrict__ mean, const float* __restrict__ rstd, const DT* __restrict__ add,
                       DT* __restrict__ dx, __nv_bfloat16* __restrict__ dx_lp, float* __restrict__ partial, int rows) {
   constexpr int kCols = 128 * VPL;
+  constexpr int kParts = kSum ? 3 : 2;
   __shared__ float s_red[8][128];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float g[VPL][4], ag[VPL][4], ab[VPL][4];
+  float g[VPL][4], ag[VPL][4], ab[VPL][4], as[kSum ? VPL : 1][4];
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     Vec4<PT>::load(gamma + 4 * (lane + 32 * i), g[i]);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) ag[i][j] = ab[i][j] = 0.0f;
+    for (int j = 0; j < 4; ++j) {
+      ag[i][j] = ab[i][j] = 0.0f;
+      if (kSum) as[i][j] = 0.0f;
+    }
   }
   for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
     const XT* xr = x + static_cast<int64_t>(row) * kCols;
@@ -320,18 +326,23 @@ norm_bwd_fused_kernel(const GT* __restrict__ dy, const XT* __restrict__ x, const
         }
         Vec4<DT>::store(dxr + 4 * (lane + 32 * i), o);
         if (dx_lp) Vec4<__nv_bfloat16>::store(dx_lp + static_cast<int64_t>(row) * kCols + 4 * (lane + 32 * i), o);
+        if (kSum) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) as[i][j] += __bfloat162float(__float2bfloat16_rn(o[j]));  // what the copy holds
+        }
       }
     }
   }
   if (partial == nullptr) return;
-  float* out = partial + static_cast<int64_t>(blockIdx.x) * 2 * kCols;
+  float* out = partial + static_cast<int64_t>(blockIdx.x) * kParts * kCols;
 #pragma unroll 1
-  for (int which = 0; which < 2; ++which) {
+  for (int which = 0; which < kParts; ++which) {
 #pragma unroll 1
     for (int i = 0; i < VPL; ++i) {
       __syncthreads();
 #pragma unroll
-      for (int j = 0; j < 4; ++j) s_red[warp][lane * 4 + j] = which == 0 ? ag[i][j] : ab[i][j];
+      for (int j = 0; j < 4; ++j)
+        s_red[warp][lane * 4 + j] = which == 0 ? ag[i][j] : (which == 1 ? ab[i][j] : as[kSum ? i : 0][j]);
       __syncthreads();
       if (threadIdx.x < 128) {
         float t = 0.0f;
@@ -343,31 +354,37 @@ norm_bwd_fused_kernel(const GT* __restrict__ dy, const XT* __restrict__ x, const
   }
 }
 
-// dgamma / dbeta = sum over chunks of partial[chunk][0/1][c]; block (32 columns x 8 chunk lanes).
+// dgamma / dbeta (/ dsum) = sum over chunks of partial[chunk][0/1(/2)][c]; block (32 columns x 8 chunk lanes).
 __global__ void norm_bwd_param_final2_kernel(const float* __restrict__ partial, float* __restrict__ dgamma,
-                                             float* __restrict__ dbeta, int cols, int chunks, int accumulate) {
+                                             float* __restrict__ dbeta, float* __restrict__ dsum, int parts, int cols,
+                                             int chunks, int accumulate) {
   __shared__ float sg[8][33];
   __shared__ float sb[8][33];
+  __shared__ float ss[8][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
-  float tg = 0.0f, tb = 0.0f;
+  float tg = 0.0f, tb = 0.0f, ts = 0.0f;
   if (c < cols) {
     for (int k = threadIdx.y; k < chunks; k += 8) {
-      tg += partial[(static_cast<int64_t>(k) * 2 + 0) * cols + c];
-      tb += partial[(static_cast<int64_t>(k) * 2 + 1) * cols + c];
+      tg += partial[(static_cast<int64_t>(k) * parts + 0) * cols + c];
+      tb += partial[(static_cast<int64_t>(k) * parts + 1) * cols + c];
+      if (parts == 3) ts += partial[(static_cast<int64_t>(k) * parts + 2) * cols + c];
     }
   }
   sg[threadIdx.y][threadIdx.x] = tg;
   sb[threadIdx.y][threadIdx.x] = tb;
+  ss[threadIdx.y][threadIdx.x] = ts;
   __syncthreads();
   if (threadIdx.y == 0 && c < cols) {
-    tg = tb = 0.0f;
+    tg = tb = ts = 0.0f;
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       tg += sg[k][threadIdx.x];
       tb += sb[k][threadIdx.x];
+      ts += ss[k][threadIdx.x];
     }
     if (dgamma) dgamma[c] = accumulate ? dgamma[c] + tg : tg;
     if (dbeta) dbeta[c] = accumulate ? dbeta[c] + tb : tb;
+    if (dsum && parts == 3) dsum[c] = accumulate ? dsum[c] + ts : ts;
   }
 }
 
@@ -376,24 +393,29 @@ constexpr int kFusedBwdBlocks = kNumSmsB200 * 2;
 template <typename XT, typename PT, typename GT, typename DT, int VPL>
 int launch_bwd_fused_v(bool rms, const void* dy, const void* x, const void* gamma, const float* mean,
                        const float* rstd, const void* add, void* dx, void* dx_lp, float* partial, int rows,
-                       cudaStream_t st) {
+                       bool colsum, cudaStream_t st) {
   const int blocks = std::min(kFusedBwdBlocks, (rows + 7) / 8);
-  if (rms)
-    norm_bwd_fused_kernel<XT, PT, GT, DT, true, VPL><<<blocks, 256, 0, st>>>(
-        (const GT*)dy, (const XT*)x, (const PT*)gamma, mean, rstd, (const DT*)add, (DT*)dx, (__nv_bfloat16*)dx_lp,
-        partial, rows);
-  else
-    norm_bwd_fused_kernel<XT, PT, GT, DT, false, VPL><<<blocks, 256, 0, st>>>(
-        (const GT*)dy, (const XT*)x, (const PT*)gamma, mean, rstd, (const DT*)add, (DT*)dx, (__nv_bfloat16*)dx_lp,
-        partial, rows);
+#define NX_K(RMS, SUM)                                                                                              \
+  norm_bwd_fused_kernel<XT, PT, GT, DT, RMS, VPL, SUM><<<blocks, 256, 0, st>>>(                                       \
+      (const GT*)dy, (const XT*)x, (const PT*)gamma, mean, rstd, (const DT*)add, (DT*)dx, (__nv_bfloat16*)dx_lp, \
+      partial, rows)
+  if (rms) {
+    if (colsum) NX_K(true, true);
+    else NX_K(true, false);
+  } else {
+    if (colsum) NX_K(false, true);
+    else NX_K(false, false);
+  }
+#undef NX_K
   return launch_status() != 0 ? -2 : blocks;
 }
 
 // Returns the number of partial chunks written (> 0), 0 when the shape has no fused instance, < 0 on error.
 template <typename XT, typename PT, typename GT, typename DT>
 int launch_bwd_fused(bool rms, const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
-                     const void* add, void* dx, void* dx_lp, float* partial, int rows, int cols, cudaStream_t st) {
-#define NX_V(V) case V: return launch_bwd_fused_v<XT, PT, GT, DT, V>(rms, dy, x, gamma, mean, rstd, add, dx, dx_lp, partial, rows, st)
+                     const void* add, void* dx, void* dx_lp, float* partial, int rows, int cols, bool colsum,
+                     cudaStream_t st) {
+#define NX_V(V) case V: return launch_bwd_fused_v<XT, PT, GT, DT, V>(rms, dy, x, gamma, mean, rstd, add, dx, dx_lp, partial, rows, colsum, st)
   if (cols % 128) return 0;
   switch (cols / 128) {
     NX_V(2); NX_V(4); NX_V(6); NX_V(8);
@@ -426,7 +448,7 @@ extern "C" int nx_norm_fwd(int rms, const void* x, int x_dtype, const void* resi
 
 static size_t nx_norm_bwd_partial_floats(int rows, int cols) {
   const int chunks = std::max(kFusedBwdBlocks, std::max(1, std::min(64, (rows + 255) / 256)));
-  return static_cast<size_t>(chunks) * 2 * cols;
+  return static_cast<size_t>(chunks) * 3 * cols;
 }
 
 extern "C" size_t nx_norm_bwd_scratch_bytes(int rows, int cols) {
@@ -437,16 +459,27 @@ extern "C" int nx_norm_bwd(int rms, const void* dy, int dy_dtype, const void* x,
                            int param_dtype, const float* mean, const float* rstd, const void* add, void* dx,
                            int dx_dtype, void* dx_lp, float* dgamma, float* dbeta, int accumulate_params,
                            float* scratch, int rows, int cols, nx_stream_t stream) {
+  return nx_norm_bwd_colsum(rms, dy, dy_dtype, x, x_dtype, gamma, param_dtype, mean, rstd, add, dx, dx_dtype, dx_lp, dgamma,
+                            dbeta, nullptr, accumulate_params, scratch, rows, cols, stream);
+}
+
+// `dx_colsum` (optional, [cols]): column sums of the BF16 copy `dx_lp`, accumulated like dgamma / dbeta.  Only the
+// single-pass instances produce it; returns -4 when the shape or the types have none.
+extern "C" int nx_norm_bwd_colsum(int rms, const void* dy, int dy_dtype, const void* x, int x_dtype, const void* gamma,
+                                  int param_dtype, const float* mean, const float* rstd, const void* add, void* dx,
+                                  int dx_dtype, void* dx_lp, float* dgamma, float* dbeta, float* dx_colsum,
+                                  int accumulate_params, float* scratch, int rows, int cols, nx_stream_t stream) {
   if (rows <= 0 || cols <= 0 || (cols & 3)) return -1;
+  if (dx_colsum != nullptr && (dx == nullptr || dx_lp == nullptr)) return -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool r = rms != 0;
   int rc = -1;
-  const bool want_params = dgamma != nullptr || dbeta != nullptr;
+  const bool want_params = dgamma != nullptr || dbeta != nullptr || dx_colsum != nullptr;
   if (want_params && scratch == nullptr) return -1;
   {  // single-pass path (dx and the parameter partials from one read of dy and x)
     int chunks = 0;
 #define NX_FUSED(XT, PT, GT, DT) \
-  chunks = launch_bwd_fused<XT, PT, GT, DT>(r, dy, x, gamma, mean, rstd, add, dx, dx_lp, want_params ? scratch : nullptr, rows, cols, st)
+  chunks = launch_bwd_fused<XT, PT, GT, DT>(r, dy, x, gamma, mean, rstd, add, dx, dx_lp, want_params ? scratch : nullptr, rows, cols, dx_colsum != nullptr, st)
     if (x_dtype == NX_F32 && param_dtype == NX_F32 && dy_dtype == NX_BF16 && (dx == nullptr || dx_dtype == NX_F32))
       NX_FUSED(float, float, __nv_bfloat16, float);
     else if (x_dtype == NX_BF16 && param_dtype == NX_F32 && dy_dtype == NX_BF16 && (dx == nullptr || dx_dtype == NX_BF16))
@@ -456,10 +489,12 @@ extern "C" int nx_norm_bwd(int rms, const void* dy, int dy_dtype, const void* x,
     if (chunks > 0) {
       if (!want_params) return 0;
       dim3 grid2((cols + 31) / 32), block2(32, 8);
-      norm_bwd_param_final2_kernel<<<grid2, block2, 0, st>>>(scratch, dgamma, dbeta, cols, chunks, accumulate_params);
+      norm_bwd_param_final2_kernel<<<grid2, block2, 0, st>>>(scratch, dgamma, dbeta, dx_colsum, dx_colsum ? 3 : 2, cols,
+                                                             chunks, accumulate_params);
       return launch_status();
     }
   }
+  if (dx_colsum != nullptr) return -4;
 #define NX_BWD(XT, PT, GT, DT) rc = launch_bwd_dx<XT, PT, GT, DT>(r, dy, x, gamma, mean, rstd, add, dx, dx_lp, rows, cols, st)
   if (dx != nullptr) {
     if (x_dtype == NX_F32 && param_dtype == NX_F32 && dy_dtype == NX_BF16 && dx_dtype == NX_F32)

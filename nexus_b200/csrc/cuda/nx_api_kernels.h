@@ -44,6 +44,12 @@ int nx_norm_bwd(int rms, const void* dy, int dy_dtype, const void* x, int x_dtyp
                 int param_dtype, const float* mean, const float* rstd, const void* add, void* dx, int dx_dtype,
                 void* dx_lp /* optional BF16 copy of dx */, float* dgamma, float* dbeta, int accumulate_params,
                 float* scratch, int rows, int cols, nx_stream_t stream);
+// The same, plus `dx_colsum` ([cols], optional): column sums of `dx_lp` (the bias gradient of the linear layer whose
+// output gradient `dx_lp` is), accumulated like dgamma / dbeta.  -4: no single-pass instance for this shape / types.
+int nx_norm_bwd_colsum(int rms, const void* dy, int dy_dtype, const void* x, int x_dtype, const void* gamma,
+                       int param_dtype, const float* mean, const float* rstd, const void* add, void* dx, int dx_dtype,
+                       void* dx_lp, float* dgamma, float* dbeta, float* dx_colsum, int accumulate_params, float* scratch,
+                       int rows, int cols, nx_stream_t stream);
 
 // ---- embedding ---------------------------------------------------------------------------------
 int nx_embedding_pos_fwd(const int32_t* tokens, const int32_t* positions, const void* wte, const void* wpe,

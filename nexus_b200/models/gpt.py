@@ -226,34 +226,35 @@ class GptModel:
         K.gemm(dlogits, w["wte"], b_mn=True, out=a["dlnf"])
         K.gemm(dlogits, a["lnf"], a_mn=True, b_mn=True, out=g["wte"], accumulate=True)
         dres, dres_other, dres_lp = a["dres_a"], a["dres_b"], a["dres_lp"]
+        # each norm backward also sums the columns of its BF16 dx: the bias gradient of the projection that follows
         K.norm_bwd(a["dlnf"], res[2 * L], self.p["lnf_w"], a["lnf_mean"], a["lnf_rstd"], dx=dres, dx_lp=dres_lp,
-                   dgamma=g["lnf_w"], dbeta=g["lnf_b"], accumulate_params=True)
+                   dgamma=g["lnf_w"], dbeta=g["lnf_b"], accumulate_params=True, dx_colsum=g["fcproj_b"][L - 1])
         for l in range(L - 1, -1, -1):
             x_in, x_mid = res[2 * l], res[2 * l + 1]
             # ---- MLP
             K.gemm(dres_lp, w["fcproj_w"][l], b_mn=True, act="dgelu", aux_in=a["fch_pre"][l], out=a["dfch"])
-            K.gemm(dres_lp, a["fch"][l], a_mn=True, b_mn=True, out=g["fcproj_w"][l], accumulate=True, split_k=2)
-            K.colsum(dres_lp, out=g["fcproj_b"][l], accumulate=True)
+            K.gemm(dres_lp, a["fch"][l], a_mn=True, b_mn=True, out=g["fcproj_w"][l], accumulate=True, split_k=0)
             K.gemm(a["dfch"], w["fc_w"][l], b_mn=True, out=a["dln"])
-            K.gemm(a["dfch"], a["ln2"][l], a_mn=True, b_mn=True, out=g["fc_w"][l], accumulate=True, split_k=2)
+            K.gemm(a["dfch"], a["ln2"][l], a_mn=True, b_mn=True, out=g["fc_w"][l], accumulate=True, split_k=0)
             K.colsum(a["dfch"], out=g["fc_b"][l], accumulate=True)
             K.norm_bwd(a["dln"], x_mid, self.p["ln2_w"][l], a["ln2_mean"][l], a["ln2_rstd"][l], add=dres,
-                       dx=dres_other, dx_lp=dres_lp, dgamma=g["ln2_w"][l], dbeta=g["ln2_b"][l], accumulate_params=True)
+                       dx=dres_other, dx_lp=dres_lp, dgamma=g["ln2_w"][l], dbeta=g["ln2_b"][l], accumulate_params=True,
+                       dx_colsum=g["attproj_b"][l])
             dres, dres_other = dres_other, dres
             # ---- attention
             K.gemm(dres_lp, w["attproj_w"][l], b_mn=True, out=a["datty"].view(N, C))
             K.gemm(dres_lp, a["atty"][l].view(N, C), a_mn=True, b_mn=True, out=g["attproj_w"][l], accumulate=True,
-                   split_k=8)
-            K.colsum(dres_lp, out=g["attproj_b"][l], accumulate=True)
+                   split_k=0)
             qkv, dqkv = a["qkv"][l], a["dqkv"]
             K.attention_bwd(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], a["atty"][l], a["lse"][l], a["datty"],
                             causal=True, dq=dqkv[:, :, 0], dk=dqkv[:, :, 1], dv=dqkv[:, :, 2])
             dq2 = dqkv.view(N, 3 * C)
             K.gemm(dq2, w["qkv_w"][l], b_mn=True, out=a["dln"])
-            K.gemm(dq2, a["ln1"][l], a_mn=True, b_mn=True, out=g["qkv_w"][l], accumulate=True, split_k=3)
+            K.gemm(dq2, a["ln1"][l], a_mn=True, b_mn=True, out=g["qkv_w"][l], accumulate=True, split_k=0)
             K.colsum(dq2, out=g["qkv_b"][l], accumulate=True)
             K.norm_bwd(a["dln"], x_in, self.p["ln1_w"][l], a["ln1_mean"][l], a["ln1_rstd"][l], add=dres,
-                       dx=dres_other, dx_lp=dres_lp, dgamma=g["ln1_w"][l], dbeta=g["ln1_b"][l], accumulate_params=True)
+                       dx=dres_other, dx_lp=dres_lp, dgamma=g["ln1_w"][l], dbeta=g["ln1_b"][l], accumulate_params=True,
+                       dx_colsum=g["fcproj_b"][l - 1] if l > 0 else None)
             dres, dres_other = dres_other, dres
         K.embedding_bwd(tokens, dres.view(B, T, C), g["wte"], g["wpe"][:T], B, T,
                         deterministic=self.deterministic_embedding)

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes as C
 from pathlib import Path
-from typing import Optional
+from typing import Dict, Tuple, Optional
 
 import torch
 
@@ -145,6 +145,32 @@ def scratch(nbytes: int, tag: str = "default", device=None) -> torch.Tensor:
 
 
 # --------------------------------------------------------------------------------------------- GEMM
+_split_cache: Dict[Tuple[int, int, int], int] = {}
+
+
+def auto_split_k(m: int, n: int, k: int, clusters: int = 74) -> int:
+    """Number of K slices that fills the machine best (``split_k=0`` of ``gemm``).
+
+    The pair kernel runs one 256 x 256 tile per cluster of two SMs; a launch of `u` units takes
+    ceil(u / clusters) rounds of (k-blocks per unit + a fixed per-unit cost of about six k-blocks for the
+    accumulator hand-over and the reduction into the output).  Problems with at least two full rounds of
+    tiles are left alone.
+    """
+    key = (m, n, k)
+    s = _split_cache.get(key)
+    if s is None:
+        tiles = -(-m // 256) * -(-n // 256)
+        kb = -(-k // 64)
+        best, s = None, 1
+        if tiles < 2 * clusters:
+            for cand in range(1, min(16, kb) + 1):
+                cost = -(-tiles * cand // clusters) * (-(-kb // cand) + 6)
+                if best is None or cost < best:
+                    best, s = cost, cand
+        _split_cache[key] = s
+    return s
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          bias: Optional[torch.Tensor] = None, act: Optional[str] = None,
          aux_in: Optional[torch.Tensor] = None, aux_out: Optional[torch.Tensor] = None,
@@ -213,6 +239,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     g.max_ctas = max_ctas
     g.status = status_word(a.device).data_ptr()
     L = lib()
+    if split_k == 0:
+        split_k = auto_split_k(m, n, k) if (not batched and not fp8) else 1
     if split_k > 1 and not batched:
         kb_total = (k + 63) // 64
         split_k = min(split_k, kb_total)
@@ -251,20 +279,28 @@ def norm_fwd(x, gamma, beta=None, *, rms=False, eps=1e-5, residual=None, sum_out
 
 
 def norm_bwd(dy, x, gamma, mean, rstd, *, rms=False, add=None, dx_dtype=None, dgamma=None, dbeta=None,
-             accumulate_params=False, want_dx=True, dx=None, dx_lp=None):
+             accumulate_params=False, want_dx=True, dx=None, dx_lp=None, dx_colsum=None):
+    """``dx_colsum`` ([cols] fp32): column sums of the BF16 copy ``dx_lp`` from the same pass - the bias gradient of
+    the linear layer that ``dx_lp`` is the output gradient of (accumulated when ``accumulate_params``)."""
     rows, cols = x.numel() // x.shape[-1], x.shape[-1]
     if dx is None and want_dx:
         dx = torch.empty(x.shape, dtype=dx_dtype or x.dtype, device=x.device)
-    need_params = dgamma is not None or dbeta is not None
+    need_params = dgamma is not None or dbeta is not None or dx_colsum is not None
     L = lib()
     sc = None
     if need_params:
         sc = scratch(L.nx_norm_bwd_scratch_bytes(C.c_int(rows), C.c_int(cols)), "norm_bwd", x.device)
-    _check(L.nx_norm_bwd(C.c_int(int(rms)), _p(dy), C.c_int(_DT[dy.dtype]), _p(x), C.c_int(_DT[x.dtype]), _p(gamma),
-                         C.c_int(_DT[gamma.dtype]), _p(mean), _p(rstd), _p(add), _p(dx),
-                         C.c_int(_DT[dx.dtype] if dx is not None else F32), _p(dx_lp), _p(dgamma), _p(dbeta),
-                         C.c_int(int(accumulate_params)), _p(sc), C.c_int(rows), C.c_int(cols), _stream()),
-           "nx_norm_bwd")
+    rc = L.nx_norm_bwd_colsum(C.c_int(int(rms)), _p(dy), C.c_int(_DT[dy.dtype]), _p(x), C.c_int(_DT[x.dtype]), _p(gamma),
+                              C.c_int(_DT[gamma.dtype]), _p(mean), _p(rstd), _p(add), _p(dx),
+                              C.c_int(_DT[dx.dtype] if dx is not None else F32), _p(dx_lp), _p(dgamma), _p(dbeta),
+                              _p(dx_colsum), C.c_int(int(accumulate_params)), _p(sc), C.c_int(rows), C.c_int(cols),
+                              _stream())
+    if rc == -4:   # no single-pass instance for this shape: the plain kernels, then a column-sum pass over dx_lp
+        norm_bwd(dy, x, gamma, mean, rstd, rms=rms, add=add, dgamma=dgamma, dbeta=dbeta,
+                 accumulate_params=accumulate_params, dx=dx, dx_lp=dx_lp)
+        colsum(dx_lp.view(rows, cols), out=dx_colsum, accumulate=accumulate_params)
+        return dx
+    _check(rc, "nx_norm_bwd")
     return dx
 
 

@@ -31,6 +31,14 @@ def test_layernorm_fwd_bwd(rows, cols):
     assert close(dx, xs2.grad + add, 1e-4)
     assert close(lp, xs2.grad + add, 1e-2)
     assert close(dg, g2.grad, 1e-3) and close(db, b2.grad, 1e-3)
+    # the same pass can also return the column sums of the BF16 dx (a bias gradient), accumulated like dgamma
+    dg2, db2 = torch.zeros(cols, device=DEV), torch.zeros(cols, device=DEV)
+    cs = torch.ones(cols, device=DEV)
+    lp2 = torch.empty_like(lp)
+    dx2 = K.norm_bwd(dy, xs, g, mean, rstd, add=add, dx_dtype=torch.float32, dgamma=dg2, dbeta=db2, dx_lp=lp2,
+                     dx_colsum=cs, accumulate_params=True)
+    assert torch.equal(dx2, dx) and torch.equal(lp2, lp) and close(dg2, dg, 1e-6)
+    assert close(cs, 1.0 + lp.float().sum(0), 1e-4)
 
 
 @pytest.mark.parametrize("rows,cols", [(1000, 768), (512, 4096)])
