@@ -36,9 +36,13 @@ struct Cfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   // per epilogue warp: a ring of [32 rows][32 bf16] staging tiles for the tiled stores (the pair's smaller stages
   // leave room for four, so stores of out AND aux_out are double-buffered)
-  static constexpr int kStoreSlots = PAIR ? 4 : 2;
+#ifndef NX_PAIR_SLOTS
+#define NX_PAIR_SLOTS 4
+#endif
+  static constexpr int kStoreSlots = PAIR ? NX_PAIR_SLOTS : 2;
   static constexpr int kStoreBytes = 8 * kStoreSlots * 2048;
-  static constexpr int kStages = (PAIR ? kSmemBudget - 32 * 1024 : kSmemBudget) / kStageBytes;  // 4 (BN=256), 6 (BN=128), 5 (pair)
+  // 4 stages (BN=256), 6 (BN=128); the pair: 5 with four staging tiles per warp, 6 with two
+  static constexpr int kStages = (PAIR ? kSmemBudget + 32 * 1024 - kStoreBytes : kSmemBudget) / kStageBytes;
   static constexpr int kTmemCols = 2 * BN;
   // the pair's bias strips: [tile parity][column half][128 floats]; its buffer is declared 1 KiB-aligned, the
   // single-CTA kernel rounds its base up inside a 1 KiB slack
