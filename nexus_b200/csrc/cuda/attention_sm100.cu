@@ -24,6 +24,7 @@
 namespace {
 using namespace nx;
 
+constexpr int kThreads = 192;  // warps 0-3: softmax / row math, warp 4: TMA, warp 5: MMA + TMEM
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct AttnDev {
@@ -523,42 +524,25 @@ __global__ void attn_bwd_dsum_kernel(const __nv_bfloat16* __restrict__ o, const 
 }
 
 // ================================================================================================
-// backward, parts 1 and 2.  Shared shape: warps 0-15 do the row math (TMEM lane quarter = warp & 3; the 64 columns
-// of a score chunk are split four ways, 16 per thread), warp 16 is the TMA producer, warp 17 issues the MMAs and owns
-// TMEM.  Scores and dP are double-buffered in TMEM and the probabilities / dS in shared memory: the tensor core
-// computes chunk i+1's S and dP while the math warps turn chunk i into P and dS, and accumulates chunk i's
-// gradient tiles while they work on chunk i+1.
-// ================================================================================================
-constexpr int kBwdSplit = 4;                       // column splits of a 64-wide chunk
-constexpr int kBwdCols = 64 / kBwdSplit;           // columns per math thread
-constexpr int kBwdMathWarps = 4 * kBwdSplit;
-constexpr int kBwdThreads = 32 * (kBwdMathWarps + 2);
-
-__device__ __forceinline__ void tmem_ld_cols16(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld_32x32b_x16(taddr, r); }
-
-// ================================================================================================
 // backward, part 1: dK / dV.  One CTA per (kv block of 128, kv head, batch); loops over the q heads
-// of the group and over q chunks of 64 rows.  TMEM: S^T [2][128 kv][64 q], dP^T [2][128][64], dV [128][HD],
-// dK [128][HD].  A math thread owns kv row r and 16 of the chunk's 64 q columns.
+// of the group and over q chunks of 64 rows.  TMEM: S^T [128 kv][64 q], dP^T [128][64], dV [128][HD],
+// dK [128][HD].  Thread r owns kv row r.
 // ================================================================================================
 template <int HD>
 struct DkvCfg {
-  static constexpr int kStages = (HD == 64) ? 3 : 2;  // Q / dO chunk stages
-  static constexpr int kKVBytes = 128 * HD * 2;       // K and V tiles (resident)
-  static constexpr int kQBytes = 64 * HD * 2;         // Q / dO chunk
-  static constexpr int kPBytes = 128 * 64 * 2;        // P^T and dS^T, two buffers each
-  static constexpr int kStatBytes = kBwdMathWarps * 2 * 32 * 4;  // per warp: [2 buffers][lse x16 | dsum x16]
-  static constexpr int kSmem = 2 * kKVBytes + 2 * kStages * kQBytes + 4 * kPBytes + kStatBytes + 256;
-  static constexpr int kTmemCols = 512;  // 2*64 + 2*64 + 2*HD, rounded to a power of two
+  static constexpr int kKVBytes = 128 * HD * 2;   // K and V tiles (resident)
+  static constexpr int kQBytes = 64 * HD * 2;     // Q / dO chunk
+  static constexpr int kPBytes = 128 * 64 * 2;    // P^T and dS^T
+  static constexpr int kSmem = 2 * kKVBytes + 4 * kQBytes + 2 * kPBytes + 2 * 2 * 64 * 4 + 128;
+  static constexpr int kTmemCols = (HD == 64) ? 256 : 512;  // 64 + 64 + 2*HD
 };
 
 template <int HD>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kThreads, (HD == 64 ? 2 : 1))
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                      const AttnDev p) {
   using C = DkvCfg<HD>;
-  constexpr int NS = C::kStages;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (smem_u32(smem) & 1023u) {  // the swizzled tiles need a 1 KiB aligned base; uniform early exit
@@ -567,19 +551,21 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   }
   uint8_t* sK = smem;
   uint8_t* sV = sK + C::kKVBytes;
-  uint8_t* sQ = sV + C::kKVBytes;         // NS stages
-  uint8_t* sDO = sQ + NS * C::kQBytes;    // NS stages
-  uint8_t* sPT = sDO + NS * C::kQBytes;   // [2][128 kv][64 q] bf16
-  uint8_t* sDST = sPT + 2 * C::kPBytes;   // [2][128 kv][64 q] bf16
-  float* sStat = reinterpret_cast<float*>(sDST + 2 * C::kPBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sStat) + C::kStatBytes);
+  uint8_t* sQ = sV + C::kKVBytes;        // 2 stages
+  uint8_t* sDO = sQ + 2 * C::kQBytes;    // 2 stages
+  uint8_t* sPT = sDO + 2 * C::kQBytes;   // [128 kv][64 q] bf16
+  uint8_t* sDST = sPT + C::kPBytes;      // [128 kv][64 q] bf16
+  float* sLse = reinterpret_cast<float*>(sDST + C::kPBytes);  // [2][64] (log2 domain)
+  float* sDsum = sLse + 2 * 64;                               // [2][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDsum + 2 * 64);
   uint64_t* kv_full = bars;
-  uint64_t* q_full = bars + 1;            // [NS]
-  uint64_t* q_empty = q_full + NS;        // [NS]
-  uint64_t* s_full = q_empty + NS;        // [2] S^T and dP^T of a chunk ready
-  uint64_t* p_full = s_full + 2;          // [2] P^T and dS^T of a chunk written
-  uint64_t* acc_done = p_full + 2;        // [2] dV/dK MMAs of a chunk retired (its P^T/dS^T buffer is free)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 2);
+  uint64_t* q_full = bars + 1;    // [2]
+  uint64_t* q_empty = bars + 3;   // [2]
+  uint64_t* s_full = bars + 5;    // S^T and dP^T ready
+  uint64_t* p_full = bars + 6;    // P^T and dS^T written
+  uint64_t* acc_done = bars + 7;  // dV/dK MMAs of this chunk retired (P^T/dS^T reusable)
+  uint64_t* stat_full = bars + 8;  // per-q statistics of the chunk staged in shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -602,19 +588,18 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int s = 0; s < NS; ++s) {
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&q_full[s], 1);
       mbar_init(&q_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], kBwdMathWarps);  // one arrival per math warp
-      mbar_init(&acc_done[s], 1);
-    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 4);  // one arrival per math warp
+    mbar_init(acc_done, 1);
+    mbar_init(stat_full, 2);  // warps 0 and 1 stage the statistics
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == kBwdMathWarps + 1) {
+  if (warp == 5) {
     tmem_alloc(tmem_slot, C::kTmemCols);
     tmem_relinquish();
   }
@@ -622,21 +607,21 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_st = tmem_base;          // S^T   [2] x 64 cols
-  const uint32_t tmem_dpt = tmem_base + 128;   // dP^T  [2] x 64 cols
-  const uint32_t tmem_dv = tmem_base + 256;    // dV    HD cols
-  const uint32_t tmem_dk = tmem_base + 256 + HD;
+  const uint32_t tmem_st = tmem_base;         // S^T   64 cols
+  const uint32_t tmem_dpt = tmem_base + 64;   // dP^T  64 cols
+  const uint32_t tmem_dv = tmem_base + 128;   // dV    HD cols
+  const uint32_t tmem_dk = tmem_base + 128 + HD;
 
-  if (warp == kBwdMathWarps) {
+  if (warp == 4) {
     if (lane == 0) {
       mbar_arrive_expect_tx(kv_full, 2 * C::kKVBytes);
       load_tile<HD>(sK, &tm_k, kv_full, 128, k0, hk, b, p.hfirst);
       load_tile<HD>(sV, &tm_v, kv_full, 128, k0, hk, b, p.hfirst);
       for (int it = 0; it < iters; ++it) {
-        const int s = it % NS;
+        const int s = it & 1;
         const int hq = hk * group + it / nchunk;
         const int c0 = (cb + it % nchunk) * 64;
-        if (!mbar_wait_bounded(&q_empty[s], ((it / NS) & 1) ^ 1u, abort_flag)) {
+        if (!mbar_wait_bounded(&q_empty[s], ((it >> 1) & 1) ^ 1u, abort_flag)) {
           atomicCAS(p.status, 0, kStatusTimeoutProducer);
           break;
         }
@@ -645,146 +630,128 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         load_tile<HD>(sDO + s * C::kQBytes, &tm_do, &q_full[s], 64, c0, hq, b, p.hfirst);
       }
     }
-  } else if (warp == kBwdMathWarps + 1) {
+  } else if (warp == 5) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, false, false, 128, 64);   // K Q^T, V dO^T
       const uint32_t idesc_g = make_idesc(kFmtBF16, kFmtBF16, false, true, 128, HD);    // P^T dO, dS^T Q
       bool ok = mbar_wait_bounded(kv_full, 0, abort_flag);
       if (!ok) atomicCAS(p.status, 0, kStatusTimeoutMma);
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV);
-      // pass `it` issues the score MMAs of chunk `it` and then the gradient MMAs of chunk `it - 1`
-      for (int it = 0; it <= iters && ok; ++it) {
-        if (it < iters) {
-          const int s = it % NS, bf = it & 1;
-          if (!mbar_wait_bounded(&q_full[s], (it / NS) & 1, abort_flag)) {
-            atomicCAS(p.status, 0, kStatusTimeoutMma);
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t aQ = smem_u32(sQ + s * C::kQBytes), aDO = smem_u32(sDO + s * C::kQBytes);
-#pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks)
-            umma_f16_ss(tmem_st + bf * 64, desc_kmajor(aK, 128, ks), desc_kmajor(aQ, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
-#pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks)
-            umma_f16_ss(tmem_dpt + bf * 64, desc_kmajor(aV, 128, ks), desc_kmajor(aDO, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
-          umma_commit(&s_full[bf]);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aPT = smem_u32(sPT), aDST = smem_u32(sDST);
+      for (int it = 0; it < iters && ok; ++it) {
+        const int s = it & 1;
+        if (!mbar_wait_bounded(&q_full[s], (it >> 1) & 1, abort_flag)) {
+          atomicCAS(p.status, 0, kStatusTimeoutMma);
+          break;
         }
-        if (it > 0) {
-          const int j = it - 1, s = j % NS, bf = j & 1;
-          if (!mbar_wait_bounded(&p_full[bf], (j >> 1) & 1, abort_flag)) {
-            atomicCAS(p.status, 0, kStatusTimeoutMma);
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t aQ = smem_u32(sQ + s * C::kQBytes), aDO = smem_u32(sDO + s * C::kQBytes);
-          const uint32_t aPT = smem_u32(sPT + bf * C::kPBytes), aDST = smem_u32(sDST + bf * C::kPBytes);
-          // dV += P^T dO ; dK += dS^T Q   (reduction over the 64 q rows of the chunk: 4 k-steps)
+        tc_fence_after_sync();
+        const uint32_t aQ = smem_u32(sQ + s * C::kQBytes), aDO = smem_u32(sDO + s * C::kQBytes);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_f16_ss(tmem_dv, desc_kmajor(aPT, 128, ks), desc_mnmajor(aDO, 64, ks), idesc_g, (j > 0 || ks > 0) ? 1u : 0u);
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_f16_ss(tmem_st, desc_kmajor(aK, 128, ks), desc_kmajor(aQ, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_f16_ss(tmem_dk, desc_kmajor(aDST, 128, ks), desc_mnmajor(aQ, 64, ks), idesc_g, (j > 0 || ks > 0) ? 1u : 0u);
-          umma_commit(&q_empty[s]);
-          umma_commit(&acc_done[bf]);
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_f16_ss(tmem_dpt, desc_kmajor(aV, 128, ks), desc_kmajor(aDO, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
+        umma_commit(s_full);
+        if (!mbar_wait_bounded(p_full, it & 1, abort_flag)) {
+          atomicCAS(p.status, 0, kStatusTimeoutMma);
+          break;
         }
+        tc_fence_after_sync();
+        // dV += P^T dO ; dK += dS^T Q   (reduction over the 64 q rows of the chunk: 4 k-steps)
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_f16_ss(tmem_dv, desc_kmajor(aPT, 128, ks), desc_mnmajor(aDO, 64, ks), idesc_g,
+                      (it > 0 || ks > 0) ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_f16_ss(tmem_dk, desc_kmajor(aDST, 128, ks), desc_mnmajor(aQ, 64, ks), idesc_g,
+                      (it > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&q_empty[s]);
+        umma_commit(acc_done);
       }
     }
   } else {
-    const int quarter = warp & 3, split = warp >> 2;
-    const int r = quarter * 32 + lane;  // kv row inside the block == TMEM lane
+    const int r = warp * 32 + lane;  // kv row inside the block == TMEM lane
     const int k = k0 + r;
-    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const float sc = p.scale * kLog2e;
-    float* strip = sStat + warp * 64;  // [2][lse x16 | dsum x16]
     // queries that may attend to key k:  k - off <= q (causal),  q <= k - off + window - 1 (window)
     int q_row_lo = p.causal ? k - off : 0;
     int q_row_hi = p.Tq - 1;
     if (p.window > 0) q_row_hi = min(q_row_hi, k - off + p.window - 1);
     if (k >= p.Tk) q_row_lo = 0x3fffffff;  // key out of range: nothing valid
     bool ok = true;
-    // this warp's per-q statistics of a chunk (lanes 0-15: lse in the log2 domain, lanes 16-31: dsum), fetched one
-    // chunk ahead so that the load never sits on the critical path
-    auto load_stat = [&](int it) -> float {
-      if (it >= iters) return 0.0f;
+    for (int it = 0; it < iters; ++it) {
       const int hq = hk * group + it / nchunk;
-      const int q = (cb + it % nchunk) * 64 + split * kBwdCols + (lane & 15);
-      const int64_t idx = (static_cast<int64_t>(b) * p.H + hq) * p.Tq + q;
-      if (lane < 16) {
+      const int c0 = (cb + it % nchunk) * 64;
+      // stage the per-q statistics of this chunk (double-buffered by iteration parity)
+      float* lse_s = sLse + (it & 1) * 64;
+      float* ds_s = sDsum + (it & 1) * 64;
+      if (r < 64) {
+        const int q = c0 + r;
+        const int64_t idx = (static_cast<int64_t>(b) * p.H + hq) * p.Tq + q;
         float l = q < p.Tq ? p.lse[idx] : INFINITY;
         if (l == -INFINITY) l = INFINITY;  // row that saw no key: probabilities are zero
-        return l * kLog2e;
+        lse_s[r] = l * kLog2e;
+        ds_s[r] = q < p.Tq ? p.dsum[idx] : 0.0f;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(stat_full);
       }
-      return q < p.Tq ? p.dsum[idx] : 0.0f;
-    };
-    float stat_next = load_stat(0);
-    for (int it = 0; it < iters; ++it) {
-      const int bf = it & 1;
-      const int c0 = (cb + it % nchunk) * 64 + split * kBwdCols;  // first q column of this thread
-      const float stat = stat_next;
-      stat_next = load_stat(it + 1);
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&s_full[bf], (it >> 1) & 1, abort_flag));
-      // the P^T / dS^T buffer is free once the gradient MMAs of chunk it - 2 have retired
-      if (ok && it >= 2) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&acc_done[bf], ((it >> 1) & 1) ^ 1u, abort_flag));
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(stat_full, it & 1, abort_flag));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(s_full, it & 1, abort_flag));
+      if (ok && it > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(acc_done, (it - 1) & 1, abort_flag));
       if (!ok) {
         if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
         break;
       }
-      float* st = strip + bf * 32;
-      st[lane] = stat;
-      __syncwarp();
       tc_fence_after_sync();
-      const int cq = (cb + it % nchunk) * 64;  // first q row of the chunk
-      const bool need_mask = (k0 + 128 > p.Tk) || (cq + 64 > p.Tq) || (p.causal && (k0 + 127 > cq + off)) ||
-                             (p.window > 0 && (k0 < cq + 63 + off - p.window + 1));
-      uint32_t sv[kBwdCols], dv[kBwdCols];
-      tmem_ld_cols16(tmem_st + bf * 64 + lane_addr + split * kBwdCols, sv);
-      tmem_ld_cols16(tmem_dpt + bf * 64 + lane_addr + split * kBwdCols, dv);
-      tmem_ld_wait();
-      const int clo = q_row_lo - c0, chi = q_row_hi - c0;  // valid iff clo <= c <= chi
-      float pr[kBwdCols], dsv[kBwdCols];
+      const bool need_mask = (k0 + 128 > p.Tk) || (c0 + 64 > p.Tq) || (p.causal && (k0 + 127 > c0 + off)) ||
+                             (p.window > 0 && (k0 < c0 + 63 + off - p.window + 1));
+      auto body = [&](auto mask_tag) {
+        constexpr bool kMask = decltype(mask_tag)::value;
+#pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t sv[32], dv[32];
+          tmem_ld_32x32b_x32(tmem_st + lane_addr + cc * 32, sv);
+          tmem_ld_32x32b_x32(tmem_dpt + lane_addr + cc * 32, dv);
+          tmem_ld_wait();
+          const int clo = q_row_lo - c0 - cc * 32, chi = q_row_hi - c0 - cc * 32;  // valid iff clo <= c <= chi
+          float pr[32], dsv[32];
 #pragma unroll
-      for (int g = 0; g < kBwdCols / 4; ++g) {
-        const float4 l4 = reinterpret_cast<const float4*>(st)[g];        // same address in every lane
-        const float4 d4 = reinterpret_cast<const float4*>(st + 16)[g];
-        const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
-        const float dd[4] = {d4.x, d4.y, d4.z, d4.w};
+          for (int c = 0; c < 32; ++c) {
+            const int qi = cc * 32 + c;
+            float e = ex2f(fmaf(__uint_as_float(sv[c]), sc, -lse_s[qi]));
+            if (kMask && (c < clo || c > chi)) e = 0.0f;
+            pr[c] = e;
+            dsv[c] = e * (__uint_as_float(dv[c]) - ds_s[qi]) * p.scale;
+          }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int c = 4 * g + j;
-          float e = ex2f(fmaf(__uint_as_float(sv[c]), sc, -lv[j]));
-          if (need_mask && (c < clo || c > chi)) e = 0.0f;
-          pr[c] = e;
-          dsv[c] = e * (__uint_as_float(dv[c]) - dd[j]) * p.scale;
+          for (int g = 0; g < 4; ++g) {
+            uint4 w, z;
+            w.x = pack_bf16x2(pr[8 * g + 0], pr[8 * g + 1]);
+            w.y = pack_bf16x2(pr[8 * g + 2], pr[8 * g + 3]);
+            w.z = pack_bf16x2(pr[8 * g + 4], pr[8 * g + 5]);
+            w.w = pack_bf16x2(pr[8 * g + 6], pr[8 * g + 7]);
+            z.x = pack_bf16x2(dsv[8 * g + 0], dsv[8 * g + 1]);
+            z.y = pack_bf16x2(dsv[8 * g + 2], dsv[8 * g + 3]);
+            z.z = pack_bf16x2(dsv[8 * g + 4], dsv[8 * g + 5]);
+            z.w = pack_bf16x2(dsv[8 * g + 6], dsv[8 * g + 7]);
+            const uint32_t o = sw128_off(r, cc * 4 + g);
+            *reinterpret_cast<uint4*>(sPT + o) = w;
+            *reinterpret_cast<uint4*>(sDST + o) = z;
+          }
         }
-      }
-      uint8_t* pt = sPT + bf * C::kPBytes;
-      uint8_t* dst = sDST + bf * C::kPBytes;
-#pragma unroll
-      for (int g = 0; g < kBwdCols / 8; ++g) {
-        uint4 w, z;
-        w.x = pack_bf16x2(pr[8 * g + 0], pr[8 * g + 1]);
-        w.y = pack_bf16x2(pr[8 * g + 2], pr[8 * g + 3]);
-        w.z = pack_bf16x2(pr[8 * g + 4], pr[8 * g + 5]);
-        w.w = pack_bf16x2(pr[8 * g + 6], pr[8 * g + 7]);
-        z.x = pack_bf16x2(dsv[8 * g + 0], dsv[8 * g + 1]);
-        z.y = pack_bf16x2(dsv[8 * g + 2], dsv[8 * g + 3]);
-        z.z = pack_bf16x2(dsv[8 * g + 4], dsv[8 * g + 5]);
-        z.w = pack_bf16x2(dsv[8 * g + 6], dsv[8 * g + 7]);
-        const uint32_t o = sw128_off(r, split * (kBwdCols / 8) + g);
-        *reinterpret_cast<uint4*>(pt + o) = w;
-        *reinterpret_cast<uint4*>(dst + o) = z;
-      }
+      };
+      if (need_mask) body(std::true_type{});
+      else body(std::false_type{});
       fence_proxy_async_smem();  // this thread's tile writes -> visible to the tensor core's reads
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[bf]);
+      if (lane == 0) mbar_arrive(p_full);
     }
     // drain: wait for the last accumulation, then write dK / dV rows
     if (ok && iters > 0) {
-      const int j = iters - 1;
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&acc_done[j & 1], (j >> 1) & 1, abort_flag));
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(acc_done, (iters - 1) & 1, abort_flag));
       if (!ok && lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
     }
     if (ok) {  // warp-uniform: the TMEM loads below are warp-collective, only the stores are per row
@@ -795,19 +762,18 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       __nv_bfloat16* dvp = reinterpret_cast<__nv_bfloat16*>(p.out2) + static_cast<int64_t>(b) * p.o2_batch +
                            static_cast<int64_t>(k) * p.o2_row + static_cast<int64_t>(hk) * p.o2_head;
 #pragma unroll 1
-      for (int cc = 0; cc < HD / 64; ++cc) {
-        const int col = split * (HD / kBwdSplit) + cc * 16;
-        uint32_t a[16], c[16];
+      for (int cc = 0; cc < HD / 32; ++cc) {
+        uint32_t a[32], c[32];
         if (iters > 0) {
-          tmem_ld_cols16(tmem_dk + lane_addr + col, a);
-          tmem_ld_cols16(tmem_dv + lane_addr + col, c);
+          tmem_ld_32x32b_x32(tmem_dk + lane_addr + cc * 32, a);
+          tmem_ld_32x32b_x32(tmem_dv + lane_addr + cc * 32, c);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) a[i] = c[i] = 0u;
+          for (int i = 0; i < 32; ++i) a[i] = c[i] = 0u;
         }
 #pragma unroll
-        for (int g = 0; g < 2; ++g) {
+        for (int g = 0; g < 4; ++g) {
           uint4 w, z;
           w.x = pack_bf16x2(__uint_as_float(a[8 * g + 0]), __uint_as_float(a[8 * g + 1]));
           w.y = pack_bf16x2(__uint_as_float(a[8 * g + 2]), __uint_as_float(a[8 * g + 3]));
@@ -818,8 +784,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           z.z = pack_bf16x2(__uint_as_float(c[8 * g + 4]), __uint_as_float(c[8 * g + 5]));
           z.w = pack_bf16x2(__uint_as_float(c[8 * g + 6]), __uint_as_float(c[8 * g + 7]));
           if (row_ok) {
-            reinterpret_cast<uint4*>(dk + col)[g] = w;
-            reinterpret_cast<uint4*>(dvp + col)[g] = z;
+            reinterpret_cast<uint4*>(dk + cc * 32)[g] = w;
+            reinterpret_cast<uint4*>(dvp + cc * 32)[g] = z;
           }
         }
       }
@@ -833,7 +799,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(2000);
     __syncthreads();
   }
-  if (warp == kBwdMathWarps + 1) {
+  if (warp == 5) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, C::kTmemCols);
   }
@@ -841,26 +807,27 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
 // ================================================================================================
 // backward, part 2: dQ.  One CTA per (q block of 128, head, batch); loops over kv chunks of 64.
-// TMEM: S [2][128 q][64 kv], dP [2][128][64], dQ [128][HD].  A math thread owns q row r and 16 of the chunk's
-// 64 kv columns.
+// TMEM: S [128 q][64 kv], dP [128][64], dQ [128][HD].  Thread r owns q row r.
 // ================================================================================================
 template <int HD>
 struct DqCfg {
-  static constexpr int kStages = (HD == 64) ? 3 : 2;  // K / V chunk stages
   static constexpr int kQBytes = 128 * HD * 2;   // Q and dO tiles (resident)
   static constexpr int kKVBytes = 64 * HD * 2;   // K / V chunk
-  static constexpr int kPBytes = 128 * 64 * 2;   // dS, two buffers
-  static constexpr int kSmem = 2 * kQBytes + 2 * kStages * kKVBytes + 2 * kPBytes + 256;
-  static constexpr int kTmemCols = 512;  // 2*64 + 2*64 + HD, rounded to a power of two
+  static constexpr int kPBytes = 128 * 64 * 2;   // dS
+#ifndef NX_DQ_STAGES
+#define NX_DQ_STAGES 2
+#endif
+  static constexpr int kStages = (HD == 64) ? NX_DQ_STAGES : 2;  // K / V chunk stages (a third one measured no faster)
+  static constexpr int kSmem = 2 * kQBytes + 2 * kStages * kKVBytes + kPBytes + 256;
+  static constexpr int kTmemCols = 256;  // 64 + 64 + HD
 };
 
 template <int HD>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kThreads, (HD == 64 ? 2 : 1))
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                    const AttnDev p) {
   using C = DqCfg<HD>;
-  constexpr int NS = C::kStages;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (smem_u32(smem) & 1023u) {  // the swizzled tiles need a 1 KiB aligned base; uniform early exit
@@ -869,17 +836,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   }
   uint8_t* sQ = smem;
   uint8_t* sDO = sQ + C::kQBytes;
+  constexpr int NS = C::kStages;
   uint8_t* sK = sDO + C::kQBytes;        // NS stages
   uint8_t* sV = sK + NS * C::kKVBytes;   // NS stages
-  uint8_t* sDS = sV + NS * C::kKVBytes;  // [2][128 q][64 kv] bf16
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 2 * C::kPBytes);
+  uint8_t* sDS = sV + NS * C::kKVBytes;  // [128 q][64 kv] bf16
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + C::kPBytes);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;        // [NS]
   uint64_t* kv_empty = kv_full + NS;   // [NS]
-  uint64_t* s_full = kv_empty + NS;    // [2]
-  uint64_t* p_full = s_full + 2;       // [2]
-  uint64_t* acc_done = p_full + 2;     // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 2);
+  uint64_t* s_full = kv_empty + NS;
+  uint64_t* p_full = s_full + 1;
+  uint64_t* acc_done = p_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -902,15 +870,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], kBwdMathWarps);  // one arrival per math warp
-      mbar_init(&acc_done[s], 1);
-    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 4);  // one arrival per math warp
+    mbar_init(acc_done, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == kBwdMathWarps + 1) {
+  if (warp == 5) {
     tmem_alloc(tmem_slot, C::kTmemCols);
     tmem_relinquish();
   }
@@ -918,11 +884,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base;          // [2] x 64 cols
-  const uint32_t tmem_dp = tmem_base + 128;   // [2] x 64 cols
-  const uint32_t tmem_dq = tmem_base + 256;
+  const uint32_t tmem_s = tmem_base;
+  const uint32_t tmem_dp = tmem_base + 64;
+  const uint32_t tmem_dq = tmem_base + 128;
 
-  if (warp == kBwdMathWarps) {
+  if (warp == 4) {
     if (lane == 0) {
       mbar_arrive_expect_tx(q_full, 2 * C::kQBytes);
       load_tile<HD>(sQ, &tm_q, q_full, 128, q0, h, b, p.hfirst);
@@ -938,55 +904,47 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         load_tile<HD>(sV + s * C::kKVBytes, &tm_v, &kv_full[s], 64, (jb + it) * 64, hk, b, p.hfirst);
       }
     }
-  } else if (warp == kBwdMathWarps + 1) {
+  } else if (warp == 5) {
     if (lane == 0) {
       const uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, false, false, 128, 64);  // Q K^T, dO V^T
       const uint32_t idesc_g = make_idesc(kFmtBF16, kFmtBF16, false, true, 128, HD);   // dS K
       bool ok = mbar_wait_bounded(q_full, 0, abort_flag);
       if (!ok) atomicCAS(p.status, 0, kStatusTimeoutMma);
-      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO);
-      // pass `it` issues the score MMAs of chunk `it` and then the dQ MMAs of chunk `it - 1`
-      for (int it = 0; it <= iters && ok; ++it) {
-        if (it < iters) {
-          const int s = it % NS, bf = it & 1;
-          if (!mbar_wait_bounded(&kv_full[s], (it / NS) & 1, abort_flag)) {
-            atomicCAS(p.status, 0, kStatusTimeoutMma);
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t aK = smem_u32(sK + s * C::kKVBytes), aV = smem_u32(sV + s * C::kKVBytes);
-#pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks)
-            umma_f16_ss(tmem_s + bf * 64, desc_kmajor(aQ, 128, ks), desc_kmajor(aK, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
-#pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks)
-            umma_f16_ss(tmem_dp + bf * 64, desc_kmajor(aDO, 128, ks), desc_kmajor(aV, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
-          umma_commit(&s_full[bf]);
+      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
+      for (int it = 0; it < iters && ok; ++it) {
+        const int s = it % NS;
+        if (!mbar_wait_bounded(&kv_full[s], (it / NS) & 1, abort_flag)) {
+          atomicCAS(p.status, 0, kStatusTimeoutMma);
+          break;
         }
-        if (it > 0) {
-          const int j = it - 1, s = j % NS, bf = j & 1;
-          if (!mbar_wait_bounded(&p_full[bf], (j >> 1) & 1, abort_flag)) {
-            atomicCAS(p.status, 0, kStatusTimeoutMma);
-            break;
-          }
-          tc_fence_after_sync();
-          const uint32_t aK = smem_u32(sK + s * C::kKVBytes), aDS = smem_u32(sDS + bf * C::kPBytes);
+        tc_fence_after_sync();
+        const uint32_t aK = smem_u32(sK + s * C::kKVBytes), aV = smem_u32(sV + s * C::kKVBytes);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_f16_ss(tmem_dq, desc_kmajor(aDS, 128, ks), desc_mnmajor(aK, 64, ks), idesc_g, (j > 0 || ks > 0) ? 1u : 0u);
-          umma_commit(&kv_empty[s]);
-          umma_commit(&acc_done[bf]);
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_f16_ss(tmem_s, desc_kmajor(aQ, 128, ks), desc_kmajor(aK, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_f16_ss(tmem_dp, desc_kmajor(aDO, 128, ks), desc_kmajor(aV, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
+        umma_commit(s_full);
+        if (!mbar_wait_bounded(p_full, it & 1, abort_flag)) {
+          atomicCAS(p.status, 0, kStatusTimeoutMma);
+          break;
         }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_f16_ss(tmem_dq, desc_kmajor(aDS, 128, ks), desc_mnmajor(aK, 64, ks), idesc_g,
+                      (it > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&kv_empty[s]);
+        umma_commit(acc_done);
       }
     }
   } else {
-    const int quarter = warp & 3, split = warp >> 2;
-    const int r = quarter * 32 + lane;
+    const int r = warp * 32 + lane;
     const int q = q0 + r;
-    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const float sc = p.scale * kLog2e;
     const int off = p.Tk - p.Tq;
-    (void)off;
     const int64_t sidx = (static_cast<int64_t>(b) * p.H + h) * p.Tq + q;
     float lse_n = q < p.Tq ? p.lse[sidx] : INFINITY;
     if (lse_n == -INFINITY) lse_n = INFINITY;  // row that saw no key: probabilities are zero
@@ -997,48 +955,52 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     if (q >= p.Tq) row_lo = 0x3fffffff;
     bool ok = true;
     for (int it = 0; it < iters; ++it) {
-      const int bf = it & 1;
-      const int kc = (jb + it) * 64;               // first key of the chunk
-      const int k0 = kc + split * kBwdCols;        // first key of this thread
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&s_full[bf], (it >> 1) & 1, abort_flag));
-      if (ok && it >= 2) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&acc_done[bf], ((it >> 1) & 1) ^ 1u, abort_flag));
+      const int k0 = (jb + it) * 64;
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(s_full, it & 1, abort_flag));
+      if (ok && it > 0) ok = __all_sync(0xffffffffu, mbar_wait_bounded(acc_done, (it - 1) & 1, abort_flag));
       if (!ok) {
         if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
         break;
       }
       tc_fence_after_sync();
-      const bool need_mask = (kc + 64 > p.Tk) || (q0 + 128 > p.Tq) || (p.causal && (kc + 63 > q0 + (p.Tk - p.Tq))) ||
-                             (p.window > 0 && (kc < q0 + 127 + (p.Tk - p.Tq) - p.window + 1));
-      uint32_t sv[kBwdCols], dv[kBwdCols];
-      tmem_ld_cols16(tmem_s + bf * 64 + lane_addr + split * kBwdCols, sv);
-      tmem_ld_cols16(tmem_dp + bf * 64 + lane_addr + split * kBwdCols, dv);
-      tmem_ld_wait();
-      const int clo = row_lo - k0, chi = row_hi - k0;
-      float dsv[kBwdCols];
+      const bool need_mask = (k0 + 64 > p.Tk) || (q0 + 128 > p.Tq) || (p.causal && (k0 + 63 > q0 + off)) ||
+                             (p.window > 0 && (k0 < q0 + 127 + off - p.window + 1));
+      auto body = [&](auto mask_tag) {
+        constexpr bool kMask = decltype(mask_tag)::value;
+#pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t sv[32], dv[32];
+          tmem_ld_32x32b_x32(tmem_s + lane_addr + cc * 32, sv);
+          tmem_ld_32x32b_x32(tmem_dp + lane_addr + cc * 32, dv);
+          tmem_ld_wait();
+          const int clo = row_lo - k0 - cc * 32, chi = row_hi - k0 - cc * 32;
+          float dsv[32];
 #pragma unroll
-      for (int c = 0; c < kBwdCols; ++c) {
-        float e = ex2f(fmaf(__uint_as_float(sv[c]), sc, -lse2));
-        if (need_mask && (c < clo || c > chi)) e = 0.0f;
-        dsv[c] = e * (__uint_as_float(dv[c]) - dsum) * p.scale;
-      }
-      uint8_t* ds = sDS + bf * C::kPBytes;
+          for (int c = 0; c < 32; ++c) {
+            float e = ex2f(fmaf(__uint_as_float(sv[c]), sc, -lse2));
+            if (kMask && (c < clo || c > chi)) e = 0.0f;
+            dsv[c] = e * (__uint_as_float(dv[c]) - dsum) * p.scale;
+          }
 #pragma unroll
-      for (int g = 0; g < kBwdCols / 8; ++g) {
-        uint4 z;
-        z.x = pack_bf16x2(dsv[8 * g + 0], dsv[8 * g + 1]);
-        z.y = pack_bf16x2(dsv[8 * g + 2], dsv[8 * g + 3]);
-        z.z = pack_bf16x2(dsv[8 * g + 4], dsv[8 * g + 5]);
-        z.w = pack_bf16x2(dsv[8 * g + 6], dsv[8 * g + 7]);
-        *reinterpret_cast<uint4*>(ds + sw128_off(r, split * (kBwdCols / 8) + g)) = z;
-      }
+          for (int g = 0; g < 4; ++g) {
+            uint4 z;
+            z.x = pack_bf16x2(dsv[8 * g + 0], dsv[8 * g + 1]);
+            z.y = pack_bf16x2(dsv[8 * g + 2], dsv[8 * g + 3]);
+            z.z = pack_bf16x2(dsv[8 * g + 4], dsv[8 * g + 5]);
+            z.w = pack_bf16x2(dsv[8 * g + 6], dsv[8 * g + 7]);
+            *reinterpret_cast<uint4*>(sDS + sw128_off(r, cc * 4 + g)) = z;
+          }
+        }
+      };
+      if (need_mask) body(std::true_type{});
+      else body(std::false_type{});
       fence_proxy_async_smem();  // this thread's tile writes -> visible to the tensor core's reads
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[bf]);
+      if (lane == 0) mbar_arrive(p_full);
     }
     if (ok && iters > 0) {
-      const int j = iters - 1;
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&acc_done[j & 1], (j >> 1) & 1, abort_flag));
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(acc_done, (iters - 1) & 1, abort_flag));
       if (!ok && lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
     }
     if (ok) {  // warp-uniform: the TMEM loads below are warp-collective, only the stores are per row
@@ -1047,24 +1009,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       __nv_bfloat16* dq = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(b) * p.o_batch +
                           static_cast<int64_t>(q) * p.o_row + static_cast<int64_t>(h) * p.o_head;
 #pragma unroll 1
-      for (int cc = 0; cc < HD / 64; ++cc) {
-        const int col = split * (HD / kBwdSplit) + cc * 16;
-        uint32_t a[16];
+      for (int cc = 0; cc < HD / 32; ++cc) {
+        uint32_t a[32];
         if (iters > 0) {
-          tmem_ld_cols16(tmem_dq + lane_addr + col, a);
+          tmem_ld_32x32b_x32(tmem_dq + lane_addr + cc * 32, a);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) a[i] = 0u;
+          for (int i = 0; i < 32; ++i) a[i] = 0u;
         }
 #pragma unroll
-        for (int g = 0; g < 2; ++g) {
+        for (int g = 0; g < 4; ++g) {
           uint4 w;
           w.x = pack_bf16x2(__uint_as_float(a[8 * g + 0]), __uint_as_float(a[8 * g + 1]));
           w.y = pack_bf16x2(__uint_as_float(a[8 * g + 2]), __uint_as_float(a[8 * g + 3]));
           w.z = pack_bf16x2(__uint_as_float(a[8 * g + 4]), __uint_as_float(a[8 * g + 5]));
           w.w = pack_bf16x2(__uint_as_float(a[8 * g + 6]), __uint_as_float(a[8 * g + 7]));
-          if (row_ok) reinterpret_cast<uint4*>(dq + col)[g] = w;
+          if (row_ok) reinterpret_cast<uint4*>(dq + cc * 32)[g] = w;
         }
       }
     }
@@ -1077,7 +1038,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(2000);
     __syncthreads();
   }
-  if (warp == kBwdMathWarps + 1) {
+  if (warp == 5) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, C::kTmemCols);
   }
@@ -1222,14 +1183,14 @@ extern "C" int nx_attention_bwd(const NxAttnArgs* a, nx_stream_t stream_) {
         if (set_smem(attn_bwd_dkdv_kernel<64>, DkvCfg<64>::kSmem)) return -2;
         once = true;
       }
-      attn_bwd_dkdv_kernel<64><<<grid, kBwdThreads, DkvCfg<64>::kSmem, st>>>(tq, tk, tv, tdo, p);
+      attn_bwd_dkdv_kernel<64><<<grid, kThreads, DkvCfg<64>::kSmem, st>>>(tq, tk, tv, tdo, p);
     } else {
       static bool once = false;
       if (!once) {
         if (set_smem(attn_bwd_dkdv_kernel<128>, DkvCfg<128>::kSmem)) return -2;
         once = true;
       }
-      attn_bwd_dkdv_kernel<128><<<grid, kBwdThreads, DkvCfg<128>::kSmem, st>>>(tq, tk, tv, tdo, p);
+      attn_bwd_dkdv_kernel<128><<<grid, kThreads, DkvCfg<128>::kSmem, st>>>(tq, tk, tv, tdo, p);
     }
     if (cudaGetLastError() != cudaSuccess) return -2;
   }
@@ -1253,14 +1214,14 @@ extern "C" int nx_attention_bwd(const NxAttnArgs* a, nx_stream_t stream_) {
         if (set_smem(attn_bwd_dq_kernel<64>, DqCfg<64>::kSmem)) return -2;
         once = true;
       }
-      attn_bwd_dq_kernel<64><<<grid, kBwdThreads, DqCfg<64>::kSmem, st>>>(tq, tk, tv, tdo, p);
+      attn_bwd_dq_kernel<64><<<grid, kThreads, DqCfg<64>::kSmem, st>>>(tq, tk, tv, tdo, p);
     } else {
       static bool once = false;
       if (!once) {
         if (set_smem(attn_bwd_dq_kernel<128>, DqCfg<128>::kSmem)) return -2;
         once = true;
       }
-      attn_bwd_dq_kernel<128><<<grid, kBwdThreads, DqCfg<128>::kSmem, st>>>(tq, tk, tv, tdo, p);
+      attn_bwd_dq_kernel<128><<<grid, kThreads, DqCfg<128>::kSmem, st>>>(tq, tk, tv, tdo, p);
     }
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
