@@ -42,7 +42,38 @@ struct AttnDev {
   int items, nqb;      // fwd (persistent): number of work items = nqb * H * B, q blocks per (head, batch)
   float* merge_o;      // fwd: FP32 [B,Tq,H,D] running output of earlier key/value chunks (in/out), or null
   float* merge_lse;    // fwd: FP32 [B,H,Tq] running log-sum-exp (in/out)
+  float softcap;       // > 0: scores pass through softcap * tanh(scale * s / softcap)
+  const float* alibi;  // [H] slopes or null: slope_h * (key position - query position) is added to the scaled score
 };
+
+// Soft-capping and ALiBi, folded into an "effective raw score" s' with scale * s' = cap * tanh(scale * s / cap) +
+// slope * rel, so that the softmax code downstream stays as it is.  `dfac` receives d(scale * s')/d(scale * s).
+struct ScoreExt {
+  float scale, inv_scale, cap, inv_cap, slope;
+};
+__device__ __forceinline__ ScoreExt make_ext(const AttnDev& p, int head) {
+  ScoreExt e;
+  e.scale = p.scale;
+  e.inv_scale = 1.0f / p.scale;
+  e.cap = p.softcap;
+  e.inv_cap = p.softcap > 0.0f ? 1.0f / p.softcap : 0.0f;
+  e.slope = p.alibi != nullptr ? p.alibi[head] : 0.0f;
+  return e;
+}
+__device__ __forceinline__ float score_ext(const ScoreExt& e, float s, int rel, float& dfac) {
+  float z = s * e.scale;
+  dfac = 1.0f;
+  if (e.cap > 0.0f) {
+    const float t = tanh_approx_f(z * e.inv_cap);
+    z = e.cap * t;
+    dfac = 1.0f - t * t;
+  }
+  return fmaf(e.slope, static_cast<float>(rel), z) * e.inv_scale;
+}
+__device__ __forceinline__ float score_ext(const ScoreExt& e, float s, int rel) {
+  float d;
+  return score_ext(e, s, rel, d);
+}
 
 // byte offset of the 16-byte chunk (8 bf16) `chunk` (0..7) of row `r` inside a [rows][64] swizzled slab
 __device__ __forceinline__ uint32_t sw128_off(int r, int chunk) {
@@ -92,8 +123,9 @@ __device__ __forceinline__ void row_limits(const AttnDev& p, int q, int& lo, int
 
 // Forward softmax helpers.  A score row (128 keys) is shared by two threads of different warps: `c0` is
 // the first of the 64 columns this thread owns (0 or 64).
-template <bool kMask>
-__device__ __forceinline__ float half_row_max(uint32_t taddr, int c0, int k0, int lo, int hi) {
+template <bool kMask, bool kExt>
+__device__ __forceinline__ float half_row_max(uint32_t taddr, int c0, int k0, int lo, int hi, const ScoreExt& ext,
+                                              int qpos) {
   float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
   for (int cc = 0; cc < 2; ++cc) {
@@ -105,6 +137,13 @@ __device__ __forceinline__ float half_row_max(uint32_t taddr, int c0, int k0, in
     for (int c = 0; c < 32; c += 4) {
       float s0 = __uint_as_float(v[c]), s1 = __uint_as_float(v[c + 1]), s2 = __uint_as_float(v[c + 2]),
             s3 = __uint_as_float(v[c + 3]);
+      if (kExt) {
+        const int rel = k0 + c0 + cc * 32 + c - qpos;
+        s0 = score_ext(ext, s0, rel);
+        s1 = score_ext(ext, s1, rel + 1);
+        s2 = score_ext(ext, s2, rel + 2);
+        s3 = score_ext(ext, s3, rel + 3);
+      }
       if (kMask) {
         if (c < clo || c > chi) s0 = -INFINITY;
         if (c + 1 < clo || c + 1 > chi) s1 = -INFINITY;
@@ -121,9 +160,9 @@ __device__ __forceinline__ float half_row_max(uint32_t taddr, int c0, int k0, in
 }
 
 // P = exp2(S*sc - m) for this thread's 64 keys -> BF16 into slab `c0 / 64` of the swizzled [128][128] tile.
-template <bool kMask>
+template <bool kMask, bool kExt>
 __device__ __forceinline__ float half_softmax_store(uint32_t taddr, uint8_t* sP, int r, int c0, int k0, int lo, int hi,
-                                                    float sc, float m_use) {
+                                                    float sc, float m_use, const ScoreExt& ext, int qpos) {
   float r0 = 0.0f, r1 = 0.0f, r2 = 0.0f, r3 = 0.0f;
   uint8_t* slab = sP + (c0 >> 6) * (128 * 128);
 #pragma unroll
@@ -138,7 +177,9 @@ __device__ __forceinline__ float half_softmax_store(uint32_t taddr, uint8_t* sP,
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int c = 8 * g + j;
-        float x = ex2f(fmaf(__uint_as_float(v[c]), sc, -m_use));
+        float sv = __uint_as_float(v[c]);
+        if (kExt) sv = score_ext(ext, sv, k0 + c0 + cc * 32 + c - qpos);
+        float x = ex2f(fmaf(sv, sc, -m_use));
         if (kMask && (c < clo || c > chi)) x = 0.0f;
         e[j] = x;
       }
@@ -352,6 +393,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       float m_run = -INFINITY, l_run = 0.0f;  // l_run: partial sum over this thread's columns
       int row_lo, row_hi;
       row_limits(p, q, row_lo, row_hi);
+      const bool ext_on = p.softcap > 0.0f || p.alibi != nullptr;  // uniform over the launch
+      const ScoreExt ext = make_ext(p, h);
       float o_acc[HH];
 #pragma unroll
       for (int c = 0; c < HH; ++c) o_acc[c] = 0.0f;
@@ -368,8 +411,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const bool need_mask = (k0 + 128 > p.Tk) || (p.causal && (k0 + 127 > q0 + off)) ||
                                (p.window > 0 && (k0 < q0 + 127 + off - p.window + 1));
         float mx, rs;
-        if (need_mask) mx = half_row_max<true>(tmem_s + lane_addr, c0, k0, row_lo, row_hi);
-        else mx = half_row_max<false>(tmem_s + lane_addr, c0, k0, row_lo, row_hi);
+        const int qpos = q + off;
+        if (ext_on) {
+          if (need_mask) mx = half_row_max<true, true>(tmem_s + lane_addr, c0, k0, row_lo, row_hi, ext, qpos);
+          else mx = half_row_max<false, true>(tmem_s + lane_addr, c0, k0, row_lo, row_hi, ext, qpos);
+        } else {
+          if (need_mask) mx = half_row_max<true, false>(tmem_s + lane_addr, c0, k0, row_lo, row_hi, ext, qpos);
+          else mx = half_row_max<false, false>(tmem_s + lane_addr, c0, k0, row_lo, row_hi, ext, qpos);
+        }
         // second half publishes, first half combines and publishes the row maximum
         if (half == 1) sX[r] = mx;
         softmax_bar();
@@ -382,8 +431,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const float m_new = fmaxf(m_run, mx * sc);
         const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
         const float alpha = ex2f(m_run - m_use);  // m_run == -inf -> 0
-        if (need_mask) rs = half_softmax_store<true>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use);
-        else rs = half_softmax_store<false>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use);
+        if (ext_on) {
+          if (need_mask) rs = half_softmax_store<true, true>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use, ext, qpos);
+          else rs = half_softmax_store<false, true>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use, ext, qpos);
+        } else {
+          if (need_mask) rs = half_softmax_store<true, false>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use, ext, qpos);
+          else rs = half_softmax_store<false, false>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use, ext, qpos);
+        }
         l_run = l_run * alpha + rs;
         m_run = m_new;
         fence_proxy_async_smem();  // generic-proxy writes of P -> visible to the tensor core's async proxy
@@ -707,8 +761,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tc_fence_after_sync();
       const bool need_mask = (k0 + 128 > p.Tk) || (c0 + 64 > p.Tq) || (p.causal && (k0 + 127 > c0 + off)) ||
                              (p.window > 0 && (k0 < c0 + 63 + off - p.window + 1));
-      auto body = [&](auto mask_tag) {
+      const bool ext_on = p.softcap > 0.0f || p.alibi != nullptr;  // uniform over the launch
+      const ScoreExt ext = make_ext(p, hq);
+      auto body = [&](auto mask_tag, auto ext_tag) {
         constexpr bool kMask = decltype(mask_tag)::value;
+        constexpr bool kExt = decltype(ext_tag)::value;
 #pragma unroll 1
         for (int cc = 0; cc < 2; ++cc) {
           uint32_t sv[32], dv[32];
@@ -720,10 +777,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             const int qi = cc * 32 + c;
-            float e = ex2f(fmaf(__uint_as_float(sv[c]), sc, -lse_s[qi]));
+            float sraw = __uint_as_float(sv[c]), dfac = 1.0f;
+            if (kExt) sraw = score_ext(ext, sraw, k - (c0 + qi + off), dfac);
+            float e = ex2f(fmaf(sraw, sc, -lse_s[qi]));
             if (kMask && (c < clo || c > chi)) e = 0.0f;
             pr[c] = e;
             dsv[c] = e * (__uint_as_float(dv[c]) - ds_s[qi]) * p.scale;
+            if (kExt) dsv[c] *= dfac;
           }
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
@@ -742,8 +802,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           }
         }
       };
-      if (need_mask) body(std::true_type{});
-      else body(std::false_type{});
+      if (ext_on) {
+        if (need_mask) body(std::true_type{}, std::true_type{});
+        else body(std::false_type{}, std::true_type{});
+      } else {
+        if (need_mask) body(std::true_type{}, std::false_type{});
+        else body(std::false_type{}, std::false_type{});
+      }
       fence_proxy_async_smem();  // this thread's tile writes -> visible to the tensor core's reads
       tc_fence_before_sync();
       __syncwarp();
@@ -953,6 +1018,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     int row_lo, row_hi;
     row_limits(p, q, row_lo, row_hi);
     if (q >= p.Tq) row_lo = 0x3fffffff;
+    const bool ext_on = p.softcap > 0.0f || p.alibi != nullptr;  // uniform over the launch
+    const ScoreExt ext = make_ext(p, h);
     bool ok = true;
     for (int it = 0; it < iters; ++it) {
       const int k0 = (jb + it) * 64;
@@ -965,8 +1032,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       tc_fence_after_sync();
       const bool need_mask = (k0 + 64 > p.Tk) || (q0 + 128 > p.Tq) || (p.causal && (k0 + 63 > q0 + off)) ||
                              (p.window > 0 && (k0 < q0 + 127 + off - p.window + 1));
-      auto body = [&](auto mask_tag) {
+      auto body = [&](auto mask_tag, auto ext_tag) {
         constexpr bool kMask = decltype(mask_tag)::value;
+        constexpr bool kExt = decltype(ext_tag)::value;
 #pragma unroll 1
         for (int cc = 0; cc < 2; ++cc) {
           uint32_t sv[32], dv[32];
@@ -977,9 +1045,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           float dsv[32];
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
-            float e = ex2f(fmaf(__uint_as_float(sv[c]), sc, -lse2));
+            float sraw = __uint_as_float(sv[c]), dfac = 1.0f;
+            if (kExt) sraw = score_ext(ext, sraw, k0 + cc * 32 + c - (q + off), dfac);
+            float e = ex2f(fmaf(sraw, sc, -lse2));
             if (kMask && (c < clo || c > chi)) e = 0.0f;
             dsv[c] = e * (__uint_as_float(dv[c]) - dsum) * p.scale;
+            if (kExt) dsv[c] *= dfac;
           }
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
@@ -992,8 +1063,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
           }
         }
       };
-      if (need_mask) body(std::true_type{});
-      else body(std::false_type{});
+      if (ext_on) {
+        if (need_mask) body(std::true_type{}, std::true_type{});
+        else body(std::false_type{}, std::true_type{});
+      } else {
+        if (need_mask) body(std::true_type{}, std::false_type{});
+        else body(std::false_type{}, std::false_type{});
+      }
       fence_proxy_async_smem();  // this thread's tile writes -> visible to the tensor core's reads
       tc_fence_before_sync();
       __syncwarp();
@@ -1084,6 +1160,8 @@ AttnDev base_params(const NxAttnArgs* a) {
   p.causal = a->causal;
   p.window = a->window;
   p.scale = a->scale;
+  p.softcap = a->softcap;
+  p.alibi = a->alibi_slopes;
   p.hfirst = head_first(a->q) ? 1 : 0;
   return p;
 }

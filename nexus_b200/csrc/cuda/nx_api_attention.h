@@ -28,6 +28,9 @@ typedef struct NxAttnArgs {
   // union of the key sets) and writes the merged result to `o` and `lse` as well: one launch per ring step.
   float* merge_o;
   float* merge_lse;
+  float softcap;                // > 0: scores become softcap * tanh(scale * s / softcap) (forward and backward)
+  const float* alibi_slopes;    // [heads] or null: slope_h * (key position - query position), positions aligned
+                                // bottom-right like the causal mask, is added to the scaled score
 } NxAttnArgs;
 
 int nx_attention_fwd(const NxAttnArgs* args, nx_stream_t stream);

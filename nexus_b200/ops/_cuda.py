@@ -57,6 +57,7 @@ class AttnArgs(C.Structure):
         ("batch", C.c_int32), ("heads", C.c_int32), ("kv_heads", C.c_int32), ("tq", C.c_int32), ("tk", C.c_int32),
         ("head_dim", C.c_int32), ("causal", C.c_int32), ("window", C.c_int32), ("scale", C.c_float),
         ("merge_o", C.c_void_p), ("merge_lse", C.c_void_p),
+        ("softcap", C.c_float), ("alibi_slopes", C.c_void_p),
     ]
 
 
@@ -443,7 +444,17 @@ def _view(t: torch.Tensor) -> AttnView:
     return AttnView(t.data_ptr(), t.stride(1), t.stride(2), t.stride(0))
 
 
-def attention_fwd(q, k, v, *, causal=True, window=0, scale=None, out=None, merge_o=None, merge_lse=None):
+def _alibi_ptr(alibi_slopes, heads, device):
+    if alibi_slopes is None:
+        return None
+    if alibi_slopes.dtype != torch.float32 or alibi_slopes.numel() != heads or not alibi_slopes.is_contiguous() \
+            or alibi_slopes.device != device:
+        raise ValueError("attention: alibi_slopes must be a contiguous FP32 tensor of [heads] on the same device")
+    return alibi_slopes.data_ptr()
+
+
+def attention_fwd(q, k, v, *, causal=True, window=0, scale=None, out=None, merge_o=None, merge_lse=None,
+                  softcap=0.0, alibi_slopes=None):
     """q [B,Tq,H,D], k/v [B,Tk,Hkv,D] bf16 (strided views allowed).  Returns (o, lse[B,H,Tq]).
     ``merge_o`` (FP32 [B,Tq,H,D]) / ``merge_lse`` (FP32 [B,H,Tq]): running result of earlier key/value
     chunks; this chunk is merged into them in the kernel's epilogue (ring / chunked attention)."""
@@ -458,6 +469,7 @@ def attention_fwd(q, k, v, *, causal=True, window=0, scale=None, out=None, merge
     a.batch, a.heads, a.kv_heads, a.tq, a.tk, a.head_dim = B, H, Hkv, Tq, Tk, D
     a.causal, a.window = int(causal), int(window)
     a.scale = scale if scale is not None else D ** -0.5
+    a.softcap, a.alibi_slopes = float(softcap), _alibi_ptr(alibi_slopes, H, q.device)
     if merge_o is not None:
         if not (merge_o.is_contiguous() and merge_lse.is_contiguous() and merge_o.dtype == torch.float32):
             raise ValueError("attention_fwd: merge buffers must be contiguous FP32")
@@ -466,7 +478,8 @@ def attention_fwd(q, k, v, *, causal=True, window=0, scale=None, out=None, merge
     return o, lse
 
 
-def attention_bwd(q, k, v, o, lse, d_o, *, causal=True, window=0, scale=None, dq=None, dk=None, dv=None):
+def attention_bwd(q, k, v, o, lse, d_o, *, causal=True, window=0, scale=None, dq=None, dk=None, dv=None,
+                  softcap=0.0, alibi_slopes=None):
     B, Tq, H, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
     dq = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device) if dq is None else dq
@@ -481,5 +494,6 @@ def attention_bwd(q, k, v, o, lse, d_o, *, causal=True, window=0, scale=None, dq
     a.batch, a.heads, a.kv_heads, a.tq, a.tk, a.head_dim = B, H, Hkv, Tq, Tk, D
     a.causal, a.window = int(causal), int(window)
     a.scale = scale if scale is not None else D ** -0.5
+    a.softcap, a.alibi_slopes = float(softcap), _alibi_ptr(alibi_slopes, H, q.device)
     _check(lib().nx_attention_bwd(C.byref(a), _stream()), "nx_attention_bwd")
     return dq, dk, dv

@@ -254,7 +254,7 @@ def moe_combine(ws, bufs: SymmetricBuffer, expert, slot, gate, y, local_experts:
 
 # ---------------------------------------------------------------------------------------------- context parallel
 class RingAttention:
-    """Forward ring attention over symmetric memory: every rank publishes its K/V chunk once; each step
+    """Ring attention (forward and backward) over symmetric memory: every rank publishes its K/V chunk once; each step
     runs ONE attention kernel whose TMA loads read the owner's K/V straight from peer memory (plain,
     non-multicast loads) and whose epilogue merges the chunk into the running FP32 output / LSE.
     Layouts: ``contiguous`` (rank r holds tokens [r*Tl, (r+1)*Tl)) or ``zigzag`` (rank r holds chunks
@@ -312,6 +312,72 @@ class RingAttention:
                                     merge_o=acc[qi][0], merge_lse=acc[qi][1])
         ws.barrier()
         return torch.cat(o_half, dim=1), torch.cat([acc[0][1], acc[1][1]], dim=2)
+
+
+    # ------------------------------------------------------------------ backward
+    def _grad_buffers(self):
+        """Symmetric BF16 buffer [n owners][dk | dv][B, Tl, Hkv, D]: slot j collects what this rank's queries
+        contribute to the keys / values of rank j; the owners pull and sum their slots at the end."""
+        if not hasattr(self, "g_sym"):
+            B, Tl, Hkv, D = self.shape
+            self.slot = 2 * B * Tl * Hkv * D
+            self.g_sym = self.ws.alloc(self.ws.n * self.slot, torch.bfloat16)
+        return self.g_sym
+
+    def backward(self, q, k, v, o, lse, d_o, causal: bool = True):
+        """Gradients of ``forward``.  q/o/d_o [B, Tl, H, D], k/v [B, Tl, Hkv, D], lse [B, H, Tl] as returned by
+        ``forward`` (the log-sum-exp over ALL keys, so every chunk's probabilities come out right).  Each step
+        runs the two backward kernels on one rank's K/V chunk read from peer memory; dQ accumulates locally in
+        FP32, the chunk's dK/dV go into that owner's slot of a symmetric buffer, and after a barrier every rank
+        sums its own slot over the peers with the fused reduce kernel.  Returns (dq, dk, dv) in BF16.
+        Parity: src/dist/context_parallel.cpp (ring_attention_backward) of the reference."""
+        ws, n, r = self.ws, self.ws.n, self.ws.rank
+        B, Tl, H, D = q.shape
+        Hkv = self.shape[2]
+        g = self._grad_buffers()
+        self.k_sym.local.view(self.shape).copy_(k)
+        self.v_sym.local.view(self.shape).copy_(v)
+        g.local.zero_()
+        ws.barrier()                                   # K/V published; nobody still reads the previous slots
+        slots = g.local.view(n, 2, B, Tl, Hkv, D)
+        dq_acc = torch.zeros((B, Tl, H, D), dtype=torch.float32, device=q.device)
+        if not causal or self.layout == "contiguous":
+            dq_p = torch.empty_like(q)
+            for s in range(n):
+                src = (r - s) % n
+                if causal and src > r:
+                    continue
+                K.attention_bwd(q, self.k_peer[src], self.v_peer[src], o, lse, d_o, causal=causal and src == r,
+                                dq=dq_p, dk=slots[src, 0], dv=slots[src, 1])
+                dq_acc += dq_p
+        else:
+            half = Tl // 2
+            dq_p = torch.empty((B, half, H, D), dtype=q.dtype, device=q.device)
+            dk_p = torch.empty((B, half, Hkv, D), dtype=q.dtype, device=q.device)
+            dv_p = torch.empty_like(dk_p)
+            for s in range(n):
+                src = (r - s) % n
+                kk, vv = self.k_peer[src], self.v_peer[src]
+                for qi, qc in enumerate((r, 2 * n - 1 - r)):
+                    qs = slice(qi * half, (qi + 1) * half)
+                    for ki, kc in enumerate((src, 2 * n - 1 - src)):
+                        if kc > qc:
+                            continue
+                        ks = slice(ki * half, (ki + 1) * half)
+                        K.attention_bwd(q[:, qs], kk[:, ks], vv[:, ks], o[:, qs], lse[:, :, qs].contiguous(),
+                                        d_o[:, qs], causal=(kc == qc), dq=dq_p, dk=dk_p, dv=dv_p)
+                        dq_acc[:, qs] += dq_p
+                        slots[src, 0][:, ks] += dk_p
+                        slots[src, 1][:, ks] += dv_p
+        ws.barrier()                                   # every rank's slots are complete
+        dkv = torch.empty((2, B, Tl, Hkv, D), dtype=torch.bfloat16, device=q.device)
+        own = _table([dkv.data_ptr() - r * self.slot * 2])   # the kernel indexes outputs by global offset
+        K._check(K.lib().nx_comm_allreduce_shard(C.byref(g.table), C.c_int(K._DT[torch.bfloat16]), C.c_int(n),
+                                                 C.byref(own), C.c_int(K._DT[torch.bfloat16]), C.c_int(1),
+                                                 C.c_int64(r * self.slot), C.c_int64(self.slot), C.c_float(1.0),
+                                                 K._stream()), "nx_comm_allreduce_shard")
+        ws.barrier()                                   # slots may be overwritten again
+        return dq_acc.to(q.dtype), dkv[0], dkv[1]
 
 
 def ulysses_attention(ws: SymmetricWorkspace, q, k, v, causal: bool = True):

@@ -61,3 +61,34 @@ def test_attention_fwd_bwd(B, Tq, Tk, H, Hkv, D, causal, window, packed):
     oref.backward(do.float())
     for got, want in ((dq, qr.grad), (dk, kr.grad), (dv, vr.grad)):
         assert (got.float() - want).abs().max() <= 3e-2 * want.abs().max()
+
+
+@pytest.mark.parametrize("softcap,alibi,causal,window,Tq,Tk,H,Hkv,D", [
+    (30.0, False, True, 0, 384, 384, 4, 4, 64),
+    (0.0, True, True, 0, 384, 384, 4, 2, 64),
+    (20.0, True, True, 100, 300, 300, 2, 2, 64),
+    (15.0, True, False, 0, 200, 328, 2, 2, 128),
+])
+def test_attention_softcap_alibi(softcap, alibi, causal, window, Tq, Tk, H, Hkv, D):
+    """Soft-capping and ALiBi inside the tensor-core kernels (forward and both backward kernels) against autograd
+    through the FP32 math reference, and through the public fused op."""
+    from nexus_b200.fused import ops as F
+    from nexus_b200.ops import _cuda as K
+    torch.manual_seed(1)
+    dev = "cuda"
+    q = (torch.randn(2, Tq, H, D, device=dev) * 1.5).bfloat16()
+    k = (torch.randn(2, Tk, Hkv, D, device=dev) * 1.5).bfloat16()
+    v = torch.randn(2, Tk, Hkv, D, device=dev).bfloat16()
+    slopes = (2.0 ** (-torch.arange(1, H + 1, device=dev, dtype=torch.float32))) if alibi else None
+    qr, kr, vr = [t.float().detach().requires_grad_(True) for t in (q, k, v)]
+    oref = F.attention_reference(qr, kr, vr, causal, window, None, softcap, slopes)
+    qg, kg, vg = [t.detach().requires_grad_(True) for t in (q, k, v)]
+    o = F.attention(qg, kg, vg, causal, window, None, softcap, slopes)
+    K.check_status()
+    assert (o.float() - oref).abs().max() < 2e-2
+    do = torch.randn_like(o)
+    o.backward(do)
+    K.check_status()
+    oref.backward(do.float())
+    for got, want in ((qg.grad, qr.grad), (kg.grad, kr.grad), (vg.grad, vr.grad)):
+        assert (got.float() - want).abs().max() <= 3e-2 * want.abs().max()

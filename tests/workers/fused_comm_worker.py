@@ -100,6 +100,20 @@ def main():
     o, _ = zz.forward(qf[:, idx].contiguous(), kf[:, idx].contiguous(), vf[:, idx].contiguous(), causal=True)
     torch.cuda.synchronize()
     check("ring attention (zigzag)", (o.float() - ref_o[:, idx].float()).abs().max().item() < 3e-2)
+    # ring backward: gradients of the local tokens against the backward of full attention over all tokens
+    dof = torch.randn(Bc, Tl * world, Hc, Dc, device=dev).bfloat16()
+    pg.broadcast_tensor(dof, 0)
+    ref_o2, ref_lse = K.attention_fwd(qf, kf, vf, causal=True)
+    rdq, rdk, rdv = K.attention_bwd(qf, kf, vf, ref_o2, ref_lse, dof, causal=True)
+    for name, ra, tok in (("contiguous", ring, sl), ("zigzag", zz, idx)):
+        ql, kl, vl, dl = (t[:, tok].contiguous() for t in (qf, kf, vf, dof))
+        ol, lsel = ra.forward(ql, kl, vl, causal=True)
+        dq, dk, dv = ra.backward(ql, kl, vl, ol, lsel, dl, causal=True)
+        torch.cuda.synchronize()
+        good = True
+        for got, want in ((dq, rdq[:, tok]), (dk, rdk[:, tok]), (dv, rdv[:, tok])):
+            good &= (got.float() - want.float()).abs().max().item() <= 4e-2 * want.float().abs().max().item()
+        check(f"ring attention backward ({name})", good)
     o = ulysses_attention(ws, qf[:, sl].contiguous(), kf[:, sl].contiguous(), vf[:, sl].contiguous(), causal=True)
     torch.cuda.synchronize()
     check("ulysses attention", (o.float() - ref_o[:, sl].float()).abs().max().item() < 3e-2)
