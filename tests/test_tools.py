@@ -92,3 +92,23 @@ def test_bench_evidence_rules(tmp_path):
     bad.write_text("import sys; sys.exit(3)")
     with pytest.raises(RuntimeError):
         V.run_worker([sys.executable, str(bad)])
+
+
+def test_docs_site_builds(tmp_path):
+    """Every Markdown page under docs/ renders to an HTML page with the navigation and working relative links."""
+    import os
+    import re
+    from pathlib import Path
+
+    from nexus_b200.tools import site
+    root = Path(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    files = site.build(root / "docs", tmp_path)
+    names = {f.name for f in files}
+    assert {"index.html", "kernels.html", "distributed.html"} <= names
+    index = (tmp_path / "index.html").read_text()
+    assert "<table>" in index and '<a href="kernels.html">' in index and "<nav>" in index
+    for target in re.findall(r'href="([^"#:]+\.html)"', index):
+        assert (tmp_path / target).exists(), target
+    body, title = site.render_markdown("# T\n\ntext with `a*b*c` and *em* and [l](x.md#frag)\n\n```\n<raw>\n```\n\n1. one\n2. two\n")
+    assert title == "T" and "<code>a*b*c</code>" in body and "<em>em</em>" in body
+    assert 'href="x.html#frag"' in body and "&lt;raw&gt;" in body and "<ol><li>one</li><li>two</li></ol>" in body
