@@ -249,6 +249,36 @@ def attention(q, k, v, causal=True, window=0, scale=None, softcap=0.0, alibi_slo
                                dropout_offset)
 
 
+def attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k=None, causal=True, window=0, scale=None, softcap=0.0,
+                     alibi_slopes=None, dropout_p=0.0, dropout_seed=0, dropout_offset=0):
+    """Attention over a packed batch of variable-length sequences.
+
+    q [total_q, H, D], k / v [total_k, Hkv, D]; ``cu_seqlens_*`` are the [batch + 1] cumulative lengths
+    (``cu_seqlens_k`` defaults to ``cu_seqlens_q``).  Sequence i attends only to itself; the causal mask is
+    bottom-right aligned when its query and key lengths differ.  Each sequence is one launch of the tensor-core
+    kernels on a strided view of the packed tensors (no copy, no padding), so the gradients flow through the same
+    backward kernels.  Parity: the cu_seqlens fields of include/nexus/attention/params.hpp of the reference.
+    """
+    cq = [int(x) for x in (cu_seqlens_q.tolist() if torch.is_tensor(cu_seqlens_q) else cu_seqlens_q)]
+    ck = cq if cu_seqlens_k is None else \
+        [int(x) for x in (cu_seqlens_k.tolist() if torch.is_tensor(cu_seqlens_k) else cu_seqlens_k)]
+    if len(cq) != len(ck) or len(cq) < 2 or cq[0] != 0 or ck[0] != 0 or cq[-1] != q.shape[0] or ck[-1] != k.shape[0]:
+        raise ValueError("attention_varlen: cumulative lengths do not describe the packed tensors")
+    outs = []
+    for i in range(len(cq) - 1):
+        if cq[i + 1] < cq[i] or ck[i + 1] < ck[i]:
+            raise ValueError("attention_varlen: cumulative lengths must not decrease")
+        if cq[i + 1] == cq[i]:
+            continue
+        if ck[i + 1] == ck[i]:          # no key at all: the output rows are zero
+            outs.append(torch.zeros_like(q[cq[i]:cq[i + 1]]))
+            continue
+        o = attention(q[None, cq[i]:cq[i + 1]], k[None, ck[i]:ck[i + 1]], v[None, ck[i]:ck[i + 1]], causal, window,
+                      scale, softcap, alibi_slopes, dropout_p, dropout_seed, dropout_offset + cq[i])
+        outs.append(o[0])
+    return torch.cat(outs, 0) if outs else torch.zeros_like(q)
+
+
 # ------------------------------------------------------------------------------------ cross-entropy
 def _ce_reference(logits, targets, ignore_index, smoothing, z_loss):
     """logits [N, V] float, targets [N] long.  Mean over valid targets of

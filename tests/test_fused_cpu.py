@@ -80,3 +80,33 @@ def test_attention_reference_matches_fp64_oracle():
     got = F_.attention_reference(q, k, v, causal=True, window=6, softcap=5.0)
     want = _native.math_attention(q.double().numpy(), k.double().numpy(), v.double().numpy(), True, 6, 8 ** -0.5, 5.0)
     assert np.allclose(got.numpy(), want, atol=1e-5)
+
+
+def test_attention_varlen_matches_per_sequence_attention():
+    """The packed variable-length op equals attention run on each sequence alone (values and gradients)."""
+    from nexus_b200.fused import ops as F
+    torch.manual_seed(3)
+    lens_q, lens_k = [5, 0, 17, 9], [8, 3, 17, 0]
+    cq = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)))
+    ck = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)))
+    H, Hkv, D = 4, 2, 16
+    q = torch.randn(sum(lens_q), H, D, requires_grad=True)
+    k = torch.randn(sum(lens_k), Hkv, D, requires_grad=True)
+    v = torch.randn(sum(lens_k), Hkv, D, requires_grad=True)
+    out = F.attention_varlen(q, k, v, cq, ck, causal=True, softcap=20.0)
+    assert out.shape == q.shape
+    w = torch.randn_like(out)
+    (out * w).sum().backward()
+    got = (q.grad.clone(), k.grad.clone(), v.grad.clone())
+    q.grad = k.grad = v.grad = None
+    ref = torch.zeros_like(out)
+    for i in range(4):
+        a, b, c, d = int(cq[i]), int(cq[i + 1]), int(ck[i]), int(ck[i + 1])
+        if b > a and d > c:
+            ref[a:b] = F.attention_reference(q[None, a:b], k[None, c:d], v[None, c:d], True, 0, None, 20.0)[0]
+    assert torch.allclose(out, ref.detach(), atol=1e-6)
+    (ref * w).sum().backward()
+    for g, r in zip(got, (q.grad, k.grad, v.grad)):
+        assert torch.allclose(g, r, atol=1e-5)
+    with pytest.raises(ValueError):
+        F.attention_varlen(q, k, v, torch.tensor([0, 3]), ck)
