@@ -44,15 +44,57 @@ struct AttnDev {
   float* merge_lse;    // fwd: FP32 [B,H,Tq] running log-sum-exp (in/out)
   float softcap;       // > 0: scores pass through softcap * tanh(scale * s / softcap)
   const float* alibi;  // [H] slopes or null: slope_h * (key position - query position) is added to the scaled score
+  float dropout_p;     // > 0: probabilities are dropped with this rate (the row sums are not)
+  uint64_t drop_seed, drop_offset;  // Philox stream; element ((b*H + h)*Tq + q)*Tk + k of it decides P[b,h,q,k]
 };
+
+// Philox4x32-10, the generator of every dropout in this library: element i of a stream uses counter block
+// offset + i / 4 and lane i % 4; u = top 24 bits / 2^24; an element is kept iff u >= p.
+__device__ __forceinline__ void attn_philox4x32_10(uint32_t (&ctr)[4], uint32_t k0, uint32_t k1) {
+  const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(M0, ctr[0]), lo0 = M0 * ctr[0];
+    const uint32_t hi1 = __umulhi(M1, ctr[2]), lo1 = M1 * ctr[2];
+    const uint32_t n0 = hi1 ^ ctr[1] ^ k0, n1 = lo1, n2 = hi0 ^ ctr[3] ^ k1, n3 = lo0;
+    ctr[0] = n0; ctr[1] = n1; ctr[2] = n2; ctr[3] = n3;
+    k0 += W0;
+    k1 += W1;
+  }
+}
 
 // Soft-capping and ALiBi, folded into an "effective raw score" s' with scale * s' = cap * tanh(scale * s / cap) +
 // slope * rel, so that the softmax code downstream stays as it is.  `dfac` receives d(scale * s')/d(scale * s).
 struct ScoreExt {
   float scale, inv_scale, cap, inv_cap, slope;
+  float drop_p, keep_inv;   // dropout rate and 1 / (1 - rate)
+  uint32_t key0, key1;      // Philox key (the seed)
+  uint64_t offset, head_base;  // stream offset; flat index of P[b, h, 0, 0]
+  int Tk;
 };
-__device__ __forceinline__ ScoreExt make_ext(const AttnDev& p, int head) {
+// 1 / (1 - p) when element `idx` of the stream is kept, 0 when it is dropped
+__device__ __forceinline__ float drop_scale(const ScoreExt& e, uint64_t idx) {
+  const uint64_t blk = e.offset + (idx >> 2);
+  uint32_t ctr[4] = {static_cast<uint32_t>(blk), static_cast<uint32_t>(blk >> 32), 0u, 0u};
+  attn_philox4x32_10(ctr, e.key0, e.key1);
+  const uint32_t lane = static_cast<uint32_t>(idx) & 3u;
+  const uint32_t x = lane == 0 ? ctr[0] : (lane == 1 ? ctr[1] : (lane == 2 ? ctr[2] : ctr[3]));
+  const float u = static_cast<float>(x >> 8) * (1.0f / 16777216.0f);
+  return u >= e.drop_p ? e.keep_inv : 0.0f;
+}
+// the same for the probability of query row q (inside its sequence) and key k
+__device__ __forceinline__ float drop_scale_qk(const ScoreExt& e, int q, int k) {
+  return drop_scale(e, e.head_base + static_cast<uint64_t>(q) * static_cast<uint64_t>(e.Tk) + static_cast<uint64_t>(k));
+}
+__device__ __forceinline__ ScoreExt make_ext(const AttnDev& p, int head, int batch) {
   ScoreExt e;
+  e.drop_p = p.dropout_p;
+  e.keep_inv = p.dropout_p > 0.0f ? 1.0f / (1.0f - p.dropout_p) : 1.0f;
+  e.key0 = static_cast<uint32_t>(p.drop_seed);
+  e.key1 = static_cast<uint32_t>(p.drop_seed >> 32);
+  e.offset = p.drop_offset;
+  e.head_base = (static_cast<uint64_t>(batch) * p.H + head) * static_cast<uint64_t>(p.Tq) * static_cast<uint64_t>(p.Tk);
+  e.Tk = p.Tk;
   e.scale = p.scale;
   e.inv_scale = 1.0f / p.scale;
   e.cap = p.softcap;
@@ -162,7 +204,7 @@ __device__ __forceinline__ float half_row_max(uint32_t taddr, int c0, int k0, in
 // P = exp2(S*sc - m) for this thread's 64 keys -> BF16 into slab `c0 / 64` of the swizzled [128][128] tile.
 template <bool kMask, bool kExt>
 __device__ __forceinline__ float half_softmax_store(uint32_t taddr, uint8_t* sP, int r, int c0, int k0, int lo, int hi,
-                                                    float sc, float m_use, const ScoreExt& ext, int qpos) {
+                                                    float sc, float m_use, const ScoreExt& ext, int qpos, int qoff) {
   float r0 = 0.0f, r1 = 0.0f, r2 = 0.0f, r3 = 0.0f;
   uint8_t* slab = sP + (c0 >> 6) * (128 * 128);
 #pragma unroll
@@ -187,6 +229,10 @@ __device__ __forceinline__ float half_softmax_store(uint32_t taddr, uint8_t* sP,
       r1 += e[1] + e[5];
       r2 += e[2] + e[6];
       r3 += e[3] + e[7];
+      if (kExt && ext.drop_p > 0.0f) {  // the row sum keeps every probability; the tile that meets V does not
+#pragma unroll
+        for (int j = 0; j < 8; ++j) e[j] *= drop_scale_qk(ext, qpos - qoff, k0 + c0 + cc * 32 + 8 * g + j);
+      }
       uint4 w;
       w.x = pack_bf16x2(e[0], e[1]);
       w.y = pack_bf16x2(e[2], e[3]);
@@ -238,7 +284,7 @@ __device__ __forceinline__ void fwd_item(const AttnDev& p, int item, int& qb, in
   b = rem / p.H;
 }
 
-template <int HD>
+template <int HD, bool EXT>  // EXT: soft-capping / ALiBi / dropout row math (a build of its own)
 __global__ void __launch_bounds__(kFwdThreads, (HD == 64 ? 2 : 1))
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnDev p) {
@@ -393,8 +439,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       float m_run = -INFINITY, l_run = 0.0f;  // l_run: partial sum over this thread's columns
       int row_lo, row_hi;
       row_limits(p, q, row_lo, row_hi);
-      const bool ext_on = p.softcap > 0.0f || p.alibi != nullptr;  // uniform over the launch
-      const ScoreExt ext = make_ext(p, h);
+      constexpr bool ext_on = EXT;
+      const ScoreExt ext = EXT ? make_ext(p, h, b) : ScoreExt{};
       float o_acc[HH];
 #pragma unroll
       for (int c = 0; c < HH; ++c) o_acc[c] = 0.0f;
@@ -432,11 +478,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
         const float alpha = ex2f(m_run - m_use);  // m_run == -inf -> 0
         if (ext_on) {
-          if (need_mask) rs = half_softmax_store<true, true>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use, ext, qpos);
-          else rs = half_softmax_store<false, true>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use, ext, qpos);
+          if (need_mask) rs = half_softmax_store<true, true>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use, ext, qpos, off);
+          else rs = half_softmax_store<false, true>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use, ext, qpos, off);
         } else {
-          if (need_mask) rs = half_softmax_store<true, false>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use, ext, qpos);
-          else rs = half_softmax_store<false, false>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use, ext, qpos);
+          if (need_mask) rs = half_softmax_store<true, false>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use, ext, qpos, off);
+          else rs = half_softmax_store<false, false>(tmem_s + lane_addr, sP, r, c0, k0, row_lo, row_hi, sc, m_use, ext, qpos, off);
         }
         l_run = l_run * alpha + rs;
         m_run = m_new;
@@ -591,7 +637,7 @@ struct DkvCfg {
   static constexpr int kTmemCols = (HD == 64) ? 256 : 512;  // 64 + 64 + 2*HD
 };
 
-template <int HD>
+template <int HD, bool EXT>  // EXT: soft-capping / ALiBi / dropout row math (a build of its own)
 __global__ void __launch_bounds__(kThreads, (HD == 64 ? 2 : 1))
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -761,8 +807,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tc_fence_after_sync();
       const bool need_mask = (k0 + 128 > p.Tk) || (c0 + 64 > p.Tq) || (p.causal && (k0 + 127 > c0 + off)) ||
                              (p.window > 0 && (k0 < c0 + 63 + off - p.window + 1));
-      const bool ext_on = p.softcap > 0.0f || p.alibi != nullptr;  // uniform over the launch
-      const ScoreExt ext = make_ext(p, hq);
+      constexpr bool ext_on = EXT;
+      const ScoreExt ext = EXT ? make_ext(p, hq, b) : ScoreExt{};
       auto body = [&](auto mask_tag, auto ext_tag) {
         constexpr bool kMask = decltype(mask_tag)::value;
         constexpr bool kExt = decltype(ext_tag)::value;
@@ -781,8 +827,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
             if (kExt) sraw = score_ext(ext, sraw, k - (c0 + qi + off), dfac);
             float e = ex2f(fmaf(sraw, sc, -lse_s[qi]));
             if (kMask && (c < clo || c > chi)) e = 0.0f;
-            pr[c] = e;
-            dsv[c] = e * (__uint_as_float(dv[c]) - ds_s[qi]) * p.scale;
+            float dp = __uint_as_float(dv[c]), keep = 1.0f;
+            if (kExt && ext.drop_p > 0.0f) {
+              keep = drop_scale_qk(ext, c0 + qi, k);
+              dp *= keep;
+            }
+            pr[c] = e * keep;  // what met V in the forward pass
+            dsv[c] = e * (dp - ds_s[qi]) * p.scale;
             if (kExt) dsv[c] *= dfac;
           }
 #pragma unroll
@@ -887,7 +938,7 @@ struct DqCfg {
   static constexpr int kTmemCols = 256;  // 64 + 64 + HD
 };
 
-template <int HD>
+template <int HD, bool EXT>  // EXT: soft-capping / ALiBi / dropout row math (a build of its own)
 __global__ void __launch_bounds__(kThreads, (HD == 64 ? 2 : 1))
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -1018,8 +1069,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     int row_lo, row_hi;
     row_limits(p, q, row_lo, row_hi);
     if (q >= p.Tq) row_lo = 0x3fffffff;
-    const bool ext_on = p.softcap > 0.0f || p.alibi != nullptr;  // uniform over the launch
-    const ScoreExt ext = make_ext(p, h);
+    constexpr bool ext_on = EXT;
+    const ScoreExt ext = EXT ? make_ext(p, h, b) : ScoreExt{};
     bool ok = true;
     for (int it = 0; it < iters; ++it) {
       const int k0 = (jb + it) * 64;
@@ -1049,7 +1100,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             if (kExt) sraw = score_ext(ext, sraw, k0 + cc * 32 + c - (q + off), dfac);
             float e = ex2f(fmaf(sraw, sc, -lse2));
             if (kMask && (c < clo || c > chi)) e = 0.0f;
-            dsv[c] = e * (__uint_as_float(dv[c]) - dsum) * p.scale;
+            float dp = __uint_as_float(dv[c]);
+            if (kExt && ext.drop_p > 0.0f) dp *= drop_scale_qk(ext, q, k0 + cc * 32 + c);
+            dsv[c] = e * (dp - dsum) * p.scale;
             if (kExt) dsv[c] *= dfac;
           }
 #pragma unroll
@@ -1162,6 +1215,9 @@ AttnDev base_params(const NxAttnArgs* a) {
   p.scale = a->scale;
   p.softcap = a->softcap;
   p.alibi = a->alibi_slopes;
+  p.dropout_p = a->dropout_p;
+  p.drop_seed = a->dropout_seed;
+  p.drop_offset = a->dropout_offset;
   p.hfirst = head_first(a->q) ? 1 : 0;
   return p;
 }
@@ -1171,6 +1227,7 @@ int check_args(const NxAttnArgs* a) {
   if (a->head_dim != 64 && a->head_dim != 128) return -1;
   if (a->batch <= 0 || a->heads <= 0 || a->kv_heads <= 0 || a->heads % a->kv_heads) return -1;
   if (a->tq <= 0 || a->tk <= 0) return -1;
+  if (!(a->dropout_p >= 0.0f && a->dropout_p < 1.0f) || a->softcap < 0.0f) return -1;
   // every TMA-read view must share one coordinate order
   const bool hf = head_first(a->q);
   if (head_first(a->k) != hf || head_first(a->v) != hf) return -1;
@@ -1201,21 +1258,24 @@ extern "C" int nx_attention_fwd(const NxAttnArgs* a, nx_stream_t stream_) {
     return -2;
   // one persistent CTA per slot: two per SM for head_dim 64 (registers / shared memory allow it), one otherwise
   const int grid = std::min(p.items, sms * (HD == 64 ? 2 : 1));
+  const bool ext = p.softcap > 0.0f || p.alibi != nullptr || p.dropout_p > 0.0f;
+#define NX_FWD(HD_, EXT_)                                                                           \
+  do {                                                                                              \
+    static bool once = false;                                                                       \
+    if (!once) {                                                                                    \
+      if (set_smem(attn_fwd_kernel<HD_, EXT_>, FwdCfg<HD_>::kSmem)) return -2;                      \
+      once = true;                                                                                  \
+    }                                                                                               \
+    attn_fwd_kernel<HD_, EXT_><<<grid, kFwdThreads, FwdCfg<HD_>::kSmem, st>>>(tq, tk, tv, p);       \
+  } while (0)
   if (HD == 64) {
-    static bool once = false;
-    if (!once) {
-      if (set_smem(attn_fwd_kernel<64>, FwdCfg<64>::kSmem)) return -2;
-      once = true;
-    }
-    attn_fwd_kernel<64><<<grid, kFwdThreads, FwdCfg<64>::kSmem, st>>>(tq, tk, tv, p);
+    if (ext) NX_FWD(64, true);
+    else NX_FWD(64, false);
   } else {
-    static bool once = false;
-    if (!once) {
-      if (set_smem(attn_fwd_kernel<128>, FwdCfg<128>::kSmem)) return -2;
-      once = true;
-    }
-    attn_fwd_kernel<128><<<grid, kFwdThreads, FwdCfg<128>::kSmem, st>>>(tq, tk, tv, p);
+    if (ext) NX_FWD(128, true);
+    else NX_FWD(128, false);
   }
+#undef NX_FWD
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -1226,6 +1286,7 @@ extern "C" int nx_attention_bwd(const NxAttnArgs* a, nx_stream_t stream_) {
     return -1;
   if (a->lse == nullptr || a->dsum == nullptr) return -1;
   const int HD = a->head_dim;
+  const bool ext = a->softcap > 0.0f || a->alibi_slopes != nullptr || a->dropout_p > 0.0f;
   // part 0
   {
     const int64_t total = static_cast<int64_t>(a->batch) * a->heads * a->tq;
@@ -1255,20 +1316,21 @@ extern "C" int nx_attention_bwd(const NxAttnArgs* a, nx_stream_t stream_) {
     p.o2_head = a->dv.head_stride;
     p.o2_batch = a->dv.batch_stride;
     const unsigned grid = static_cast<unsigned>(((a->tk + 127) / 128) * a->kv_heads * a->batch);
+#define NX_BWD(KERN_, CFG_, HD_, EXT_)                                                              \
+  do {                                                                                              \
+    static bool once = false;                                                                       \
+    if (!once) {                                                                                    \
+      if (set_smem(KERN_<HD_, EXT_>, CFG_<HD_>::kSmem)) return -2;                                  \
+      once = true;                                                                                  \
+    }                                                                                               \
+    KERN_<HD_, EXT_><<<grid, kThreads, CFG_<HD_>::kSmem, st>>>(tq, tk, tv, tdo, p);                 \
+  } while (0)
     if (HD == 64) {
-      static bool once = false;
-      if (!once) {
-        if (set_smem(attn_bwd_dkdv_kernel<64>, DkvCfg<64>::kSmem)) return -2;
-        once = true;
-      }
-      attn_bwd_dkdv_kernel<64><<<grid, kThreads, DkvCfg<64>::kSmem, st>>>(tq, tk, tv, tdo, p);
+      if (ext) NX_BWD(attn_bwd_dkdv_kernel, DkvCfg, 64, true);
+      else NX_BWD(attn_bwd_dkdv_kernel, DkvCfg, 64, false);
     } else {
-      static bool once = false;
-      if (!once) {
-        if (set_smem(attn_bwd_dkdv_kernel<128>, DkvCfg<128>::kSmem)) return -2;
-        once = true;
-      }
-      attn_bwd_dkdv_kernel<128><<<grid, kThreads, DkvCfg<128>::kSmem, st>>>(tq, tk, tv, tdo, p);
+      if (ext) NX_BWD(attn_bwd_dkdv_kernel, DkvCfg, 128, true);
+      else NX_BWD(attn_bwd_dkdv_kernel, DkvCfg, 128, false);
     }
     if (cudaGetLastError() != cudaSuccess) return -2;
   }
@@ -1287,20 +1349,13 @@ extern "C" int nx_attention_bwd(const NxAttnArgs* a, nx_stream_t stream_) {
     p.nqb = (a->tq + 127) / 128;
     const unsigned grid = static_cast<unsigned>(p.nqb * a->heads * a->batch);
     if (HD == 64) {
-      static bool once = false;
-      if (!once) {
-        if (set_smem(attn_bwd_dq_kernel<64>, DqCfg<64>::kSmem)) return -2;
-        once = true;
-      }
-      attn_bwd_dq_kernel<64><<<grid, kThreads, DqCfg<64>::kSmem, st>>>(tq, tk, tv, tdo, p);
+      if (ext) NX_BWD(attn_bwd_dq_kernel, DqCfg, 64, true);
+      else NX_BWD(attn_bwd_dq_kernel, DqCfg, 64, false);
     } else {
-      static bool once = false;
-      if (!once) {
-        if (set_smem(attn_bwd_dq_kernel<128>, DqCfg<128>::kSmem)) return -2;
-        once = true;
-      }
-      attn_bwd_dq_kernel<128><<<grid, kThreads, DqCfg<128>::kSmem, st>>>(tq, tk, tv, tdo, p);
+      if (ext) NX_BWD(attn_bwd_dq_kernel, DqCfg, 128, true);
+      else NX_BWD(attn_bwd_dq_kernel, DqCfg, 128, false);
     }
+#undef NX_BWD
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

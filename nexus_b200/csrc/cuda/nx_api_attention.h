@@ -31,6 +31,11 @@ typedef struct NxAttnArgs {
   float softcap;                // > 0: scores become softcap * tanh(scale * s / softcap) (forward and backward)
   const float* alibi_slopes;    // [heads] or null: slope_h * (key position - query position), positions aligned
                                 // bottom-right like the causal mask, is added to the scaled score
+  // Attention dropout, 0 <= dropout_p < 1: P[b, h, q, k] is dropped (and the rest scaled by 1 / (1 - p)) when
+  // element ((b * heads + h) * tq + q) * tk + k of the Philox stream (seed, offset) is below p; the mask is
+  // regenerated in the backward kernels.  Out-of-range values are rejected.
+  float dropout_p;
+  uint64_t dropout_seed, dropout_offset;
 } NxAttnArgs;
 
 int nx_attention_fwd(const NxAttnArgs* args, nx_stream_t stream);

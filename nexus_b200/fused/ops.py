@@ -186,28 +186,30 @@ def fused_softmax(x: torch.Tensor, dim: int = -1) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------- attention
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal, window, scale, softcap=0.0, alibi_slopes=None):
+    def forward(ctx, q, k, v, causal, window, scale, softcap=0.0, alibi_slopes=None, dropout=(0.0, 0, 0)):
         from ..ops import _cuda as K
         o, lse = K.attention_fwd(q, k, v, causal=causal, window=window, scale=scale, softcap=softcap,
-                                 alibi_slopes=alibi_slopes)
+                                 alibi_slopes=alibi_slopes, dropout_p=dropout[0], dropout_seed=dropout[1],
+                                 dropout_offset=dropout[2])
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.cfg = (causal, window, scale, softcap, alibi_slopes)
+        ctx.cfg = (causal, window, scale, softcap, alibi_slopes, dropout)
         return o
 
     @staticmethod
     def backward(ctx, do):
         from ..ops import _cuda as K
         q, k, v, o, lse = ctx.saved_tensors
-        causal, window, scale, softcap, alibi_slopes = ctx.cfg
+        causal, window, scale, softcap, alibi_slopes, dropout = ctx.cfg
         dq, dk, dv = K.attention_bwd(q, k, v, o, lse, do.contiguous(), causal=causal, window=window, scale=scale,
-                                     softcap=softcap, alibi_slopes=alibi_slopes)
-        return dq, dk, dv, None, None, None, None, None
+                                     softcap=softcap, alibi_slopes=alibi_slopes, dropout_p=dropout[0],
+                                     dropout_seed=dropout[1], dropout_offset=dropout[2])
+        return dq, dk, dv, None, None, None, None, None, None
 
 
 def attention_reference(q, k, v, causal=True, window=0, scale=None, softcap=0.0, alibi_slopes=None,
                         dropout_p=0.0, dropout_seed=0, dropout_offset=0):
-    """Math attention in FP32 on [B, T, H, D] tensors: the oracle, and the path for features the
-    tensor-core kernel does not implement (attention dropout)."""
+    """Math attention in FP32 on [B, T, H, D] tensors: the oracle of the tensor-core kernels (which draw the same
+    Philox dropout stream), and the path for shapes and types they do not take."""
     B, Tq, H, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
     scale = D ** -0.5 if scale is None else scale
@@ -240,11 +242,11 @@ def attention(q, k, v, causal=True, window=0, scale=None, softcap=0.0, alibi_slo
               dropout_seed=0, dropout_offset=0):
     """Scaled-dot-product attention on [B, T, H, D] (GQA when k/v have fewer heads)."""
     D = q.shape[-1]
-    plain = dropout_p == 0.0   # soft-capping and ALiBi run inside the kernels
-    if plain and _use_kernels(q) and D in (64, 128) and q.dtype == torch.bfloat16 and \
+    if _use_kernels(q) and D in (64, 128) and q.dtype == torch.bfloat16 and \
             all(t.stride(-1) == 1 and t.stride(1) % 8 == 0 and t.stride(2) % 8 == 0 for t in (q, k, v)):
         slopes = None if alibi_slopes is None else alibi_slopes.detach().float().contiguous().to(q.device)
-        return _FlashAttention.apply(q, k, v, causal, window, scale, float(softcap), slopes)
+        return _FlashAttention.apply(q, k, v, causal, window, scale, float(softcap), slopes,
+                                     (float(dropout_p), int(dropout_seed), int(dropout_offset)))
     return attention_reference(q, k, v, causal, window, scale, softcap, alibi_slopes, dropout_p, dropout_seed,
                                dropout_offset)
 

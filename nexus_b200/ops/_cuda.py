@@ -58,6 +58,7 @@ class AttnArgs(C.Structure):
         ("head_dim", C.c_int32), ("causal", C.c_int32), ("window", C.c_int32), ("scale", C.c_float),
         ("merge_o", C.c_void_p), ("merge_lse", C.c_void_p),
         ("softcap", C.c_float), ("alibi_slopes", C.c_void_p),
+        ("dropout_p", C.c_float), ("dropout_seed", C.c_uint64), ("dropout_offset", C.c_uint64),
     ]
 
 
@@ -454,7 +455,7 @@ def _alibi_ptr(alibi_slopes, heads, device):
 
 
 def attention_fwd(q, k, v, *, causal=True, window=0, scale=None, out=None, merge_o=None, merge_lse=None,
-                  softcap=0.0, alibi_slopes=None):
+                  softcap=0.0, alibi_slopes=None, dropout_p=0.0, dropout_seed=0, dropout_offset=0):
     """q [B,Tq,H,D], k/v [B,Tk,Hkv,D] bf16 (strided views allowed).  Returns (o, lse[B,H,Tq]).
     ``merge_o`` (FP32 [B,Tq,H,D]) / ``merge_lse`` (FP32 [B,H,Tq]): running result of earlier key/value
     chunks; this chunk is merged into them in the kernel's epilogue (ring / chunked attention)."""
@@ -470,6 +471,7 @@ def attention_fwd(q, k, v, *, causal=True, window=0, scale=None, out=None, merge
     a.causal, a.window = int(causal), int(window)
     a.scale = scale if scale is not None else D ** -0.5
     a.softcap, a.alibi_slopes = float(softcap), _alibi_ptr(alibi_slopes, H, q.device)
+    a.dropout_p, a.dropout_seed, a.dropout_offset = float(dropout_p), int(dropout_seed), int(dropout_offset)
     if merge_o is not None:
         if not (merge_o.is_contiguous() and merge_lse.is_contiguous() and merge_o.dtype == torch.float32):
             raise ValueError("attention_fwd: merge buffers must be contiguous FP32")
@@ -479,7 +481,7 @@ def attention_fwd(q, k, v, *, causal=True, window=0, scale=None, out=None, merge
 
 
 def attention_bwd(q, k, v, o, lse, d_o, *, causal=True, window=0, scale=None, dq=None, dk=None, dv=None,
-                  softcap=0.0, alibi_slopes=None):
+                  softcap=0.0, alibi_slopes=None, dropout_p=0.0, dropout_seed=0, dropout_offset=0):
     B, Tq, H, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
     dq = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device) if dq is None else dq
@@ -495,5 +497,6 @@ def attention_bwd(q, k, v, o, lse, d_o, *, causal=True, window=0, scale=None, dq
     a.causal, a.window = int(causal), int(window)
     a.scale = scale if scale is not None else D ** -0.5
     a.softcap, a.alibi_slopes = float(softcap), _alibi_ptr(alibi_slopes, H, q.device)
+    a.dropout_p, a.dropout_seed, a.dropout_offset = float(dropout_p), int(dropout_seed), int(dropout_offset)
     _check(lib().nx_attention_bwd(C.byref(a), _stream()), "nx_attention_bwd")
     return dq, dk, dv

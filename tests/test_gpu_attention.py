@@ -122,3 +122,34 @@ def test_attention_varlen_on_kernels():
     assert (out.float() - ref).abs().max() < 2e-2
     for got, want in ((q.grad, qr.grad), (k.grad, kr.grad), (v.grad, vr.grad)):
         assert (got.float() - want).abs().max() <= 3e-2 * want.abs().max()
+
+
+@pytest.mark.parametrize("Tq,Tk,H,Hkv,D,causal", [(256, 256, 2, 2, 64, True), (130, 203, 4, 2, 64, False),
+                                                 (128, 256, 2, 1, 128, True)])
+def test_attention_dropout_in_kernels(Tq, Tk, H, Hkv, D, causal):
+    """Attention dropout inside the kernels draws the same Philox stream as the FP32 math path, so values and
+    gradients can be compared element by element; the kept fraction matches 1 - p."""
+    from nexus_b200.fused import ops as F
+    from nexus_b200.fused import philox
+    from nexus_b200.ops import _cuda as K
+    torch.manual_seed(4)
+    dev, p, seed, offset = "cuda", 0.2, 1234, 77
+    q = torch.randn(2, Tq, H, D, device=dev).bfloat16()
+    k = torch.randn(2, Tk, Hkv, D, device=dev).bfloat16()
+    v = torch.randn(2, Tk, Hkv, D, device=dev).bfloat16()
+    qr, kr, vr = [t.float().detach().requires_grad_(True) for t in (q, k, v)]
+    oref = F.attention_reference(qr, kr, vr, causal, 0, None, 0.0, None, p, seed, offset)
+    qg, kg, vg = [t.detach().requires_grad_(True) for t in (q, k, v)]
+    o = F.attention(qg, kg, vg, causal, 0, None, 0.0, None, p, seed, offset)
+    K.check_status()
+    assert (o.float() - oref).abs().max() < 3e-2
+    do = torch.randn_like(o)
+    o.backward(do)
+    K.check_status()
+    oref.backward(do.float())
+    for got, want in ((qg.grad, qr.grad), (kg.grad, kr.grad), (vg.grad, vr.grad)):
+        assert (got.float() - want).abs().max() <= 3e-2 * want.abs().max()
+    keep = philox.dropout_mask(2 * H * Tq * Tk, p, seed, offset).mean()
+    assert abs(keep - (1 - p)) < 5e-3
+    o0 = F.attention(q, k, v, causal, 0, None, 0.0, None, 0.0)
+    assert (o0.float() - o.float()).abs().max() > 1e-2          # dropout did change the result
