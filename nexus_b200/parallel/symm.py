@@ -380,6 +380,55 @@ class RingAttention:
         return dq_acc.to(q.dtype), dkv[0], dkv[1]
 
 
+class _VocabParallelCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets, ws, vocab_start, ignore_index):
+        rows, vl = logits.shape
+        lf = logits.float()
+        lmax = lf.max(dim=1).values
+        lse_local = torch.exp(lf - lmax[:, None]).sum(dim=1)
+        local_t = targets.long() - vocab_start
+        mine = (local_t >= 0) & (local_t < vl)
+        tlogit = torch.where(mine, lf.gather(1, local_t.clamp(0, vl - 1)[:, None])[:, 0], torch.zeros_like(lmax))
+        stats = torch.stack([lmax, lse_local, tlogit], dim=1).contiguous()
+        cache = ws.__dict__.setdefault("_vocab_ce", {})
+        if cache.get("rows") != rows:
+            cache["rows"] = rows
+            cache["table"] = ws.alloc(ws.n * rows * 3, torch.float32)
+        merged = torch.empty((rows, 3), dtype=torch.float32, device=logits.device)
+        ws.barrier()                         # the previous call's tables have been read by everyone
+        ws.epoch += 1
+        K._check(K.lib().nx_vocab_ce_exchange(K._p(stats), C.byref(cache["table"].table), C.byref(ws.flags.table),
+                                              C.c_int(ws.rank), C.c_int(ws.n), C.c_int(rows), C.c_int(ws.epoch),
+                                              K._p(merged), K._p(K.status_word(ws.device)), K._stream()),
+                 "nx_vocab_ce_exchange")
+        lse = merged[:, 0] + torch.log(merged[:, 1])
+        valid = targets != ignore_index
+        n_valid = valid.sum().clamp(min=1)
+        loss = ((lse - merged[:, 2]) * valid).sum() / n_valid
+        ctx.save_for_backward(logits, lse, local_t, mine & valid, valid, n_valid)
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        logits, lse, local_t, hit, valid, n_valid = ctx.saved_tensors
+        p = torch.exp(logits.float() - lse[:, None]) * valid[:, None]
+        p[hit.nonzero()[:, 0], local_t[hit]] -= 1.0
+        return (p * (g / n_valid)).to(logits.dtype), None, None, None, None
+
+
+def vocab_parallel_cross_entropy(ws: SymmetricWorkspace, logits: torch.Tensor, targets: torch.Tensor,
+                                 vocab_start: int, ignore_index: int = -100) -> torch.Tensor:
+    """Mean cross-entropy when the vocabulary dimension of the logits is split over the ranks.
+
+    ``logits`` [rows, V / n] holds columns [vocab_start, vocab_start + V / n) of the full logits; ``targets``
+    [rows] are global token ids.  Each rank reduces its columns to (max, sum-exp, target logit) per row; ONE kernel
+    stores the three numbers into every peer's table, waits on the flag barrier and merges them (max of maxima,
+    rescaled sum, sum of target logits), so the full logits never exist anywhere.  Differentiable in ``logits``.
+    Parity: src/dist/parallel_lm.cpp (vocab-parallel loss) of the reference."""
+    return _VocabParallelCE.apply(logits, targets, ws, int(vocab_start), int(ignore_index))
+
+
 def ulysses_attention(ws: SymmetricWorkspace, q, k, v, causal: bool = True):
     """DeepSpeed-Ulysses attention over symmetric memory: heads <-> sequence all-to-all by peer stores,
     local causal flash attention over the full sequence on H/n heads, all-to-all back.

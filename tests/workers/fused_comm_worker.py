@@ -12,7 +12,8 @@ from nexus_b200.models.gpt import AdamWConfig, GptModel  # noqa: E402
 from nexus_b200.ops import _cuda as K  # noqa: E402
 from nexus_b200.parallel.process_group import init_process_group  # noqa: E402
 from nexus_b200.parallel.symm import (FusedShardedOptimizer, RingAttention, SymmetricWorkspace,  # noqa: E402
-                                      fused_all_reduce, gemm_dist, moe_combine, moe_dispatch, ulysses_attention)
+                                      fused_all_reduce, gemm_dist, moe_combine, moe_dispatch, ulysses_attention,
+                                      vocab_parallel_cross_entropy)
 
 
 def main():
@@ -118,6 +119,35 @@ def main():
     torch.cuda.synchronize()
     check("ulysses attention", (o.float() - ref_o[:, sl].float()).abs().max().item() < 3e-2)
     K.check_status()
+
+    # ---- vocabulary-parallel cross-entropy: loss and logit gradients vs the full-vocabulary loss
+    rows_ce, V = 512, 1024 * world
+    gen = torch.Generator(device=dev).manual_seed(91)
+    full = torch.randn(rows_ce, V, device=dev, generator=gen) * 3
+    tg = torch.randint(0, V, (rows_ce,), device=dev, generator=gen)
+    pg.broadcast_tensor(full, 0)
+    pg.broadcast_tensor(tg, 0)
+    tg[::7] = -100
+    ref_full = full.clone().requires_grad_(True)
+    ref_loss = torch.nn.functional.cross_entropy(ref_full, tg, ignore_index=-100)
+    ref_loss.backward()
+    vs = rank * (V // world)
+    mine = full[:, vs: vs + V // world].clone().requires_grad_(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for it in range(4):
+        if it == 3:
+            e0.record()
+        loss = vocab_parallel_cross_entropy(ws, mine, tg, vs)
+        if it == 3:
+            e1.record()
+    loss.backward()
+    torch.cuda.synchronize(); K.check_status()
+    check("vocab-parallel CE loss", abs(loss.item() - ref_loss.item()) < 1e-4)
+    check("vocab-parallel CE gradient",
+          (mine.grad - ref_full.grad[:, vs: vs + V // world]).abs().max().item() < 1e-6)
+    if rank == 0:
+        print(f"INFO vocab-parallel CE forward incl. exchange: {e0.elapsed_time(e1) * 1e3:.1f} us "
+              f"({rows_ce} rows x {V // world} local columns)", flush=True)
 
     # ---- distributed GEMM: all-gather fused into the GEMM (A sharded / B sharded) and GEMM -> reduce-scatter
     torch.manual_seed(5)
