@@ -112,3 +112,21 @@ def test_docs_site_builds(tmp_path):
     body, title = site.render_markdown("# T\n\ntext with `a*b*c` and *em* and [l](x.md#frag)\n\n```\n<raw>\n```\n\n1. one\n2. two\n")
     assert title == "T" and "<code>a*b*c</code>" in body and "<em>em</em>" in body
     assert 'href="x.html#frag"' in body and "&lt;raw&gt;" in body and "<ol><li>one</li><li>two</li></ol>" in body
+
+
+@pytest.mark.parametrize("script,args", [("demo.py", []), ("dl_vision_classifier.py", []),
+                                         ("hybrid_cluster_benchmark.py", []), ("lm_baseline.py", ["--json", "{tmp}/r.json"])])
+def test_examples_run_on_cpu(tmp_path, script, args):
+    """The example programs exit 0 on a machine without a GPU (each checks its own result)."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, os.path.join(root, "examples", script)] + [a.replace("{tmp}", str(tmp_path)) for a in args]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="", PYTHONPATH=root)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    if script == "lm_baseline.py":
+        import json
+        rep = json.load(open(tmp_path / "r.json"))
+        assert rep["params_counted"] == rep["params_formula"] and rep["mfu"] is None and rep["tokens_per_second"] > 0
