@@ -30,6 +30,7 @@ def main():
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, w.vocab, (a.prompt_len,), generator=g).tolist() for _ in range(a.requests)]
     sp = SamplingParams(temperature=0.8, top_k=50, top_p=0.95, seed=7)
+    generate(eng, prompts[0], 8, sp)                # warm-up: scratch buffers and the decode graph of batch size 1
     t0 = time.perf_counter()
     single = generate(eng, prompts[0], a.max_new, sp)
     t_single = time.perf_counter() - t0

@@ -926,14 +926,22 @@ int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const DevParams
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
+// Sums the K slices of a split GEMM (fixed order) and applies what the GEMM's own epilogue would have: bias,
+// activation, and the add into the existing output.
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, void* out, int out_dtype, int64_t ldo, int m,
-                                     int n, int split_k, int accumulate) {
+                                     int n, int split_k, int accumulate, const void* bias, int bias_dtype, int act) {
   const int64_t total = static_cast<int64_t>(m) * n;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     float s = 0.0f;
     for (int k = 0; k < split_k; ++k) s += ws[static_cast<int64_t>(k) * total + i];
     const int r = static_cast<int>(i / n), c = static_cast<int>(i % n);
+    if (bias != nullptr)
+      s += bias_dtype == NX_F32 ? reinterpret_cast<const float*>(bias)[c]
+                                : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[c]);
+    if (act == NX_ACT_GELU) s = gelu_tanh_f(s);
+    else if (act == NX_ACT_RELU) s = fmaxf(s, 0.0f);
+    else if (act == NX_ACT_SILU) s = silu_f(s);
     const int64_t off = static_cast<int64_t>(r) * ldo + c;
     if (out_dtype == NX_F32) {
       float* o = reinterpret_cast<float*>(out);
@@ -963,11 +971,19 @@ extern "C" size_t nx_gemm_workspace_bytes(int m, int n, int split_k) {
 
 extern "C" int nx_splitk_reduce(const float* workspace, void* out, int out_dtype, int64_t ldo, int m, int n,
                                 int split_k, int accumulate, nx_stream_t stream) {
+  return nx_splitk_reduce_epilogue(workspace, out, out_dtype, ldo, m, n, split_k, accumulate, nullptr, NX_F32, NX_ACT_NONE,
+                                   stream);
+}
+
+extern "C" int nx_splitk_reduce_epilogue(const float* workspace, void* out, int out_dtype, int64_t ldo, int m, int n,
+                                         int split_k, int accumulate, const void* bias, int bias_dtype, int act,
+                                         nx_stream_t stream) {
   const int64_t total = static_cast<int64_t>(m) * n;
   if (total == 0) return 0;
+  if (act != NX_ACT_NONE && act != NX_ACT_GELU && act != NX_ACT_RELU && act != NX_ACT_SILU) return -1;
   int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 8));
   splitk_reduce_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(workspace, out, out_dtype, ldo, m, n,
-                                                                              split_k, accumulate);
+                                                                              split_k, accumulate, bias, bias_dtype, act);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

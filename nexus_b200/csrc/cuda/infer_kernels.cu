@@ -296,15 +296,17 @@ __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, int64_t ld, int vocab, const NxSampleParams* __restrict__ params,
               const int32_t* __restrict__ counts_all, const int32_t* __restrict__ counts_out,
               const int32_t* __restrict__ count_row, const uint64_t* __restrict__ offsets, float* __restrict__ work,
-              int32_t* __restrict__ out) {
+              int32_t* __restrict__ out, int row_in_smem) {
+  extern __shared__ float s_row[];  // the row's working values when they fit (vocab floats): every later pass reads them
   __shared__ float s_f[32];
+  __shared__ float s_g[32];
   __shared__ int s_i[32];
   __shared__ float s_bcast;
   __shared__ int s_pick;
   const int row = blockIdx.x;
   const NxSampleParams p = params[row];
   const float* lr = logits + row * ld;
-  float* wk = work + static_cast<int64_t>(row) * vocab;
+  float* wk = row_in_smem ? s_row : work + static_cast<int64_t>(row) * vocab;
   const int64_t crow = count_row ? count_row[row] : row;
   const int32_t* cnt_all = counts_all ? counts_all + crow * vocab : nullptr;  // prompt + generated tokens
   const int32_t* cnt_out = counts_out ? counts_out + crow * vocab : nullptr;  // generated tokens only
@@ -367,27 +369,30 @@ sample_kernel(const float* __restrict__ logits, int64_t ld, int vocab, const NxS
   const float total = block_sum<float>(se, s_f);
   // threshold on e: keep {e >= thr}.  min-p: thr >= min_p (the top token has e = 1).
   float thr = p.min_p > 0.0f ? p.min_p : 0.0f;
-  if (p.top_k > 0 && p.top_k < vocab) {  // largest thr such that count(e >= thr) >= top_k  (bisection on e)
-    float lo = 0.0f, hi = 1.0f;
+  const bool want_k = p.top_k > 0 && p.top_k < vocab;       // largest thr such that count(e >= thr) >= top_k
+  const bool want_p = p.top_p > 0.0f && p.top_p < 1.0f;     // largest thr such that mass(e >= thr) >= top_p * total
+  if (want_k || want_p) {
+    // the two bisections on e are independent: they share each pass over the row
+    float lo_k = 0.0f, hi_k = 1.0f, lo_p = 0.0f, hi_p = 1.0f;
     for (int it = 0; it < 30; ++it) {
-      const float mid = 0.5f * (lo + hi);
-      float n = 0.0f;
-      for (int c = threadIdx.x; c < vocab; c += blockDim.x) n += wk[c] >= mid ? 1.0f : 0.0f;
-      n = block_sum<float>(n, s_f);
-      if (n >= static_cast<float>(p.top_k)) lo = mid; else hi = mid;
+      const float mid_k = 0.5f * (lo_k + hi_k), mid_p = 0.5f * (lo_p + hi_p);
+      float n = 0.0f, ms = 0.0f;
+      for (int c = threadIdx.x; c < vocab; c += blockDim.x) {
+        const float e = wk[c];
+        n += e >= mid_k ? 1.0f : 0.0f;
+        ms += e >= mid_p ? e : 0.0f;
+      }
+      if (want_k) {
+        n = block_sum<float>(n, s_f);
+        if (n >= static_cast<float>(p.top_k)) lo_k = mid_k; else hi_k = mid_k;
+      }
+      if (want_p) {
+        ms = block_sum<float>(ms, s_g);
+        if (ms >= p.top_p * total) lo_p = mid_p; else hi_p = mid_p;
+      }
     }
-    thr = fmaxf(thr, lo);
-  }
-  if (p.top_p > 0.0f && p.top_p < 1.0f) {  // largest thr such that mass(e >= thr) >= top_p * total
-    float lo = 0.0f, hi = 1.0f;
-    for (int it = 0; it < 30; ++it) {
-      const float mid = 0.5f * (lo + hi);
-      float ms = 0.0f;
-      for (int c = threadIdx.x; c < vocab; c += blockDim.x) ms += wk[c] >= mid ? wk[c] : 0.0f;
-      ms = block_sum<float>(ms, s_f);
-      if (ms >= p.top_p * total) lo = mid; else hi = mid;
-    }
-    thr = fmaxf(thr, lo);
+    if (want_k) thr = fmaxf(thr, lo_k);
+    if (want_p) thr = fmaxf(thr, lo_p);
   }
   float kept = 0.0f;
   for (int c = threadIdx.x; c < vocab; c += blockDim.x) kept += wk[c] >= thr ? wk[c] : 0.0f;
@@ -677,8 +682,17 @@ extern "C" int nx_sample(const float* logits, int64_t ld, int vocab, const NxSam
                          const uint64_t* offsets, float* work, int32_t* out, int rows, nx_stream_t stream) {
   if (rows <= 0) return 0;
   if (work == nullptr) return -1;
-  sample_kernel<<<rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(logits, ld, vocab, params, counts_all, counts_out,
-                                                                      count_row, offsets, work, out);
+  // rows of up to ~55 k entries live in shared memory for the threshold searches
+  const size_t row_bytes = static_cast<size_t>(vocab) * sizeof(float);
+  const bool in_smem = row_bytes <= 220 * 1024;
+  static bool attr_set = false;
+  if (in_smem && !attr_set) {
+    if (cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess)
+      return -2;
+    attr_set = true;
+  }
+  sample_kernel<<<rows, 1024, in_smem ? row_bytes : 0, static_cast<cudaStream_t>(stream)>>>(
+      logits, ld, vocab, params, counts_all, counts_out, count_row, offsets, work, out, in_smem ? 1 : 0);
   return launch_status();
 }
 

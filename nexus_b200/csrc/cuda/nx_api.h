@@ -55,6 +55,10 @@ int nx_gemm(const NxGemmArgs* args, nx_stream_t stream);
 // Sum split-K partials in slice order and apply "out (+)= v" with the dtype of `out`.
 int nx_splitk_reduce(const float* workspace, void* out, int out_dtype, int64_t ldo, int m, int n, int split_k,
                      int accumulate, nx_stream_t stream);
+// The same, with the epilogue the split GEMM could not apply itself: out = act(sum of slices + bias) (+ out when
+// `accumulate`).  act: NX_ACT_NONE / GELU / RELU / SILU.
+int nx_splitk_reduce_epilogue(const float* workspace, void* out, int out_dtype, int64_t ldo, int m, int n, int split_k,
+                              int accumulate, const void* bias, int bias_dtype, int act, nx_stream_t stream);
 int nx_sm_count(void);
 size_t nx_gemm_workspace_bytes(int m, int n, int split_k);
 

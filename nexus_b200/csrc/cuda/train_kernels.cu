@@ -226,11 +226,9 @@ __global__ void __launch_bounds__(512) ce_row_vec_kernel(LT* __restrict__ logits
     return;
   }
   const int full = vocab / VN;  // vectors entirely inside the vocabulary
+  const int nuse = (vocab + VN - 1) / VN;  // vectors that hold at least one vocabulary entry
   float mx = -INFINITY, se = 0.0f, sl = 0.0f;
-  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
-    if (i * VN >= vocab) break;
-    float v[VN];
-    RowVec<LT>::load(lr + i * VN, v);
+  auto absorb = [&](int i, float (&v)[VN]) {
     float vm = -INFINITY;
 #pragma unroll
     for (int j = 0; j < VN; ++j) {
@@ -245,6 +243,27 @@ __global__ void __launch_bounds__(512) ce_row_vec_kernel(LT* __restrict__ logits
     for (int j = 0; j < VN; ++j) {
       se += exp2f((v[j] - mx) * kL2e);
       sl += (v[j] == -INFINITY) ? 0.0f : v[j];
+    }
+  };
+  {
+    // four independent loads in flight per thread: one row is read once from HBM and latency is what limits it
+    const int step = blockDim.x;
+    int i = threadIdx.x;
+    for (; i + 3 * step < nuse; i += 4 * step) {
+      float v0[VN], v1[VN], v2[VN], v3[VN];
+      RowVec<LT>::load(lr + i * VN, v0);
+      RowVec<LT>::load(lr + (i + step) * VN, v1);
+      RowVec<LT>::load(lr + (i + 2 * step) * VN, v2);
+      RowVec<LT>::load(lr + (i + 3 * step) * VN, v3);
+      absorb(i, v0);
+      absorb(i + step, v1);
+      absorb(i + 2 * step, v2);
+      absorb(i + 3 * step, v3);
+    }
+    for (; i < nuse; i += step) {
+      float v[VN];
+      RowVec<LT>::load(lr + i * VN, v);
+      absorb(i, v);
     }
   }
   const float bmx = block_max(mx, s_scratch);
@@ -262,22 +281,40 @@ __global__ void __launch_bounds__(512) ce_row_vec_kernel(LT* __restrict__ logits
   const float sv = smoothing / vocab * k;
   const float onehot = (1.0f - smoothing) * k;
   const float lse2 = lse * kL2e;
-  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
-    float v[VN];
-    if (i * VN < vocab) {
-      RowVec<LT>::load(lr + i * VN, v);
+  auto grad_store = [&](int i, float (&v)[VN]) {
 #pragma unroll
-      for (int j = 0; j < VN; ++j) {
-        const int c = i * VN + j;
-        float g = exp2f(fmaf(v[j], kL2e, -lse2)) * pz - sv;
-        if (c == tg) g -= onehot;
-        v[j] = (c < vocab) ? g : 0.0f;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < VN; ++j) v[j] = 0.0f;
+    for (int j = 0; j < VN; ++j) {
+      const int c = i * VN + j;
+      float g = exp2f(fmaf(v[j], kL2e, -lse2)) * pz - sv;
+      if (c == tg) g -= onehot;
+      v[j] = (c < vocab) ? g : 0.0f;
     }
     RowVec<LT>::store(lr + i * VN, v);
+  };
+  {
+    // the row is rewritten in place: the loads of a group are issued before its stores
+    const int step = blockDim.x;
+    int i = threadIdx.x;
+    for (; i + 3 * step < nuse; i += 4 * step) {
+      float v0[VN], v1[VN], v2[VN], v3[VN];
+      RowVec<LT>::load(lr + i * VN, v0);
+      RowVec<LT>::load(lr + (i + step) * VN, v1);
+      RowVec<LT>::load(lr + (i + 2 * step) * VN, v2);
+      RowVec<LT>::load(lr + (i + 3 * step) * VN, v3);
+      grad_store(i, v0);
+      grad_store(i + step, v1);
+      grad_store(i + 2 * step, v2);
+      grad_store(i + 3 * step, v3);
+    }
+    for (; i < nuse; i += step) {
+      float v[VN];
+      RowVec<LT>::load(lr + i * VN, v);
+      grad_store(i, v);
+    }
+    float z[VN];
+#pragma unroll
+    for (int j = 0; j < VN; ++j) z[j] = 0.0f;
+    for (i = nuse + threadIdx.x; i < nvec; i += step) RowVec<LT>::store(lr + i * VN, z);  // padding columns
   }
 }
 

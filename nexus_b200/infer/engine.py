@@ -254,6 +254,10 @@ class Engine:
         self.block_table = torch.zeros((cfg.max_seqs, self.max_blocks), dtype=torch.int32, device=self.dev)
         self.counts_all = torch.zeros((cfg.max_seqs, self.V), dtype=torch.int32, device=self.dev)
         self.counts_out = torch.zeros((cfg.max_seqs, self.V), dtype=torch.int32, device=self.dev)
+        self._ones = torch.ones(cfg.max_tokens, dtype=torch.int32, device=self.dev)
+        self._stage_bufs: Dict[int, torch.Tensor] = {}
+        self._stage_evt: dict = {}
+        self._sample_cache: dict = {}
         self._logits: Optional[torch.Tensor] = None
         self._logit_seq: List[int] = []
         self._stats = StepStats()
@@ -507,7 +511,11 @@ class Engine:
         w = lin.dense()
         if n <= self._skinny:
             return I.skinny_gemm(x, w, lin.bias, act=act, residual=residual, out=residual, out_dtype=od)
-        return K.gemm(x, w, bias=lin.bias, act=act, residual=residual, out=residual, out_dtype=od)
+        # a few rows give the tensor-core GEMM one row of tiles: slices along K keep every SM busy (fixed summation
+        # order, so a row's result does not depend on what else is in the batch)
+        few = n < 256
+        return K.gemm(x, w, bias=lin.bias, act=act, residual=residual, out=residual, out_dtype=od,
+                      split_k=0 if few else 1, block_n=128 if few else 0, deterministic=True)
 
     def _norm(self, x, w, b):
         if not self.fast:
@@ -581,25 +589,37 @@ class Engine:
         use_graph = self.fast and cfg.cuda_graphs and decode_only and nl == self.L and self.tp == 1
         R = len(logit_rows)
         bucket = 1 << (N - 1).bit_length() if use_graph else N
-        ints = torch.tensor([tok + [0] * (bucket - N), pos + [0] * (bucket - N), slot + [-1] * (bucket - N),
-                             rseq + [0] * (bucket - N), [p + 1 for p in pos] + [0] * (bucket - N),
-                             logit_rows + [0] * (bucket - R)], dtype=torch.int32)
-        if self.dev.type == "cuda":
-            ints = ints.pin_memory()
+        # one staging buffer in pinned memory, reused every step, and ONE host-to-device copy for all index arrays
+        ints = self._stage(bucket)
+        h = ints.numpy()
+        h[:, N:] = 0
+        h[2, N:] = -1
+        h[0, :N], h[1, :N], h[2, :N], h[3, :N] = tok, pos, slot, rseq
+        h[4, :N] = h[1, :N] + 1
+        h[5, :R] = logit_rows
+        h[5, R:] = 0
         if use_graph:
             logits = self._decode_graph(bucket, ints)[:R]
+            dv = self._static[bucket]["ints"]
             stats.graph = True
         else:
             dv = ints.to(self.dev, non_blocking=True)
             logits = self._body(dv[0], dv[1], dv[2], dv[3], dv[4], dv[5][:R], runs, nl)
-        # token counters (repetition: every token; frequency / presence: output tokens only)
-        tk = torch.tensor(tok, dtype=torch.long)
-        rs = torch.tensor(rseq, dtype=torch.long)
-        flat = (rs * self.V + tk).to(self.dev)
-        self.counts_all.view(-1).index_add_(0, flat, torch.ones_like(flat, dtype=torch.int32))
-        if out_rows:
-            fo = flat[torch.tensor(out_rows, dtype=torch.long, device=self.dev)]
-            self.counts_out.view(-1).index_add_(0, fo, torch.ones_like(fo, dtype=torch.int32))
+        if self.dev.type == "cuda":
+            ev = self._stage_evt.get(bucket)
+            if ev is None:
+                ev = self._stage_evt[bucket] = torch.cuda.Event()
+            ev.record()
+        # token counters (repetition: every token; frequency / presence: output tokens only), from the index arrays
+        # that are on the device already
+        flat = dv[3, :N].long() * self.V + dv[0, :N].long()
+        ones = self._ones[:N]
+        self.counts_all.view(-1).index_add_(0, flat, ones)
+        if len(out_rows) == N:
+            self.counts_out.view(-1).index_add_(0, flat, ones)
+        elif out_rows:
+            fo = flat[torch.tensor(out_rows, dtype=torch.long).to(self.dev, non_blocking=True)]
+            self.counts_out.view(-1).index_add_(0, fo, self._ones[: len(out_rows)])
         self._logits = logits
         stats.ms = (time.perf_counter() - t0) * 1e3
         self._stats = stats
@@ -707,6 +727,22 @@ class Engine:
             s = torch.einsum("hd,nhd->hn", q[r].float(), kk) * scale
             att[r] = torch.einsum("hn,nhd->hd", s.softmax(-1), vv).to(att.dtype)
 
+    def _stage(self, width: int) -> torch.Tensor:
+        """Host staging tensor [6, width] int32 (pinned on a GPU), one per width, reused by every step."""
+        t = self._stage_bufs.get(width)
+        ev = self._stage_evt.get(width)
+        if ev is not None:
+            ev.synchronize()          # the copy that last read this buffer has run
+        if t is None:
+            t = torch.zeros((6, width), dtype=torch.int32)
+            if self.dev.type == "cuda":
+                t = t.pin_memory()
+            if len(self._stage_bufs) > 64:
+                self._stage_bufs.clear()
+                self._stage_evt.clear()
+            self._stage_bufs[width] = t
+        return t
+
     # ----------------------------------------------------------------------------- decode graphs
     def _decode_graph(self, bucket: int, ints: torch.Tensor) -> torch.Tensor:
         st = self._static.get(bucket)
@@ -755,13 +791,29 @@ class Engine:
         offs = [int(offsets)] * R if isinstance(offsets, int) else [int(o) for o in offsets]
         if self.fast:
             from ..ops import _infer as I
-            pd = I.pack_sample_params(params).to(self.dev, non_blocking=True)
-            od = torch.tensor(offs, dtype=torch.int64).view(torch.uint8).to(self.dev).view(torch.int64)
-            rows = torch.tensor(seqs, dtype=torch.int32).to(self.dev)
-            need_counts = any(p.repetition_penalty != 1.0 or p.frequency_penalty or p.presence_penalty for p in params)
+            # the packed parameter block of an unchanged set of requests stays on the device
+            key = tuple((id(p), p.temperature, p.top_k, p.top_p, p.min_p, p.repetition_penalty, p.frequency_penalty,
+                         p.presence_penalty, p.seed) for p in params)
+            cached = self._sample_cache.get("params")
+            if cached is None or cached[0] != key:
+                need = any(p.repetition_penalty != 1.0 or p.frequency_penalty or p.presence_penalty for p in params)
+                cached = (key, I.pack_sample_params(params).to(self.dev, non_blocking=True), need)
+                self._sample_cache["params"] = cached
+            _, pd, need_counts = cached
+            # offsets (uint64) and count rows (int32) travel in one pinned staging tensor
+            st = self._sample_cache.get(R)
+            if st is None:
+                st = torch.zeros(3 * R, dtype=torch.int32)
+                st = st.pin_memory() if self.dev.type == "cuda" else st
+                self._sample_cache[R] = st
+            hn = st.numpy()
+            hn[: 2 * R].view("int64")[:] = offs
+            hn[2 * R:] = seqs
+            dvs = st.to(self.dev, non_blocking=True)
+            od, rows = dvs[: 2 * R].view(torch.int64), dvs[2 * R:]
             out = I.sample(self._logits, pd, od, vocab=self.V, counts_all=self.counts_all if need_counts else None,
                            counts_out=self.counts_out if need_counts else None, count_row=rows)
-            return [int(t) for t in out.cpu()]
+            return out.cpu().tolist()
         from .sampling import sample_reference
         return [sample_reference(self._logits[r, : self.V].float().cpu(), params[r], self.counts_all[seqs[r]].cpu(),
                                  self.counts_out[seqs[r]].cpu(), offs[r]) for r in range(R)]

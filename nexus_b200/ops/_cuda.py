@@ -161,7 +161,11 @@ def auto_split_k(m: int, n: int, k: int, clusters: int = 74) -> int:
     key = (m, n, k)
     s = _split_cache.get(key)
     if s is None:
-        tiles = -(-m // 256) * -(-n // 256)
+        if m >= 256 and n >= 256:
+            tiles = -(-m // 256) * -(-n // 256)
+        else:                     # single-CTA tiles of 128 x (256 | 128) on every SM
+            tiles = -(-m // 128) * -(-n // (256 if n >= 256 else 128))
+            clusters = 2 * clusters
         kb = -(-k // 64)
         best, s = None, 1
         if tiles < 2 * clusters:
@@ -243,6 +247,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     L = lib()
     if split_k == 0:
         split_k = auto_split_k(m, n, k) if (not batched and not fp8) else 1
+    if split_k > 1 and (aux_in is not None or aux_out is not None or scale_a is not None or scale_b is not None or
+                        amax_out is not None or (residual is not None and residual.data_ptr() != out.data_ptr()) or
+                        act in ("dgelu",)):
+        split_k = 1      # epilogues that only the GEMM itself can apply
     if split_k > 1 and not batched:
         kb_total = (k + 63) // 64
         split_k = min(split_k, kb_total)
@@ -254,13 +262,18 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         g.accumulate = 2
         _check(L.nx_gemm(C.byref(g), _stream()), "nx_gemm")
     elif split_k > 1 and not batched:
+        # slices go to an FP32 workspace; the reduction pass sums them in a fixed order and applies bias / activation /
+        # the add into `out` (a residual that IS `out` counts as accumulate)
         ws = scratch(split_k * m * n * 4, "gemm_splitk", a.device)
         g.workspace = ws.data_ptr()
         g.split_k = split_k
+        acc = bool(accumulate) or (residual is not None)
+        g.bias, g.residual, g.act, g.accumulate = None, None, ACT["none"], 0
         _check(L.nx_gemm(C.byref(g), _stream()), "nx_gemm")
-        _check(L.nx_splitk_reduce(C.c_void_p(ws.data_ptr()), _p(out), C.c_int(_DT[out.dtype]),
-                                  C.c_int64(out.stride(-2)), C.c_int(m), C.c_int(n), C.c_int(split_k),
-                                  C.c_int(int(accumulate)), _stream()), "nx_splitk_reduce")
+        _check(L.nx_splitk_reduce_epilogue(C.c_void_p(ws.data_ptr()), _p(out), C.c_int(_DT[out.dtype]),
+                                           C.c_int64(out.stride(-2)), C.c_int(m), C.c_int(n), C.c_int(split_k),
+                                           C.c_int(int(acc)), _p(bias), C.c_int(_DT[bias.dtype] if bias is not None else F32),
+                                           C.c_int(ACT[act]), _stream()), "nx_splitk_reduce")
     else:
         g.split_k = 1
         _check(L.nx_gemm(C.byref(g), _stream()), "nx_gemm")

@@ -126,3 +126,27 @@ def test_gemm_rejects_unaligned_pitch():
     b = torch.randn(64, 36, device="cuda").bfloat16()
     with pytest.raises(RuntimeError):
         K.gemm(a, b)
+
+
+def test_gemm_split_k_with_epilogue_in_the_reduction():
+    """Few rows, many K slices: bias + GELU (BF16 out) and bias + in-place FP32 residual come out of the reduction
+    pass exactly as from the unsplit GEMM's epilogue, run to run bit-identical."""
+    K = _K()
+    torch.manual_seed(9)
+    M, N, Kd = 64, 768, 3072
+    A, B, a, b = _operands(M, N, Kd, False, False)
+    bias = torch.randn(N, device="cuda")
+    ref = A.float() @ B.float().t() + bias
+    o1 = K.gemm(a, b, bias=bias, act="gelu", split_k=0, block_n=128, deterministic=True)
+    o2 = K.gemm(a, b, bias=bias, act="gelu", split_k=8, block_n=128, deterministic=True)
+    K.check_status()
+    want = torch.nn.functional.gelu(ref, approximate="tanh")
+    assert (o1.float() - want).abs().max() <= 1.5e-2 * want.abs().max()
+    assert (o2.float() - want).abs().max() <= 1.5e-2 * want.abs().max()
+    assert torch.equal(o1, K.gemm(a, b, bias=bias, act="gelu", split_k=0, block_n=128, deterministic=True))
+    res = torch.randn(M, N, device="cuda")
+    want = res + ref
+    out = res.clone()
+    K.gemm(a, b, bias=bias, residual=out, out=out, out_dtype=torch.float32, split_k=0, block_n=128, deterministic=True)
+    K.check_status()
+    assert (out - want).abs().max() <= 2e-3 * want.abs().max()
