@@ -1,6 +1,6 @@
 // Flash-style attention for sm_100a on tcgen05 tensor cores: forward, and a two-kernel
-// deterministic backward (dK/dV kernel with the kv block resident, dQ kernel with the q block
-// resident; no atomics, every gradient tile accumulates in TMEM).
+// deterministic backward (dQ kernel with the q block resident, which also forms rowsum(dO * O), then the
+// dK/dV kernel with the kv block resident; no atomics, every gradient tile accumulates in TMEM).
 //
 // Shared design:
 //   * Q/K/V/dO tiles arrive by TMA (4-D maps over [B, T, H, D] with arbitrary strides, so packed
@@ -44,6 +44,12 @@ struct AttnDev {
   float* merge_lse;    // fwd: FP32 [B,H,Tq] running log-sum-exp (in/out)
   float softcap;       // > 0: scores pass through softcap * tanh(scale * s / softcap)
   const float* alibi;  // [H] slopes or null: slope_h * (key position - query position) is added to the scaled score
+  // dq kernel: forward output and its gradient as plain row views; the kernel forms dsum = rowsum(dO * O) itself
+  // and leaves it in `dsum_out` for the dK/dV kernel that follows
+  const __nv_bfloat16* o_in;
+  const __nv_bfloat16* do_in;
+  int64_t oi_row, oi_head, oi_batch, di_row, di_head, di_batch;
+  float* dsum_out;
   float dropout_p;     // > 0: probabilities are dropped with this rate (the row sums are not)
   uint64_t drop_seed, drop_offset;  // Philox stream; element ((b*H + h)*Tq + q)*Tk + k of it decides P[b,h,q,k]
 };
@@ -583,47 +589,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // ================================================================================================
-// backward, part 0: dsum[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]
-// ================================================================================================
-__global__ void attn_bwd_dsum_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
-                                     float* __restrict__ dsum, int B, int T, int H, int HD, int64_t o_row,
-                                     int64_t o_head, int64_t o_batch, int64_t do_row, int64_t do_head,
-                                     int64_t do_batch) {
-  // HD/8 adjacent lanes share one row: 16-byte loads, shuffle reduction inside the lane group
-  const int lpr = HD >> 3;
-  const int64_t total = static_cast<int64_t>(B) * H * T;
-  const int64_t gthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  const int64_t rows_per_pass = gthreads / lpr;
-  const int sub = threadIdx.x % lpr;
-  for (int64_t base = 0; base < total; base += rows_per_pass) {  // trip count is grid-uniform (shuffles below)
-    const int64_t i = base + (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) / lpr;
-    float acc = 0.0f;
-    if (i < total) {
-      const int h = static_cast<int>(i % H);
-      const int t = static_cast<int>((i / H) % T);
-      const int b = static_cast<int>(i / (static_cast<int64_t>(T) * H));
-      const uint4 a = *reinterpret_cast<const uint4*>(o + b * o_batch + t * o_row + h * o_head + sub * 8);
-      const uint4 g = *reinterpret_cast<const uint4*>(d_o + b * do_batch + t * do_row + h * do_head + sub * 8);
-      const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float a0, a1, g0, g1;
-        unpack_bf16x2(aw[j], a0, a1);
-        unpack_bf16x2(gw[j], g0, g1);
-        acc += a0 * g0 + a1 * g1;
-      }
-    }
-    for (int sft = lpr >> 1; sft > 0; sft >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sft);
-    if (sub == 0 && i < total) {
-      const int h = static_cast<int>(i % H);
-      const int t = static_cast<int>((i / H) % T);
-      const int b = static_cast<int>(i / (static_cast<int64_t>(T) * H));
-      dsum[(static_cast<int64_t>(b) * H + h) * T + t] = acc;
-    }
-  }
-}
-
-// ================================================================================================
 // backward, part 1: dK / dV.  One CTA per (kv block of 128, kv head, batch); loops over the q heads
 // of the group and over q chunks of 64 rows.  TMEM: S^T [128 kv][64 q], dP^T [128][64], dV [128][HD],
 // dK [128][HD].  Thread r owns kv row r.
@@ -1065,7 +1030,31 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     float lse_n = q < p.Tq ? p.lse[sidx] : INFINITY;
     if (lse_n == -INFINITY) lse_n = INFINITY;  // row that saw no key: probabilities are zero
     const float lse2 = lse_n * kLog2e;
-    const float dsum = q < p.Tq ? p.dsum[sidx] : 0.0f;
+    // dsum = rowsum(dO * O) of this thread's row, straight from global memory (the loads overlap the first tiles'
+    // TMA traffic); published for the dK/dV kernel
+    float dsum = 0.0f;
+    if (q < p.Tq) {
+      const uint4* orow = reinterpret_cast<const uint4*>(p.o_in + static_cast<int64_t>(b) * p.oi_batch +
+                                                         static_cast<int64_t>(q) * p.oi_row + static_cast<int64_t>(h) * p.oi_head);
+      const uint4* grow = reinterpret_cast<const uint4*>(p.do_in + static_cast<int64_t>(b) * p.di_batch +
+                                                         static_cast<int64_t>(q) * p.di_row + static_cast<int64_t>(h) * p.di_head);
+      float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) {
+        const uint4 ov = orow[i], gv = grow[i];
+        const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float x0, x1, y0, y1;
+          unpack_bf16x2(ow[j], x0, x1);
+          unpack_bf16x2(gw[j], y0, y1);
+          a0 = fmaf(x0, y0, a0);
+          a1 = fmaf(x1, y1, a1);
+        }
+      }
+      dsum = a0 + a1;
+      p.dsum_out[sidx] = dsum;
+    }
     int row_lo, row_hi;
     row_limits(p, q, row_lo, row_hi);
     if (q >= p.Tq) row_lo = 0x3fffffff;
@@ -1287,19 +1276,48 @@ extern "C" int nx_attention_bwd(const NxAttnArgs* a, nx_stream_t stream_) {
   if (a->lse == nullptr || a->dsum == nullptr) return -1;
   const int HD = a->head_dim;
   const bool ext = a->softcap > 0.0f || a->alibi_slopes != nullptr || a->dropout_p > 0.0f;
-  // part 0
-  {
-    const int64_t total = static_cast<int64_t>(a->batch) * a->heads * a->tq;
-    const int rows_per_block = 256 / (HD / 8);
-    const int blocks = static_cast<int>(std::min<int64_t>((total + rows_per_block - 1) / rows_per_block, 148 * 16));
-    attn_bwd_dsum_kernel<<<blocks, 256, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(a->o.ptr), static_cast<const __nv_bfloat16*>(a->d_o.ptr), a->dsum, a->batch,
-        a->tq, a->heads, HD, a->o.row_stride, a->o.head_stride, a->o.batch_stride, a->d_o.row_stride,
-        a->d_o.head_stride, a->d_o.batch_stride);
-    if (cudaGetLastError() != cudaSuccess) return -2;
-  }
   int rc;
-  // part 1: dK, dV
+#define NX_BWD(KERN_, CFG_, HD_, EXT_)                                                              \
+  do {                                                                                              \
+    static bool once = false;                                                                       \
+    if (!once) {                                                                                    \
+      if (set_smem(KERN_<HD_, EXT_>, CFG_<HD_>::kSmem)) return -2;                                  \
+      once = true;                                                                                  \
+    }                                                                                               \
+    KERN_<HD_, EXT_><<<grid, kThreads, CFG_<HD_>::kSmem, st>>>(tq, tk, tv, tdo, p);                 \
+  } while (0)
+  // part 1: dQ (also forms dsum = rowsum(dO * O) and leaves it for part 2)
+  {
+    CUtensorMap tq, tk, tv, tdo;
+    if ((rc = make_map(&tq, a->q, a->tq, a->heads, a->batch, HD, 128))) return rc;
+    if ((rc = make_map(&tdo, a->d_o, a->tq, a->heads, a->batch, HD, 128))) return rc;
+    if ((rc = make_map(&tk, a->k, a->tk, a->kv_heads, a->batch, HD, 64))) return rc;
+    if ((rc = make_map(&tv, a->v, a->tk, a->kv_heads, a->batch, HD, 64))) return rc;
+    AttnDev p = base_params(a);
+    p.out = a->dq.ptr;
+    p.o_row = a->dq.row_stride;
+    p.o_head = a->dq.head_stride;
+    p.o_batch = a->dq.batch_stride;
+    p.nqb = (a->tq + 127) / 128;
+    p.o_in = static_cast<const __nv_bfloat16*>(a->o.ptr);
+    p.oi_row = a->o.row_stride;
+    p.oi_head = a->o.head_stride;
+    p.oi_batch = a->o.batch_stride;
+    p.do_in = static_cast<const __nv_bfloat16*>(a->d_o.ptr);
+    p.di_row = a->d_o.row_stride;
+    p.di_head = a->d_o.head_stride;
+    p.di_batch = a->d_o.batch_stride;
+    p.dsum_out = a->dsum;
+    const unsigned grid = static_cast<unsigned>(p.nqb * a->heads * a->batch);
+    if (HD == 64) {
+      if (ext) NX_BWD(attn_bwd_dq_kernel, DqCfg, 64, true);
+      else NX_BWD(attn_bwd_dq_kernel, DqCfg, 64, false);
+    } else {
+      if (ext) NX_BWD(attn_bwd_dq_kernel, DqCfg, 128, true);
+      else NX_BWD(attn_bwd_dq_kernel, DqCfg, 128, false);
+    }
+  }
+  // part 2: dK, dV (reads the dsum that part 1 wrote)
   {
     CUtensorMap tq, tk, tv, tdo;
     if ((rc = make_map(&tq, a->q, a->tq, a->heads, a->batch, HD, 64))) return rc;
@@ -1316,15 +1334,6 @@ extern "C" int nx_attention_bwd(const NxAttnArgs* a, nx_stream_t stream_) {
     p.o2_head = a->dv.head_stride;
     p.o2_batch = a->dv.batch_stride;
     const unsigned grid = static_cast<unsigned>(((a->tk + 127) / 128) * a->kv_heads * a->batch);
-#define NX_BWD(KERN_, CFG_, HD_, EXT_)                                                              \
-  do {                                                                                              \
-    static bool once = false;                                                                       \
-    if (!once) {                                                                                    \
-      if (set_smem(KERN_<HD_, EXT_>, CFG_<HD_>::kSmem)) return -2;                                  \
-      once = true;                                                                                  \
-    }                                                                                               \
-    KERN_<HD_, EXT_><<<grid, kThreads, CFG_<HD_>::kSmem, st>>>(tq, tk, tv, tdo, p);                 \
-  } while (0)
     if (HD == 64) {
       if (ext) NX_BWD(attn_bwd_dkdv_kernel, DkvCfg, 64, true);
       else NX_BWD(attn_bwd_dkdv_kernel, DkvCfg, 64, false);
@@ -1334,28 +1343,6 @@ extern "C" int nx_attention_bwd(const NxAttnArgs* a, nx_stream_t stream_) {
     }
     if (cudaGetLastError() != cudaSuccess) return -2;
   }
-  // part 2: dQ
-  {
-    CUtensorMap tq, tk, tv, tdo;
-    if ((rc = make_map(&tq, a->q, a->tq, a->heads, a->batch, HD, 128))) return rc;
-    if ((rc = make_map(&tdo, a->d_o, a->tq, a->heads, a->batch, HD, 128))) return rc;
-    if ((rc = make_map(&tk, a->k, a->tk, a->kv_heads, a->batch, HD, 64))) return rc;
-    if ((rc = make_map(&tv, a->v, a->tk, a->kv_heads, a->batch, HD, 64))) return rc;
-    AttnDev p = base_params(a);
-    p.out = a->dq.ptr;
-    p.o_row = a->dq.row_stride;
-    p.o_head = a->dq.head_stride;
-    p.o_batch = a->dq.batch_stride;
-    p.nqb = (a->tq + 127) / 128;
-    const unsigned grid = static_cast<unsigned>(p.nqb * a->heads * a->batch);
-    if (HD == 64) {
-      if (ext) NX_BWD(attn_bwd_dq_kernel, DqCfg, 64, true);
-      else NX_BWD(attn_bwd_dq_kernel, DqCfg, 64, false);
-    } else {
-      if (ext) NX_BWD(attn_bwd_dq_kernel, DqCfg, 128, true);
-      else NX_BWD(attn_bwd_dq_kernel, DqCfg, 128, false);
-    }
 #undef NX_BWD
-  }
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -107,7 +107,7 @@ def _p(t: Optional[torch.Tensor]) -> C.c_void_p:
 
 
 _KERNELS_PER_CALL = {"nx_norm_bwd": 2, "nx_embedding_bwd": 2, "nx_cross_entropy_shifted": 3, "nx_grad_norm": 2,
-                     "nx_colsum": 2, "nx_attention_bwd": 3}
+                     "nx_colsum": 2, "nx_attention_bwd": 2}
 
 
 def _check(rc: int, what: str) -> None:
