@@ -294,6 +294,7 @@ template <int HD, bool EXT>  // EXT: soft-capping / ALiBi / dropout row math (a 
 __global__ void __launch_bounds__(kFwdThreads, (HD == 64 ? 2 : 1))
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnDev p) {
+  pdl_launch_dependents();
   using C = FwdCfg<HD>;
   constexpr int HH = HD / 2;  // output columns per softmax thread
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -607,6 +608,7 @@ __global__ void __launch_bounds__(kThreads, (HD == 64 ? 2 : 1))
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                      const AttnDev p) {
+  pdl_launch_dependents();
   using C = DkvCfg<HD>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;

@@ -11,6 +11,11 @@ namespace nx {
 
 constexpr int kNumSmsB200 = 148;
 
+// Lets a following kernel that was launched with the programmatic-serialization attribute (the tensor-core GEMM)
+// begin its prologue early; that kernel still waits for this grid to complete before it reads anything.  A no-op
+// when the next launch is an ordinary one.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

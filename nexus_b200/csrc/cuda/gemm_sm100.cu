@@ -9,6 +9,10 @@
 // epilogue of unit i overlap the main loop of unit i+1.  Operands may be K-major or MN-major, so
 // forward (x W^T), dgrad (dy W) and wgrad (dy^T x) all run without a transpose pass.
 //
+// The pair kernel is launched with programmatic stream serialization: its set-up (barriers, TMEM, cluster sync) runs
+// while the previous kernel of the stream drains, and `griddepcontrol.wait` orders everything that touches global
+// memory after that kernel.  The kernels that precede GEMMs in a training step issue `griddepcontrol.launch_dependents`.
+//
 // Replaces the reference's cuBLASLt layer and its epilogues Bias / BiasGelu(+aux) / DGelu /
 // beta=1 accumulate (include/nexus/cuda/gemm.hpp:38-121, src/cuda/gemm_lt.cpp:260-360).
 #include "nx_api_comm.h"
@@ -293,6 +297,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above touched only this CTA's own state: when the launch allows it, it ran while the previous kernel
+  // of the stream was still finishing.  From here on operands, bias, residual and outputs are read and written.
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -874,16 +882,19 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const DevParams& p
   static int max_clusters = 0;  // 0: not asked yet, < 0: clusters of two cannot be placed
   auto kern = gemm_kernel<256, A_MN, B_MN, false, true, FAST>;
   cudaLaunchConfig_t cfg{};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // prologue may overlap the previous kernel's tail
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = C::kSmemBytes;
   cfg.stream = stream;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  static const bool no_pdl = std::getenv("NX_NO_PDL") != nullptr;  // measurement switch
+  cfg.numAttrs = no_pdl ? 1 : 2;
   if (max_clusters == 0) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess) return -2;
     cfg.gridDim = dim3(2 * 74);

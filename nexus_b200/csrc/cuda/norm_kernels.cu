@@ -48,6 +48,7 @@ __global__ void norm_fwd_kernel(const XT* __restrict__ x, const XT* __restrict__
                                 const PT* __restrict__ gamma, const PT* __restrict__ beta, YT* __restrict__ y,
                                 float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int cols,
                                 float eps) {
+  pdl_trigger();
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nvec = cols >> 2;
@@ -358,6 +359,7 @@ norm_bwd_fused_kernel(const GT* __restrict__ dy, const XT* __restrict__ x, const
 __global__ void norm_bwd_param_final2_kernel(const float* __restrict__ partial, float* __restrict__ dgamma,
                                              float* __restrict__ dbeta, float* __restrict__ dsum, int parts, int cols,
                                              int chunks, int accumulate) {
+  pdl_trigger();
   __shared__ float sg[8][33];
   __shared__ float sb[8][33];
   __shared__ float ss[8][33];

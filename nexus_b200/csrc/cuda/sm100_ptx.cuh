@@ -43,6 +43,14 @@ __device__ __forceinline__ void prefetch_l1(const void* p) {
   asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
 }
 
+// Programmatic dependent launch.  `pdl_launch_dependents`: the next kernel in the stream, if it was launched with
+// the programmatic-serialization attribute, may start its prologue once every CTA of this grid has passed this point
+// (or exited).  `pdl_wait`: blocks until the grids this one depends on have completed and their memory is visible;
+// a kernel launched with the attribute must pass it before touching anything its predecessors wrote.  Both are
+// no-ops for ordinary launches.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31u; }
 
 // ----------------------------------------------------------------------------------------------

@@ -320,6 +320,7 @@ __global__ void __launch_bounds__(512) ce_row_vec_kernel(LT* __restrict__ logits
 
 __global__ void ce_reduce_kernel(const float* __restrict__ row_loss, int64_t rows, CeState* st,
                                  float* __restrict__ loss_out, float loss_weight, int accumulate) {
+  pdl_trigger();
   __shared__ double s_scratch[32];
   double acc = 0.0;
   for (int64_t r = threadIdx.x; r < rows; r += blockDim.x) acc += row_loss[r];
@@ -589,6 +590,7 @@ __global__ void colsum_partial_vec_kernel(const __nv_bfloat16* __restrict__ dy, 
 }
 __global__ void colsum_final_kernel(const float* __restrict__ partial, float* __restrict__ out, int cols, int chunks,
                                     int accumulate) {
+  pdl_trigger();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= cols) return;
   float t = 0.0f;
