@@ -144,11 +144,14 @@ def main() -> int:
     ap.add_argument("--model", default="gpt2-124m")
     ap.add_argument("--seqs", type=int, default=SEQS_PER_GPU)
     ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
-    ap.add_argument("--graph", type=int, default=0, help="capture the whole step in a CUDA graph")
+    ap.add_argument("--graph", type=int, default=-1,
+                    help="trainer API replays the whole step as one CUDA graph (default: on for 1 GPU, off otherwise)")
     ap.add_argument("--skip-e2e", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.graph < 0:
+        args.graph = 1 if args.gpus == 1 else 0
 
     import numpy as np
     import torch
