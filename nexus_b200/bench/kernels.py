@@ -79,6 +79,23 @@ def build_cases(small: bool) -> Dict[str, Tuple[Callable[[], None], float, float
     else:
         add_gemm("gemm_4096", 4096, 4096, 4096)
 
+    # block-scaled FP8 (MX) GEMMs: Llama-7B projection shapes at 8192 tokens, and the quantiser that feeds them
+    from ..ops import _lowp as L
+
+    def add_mx(name, m, n, k, out_dtype=bf):
+        aq, asf = L.mx_quantize(rn(m, k))
+        bq, bsf = L.mx_quantize(rn(n, k, scale=0.05))
+        cases[name] = (lambda: L.mx_gemm(aq, asf, bq, bsf, out_dtype=out_dtype), 2.0 * m * n * k, 0.0)
+
+    mm = 2048 if small else 8192
+    add_mx("mxfp8_gemm_llama_qkv", mm, 3 * 4096, 4096)
+    add_mx("mxfp8_gemm_llama_ffn_up", mm, 11008, 4096)
+    add_mx("mxfp8_gemm_llama_ffn_down", mm, 4096, 11008)
+    add_mx("mxfp8_gemm_8192_fp8_out", mm, 8192, 8192, out_dtype=torch.float8_e4m3fn)
+    xq_src = rn(mm, 4096)
+    cases["mxfp8_quantize_rows"] = (lambda: L.mx_quantize(xq_src), 0.0, mm * 4096 * 3 + mm * 4096 // 32)
+    cases["mxfp8_quantize_transposed"] = (lambda: L.mx_quantize(xq_src, transpose=True), 0.0, mm * 4096 * 3 + mm * 4096 // 32)
+
     B, H, T, D = (4 if small else 16), 12, 1024, 64
     qkv = rn(B, T, 3, H, D)
     q, k, v = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
