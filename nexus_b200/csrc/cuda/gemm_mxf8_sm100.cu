@@ -24,6 +24,8 @@
 #include "sm100_ptx.cuh"
 #include "tensor_map.h"
 
+#include <algorithm>
+#include <cstdlib>
 #include <cuda_fp8.h>
 
 namespace {
@@ -187,6 +189,76 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   return v;
 }
 
+// One 32-column chunk of one accumulator row: alpha, bias, activation, running |max|, then the store - values as
+// BF16 / FP32, or, for an 8-bit output, the chunk as one block of the result's block-scaled form (its own power-of-two
+// scale, 32 codes, and the scale byte at its place in the atom order).
+__device__ __forceinline__ void mx_epilogue_chunk(const MxParams& p, const uint32_t (&raw)[32], int row, int col0, bool out8,
+                                                  float& tmax) {
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]) * p.alpha;
+  if (p.bias != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.n) v[j] += load_as_float(p.bias, p.bias_dtype, col0 + j);
+  }
+  if (p.act != NX_ACT_NONE) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
+  }
+  const bool row_ok = row < p.m;
+  const int valid = min(32, p.n - col0);  // <= 0: the whole chunk is past N
+  if (p.amax_out != nullptr && row_ok) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < valid) tmax = fmaxf(tmax, fabsf(v[j]));
+  }
+  if (out8) {
+    // one 32-block of the result's row: its own power-of-two scale, codes, and the scale byte in atom order
+    if ((col0 >> 5) < p.out_fmt_kb128 * 4) {
+      uint32_t sbyte = 127u;
+      if (row_ok && valid > 0) {
+        float am = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) am = fmaxf(am, fabsf(v[j]));
+        sbyte = mx_scale_byte(am, p.out_dtype);
+        const float inv = mx_inv_scale(sbyte);
+        uint32_t w[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          w[q] = enc8(v[4 * q] * inv, p.out_dtype) | (enc8(v[4 * q + 1] * inv, p.out_dtype) << 8) |
+                 (enc8(v[4 * q + 2] * inv, p.out_dtype) << 16) | (enc8(v[4 * q + 3] * inv, p.out_dtype) << 24);
+        uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.out) + static_cast<int64_t>(row) * p.ldo + col0);
+        op[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        op[1] = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+      p.out_scales[mx_scale_offset(row, col0 >> 5, p.out_fmt_kb128)] = static_cast<uint8_t>(sbyte);
+    }
+  } else if (row_ok && valid > 0) {
+    if (p.out_dtype == NX_F32) {
+      float* op = reinterpret_cast<float*>(p.out) + static_cast<int64_t>(row) * p.ldo + col0;
+      if (valid == 32 && (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          reinterpret_cast<float4*>(op)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      } else {
+        for (int j = 0; j < valid; ++j) op[j] = v[j];
+      }
+    } else {
+      __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(row) * p.ldo + col0;
+      if (valid == 32 && (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          reinterpret_cast<uint4*>(op)[q] =
+              make_uint4(pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                         pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+      } else {
+        for (int j = 0; j < valid; ++j) op[j] = __float2bfloat16_rn(v[j]);
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const MxParams p,
                  const uint32_t idesc) {
@@ -330,70 +402,7 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         uint32_t raw[32];
         tmem_ld_32x32b_x32(taddr + c * 32, raw);
         tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]) * p.alpha;
-        if (p.bias != nullptr) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.n) v[j] += load_as_float(p.bias, p.bias_dtype, col0 + j);
-        }
-        if (p.act != NX_ACT_NONE) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
-        }
-        const bool row_ok = row < p.m;
-        const int valid = min(32, p.n - col0);  // <= 0: the whole chunk is past N
-        if (p.amax_out != nullptr && row_ok) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < valid) tmax = fmaxf(tmax, fabsf(v[j]));
-        }
-        if (out8) {
-          // one 32-block of the result's row: its own power-of-two scale, codes, and the scale byte in atom order
-          if ((col0 >> 5) < p.out_fmt_kb128 * 4) {
-            uint32_t sbyte = 127u;
-            if (row_ok && valid > 0) {
-              float am = 0.0f;
-#pragma unroll
-              for (int j = 0; j < 32; ++j) am = fmaxf(am, fabsf(v[j]));
-              sbyte = mx_scale_byte(am, p.out_dtype);
-              const float inv = mx_inv_scale(sbyte);
-              uint32_t w[8];
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                w[q] = enc8(v[4 * q] * inv, p.out_dtype) | (enc8(v[4 * q + 1] * inv, p.out_dtype) << 8) |
-                       (enc8(v[4 * q + 2] * inv, p.out_dtype) << 16) | (enc8(v[4 * q + 3] * inv, p.out_dtype) << 24);
-              uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.out) + static_cast<int64_t>(row) * p.ldo + col0);
-              op[0] = make_uint4(w[0], w[1], w[2], w[3]);
-              op[1] = make_uint4(w[4], w[5], w[6], w[7]);
-            }
-            p.out_scales[mx_scale_offset(row, col0 >> 5, p.out_fmt_kb128)] = static_cast<uint8_t>(sbyte);
-          }
-        } else if (row_ok && valid > 0) {
-          if (p.out_dtype == NX_F32) {
-            float* op = reinterpret_cast<float*>(p.out) + static_cast<int64_t>(row) * p.ldo + col0;
-            if (valid == 32 && (p.ldo & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
-#pragma unroll
-              for (int q = 0; q < 8; ++q)
-                reinterpret_cast<float4*>(op)[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            } else {
-              for (int j = 0; j < valid; ++j) op[j] = v[j];
-            }
-          } else {
-            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(row) * p.ldo + col0;
-            if (valid == 32 && (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q)
-                reinterpret_cast<uint4*>(op)[q] =
-                    make_uint4(pack_bf16x2(v[8 * q], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
-                               pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
-            } else {
-              for (int j = 0; j < valid; ++j) op[j] = __float2bfloat16_rn(v[j]);
-            }
-          }
-        }
+        mx_epilogue_chunk(p, raw, row, n0 + c * 32, out8, tmax);
       }
       // this warp has read its part of the accumulator: hand it back to the MMA issuer
       tc_fence_before_sync();
@@ -415,6 +424,216 @@ gemm_mxf8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// CTA-pair variant: one 256 x 256 tile per cluster of two (tcgen05 cta_group::2).  Each CTA stages its own 128 rows
+// of A, half (128 rows) of the B tile, the scale atom of its A rows and both scale atoms of the B tile, so a tile's
+// operands cross L2 -> shared memory once per 256 x 256 outputs instead of once per 128 x 128.  The accumulator takes
+// 256 of the 512 TMEM columns and the scales 12 more, so there is one accumulator: the epilogue (eight warps per CTA)
+// drains it before the next tile's MMAs start, while the producer keeps filling stages.
+// ------------------------------------------------------------------------------------------------
+constexpr int kPairBN = 256;
+constexpr int kPairStages = 6;
+constexpr int kPairSfBytes = 3 * kAtomBytes;  // per stage: A atom, B atom (columns 0..127), B atom (columns 128..255)
+constexpr int kPairThreads = 320;             // warp 0 producer, warp 1 MMA, warps 2..9 epilogue
+constexpr int kPairSfaCol = 256, kPairSfbCol = 260;
+constexpr int kPairSmemBytes = kPairStages * (2 * kTileBytes + kPairSfBytes) + 1024 + 256;
+
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void umma_mxf8_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                  uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n\t"
+      "}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(tmem_sfa), "r"(tmem_sfb), "r"(accumulate)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kPairThreads, 1)
+gemm_mxf8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                      const MxParams p, const uint32_t idesc) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sf_base = smem + kPairStages * 2 * kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sf_base + kPairStages * kPairSfBytes);
+  uint64_t* full_bar = bars;                   // [stages]  used in the even CTA: bytes of both CTAs
+  uint64_t* empty_bar = bars + kPairStages;    // [stages]  in both CTAs
+  uint64_t* tfull_bar = bars + 2 * kPairStages;  // in both CTAs
+  uint64_t* tempty_bar = tfull_bar + 1;          // used in the even CTA: 16 epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const int tile_first = static_cast<int>(blockIdx.x >> 1), tile_step = static_cast<int>(gridDim.x >> 1);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tfull_bar, 1);
+    mbar_init(tempty_bar, 16);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  cluster_sync_all();
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_sfa);
+    tma_prefetch_desc(&tmap_sfb);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t kCtaStageBytes = 2 * kTileBytes + kPairSfBytes;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer (one lane in each CTA)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = tile_first; t < p.num_tiles && ok; t += tile_step) {
+        const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+        const int m0 = tm * 256 + static_cast<int>(cta_rank) * kBM;
+        const int n0 = tn * kPairBN;
+        for (int kb = 0; kb < p.kb_total; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+            ok = false;
+            atomicCAS(p.status, 0, kStatusTimeoutProducer);
+            break;
+          }
+          uint8_t* sa = smem + stage * 2 * kTileBytes;
+          uint8_t* sb = sa + kTileBytes;
+          uint8_t* ss = sf_base + stage * kPairSfBytes;
+          if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * kCtaStageBytes);
+          const uint32_t bar = mapa_shared(smem_u32(&full_bar[stage]), 0);
+          tma_load_3d_pair(sa, &tmap_a, bar, kb * kBK, m0, 0);
+          tma_load_3d_pair(sb, &tmap_b, bar, kb * kBK, n0 + static_cast<int>(cta_rank) * 128, 0);
+          // scale atoms as rows of 256 bytes: atom index * 2 is the row
+          tma_load_3d_pair(ss, &tmap_sfa, bar, 0, 2 * ((2 * tm + static_cast<int>(cta_rank)) * p.kb_total + kb), 0);
+          tma_load_3d_pair(ss + kAtomBytes, &tmap_sfb, bar, 0, 2 * ((2 * tn) * p.kb_total + kb), 0);
+          tma_load_3d_pair(ss + 2 * kAtomBytes, &tmap_sfb, bar, 0, 2 * ((2 * tn + 1) * p.kb_total + kb), 0);
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      // the even CTA's commits also arrive on this CTA's barriers: leave only after every filled stage was released
+      for (int s = 0; s < kPairStages && ok; ++s) {
+        ok = mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag);
+        if (++stage == kPairStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (even CTA only)
+    if (lane == 0 && cta_rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int t = tile_first; t < p.num_tiles && ok; t += tile_step) {
+        if (!mbar_wait_bounded(tempty_bar, acc_phase ^ 1u, abort_flag)) {
+          atomicCAS(p.status, 0, kStatusTimeoutMma);
+          break;
+        }
+        tc_fence_after_sync();
+        for (int kb = 0; kb < p.kb_total; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+            ok = false;
+            atomicCAS(p.status, 0, kStatusTimeoutMma);
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * 2 * kTileBytes);
+          const uint32_t sb = sa + kTileBytes;
+          const uint32_t ss = smem_u32(sf_base + stage * kPairSfBytes);
+          // each CTA's atoms (same shared-memory offsets) -> its own TMEM
+          tmem_cp_32x128b_warpx4_pair(tmem_base + kPairSfaCol, make_sf_desc(ss));
+          tmem_cp_32x128b_warpx4_pair(tmem_base + kPairSfbCol, make_sf_desc(ss + kAtomBytes));
+          tmem_cp_32x128b_warpx4_pair(tmem_base + kPairSfbCol + 4, make_sf_desc(ss + 2 * kAtomBytes));
+#pragma unroll
+          for (int ks = 0; ks < kBK / 32; ++ks) {
+            const uint64_t da = make_smem_desc_sw128(sa + ks * 32, 16, 1024);
+            const uint64_t db = make_smem_desc_sw128(sb + ks * 32, 16, 1024);
+            umma_mxf8_ss_pair(tmem_base, da, db, idesc_with_sf_id(idesc, ks), tmem_base + kPairSfaCol,
+                              tmem_base + kPairSfbCol, (kb > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[stage], 3);
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(tfull_bar, 3);
+        acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 2..9 of both CTAs)
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;  // columns [128 * half, 128 * half + 128) of the tile
+    uint32_t acc_phase = 0;
+    float tmax = 0.0f;
+    const bool out8 = p.out_dtype == NX_E4M3 || p.out_dtype == NX_E5M2;
+    for (int t = tile_first; t < p.num_tiles; t += tile_step) {
+      const int tm = t % p.tiles_m, tn = t / p.tiles_m;
+      const int row = tm * 256 + static_cast<int>(cta_rank) * kBM + quarter * 32 + lane;
+      const int n0 = tn * kPairBN + half * 128;
+      if (!mbar_wait_bounded(tfull_bar, acc_phase, abort_flag)) {
+        atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(half * 128);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t raw[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, raw);
+        tmem_ld_wait();
+        if (c == 3) {
+          // everything this warp needs has left TMEM: the next tile's MMAs may overwrite the accumulator
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(tempty_bar), 0));
+        }
+        mx_epilogue_chunk(p, raw, row, n0 + c * 32, out8, tmax);
+      }
+      acc_phase ^= 1u;
+    }
+    if (p.amax_out != nullptr) {
+      tmax = warp_max(tmax);
+      if (lane == 0 && tmax > 0.0f) atomicMax(p.amax_out, __float_as_uint(tmax));
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees TMEM or leaves while the other may still use the pair
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 
@@ -453,6 +672,62 @@ extern "C" int nx_mx_dequantize(const void* codes, const void* scales, int fmt, 
       static_cast<const uint8_t*>(codes), static_cast<const uint8_t*>(scales), fmt, rows, cols, dst, dst_dtype);
   return launch_status();
 }
+
+namespace {
+// -3: clusters of two cannot be placed on this device (the caller falls back to single-CTA tiles)
+int launch_mx_pair(const NxMxGemmArgs* a, MxParams p, const CUtensorMap& ta, cudaStream_t stream) {
+  static int max_clusters = 0;  // 0: not asked yet, < 0: unavailable
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kPairThreads);
+  cfg.dynamicSmemBytes = kPairSmemBytes;
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (max_clusters == 0) {
+    if (cudaFuncSetAttribute(gemm_mxf8_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) !=
+        cudaSuccess)
+      return -2;
+    cfg.gridDim = dim3(2 * 74);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_mxf8_pair_kernel, &cfg) != cudaSuccess || n < 1) {
+      (void)cudaGetLastError();
+      max_clusters = -1;
+    } else {
+      max_clusters = n;
+    }
+  }
+  if (max_clusters < 0) return -3;
+  p.tiles_m = (a->m + 255) / 256;
+  p.tiles_n = (a->n + kPairBN - 1) / kPairBN;
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  // B: 128 rows per CTA; the scale atoms seen as rows of 256 bytes (two rows per atom)
+  CUtensorMap tb, tsa, tsb;
+  int rc = nx::make_tensor_map_3d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->b, a->k, a->n, 1, a->ldb, 0, kBK, 128);
+  if (rc != 0) return rc;
+  const uint64_t kb128 = static_cast<uint64_t>(p.kb_total);
+  rc = nx::make_tensor_map_3d(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->sfa, 256, 2 * ((a->m + 127) / 128) * kb128, 1, 256, 0,
+                              256, 2, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != 0) return rc;
+  rc = nx::make_tensor_map_3d(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->sfb, 256, 2 * ((a->n + 127) / 128) * kb128, 1, 256, 0,
+                              256, 2, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc != 0) return rc;
+  int clusters = std::min(p.num_tiles, max_clusters);
+  if (a->max_ctas > 1) clusters = std::min(clusters, a->max_ctas / 2);
+  cfg.gridDim = dim3(2 * clusters);
+  const uint32_t idesc = make_idesc_mx(a->a_dtype == NX_E4M3 ? kFmtE4M3 : kFmtE5M2,
+                                       a->b_dtype == NX_E4M3 ? kFmtE4M3 : kFmtE5M2, 256, kPairBN);
+  if (cudaLaunchKernelEx(&cfg, gemm_mxf8_pair_kernel, ta, tb, tsa, tsb, p, idesc) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return -2;
+  }
+  return 0;
+}
+}  // namespace
 
 extern "C" int nx_gemm_mxf8(const NxMxGemmArgs* a, nx_stream_t stream_) {
   if (a == nullptr || a->a == nullptr || a->b == nullptr || a->sfa == nullptr || a->sfb == nullptr || a->out == nullptr ||
@@ -501,6 +776,14 @@ extern "C" int nx_gemm_mxf8(const NxMxGemmArgs* a, nx_stream_t stream_) {
   if (rc != 0) return rc;
   rc = nx::make_tensor_map_3d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->b, a->k, a->n, 1, a->ldb, 0, kBK, kBN);
   if (rc != 0) return rc;
+
+  // CTA pairs (256 x 256 tiles) when the problem fills them; otherwise, or where clusters of two cannot be placed,
+  // single-CTA 128 x 128 tiles
+  static const bool single_only = std::getenv("NX_MX_SINGLE") != nullptr;  // measurement switch
+  if (a->m >= 256 && a->n >= 256 && !single_only && (a->max_ctas <= 0 || a->max_ctas >= 2)) {
+    const int rc_pair = launch_mx_pair(a, p, ta, stream);
+    if (rc_pair != -3) return rc_pair;
+  }
 
   static bool attr_set = false;
   if (!attr_set) {

@@ -104,10 +104,36 @@ class _FusedLinear(torch.autograd.Function):
         return dx, dw, db, None
 
 
+_LINEAR_PRECISION = ["native"]
+
+
+class linear_precision:
+    """Context manager: ``with linear_precision("mxfp8"):`` runs every :func:`fused_linear` inside it (forward,
+    input gradient and weight gradient) on the block-scaled FP8 tensor-core path - FP8 codes with one power-of-two
+    scale per 32 elements along the contraction axis, E4M3 for activations and weights, E5M2 for gradients.
+    Layers whose sizes the path does not take (K or N not a multiple of 16) keep their native precision."""
+
+    def __init__(self, kind: str = "mxfp8"):
+        if kind not in ("native", "mxfp8"):
+            raise ValueError("linear_precision: kind must be 'native' or 'mxfp8'")
+        self.kind = kind
+
+    def __enter__(self):
+        _LINEAR_PRECISION.append(self.kind)
+        return self
+
+    def __exit__(self, *exc):
+        _LINEAR_PRECISION.pop()
+        return False
+
+
 def fused_linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None, act: str = "identity"):
     """``act(x @ w.T + b)`` with ``w`` [out, in]; one autograd node."""
     if act not in _ACTS:
         raise ValueError(f"fused_linear: activation must be one of {_ACTS}")
+    if _LINEAR_PRECISION[-1] == "mxfp8" and x.shape[-1] % 16 == 0 and w.shape[0] % 16 == 0 and w.is_contiguous():
+        from ..ops import _lowp as L
+        return _act_fwd(L.mx_linear(x, w, b), act)
     k_ok = x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0
     if _use_kernels(x) and w.dtype == x.dtype and k_ok and w.is_contiguous():
         return _FusedLinear.apply(x, w, b, act)

@@ -43,3 +43,22 @@ def test_mx_gemm_and_linear_reference():
     x2, w2 = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
     torch.nn.functional.linear(x2, w2).square().sum().backward()
     assert (x.grad - x2.grad).norm() / x2.grad.norm() < 0.1 and (w.grad - w2.grad).norm() / w2.grad.norm() < 0.1
+
+
+def test_language_model_under_mxfp8_linear_precision():
+    from nexus_b200.fused.ops import linear_precision
+    from nexus_b200.lm.config import preset
+    from nexus_b200.lm.model import build
+    cfg = preset("llama2-7b")
+    cfg.n_layer, cfg.d_model, cfg.n_head, cfg.n_kv_head, cfg.d_ff, cfg.vocab_size, cfg.max_position = 2, 64, 4, 4, 192, 128, 64
+    model = build(cfg)
+    toks = torch.randint(0, 128, (2, 32))
+    native = model.loss(toks)
+    with linear_precision("mxfp8"):
+        low = model.loss(toks)
+        low.backward()
+    assert abs(float(low) - float(native)) < 0.05 * abs(float(native))
+    grads = [p.grad for p in model.parameters() if p.grad is not None]
+    assert grads and all(torch.isfinite(g).all() for g in grads)
+    model.zero_grad()
+    native.backward()
