@@ -607,19 +607,18 @@ gemm_mxf8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(half * 128);
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t raw[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, raw);
-        tmem_ld_wait();
-        if (c == 3) {
-          // everything this warp needs has left TMEM: the next tile's MMAs may overwrite the accumulator
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(tempty_bar), 0));
-        }
-        mx_epilogue_chunk(p, raw, row, n0 + c * 32, out8, tmax);
-      }
+      // The warp's whole share of the accumulator (32 rows x 128 columns) moves to registers first, so that the
+      // accumulator goes back to the MMA issuer after four TMEM loads; bias, activation, conversion and the global
+      // stores then run under the next tile's MMAs.
+      uint32_t raw[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(taddr + c * 32, raw[c]);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(tempty_bar), 0));
+#pragma unroll
+      for (int c = 0; c < 4; ++c) mx_epilogue_chunk(p, raw[c], row, n0 + c * 32, out8, tmax);
       acc_phase ^= 1u;
     }
     if (p.amax_out != nullptr) {
