@@ -169,8 +169,14 @@ class _VocabParallelCE(torch.autograd.Function):
 
 # ------------------------------------------------------------------------------------- engine
 class ParallelLm:
-    def __init__(self, model, pg, cfg: ParallelConfig):
+    def __init__(self, model, pg, cfg: ParallelConfig, device=None, compute_dtype: Optional[torch.dtype] = None):
+        """``device``: where this rank's parameter slices, optimizer state and activations live (default: CPU).
+        ``compute_dtype``: dtype of activations and of the weights as the GEMMs see them (default: FP32); the FP32
+        slices stay the master copy that AdamW updates.  On a CUDA device the linear layers run on the tcgen05 GEMM
+        kernels (``fused_linear``; block-scaled FP8 under ``fused.ops.linear_precision("mxfp8")``)."""
         self.cfg, self.pg = cfg, pg
+        self.device = torch.device(device) if device is not None else torch.device("cpu")
+        self.cd = compute_dtype or torch.float32
         if cfg.world() != pg.size():
             raise ValueError(f"dp*pp*cp*tp = {cfg.world()} but the group has {pg.size()} ranks")
         mc: LmConfig = model.config
@@ -202,6 +208,8 @@ class ParallelLm:
         self.kind: Dict[str, str] = {}   # "sharded" (tp-split) | "replicated"
         self._slice_model(model)
         self.rope = RopeCache(mc) if mc.pos == "rope" else None
+        if self.rope is not None and self.device.type != "cpu":
+            self.rope.to(self.device)
         self.names = list(self.params.keys())
         self.m = {n: torch.zeros_like(p) for n, p in self.params.items()}
         self.v = {n: torch.zeros_like(p) for n, p in self.params.items()}
@@ -212,7 +220,7 @@ class ParallelLm:
 
     # ------------------------------------------------------------------------------- slicing
     def _add(self, name: str, t: torch.Tensor, kind: str) -> None:
-        self.params[name] = torch.nn.Parameter(t.detach().clone().float())
+        self.params[name] = torch.nn.Parameter(t.detach().to(device=self.device, dtype=torch.float32, copy=True))
         self.kind[name] = kind
 
     def _slice_model(self, model) -> None:
@@ -221,9 +229,10 @@ class ParallelLm:
         first = 0 in self.my_chunks
         last = (self.nchunks - 1) in self.my_chunks
         sd = {n: p.detach() for n, p in model.named_parameters()}
+        wdev = sd["wte"].device
         Vl = self.Vp // tp
         if first or (last and mc.tie_embeddings):
-            w = torch.zeros(self.Vp, mc.d_model)
+            w = torch.zeros(self.Vp, mc.d_model, device=wdev, dtype=sd["wte"].dtype)
             w[: sd["wte"].shape[0]] = sd["wte"]
             self._add("wte", w[r * Vl: (r + 1) * Vl], "sharded")
         if first and mc.pos == "learned":
@@ -269,7 +278,7 @@ class ParallelLm:
             if "norm_f.bias" in sd:
                 self._add("norm_f.bias", sd["norm_f.bias"], "replicated")
             if not mc.tie_embeddings:
-                w = torch.zeros(self.Vp, mc.d_model)
+                w = torch.zeros(self.Vp, mc.d_model, device=wdev, dtype=sd["lm_head"].dtype)
                 w[: sd["lm_head"].shape[0]] = sd["lm_head"]
                 self._add("lm_head", w[r * Vl: (r + 1) * Vl], "sharded")
 
@@ -281,25 +290,32 @@ class ParallelLm:
             return F_.rms_norm(x, w, self.mc.norm_eps)
         return F_.fused_layernorm(x, w, b, self.mc.norm_eps)
 
+    def _w(self, w):
+        """The weight as the GEMM sees it: the FP32 master slice cast to the compute dtype (the cast is part of the
+        graph, so the gradient arrives in FP32)."""
+        return w if w.dtype == self.cd else w.to(self.cd)
+
     def _col_linear(self, h, w, b):
         """Column-parallel linear on the region input (replicated, or token-sharded under SP)."""
+        w = self._w(w)
         if self.cfg.sp and self.cfg.tp > 1:
             if self.cfg.async_tp:
                 y = _RingAllGatherMatmul.apply(h, w, self.tp_g)
             else:
-                y = C.all_gather_rows(h, self.tp_g) @ w.t()
+                y = F_.fused_linear(C.all_gather_rows(h, self.tp_g), w)
         else:
-            y = C.copy_to_group(h, self.tp_g) @ w.t()
-        return y if b is None else y + b
+            y = F_.fused_linear(C.copy_to_group(h, self.tp_g), w)
+        return y if b is None else y + b.to(y.dtype)
 
     def _row_linear(self, a, w, b):
         """Row-parallel linear back into the region output."""
+        w = self._w(w)
         if self.cfg.sp and self.cfg.tp > 1:
             y = _MatmulRingReduceScatter.apply(a, w, self.tp_g) if self.cfg.async_tp else \
-                C.reduce_scatter_rows(a @ w.t(), self.tp_g)
+                C.reduce_scatter_rows(F_.fused_linear(a, w), self.tp_g)
         else:
-            y = C.all_reduce(a @ w.t(), self.tp_g)
-        return y if b is None else y + b
+            y = C.all_reduce(F_.fused_linear(a, w), self.tp_g)
+        return y if b is None else y + b.to(y.dtype)
 
     def _block(self, x, l: int, B: int, Tl: int, positions):
         mc, tp = self.mc, self.cfg.tp
@@ -338,11 +354,11 @@ class ParallelLm:
         Vl = self.Vp // tp
         ids = tokens.reshape(-1).long() - r * Vl
         ok = (ids >= 0) & (ids < Vl)
-        x = self.params["wte"][ids.clamp(0, Vl - 1)] * ok[:, None]
+        x = (self.params["wte"][ids.clamp(0, Vl - 1)] * ok[:, None]).to(self.cd)
         if self.mc.pos == "learned":
             # added once (not once per tp rank): only tp rank 0 contributes before the reduction
             pe = self.params["wpe"][positions.reshape(-1)]
-            x = x + (pe if r == 0 else torch.zeros_like(pe))
+            x = x + (pe if r == 0 else torch.zeros_like(pe)).to(self.cd)
         if self.cfg.sp and tp > 1:
             return C.reduce_scatter_rows(x, self.tp_g)
         return C.all_reduce(x, self.tp_g)
@@ -355,7 +371,7 @@ class ParallelLm:
         else:
             h = C.copy_to_group(h, self.tp_g)
         w = self.params["wte"] if self.mc.tie_embeddings else self.params["lm_head"]
-        logits = h @ w.t()
+        logits = F_.fused_linear(h, self._w(w)).float()
         return _VocabParallelCE.apply(logits, targets.reshape(-1), self.tp_g, self.tp_r * (self.Vp // self.cfg.tp),
                                       self.mc.vocab_size, -100)
 
@@ -375,7 +391,7 @@ class ParallelLm:
         B, T = tokens.shape
         tg = torch.full_like(tokens, -100, dtype=torch.long)
         tg[:, :-1] = tokens[:, 1:].long()
-        pos = torch.arange(T)[None].expand(B, T)
+        pos = torch.arange(T, device=tokens.device)[None].expand(B, T)
         cp = self.cfg.cp
         if cp > 1:
             layout = "contiguous" if self.cfg.cp_algorithm == "ulysses" else self.cfg.cp_layout
@@ -422,7 +438,7 @@ class ParallelLm:
             if a.kind == "F":
                 x_in = None
                 if g > 0:
-                    x_in = torch.empty(rows, d)
+                    x_in = torch.empty(rows, d, device=self.device, dtype=self.cd)
                     self._p2p_recv(x_in, prev_rank, tag=1000 + mb * 64 + g)
                     x_in.requires_grad_(True)
                 out = self._run_chunk(g, x_in, tok, pos, tg, B, Tl)
@@ -435,9 +451,9 @@ class ParallelLm:
             else:  # B
                 x_in, out = saved.pop((mb, g))
                 if g == self.nchunks - 1:
-                    gout = torch.tensor(weights[mb], dtype=out.dtype)
+                    gout = torch.tensor(weights[mb], dtype=out.dtype, device=out.device)
                 else:
-                    gout = torch.empty(rows, d)
+                    gout = torch.empty(rows, d, device=self.device, dtype=self.cd)
                     self._p2p_recv(gout, next_rank, tag=5000 + mb * 64 + g)
                 if split_w:
                     if x_in is not None:
@@ -457,7 +473,7 @@ class ParallelLm:
         self._sends = []
         self._sync_grads()
         # loss: sum over cp shards, known on the last stage -> broadcast over pp
-        lt = torch.tensor([total_loss], dtype=torch.float64)
+        lt = torch.tensor([total_loss], dtype=torch.float64, device=self.device)
         if self.cp_g is not None:
             self.cp_g.all_reduce_tensor(lt, "sum")
         if self.pp_g is not None:
@@ -505,7 +521,7 @@ class ParallelLm:
             pad = (-flat.numel()) % n
             if pad:
                 flat = torch.cat([flat, flat.new_zeros(pad)])
-            shard = torch.empty(flat.numel() // n)
+            shard = torch.empty(flat.numel() // n, device=flat.device, dtype=flat.dtype)
             self.dpcp_g.reduce_scatter_tensor(shard, flat, "sum")
             self.dpcp_g.all_gather_tensor(flat, shard)
             off = 0
@@ -524,7 +540,7 @@ class ParallelLm:
             if n == "wte" and self.tie_g is not None and self.pp_r != 0:
                 s = 0.0  # the tied table lives on two stages: count it once
             sq += s
-        t = torch.tensor([sq], dtype=torch.float64)
+        t = torch.tensor([sq], dtype=torch.float64, device=self.device)
         if self.tppp_g is not None:
             self.tppp_g.all_reduce_tensor(t, "sum")
         return math.sqrt(float(t))
@@ -555,13 +571,13 @@ class ParallelLm:
         names = self.names
         flat_p = torch.cat([self.params[x].data.reshape(-1) for x in names])
         flat_g = torch.cat([self.params[x].grad.reshape(-1) for x in names])
-        flat_wd = torch.cat([torch.full((self.params[x].numel(),), w) for x, w in zip(names, wd)])
+        flat_wd = torch.cat([torch.full((self.params[x].numel(),), w, device=self.device) for x, w in zip(names, wd)])
         pad = (-flat_p.numel()) % n
         if pad:
             flat_p, flat_g, flat_wd = (torch.cat([t, t.new_zeros(pad)]) for t in (flat_p, flat_g, flat_wd))
         S = flat_p.numel() // n
         if self._zero_shards is None:
-            self._zero_shards = (torch.zeros(S), torch.zeros(S))
+            self._zero_shards = (torch.zeros(S, device=self.device), torch.zeros(S, device=self.device))
         ms, vs = self._zero_shards
         sl = slice(r * S, (r + 1) * S)
         ps, gs, ws = flat_p[sl].clone(), flat_g[sl], flat_wd[sl]
@@ -592,7 +608,7 @@ class ParallelLm:
         tok, pos, tg = self._prepare(tokens)
         B, Tl = tok.shape
         loss = self._run_chunk(0, None, tok, pos, tg, B, Tl) if self.nchunks == 1 else None
-        t = torch.tensor([float(loss)], dtype=torch.float64)
+        t = torch.tensor([float(loss)], dtype=torch.float64, device=self.device)
         if self.cp_g is not None:
             self.cp_g.all_reduce_tensor(t, "sum")
         return float(t) / max(1, tokens.shape[0] * (tokens.shape[1] - 1))
