@@ -88,14 +88,35 @@ __global__ void mx_quantize_kernel(const void* __restrict__ src, int src_dtype, 
     }
     float v[32];
     float am = 0.0f;
+    bool loaded = false;
+    if constexpr (!TRANSPOSE) {
+      // a whole block of a BF16 row in four 16-byte loads
+      if (src_dtype == NX_BF16 && k0 + 32 <= Kc && (ld & 7) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        const uint4* sp4 = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(src) +
+                                                          static_cast<int64_t>(r) * ld + k0);
 #pragma unroll
-    for (int t = 0; t < 32; ++t) {
-      const int k = k0 + t;
-      float x = 0.0f;
-      if (k < Kc) x = TRANSPOSE ? load_as_float(src, src_dtype, static_cast<int64_t>(k) * ld + r)
-                                : load_as_float(src, src_dtype, static_cast<int64_t>(r) * ld + k);
-      v[t] = x;
-      am = fmaxf(am, fabsf(x));
+        for (int q = 0; q < 4; ++q) {
+          const uint4 u = sp4[q];
+          unpack_bf16x2(u.x, v[8 * q + 0], v[8 * q + 1]);
+          unpack_bf16x2(u.y, v[8 * q + 2], v[8 * q + 3]);
+          unpack_bf16x2(u.z, v[8 * q + 4], v[8 * q + 5]);
+          unpack_bf16x2(u.w, v[8 * q + 6], v[8 * q + 7]);
+        }
+#pragma unroll
+        for (int t = 0; t < 32; ++t) am = fmaxf(am, fabsf(v[t]));
+        loaded = true;
+      }
+    }
+    if (!loaded) {
+#pragma unroll
+      for (int t = 0; t < 32; ++t) {
+        const int k = k0 + t;
+        float x = 0.0f;
+        if (k < Kc) x = TRANSPOSE ? load_as_float(src, src_dtype, static_cast<int64_t>(k) * ld + r)
+                                  : load_as_float(src, src_dtype, static_cast<int64_t>(r) * ld + k);
+        v[t] = x;
+        am = fmaxf(am, fabsf(x));
+      }
     }
     const uint32_t sb = mx_scale_byte(am, fmt);
     const float inv = mx_inv_scale(sb);
