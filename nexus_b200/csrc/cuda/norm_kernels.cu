@@ -5,6 +5,7 @@
 // (layernorm_forward, residual_layernorm_forward, rmsnorm_forward, norm backward + 2-stage
 // deterministic parameter reduce).
 #include "common.cuh"
+#include <cstdlib>
 #include "nx_api_kernels.h"
 
 #include <algorithm>
@@ -123,6 +124,94 @@ __global__ void norm_fwd_kernel(const XT* __restrict__ x, const XT* __restrict__
   }
 }
 
+// Rows of 128 * VPL columns: a warp keeps its row in registers (VPL vectors of four per lane), so the row is read
+// from memory once with all of its loads in flight together, and gamma / beta are loaded once per warp.  Same
+// arithmetic and summation order as norm_fwd_kernel.
+template <typename XT, typename PT, typename YT, bool kRms, int VPL>
+__global__ void __launch_bounds__(256)
+norm_fwd_reg_kernel(const XT* __restrict__ x, const XT* __restrict__ res, XT* __restrict__ sum_out,
+                    const PT* __restrict__ gamma, const PT* __restrict__ beta, YT* __restrict__ y,
+                    float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, float eps) {
+  pdl_trigger();
+  constexpr int kCols = 128 * VPL;
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  float g[VPL][4], b[VPL][4];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    Vec4<PT>::load(gamma + 4 * (lane + 32 * i), g[i]);
+    if (!kRms && beta) {
+      Vec4<PT>::load(beta + 4 * (lane + 32 * i), b[i]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[i][j] = 0.0f;
+    }
+  }
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < rows; row += gridDim.x * warps_per_block) {
+    const XT* xr = x + static_cast<int64_t>(row) * kCols;
+    float v[VPL][4];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) Vec4<XT>::load(xr + 4 * (lane + 32 * i), v[i]);
+    if (res) {
+      const XT* rr = res + static_cast<int64_t>(row) * kCols;
+      float q[VPL][4];
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) Vec4<XT>::load(rr + 4 * (lane + 32 * i), q[i]);
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[i][j] += q[i][j];
+      }
+      if (sum_out) {
+        XT* sr = sum_out + static_cast<int64_t>(row) * kCols;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+          Vec4<XT>::store(sr + 4 * (lane + 32 * i), v[i]);
+          // what the later passes normalise is the stored (rounded) sum
+          Vec4<XT>::load(sr + 4 * (lane + 32 * i), v[i]);
+        }
+      }
+    }
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i)
+      s += kRms ? (v[i][0] * v[i][0] + v[i][1] * v[i][1] + v[i][2] * v[i][2] + v[i][3] * v[i][3])
+                : (v[i][0] + v[i][1] + v[i][2] + v[i][3]);
+    s = warp_sum(s);
+    float mean = 0.0f, rstd;
+    if (kRms) {
+      rstd = rsqrtf(s / kCols + eps);
+    } else {
+      mean = s / kCols;
+      float var = 0.0f;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) var += (v[i][j] - mean) * (v[i][j] - mean);
+      }
+      var = warp_sum(var);
+      rstd = rsqrtf(var / kCols + eps);
+    }
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+    YT* yr = y + static_cast<int64_t>(row) * kCols;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      float o[4];
+      if (!kRms && beta) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = (v[i][j] - mean) * rstd * g[i][j] + b[i][j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = (v[i][j] - mean) * rstd * g[i][j];
+      }
+      Vec4<YT>::store(yr + 4 * (lane + 32 * i), o);
+    }
+  }
+}
+
 // dx[row] = (add ? add[row] : 0) + rstd * (g*dy - mean(g*dy) - xhat * mean(g*dy*xhat))        (LayerNorm)
 // dx[row] = (add ? add[row] : 0) + rstd * (g*dy - xhat * mean(g*dy*xhat))                     (RMSNorm)
 template <typename XT, typename PT, typename GT, typename DT, bool kRms>
@@ -231,6 +320,22 @@ int launch_fwd(bool rms, const void* x, const void* res, void* sum_out, const vo
                float* mean, float* rstd, int rows, int cols, float eps, cudaStream_t st) {
   const int threads = 256, wpb = threads / 32;
   const int blocks = std::min((rows + wpb - 1) / wpb, kNumSmsB200 * 8);
+  static const bool no_reg = std::getenv("NX_NORM_FWD_GENERIC") != nullptr;  // measurement switch
+  if (!no_reg && cols % 128 == 0 && cols / 128 <= 8) {
+#define NX_FWD_REG(V_)                                                                                                   \
+  case V_:                                                                                                               \
+    if (rms)                                                                                                             \
+      norm_fwd_reg_kernel<XT, PT, YT, true, V_><<<blocks, threads, 0, st>>>(                                             \
+          (const XT*)x, (const XT*)res, (XT*)sum_out, (const PT*)gamma, (const PT*)beta, (YT*)y, mean, rstd, rows, eps); \
+    else                                                                                                                 \
+      norm_fwd_reg_kernel<XT, PT, YT, false, V_><<<blocks, threads, 0, st>>>(                                            \
+          (const XT*)x, (const XT*)res, (XT*)sum_out, (const PT*)gamma, (const PT*)beta, (YT*)y, mean, rstd, rows, eps); \
+    return launch_status();
+    switch (cols / 128) {
+      NX_FWD_REG(1) NX_FWD_REG(2) NX_FWD_REG(3) NX_FWD_REG(4) NX_FWD_REG(5) NX_FWD_REG(6) NX_FWD_REG(7) NX_FWD_REG(8)
+    }
+#undef NX_FWD_REG
+  }
   if (rms)
     norm_fwd_kernel<XT, PT, YT, true><<<blocks, threads, 0, st>>>(
         (const XT*)x, (const XT*)res, (XT*)sum_out, (const PT*)gamma, (const PT*)beta, (YT*)y, mean, rstd, rows, cols,
@@ -284,17 +389,45 @@ norm_bwd_fused_kernel(const GT* __restrict__ dy, const XT* __restrict__ x, const
       if (kSum) as[i][j] = 0.0f;
     }
   }
-  for (int row = blockIdx.x * 8 + warp; row < rows; row += gridDim.x * 8) {
-    const XT* xr = x + static_cast<int64_t>(row) * kCols;
-    const GT* gr = dy + static_cast<int64_t>(row) * kCols;
-    const float mu = kRms ? 0.0f : mean[row];
-    const float rs = rstd[row];
+  // The loads of a warp's next row are issued before the arithmetic and the stores of the current one, so a warp
+  // always has a row of x and dy in flight (the kernel runs one block of eight warps per SM).
+  float xn[VPL][4], dn[VPL][4];
+  float mu_n = 0.0f, rs_n = 0.0f;
+  const int row_step = gridDim.x * 8;
+  {
+    const int row = blockIdx.x * 8 + warp;
+    if (row < rows) {
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        Vec4<XT>::load(x + static_cast<int64_t>(row) * kCols + 4 * (lane + 32 * i), xn[i]);
+        Vec4<GT>::load(dy + static_cast<int64_t>(row) * kCols + 4 * (lane + 32 * i), dn[i]);
+      }
+      mu_n = kRms ? 0.0f : mean[row];
+      rs_n = rstd[row];
+    }
+  }
+  for (int row = blockIdx.x * 8 + warp; row < rows; row += row_step) {
+    const float mu = mu_n;
+    const float rs = rs_n;
     float xh[VPL][4], d[VPL][4];
     float s1 = 0.0f, s2 = 0.0f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
-      Vec4<XT>::load(xr + 4 * (lane + 32 * i), xh[i]);
-      Vec4<GT>::load(gr + 4 * (lane + 32 * i), d[i]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        xh[i][j] = xn[i][j];
+        d[i][j] = dn[i][j];
+      }
+    }
+    if (row + row_step < rows) {
+      const int64_t nrow = row + row_step;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        Vec4<XT>::load(x + nrow * kCols + 4 * (lane + 32 * i), xn[i]);
+        Vec4<GT>::load(dy + nrow * kCols + 4 * (lane + 32 * i), dn[i]);
+      }
+      mu_n = kRms ? 0.0f : mean[nrow];
+      rs_n = rstd[nrow];
     }
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {

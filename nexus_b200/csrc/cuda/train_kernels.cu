@@ -568,7 +568,19 @@ __global__ void colsum_partial_vec_kernel(const __nv_bfloat16* __restrict__ dy, 
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
   if (c0 < cols) {
-    for (int r = r_begin + threadIdx.y; r < r_end; r += 8) {
+    int r = r_begin + threadIdx.y;
+    // four rows per trip: their loads are all issued before the first sum (more bytes in flight per thread)
+    for (; r + 24 < r_end; r += 32) {
+      float v[4][8];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) RowVec<__nv_bfloat16>::load(dy + static_cast<int64_t>(r + 8 * u) * ld + c0, v[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += v[u][j];
+      }
+    }
+    for (; r < r_end; r += 8) {
       float v[8];
       RowVec<__nv_bfloat16>::load(dy + static_cast<int64_t>(r) * ld + c0, v);
 #pragma unroll

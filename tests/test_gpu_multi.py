@@ -17,3 +17,18 @@ def test_fused_comm_paths_two_gpus():
            "127.0.0.1", "--master-port", "29611", os.path.join(ROOT, "tests", "workers", "fused_comm_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=420, env=env)
     assert "WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("precision", ["bf16", "mxfp8"])
+def test_tensor_parallel_lm_two_gpus_matches_single_process_loss(precision):
+    """ParallelLm with tp = 2 on two GPUs (linears on the tcgen05 GEMMs, BF16 or block-scaled FP8): the first loss
+    equals the single-process model's on the same tokens, and training steps run."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29613", "-m", "nexus_b200.bench.parallel", "--model", "llama2-7b", "--layers", "1",
+           "--tp", "2", "--seq-len", "256", "--global-batch", "2", "--micro-batch", "1", "--precision", precision,
+           "--steps", "2", "--warmup", "1", "--check"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert r.returncode == 0 and '"check": "first loss"' in r.stdout and "tokens/s" in r.stdout, \
+        r.stdout[-3000:] + r.stderr[-3000:]
