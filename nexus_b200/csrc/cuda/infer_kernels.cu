@@ -104,39 +104,80 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, c
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
   const int32_t* bt = block_table + static_cast<int64_t>(seq) * max_blocks;
-  // the loop bound is warp-uniform: the shuffles below need every lane of the warp
-  for (int tb = t_begin + warp * TPW; tb < t_end; tb += 4 * TPW) {
-    const bool valid = tb + grp < t_end;
-    const int t = valid ? tb + grp : t_end - 1;
-    const int64_t slot = static_cast<int64_t>(bt[t / block_size]) * block_size + t % block_size;
-    const int64_t base = (slot * kv_heads + hk) * D + sub * 8;
-    float kv[8], vv[8];
-    if (KV == 0) {
-      unpack8(*reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(kc) + base), kv);
-      unpack8(*reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(vc) + base), vv);
-    } else {
-      const uint2 kq = *reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(kc) + base);
-      const uint2 vq = *reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(vc) + base);
-      const float ks = kscale[slot * kv_heads + hk], vs = vscale[slot * kv_heads + hk];
-      const uint8_t* kb = reinterpret_cast<const uint8_t*>(&kq);
-      const uint8_t* vb = reinterpret_cast<const uint8_t*>(&vq);
+  // The loop bound is warp-uniform: the shuffles below need every lane of the warp.  Each trip takes kU tokens per
+  // lane group: their block-table entries, then all their K and V loads, are issued before any arithmetic, so a lane
+  // keeps 2 * kU loads in flight (the kernel is bound by KV bytes), and the running maximum is updated once per trip.
+  constexpr int kU = 4;
+  for (int tb = t_begin + warp * TPW; tb < t_end; tb += 4 * TPW * kU) {
+    bool valid[kU];
+    int64_t slot[kU];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        kv[j] = (KV == 1 ? static_cast<float>(static_cast<int8_t>(kb[j])) : fp8_e4m3_to_float(kb[j])) * ks;
-        vv[j] = (KV == 1 ? static_cast<float>(static_cast<int8_t>(vb[j])) : fp8_e4m3_to_float(vb[j])) * vs;
+    for (int u = 0; u < kU; ++u) {
+      const int tt = tb + u * 4 * TPW + grp;
+      valid[u] = tt < t_end;
+      const int t = valid[u] ? tt : t_end - 1;
+      slot[u] = static_cast<int64_t>(bt[t / block_size]) * block_size + t % block_size;
+    }
+    uint4 kr[kU], vr[kU];     // BF16: 8 values; 8-bit kinds: the low 8 bytes are used
+    float ks[kU], vs[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int64_t base = (slot[u] * kv_heads + hk) * D + sub * 8;
+      if (KV == 0) {
+        kr[u] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(kc) + base);
+        vr[u] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(vc) + base);
+      } else {
+        const uint2 kq = *reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(kc) + base);
+        const uint2 vq = *reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(vc) + base);
+        kr[u] = make_uint4(kq.x, kq.y, 0u, 0u);
+        vr[u] = make_uint4(vq.x, vq.y, 0u, 0u);
+        ks[u] = kscale[slot[u] * kv_heads + hk];
+        vs[u] = vscale[slot[u] * kv_heads + hk];
       }
     }
-    float s = 0.0f;
+    float sc[kU];
+    float mn = m;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) s += qv[j] * kv[j];
+    for (int u = 0; u < kU; ++u) {
+      float kv[8];
+      if (KV == 0) {
+        unpack8(kr[u], kv);
+      } else {
+        const uint8_t* kb = reinterpret_cast<const uint8_t*>(&kr[u]);
 #pragma unroll
-    for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (!valid) continue;
-    const float mn = fmaxf(m, s);
-    const float alpha = exp2f(m - mn), p = exp2f(s - mn);
-    l = l * alpha + p;
+        for (int j = 0; j < 8; ++j)
+          kv[j] = (KV == 1 ? static_cast<float>(static_cast<int8_t>(kb[j])) : fp8_e4m3_to_float(kb[j])) * ks[u];
+      }
+      float t = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = acc[j] * alpha + p * vv[j];
+      for (int j = 0; j < 8; ++j) t += qv[j] * kv[j];
+#pragma unroll
+      for (int o = LPT / 2; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+      sc[u] = t;
+      if (valid[u]) mn = fmaxf(mn, t);
+    }
+    if (mn == -INFINITY) continue;  // nothing valid for this lane group yet
+    const float alpha = exp2f(m - mn);
+    l *= alpha;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] *= alpha;
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      if (!valid[u]) continue;
+      float vv[8];
+      if (KV == 0) {
+        unpack8(vr[u], vv);
+      } else {
+        const uint8_t* vb = reinterpret_cast<const uint8_t*>(&vr[u]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          vv[j] = (KV == 1 ? static_cast<float>(static_cast<int8_t>(vb[j])) : fp8_e4m3_to_float(vb[j])) * vs[u];
+      }
+      const float pw = exp2f(sc[u] - mn);
+      l += pw;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += pw * vv[j];
+    }
     m = mn;
   }
   // merge the token groups of the warp, then the warps of the block
