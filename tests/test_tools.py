@@ -130,3 +130,19 @@ def test_examples_run_on_cpu(tmp_path, script, args):
         import json
         rep = json.load(open(tmp_path / "r.json"))
         assert rep["params_counted"] == rep["params_formula"] and rep["mfu"] is None and rep["tokens_per_second"] > 0
+
+
+def test_parallel_bench_parameter_table_matches_the_model():
+    """`bench.parallel` draws random weights from a (name, shape) table instead of building the model: the table
+    must list exactly the parameters `lm.model.build` creates."""
+    from nexus_b200.bench.parallel import build_meta
+    from nexus_b200.lm.config import preset
+    from nexus_b200.lm.model import build
+    for name in ("llama2-7b", "gpt2-124m"):
+        cfg = preset(name)
+        cfg.n_layer, cfg.d_model, cfg.n_head, cfg.d_ff, cfg.vocab_size, cfg.max_position = 2, 64, 4, 128, 96, 32
+        if hasattr(cfg, "n_kv_head") and cfg.n_kv_head:
+            cfg.n_kv_head = 4
+        want = {n: tuple(p.shape) for n, p in build(cfg).named_parameters()}
+        got = dict(build_meta(cfg))
+        assert got == want
