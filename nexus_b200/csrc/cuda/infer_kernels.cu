@@ -88,7 +88,9 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, c
                     float* __restrict__ part_ml) {
   constexpr int LPT = D / 8;        // lanes per token
   constexpr int TPW = 32 / LPT;     // tokens per warp step
-  const int row = blockIdx.x, h = blockIdx.y, split = blockIdx.z;
+  // heads vary fastest over the grid: the blocks that run together read the adjacent head rows of the same cached
+  // tokens (one token's K or V row is [kv_heads][D] contiguous), which keeps their DRAM bursts in the same pages
+  const int h = blockIdx.x, row = blockIdx.y, split = blockIdx.z;
   const int hk = h / (heads / kv_heads);
   const int seq = row_seq[row];
   const int ctx = ctx_len[row];
@@ -647,7 +649,8 @@ extern "C" int nx_paged_attention_decode(const NxPagedArgs* a, nx_stream_t strea
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int splits = a->splits < 1 ? 1 : a->splits;
   if (splits > 1 && (a->part_o == nullptr || a->part_ml == nullptr)) return -1;
-  dim3 grid(a->rows, a->heads, splits);
+  if (a->rows > 65535) return -1;
+  dim3 grid(a->heads, a->rows, splits);
 #define NX_PD(D_, KV_)                                                                                              \
   paged_decode_kernel<D_, KV_><<<grid, 128, 0, st>>>((const __nv_bfloat16*)a->q, a->q_row_stride, a->k_cache, a->v_cache, \
       a->k_scale, a->v_scale, a->block_table, a->max_blocks, a->row_seq, a->ctx_len, a->block_size, a->heads,        \

@@ -246,7 +246,8 @@ def reference(x, router_w, up, down, spec: Spec):
 
 
 def quantize_experts(w: torch.Tensor, kind: str):
-    """Expert weight storage for inference: 'bf16' or 'fp8' (E4M3, one scale = amax/448 per expert).
+    """Expert weight storage for inference: 'bf16', 'fp8' (E4M3, one scale = amax/448 per expert) or 'mxfp8'
+    (E4M3 with one E8M0 scale per 32 elements along the contraction axis).
     Returns (stored, scales or None); ``dequantize_experts`` restores FP32."""
     if kind == "bf16":
         return w.to(torch.bfloat16), None
@@ -255,10 +256,21 @@ def quantize_experts(w: torch.Tensor, kind: str):
         scale = amax / 448.0
         q = (w / scale.view(-1, *([1] * (w.dim() - 1)))).to(torch.float8_e4m3fn)
         return q, scale
-    raise ValueError("quantize_experts: kind must be 'bf16' or 'fp8'")
+    if kind == "mxfp8":
+        # block-scaled: one power-of-two scale per 32 elements of each weight row (the contraction axis), stored per
+        # expert in the atom order the block-scaled tensor-core GEMM reads (ops._lowp.mx_gemm takes them as they are)
+        from ..ops import _lowp as L
+        pairs = [L.mx_quantize(w[e].reshape(-1, w.shape[-1]).contiguous()) for e in range(w.shape[0])]
+        q = torch.stack([c for c, _ in pairs]).view(w.shape)
+        return q, torch.stack([sc for _, sc in pairs])
+    raise ValueError("quantize_experts: kind must be 'bf16', 'fp8' or 'mxfp8'")
 
 
 def dequantize_experts(q: torch.Tensor, scale: Optional[torch.Tensor]) -> torch.Tensor:
+    if scale is not None and scale.dtype == torch.uint8:   # block-scaled storage
+        from ..ops import _lowp as L
+        rows = q[0].numel() // q.shape[-1]
+        return torch.stack([L.mx_dequantize(q[e].reshape(rows, q.shape[-1]), scale[e]) for e in range(q.shape[0])]).view(q.shape)
     w = q.float()
     return w if scale is None else w * scale.view(-1, *([1] * (w.dim() - 1)))
 

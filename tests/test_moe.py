@@ -51,3 +51,20 @@ def test_expert_quantisation():
     assert (dequantize_experts(q, sc) - w).abs().max() < 0.07 * w.abs().max()
     q, sc = quantize_experts(w, "bf16")
     assert sc is None and (q.float() - w).abs().max() < 0.01 * w.abs().max()
+
+
+def test_block_scaled_expert_storage_round_trip():
+    """'mxfp8' expert storage: E4M3 codes with a power-of-two scale per 32 elements of each row; a column range that a
+    per-expert scale would flush to zero survives."""
+    from nexus_b200.moe.moe import dequantize_experts, quantize_experts
+    torch.manual_seed(0)
+    w = torch.randn(3, 40, 64) * 0.02
+    w[:, :, :32] *= 1e-6                                   # tiny columns next to ordinary ones
+    q, s = quantize_experts(w, "mxfp8")
+    assert q.dtype == torch.float8_e4m3fn and s.dtype == torch.uint8 and s.shape[0] == 3
+    back = dequantize_experts(q, s)
+    small = (back[:, :, :32] - w[:, :, :32]).norm() / w[:, :, :32].norm()
+    assert small < 0.05
+    q1, s1 = quantize_experts(w, "fp8")
+    coarse = (dequantize_experts(q1, s1)[:, :, :32] - w[:, :, :32]).norm() / w[:, :, :32].norm()
+    assert coarse > 0.5                                    # per-expert scaling loses those columns
