@@ -469,6 +469,10 @@ def adamw_multi_tensor(params: Sequence[torch.Tensor], grads: Sequence[torch.Ten
     inv2 = np.float32(1.0 / (1.0 - beta2 ** step))
     b1, b2 = np.float32(beta1), np.float32(beta2)
     omb1, omb2 = np.float32(1.0) - b1, np.float32(1.0) - b2
+    import sys
+    lowp = sys.modules.get("nexus_b200.ops._lowp")
+    if lowp is not None:
+        lowp.mx_weight_cache.invalidate()   # block-scaled copies of the weights are stale after this update
     with torch.no_grad():
         for i, (p, g, mi, vi) in enumerate(zip(params, grads, m, v)):
             lr_i = np.float32(lr) * np.float32(1.0 if lr_scales is None else lr_scales[i])

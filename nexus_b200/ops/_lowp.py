@@ -209,6 +209,44 @@ def mx_gemm(a: torch.Tensor, sfa: torch.Tensor, b: torch.Tensor, sfb: torch.Tens
     return (out, out_scales) if out_scales is not None else out
 
 
+class _MxWeightCache:
+    """Block-scaled forms of a weight (as stored, and transposed) keyed by the tensor and its version counter: between
+    two optimizer steps the micro-batches of an accumulation step quantise each weight once per form.  Entries die
+    with their tensor."""
+
+    def __init__(self):
+        self._store = {}
+        self.hits = self.misses = 0
+        # Off by default: an update made through ``w.data`` (or any alias with its own version counter) does not bump
+        # ``w._version``.  Turn it on when weights change only through the tensor itself (torch.optim does) or when
+        # the training loop calls ``invalidate()`` after each optimizer step (`fused.ops.adamw_multi_tensor` does).
+        self.enabled = False
+
+    def invalidate(self) -> None:
+        self._store.clear()
+
+    def get(self, w: torch.Tensor, transpose: bool):
+        import weakref
+        if not self.enabled:
+            return mx_quantize(w.detach(), transpose=transpose)
+        key = (id(w), transpose)
+        ent = self._store.get(key)
+        if ent is not None and ent[0]() is w and ent[1] == w._version and ent[2] == w.data_ptr():
+            self.hits += 1
+            return ent[3]
+        self.misses += 1
+        val = mx_quantize(w.detach(), transpose=transpose)
+        try:
+            ref = weakref.ref(w, lambda _r, k=key: self._store.pop(k, None))
+        except TypeError:
+            return val
+        self._store[key] = (ref, w._version, w.data_ptr(), val)
+        return val
+
+
+mx_weight_cache = _MxWeightCache()
+
+
 class _MxLinearFn(torch.autograd.Function):
     """y = x W^T (+ b) with all three GEMMs of the layer on the block-scaled FP8 path: forward and input gradient use
     E4M3 activations / weights (E5M2 for dy), the weight gradient contracts over the tokens, so dy and x are
@@ -218,7 +256,7 @@ class _MxLinearFn(torch.autograd.Function):
     def forward(ctx, x, w, bias):
         x2 = x.reshape(-1, x.shape[-1])
         xq, xs = mx_quantize(x2)
-        wq, ws = mx_quantize(w)
+        wq, ws = mx_weight_cache.get(w, False)
         y = mx_gemm(xq, xs, wq, ws, bias=bias, out_dtype=x.dtype if x.dtype != torch.float32 else torch.float32)
         ctx.save_for_backward(x2, w)
         ctx.has_bias = bias is not None
@@ -230,7 +268,7 @@ class _MxLinearFn(torch.autograd.Function):
         x2, w = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
         gq, gs = mx_quantize(dy2, torch.float8_e5m2)                    # [M, N], blocks along N
-        wtq, wts = mx_quantize(w, transpose=True)                       # [K, N], blocks along N
+        wtq, wts = mx_weight_cache.get(w, True)                         # [K, N], blocks along N
         dx = mx_gemm(gq, gs, wtq, wts, out_dtype=x2.dtype)              # [M, K]
         gtq, gts = mx_quantize(dy2, torch.float8_e5m2, transpose=True)  # [N, M], blocks along M
         xtq, xts = mx_quantize(x2, transpose=True)                      # [K, M], blocks along M

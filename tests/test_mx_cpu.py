@@ -62,3 +62,26 @@ def test_language_model_under_mxfp8_linear_precision():
     assert grads and all(torch.isfinite(g).all() for g in grads)
     model.zero_grad()
     native.backward()
+
+
+def test_weight_forms_are_quantised_once_per_version():
+    torch.manual_seed(2)
+    w = torch.randn(32, 64, requires_grad=True)
+    x = torch.randn(8, 64)
+    L.mx_weight_cache.enabled = True
+    h0, m0 = L.mx_weight_cache.hits, L.mx_weight_cache.misses
+    for _ in range(3):                                       # three micro-batches between two optimizer steps
+        L.mx_linear(x.clone().requires_grad_(), w).sum().backward()
+    assert L.mx_weight_cache.misses - m0 == 2               # the stored form and the transposed form
+    assert L.mx_weight_cache.hits - h0 == 4
+    with torch.no_grad():
+        w.mul_(0.5)                                          # the optimizer step bumps the version
+    y = L.mx_linear(x, w)
+    assert L.mx_weight_cache.misses - m0 == 3
+    assert (y - x @ w.t()).norm() / (x @ w.t()).norm() < 0.06
+    w.data.mul_(2.0)                                         # invisible to the version counter: needs invalidate()
+    L.mx_weight_cache.invalidate()
+    y = L.mx_linear(x, w)
+    assert (y - x @ w.t()).norm() / (x @ w.t()).norm() < 0.06
+    L.mx_weight_cache.enabled = False
+    L.mx_weight_cache.invalidate()
