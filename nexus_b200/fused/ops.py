@@ -140,6 +140,43 @@ def fused_linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = N
     return _act_fwd(F.linear(x, w, b), act)
 
 
+# ------------------------------------------------------------------------------- gated activations
+class _GatedActivation(torch.autograd.Function):
+    """y = act(h[:, :F]) * h[:, F:] for h = [gate | up] (SwiGLU / GeGLU): one kernel forward, one backward."""
+
+    @staticmethod
+    def forward(ctx, h, kind):
+        from ..ops import _infer as I
+        h2 = h.reshape(-1, h.shape[-1])
+        if not h2.is_contiguous():
+            h2 = h2.contiguous()
+        ctx.save_for_backward(h2)
+        ctx.kind, ctx.shape = kind, h.shape
+        return I.gated_fwd(h2, "silu" if kind == "swiglu" else "gelu").view(*h.shape[:-1], h.shape[-1] // 2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import _infer as I
+        (h2,) = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        return I.gated_bwd(h2, dy2, "silu" if ctx.kind == "swiglu" else "gelu").view(ctx.shape), None
+
+
+def gated_activation(h: torch.Tensor, kind: str = "swiglu") -> torch.Tensor:
+    """``silu(gate) * up`` (``kind="swiglu"``) or ``gelu_tanh(gate) * up`` (``"geglu"``) of ``h = [gate | up]`` along
+    the last axis.  BF16 tensors on a GPU run the fused kernels; everything else the FP32 formula."""
+    if kind not in ("swiglu", "geglu"):
+        raise ValueError("gated_activation: kind must be 'swiglu' or 'geglu'")
+    if _use_kernels(h) and h.dtype == torch.bfloat16 and h.shape[-1] % 2 == 0:
+        return _GatedActivation.apply(h, kind)
+    Fd = h.shape[-1] // 2
+    a, b = h[..., :Fd], h[..., Fd:]
+    g = F.silu(a.float()) if kind == "swiglu" else gelu_tanh(a.float())
+    return (g * b.float()).to(h.dtype)
+
+
 # -------------------------------------------------------------------------------------------- norms
 class _FusedNorm(torch.autograd.Function):
     @staticmethod

@@ -106,10 +106,7 @@ class Mlp(nn.Module):
     def forward(self, x):
         if self.kind == "gelu":
             return self.down(self.up(x, "gelu"))
-        h = self.up(x)
-        a, b = h[..., : self.F], h[..., self.F:]
-        g = torch.nn.functional.silu(a.float()) if self.kind == "swiglu" else F_.gelu_tanh(a.float())
-        return self.down((g * b.float()).to(x.dtype))
+        return self.down(F_.gated_activation(self.up(x), "swiglu" if self.kind == "swiglu" else "geglu"))
 
 
 class Block(nn.Module):

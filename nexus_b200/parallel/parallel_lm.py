@@ -344,9 +344,7 @@ class ParallelLm:
         if mc.mlp == "gelu":
             act = F_.gelu_tanh(u)
         else:
-            Fl = u.shape[-1] // 2
-            gate = F.silu(u[..., :Fl]) if mc.mlp == "swiglu" else F_.gelu_tanh(u[..., :Fl])
-            act = gate * u[..., Fl:]
+            act = F_.gated_activation(u, "swiglu" if mc.mlp == "swiglu" else "geglu")
         return x + self._row_linear(act, self.params[p + "mlp.down.weight"], self.params.get(p + "mlp.down.bias"))
 
     def _embed(self, tokens, positions):

@@ -146,3 +146,19 @@ def test_colsum_and_nonfinite():
     dy = torch.randn(777, 300, device=DEV)
     assert close(K.colsum(dy), dy.sum(0), 1e-5)
     assert K.count_nonfinite(torch.tensor([1.0, float("nan"), float("inf")], device=DEV)).item() == 2
+
+
+@pytest.mark.parametrize("kind", ["swiglu", "geglu"])
+def test_gated_activation_autograd_matches_fp32_formula(kind):
+    from nexus_b200.fused import ops as F_
+    torch.manual_seed(11)
+    h = torch.randn(3, 70, 2 * 96, device="cuda").bfloat16().requires_grad_()
+    t = torch.randn(3, 70, 96, device="cuda")
+    y = F_.gated_activation(h, kind)
+    (y.float() * t).sum().backward()
+    h2 = h.detach().float().requires_grad_()
+    a, b = h2[..., :96], h2[..., 96:]
+    ref = (torch.nn.functional.silu(a) if kind == "swiglu" else torch.nn.functional.gelu(a, approximate="tanh")) * b
+    (ref * t).sum().backward()
+    assert (y.float() - ref).abs().max() < 2e-2 * ref.abs().max()
+    assert (h.grad.float() - h2.grad).abs().max() < 2e-2 * h2.grad.abs().max()
