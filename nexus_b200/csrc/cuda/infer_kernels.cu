@@ -106,17 +106,6 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, c
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
   const int32_t* bt = block_table + static_cast<int64_t>(seq) * max_blocks;
-  // The block-table entries of this block's token range go to shared memory once, so that the address of a K / V row
-  // does not wait on a global load in every trip (ranges of more than kBtSmem pages keep reading the table in place).
-  constexpr int kBtSmem = 512;
-  __shared__ int32_t s_bt[kBtSmem];
-  const int pg_first = t_begin / block_size;
-  const int pg_count = t_end > t_begin ? (t_end - 1) / block_size - pg_first + 1 : 0;
-  const bool bt_smem = pg_count <= kBtSmem;
-  if (bt_smem) {
-    for (int i = threadIdx.x; i < pg_count; i += 128) s_bt[i] = bt[pg_first + i];
-    __syncthreads();
-  }
   // The loop bound is warp-uniform: the shuffles below need every lane of the warp.  Each trip takes kU tokens per
   // lane group: their block-table entries, then all their K and V loads, are issued before any arithmetic, so a lane
   // keeps 2 * kU loads in flight (the kernel is bound by KV bytes), and the running maximum is updated once per trip.
@@ -129,8 +118,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, c
       const int tt = tb + u * 4 * TPW + grp;
       valid[u] = tt < t_end;
       const int t = valid[u] ? tt : t_end - 1;
-      const int pg = t / block_size;
-      slot[u] = static_cast<int64_t>(bt_smem ? s_bt[pg - pg_first] : bt[pg]) * block_size + t % block_size;
+      slot[u] = static_cast<int64_t>(bt[t / block_size]) * block_size + t % block_size;
     }
     uint4 kr[kU], vr[kU];     // BF16: 8 values; 8-bit kinds: the low 8 bytes are used
     float ks[kU], vs[kU];
