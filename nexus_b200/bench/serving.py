@@ -32,6 +32,7 @@ def main(argv=None) -> int:
     ap.add_argument("--kv", default="bf16", help="KV cache: bf16 | int8 | fp8")
     ap.add_argument("--batch-tokens", type=int, default=8192)
     ap.add_argument("--kv-gb", type=float, default=0.0, help="KV pool per GPU in GiB (0: sized for the workload)")
+    ap.add_argument("--tp-graphs", type=int, default=0, help="1: capture the decode steps of a tensor-parallel engine too")
     args = ap.parse_args(argv)
 
     from ..infer import Engine, EngineConfig, Gpt2Weights, QuantOptions, SamplingParams
@@ -62,7 +63,8 @@ def main(argv=None) -> int:
     kv_bytes = int(args.kv_gb * 2 ** 30) if args.kv_gb > 0 else int(kv_need * 1.15) + (1 << 28)
     eng = Engine(w, EngineConfig(device=dev, precision="bf16" if cuda else "fp32", max_seqs=args.requests,
                                  max_tokens=args.batch_tokens, block_size=16, kv_bytes=kv_bytes,
-                                 quant=QuantOptions(weights=args.quant, kv=args.kv)), group=group)
+                                 quant=QuantOptions(weights=args.quant, kv=args.kv), tp_graphs=bool(args.tp_graphs)),
+                 group=group)
     greedy = SamplingParams(temperature=0.0)
 
     def serve(reqs, new):
@@ -93,9 +95,17 @@ def main(argv=None) -> int:
             "mean_ttft_ms": m.mean_ttft_ms(), "mean_tpot_ms": m.mean_tpot_ms(), "preemptions": m.preemptions,
             "config": {"model": args.model, "tp": world, "requests": args.requests, "prompt_len": [args.prompt_min, args.prompt_max],
                        "max_new": args.max_new, "page_size": 16, "weights": args.quant, "kv": args.kv,
-                       "kv_pool_gib": round(kv_bytes / 2 ** 30, 1), "batch_tokens": args.batch_tokens},
+                       "kv_pool_gib": round(kv_bytes / 2 ** 30, 1), "batch_tokens": args.batch_tokens,
+                       "tp_graphs": bool(args.tp_graphs)},
             "data": "random prompts from seed 0, random-init weights"}), flush=True)
     if group is not None:
+        if args.tp_graphs:
+            # graphs that captured collectives go first; the process then leaves without tearing the communicator down
+            eng.release_graphs()
+            group.barrier()
+            torch.cuda.synchronize()
+            sys.stdout.flush()
+            os._exit(0)
         group.destroy()
     return 0
 

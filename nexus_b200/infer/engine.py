@@ -131,6 +131,8 @@ class EngineConfig:
     quant: QuantOptions = field(default_factory=QuantOptions)
     device: str = "cuda"
     decode_splits: int = 0       # 0: chosen per step from the batch size and context length
+    tp_graphs: bool = False      # decode CUDA graphs of a tensor-parallel engine (its NCCL all-reduces are captured too);
+                                 # call Engine.release_graphs() before the process group is destroyed
 
 
 @dataclass
@@ -586,7 +588,9 @@ class Engine:
             raise ValueError(f"{N} tokens exceed max_tokens {cfg.max_tokens}")
         self._skinny = 16
         decode_only = all(k == "paged" for k, *_ in runs) and N == len(logit_rows) == stats.decode_tokens
-        use_graph = self.fast and cfg.cuda_graphs and decode_only and nl == self.L and self.tp == 1
+        # tensor-parallel ranks run the same schedule, so with tp_graphs every rank captures and replays the same buckets
+        # in the same order, the all-reduces of the layer loop captured with the kernels around them
+        use_graph = self.fast and cfg.cuda_graphs and decode_only and nl == self.L and (self.tp == 1 or cfg.tp_graphs)
         R = len(logit_rows)
         bucket = 1 << (N - 1).bit_length() if use_graph else N
         # one staging buffer in pinned memory, reused every step, and ONE host-to-device copy for all index arrays
@@ -767,6 +771,17 @@ class Engine:
         st["ints"].copy_(ints, non_blocking=True)
         self._graphs[bucket].replay()
         return st["logits"]
+
+    def release_graphs(self) -> None:
+        """Drops every captured decode graph and its static buffers.  A tensor-parallel engine must do this before its
+        process group is destroyed: tearing the communicator down while graphs that captured its collectives are alive
+        did not return."""
+        if self.dev.type == "cuda":
+            torch.cuda.synchronize()
+        self._graphs.clear()
+        self._static.clear()
+        if self.dev.type == "cuda":
+            torch.cuda.synchronize()
 
     # ----------------------------------------------------------------------------- outputs
     def logit_rows(self) -> int:
