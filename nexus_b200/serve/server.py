@@ -127,15 +127,17 @@ class Server:
             # 1. every running request needs room for one more token: preempt the newest while short
             def decode_need() -> int:
                 return sum(eng.blocks_needed(r.seq, 1) for r in self.running)
-            while self.running and decode_need() > eng.free_blocks():
+            need = decode_need()                     # walked once per step unless something is preempted
+            while self.running and need > eng.free_blocks():
                 victim = self.running.pop()          # newest admitted
                 eng.free_sequence(victim.seq)
                 victim.seq = -1
                 victim.preemptions += 1
                 self.metrics.preemptions += 1
                 self.waiting.appendleft(victim)      # re-prefills prompt + generated tokens later
+                need = decode_need()
             budget = cfg.max_batch_tokens - len(self.running)
-            free = eng.free_blocks() - decode_need()
+            free = eng.free_blocks() - need
             admitted: List[_Live] = []
             bs = eng.block_size()
             # 2. admission in arrival order (no overtaking: keeps latency fair)
