@@ -5,8 +5,8 @@ random-init weights.  Weak scaling: per-GPU work is fixed; N > 1 shards optimize
 gradients over the data-parallel group (launched by torch.distributed.run, one rank per GPU).
 
   python bench.py --gpus N --steps K --warmup W          our implementation
-  python bench.py --impl reference ...                   the unmodified reference (unavailable: it
-                                                         cannot be built offline)
+  python bench.py --impl reference ...                   the unmodified reference's own single-GPU trainer,
+                                                         built by baseline/build_ref.py (1 GPU only)
 
 Prints ONE JSON line on rank 0.  `value` is the device-timed (CUDA events, max over ranks)
 throughput of K optimizer steps with inputs resident on the device; `e2e` is the same metric through
@@ -127,11 +127,81 @@ class ClockSampler:
 
 
 def run_reference(args) -> int:
+    """The unmodified reference on the same metric and config: its `cuda::GptModel` + `cuda::GptTrainer`
+    (cuBLASLt GEMMs, its own FlashAttention-2, fused CE and foreach AdamW kernels) compiled from its sources by
+    `baseline/build_ref.py` into `baseline/_ref/lib/libnexus_ref_gpt.so`.  Nothing of nexus_b200 is imported on
+    this path.  The reference has no multi-GPU training path that builds offline (its GPU data-parallel backend
+    sits behind `LanguageModelTrainer`, whose sources include the empty `NexusOptim` / `NexusData` submodules), so
+    N > 1 reports `unavailable`."""
+    import ctypes
+
+    def unavailable(why: str) -> int:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 or world > 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            return unavailable("the reference's only multi-GPU training path (cuda::gpt_backend data parallel inside "
+                               "LanguageModelTrainer) does not compile offline: src/train/lm_trainer.cpp includes "
+                               "headers of the empty NexusOptim / NexusData submodules; single-GPU arm only")
+        return 0
+    here = os.path.dirname(os.path.abspath(__file__))
+    lib_path = os.path.join(here, "baseline", "_ref", "lib", "libnexus_ref_gpt.so")
+    if not os.path.exists(lib_path):
+        try:
+            sys.path.insert(0, os.path.join(here, "baseline"))
+            import build_ref
+            build_ref.build(verbose=False)
+        except Exception as e:  # no reference sources or no compiler on this machine
+            return unavailable(("reference library not built and cannot be built here: %s" % e).splitlines()[0][:300])
+    try:
+        lib = ctypes.CDLL(lib_path)
+    except OSError as e:
+        return unavailable(("cannot load %s: %s" % (lib_path, e))[:300])
+    lib.nexus_ref_gpt_error.restype = ctypes.c_char_p
+    rc = lib.nexus_ref_gpt_open(args.seqs, args.seq_len, 1, 0)
+    if rc != 0:
+        return unavailable("reference GptModel construction failed (rc %d): %s" % (rc, lib.nexus_ref_gpt_error().decode()))
+    warm = max(args.warmup, 3)
+    ms, loss = ctypes.c_double(0.0), ctypes.c_float(0.0)
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
+    rc = lib.nexus_ref_gpt_device(args.steps, warm, ctypes.byref(ms), ctypes.byref(loss))
+    clocks = sampler.stop()
+    if rc != 0:
+        return unavailable("reference device-timed run failed (rc %d): %s" % (rc, lib.nexus_ref_gpt_error().decode()))
+    e2e = None
+    if not args.skip_e2e:
+        ems, eloss = ctypes.c_double(0.0), ctypes.c_float(0.0)
+        rc = lib.nexus_ref_gpt_e2e(args.steps, warm, ctypes.byref(ems), ctypes.byref(eloss))
+        if rc == 0:
+            e2e = {"value": args.seqs * args.seq_len / (ems.value * 1e-3), "unit": "tokens/s",
+                   "h2d_bytes_per_step": args.seqs * args.seq_len * 4, "d2h_bytes_per_step": 4,
+                   "final_loss": eloss.value}
+    buf = ctypes.create_string_buffer(2048)
+    lib.nexus_ref_gpt_info(buf, 2048)
+    try:
+        info = json.loads(buf.value.decode())
+    except Exception:
+        info = {}
+    lib.nexus_ref_gpt_close()
+    value = args.seqs * args.seq_len / (ms.value * 1e-3)
     print(json.dumps({
+        "metric": "train tokens/s GPT-2 124M bf16 (FSDP-sharded optimizer when N>1)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warm,
+        "ms_per_step": ms.value, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": value / BASELINE_TOK_S, "dtype": "bf16", "data": "synthetic uniform tokens, random-init weights",
         "impl": "reference",
-        "unavailable": "reference cannot be installed offline: pip finds no setup.py/pyproject.toml at its root, "
-                       "and its python/ sub-project's CMake build stops at five empty git submodules "
-                       "(lib/MatrixFlash-Pro, NexusOptim, NexusModel, NexusLoss, NexusData)"}))
+        "config": {"model": args.model, "global_batch": args.seqs, "seq_len": args.seq_len, "parallelism": "single",
+                   "l2": "working set per step exceeds the 126 MB L2; no explicit flush",
+                   "reference_path": "cuda::GptModel::forward_backward + optimizer_step; e2e: cuda::GptTrainer::step",
+                   "reference_options": "BF16 autocast, FP32 master, flash attention, no recompute, vocab padded to 64, "
+                                        "fused CE cast, fast CE (its compile-mode settings)",
+                   "final_loss": loss.value, **info},
+        "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"]},
+        "e2e": e2e,
+    }))
     return 0
 
 

@@ -94,7 +94,8 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
 
 
 def build_gemm_profile(verbose: bool = False) -> Path:
-    """Instrumented GEMM library (`-DNX_PROFILE_MMA`) for `python -m nexus_b200.bench.mma_profile`."""
+    """Instrumented GEMM library (`-DNX_PROFILE_MMA`), built on demand by `python -m nexus_b200.bench.mma_profile`;
+    not part of `build_all` and never loaded by the framework itself."""
     out = CUDA_LIB.parent / "libnexus_b200_gemm_prof.so"
     src = CSRC / "cuda" / "gemm_sm100.cu"
     if not out.exists() or out.stat().st_mtime < max(src.stat().st_mtime, _newest_header([CSRC / "cuda"])):
@@ -146,7 +147,7 @@ def build_tools(force: bool = False, verbose: bool = False):
 
 
 def build_all(force: bool = False, verbose: bool = False):
-    return build_cuda(force, verbose), build_host(force, verbose), build_tools(force, verbose), build_gemm_profile(verbose)
+    return build_cuda(force, verbose), build_host(force, verbose), build_tools(force, verbose)
 
 
 if __name__ == "__main__":

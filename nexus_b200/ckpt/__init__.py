@@ -1,1 +1,2 @@
-from .checkpoint import CheckpointError, CheckpointManager, CheckpointOptions, LoadedCheckpoint  # noqa: F401
+from .checkpoint import (CheckpointError, CheckpointManager, CheckpointOptions, LoadedCheckpoint,  # noqa: F401
+                         TrainerState, trailer_hex)

@@ -58,8 +58,17 @@ __device__ __forceinline__ bool signal_and_wait(const NxPeerTable& flags, int ra
   return ok;
 }
 
-__global__ void barrier_kernel(NxPeerTable flags, int rank, int n, int epoch, int* status) {
+// The barrier generation lives in device memory (`counter`, one int per rank, advanced in lockstep by every
+// barrier-bearing kernel of the group), not in a kernel argument: a CUDA graph that captured such a kernel
+// waits for a fresh generation on every replay.
+__device__ __forceinline__ int next_epoch(const int* counter) { return *reinterpret_cast<const volatile int*>(counter) + 1; }
+
+__global__ void barrier_kernel(NxPeerTable flags, int rank, int n, int* counter, int* status) {
+  const int epoch = next_epoch(counter);
+  __syncwarp();
   signal_and_wait(flags, rank, n, epoch, status);
+  __syncwarp();
+  if (threadIdx.x == 0) *counter = epoch;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -103,9 +112,10 @@ reduce_shard_kernel(NxPeerTable grads, int n, int64_t shard_off, int64_t count, 
 
 // One block.  Local square sum -> every peer's slot -> wait for all -> global norm -> optimizer state.
 __global__ void norm_exchange_kernel(const double* __restrict__ partial, int nparts, NxPeerTable slots,
-                                     NxPeerTable flags, int rank, int n, int epoch, NxOptState* st, int* status) {
+                                     NxPeerTable flags, int rank, int n, int* counter, NxOptState* st, int* status) {
   __shared__ double s_scratch[32];
   __shared__ int s_ok;
+  const int epoch = next_epoch(counter);
   double acc = 0.0;
   for (int i = threadIdx.x; i < nparts; i += blockDim.x) acc += partial[i];
   acc = block_sum<double>(acc, s_scratch);
@@ -119,6 +129,7 @@ __global__ void norm_exchange_kernel(const double* __restrict__ partial, int npa
   if (!ok) s_ok = 0;
   __syncthreads();
   if (threadIdx.x != 0) return;
+  *counter = epoch;
   if (!s_ok) {
     st->found_inf = 1;  // no update on a step whose exchange failed
     return;
@@ -350,8 +361,9 @@ __global__ void moe_combine_kernel(NxPeerTable bufs, const int32_t* __restrict__
 // Every rank publishes its rows into every peer's table, waits, then merges in rank order:
 //   gmax = max_q max_q;  sumexp = sum_q se_q * exp(max_q - gmax);  tlogit = sum_q t_q.
 __global__ void vocab_ce_exchange_kernel(const float* __restrict__ local_stats, NxPeerTable tables, NxPeerTable flags,
-                                         int rank, int n, int rows, int epoch, float* __restrict__ merged, int* status) {
+                                         int rank, int n, int rows, int* counter, float* __restrict__ merged, int* status) {
   __shared__ int s_ok;
+  const int epoch = next_epoch(counter);
   for (int i = threadIdx.x; i < rows * 3; i += blockDim.x) {
     const float v = local_stats[i];
     for (int q = 0; q < n; ++q) reinterpret_cast<float*>(tables.ptr[q])[static_cast<int64_t>(rank) * rows * 3 + i] = v;
@@ -361,6 +373,7 @@ __global__ void vocab_ce_exchange_kernel(const float* __restrict__ local_stats, 
   const bool ok = signal_and_wait(flags, rank, n, epoch, status);
   if (!ok) s_ok = 0;
   __syncthreads();
+  if (threadIdx.x == 0) *counter = epoch;
   if (!s_ok) return;
   const volatile float* mine = reinterpret_cast<const volatile float*>(tables.ptr[rank]);
   for (int r = threadIdx.x; r < rows; r += blockDim.x) {
@@ -381,9 +394,10 @@ __global__ void vocab_ce_exchange_kernel(const float* __restrict__ local_stats, 
 }  // namespace
 
 // ================================================================================================
-extern "C" int nx_comm_barrier(const NxPeerTable* flags, int rank, int n, int epoch, int* status, nx_stream_t stream) {
-  if (flags == nullptr || n < 1 || n > NX_MAX_PEERS || rank < 0 || rank >= n || status == nullptr) return -1;
-  barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(*flags, rank, n, epoch, status);
+extern "C" int nx_comm_barrier(const NxPeerTable* flags, int rank, int n, int* counter, int* status, nx_stream_t stream) {
+  if (flags == nullptr || n < 1 || n > NX_MAX_PEERS || rank < 0 || rank >= n || status == nullptr || counter == nullptr)
+    return -1;
+  barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(*flags, rank, n, counter, status);
   return launch_status();
 }
 
@@ -399,10 +413,10 @@ extern "C" int nx_comm_reduce_shard(const NxPeerTable* grads, int n, int64_t sha
 }
 
 extern "C" int nx_comm_norm_exchange(const double* partial, int nparts, const NxPeerTable* slots,
-                                     const NxPeerTable* flags, int rank, int n, int epoch, NxOptState* state,
+                                     const NxPeerTable* flags, int rank, int n, int* counter, NxOptState* state,
                                      int* status, nx_stream_t stream) {
   if (slots == nullptr || flags == nullptr || n < 1 || n > NX_MAX_PEERS || status == nullptr) return -1;
-  norm_exchange_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(partial, nparts, *slots, *flags, rank, n, epoch,
+  norm_exchange_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(partial, nparts, *slots, *flags, rank, n, counter,
                                                                          state, status);
   return launch_status();
 }
@@ -470,10 +484,10 @@ extern "C" int nx_moe_combine(const NxPeerTable* bufs, const int32_t* expert, co
 }
 
 extern "C" int nx_vocab_ce_exchange(const float* local_stats, const NxPeerTable* tables, const NxPeerTable* flags,
-                                    int rank, int n, int rows, int epoch, float* merged, int* status,
+                                    int rank, int n, int rows, int* counter, float* merged, int* status,
                                     nx_stream_t stream) {
-  if (tables == nullptr || flags == nullptr || n < 1 || n > NX_MAX_PEERS || rows <= 0) return -1;
+  if (tables == nullptr || flags == nullptr || counter == nullptr || n < 1 || n > NX_MAX_PEERS || rows <= 0) return -1;
   vocab_ce_exchange_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(local_stats, *tables, *flags, rank, n,
-                                                                              rows, epoch, merged, status);
+                                                                              rows, counter, merged, status);
   return launch_status();
 }

@@ -15,8 +15,12 @@ typedef struct NxPeerTable {
   void* ptr[NX_MAX_PEERS];
 } NxPeerTable;
 
-// flags: per rank an int[n] array (zero-initialised); `epoch` must grow by one per call on every rank.
-int nx_comm_barrier(const NxPeerTable* flags, int rank, int n, int epoch, int* status, nx_stream_t stream);
+// flags: per rank an int[n] array (zero-initialised).  `counter`: this rank's barrier generation, one int in
+// device memory, zero-initialised; every barrier-bearing call (this one, nx_comm_norm_exchange,
+// nx_vocab_ce_exchange) waits for generation *counter + 1 and then stores it, so all ranks must issue the same
+// sequence of such calls.  Because the generation is read on the device, these kernels stay correct when a
+// captured CUDA graph replays them.
+int nx_comm_barrier(const NxPeerTable* flags, int rank, int n, int* counter, int* status, nx_stream_t stream);
 
 // out[i] = scale * sum_p grads[p][shard_off + i] (p = 0..n-1 in order), i < count; partial[] receives
 // per-block FP64 square sums (nx_comm_reduce_partials(count) entries).  shard_off % 4 == 0.
@@ -26,7 +30,7 @@ int nx_comm_reduce_shard(const NxPeerTable* grads, int n, int64_t shard_off, int
 // slots: per rank a double[n] array.  Publishes this rank's square sum to every rank, waits for all,
 // then fills grad_norm / clip_coef / found_inf / step / bias corrections of `state`.
 int nx_comm_norm_exchange(const double* partial, int nparts, const NxPeerTable* slots, const NxPeerTable* flags,
-                          int rank, int n, int epoch, NxOptState* state, int* status, nx_stream_t stream);
+                          int rank, int n, int* counter, NxOptState* state, int* status, nx_stream_t stream);
 // AdamW on shard-local FP32 state; chunks carry GLOBAL offsets inside [shard_off, shard_off + shard);
 // the BF16 weights are written into every rank's full shadow buffer (the all-gather).  fp32_tails
 // (optional): per rank an FP32 buffer holding the parameters at global offsets >= tail_off, which
@@ -57,7 +61,7 @@ int nx_moe_combine(const NxPeerTable* bufs, const int32_t* expert, const int32_t
 
 // Vocabulary-parallel CE: local_stats [rows][3]; tables[q]: float[n][rows][3]; merged [rows][3].
 int nx_vocab_ce_exchange(const float* local_stats, const NxPeerTable* tables, const NxPeerTable* flags, int rank, int n,
-                         int rows, int epoch, float* merged, int* status, nx_stream_t stream);
+                         int rows, int* counter, float* merged, int* status, nx_stream_t stream);
 
 // Distributed GEMM (see nx_gemm): operand A and/or B is row-sharded over the ranks and its tiles are
 // fetched by (non-multicast) TMA straight from the owning rank's memory; the output can be

@@ -70,7 +70,8 @@ class SymmetricWorkspace:
             symm_mem.enable_symm_mem_for_group(self.group.group_name)
         except Exception:
             pass
-        self.epoch = 0
+        # barrier generation, advanced on the device by every barrier-bearing kernel (graph-replay safe)
+        self.counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.flags = self.alloc(MAX_PEERS, torch.int32)
         self.flags.local.zero_()
         self.slots = self.alloc(MAX_PEERS, torch.float64)
@@ -86,9 +87,8 @@ class SymmetricWorkspace:
 
     def barrier(self) -> None:
         """Device-side barrier over the group on the current stream (bounded wait)."""
-        self.epoch += 1
         K._check(K.lib().nx_comm_barrier(C.byref(self.flags.table), C.c_int(self.rank), C.c_int(self.n),
-                                         C.c_int(self.epoch), K._p(K.status_word(self.device)), K._stream()),
+                                         K._p(self.counter), K._p(K.status_word(self.device)), K._stream()),
                  "nx_comm_barrier")
 
 
@@ -150,10 +150,9 @@ class FusedShardedOptimizer:
             K._check(L.nx_comm_reduce_shard(C.byref(self.grads.table), C.c_int(n), C.c_int64(self.off),
                                             C.c_int64(self.count), C.c_float(1.0), K._p(self.gshard),
                                             K._p(self.partials), st), "nx_comm_reduce_shard")
-        ws.epoch += 1
         K._check(L.nx_comm_norm_exchange(K._p(self.partials), C.c_int(self.nparts if self.count > 0 else 0),
                                          C.byref(ws.slots.table), C.byref(ws.flags.table), C.c_int(r), C.c_int(n),
-                                         C.c_int(ws.epoch), K._p(m.opt_state), status, st), "nx_comm_norm_exchange")
+                                         K._p(ws.counter), K._p(m.opt_state), status, st), "nx_comm_norm_exchange")
         m.grads.zero_()  # every peer has finished reading this rank's gradients
         if self.count > 0 and self.chunks is not None:
             K._check(L.nx_comm_adamw_allgather(K._p(self.master), K._p(self.gshard), K._p(self.m), K._p(self.v),
@@ -163,6 +162,16 @@ class FusedShardedOptimizer:
                                                st), "nx_comm_adamw_allgather")
         ws.barrier()  # updated weights are visible on every rank
         m.step_count += 1
+
+    def install_weights(self, full_master: torch.Tensor) -> None:
+        """Rebuilds what the model reads (BF16 shadow, FP32 norm / bias tail) and the flat FP32 copy from a full
+        master vector, e.g. after a checkpoint load."""
+        m = self.model
+        N = m.num_params
+        full = full_master[:N].to(m.device, torch.float32)
+        m.params.copy_(full)
+        self.shadow.local.copy_(full)
+        self.tail.local[: N - self.tail_off].copy_(full[self.tail_off:])
 
     def gather_master(self) -> torch.Tensor:
         """Full FP32 master vector (for checkpoints / tests) through NCCL."""
@@ -397,9 +406,8 @@ class _VocabParallelCE(torch.autograd.Function):
             cache["table"] = ws.alloc(ws.n * rows * 3, torch.float32)
         merged = torch.empty((rows, 3), dtype=torch.float32, device=logits.device)
         ws.barrier()                         # the previous call's tables have been read by everyone
-        ws.epoch += 1
         K._check(K.lib().nx_vocab_ce_exchange(K._p(stats), C.byref(cache["table"].table), C.byref(ws.flags.table),
-                                              C.c_int(ws.rank), C.c_int(ws.n), C.c_int(rows), C.c_int(ws.epoch),
+                                              C.c_int(ws.rank), C.c_int(ws.n), C.c_int(rows), K._p(ws.counter),
                                               K._p(merged), K._p(K.status_word(ws.device)), K._stream()),
                  "nx_vocab_ce_exchange")
         lse = merged[:, 0] + torch.log(merged[:, 1])

@@ -247,25 +247,88 @@ class GptLmBackend(LmBackend):
 
     # ------------------------------------------------------------------------------------ state
     def save_state(self) -> bytes:
+        """This rank's training state.  Replicated layout: the full FP32 master, both moments and the device
+        optimizer state.  Sharded layout (after `attach_fsdp`): the live FP32 master and moments are the
+        shards owned by the fused optimizer, so exactly those are written with their offset and count; the
+        flat `model.params/m/v` buffers are not current in that mode and are never written."""
         m = self.model
         buf = io.BytesIO()
-        torch.save({"params": m.params.cpu(), "m": m.m.cpu(), "v": m.v.cpu(), "opt": m.opt_state.cpu(),
-                    "step_count": m.step_count}, buf)
+        if self._sharded is not None:
+            sh = self._sharded
+            torch.save({"layout": "fsdp", "world": sh.ws.n, "rank": sh.ws.rank, "off": sh.off, "count": sh.count,
+                        "num_params": m.num_params, "master": sh.master.cpu(), "m": sh.m.cpu(), "v": sh.v.cpu(),
+                        "opt": m.opt_state.cpu(), "step_count": m.step_count}, buf)
+        else:
+            torch.save({"layout": "replicated", "params": m.params.cpu(), "m": m.m.cpu(), "v": m.v.cpu(),
+                        "opt": m.opt_state.cpu(), "step_count": m.step_count}, buf)
         return buf.getvalue()
 
-    def load_state(self, blob: bytes) -> None:
+    @staticmethod
+    def _full_state(blobs):
+        """Full (params, m, v, opt, step_count) on the host from one replicated blob or from every rank's shard."""
+        ds = [torch.load(io.BytesIO(b), map_location="cpu") for b in blobs]
+        first = ds[0]
+        if first.get("layout", "replicated") == "replicated":
+            return first["params"], first["m"], first["v"], first["opt"], first["step_count"]
+        world = first["world"]
+        if len(ds) != world or sorted(d["rank"] for d in ds) != list(range(world)):
+            raise ValueError(f"sharded state needs the blobs of all {world} ranks, got {len(ds)}")
+        n = first["num_params"]
+        full = [torch.zeros(n, dtype=torch.float32) for _ in range(3)]
+        covered = 0
+        for d in ds:
+            lo, cnt = d["off"], d["count"]
+            for dst, key in zip(full, ("master", "m", "v")):
+                dst[lo: lo + cnt] = d[key]
+            covered += cnt
+        if covered != n:
+            raise ValueError(f"sharded state covers {covered} of {n} parameters")
+        return full[0], full[1], full[2], first["opt"], first["step_count"]
+
+    def _install_full_state(self, params, m_, v_, opt, step_count) -> None:
         m = self.model
-        d = torch.load(io.BytesIO(blob), map_location="cpu")
-        m.params.copy_(d["params"])
-        m.m.copy_(d["m"])
-        m.v.copy_(d["v"])
-        m.opt_state.copy_(d["opt"])
-        m.step_count = d["step_count"]
-        m.refresh_shadow()
+        m.opt_state.copy_(opt)
+        m.step_count = step_count
+        if self._sharded is not None:
+            sh = self._sharded
+            sl = slice(sh.off, sh.off + sh.count)
+            sh.master.copy_(params[sl])
+            sh.m.copy_(m_[sl])
+            sh.v.copy_(v_[sl])
+            sh.install_weights(params.to(m.device))
+        else:
+            m.params.copy_(params)
+            m.m.copy_(m_)
+            m.v.copy_(v_)
+            m.refresh_shadow()
         m.grads.zero_()
 
+    def load_state(self, blob: bytes) -> None:
+        """Restores what `save_state` wrote on this rank.  A shard written under the same sharding goes straight
+        back into the fused optimizer's buffers and the BF16 weights / FP32 norm-and-bias tail are rebuilt from the
+        gathered master (a collective: every rank of the group loads at the same point)."""
+        d = torch.load(io.BytesIO(blob), map_location="cpu")
+        m = self.model
+        if d.get("layout", "replicated") == "fsdp":
+            sh = self._sharded
+            if sh is None or (sh.ws.n, sh.off, sh.count) != (d["world"], d["off"], d["count"]):
+                raise ValueError("this blob is one shard of an fsdp:%d state; use load_resharded_state with every "
+                                 "rank's blob to load it under a different layout" % d["world"])
+            sh.master.copy_(d["master"])
+            sh.m.copy_(d["m"])
+            sh.v.copy_(d["v"])
+            m.opt_state.copy_(d["opt"])
+            m.step_count = d["step_count"]
+            sh.install_weights(sh.gather_master())
+            m.grads.zero_()
+            return
+        self._install_full_state(d["params"], d["m"], d["v"], d["opt"], d["step_count"])
+
     def load_resharded_state(self, blobs) -> None:
-        self.load_state(blobs[0])  # replicated layout: every old rank holds the full state
+        """Loads a state written under another layout / world size: ``blobs`` holds every old rank's blob (one is
+        enough when the old layout was replicated); the full vectors are rebuilt on the host and this rank keeps
+        what its own layout owns."""
+        self._install_full_state(*self._full_state(list(blobs)))
 
     def peak_memory_bytes(self) -> int: return int(torch.cuda.max_memory_allocated(self.dev))
     def reset_peak_memory(self) -> None: torch.cuda.reset_peak_memory_stats(self.dev)

@@ -560,7 +560,8 @@ class LanguageModelTrainer:
                 "rng_offset": self.rng_offset, "train_cursor": cursor,
                 "val_cursor": self.val.global_cursor() if self.val is not None else 0,
                 "world": self.dp, "rank": self.rank, "tokens_seen": self.tokens_seen,
-                "schedule_step": self.step}
+                "schedule_step": self.step, "accum_steps": self.accum, "micro_batch": self.micro,
+                "seq_len": self.T, "global_batch_tokens": self.accum * self.micro * self.T * self.dp}
 
     def load_trainer_state(self, st: dict) -> None:
         self.step = int(st["step"])

@@ -34,17 +34,39 @@ def test_save_load_prune(tmp_path, asynchronous):
         m.save(step, {"lr_factor": 1.0, "train_cursor": step * 10}, b"blob%d" % step)
     m.wait()
     assert m.list_steps() == [6, 8]
-    assert open(tmp_path / "latest").read() == "step-000000008"
+    assert open(tmp_path / "latest").read() == "8"          # the bare step number, as the reference writes it
     got = m.load_latest()
     assert got.step == 8 and got.backend_blobs == [b"blob8"] and got.state["train_cursor"] == 80 and not got.resharded
-    # damage the newest checkpoint: the loader falls back to the previous one
+    # the manifest records the archive's own trailer (digest of everything before the last 32 bytes)
+    man = json.load(open(tmp_path / "step-000000008" / "manifest.json"))
+    raw = (tmp_path / "step-000000008" / "rank0.nxs3").read_bytes()
+    assert man["files"][0]["sha256"] == raw[-32:].hex() == __import__("hashlib").sha256(raw[:-32]).hexdigest()
+    assert man["files"][0]["bytes"] == len(raw) and man["state"]["step"] == 8
+    # damage the newest checkpoint: the loader warns and falls back to the previous one, or raises when asked to
     f = tmp_path / "step-000000008" / "rank0.nxs3"
     data = bytearray(f.read_bytes())
     data[30] ^= 0xFF
     f.write_bytes(bytes(data))
-    assert m.load_latest().step == 6
+    with pytest.warns(RuntimeWarning, match="failed verification"):
+        assert m.load_latest().step == 6
+    with pytest.raises(CheckpointError, match="newest checkpoint"):
+        m.load_latest(fallback=False)
     with pytest.raises(CheckpointError):
         m.load(8)
+
+
+def test_trainer_state_uses_the_reference_byte_layout():
+    from nexus_b200.ckpt import TrainerState
+    st = TrainerState(step=7, epoch=1, global_sample_index=99, train_cursor="abc", val_cursor="", lr_factor=0.5,
+                      schedule_step=7, loss_scale=1024.0, rng_seed=42, rng_offset=3, accum_counter=0, accum_steps=4,
+                      micro_batch=8, seq_len=1024, global_batch_tokens=32768, rollbacks=2, world=2, rank=1)
+    raw = st.encode()
+    # u32 schema | i64 step | i64 epoch | u64 samples | u64 len + bytes (x2) | f64 | i64 | f64 | u64 | u64 | 4 x i32 | i64 | 3 x i32
+    assert len(raw) == 4 + 8 + 8 + 8 + (8 + 3) + 8 + 8 + 8 + 8 + 8 + 8 + 16 + 8 + 12
+    assert raw[:4] == b"\x01\0\0\0" and raw[4:12] == (7).to_bytes(8, "little") and raw[36:39] == b"abc"
+    assert TrainerState.decode(raw) == st
+    with pytest.raises(CheckpointError):
+        TrainerState.decode(raw[:-5])
 
 
 def test_world_size_change_is_reported(tmp_path):
@@ -55,6 +77,9 @@ def test_world_size_change_is_reported(tmp_path):
     [t.join() for t in ts]
     got = CheckpointManager(CheckpointOptions(str(tmp_path)), rank=0, world=1).load_latest()
     assert got.resharded and got.world == 2 and got.backend_blobs == [b"r0", b"r1"] and got.layout == "fsdp:3:2"
+    assert got.state["x"] == 0    # keys the fixed record does not know travel in the side entry
+    same = CheckpointManager(CheckpointOptions(str(tmp_path)), rank=1, world=2).load_latest()
+    assert not same.resharded and same.backend_blobs == [None, b"r1"] and same.state["rank"] == 1
 
 
 @pytest.mark.parametrize("point", ("rank_file", "before_manifest", "before_rename"))

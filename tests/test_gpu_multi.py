@@ -10,11 +10,19 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def _free_port() -> str:
+    """A TCP port that is free right now on the loopback interface (shared boxes: no fixed port numbers)."""
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return str(s.getsockname()[1])
+
+
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fused_comm_paths_two_gpus():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29611", os.path.join(ROOT, "tests", "workers", "fused_comm_worker.py")]
+           "127.0.0.1", "--master-port", _free_port(), os.path.join(ROOT, "tests", "workers", "fused_comm_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=420, env=env)
     assert "WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
@@ -26,7 +34,7 @@ def test_tensor_parallel_lm_two_gpus_matches_single_process_loss(precision):
     equals the single-process model's on the same tokens, and training steps run."""
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", "29613", "-m", "nexus_b200.bench.parallel", "--model", "llama2-7b", "--layers", "1",
+           "127.0.0.1", "--master-port", _free_port(), "-m", "nexus_b200.bench.parallel", "--model", "llama2-7b", "--layers", "1",
            "--tp", "2", "--seq-len", "256", "--global-batch", "2", "--micro-batch", "1", "--precision", precision,
            "--steps", "2", "--warmup", "1", "--check"]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
