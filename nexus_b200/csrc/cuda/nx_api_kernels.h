@@ -103,6 +103,8 @@ int nx_colsum(const void* dy, int dtype, float* out, float* scratch, int rows, i
 //   * The first call on each device looks the array's device address up (cudaGetSymbolAddress, with
 //     that device current) and caches it; make that first call during set-up, before any stream
 //     capture begins.  Every GPU that loads the library keeps the 2 MiB until the process exits.
+//   * The device that holds the data must be the current device, and `stream` must be one of its streams: the
+//     array that is used is the current device's copy.  Data on another device returns -6.
 //   * All calls on a device share the one array and it keeps the previous call's partials.  Each
 //     call overwrites every entry it later reads, so nothing needs clearing, but two calls that
 //     overlap on the GPU (different streams) race on it: keep them on one stream or order them.

@@ -3,6 +3,8 @@
 // Philox4x32-10 dropout, global gradient norm, multi-tensor AdamW over chunk descriptors with FP32
 // master weights and a narrow shadow copy, dynamic loss scale, non-finite guard, bias gradient.
 // Parity: src/cuda/kernels_train.cu:35-1107 and src/fused/training.cpp:53-459 of the reference.
+#include <atomic>
+
 #include "common.cuh"
 #include "nx_api_kernels.h"
 
@@ -798,14 +800,17 @@ constexpr int kStaticColsumMaxChunks = 64;
 static __device__ __align__(256) float g_colsum_static_scratch[kStaticColsumMaxChunks * kStaticColsumMaxCols];
 
 constexpr int kMaxDevices = 64;
-float* g_colsum_static_ptr[kMaxDevices] = {};  // device address of the array, per device ordinal
+// device address of the array, per device ordinal; atomics because two host threads may make the first call at once
+// (both would look up the same address, so a lost race only repeats the lookup)
+std::atomic<float*> g_colsum_static_ptr[kMaxDevices];
 
 // In host code `g_colsum_static_scratch` is only a handle for the symbol, not a device address, so
 // the address a kernel can use is asked for once per device (with that device current).
 int colsum_static_scratch_for_current_device(float** out) {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -2;
-  if (g_colsum_static_ptr[dev] == nullptr) {
+  float* cached = g_colsum_static_ptr[dev].load(std::memory_order_acquire);
+  if (cached == nullptr) {
     void* p = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(&p, g_colsum_static_scratch);
     if (e != cudaSuccess || p == nullptr) {
@@ -813,9 +818,10 @@ int colsum_static_scratch_for_current_device(float** out) {
               cudaGetErrorString(e));
       return -2;
     }
-    g_colsum_static_ptr[dev] = static_cast<float*>(p);
+    cached = static_cast<float*>(p);
+    g_colsum_static_ptr[dev].store(cached, std::memory_order_release);
   }
-  *out = g_colsum_static_ptr[dev];
+  *out = cached;
   return 0;
 }
 
@@ -835,6 +841,20 @@ extern "C" int nx_colsum_static(const void* dy, int dtype, float* out, int rows,
   const int rc = colsum_static_scratch_for_current_device(&scratch);
   if (rc != 0) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  {
+    // the array that was looked up belongs to the CURRENT device; data on another device would make the
+    // kernels write partial sums into memory they cannot reach, so a mismatch is refused, not launched
+    cudaPointerAttributes attr{};
+    int dev = -1;
+    cudaGetDevice(&dev);
+    const cudaError_t pe = cudaPointerGetAttributes(&attr, out);
+    if (pe != cudaSuccess) cudaGetLastError();  // an unknown pointer is not this check's business
+    if (pe == cudaSuccess && attr.type == cudaMemoryTypeDevice && attr.device != dev) {
+      fprintf(stderr, "nx_colsum_static: output lives on device %d but device %d is current; make the data's "
+                      "device (and the stream's) current before the call\n", attr.device, dev);
+      return -6;
+    }
+  }
   const int chunks = std::max(1, std::min(kStaticColsumMaxChunks, (rows + 255) / 256));
   const int rpc = (rows + chunks - 1) / chunks;
   dim3 grid((cols + 31) / 32, chunks), block(32, 8);

@@ -1,16 +1,24 @@
 """Python-defined activations and modules inside NXS archives.
 
-A user body (a plain function or a ``torch.nn.Module`` subclass defined in Python) is registered
-under a name; when a model using it is saved, the code object (``marshal``) and defaults travel in
-the archive's python payload, so ``nexus.load(path)`` works in a process that never imported the
-defining script.  Only load archives you trust: the payload is executable code.
+A user body (a plain function, or a factory returning a ``torch.nn.Module``) is registered under a name; when
+a model using it is saved, its code object travels in the archive's python payload, so ``nexus.load(path)``
+works in a process that never imported the defining script.
+
+Payload = the reference's ``NXPY`` record stream: ``"NXPY" | u16 version 1 | u32 count`` then per record
+``u8 kind (1 activation, 2 module) | u32 len + name | code | code`` (forward, backward) and, for modules,
+``u32 n_shapes | (u32 rank | u64 dims...)``; a code field is ``u32 len | marshal bytes | u32 n_cells |
+(u8 tag | 8 bytes)`` with tag 1 = float64, 2 = int64, 3 = bool.  Closure cells may only hold float, int or
+bool, and nothing but ``marshal`` is used to read the payload (no pickle: loading runs no code until a body
+is called).  A loaded body sees ``math``, ``torch`` and the builtins.  The backward slot is written empty:
+gradients come from autograd here.  Only load archives you trust: the bodies are executable code.
 
 Parity: python/src/nexus/fnstore.py of the reference.
 """
 from __future__ import annotations
 
 import marshal
-import pickle
+import math
+import struct
 import types
 from typing import Callable, Dict
 
@@ -37,37 +45,127 @@ def module_factory(name: str):
     return PythonModule(name, _MODULE_FACTORIES[name]())
 
 
-def _dump_fn(fn: Callable) -> dict:
-    return {"code": marshal.dumps(fn.__code__), "name": fn.__name__, "defaults": fn.__defaults__}
+_ACTIVATION, _MODULE = 1, 2
 
 
-def _load_fn(rec: dict) -> Callable:
-    code = marshal.loads(rec["code"])
-    return types.FunctionType(code, {"torch": torch, "__builtins__": __builtins__}, rec["name"], rec["defaults"])
+def _check(fn: Callable) -> None:
+    """Only plain functions whose closure cells hold float / int / bool can be archived."""
+    if not hasattr(fn, "__code__"):
+        raise TypeError("this callable has no code object and cannot be written into an archive")
+    if fn.__defaults__ or fn.__kwdefaults__:
+        raise TypeError("python bodies with default arguments cannot be written into an archive")
+    for cell in fn.__closure__ or ():
+        v = cell.cell_contents
+        if isinstance(v, bool) or isinstance(v, float):
+            continue
+        if isinstance(v, int) and -(1 << 63) <= v < (1 << 63):
+            continue
+        raise TypeError("a python body may only close over float, int or bool values")
+
+
+def _write_code(buf: bytearray, fn) -> None:
+    blob = b"" if fn is None else marshal.dumps(fn.__code__)
+    buf += struct.pack("<I", len(blob)) + blob
+    cells = () if fn is None or not fn.__closure__ else fn.__closure__
+    buf += struct.pack("<I", len(cells))
+    for cell in cells:
+        v = cell.cell_contents
+        if isinstance(v, bool):
+            buf += struct.pack("<Bq", 3, int(v))
+        elif isinstance(v, int):
+            buf += struct.pack("<Bq", 2, v)
+        else:
+            buf += struct.pack("<Bd", 1, float(v))
+
+
+def _cell(value):
+    return (lambda: value).__closure__[0]
+
+
+def _read_code(view, off: int):
+    (n,) = struct.unpack_from("<I", view, off)
+    off += 4
+    blob = bytes(view[off: off + n])
+    if len(blob) != n:
+        raise ValueError("nxs python payload is truncated")
+    off += n
+    (ncell,) = struct.unpack_from("<I", view, off)
+    off += 4
+    cells = []
+    for _ in range(ncell):
+        (tag,) = struct.unpack_from("<B", view, off)
+        if tag == 1:
+            cells.append(struct.unpack_from("<d", view, off + 1)[0])
+        elif tag in (2, 3):
+            raw = struct.unpack_from("<q", view, off + 1)[0]
+            cells.append(bool(raw) if tag == 3 else int(raw))
+        else:
+            raise ValueError("nxs python payload: unknown closure cell tag %d" % tag)
+        off += 9
+    fn = None
+    if blob:
+        code = marshal.loads(blob)
+        closure = tuple(_cell(v) for v in cells) if cells else None
+        fn = types.FunctionType(code, {"__builtins__": __builtins__, "math": math, "torch": torch}, closure=closure)
+    return fn, off
 
 
 def payload_for(model) -> bytes:
-    """Bodies of every Python-defined activation / module that ``model`` uses (empty when none)."""
+    """``NXPY`` records of every Python-defined activation / module that ``model`` uses (empty when none)."""
     from .nn.modules import KIND, Module
     acts, mods = {}, {}
     for m in model.modules():
         if isinstance(m, Module):
             if m.kind == KIND["NamedActivation"] and m.layer_name in _ACTIVATION_SOURCES:
-                acts[m.layer_name] = _dump_fn(_ACTIVATION_SOURCES[m.layer_name])
+                acts[m.layer_name] = _ACTIVATION_SOURCES[m.layer_name]
             if m.kind == KIND["PythonModule"] and m.layer_name in _MODULE_FACTORIES:
-                mods[m.layer_name] = _dump_fn(_MODULE_FACTORIES[m.layer_name])
+                mods[m.layer_name] = _MODULE_FACTORIES[m.layer_name]
     if not acts and not mods:
         return b""
-    return pickle.dumps({"activations": acts, "modules": mods})
+    buf = bytearray(b"NXPY") + struct.pack("<HI", 1, len(acts) + len(mods))
+    for kind, table in ((_ACTIVATION, acts), (_MODULE, mods)):
+        for name, fn in table.items():
+            _check(fn)
+            raw = name.encode("utf-8")
+            buf += struct.pack("<BI", kind, len(raw)) + raw
+            _write_code(buf, fn)
+            _write_code(buf, None)          # backward slot: autograd differentiates the forward body
+            if kind == _MODULE:
+                buf += struct.pack("<I", 0)   # parameter shapes live in the module's own tensors
+    return bytes(buf)
 
 
 def restore_payload(blob: bytes) -> None:
+    """Registers the bodies of an ``NXPY`` payload that this process does not know yet."""
     if not blob:
         return
-    d = pickle.loads(blob)
-    for name, rec in d.get("activations", {}).items():
-        if name not in _ACTIVATION_SOURCES:
-            register_python_activation(name, _load_fn(rec))
-    for name, rec in d.get("modules", {}).items():
-        if name not in _MODULE_FACTORIES:
-            register_python_module(name, _load_fn(rec))
+    view = memoryview(blob)
+    if bytes(view[:4]) != b"NXPY":
+        raise ValueError("nxs python payload: not an NXPY record stream")
+    try:
+        version, count = struct.unpack_from("<HI", view, 4)
+        if version != 1:
+            raise ValueError("nxs python payload version %d is unsupported" % version)
+        off = 10
+        for _ in range(count):
+            kind, nlen = struct.unpack_from("<BI", view, off)
+            off += 5
+            name = bytes(view[off: off + nlen]).decode("utf-8")
+            off += nlen
+            forward, off = _read_code(view, off)
+            _backward, off = _read_code(view, off)
+            if kind == _MODULE:
+                (nshape,) = struct.unpack_from("<I", view, off)
+                off += 4
+                for _s in range(nshape):
+                    (rank,) = struct.unpack_from("<I", view, off)
+                    off += 4 + 8 * rank
+                if forward is not None and name not in _MODULE_FACTORIES:
+                    register_python_module(name, forward)
+            elif kind == _ACTIVATION:
+                if forward is not None and name not in _ACTIVATION_SOURCES:
+                    register_python_activation(name, forward)
+            else:
+                raise ValueError("nxs python payload: unknown record kind %d" % kind)
+    except struct.error:
+        raise ValueError("nxs python payload is truncated") from None

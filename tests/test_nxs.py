@@ -1,3 +1,4 @@
+import os
 import struct
 
 import numpy as np
@@ -56,6 +57,43 @@ def test_model_round_trips(tmp_path):
     lm.save_nxs(p)
     t = torch.randint(0, 256, (2, 16))
     assert torch.equal(LanguageModel.load_nxs(p).loss(t), lm.loss(t))
+
+
+def test_python_payload_is_an_nxpy_record_stream_and_survives_a_fresh_process(tmp_path):
+    """Byte layout of the python payload (kind / name / marshal code / typed closure cells), closure restrictions,
+    and a load in a process that never saw the defining code."""
+    import subprocess
+    import sys
+    scale, shift, flag = 2.5, 3, True
+
+    def squish(x):
+        return x * scale + shift if flag else x
+
+    fnstore.register_python_activation("squish_t", squish)
+    m = nn.Sequential().add(nn.Linear(3, 3)).add(nn.Activation("squish_t"))
+    blob = fnstore.payload_for(m)
+    assert blob[:4] == b"NXPY" and struct.unpack_from("<HI", blob, 4) == (1, 1)
+    assert blob[10] == 1 and struct.unpack_from("<I", blob, 11)[0] == len("squish_t") and blob[15:23] == b"squish_t"
+    (code_len,) = struct.unpack_from("<I", blob, 23)
+    cells_at = 27 + code_len
+    assert struct.unpack_from("<I", blob, cells_at)[0] == 3
+    tags = sorted(blob[cells_at + 4 + 9 * i] for i in range(3))
+    assert tags == [1, 2, 3]                         # one float64, one int64, one bool cell
+    p = str(tmp_path / "py.nxs")
+    m.save_nxs(p)
+    x = torch.randn(2, 3)
+    torch.save((x, m(x)), str(tmp_path / "io.pt"))
+    code = ("import sys, torch; sys.path.insert(0, %r)\nfrom nexus_b200 import nn\n"
+            "x, y = torch.load(%r)\nm = nn.Sequential.load_nxs(%r)\nassert torch.equal(m(x), y)\nprint('fresh ok')\n"
+            % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))), str(tmp_path / "io.pt"), p))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True)
+    assert "fresh ok" in r.stdout, r.stderr[-2000:]
+    table = {"a": 1}
+    fnstore.register_python_activation("bad_t", lambda x: x * table["a"])
+    with pytest.raises(TypeError, match="float, int or bool"):
+        fnstore.payload_for(nn.Sequential().add(nn.Activation("bad_t")))
+    with pytest.raises(ValueError, match="NXPY"):
+        fnstore.restore_payload(b"\x80\x04junk")       # e.g. a pickle: rejected, never unpickled
 
 
 def test_rejections(tmp_path):

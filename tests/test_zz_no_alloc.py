@@ -46,6 +46,25 @@ def test_colsum_static_matches_regular_entry_point_twice():
     assert (got - want).abs().max().item() <= 1e-4 * max(want.abs().max().item(), 1.0)
 
 
+def test_colsum_static_strided_odd_width_and_tall_inputs():
+    """A BF16 view whose row stride exceeds its width and whose width is not a multiple of 8 (the scalar path),
+    and an input tall enough to use all 64 row chunks of the built-in array."""
+    from nexus_b200.ops import _cuda as K
+    lib = K.lib()
+    torch.manual_seed(1)
+    wide = torch.randn(700, 1024, device="cuda").bfloat16()
+    view = wide[:, 3:3 + 501]                                  # ld 1024 > cols 501, 501 % 8 != 0, unaligned start
+    tall = torch.randn(16384 + 777, 264, device="cuda").bfloat16()
+    for dy in (view, tall, view):                              # the repeat runs on the tall call's leftovers
+        got = torch.full((dy.shape[1],), float("nan"), device="cuda")
+        assert _call_static(lib, dy, got) == 0
+        torch.cuda.synchronize()
+        ref = dy.float().sum(0)
+        assert (got - ref).abs().max().item() <= 1e-4 * max(ref.abs().max().item(), 1.0)
+        want = K.colsum(dy)
+        assert (got - want).abs().max().item() <= 1e-4 * max(want.abs().max().item(), 1.0)
+
+
 def test_colsum_static_rejects_oversize():
     from nexus_b200.ops import _cuda as K
     lib = K.lib()
