@@ -1,0 +1,11 @@
+"""`nexus.custom`: the shell's call signatures (flat lists, shell tensors); every other name of
+:mod:`nexus_b200.custom` stays reachable from here with its native (torch) interface."""
+import importlib as _importlib
+
+from nexus._shell import (MicroTape, Tape)  # noqa: F401
+
+_native = _importlib.import_module("nexus_b200.custom")
+
+
+def __getattr__(name):
+    return getattr(_native, name)

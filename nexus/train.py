@@ -1,0 +1,11 @@
+"""`nexus.train`: the shell's call signatures (flat lists, shell tensors); every other name of
+:mod:`nexus_b200.train` stays reachable from here with its native (torch) interface."""
+import importlib as _importlib
+
+from nexus._shell import (Callback, ProgressLogger, TrainerBuilder, Trainer, LanguageTrainer, all_reduce_mean)  # noqa: F401
+
+_native = _importlib.import_module("nexus_b200.train")
+
+
+def __getattr__(name):
+    return getattr(_native, name)

@@ -18,6 +18,8 @@
 // exits between steps cannot fault its peers.
 // Replaces (reference, CPU only): FsdpEngine::launch_reduce + step (src/dist/fsdp.cpp:387-568),
 // MoeExpertParallel (src/dist/moe_ep.cpp:45-90), vocab-parallel CE (src/dist/parallel_lm.cpp:611-665).
+#include <algorithm>
+
 #include "common.cuh"
 #include "nx_api_comm.h"
 #include "sm100_ptx.cuh"
@@ -391,9 +393,87 @@ __global__ void vocab_ce_exchange_kernel(const float* __restrict__ local_stats, 
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// owner's half of the slot form of GEMM -> reduce-scatter: out = residual + sum over the n BF16 slots (rank order)
+// ------------------------------------------------------------------------------------------------
+template <typename RT, typename OT>
+__global__ void __launch_bounds__(256)
+sum_slots_kernel(const __nv_bfloat16* __restrict__ slots, int n, int rows, int cols, int64_t ld_slots,
+                 const RT* __restrict__ residual, int64_t ld_res, OT* __restrict__ out, int64_t ld_out,
+                 __nv_bfloat16* __restrict__ out_lp, int64_t ld_lp) {
+  constexpr int V = 8;
+  const int vec_per_row = cols / V;
+  const int64_t total = static_cast<int64_t>(rows) * vec_per_row;
+  const int64_t slot_stride = static_cast<int64_t>(rows) * ld_slots;
+  NX_GRID_STRIDE(i, total) {
+    const int r = static_cast<int>(i / vec_per_row);
+    const int c = static_cast<int>(i % vec_per_row) * V;
+    float acc[V];
+    if (residual != nullptr) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] = Num<RT>::load(residual + static_cast<int64_t>(r) * ld_res + c + j);
+    } else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] = 0.0f;
+    }
+#pragma unroll 1
+    for (int q = 0; q < n; ++q) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(slots + q * slot_stride + static_cast<int64_t>(r) * ld_slots + c);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) Num<OT>::store(out + static_cast<int64_t>(r) * ld_out + c + j, acc[j]);
+    if (out_lp != nullptr) {
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(out_lp + static_cast<int64_t>(r) * ld_lp + c) = o;
+    }
+  }
+}
+
+__global__ void bump_kernel(int* counter) { *counter += 1; }
+
 }  // namespace
 
 // ================================================================================================
+extern "C" int nx_comm_bump(int* counter, nx_stream_t stream) {
+  if (counter == nullptr) return -1;
+  bump_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(counter);
+  return launch_status();
+}
+
+extern "C" int nx_comm_sum_slots(const void* slots, int n, int rows, int cols, int64_t ld_slots, const void* residual,
+                                 int res_dtype, int64_t ld_res, void* out, int out_dtype, int64_t ld_out, void* out_lp,
+                                 int64_t ld_lp, nx_stream_t stream) {
+  if (slots == nullptr || out == nullptr || n < 1 || n > NX_MAX_PEERS || rows <= 0 || cols <= 0 || (cols & 7) ||
+      (ld_slots & 7) || (reinterpret_cast<uintptr_t>(slots) & 15) || (out_lp != nullptr && ((ld_lp & 7) ||
+      (reinterpret_cast<uintptr_t>(out_lp) & 15))))
+    return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t total = static_cast<int64_t>(rows) * (cols / 8);
+  const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 16));
+  const __nv_bfloat16* sl = static_cast<const __nv_bfloat16*>(slots);
+  __nv_bfloat16* lp = static_cast<__nv_bfloat16*>(out_lp);
+#define NX_SS(RT, OT) sum_slots_kernel<RT, OT><<<blocks, 256, 0, st>>>(sl, n, rows, cols, ld_slots, static_cast<const RT*>(residual), ld_res, static_cast<OT*>(out), ld_out, lp, ld_lp)
+  const int rd = residual == nullptr ? out_dtype : res_dtype;
+  if (rd == NX_F32 && out_dtype == NX_F32) NX_SS(float, float);
+  else if (rd == NX_BF16 && out_dtype == NX_BF16) NX_SS(__nv_bfloat16, __nv_bfloat16);
+  else if (rd == NX_F32 && out_dtype == NX_BF16) NX_SS(float, __nv_bfloat16);
+  else if (rd == NX_BF16 && out_dtype == NX_F32) NX_SS(__nv_bfloat16, float);
+  else return -1;
+#undef NX_SS
+  return launch_status();
+}
+
 extern "C" int nx_comm_barrier(const NxPeerTable* flags, int rank, int n, int* counter, int* status, nx_stream_t stream) {
   if (flags == nullptr || n < 1 || n > NX_MAX_PEERS || rank < 0 || rank >= n || status == nullptr || counter == nullptr)
     return -1;

@@ -76,6 +76,23 @@ struct DevParams {
   unsigned int* amax_out;  // max |out| as float bits (may be null)
   int tma_store;           // BF16 out (and aux_out) leave through shared memory and tiled TMA stores
   int n_fastest;           // consecutive work units walk along N (A tile reused from L2) instead of along M
+  // All-gather fused into the GEMM (nx_gemm_ag): A is this rank's [M][lda] gather buffer; the last `ag_copiers`
+  // CTAs of the grid push this rank's row block into every peer's buffer and raise per-chunk flags there, while
+  // the GEMM CTAs start with the local rows and take the other ranks' rows in ring order as their flags come up.
+  int ag_ranks, ag_rank, ag_rows, ag_copiers;  // ag_ranks <= 1: plain GEMM
+  int64_t ag_ld_bytes;                        // bytes between rows of the gather buffers
+  int ag_row_bytes;                           // bytes of one row that are copied (K * 2)
+  const int* ag_counter;                      // generation of this call = *ag_counter + 1
+  void* ag_gather[NX_MAX_PEERS];
+  int* ag_flags[NX_MAX_PEERS];                // per rank: int[ag_ranks][ag_rows / 128]
+  int rot_rows;                               // work units start at this row and wrap around (ring order)
+  // GEMM fused with a reduce-scatter (nx_gemm_rs): `out` is a local BF16 [M][ldo] buffer of partial sums; every
+  // epilogue warp counts a finished tile on rs_done[row block], and the last `rs_copiers` CTAs store each complete
+  // 256-row block into slot `rs_rank` of the buffer of the rank that owns those rows.
+  int rs_ranks, rs_rank, rs_rows, rs_copiers;  // rs_ranks <= 1: plain GEMM
+  int rs_expected;                            // arrivals that complete one row block (16 per column tile)
+  int* rs_done;                               // [M / 256], zeroed by the caller before the launch
+  void* rs_slots[NX_MAX_PEERS];               // per rank: BF16 [rs_ranks][rs_rows][ldo]
 };
 
 struct Unit {
@@ -94,7 +111,8 @@ struct alignas(64) DistParam<true> {
   CUtensorMap b[NX_MAX_PEERS];
   float* out[NX_MAX_PEERS];
   int a_rows, b_rows, out_rows;  // rows per rank
-  int a_sharded, b_sharded, out_scatter;
+  int k_rows;                    // K rows per rank when an MN-major operand is sharded along K
+  int a_sharded, b_sharded, out_scatter, rank;
 };
 
 template <int TILE_M = kBM>
@@ -117,6 +135,10 @@ __device__ __forceinline__ Unit decode_unit(const DevParams& p, int u) {
     w.batch = u / p.tiles_n;
   }
   w.m0 = tm * TILE_M;
+  if (p.rot_rows > 0) {  // ring order: all-gather starts with the local rows, reduce-scatter ends with them
+    w.m0 += p.rot_rows;
+    if (w.m0 >= p.m) w.m0 -= p.m;
+  }
   w.n0 = tn;  // multiplied by BN by the caller
   w.kb_begin = w.slice * p.kb_per_slice;
   w.kb_end = min(p.kb_total, w.kb_begin + p.kb_per_slice);
@@ -229,6 +251,130 @@ __device__ long long g_epi_prof[148 * 8];  // first epilogue warp: busy cycles p
 // FAST (pair only): the epilogue of the training GEMMs and nothing else - BF16 result through tiled stores,
 // optional bias, GELU with saved pre-activation, or dGELU of a saved pre-activation - with the bias staged once
 // per tile in shared memory and one proxy fence / store group per tile (two with aux_out).
+// Copier CTA of the all-gather GEMM: pushes chunk after chunk (128 rows) of this rank's row block into the gather
+// buffer of one peer after the other (the peer that needs it soonest first), then raises that chunk's flag on the peer.
+// Plain stores to peer memory; the release store of the flag follows a system-scope fence by every storing thread.
+__device__ __forceinline__ void ag_copier_run(const DevParams& p, int cid) {
+  const int n = p.ag_ranks, r = p.ag_rank;
+  const int chunks = p.ag_rows / kBM;
+  const int epoch = *reinterpret_cast<const volatile int*>(p.ag_counter) + 1;
+  const int vpr = p.ag_row_bytes / 16;  // 16-byte vectors per row
+  const int total = kBM * vpr;
+  const char* src_base = reinterpret_cast<const char*>(p.ag_gather[r]) + static_cast<int64_t>(r) * p.ag_rows * p.ag_ld_bytes;
+  for (int s = 1; s < n; ++s) {
+    const int dest = (r - s + n) % n;
+    char* dst_base = reinterpret_cast<char*>(p.ag_gather[dest]) + static_cast<int64_t>(r) * p.ag_rows * p.ag_ld_bytes;
+    for (int j = cid; j < chunks; j += p.ag_copiers) {
+      const char* src = src_base + static_cast<int64_t>(j) * kBM * p.ag_ld_bytes;
+      char* dst = dst_base + static_cast<int64_t>(j) * kBM * p.ag_ld_bytes;
+      int i = threadIdx.x;
+      for (; i + 3 * static_cast<int>(blockDim.x) < total; i += 4 * blockDim.x) {
+        uint4 v[4];
+        int64_t off[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int idx = i + u * blockDim.x;
+          off[u] = static_cast<int64_t>(idx / vpr) * p.ag_ld_bytes + static_cast<int64_t>(idx % vpr) * 16;
+          v[u] = *reinterpret_cast<const uint4*>(src + off[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) *reinterpret_cast<uint4*>(dst + off[u]) = v[u];
+      }
+      for (; i < total; i += blockDim.x) {
+        const int64_t off = static_cast<int64_t>(i / vpr) * p.ag_ld_bytes + static_cast<int64_t>(i % vpr) * 16;
+        *reinterpret_cast<uint4*>(dst + off) = *reinterpret_cast<const uint4*>(src + off);
+      }
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x == 0)
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.ag_flags[dest] + r * chunks + j), "r"(epoch) : "memory");
+    }
+  }
+}
+
+// Copier CTA of the reduce-scatter GEMM: block after block (256 rows, in the order the GEMM CTAs finish them) waits
+// until every tile of the block has been stored, then copies its share of the block's rows from the local buffer of
+// partial sums into slot `rs_rank` of the owner's buffer (plain stores, over NVLink unless the owner is this rank).
+__device__ __forceinline__ void rs_copier_run(const DevParams& p, int cid) {
+  const int n = p.rs_ranks;
+  const int blocks = p.m / (2 * kBM);
+  const int rows_per = (2 * kBM) / p.rs_copiers;  // rows of every block that this copier moves
+  const int64_t ld_bytes = p.ldo * 2;
+  const int vpr = (p.n * 2) / 16;
+  const int total = rows_per * vpr;
+  const int first = p.rot_rows / (2 * kBM);
+  __shared__ int s_ok;
+  for (int i = 0; i < blocks; ++i) {
+    int rb = first + i;
+    if (rb >= blocks) rb -= blocks;
+    if (threadIdx.x == 0) {
+      s_ok = 1;
+      const uint64_t t0 = globaltimer_ns();
+      for (;;) {
+        int v;
+        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.rs_done + rb) : "memory");
+        if (v >= p.rs_expected) break;
+        if (globaltimer_ns() - t0 > NX_WAIT_LIMIT_NS) {
+          atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+          s_ok = 0;
+          break;
+        }
+        __nanosleep(200);
+      }
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const int row0 = rb * 2 * kBM + cid * rows_per;
+    const int owner = row0 / p.rs_rows;
+    const char* src = reinterpret_cast<const char*>(p.out) + static_cast<int64_t>(row0) * ld_bytes;
+    char* dst = reinterpret_cast<char*>(p.rs_slots[owner]) +
+                (static_cast<int64_t>(p.rs_rank) * p.rs_rows + (row0 - owner * p.rs_rows)) * ld_bytes;
+    asm volatile("fence.proxy.async;" ::: "memory");  // the block was written by TMA stores; read it with plain loads
+    int j = threadIdx.x;
+    for (; j + 3 * static_cast<int>(blockDim.x) < total; j += 4 * blockDim.x) {
+      uint4 v[4];
+      int64_t off[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = j + u * blockDim.x;
+        off[u] = static_cast<int64_t>(idx / vpr) * ld_bytes + static_cast<int64_t>(idx % vpr) * 16;
+        v[u] = *reinterpret_cast<const uint4*>(src + off[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) *reinterpret_cast<uint4*>(dst + off[u]) = v[u];
+    }
+    for (; j < total; j += blockDim.x) {
+      const int64_t off = static_cast<int64_t>(j / vpr) * ld_bytes + static_cast<int64_t>(j % vpr) * 16;
+      *reinterpret_cast<uint4*>(dst + off) = *reinterpret_cast<const uint4*>(src + off);
+    }
+    __syncthreads();
+  }
+  __threadfence_system();  // the partial sums are in the owners' memory before this grid counts as complete
+}
+
+// Producer side of the all-gather GEMM: rows [row0, row0 + 128) belong to rank row0 / ag_rows; unless they are this
+// rank's own, wait (bounded) until their owner's copier has raised the chunk's flag for this call.
+__device__ __forceinline__ bool ag_wait_rows(const DevParams& p, int row0, int epoch, volatile int* abort_flag) {
+  const int q = row0 / p.ag_rows;
+  if (q == p.ag_rank) return true;
+  const int chunks = p.ag_rows / kBM;
+  const int* flag = p.ag_flags[p.ag_rank] + q * chunks + (row0 - q * p.ag_rows) / kBM;
+  const uint64_t t0 = globaltimer_ns();
+  for (;;) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v >= epoch) break;
+    if (*abort_flag != 0 || globaltimer_ns() - t0 > NX_WAIT_LIMIT_NS) {
+      *abort_flag = 1;
+      atomicCAS(p.status, 0, kStatusTimeoutPeer);
+      return false;
+    }
+    __nanosleep(100);
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");  // the rows were written through the generic proxy; TMA reads them
+  return true;
+}
+
 template <int BN, bool A_MN, bool B_MN, bool DIST, bool PAIR = false, bool FAST = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -238,6 +384,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   static_assert(!(PAIR && DIST), "the CTA-pair tile is for single-GPU operands");
   static_assert(!FAST || PAIR, "the lean epilogue is built for the pair kernel");
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // all-gather GEMM: the last ag_copiers CTAs (whole clusters) only move data and never touch barriers or TMEM
+  const int gemm_ctas = static_cast<int>(gridDim.x) - (p.ag_ranks > 1 ? p.ag_copiers : 0) - (p.rs_ranks > 1 ? p.rs_copiers : 0);
+  if (static_cast<int>(blockIdx.x) >= gemm_ctas) {
+    pdl_wait();  // this rank's rows come from the previous kernel of the stream
+    if (p.ag_ranks > 1) ag_copier_run(p, static_cast<int>(blockIdx.x) - gemm_ctas);
+    else rs_copier_run(p, static_cast<int>(blockIdx.x) - gemm_ctas);
+    return;
+  }
   if constexpr (PAIR) {
     // no slack to round the base up in: refuse to run on a base that is not 1 KiB-aligned (same in every CTA)
     if ((smem_u32(smem_raw) & 1023u) != 0u) {
@@ -263,7 +417,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   // pair: consecutive CTAs form a cluster; the even one issues the MMAs and owns the barriers both wait on
   const uint32_t cta_rank = PAIR ? cluster_ctarank() : 0u;
   const int unit_first = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
-  const int unit_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int unit_step = PAIR ? (gemm_ctas >> 1) : gemm_ctas;
   constexpr int kTileM = PAIR ? 2 * kBM : kBM;
   const int m_off = static_cast<int>(cta_rank) * kBM;  // this CTA's rows inside the pair's tile
 
@@ -308,10 +462,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      const int ag_epoch = p.ag_ranks > 1 ? *reinterpret_cast<const volatile int*>(p.ag_counter) + 1 : 0;
       for (int u = unit_first; u < p.num_units && ok; u += unit_step) {
         Unit w = decode_unit<kTileM>(p, u);
         w.m0 += m_off;
         const int n0 = w.n0 * BN;
+        if (p.ag_ranks > 1 && !ag_wait_rows(p, w.m0, ag_epoch, abort_flag)) {
+          ok = false;
+          break;
+        }
         for (int kb = w.kb_begin; kb < w.kb_end; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) {
             ok = false;
@@ -349,33 +508,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
           const CUtensorMap* ma = &tmap_a;
           const CUtensorMap* mb = &tmap_b;
-          int am0 = w.m0, bn0 = n0;
+          int am0 = w.m0, bn0 = n0, ak0 = k0, bk0 = k0;
           if constexpr (DIST) {
-            // the tile's rows live in the memory of the rank that owns them: plain (non-multicast) TMA
-            if (dist.a_sharded) {
+            // the tile lives in the memory of the rank that owns it: plain (non-multicast) TMA from peer memory
+            if (dist.a_sharded == NX_DIST_ROWS) {
               const int q = w.m0 / dist.a_rows;
               ma = &dist.a[q];
               am0 = w.m0 - q * dist.a_rows;
+            } else if (dist.a_sharded == NX_DIST_K) {
+              const int q = k0 / dist.k_rows;
+              ma = &dist.a[q];
+              ak0 = k0 - q * dist.k_rows;
             }
-            if (dist.b_sharded) {
+            if (dist.b_sharded == NX_DIST_ROWS) {
               const int q = n0 / dist.b_rows;
               mb = &dist.b[q];
               bn0 = n0 - q * dist.b_rows;
+            } else if (dist.b_sharded == NX_DIST_K) {
+              const int q = k0 / dist.k_rows;
+              mb = &dist.b[q];
+              bk0 = k0 - q * dist.k_rows;
             }
           }
           if (!A_MN) {
-            tma_load_3d(sa, ma, &full_bar[stage], k0, am0, w.batch);
+            tma_load_3d(sa, ma, &full_bar[stage], ak0, am0, w.batch);
           } else {
 #pragma unroll
             for (int j = 0; j < kBM / 64; ++j)
-              tma_load_3d(sa + j * (64 * kBK * 2), ma, &full_bar[stage], am0 + 64 * j, k0, w.batch);
+              tma_load_3d(sa + j * (64 * kBK * 2), ma, &full_bar[stage], am0 + 64 * j, ak0, w.batch);
           }
           if (!B_MN) {
-            tma_load_3d(sb, mb, &full_bar[stage], k0, bn0, w.batch);
+            tma_load_3d(sb, mb, &full_bar[stage], bk0, bn0, w.batch);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_3d(sb + j * (64 * kBK * 2), mb, &full_bar[stage], bn0 + 64 * j, k0, w.batch);
+              tma_load_3d(sb + j * (64 * kBK * 2), mb, &full_bar[stage], bn0 + 64 * j, bk0, w.batch);
           }
           if (++stage == C::kStages) {
             stage = 0;
@@ -604,6 +771,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty_bar[acc]), 0));
         }
+        if (p.rs_ranks > 1 && lane == 0) {
+          // reduce-scatter form: this warp's part of the tile is in global memory -> count it on the tile's row block
+          tma_store_wait_all();
+          __threadfence();
+          atomicAdd(p.rs_done + (w.m0 - m_off) / (2 * kBM), 1);
+        }
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1u;
@@ -713,6 +886,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
 
         if constexpr (DIST) {
+          if (dist.out_scatter == NX_SCATTER_SLOTS_BF16) {
+            // GEMM -> reduce-scatter, slot form: this rank's partial tile goes, as BF16, into slot `rank` of the
+            // buffer of the rank that owns these rows; the owner sums the slots in rank order afterwards
+            const int owner = row / dist.out_rows;
+            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(dist.out[owner]) +
+                                (static_cast<int64_t>(dist.rank) * dist.out_rows + (row - owner * dist.out_rows)) * p.ldo + col0;
+            store_row32_bf16(op, (valid == 32) && ((p.ldo & 7) == 0), valid, v);
+            continue;
+          }
           if (dist.out_scatter) {
             // GEMM -> reduce-scatter: add the tile into the FP32 buffer of the rank that owns these rows
             const int owner = row / dist.out_rows;
@@ -909,6 +1091,12 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const DevParams& p
   if (max_clusters < 0) return -3;
   int clusters = std::min(p.num_units, max_clusters);
   if (max_ctas > 1) clusters = std::min(clusters, max_ctas / 2);
+  if (p.ag_ranks > 1 || p.rs_ranks > 1) {
+    // copier clusters share the device with the GEMM clusters: all of them must be resident at once
+    const int copier_clusters = (p.ag_ranks > 1 ? p.ag_copiers : p.rs_copiers) / 2;
+    if (copier_clusters < 1 || copier_clusters >= max_clusters) return -1;
+    clusters = std::min(clusters, max_clusters - copier_clusters) + copier_clusters;
+  }
   cfg.gridDim = dim3(2 * clusters);
   const uint32_t idesc = make_idesc(in_fmt, in_fmt, A_MN, B_MN, 2 * kBM, 256);
   DistParam<false> dist{};
@@ -998,7 +1186,43 @@ extern "C" int nx_splitk_reduce_epilogue(const float* workspace, void* out, int 
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
+namespace {
+int gemm_impl(const NxGemmArgs* a, const NxGemmAg* ag, nx_stream_t stream_, const NxGemmRs* rs = nullptr);
+}
+extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) { return gemm_impl(a, nullptr, stream_); }
+
+// GEMM fused with the reduce-scatter of its output; see nx_api_comm.h.
+extern "C" int nx_gemm_rs(const NxGemmArgs* a, const NxGemmRs* rs, nx_stream_t stream_) {
+  if (a == nullptr || rs == nullptr) return -1;
+  const int n = rs->n_ranks;
+  if (n < 2 || n > NX_MAX_PEERS || rs->rank < 0 || rs->rank >= n || rs->done == nullptr) return -1;
+  if (a->in_dtype != NX_BF16 || a->out_dtype != NX_BF16 || a->batch != 1 || a->split_k > 1 || a->accumulate) return -1;
+  if (a->bias != nullptr || a->residual != nullptr || a->aux_in != nullptr || a->aux_out != nullptr || a->act != NX_ACT_NONE)
+    return -1;
+  if (a->m % n || (a->m / n) % (2 * kBM) || a->n < 256 || (a->n & 7) || (a->ldo & 7)) return -1;
+  const int c = rs->copier_ctas;
+  if (c < 2 || c > 2 * kBM || (c & (c - 1))) return -1;  // a power of two that divides the 256-row block
+  for (int q = 0; q < n; ++q)
+    if (rs->slots[q] == nullptr || (reinterpret_cast<uintptr_t>(rs->slots[q]) & 15)) return -1;
+  return gemm_impl(a, nullptr, stream_, rs);
+}
+
+// All-gather fused into the GEMM; see nx_api_comm.h.
+extern "C" int nx_gemm_ag(const NxGemmArgs* a, const NxGemmAg* ag, nx_stream_t stream_) {
+  if (a == nullptr || ag == nullptr) return -1;
+  const int n = ag->n_ranks;
+  if (n < 2 || n > NX_MAX_PEERS || ag->rank < 0 || ag->rank >= n || ag->counter == nullptr) return -1;
+  if (a->in_dtype != NX_BF16 || a->a_mn_major || a->batch != 1 || a->split_k > 1) return -1;
+  if (a->m % n || (a->m / n) % (2 * kBM) || a->n < 256 || (a->k & 7)) return -1;
+  if (ag->copier_ctas < 2 || (ag->copier_ctas & 1)) return -1;
+  for (int q = 0; q < n; ++q)
+    if (ag->gather[q] == nullptr || ag->flags[q] == nullptr || (reinterpret_cast<uintptr_t>(ag->gather[q]) & 15)) return -1;
+  if (a->a != ag->gather[ag->rank]) return -1;  // A is this rank's gather buffer
+  return gemm_impl(a, ag, stream_);
+}
+
+namespace {
+int gemm_impl(const NxGemmArgs* a, const NxGemmAg* ag, nx_stream_t stream_, const NxGemmRs* rs) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (a == nullptr || a->m <= 0 || a->n <= 0 || a->k <= 0 || a->batch <= 0) return -1;
   const bool fp8 = a->in_dtype == NX_E4M3 || a->in_dtype == NX_E5M2;
@@ -1024,7 +1248,9 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
   // Two-CTA tiles (256 x 256 over a cluster of two) whenever the problem has at least one such tile of BF16/FP16.
   static const bool single_only = std::getenv("NX_GEMM_SINGLE_CTA") != nullptr;  // measurement switch
   static bool pair_ok = true;  // cleared when the device cannot place clusters of two
-  const bool pair = bn == 256 && !fp8 && a->m >= 2 * kBM && pair_ok && !single_only && (a->max_ctas <= 0 || a->max_ctas >= 2);
+  const bool pair = bn == 256 && !fp8 && a->m >= 2 * kBM && pair_ok && (!single_only || ag != nullptr || rs != nullptr) &&
+                    (a->max_ctas <= 0 || a->max_ctas >= 2);
+  if ((ag != nullptr || rs != nullptr) && !pair) return -3;  // the fused forms run on the CTA-pair kernel only
   const int tile_m = pair ? 2 * kBM : kBM;
 
   const int bk = fp8 ? 2 * kBK : kBK;  // elements per 128-byte swizzle row
@@ -1070,6 +1296,21 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
   // matrix (its whole K-panel set stays in L2 while each A tile is fetched from DRAM once), else along M.
   static const char* order_env = std::getenv("NX_GEMM_ORDER");  // measurement switch: "m" or "n"
   p.n_fastest = order_env ? (order_env[0] == 'n') : (a->n < a->m);
+  if (ag != nullptr) {
+    p.n_fastest = 1;  // all column tiles of a row block run together: rows are consumed in their order of arrival
+    p.ag_ranks = ag->n_ranks;
+    p.ag_rank = ag->rank;
+    p.ag_rows = a->m / ag->n_ranks;
+    p.rot_rows = ag->rank * p.ag_rows;
+    p.ag_copiers = ag->copier_ctas;
+    p.ag_ld_bytes = a->lda * 2;
+    p.ag_row_bytes = a->k * 2;
+    p.ag_counter = ag->counter;
+    for (int q = 0; q < ag->n_ranks; ++q) {
+      p.ag_gather[q] = ag->gather[q];
+      p.ag_flags[q] = ag->flags[q];
+    }
+  }
 
   const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                      : (a->in_dtype == NX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
@@ -1120,8 +1361,20 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
     const CUtensorMap* px = (p.tma_store && a->aux_out) ? &tx : nullptr;
     // the lean epilogue covers what the training step's BF16-output GEMMs ask for
     static const bool generic_only = std::getenv("NX_GEMM_GENERIC_EPILOGUE") != nullptr;  // measurement switch
-    const bool fast = p.tma_store && !generic_only && a->residual == nullptr && a->scale_a == nullptr && a->scale_b == nullptr &&
-                      a->amax_out == nullptr && (reinterpret_cast<uintptr_t>(a->bias) & 15) == 0 &&
+    if (rs != nullptr) {
+      if (!p.tma_store) return -1;  // the reduce-scatter form counts tiles in the lean epilogue (tiled BF16 stores)
+      p.n_fastest = 1;              // row blocks finish one after the other, in ring order
+      p.rs_ranks = rs->n_ranks;
+      p.rs_rank = rs->rank;
+      p.rs_rows = a->m / rs->n_ranks;
+      p.rot_rows = ((rs->rank + 1) % rs->n_ranks) * p.rs_rows;  // the rows this rank keeps come last
+      p.rs_copiers = rs->copier_ctas;
+      p.rs_expected = 16 * p.tiles_n;
+      p.rs_done = rs->done;
+      for (int q = 0; q < rs->n_ranks; ++q) p.rs_slots[q] = rs->slots[q];
+    }
+    const bool fast = (rs != nullptr || !generic_only) && p.tma_store && a->residual == nullptr && a->scale_a == nullptr &&
+                      a->scale_b == nullptr && a->amax_out == nullptr && (reinterpret_cast<uintptr_t>(a->bias) & 15) == 0 &&
                       (a->aux_in == nullptr || (reinterpret_cast<uintptr_t>(a->aux_in) & 15) == 0) &&
                       (a->act == NX_ACT_NONE || a->act == NX_ACT_GELU || (a->act == NX_ACT_DGELU && a->aux_in != nullptr));
 #define NX_PAIR(AM_, BM_) \
@@ -1135,7 +1388,7 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
     if (rc != -3) return rc;
     // no room for clusters of two on this device: rebuild the launch for single-CTA tiles
     pair_ok = false;
-    return nx_gemm(a, stream_);
+    return gemm_impl(a, ag, stream_, rs);
   }
 
 #define NX_LAUNCH(BN_, AM_, BM_) \
@@ -1155,24 +1408,35 @@ extern "C" int nx_gemm(const NxGemmArgs* a, nx_stream_t stream_) {
 #undef NX_LAUNCH
   return rc;
 }
+}  // namespace
 
-// K-major operands only; batch 1; no split-K.  Rows per rank must be multiples of the tile size.
+// BF16; batch 1; no split-K.  Rows (or K rows) per rank must be multiples of the tile size.
 extern "C" int nx_gemm_dist(const NxGemmArgs* a, const NxGemmDist* d, nx_stream_t stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (a == nullptr || d == nullptr || a->m <= 0 || a->n <= 0 || a->k <= 0 || a->status == nullptr) return -1;
-  if (a->batch != 1 || a->a_mn_major || a->b_mn_major || a->in_dtype != NX_BF16) return -1;
+  if (a->batch != 1 || a->in_dtype != NX_BF16) return -1;
   const int n = d->n_ranks;
-  if (n < 1 || n > NX_MAX_PEERS || (a->lda & 7) || (a->ldb & 7)) return -1;
-  if (d->a_sharded && (a->m % n || (a->m / n) % kBM)) return -1;
+  if (n < 1 || n > NX_MAX_PEERS || d->rank < 0 || d->rank >= n || (a->lda & 7) || (a->ldb & 7)) return -1;
+  const bool a_mn = a->a_mn_major != 0, b_mn = a->b_mn_major != 0;
+  // a row-sharded operand is K-major, a K-sharded one MN-major
+  if (d->a_sharded == NX_DIST_ROWS && (a_mn || a->m % n || (a->m / n) % kBM)) return -1;
+  if (d->a_sharded == NX_DIST_K && (!a_mn || a->k % n || (a->k / n) % kBK)) return -1;
+  if (d->b_sharded == NX_DIST_K && (!b_mn || a->k % n || (a->k / n) % kBK)) return -1;
+  if (d->a_sharded < 0 || d->a_sharded > 2 || d->b_sharded < 0 || d->b_sharded > 2 || d->out_scatter < 0 ||
+      d->out_scatter > 2)
+    return -1;
   int bn = (a->n >= 256) ? 256 : 128;
-  if (d->b_sharded) {
-    if (a->n % n) return -1;
+  if (d->b_sharded == NX_DIST_ROWS) {
+    if (b_mn || a->n % n) return -1;
     const int per = a->n / n;
     if (per % 256 == 0) bn = 256;
     else if (per % 128 == 0) bn = 128;
     else return -1;
   }
-  if (d->out_scatter && (a->m % n || (a->m / n) % kBM || a->out_dtype != NX_F32)) return -1;
+  if (d->out_scatter && (a->m % n || (a->m / n) % kBM)) return -1;
+  if (d->out_scatter == NX_SCATTER_ADD_F32 && a->out_dtype != NX_F32) return -1;
+  if (d->out_scatter == NX_SCATTER_SLOTS_BF16 && a->out_dtype != NX_BF16) return -1;
+  if (a_mn && !b_mn) return -1;  // (MN, K) is not instantiated for the distributed kernel
 
   DevParams p{};
   p.out = a->out;
@@ -1205,37 +1469,64 @@ extern "C" int nx_gemm_dist(const NxGemmArgs* a, const NxGemmDist* d, nx_stream_
   p.amax_out = nullptr;
   p.num_units = p.tiles_m * p.tiles_n;
   p.alpha = a->alpha;
+  // units that run together share the smaller operand through L2 (same rule as nx_gemm)
+  p.n_fastest = a->n < a->m;
 
   const CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   DistParam<true> dist{};
   dist.a_sharded = d->a_sharded;
   dist.b_sharded = d->b_sharded;
   dist.out_scatter = d->out_scatter;
-  dist.a_rows = d->a_sharded ? a->m / n : a->m;
-  dist.b_rows = d->b_sharded ? a->n / n : a->n;
+  dist.rank = d->rank;
+  dist.a_rows = d->a_sharded == NX_DIST_ROWS ? a->m / n : a->m;
+  dist.b_rows = d->b_sharded == NX_DIST_ROWS ? a->n / n : a->n;
   dist.out_rows = d->out_scatter ? a->m / n : a->m;
+  dist.k_rows = (d->a_sharded == NX_DIST_K || d->b_sharded == NX_DIST_K) ? a->k / n : a->k;
   CUtensorMap ta, tb;
   int rc;
+  // K-major operand: [rows][K] with a {64, tile rows} box; MN-major operand: [K][rows] with a {64, 64} box
+  auto map_a = [&](CUtensorMap* t, const void* base, int rows, int krows) {
+    return a_mn ? nx::make_tensor_map_3d(t, dt, 2, base, rows, krows, 1, a->lda, 0, 64, kBK)
+                : nx::make_tensor_map_3d(t, dt, 2, base, krows, rows, 1, a->lda, 0, kBK, kBM);
+  };
+  auto map_b = [&](CUtensorMap* t, const void* base, int rows, int krows) {
+    return b_mn ? nx::make_tensor_map_3d(t, dt, 2, base, rows, krows, 1, a->ldb, 0, 64, kBK)
+                : nx::make_tensor_map_3d(t, dt, 2, base, krows, rows, 1, a->ldb, 0, kBK, bn);
+  };
+  const int a_map_rows = d->a_sharded == NX_DIST_ROWS ? dist.a_rows : a->m;
+  const int b_map_rows = d->b_sharded == NX_DIST_ROWS ? dist.b_rows : a->n;
+  const int a_map_k = d->a_sharded == NX_DIST_K ? dist.k_rows : a->k;
+  const int b_map_k = d->b_sharded == NX_DIST_K ? dist.k_rows : a->k;
   for (int q = 0; q < n; ++q) {
     if (d->a_sharded) {
-      if (reinterpret_cast<uintptr_t>(d->a_ptrs[q]) & 15) return -1;
-      if ((rc = nx::make_tensor_map_3d(&dist.a[q], dt, 2, d->a_ptrs[q], a->k, dist.a_rows, 1, a->lda, 0, kBK, kBM))) return rc;
+      if (d->a_ptrs[q] == nullptr || (reinterpret_cast<uintptr_t>(d->a_ptrs[q]) & 15)) return -1;
+      if ((rc = map_a(&dist.a[q], d->a_ptrs[q], a_map_rows, a_map_k))) return rc;
     }
     if (d->b_sharded) {
-      if (reinterpret_cast<uintptr_t>(d->b_ptrs[q]) & 15) return -1;
-      if ((rc = nx::make_tensor_map_3d(&dist.b[q], dt, 2, d->b_ptrs[q], a->k, dist.b_rows, 1, a->ldb, 0, kBK, bn))) return rc;
+      if (d->b_ptrs[q] == nullptr || (reinterpret_cast<uintptr_t>(d->b_ptrs[q]) & 15)) return -1;
+      if ((rc = map_b(&dist.b[q], d->b_ptrs[q], b_map_rows, b_map_k))) return rc;
     }
+    if (d->out_scatter && d->out_ptrs[q] == nullptr) return -1;
     dist.out[q] = static_cast<float*>(d->out_ptrs[q]);
   }
   const void* a0 = d->a_sharded ? d->a_ptrs[d->rank] : a->a;
   const void* b0 = d->b_sharded ? d->b_ptrs[d->rank] : a->b;
-  if ((rc = nx::make_tensor_map_3d(&ta, dt, 2, a0, a->k, d->a_sharded ? dist.a_rows : a->m, 1, a->lda, 0, kBK, kBM))) return rc;
-  if ((rc = nx::make_tensor_map_3d(&tb, dt, 2, b0, a->k, d->b_sharded ? dist.b_rows : a->n, 1, a->ldb, 0, kBK, bn))) return rc;
+  if (a0 == nullptr || b0 == nullptr) return -1;
+  if ((rc = map_a(&ta, a0, a_map_rows, a_map_k))) return rc;
+  if ((rc = map_b(&tb, b0, b_map_rows, b_map_k))) return rc;
   int sms = nx_sm_count();
   if (sms <= 0) return -2;
   const int grid = p.num_units < sms ? p.num_units : sms;
-  if (bn == 256) return launch_variant<256, false, false, true>(ta, tb, p, kFmtBF16, grid, stream, dist);
-  return launch_variant<128, false, false, true>(ta, tb, p, kFmtBF16, grid, stream, dist);
+#define NX_DIST_LAUNCH(BN_, AM_, BM_) launch_variant<BN_, AM_, BM_, true>(ta, tb, p, kFmtBF16, grid, stream, dist)
+  if (bn == 256) {
+    if (!a_mn && !b_mn) return NX_DIST_LAUNCH(256, false, false);
+    if (!a_mn && b_mn) return NX_DIST_LAUNCH(256, false, true);
+    return NX_DIST_LAUNCH(256, true, true);
+  }
+  if (!a_mn && !b_mn) return NX_DIST_LAUNCH(128, false, false);
+  if (!a_mn && b_mn) return NX_DIST_LAUNCH(128, false, true);
+  return NX_DIST_LAUNCH(128, true, true);
+#undef NX_DIST_LAUNCH
 }
 
 #ifdef NX_PROFILE_MMA

@@ -63,17 +63,74 @@ int nx_moe_combine(const NxPeerTable* bufs, const int32_t* expert, const int32_t
 int nx_vocab_ce_exchange(const float* local_stats, const NxPeerTable* tables, const NxPeerTable* flags, int rank, int n,
                          int rows, int* counter, float* merged, int* status, nx_stream_t stream);
 
-// Distributed GEMM (see nx_gemm): operand A and/or B is row-sharded over the ranks and its tiles are
-// fetched by (non-multicast) TMA straight from the owning rank's memory; the output can be
-// reduce-scattered by adding each tile into the owning rank's FP32 buffer.
+// Distributed GEMM (see nx_gemm): an operand is sharded over the ranks and its tiles are fetched by
+// (non-multicast) TMA straight from the owning rank's memory, and/or the output is reduce-scattered from
+// inside the epilogue.  BF16 operands; each operand K-major or MN-major as in nx_gemm (a_mn_major / b_mn_major).
+//   a_sharded / b_sharded = 1 (NX_DIST_ROWS): the operand is K-major and rank q holds its rows
+//       [q*M/n, (q+1)*M/n) (A) or [q*N/n, (q+1)*N/n) (B): all-gather fused into the GEMM.
+//   a_sharded / b_sharded = 2 (NX_DIST_K): the operand is MN-major (stored [K][M or N]) and rank q holds the
+//       K rows [q*K/n, (q+1)*K/n): the contraction runs over a dimension that is spread over the ranks
+//       (weight gradients of a sequence-parallel layer).  K/n must be a multiple of 64.
+//   out_scatter = 1 (NX_SCATTER_ADD_F32): rank q owns output rows [q*M/n, (q+1)*M/n); every rank adds its partial
+//       tile into the owner's FP32 buffer with vector reductions (order of the additions is not fixed).
+//   out_scatter = 2 (NX_SCATTER_SLOTS_BF16): the owner's buffer is BF16 [n][M/n][ldo]; rank r stores its partial
+//       tile into slot r, and the owner sums the n slots in rank order afterwards (nx_comm_sum_slots): half the
+//       NVLink bytes of the FP32 form and a deterministic result.
+#define NX_DIST_ROWS 1
+#define NX_DIST_K 2
+#define NX_SCATTER_ADD_F32 1
+#define NX_SCATTER_SLOTS_BF16 2
 typedef struct NxGemmDist {
-  const void* a_ptrs[NX_MAX_PEERS];  // when a_sharded: rank q holds rows [q*M/n, (q+1)*M/n) of A (K-major)
-  const void* b_ptrs[NX_MAX_PEERS];  // when b_sharded: rank q holds rows [q*N/n, (q+1)*N/n) of B (K-major)
-  void* out_ptrs[NX_MAX_PEERS];      // when out_scatter: rank q owns output rows [q*M/n, (q+1)*M/n), FP32
+  const void* a_ptrs[NX_MAX_PEERS];  // per rank: its part of A (used when a_sharded)
+  const void* b_ptrs[NX_MAX_PEERS];  // per rank: its part of B (used when b_sharded)
+  void* out_ptrs[NX_MAX_PEERS];      // per rank: its output buffer (used when out_scatter)
   int32_t n_ranks, rank;
   int32_t a_sharded, b_sharded, out_scatter;
 } NxGemmDist;
 int nx_gemm_dist(const NxGemmArgs* args, const NxGemmDist* dist, nx_stream_t stream);
+
+// All-gather fused into ONE tcgen05 GEMM kernel (the CTA-pair kernel of nx_gemm), push form.  Every rank owns a
+// peer-mapped gather buffer [M][lda] (BF16) whose row block `rank` it has already filled; args->a must be
+// gather[rank].  The last `copier_ctas` CTAs of the grid store this rank's rows into every peer's buffer, 128 rows
+// at a time, and raise flags[peer][rank][chunk] to the call's generation (*counter + 1, release at system scope).
+// The GEMM CTAs compute the local row block first and then the other ranks' blocks in ring order, each producer
+// waiting (bounded: kStatusTimeoutPeer) for the flag of the rows it is about to load.  Each row crosses NVLink once
+// and the transfer overlaps the tensor-core work tile by tile; afterwards every rank also holds the complete
+// gathered A for later use (e.g. the weight-gradient GEMM).  The caller bumps *counter on every rank after the
+// call (nx_comm_bump) and orders re-use of the gather buffers with nx_comm_barrier.
+// Requirements: BF16, K-major A, M / n_ranks a multiple of 256, N >= 256, copier_ctas even and >= 2.
+typedef struct NxGemmAg {
+  void* gather[NX_MAX_PEERS];
+  int* flags[NX_MAX_PEERS];   // per rank: int[n_ranks][M / n_ranks / 128], zero-initialised once
+  const int* counter;         // this rank's generation counter of the flag array (device memory)
+  int32_t n_ranks, rank, copier_ctas;
+} NxGemmAg;
+int nx_gemm_ag(const NxGemmArgs* args, const NxGemmAg* ag, nx_stream_t stream);
+// GEMM fused with the reduce-scatter of its output in ONE kernel (the CTA-pair kernel of nx_gemm), push form.
+// args->out is a LOCAL BF16 [M][ldo] buffer that receives this rank's partial sums through the kernel's normal tiled
+// stores; every epilogue warp then counts its finished tile on done[row block].  The last `copier_ctas` CTAs of the
+// grid wait for a 256-row block to be complete and store it into slot `rank` of the buffer slots[owner]
+// (BF16 [n_ranks][M / n_ranks][ldo]) of the rank that owns those rows, over NVLink, while the tensor-core CTAs are
+// already on the next blocks; work starts with the next rank's rows and ends with this rank's own.  Afterwards
+// (nx_comm_barrier, then nx_comm_sum_slots) each owner adds the n slots in rank order: deterministic, BF16 on the wire.
+// `done`: int[M / 256] in local device memory, zeroed by the caller before every call.
+// Requirements: BF16 in and out, no epilogue extras, M / n_ranks a multiple of 256, N >= 256, copier_ctas a power
+// of two in [2, 256].
+typedef struct NxGemmRs {
+  void* slots[NX_MAX_PEERS];
+  int* done;
+  int32_t n_ranks, rank, copier_ctas;
+} NxGemmRs;
+int nx_gemm_rs(const NxGemmArgs* args, const NxGemmRs* rs, nx_stream_t stream);
+// *counter += 1 (one thread), stream-ordered after the kernels that read it.
+int nx_comm_bump(int* counter, nx_stream_t stream);
+
+// out[r][c] = (residual ? residual[r][c] : 0) + sum_{q < n} slots[q][r][c] (q in order, FP32 accumulation):
+// the owner's half of the slot form of GEMM -> reduce-scatter.  slots: BF16 [n][rows][ld_slots]; residual / out:
+// FP32 or BF16 with row strides ld_res / ld_out; out_lp (optional): a BF16 copy of the result, row stride ld_lp.
+int nx_comm_sum_slots(const void* slots, int n, int rows, int cols, int64_t ld_slots, const void* residual,
+                      int res_dtype, int64_t ld_res, void* out, int out_dtype, int64_t ld_out, void* out_lp,
+                      int64_t ld_lp, nx_stream_t stream);
 
 #ifdef __cplusplus
 }

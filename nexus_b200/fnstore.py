@@ -24,25 +24,104 @@ from typing import Callable, Dict
 
 import torch
 
-_ACTIVATION_SOURCES: Dict[str, Callable] = {}
-_MODULE_FACTORIES: Dict[str, Callable] = {}
+_ACTIVATION_SOURCES: Dict[str, tuple] = {}     # name -> (forward, backward or None)
+_MODULE_SOURCES: Dict[str, tuple] = {}         # name -> (forward or factory, backward or None, parameter shapes)
+_MODULE_FACTORIES: Dict[str, Callable] = {}    # name -> callable returning the torch module that runs the body
 
 
-def register_python_activation(name: str, fn: Callable) -> None:
+class _ScalarFn(torch.autograd.Function):
+    """Elementwise application of a body written for one number; its derivative comes from the backward body, or
+    from a central difference when none was given."""
+
+    @staticmethod
+    def forward(ctx, x, fwd, bwd):
+        flat = x.detach().reshape(-1).tolist()
+        y = torch.tensor([float(fwd(v)) for v in flat], dtype=x.dtype, device=x.device).view(x.shape)
+        ctx.save_for_backward(x)
+        ctx.fwd, ctx.bwd = fwd, bwd
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        (x,) = ctx.saved_tensors
+        flat = x.detach().reshape(-1).tolist()
+        if ctx.bwd is not None:
+            d = [float(ctx.bwd(v)) for v in flat]
+        else:
+            d = []
+            for v in flat:
+                h = 1e-3 * max(1.0, abs(v))
+                d.append((float(ctx.fwd(v + h)) - float(ctx.fwd(v - h))) / (2 * h))
+        return g * torch.tensor(d, dtype=g.dtype, device=g.device).view(g.shape), None, None
+
+
+def tensor_level(forward: Callable, backward=None) -> Callable:
+    """Runtime form of an activation body.  A body that only uses arithmetic runs on the whole tensor (autograd
+    differentiates it); one that needs real numbers (``math.tanh(x)``) or brings its own derivative is applied
+    element by element."""
+    def run(x: torch.Tensor) -> torch.Tensor:
+        if backward is None:
+            import warnings
+            try:
+                with warnings.catch_warnings():
+                    warnings.simplefilter("ignore")
+                    y = forward(x)
+                if isinstance(y, torch.Tensor) and y.shape == x.shape:
+                    return y
+            except (TypeError, ValueError, RuntimeError):
+                pass
+        return _ScalarFn.apply(x, forward, backward)
+    return run
+
+
+def remember(name: str, forward: Callable, backward=None) -> None:
+    """Registers an activation's bodies (checked: plain functions closing over numbers only) for archiving."""
+    _check(forward)
+    if backward is not None:
+        _check(backward)
+    _ACTIVATION_SOURCES[name] = (forward, backward)
+
+
+def register_python_activation(name: str, fn: Callable, backward=None) -> None:
     from .nn.modules import register_activation
-    _ACTIVATION_SOURCES[name] = fn
-    register_activation(name, fn)
+    _ACTIVATION_SOURCES[name] = (fn, backward)
+    register_activation(name, tensor_level(fn, backward))
 
 
 def register_python_module(name: str, factory: Callable) -> None:
+    """``factory()`` returns the torch module that implements the body."""
+    _MODULE_SOURCES[name] = (factory, None, [])
     _MODULE_FACTORIES[name] = factory
+
+
+def remember_module(name: str, forward: Callable, backward=None, shapes=None, builder=None) -> None:
+    """Registers a module given as ``forward(values, params)`` / ``backward(grad, params)`` bodies over the shell's
+    tensors plus its parameter shapes; ``builder(name, forward, backward, shapes)`` returns the runtime factory."""
+    _check(forward)
+    if backward is not None:
+        _check(backward)
+    shapes = [list(map(int, s)) for s in (shapes or [])]
+    _MODULE_SOURCES[name] = (forward, backward, shapes)
+    if builder is None:
+        builder = _shell_module_builder()
+    _MODULE_FACTORIES[name] = builder(name, forward, backward, shapes)
+
+
+def _shell_module_builder():
+    from nexus import _shell      # the shell owns the tensor type those bodies are written against
+    return _shell._py_module_factory
+
+
+def set_shell_builders(activation_wrapper=None, module_builder=None) -> None:
+    """Kept for the shell's start-up: nothing to install, the runtime forms live in this module."""
 
 
 def module_factory(name: str):
     from .nn.modules import PythonModule
     if name not in _MODULE_FACTORIES:
         raise RuntimeError(f"python module body '{name}' is not registered in this process")
-    return PythonModule(name, _MODULE_FACTORIES[name]())
+    made = _MODULE_FACTORIES[name]()
+    return made if isinstance(made, PythonModule) else PythonModule(name, made)
 
 
 _ACTIVATION, _MODULE = 1, 2
@@ -118,20 +197,32 @@ def payload_for(model) -> bytes:
         if isinstance(m, Module):
             if m.kind == KIND["NamedActivation"] and m.layer_name in _ACTIVATION_SOURCES:
                 acts[m.layer_name] = _ACTIVATION_SOURCES[m.layer_name]
-            if m.kind == KIND["PythonModule"] and m.layer_name in _MODULE_FACTORIES:
-                mods[m.layer_name] = _MODULE_FACTORIES[m.layer_name]
+            if m.kind == KIND["PythonModule"] and m.layer_name in _MODULE_SOURCES:
+                mods[m.layer_name] = _MODULE_SOURCES[m.layer_name]
     if not acts and not mods:
         return b""
     buf = bytearray(b"NXPY") + struct.pack("<HI", 1, len(acts) + len(mods))
-    for kind, table in ((_ACTIVATION, acts), (_MODULE, mods)):
-        for name, fn in table.items():
-            _check(fn)
-            raw = name.encode("utf-8")
-            buf += struct.pack("<BI", kind, len(raw)) + raw
-            _write_code(buf, fn)
-            _write_code(buf, None)          # backward slot: autograd differentiates the forward body
-            if kind == _MODULE:
-                buf += struct.pack("<I", 0)   # parameter shapes live in the module's own tensors
+    for name, (fwd, bwd) in acts.items():
+        _check(fwd)
+        if bwd is not None:
+            _check(bwd)
+        raw = name.encode("utf-8")
+        buf += struct.pack("<BI", _ACTIVATION, len(raw)) + raw
+        _write_code(buf, fwd)
+        _write_code(buf, bwd)
+    for name, (fwd, bwd, shapes) in mods.items():
+        _check(fwd)
+        if bwd is not None:
+            _check(bwd)
+        raw = name.encode("utf-8")
+        buf += struct.pack("<BI", _MODULE, len(raw)) + raw
+        _write_code(buf, fwd)
+        _write_code(buf, bwd)
+        buf += struct.pack("<I", len(shapes))
+        for shp in shapes:
+            buf += struct.pack("<I", len(shp))
+            for dim in shp:
+                buf += struct.pack("<Q", int(dim))
     return bytes(buf)
 
 
@@ -153,18 +244,24 @@ def restore_payload(blob: bytes) -> None:
             name = bytes(view[off: off + nlen]).decode("utf-8")
             off += nlen
             forward, off = _read_code(view, off)
-            _backward, off = _read_code(view, off)
+            backward, off = _read_code(view, off)
             if kind == _MODULE:
                 (nshape,) = struct.unpack_from("<I", view, off)
                 off += 4
+                shapes = []
                 for _s in range(nshape):
                     (rank,) = struct.unpack_from("<I", view, off)
-                    off += 4 + 8 * rank
+                    off += 4
+                    shapes.append([int(v) for v in struct.unpack_from("<%dQ" % rank, view, off)])
+                    off += 8 * rank
                 if forward is not None and name not in _MODULE_FACTORIES:
-                    register_python_module(name, forward)
+                    if forward.__code__.co_argcount == 0 and backward is None and not shapes:
+                        register_python_module(name, forward)      # a factory returning the torch module
+                    else:
+                        remember_module(name, forward, backward, shapes)
             elif kind == _ACTIVATION:
                 if forward is not None and name not in _ACTIVATION_SOURCES:
-                    register_python_activation(name, forward)
+                    register_python_activation(name, forward, backward)
             else:
                 raise ValueError("nxs python payload: unknown record kind %d" % kind)
     except struct.error:

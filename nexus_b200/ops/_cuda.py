@@ -468,14 +468,15 @@ def _alibi_ptr(alibi_slopes, heads, device):
 
 
 def attention_fwd(q, k, v, *, causal=True, window=0, scale=None, out=None, merge_o=None, merge_lse=None,
-                  softcap=0.0, alibi_slopes=None, dropout_p=0.0, dropout_seed=0, dropout_offset=0):
+                  softcap=0.0, alibi_slopes=None, dropout_p=0.0, dropout_seed=0, dropout_offset=0, lse=None):
     """q [B,Tq,H,D], k/v [B,Tk,Hkv,D] bf16 (strided views allowed).  Returns (o, lse[B,H,Tq]).
     ``merge_o`` (FP32 [B,Tq,H,D]) / ``merge_lse`` (FP32 [B,H,Tq]): running result of earlier key/value
     chunks; this chunk is merged into them in the kernel's epilogue (ring / chunked attention)."""
     B, Tq, H, D = q.shape
     Tk, Hkv = k.shape[1], k.shape[2]
     o = torch.empty((B, Tq, H, D), dtype=q.dtype, device=q.device) if out is None else out
-    lse = torch.empty((B, H, Tq), dtype=torch.float32, device=q.device)
+    if lse is None:
+        lse = torch.empty((B, H, Tq), dtype=torch.float32, device=q.device)
     a = AttnArgs()
     a.q, a.k, a.v, a.o = _view(q), _view(k), _view(v), _view(o)
     a.lse = lse.data_ptr()

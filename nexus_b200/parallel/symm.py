@@ -214,34 +214,152 @@ def fused_all_reduce(ws: SymmetricWorkspace, src: SymmetricBuffer, dst: Symmetri
 
 def gemm_dist(ws: SymmetricWorkspace, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *,
               a_peers: Optional[SymmetricBuffer] = None, b_peers: Optional[SymmetricBuffer] = None,
-              out_peers: Optional[SymmetricBuffer] = None, bias=None, act=None, m: Optional[int] = None,
-              n: Optional[int] = None) -> torch.Tensor:
-    """out = epilogue(A @ B^T) where A and/or B is row-sharded over the group and read tile by tile from
-    its owners (all-gather fused into the GEMM), and/or the FP32 output is added into the owner of each
-    row block (GEMM fused with reduce-scatter).  ``a`` / ``b`` are this rank's (local) operands."""
+              out_peers: Optional[SymmetricBuffer] = None, a_mn: bool = False, b_mn: bool = False,
+              a_shard: str = "rows", b_shard: str = "rows", scatter: str = "add_f32", accumulate: bool = False,
+              bias=None, act=None, m: Optional[int] = None, n: Optional[int] = None, k: Optional[int] = None,
+              a_offset: int = 0, b_offset: int = 0) -> torch.Tensor:
+    """out = epilogue(A @ B^T) on the tcgen05 GEMM with operands and/or output spread over the group.
+
+    ``a`` / ``b`` are this rank's (local) operands: K-major ``[rows, K]`` by default, MN-major ``[K, rows]`` with
+    ``a_mn`` / ``b_mn``.  ``a_peers`` / ``b_peers`` name the symmetric buffer that holds every rank's part of that
+    operand (``a_offset`` / ``b_offset``: element offset of the part inside the buffer):
+
+    * ``*_shard="rows"`` (K-major): rank q holds row block q; tiles are fetched from their owners (all-gather -> GEMM);
+    * ``*_shard="k"`` (MN-major): rank q holds K rows block q: the contraction dimension is spread over the ranks
+      (weight gradients under sequence parallelism).
+
+    ``out_peers``: GEMM -> reduce-scatter.  ``scatter="add_f32"`` adds partial tiles into the owner's FP32 buffer;
+    ``scatter="slots"`` stores them as BF16 into slot ``rank`` of the owner's ``[n][M/n][N]`` buffer (sum them with
+    `sum_slots` after a barrier: deterministic, half the NVLink bytes).  ``accumulate`` adds into ``out`` (beta = 1)."""
     g = K.GemmArgs()
-    k = a.shape[1]
-    M = m if m is not None else (a.shape[0] * ws.n if a_peers is not None else a.shape[0])
-    N = n if n is not None else (b.shape[0] * ws.n if b_peers is not None else b.shape[0])
+    kk = k if k is not None else (a.shape[0] if a_mn else a.shape[1])
+    a_rows = a.shape[1] if a_mn else a.shape[0]
+    b_rows = b.shape[1] if b_mn else b.shape[0]
+    a_mode = 0 if a_peers is None else (1 if a_shard == "rows" else 2)
+    b_mode = 0 if b_peers is None else (1 if b_shard == "rows" else 2)
+    M = m if m is not None else (a_rows * ws.n if a_mode == 1 else a_rows)
+    N = n if n is not None else (b_rows * ws.n if b_mode == 1 else b_rows)
+    if k is None and (a_mode == 2 or b_mode == 2):
+        kk = (a.shape[0] if a_mode == 2 else b.shape[0]) * ws.n
     g.a, g.b, g.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
     g.lda, g.ldb, g.ldo = a.stride(0), b.stride(0), out.stride(0)
-    g.m, g.n, g.k, g.batch = M, N, k, 1
+    g.m, g.n, g.k, g.batch = M, N, kk, 1
+    g.a_mn_major, g.b_mn_major = int(a_mn), int(b_mn)
     g.in_dtype, g.out_dtype = K._DT[a.dtype], K._DT[out.dtype]
+    g.accumulate = int(accumulate)
     if bias is not None:
         g.bias, g.bias_dtype = bias.data_ptr(), K._DT[bias.dtype]
     g.act, g.alpha, g.split_k = K.ACT[act], 1.0, 1
     g.status = K.status_word(a.device).data_ptr()
     d = GemmDist()
     d.n_ranks, d.rank = ws.n, ws.rank
+    ea, eb = a.element_size(), b.element_size()
     for q in range(ws.n):
         if a_peers is not None:
-            d.a_ptrs[q] = a_peers.ptrs[q]
+            d.a_ptrs[q] = a_peers.ptrs[q] + a_offset * ea
         if b_peers is not None:
-            d.b_ptrs[q] = b_peers.ptrs[q]
+            d.b_ptrs[q] = b_peers.ptrs[q] + b_offset * eb
         if out_peers is not None:
             d.out_ptrs[q] = out_peers.ptrs[q]
-    d.a_sharded, d.b_sharded, d.out_scatter = int(a_peers is not None), int(b_peers is not None), int(out_peers is not None)
+    d.a_sharded, d.b_sharded = a_mode, b_mode
+    d.out_scatter = 0 if out_peers is None else (1 if scatter == "add_f32" else 2)
     K._check(K.lib().nx_gemm_dist(C.byref(g), C.byref(d), K._stream()), "nx_gemm_dist")
+    return out
+
+
+class GemmAg(C.Structure):
+    _fields_ = [("gather", C.c_void_p * MAX_PEERS), ("flags", C.c_void_p * MAX_PEERS), ("counter", C.c_void_p),
+                ("n_ranks", C.c_int32), ("rank", C.c_int32), ("copier_ctas", C.c_int32)]
+
+
+class GatherSite:
+    """Flags and generation counter shared by the all-gather GEMMs of one group whose row blocks have ``rows_per_rank``
+    rows (any number of gather buffers can use one site, one call at a time)."""
+
+    def __init__(self, ws: SymmetricWorkspace, rows_per_rank: int):
+        if rows_per_rank % 256:
+            raise ValueError("all-gather GEMM: rows per rank must be a multiple of 256")
+        self.ws, self.rows = ws, rows_per_rank
+        self.flags = ws.alloc(ws.n * (rows_per_rank // 128), torch.int32)
+        self.flags.local.zero_()
+        self.counter = torch.zeros(1, dtype=torch.int32, device=ws.device)
+        torch.cuda.synchronize()
+        ws.pg.barrier()
+
+
+def gemm_ag(site: GatherSite, gather: SymmetricBuffer, b: torch.Tensor, out: torch.Tensor, *, k: int,
+            b_mn: bool = False, bias=None, act=None, aux_out=None, copier_ctas: int = 8) -> torch.Tensor:
+    """out[M, N] = epilogue(all-gather(A)[M, k] @ B^T) as ONE kernel.  ``gather`` is the group's peer-mapped gather
+    buffer ([M, k] BF16 on every rank); this rank has already written its own row block ``rank`` into its local copy.
+    Copier CTAs of the kernel push that block to every peer while the tensor-core CTAs work through the rows in their
+    order of arrival; on return (stream order) this rank's copy holds the complete gathered A.  The caller separates
+    two uses of the same gather buffer by ``ws.barrier()`` (peers may still be reading the old contents)."""
+    ws = site.ws
+    M = site.rows * ws.n
+    a = gather.local.view(M, k)
+    g = K.GemmArgs()
+    g.a, g.b, g.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    g.lda, g.ldb, g.ldo = k, b.stride(0), out.stride(0)
+    g.m, g.n, g.k, g.batch = M, (b.shape[1] if b_mn else b.shape[0]), k, 1
+    g.a_mn_major, g.b_mn_major = 0, int(b_mn)
+    g.in_dtype, g.out_dtype = K._DT[a.dtype], K._DT[out.dtype]
+    if bias is not None:
+        g.bias, g.bias_dtype = bias.data_ptr(), K._DT[bias.dtype]
+    if aux_out is not None:
+        g.aux_out, g.ld_aux = aux_out.data_ptr(), aux_out.stride(0)
+    g.act, g.alpha, g.split_k = K.ACT[act], 1.0, 1
+    g.status = K.status_word(a.device).data_ptr()
+    d = GemmAg()
+    for q in range(ws.n):
+        d.gather[q] = gather.ptrs[q]
+        d.flags[q] = site.flags.ptrs[q]
+    d.counter = site.counter.data_ptr()
+    d.n_ranks, d.rank, d.copier_ctas = ws.n, ws.rank, copier_ctas
+    L = K.lib()
+    K._check(L.nx_gemm_ag(C.byref(g), C.byref(d), K._stream()), "nx_gemm_ag")
+    K._check(L.nx_comm_bump(K._p(site.counter), K._stream()), "nx_comm_bump")
+    return out
+
+
+class GemmRs(C.Structure):
+    _fields_ = [("slots", C.c_void_p * MAX_PEERS), ("done", C.c_void_p), ("n_ranks", C.c_int32), ("rank", C.c_int32),
+                ("copier_ctas", C.c_int32)]
+
+
+def gemm_rs(ws: SymmetricWorkspace, a: torch.Tensor, b: torch.Tensor, partial: torch.Tensor, slots: SymmetricBuffer,
+            done: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, copier_ctas: int = 8) -> None:
+    """GEMM -> reduce-scatter as ONE kernel: ``partial[M, N] = a @ b^T`` (BF16, local scratch) on the CTA-pair kernel,
+    whose copier CTAs push every finished 256-row block into slot ``rank`` of the owner's ``slots`` buffer
+    ([n][M/n][N] BF16).  ``done``: int32 [M / 256] scratch.  Follow with ``ws.barrier()`` and `sum_slots`; precede
+    with ``ws.barrier()`` when the owners may still be reading the previous contents of their slots."""
+    M = a.shape[1] if a_mn else a.shape[0]
+    g = K.GemmArgs()
+    g.a, g.b, g.out = a.data_ptr(), b.data_ptr(), partial.data_ptr()
+    g.lda, g.ldb, g.ldo = a.stride(0), b.stride(0), partial.stride(0)
+    g.m, g.n, g.k, g.batch = M, (b.shape[1] if b_mn else b.shape[0]), (a.shape[0] if a_mn else a.shape[1]), 1
+    g.a_mn_major, g.b_mn_major = int(a_mn), int(b_mn)
+    g.in_dtype, g.out_dtype = K._DT[a.dtype], K._DT[partial.dtype]
+    g.act, g.alpha, g.split_k = K.ACT[None], 1.0, 1
+    g.status = K.status_word(a.device).data_ptr()
+    d = GemmRs()
+    for q in range(ws.n):
+        d.slots[q] = slots.ptrs[q]
+    d.done = done.data_ptr()
+    d.n_ranks, d.rank, d.copier_ctas = ws.n, ws.rank, copier_ctas
+    done.zero_()
+    K._check(K.lib().nx_gemm_rs(C.byref(g), C.byref(d), K._stream()), "nx_gemm_rs")
+
+
+def sum_slots(slots: torch.Tensor, n: int, rows: int, cols: int, out: torch.Tensor, *, residual=None,
+              out_lp: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = residual + sum of the n BF16 slots ``slots[q][rows][cols]`` in rank order (the owner's half of the slot
+    form of GEMM -> reduce-scatter); ``out_lp`` receives a BF16 copy."""
+    K._check(K.lib().nx_comm_sum_slots(K._p(slots), C.c_int(n), C.c_int(rows), C.c_int(cols), C.c_int64(cols),
+                                       K._p(residual), C.c_int(K._DT[residual.dtype] if residual is not None else 0),
+                                       C.c_int64(residual.stride(0) if residual is not None else 0), K._p(out),
+                                       C.c_int(K._DT[out.dtype]), C.c_int64(out.stride(0)), K._p(out_lp),
+                                       C.c_int64(out_lp.stride(0) if out_lp is not None else 0), K._stream()),
+             "nx_comm_sum_slots")
     return out
 
 

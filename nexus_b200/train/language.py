@@ -7,6 +7,7 @@ from dataclasses import dataclass
 from typing import List, Sequence
 
 import numpy as np
+import torch
 
 from .lm_trainer import AdamW, ArrayTokens, LanguageTrainerBuilder, ParamGroupPolicy
 
@@ -18,8 +19,30 @@ class TokenRows:
     time: int
 
 
+class SequenceLm(torch.nn.Module):
+    """Gives a plain layer stack (token ids -> logits, e.g. ``Sequential(Embedding, PositionalEncoding,
+    CausalTransformerBlock, Linear)``) the interface the LM trainer drives: `logits(tokens)` and the shifted
+    next-token `loss(tokens)`.  The wrapped stack's parameters are trained in place."""
+
+    def __init__(self, net: torch.nn.Module):
+        super().__init__()
+        self.net = net
+
+    def logits(self, tokens: torch.Tensor) -> torch.Tensor:
+        return self.net(tokens.long())
+
+    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        return self.logits(tokens)
+
+    def loss(self, tokens: torch.Tensor) -> torch.Tensor:
+        lg = self.logits(tokens).float()
+        return torch.nn.functional.cross_entropy(lg[:, :-1].reshape(-1, lg.shape[-1]), tokens[:, 1:].reshape(-1).long())
+
+
 class LanguageTrainer:
     def __init__(self, model, lr: float = 3e-4, weight_decay: float = 0.0, device: str = "cpu"):
+        if not hasattr(model, "loss"):
+            model = SequenceLm(model)
         self.model, self.lr, self.wd, self.device = model, lr, weight_decay, device
         self.losses: List[float] = []
         self._trainer = None

@@ -40,3 +40,15 @@ def test_tensor_parallel_lm_two_gpus_matches_single_process_loss(precision):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert r.returncode == 0 and '"check": "first loss"' in r.stdout and "tokens/s" in r.stdout, \
         r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_llama_on_fused_kernels_matches_single_rank():
+    """`models.llama_tp.LlamaTpModel` over 2 GPUs (all-gather -> GEMM and GEMM -> reduce-scatter inside the tcgen05
+    kernels, vocabulary-parallel embedding and loss, fused norm exchange) against the one-rank model: loss, gradients,
+    gradient norm and three optimizer steps."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", _free_port(), os.path.join(ROOT, "tests", "workers", "llama_tp_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=420, env=env)
+    assert "WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

@@ -239,6 +239,102 @@ def main():
     mine = ref_rs[rank * (M // world): (rank + 1) * (M // world)]
     check("GEMM->RS", (o_sym.local.view(M // world, N) - mine).abs().max() <= 1e-2 * ref_rs.abs().max())
 
+    # ---- GEMM -> reduce-scatter, slot form (BF16 on the wire, owner sums the slots in rank order): deterministic
+    from nexus_b200.parallel.symm import sum_slots
+    slots = ws.alloc(world * (M // world) * N, torch.bfloat16)
+    res = torch.randn(M // world, N, device=dev)
+    outs = []
+    for rep in range(2):
+        ws.barrier()
+        gemm_dist(ws, Ak, Bk, slots.local.view(M, N), out_peers=slots, scatter="slots", m=M, n=N)
+        ws.barrier()
+        z = torch.empty(M // world, N, device=dev)
+        z_lp = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
+        sum_slots(slots.local, world, M // world, N, z, residual=res, out_lp=z_lp)
+        torch.cuda.synchronize(); K.check_status()
+        outs.append(z.clone())
+    check("GEMM->RS (slots) + residual", (outs[0] - res - mine).abs().max() <= 1.5e-2 * ref_rs.abs().max())
+    check("GEMM->RS (slots) is bit-reproducible", torch.equal(outs[0], outs[1]) and torch.equal(z_lp, z.bfloat16()))
+
+    # ---- all-gather fused into the CTA-pair GEMM (push form): result, gathered copy, repeated calls
+    from nexus_b200.parallel.symm import GatherSite, gemm_ag
+    Mg_l, Kg, Ng = 512, 320, 384
+    site = GatherSite(ws, Mg_l)
+    Xg_full = torch.randn(Mg_l * world, Kg, device=dev).bfloat16()
+    Wg = torch.randn(Ng, Kg, device=dev).bfloat16()
+    pg.broadcast_tensor(Xg_full, 0)
+    pg.broadcast_tensor(Wg, 0)
+    xg = ws.alloc(Mg_l * world * Kg, torch.bfloat16)
+    good = True
+    for rep in range(3):
+        xv = xg.local.view(Mg_l * world, Kg)
+        xv.zero_()
+        xv[rank * Mg_l: (rank + 1) * Mg_l].copy_(Xg_full[rank * Mg_l: (rank + 1) * Mg_l] * (rep + 1))
+        ws.barrier()
+        yg = torch.empty(Mg_l * world, Ng, device=dev, dtype=torch.bfloat16)
+        gemm_ag(site, xg, Wg, yg, k=Kg, copier_ctas=4)
+        torch.cuda.synchronize(); K.check_status()
+        ref_g = (Xg_full.float() * (rep + 1)) @ Wg.float().t()
+        good &= bool((yg.float() - ref_g).abs().max() <= 1.5e-2 * ref_g.abs().max())
+        good &= torch.equal(xv, (Xg_full * (rep + 1)))
+        ws.barrier()
+    check("AG->GEMM, push form on the CTA-pair kernel (3 calls, gathered copy complete)", good)
+
+    # ---- GEMM -> reduce-scatter in one kernel (push form on the CTA-pair kernel), three calls, vs FP32 reference
+    from nexus_b200.parallel.symm import gemm_rs
+    Mr, Nr, Kr = 512 * world, 384, 192
+    Ar = torch.randn(Mr, Kr, device=dev).bfloat16()              # this rank's K slice of A and B (different per rank)
+    Br = torch.randn(Nr, Kr, device=dev).bfloat16()
+    prod = Ar.float() @ Br.float().t()
+    want = prod.clone()
+    pg.all_reduce_tensor(want)
+    slots_r = ws.alloc(world * (Mr // world) * Nr, torch.bfloat16)
+    partial_r = torch.empty(Mr, Nr, device=dev, dtype=torch.bfloat16)
+    done_r = torch.zeros(Mr // 256, dtype=torch.int32, device=dev)
+    good = True
+    for rep in range(3):
+        ws.barrier()
+        gemm_rs(ws, Ar, Br, partial_r, slots_r, done_r, copier_ctas=4)
+        ws.barrier()
+        zr = torch.empty(Mr // world, Nr, device=dev)
+        sum_slots(slots_r.local, world, Mr // world, Nr, zr)
+        torch.cuda.synchronize(); K.check_status()
+        mine_r = want[rank * (Mr // world): (rank + 1) * (Mr // world)]
+        good &= bool((zr - mine_r).abs().max() <= 2e-2 * want.abs().max())
+        slots_r.local.zero_()
+        torch.cuda.synchronize()
+    check("GEMM->RS, push form on the CTA-pair kernel (3 calls)", good)
+
+    # ---- MN-major operands in the distributed GEMM: dgrad with all-gathered rows, wgrad over K-sharded rows
+    W_mn = torch.randn(Kd, 384, device=dev).bfloat16()          # B stored [K][N]
+    pg.broadcast_tensor(W_mn, 0)
+    out_d = torch.empty(M, 384, device=dev, dtype=torch.bfloat16)
+    gemm_dist(ws, a_loc, W_mn, out_d, a_peers=a_sym, b_mn=True)
+    torch.cuda.synchronize(); K.check_status()
+    ref_d = A.float() @ W_mn.float()
+    check("AG(A)->GEMM with MN-major B (dgrad form)", (out_d.float() - ref_d).abs().max() <= 1.5e-2 * ref_d.abs().max())
+    Mk = 128 * world                                            # contraction length, 128 rows per rank
+    Xs = ws.alloc(128 * 384, torch.bfloat16)                     # this rank's rows of X [Mk, 384]
+    Xfull = torch.randn(Mk, 384, device=dev).bfloat16()
+    dYfull = torch.randn(Mk, 256, device=dev).bfloat16()
+    pg.broadcast_tensor(Xfull, 0)
+    pg.broadcast_tensor(dYfull, 0)
+    Xs.local.view(128, 384).copy_(Xfull[rank * 128: (rank + 1) * 128])
+    torch.cuda.synchronize(); ws.barrier()
+    dW = torch.ones(256, 384, device=dev)
+    gemm_dist(ws, dYfull, Xs.local.view(128, 384), dW, b_peers=Xs, a_mn=True, b_mn=True, b_shard="k", accumulate=True)
+    torch.cuda.synchronize(); K.check_status()
+    ref_w = 1.0 + dYfull.float().t() @ Xfull.float()
+    check("wgrad with K-sharded B (beta = 1)", (dW - ref_w).abs().max() <= 1.5e-2 * ref_w.abs().max())
+    dYs = ws.alloc(128 * 256, torch.bfloat16)
+    dYs.local.view(128, 256).copy_(dYfull[rank * 128: (rank + 1) * 128])
+    torch.cuda.synchronize(); ws.barrier()
+    dW2 = torch.zeros(256, 384, device=dev)
+    gemm_dist(ws, dYs.local.view(128, 256), Xfull, dW2, a_peers=dYs, a_mn=True, b_mn=True, a_shard="k")
+    torch.cuda.synchronize(); K.check_status()
+    check("wgrad with K-sharded A", (dW2 - (ref_w - 1.0)).abs().max() <= 1.5e-2 * ref_w.abs().max())
+    ws.barrier()
+
     # ---- MoE dispatch / combine over peer memory (identity experts)
     E, k, d, T, cap = 2 * world, 2, 64, 32, 64
     le = E // world
