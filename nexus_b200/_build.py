@@ -93,6 +93,28 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
     return CUDA_LIB
 
 
+def build_cuda_debug(verbose: bool = False) -> Path:
+    """The kernel library with the debug-build bounds checks of the tile index arithmetic compiled in
+    (`-DNX_DEBUG_BOUNDS`: a coordinate that leaves its tensor is recorded in the status word and the access is
+    skipped).  Built on demand into `lib/libnexus_b200_cuda_dbg.so`; `NEXUS_B200_DEBUG_BOUNDS=1` makes
+    `ops._cuda.lib()` load it instead of the release library."""
+    out = CUDA_LIB.parent / "libnexus_b200_cuda_dbg.so"
+    srcs = cuda_sources()
+    newest = max([s.stat().st_mtime for s in srcs] + [_newest_header([CSRC / "cuda"])])
+    if not out.exists() or out.stat().st_mtime < newest:
+        dbg = OBJ_DIR / "dbg"
+        dbg.mkdir(parents=True, exist_ok=True)
+        cmds = [[_nvcc(), *NVCC_FLAGS, "-DNX_DEBUG_BOUNDS", "-I", str(CSRC / "cuda"), "-c", str(s), "-o",
+                 str(dbg / (s.stem + ".o"))] for s in srcs]
+        with ThreadPoolExecutor(max_workers=8) as ex:
+            list(ex.map(_run, cmds))
+        _run([_nvcc(), "-shared", "-o", str(out), *[str(dbg / (s.stem + ".o")) for s in srcs], "-gencode",
+              "arch=compute_100a,code=sm_100a", "-cudart", "static"])
+        if verbose:
+            print("linked", out)
+    return out
+
+
 def build_gemm_profile(verbose: bool = False) -> Path:
     """Instrumented GEMM library (`-DNX_PROFILE_MMA`), built on demand by `python -m nexus_b200.bench.mma_profile`;
     not part of `build_all` and never loaded by the framework itself."""
@@ -147,7 +169,7 @@ def build_tools(force: bool = False, verbose: bool = False):
 
 
 def build_all(force: bool = False, verbose: bool = False):
-    return build_cuda(force, verbose), build_host(force, verbose), build_tools(force, verbose)
+    return build_cuda(force, verbose), build_host(force, verbose), build_tools(force, verbose), build_cuda_debug(verbose)
 
 
 if __name__ == "__main__":

@@ -144,7 +144,7 @@ def main(argv=None) -> int:
             ws.barrier()       # the owners have consumed the previous contents of their slots
             gemm_rs(ws, a, w, partial, slots, done, copier_ctas=args.copiers)
             ws.barrier()       # every rank's partial blocks have landed
-            sum_slots(slots.local, n, Ml, d, z)
+            sum_slots(slots.local, n, Ml, d, z, own=partial[rank * Ml: (rank + 1) * Ml], own_rank=rank)
 
         def base_rs():
             K.gemm(a, w, out=full)

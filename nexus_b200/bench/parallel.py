@@ -84,7 +84,15 @@ def main(argv=None) -> int:
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--check", action="store_true")
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
+                    help="fused: models.llama_tp.LlamaTpModel (all-gather -> GEMM / GEMM -> reduce-scatter inside the "
+                         "tcgen05 kernels over peer memory, hand-scheduled backward); nccl: parallel.ParallelLm "
+                         "(autograd, NCCL all-reduces at the region boundaries) - the same-box baseline")
+    ap.add_argument("--copiers", type=int, default=8, help="copier CTAs of the fused GEMM kernels")
+    ap.add_argument("--graph", type=int, default=0, help="fused: replay the whole step as one CUDA graph")
     args = ap.parse_args(argv)
+    if args.comm == "fused" and args.precision == "bf16" and not args.check:
+        return run_fused(args)
 
     from ..fused.ops import linear_precision
     from ..lm.config import preset
@@ -161,6 +169,102 @@ def main(argv=None) -> int:
             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 2),
             "data": "synthetic uniform tokens, random-init weights"}), flush=True)
     pg.destroy()
+    return 0
+
+
+def run_fused(args) -> int:
+    """The tensor + sequence parallel model on the fused kernels: one pass over the whole batch per optimizer step
+    (micro-batches accumulate when --micro-batch is smaller than the per-replica batch)."""
+    from ..lm.config import preset
+    from ..models.gpt import AdamWConfig
+    from ..models.llama_tp import LlamaTpModel
+    from ..ops import _cuda as K
+    from ..parallel.process_group import init_process_group
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    pg = init_process_group(backend="nccl", device=f"cuda:{local}") if world > 1 else None
+    cfg = preset(args.model)
+    if args.layers > 0:
+        cfg.n_layer = args.layers
+    cfg.max_position = max(cfg.max_position, args.seq_len)
+    model = LlamaTpModel(cfg, pg, device=dev, copier_ctas=args.copiers)
+    model.set_optimizer(AdamWConfig(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, grad_clip=1.0))
+    n_micro = max(1, args.global_batch // args.micro_batch)
+    gen = torch.Generator(device=dev).manual_seed(1234)
+    sets = [[torch.empty((args.micro_batch, args.seq_len), device=dev, dtype=torch.int32) for _ in range(n_micro)]
+            for _ in range(2)]
+
+    def refill(tokens):   # fresh uniform tokens for every step, drawn on the device (the same on every rank)
+        for t in tokens:
+            t.random_(0, cfg.vocab_size, generator=gen)
+
+    loss_log = torch.zeros(args.steps + max(1, args.warmup), dtype=torch.float32, device=dev)
+    step_no = [0]
+
+    def step(tokens):
+        refill(tokens)
+        for i, t in enumerate(tokens):
+            model.forward_backward(t, grad_scale=1.0 / n_micro, accumulate_loss=i > 0, loss_weight=1.0 / n_micro)
+        model.optimizer_step()
+
+    def barrier():
+        if pg is not None:
+            pg.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(1, args.warmup)):
+        step(sets[i % 2])
+        loss_log[step_no[0]].copy_(model.loss_buf[0])
+        step_no[0] += 1
+    graph = None
+    if args.graph:
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step(sets[0])
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = K.launch_count
+    e0.record()
+    for i in range(args.steps):
+        if graph is not None:
+            graph.replay()
+        else:
+            step(sets[i % 2])
+        loss_log[step_no[0]].copy_(model.loss_buf[0])
+        step_no[0] += 1
+    e1.record()
+    barrier()
+    K.check_status(dev)
+    ms = e0.elapsed_time(e1) / args.steps
+    if pg is not None:
+        ms = float(pg.all_reduce_scalar(ms, "max"))
+    tokens = args.global_batch * args.seq_len
+    if rank == 0:
+        try:
+            root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+            peak = float(json.load(open(os.path.join(root, "MEASURED_PEAKS.json")))["bf16_tflops_sustained"])
+        except Exception:
+            peak = 1400.0
+        tflops = model.flops_per_token(args.seq_len) * tokens / (ms * 1e-3) / 1e12 / world
+        print(json.dumps({
+            "metric": f"train tokens/s {args.model} tensor-parallel", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "ms_per_step": ms, "steps": args.steps, "warmup": max(1, args.warmup),
+            "tflops_per_gpu": round(tflops, 1), "fraction_of_sustained_bf16": round(tflops / peak, 3),
+            "config": {"model": args.model, "layers": cfg.n_layer, "tp": world, "sp": True, "comm": "fused",
+                       "seq_len": args.seq_len, "global_batch": args.global_batch, "micro_batch": args.micro_batch,
+                       "linear_precision": "bf16", "compute_dtype": "bf16", "master": "fp32 AdamW, clip 1.0",
+                       "copier_ctas": args.copiers, "cuda_graph": bool(args.graph)},
+            "losses": [round(float(x), 4) for x in loss_log[: step_no[0]].cpu()],
+            "kernel_launches_per_step": (K.launch_count - launches0) // max(args.steps, 1),
+            "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 2),
+            "data": "synthetic uniform tokens, random-init weights"}), flush=True)
+    if pg is not None:
+        pg.destroy()
     return 0
 
 

@@ -134,6 +134,7 @@ __device__ __forceinline__ uint32_t sw128_off(int r, int chunk) {
 template <int HD>
 __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int rows, int row0,
                                           int head, int batch, int hfirst) {
+  // (debug builds check the tile coordinates at the call sites, where the tensor extents are known: NX_INDEX_OK)
 #pragma unroll
   for (int s = 0; s < HD / 64; ++s) {
     if (hfirst)
@@ -358,6 +359,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         int kv_lo, kv_hi;
         kv_range(p, q0, min(128, p.Tq - q0), kv_lo, kv_hi);
         const int jb = kv_lo / 128, je = (kv_hi + 127) / 128;
+        // debug builds: the item's tile coordinates lie inside the tensors (a tile may run past the end, never start there)
+        if (!NX_INDEX_OK(q0 >= 0 && q0 < p.Tq && h >= 0 && h < p.H && hk < p.Hkv && b >= 0 && b < p.B && jb >= 0 &&
+                         (je == jb || (je - 1) * 128 < p.Tk), p.status)) {
+          *abort_flag = 1;
+          break;
+        }
         if (!mbar_wait_bounded(q_empty, (n_item & 1) ^ 1u, abort_flag)) {  // the previous item's QK^T are done
           atomicCAS(p.status, 0, kStatusTimeoutProducer);
           break;

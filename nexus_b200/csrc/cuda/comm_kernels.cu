@@ -356,6 +356,38 @@ __global__ void moe_combine_kernel(NxPeerTable bufs, const int32_t* __restrict__
   }
 }
 
+// dgate[t, j] = dy[t] . out_buf[owner(e_tj)][le][slot_tj] read from the owner's memory (0 for dropped assignments);
+// one warp per (t, j)
+__global__ void moe_gate_grad_peers_kernel(const __nv_bfloat16* __restrict__ dy, NxPeerTable bufs,
+                                           const int32_t* __restrict__ expert, const int32_t* __restrict__ slot,
+                                           float* __restrict__ dgate, int entries, int k, int d, int local_experts,
+                                           int capacity) {
+  const int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (i >= entries) return;
+  const int s = slot[i];
+  float acc = 0.0f;
+  if (s >= 0) {
+    const int e = expert[i];
+    const __nv_bfloat16* a = dy + static_cast<int64_t>(i / k) * d;
+    const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(bufs.ptr[e / local_experts]) +
+                             (static_cast<int64_t>(e % local_experts) * capacity + s) * d;
+    for (int c = lane * 8; c < d; c += 256) {
+      const uint4 x = *reinterpret_cast<const uint4*>(a + c);
+      const uint4 y = *reinterpret_cast<const uint4*>(b + c);
+      const uint32_t xw[4] = {x.x, x.y, x.z, x.w}, yw[4] = {y.x, y.y, y.z, y.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float xl, xh, yl, yh;
+        unpack_bf16x2(xw[j], xl, xh);
+        unpack_bf16x2(yw[j], yl, yh);
+        acc += xl * yl + xh * yh;
+      }
+    }
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) dgate[i] = acc;
+}
+
 // ------------------------------------------------------------------------------------------------
 // vocabulary-parallel cross-entropy: exchange of per-row statistics
 // ------------------------------------------------------------------------------------------------
@@ -400,7 +432,7 @@ template <typename RT, typename OT>
 __global__ void __launch_bounds__(256)
 sum_slots_kernel(const __nv_bfloat16* __restrict__ slots, int n, int rows, int cols, int64_t ld_slots,
                  const RT* __restrict__ residual, int64_t ld_res, OT* __restrict__ out, int64_t ld_out,
-                 __nv_bfloat16* __restrict__ out_lp, int64_t ld_lp) {
+                 __nv_bfloat16* __restrict__ out_lp, int64_t ld_lp, const __nv_bfloat16* __restrict__ own_rows, int own_rank) {
   constexpr int V = 8;
   const int vec_per_row = cols / V;
   const int64_t total = static_cast<int64_t>(rows) * vec_per_row;
@@ -418,7 +450,8 @@ sum_slots_kernel(const __nv_bfloat16* __restrict__ slots, int n, int rows, int c
     }
 #pragma unroll 1
     for (int q = 0; q < n; ++q) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(slots + q * slot_stride + static_cast<int64_t>(r) * ld_slots + c);
+      const __nv_bfloat16* base = (own_rows != nullptr && q == own_rank) ? own_rows : slots + q * slot_stride;
+      const uint4 raw = *reinterpret_cast<const uint4*>(base + static_cast<int64_t>(r) * ld_slots + c);
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -453,7 +486,7 @@ extern "C" int nx_comm_bump(int* counter, nx_stream_t stream) {
 
 extern "C" int nx_comm_sum_slots(const void* slots, int n, int rows, int cols, int64_t ld_slots, const void* residual,
                                  int res_dtype, int64_t ld_res, void* out, int out_dtype, int64_t ld_out, void* out_lp,
-                                 int64_t ld_lp, nx_stream_t stream) {
+                                 int64_t ld_lp, const void* own_rows, int own_rank, nx_stream_t stream) {
   if (slots == nullptr || out == nullptr || n < 1 || n > NX_MAX_PEERS || rows <= 0 || cols <= 0 || (cols & 7) ||
       (ld_slots & 7) || (reinterpret_cast<uintptr_t>(slots) & 15) || (out_lp != nullptr && ((ld_lp & 7) ||
       (reinterpret_cast<uintptr_t>(out_lp) & 15))))
@@ -463,7 +496,7 @@ extern "C" int nx_comm_sum_slots(const void* slots, int n, int rows, int cols, i
   const int blocks = static_cast<int>(std::min<int64_t>((total + 255) / 256, 148 * 16));
   const __nv_bfloat16* sl = static_cast<const __nv_bfloat16*>(slots);
   __nv_bfloat16* lp = static_cast<__nv_bfloat16*>(out_lp);
-#define NX_SS(RT, OT) sum_slots_kernel<RT, OT><<<blocks, 256, 0, st>>>(sl, n, rows, cols, ld_slots, static_cast<const RT*>(residual), ld_res, static_cast<OT*>(out), ld_out, lp, ld_lp)
+#define NX_SS(RT, OT) sum_slots_kernel<RT, OT><<<blocks, 256, 0, st>>>(sl, n, rows, cols, ld_slots, static_cast<const RT*>(residual), ld_res, static_cast<OT*>(out), ld_out, lp, ld_lp, static_cast<const __nv_bfloat16*>(own_rows), own_rank)
   const int rd = residual == nullptr ? out_dtype : res_dtype;
   if (rd == NX_F32 && out_dtype == NX_F32) NX_SS(float, float);
   else if (rd == NX_BF16 && out_dtype == NX_BF16) NX_SS(__nv_bfloat16, __nv_bfloat16);
@@ -560,6 +593,17 @@ extern "C" int nx_moe_combine(const NxPeerTable* bufs, const int32_t* expert, co
   const int blocks = tokens < 148 * 8 ? tokens : 148 * 8;
   moe_combine_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       *bufs, expert, slot, gate, static_cast<__nv_bfloat16*>(y), tokens, top_k, d, local_experts, capacity);
+  return launch_status();
+}
+
+extern "C" int nx_moe_gate_grad_peers(const void* dy, const NxPeerTable* bufs, const int32_t* expert, const int32_t* slot,
+                                      float* dgate, int tokens, int top_k, int d, int local_experts, int capacity,
+                                      nx_stream_t stream) {
+  const int entries = tokens * top_k;
+  if (entries <= 0) return 0;
+  if (bufs == nullptr || (d & 7)) return -1;
+  moe_gate_grad_peers_kernel<<<(entries + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(dy), *bufs, expert, slot, dgate, entries, top_k, d, local_experts, capacity);
   return launch_status();
 }
 

@@ -91,6 +91,7 @@ struct DevParams {
   // 256-row block into slot `rs_rank` of the buffer of the rank that owns those rows.
   int rs_ranks, rs_rank, rs_rows, rs_copiers;  // rs_ranks <= 1: plain GEMM
   int rs_expected;                            // arrivals that complete one row block (16 per column tile)
+  int rs_copy_own;                            // 0: the rows this rank owns stay in `out` only (the caller sums them from there)
   int* rs_done;                               // [M / 256], zeroed by the caller before the launch
   void* rs_slots[NX_MAX_PEERS];               // per rank: BF16 [rs_ranks][rs_rows][ldo]
 };
@@ -251,15 +252,78 @@ __device__ long long g_epi_prof[148 * 8];  // first epilogue warp: busy cycles p
 // FAST (pair only): the epilogue of the training GEMMs and nothing else - BF16 result through tiled stores,
 // optional bias, GELU with saved pre-activation, or dGELU of a saved pre-activation - with the bias staged once
 // per tile in shared memory and one proxy fence / store group per tile (two with aux_out).
+// Copier CTAs move contiguous byte ranges from this GPU's memory into a peer's (or its own) memory.  Loads are
+// untiled bulk copies (TMA engine) from LOCAL global memory into the CTA's shared memory, two stages of kCopyStage
+// bytes in flight so that the load latency hides behind the previous stage's stores; the stores are plain 16-byte
+// stores by all threads (posted writes, coalesced), so nothing but this GPU's own memory is ever bulk-loaded.
+constexpr int kCopyPiece = 16 * 1024;
+constexpr int kCopyPieces = 6;
+constexpr int kCopyStage = kCopyPiece * kCopyPieces;  // 96 KiB per stage, two stages
+
+struct CopierSmem {
+  uint64_t* bars;      // [2]
+  volatile int* flag;  // scratch int for CTA-wide decisions
+  uint8_t* buf;        // 2 * kCopyStage bytes, 128-byte aligned
+  uint32_t phase[2];
+};
+
+__device__ __forceinline__ CopierSmem copier_smem_init(uint8_t* smem_raw) {
+  CopierSmem cs;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  cs.bars = reinterpret_cast<uint64_t*>(base);
+  cs.flag = reinterpret_cast<volatile int*>(base + 16);
+  cs.buf = base + 128;
+  cs.phase[0] = cs.phase[1] = 0;
+  if (threadIdx.x == 0) {
+    mbar_init(&cs.bars[0], 1);
+    mbar_init(&cs.bars[1], 1);
+    *cs.flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  return cs;
+}
+
+// All threads of the CTA call this with the same arguments.  Returns false when a wait ran out (status is set).
+__device__ __forceinline__ bool copier_copy(CopierSmem& cs, const char* __restrict__ src, char* __restrict__ dst, int64_t bytes,
+                                            int* status) {
+  const int rounds = static_cast<int>((bytes + kCopyStage - 1) / kCopyStage);
+  auto issue = [&](int r) {  // thread 0 only
+    const int s = r & 1;
+    const int64_t off = static_cast<int64_t>(r) * kCopyStage;
+    const int len = static_cast<int>(min(static_cast<int64_t>(kCopyStage), bytes - off));
+    mbar_arrive_expect_tx(&cs.bars[s], static_cast<uint32_t>(len));
+    for (int o = 0; o < len; o += kCopyPiece)
+      bulk_load(cs.buf + s * kCopyStage + o, src + off + o, static_cast<uint32_t>(min(kCopyPiece, len - o)), &cs.bars[s]);
+  };
+  if (threadIdx.x == 0) issue(0);
+  for (int r = 0; r < rounds; ++r) {
+    const int s = r & 1;
+    if (threadIdx.x == 0 && r + 1 < rounds) issue(r + 1);  // the other stage was drained before the last barrier
+    if (!mbar_wait_bounded(&cs.bars[s], cs.phase[s], cs.flag)) {
+      atomicCAS(status, 0, kStatusTimeoutProducer);
+      return false;  // every thread sees the same barrier and the shared abort flag: the exit is CTA-wide
+    }
+    cs.phase[s] ^= 1u;
+    const int64_t off = static_cast<int64_t>(r) * kCopyStage;
+    const int len = static_cast<int>(min(static_cast<int64_t>(kCopyStage), bytes - off));
+    const uint8_t* sb = cs.buf + s * kCopyStage;
+    for (int i = threadIdx.x * 16; i < len; i += blockDim.x * 16)
+      *reinterpret_cast<uint4*>(dst + off + i) = *reinterpret_cast<const uint4*>(sb + i);
+    __syncthreads();  // the stage may be refilled
+  }
+  return true;
+}
+
 // Copier CTA of the all-gather GEMM: pushes chunk after chunk (128 rows) of this rank's row block into the gather
 // buffer of one peer after the other (the peer that needs it soonest first), then raises that chunk's flag on the peer.
 // Plain stores to peer memory; the release store of the flag follows a system-scope fence by every storing thread.
-__device__ __forceinline__ void ag_copier_run(const DevParams& p, int cid) {
+__device__ __forceinline__ void ag_copier_run(const DevParams& p, int cid, uint8_t* smem_raw) {
   const int n = p.ag_ranks, r = p.ag_rank;
   const int chunks = p.ag_rows / kBM;
   const int epoch = *reinterpret_cast<const volatile int*>(p.ag_counter) + 1;
-  const int vpr = p.ag_row_bytes / 16;  // 16-byte vectors per row
-  const int total = kBM * vpr;
+  CopierSmem cs = copier_smem_init(smem_raw);
+  const bool contiguous = p.ag_ld_bytes == p.ag_row_bytes;
   const char* src_base = reinterpret_cast<const char*>(p.ag_gather[r]) + static_cast<int64_t>(r) * p.ag_rows * p.ag_ld_bytes;
   for (int s = 1; s < n; ++s) {
     const int dest = (r - s + n) % n;
@@ -267,22 +331,11 @@ __device__ __forceinline__ void ag_copier_run(const DevParams& p, int cid) {
     for (int j = cid; j < chunks; j += p.ag_copiers) {
       const char* src = src_base + static_cast<int64_t>(j) * kBM * p.ag_ld_bytes;
       char* dst = dst_base + static_cast<int64_t>(j) * kBM * p.ag_ld_bytes;
-      int i = threadIdx.x;
-      for (; i + 3 * static_cast<int>(blockDim.x) < total; i += 4 * blockDim.x) {
-        uint4 v[4];
-        int64_t off[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int idx = i + u * blockDim.x;
-          off[u] = static_cast<int64_t>(idx / vpr) * p.ag_ld_bytes + static_cast<int64_t>(idx % vpr) * 16;
-          v[u] = *reinterpret_cast<const uint4*>(src + off[u]);
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) *reinterpret_cast<uint4*>(dst + off[u]) = v[u];
-      }
-      for (; i < total; i += blockDim.x) {
-        const int64_t off = static_cast<int64_t>(i / vpr) * p.ag_ld_bytes + static_cast<int64_t>(i % vpr) * 16;
-        *reinterpret_cast<uint4*>(dst + off) = *reinterpret_cast<const uint4*>(src + off);
+      if (contiguous) {
+        if (!copier_copy(cs, src, dst, static_cast<int64_t>(kBM) * p.ag_row_bytes, p.status)) return;
+      } else {
+        for (int row = 0; row < kBM; ++row)
+          if (!copier_copy(cs, src + row * p.ag_ld_bytes, dst + row * p.ag_ld_bytes, p.ag_row_bytes, p.status)) return;
       }
       __threadfence_system();
       __syncthreads();
@@ -292,23 +345,24 @@ __device__ __forceinline__ void ag_copier_run(const DevParams& p, int cid) {
   }
 }
 
-// Copier CTA of the reduce-scatter GEMM: block after block (256 rows, in the order the GEMM CTAs finish them) waits
-// until every tile of the block has been stored, then copies its share of the block's rows from the local buffer of
-// partial sums into slot `rs_rank` of the owner's buffer (plain stores, over NVLink unless the owner is this rank).
-__device__ __forceinline__ void rs_copier_run(const DevParams& p, int cid) {
-  const int n = p.rs_ranks;
+// Copier CTA of the reduce-scatter GEMM: takes finished 256-row blocks (in the order the GEMM CTAs finish them) and
+// copies them from the local buffer of partial sums into slot `rs_rank` of the owner's buffer.
+__device__ __forceinline__ void rs_copier_run(const DevParams& p, int cid, uint8_t* smem_raw) {
   const int blocks = p.m / (2 * kBM);
-  const int rows_per = (2 * kBM) / p.rs_copiers;  // rows of every block that this copier moves
   const int64_t ld_bytes = p.ldo * 2;
-  const int vpr = (p.n * 2) / 16;
-  const int total = rows_per * vpr;
+  const int row_bytes = p.n * 2;
+  const bool contiguous = ld_bytes == row_bytes;
   const int first = p.rot_rows / (2 * kBM);
-  __shared__ int s_ok;
-  for (int i = 0; i < blocks; ++i) {
+  CopierSmem cs = copier_smem_init(smem_raw);
+  // copier `cid` takes every rs_copiers-th block of the ring order: the copiers work on different blocks at once
+  for (int i = cid; i < blocks; i += p.rs_copiers) {
     int rb = first + i;
     if (rb >= blocks) rb -= blocks;
+    const int row0 = rb * 2 * kBM;
+    const int owner = row0 / p.rs_rows;
+    if (owner == p.rs_rank && !p.rs_copy_own) continue;  // stays in `out`; nothing to wait for
     if (threadIdx.x == 0) {
-      s_ok = 1;
+      *cs.flag = 0;
       const uint64_t t0 = globaltimer_ns();
       for (;;) {
         int v;
@@ -316,38 +370,24 @@ __device__ __forceinline__ void rs_copier_run(const DevParams& p, int cid) {
         if (v >= p.rs_expected) break;
         if (globaltimer_ns() - t0 > NX_WAIT_LIMIT_NS) {
           atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
-          s_ok = 0;
+          *cs.flag = 1;
           break;
         }
         __nanosleep(200);
       }
+      asm volatile("fence.proxy.async;" ::: "memory");  // the block was written by TMA stores and is read by bulk loads
     }
     __syncthreads();
-    if (!s_ok) return;
-    const int row0 = rb * 2 * kBM + cid * rows_per;
-    const int owner = row0 / p.rs_rows;
+    if (*cs.flag) return;
     const char* src = reinterpret_cast<const char*>(p.out) + static_cast<int64_t>(row0) * ld_bytes;
     char* dst = reinterpret_cast<char*>(p.rs_slots[owner]) +
                 (static_cast<int64_t>(p.rs_rank) * p.rs_rows + (row0 - owner * p.rs_rows)) * ld_bytes;
-    asm volatile("fence.proxy.async;" ::: "memory");  // the block was written by TMA stores; read it with plain loads
-    int j = threadIdx.x;
-    for (; j + 3 * static_cast<int>(blockDim.x) < total; j += 4 * blockDim.x) {
-      uint4 v[4];
-      int64_t off[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int idx = j + u * blockDim.x;
-        off[u] = static_cast<int64_t>(idx / vpr) * ld_bytes + static_cast<int64_t>(idx % vpr) * 16;
-        v[u] = *reinterpret_cast<const uint4*>(src + off[u]);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) *reinterpret_cast<uint4*>(dst + off[u]) = v[u];
+    if (contiguous) {
+      if (!copier_copy(cs, src, dst, static_cast<int64_t>(2 * kBM) * row_bytes, p.status)) return;
+    } else {
+      for (int row = 0; row < 2 * kBM; ++row)
+        if (!copier_copy(cs, src + row * ld_bytes, dst + row * ld_bytes, row_bytes, p.status)) return;
     }
-    for (; j < total; j += blockDim.x) {
-      const int64_t off = static_cast<int64_t>(j / vpr) * ld_bytes + static_cast<int64_t>(j % vpr) * 16;
-      *reinterpret_cast<uint4*>(dst + off) = *reinterpret_cast<const uint4*>(src + off);
-    }
-    __syncthreads();
   }
   __threadfence_system();  // the partial sums are in the owners' memory before this grid counts as complete
 }
@@ -388,8 +428,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const int gemm_ctas = static_cast<int>(gridDim.x) - (p.ag_ranks > 1 ? p.ag_copiers : 0) - (p.rs_ranks > 1 ? p.rs_copiers : 0);
   if (static_cast<int>(blockIdx.x) >= gemm_ctas) {
     pdl_wait();  // this rank's rows come from the previous kernel of the stream
-    if (p.ag_ranks > 1) ag_copier_run(p, static_cast<int>(blockIdx.x) - gemm_ctas);
-    else rs_copier_run(p, static_cast<int>(blockIdx.x) - gemm_ctas);
+    if (p.ag_ranks > 1) ag_copier_run(p, static_cast<int>(blockIdx.x) - gemm_ctas, smem_raw);
+    else rs_copier_run(p, static_cast<int>(blockIdx.x) - gemm_ctas, smem_raw);
     return;
   }
   if constexpr (PAIR) {
@@ -480,6 +520,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           uint8_t* sa = stage_base + stage * C::kStageBytes;
           uint8_t* sb = sa + C::kABytes;
           const int k0 = kb * p.bk_elems;
+          // debug builds: the tile must start inside the operands (partial tiles are zero-filled by TMA, but a tile
+          // that starts outside means the unit decoding went wrong) and x must be 16-byte aligned
+          if (!NX_INDEX_OK(w.m0 >= 0 && w.m0 < p.m && n0 >= 0 && n0 < p.n && k0 >= 0 && k0 < p.k && (k0 & 7) == 0 &&
+                           w.batch >= 0 && w.batch < p.batch, p.status)) {
+            ok = false;
+            *abort_flag = 1;
+            break;
+          }
           if constexpr (PAIR) {
             // both CTAs' bytes are counted on the even CTA's barrier, which that CTA arms for the pair
             if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * C::kStageBytes);
@@ -758,6 +806,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             if (lane == 0 && row0 < p.m) {
               for (int g = 0; g < gpos; ++g) {
                 const uint8_t* sg = st_base + g * per * 2048;
+                // a tiled store never starts at a negative or out-of-range coordinate, and x stays 16-byte aligned
+                if (!NX_INDEX_OK(gcol0 + 32 * g >= 0 && gcol0 + 32 * g < p.n && ((gcol0 + 32 * g) & 7) == 0 && row0 >= 0,
+                                 p.status))
+                  continue;
                 if (p.aux_out != nullptr) tma_store_3d(&tmap_aux, sg + 2048, gcol0 + 32 * g, row0, w.batch);
                 tma_store_3d(&tmap_out, sg, gcol0 + 32 * g, row0, w.batch);
               }
@@ -1009,6 +1061,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             gpos = 0;
             NX_PROF(e_issue += clock64() - e6;)
           }
+        } else if (!NX_INDEX_OK(row < p.m && col0 < p.n && valid > 0, p.status)) {
+          continue;
         } else if (p.out_dtype == NX_F32) {
           store_row32_f32(reinterpret_cast<float*>(p.out) + out_off, out_vec, valid, v);
         } else {
@@ -1201,7 +1255,7 @@ extern "C" int nx_gemm_rs(const NxGemmArgs* a, const NxGemmRs* rs, nx_stream_t s
     return -1;
   if (a->m % n || (a->m / n) % (2 * kBM) || a->n < 256 || (a->n & 7) || (a->ldo & 7)) return -1;
   const int c = rs->copier_ctas;
-  if (c < 2 || c > 2 * kBM || (c & (c - 1))) return -1;  // a power of two that divides the 256-row block
+  if (c < 2 || (c & 1)) return -1;  // whole clusters of two
   for (int q = 0; q < n; ++q)
     if (rs->slots[q] == nullptr || (reinterpret_cast<uintptr_t>(rs->slots[q]) & 15)) return -1;
   return gemm_impl(a, nullptr, stream_, rs);
@@ -1370,6 +1424,7 @@ int gemm_impl(const NxGemmArgs* a, const NxGemmAg* ag, nx_stream_t stream_, cons
       p.rot_rows = ((rs->rank + 1) % rs->n_ranks) * p.rs_rows;  // the rows this rank keeps come last
       p.rs_copiers = rs->copier_ctas;
       p.rs_expected = 16 * p.tiles_n;
+      p.rs_copy_own = rs->copy_own;
       p.rs_done = rs->done;
       for (int q = 0; q < rs->n_ranks; ++q) p.rs_slots[q] = rs->slots[q];
     }

@@ -59,6 +59,11 @@ int nx_moe_dispatch(const void* x, const int32_t* token_of, const int32_t* exper
 int nx_moe_combine(const NxPeerTable* bufs, const int32_t* expert, const int32_t* slot, const float* gate, void* y,
                    int tokens, int top_k, int d, int local_experts, int capacity, nx_stream_t stream);
 
+// dgate[t, j] = dy[t] . expert_output[owner][local expert][slot] with the row read from its owner's buffer.
+int nx_moe_gate_grad_peers(const void* dy, const NxPeerTable* bufs, const int32_t* expert, const int32_t* slot,
+                           float* dgate, int tokens, int top_k, int d, int local_experts, int capacity,
+                           nx_stream_t stream);
+
 // Vocabulary-parallel CE: local_stats [rows][3]; tables[q]: float[n][rows][3]; merged [rows][3].
 int nx_vocab_ce_exchange(const float* local_stats, const NxPeerTable* tables, const NxPeerTable* flags, int rank, int n,
                          int rows, int* counter, float* merged, int* status, nx_stream_t stream);
@@ -116,10 +121,12 @@ int nx_gemm_ag(const NxGemmArgs* args, const NxGemmAg* ag, nx_stream_t stream);
 // `done`: int[M / 256] in local device memory, zeroed by the caller before every call.
 // Requirements: BF16 in and out, no epilogue extras, M / n_ranks a multiple of 256, N >= 256, copier_ctas a power
 // of two in [2, 256].
+// copy_own = 0: the row block this rank owns is not copied into its own slot; it stays in args->out, and the caller
+// hands nx_comm_sum_slots that block as the rank's own contribution (own_rows).
 typedef struct NxGemmRs {
   void* slots[NX_MAX_PEERS];
   int* done;
-  int32_t n_ranks, rank, copier_ctas;
+  int32_t n_ranks, rank, copier_ctas, copy_own;
 } NxGemmRs;
 int nx_gemm_rs(const NxGemmArgs* args, const NxGemmRs* rs, nx_stream_t stream);
 // *counter += 1 (one thread), stream-ordered after the kernels that read it.
@@ -128,9 +135,10 @@ int nx_comm_bump(int* counter, nx_stream_t stream);
 // out[r][c] = (residual ? residual[r][c] : 0) + sum_{q < n} slots[q][r][c] (q in order, FP32 accumulation):
 // the owner's half of the slot form of GEMM -> reduce-scatter.  slots: BF16 [n][rows][ld_slots]; residual / out:
 // FP32 or BF16 with row strides ld_res / ld_out; out_lp (optional): a BF16 copy of the result, row stride ld_lp.
+// own_rows (optional): BF16 [rows][ld_slots] that stands in for slot `own_rank` (that slot is then not read).
 int nx_comm_sum_slots(const void* slots, int n, int rows, int cols, int64_t ld_slots, const void* residual,
                       int res_dtype, int64_t ld_res, void* out, int out_dtype, int64_t ld_out, void* out_lp,
-                      int64_t ld_lp, nx_stream_t stream);
+                      int64_t ld_lp, const void* own_rows, int own_rank, nx_stream_t stream);
 
 #ifdef __cplusplus
 }

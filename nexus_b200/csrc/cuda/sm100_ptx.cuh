@@ -27,7 +27,17 @@ enum StatusCode : int {
   kStatusTimeoutEpilogue = 3,
   kStatusTimeoutPeer = 4,
   kStatusBadArgument = 5,
+  kStatusBadIndex = 6,  // debug builds (-DNX_DEBUG_BOUNDS): a tile coordinate left its tensor; the access was skipped
 };
+
+// Debug-build bounds checks of tile index arithmetic.  With -DNX_DEBUG_BOUNDS, NX_INDEX_OK(cond, status) evaluates the
+// condition, records kStatusBadIndex in the status word when it fails and yields false so that the caller skips the
+// access (no trap, no assert: the context stays usable and the host reads the status).  In release builds it is `true`.
+#ifdef NX_DEBUG_BOUNDS
+#define NX_INDEX_OK(cond, status) ((cond) ? true : (atomicCAS((status), 0, ::nx::kStatusBadIndex), false))
+#else
+#define NX_INDEX_OK(cond, status) (true)
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -130,6 +140,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
       }
     }
   }
+}
+
+// Untiled bulk copy global -> this CTA's shared memory (no multicast); bytes a multiple of 16, both addresses 16-byte
+// aligned; completion is counted on `bar`.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 
 // ----------------------------------------------------------------------------------------------

@@ -45,7 +45,42 @@ def _align(n: int, a: int = 64) -> int:
 class GptModel:
     """Flat-buffer GPT-2 (pre-norm, learned positions, tied head, GELU-tanh) for one CUDA device."""
 
-    def __init__(self, config: LmConfig, device="cuda", seed: Optional[int] = None, vocab_pad: int = 128):
+    RECOMPUTE = ("none", "selective", "full", "every_k")
+    OPTIMIZERS = ("adamw", "adamw8bit", "zero_offload")
+    MASTERS = ("fp32", "cast_per_forward")
+
+    def __init__(self, config: LmConfig, device="cuda", seed: Optional[int] = None, vocab_pad: int = 128,
+                 recompute: str = "none", recompute_every: int = 2, optimizer: str = "adamw", master: str = "fp32",
+                 compute_dtype: str = "bf16", offload_grad_dtype: str = "bf16"):
+        """``recompute`` (activation memory against recomputation in the backward pass; include/nexus/cuda/gpt.hpp:66 of
+        the reference): "none" keeps every activation; "selective" keeps the GEMM outputs (qkv, attention output,
+        MLP pre-activation) and recomputes the norm outputs and the GELU output; "full" keeps only the residual stream
+        and re-runs the layer's forward; "every_k" treats layers with ``l % recompute_every == 0`` as "full".
+        ``optimizer``: "adamw" (FP32 moments on the device), "adamw8bit" (block-wise 8-bit moments for the matrices,
+        FP32 moments for norms and biases), "zero_offload" (FP32 master and moments in pinned host memory, gradients
+        copied to the host, AdamW on the CPU, BF16 weights copied back).  ``master``: "fp32" (BF16 working copy written
+        by the optimizer kernel) or "cast_per_forward" (the working copy is re-cast from the FP32 parameters at the
+        start of every forward pass).  Anything else the reference's model offers (FP16 with a loss scale, BF16-only
+        weights with stochastic rounding, the 8-bit optimizer applied layer by layer inside the backward pass) is
+        refused here with an error rather than ignored."""
+        if recompute not in self.RECOMPUTE:
+            raise ValueError(f"GptModel: recompute must be one of {self.RECOMPUTE}, got {recompute!r}")
+        if optimizer not in self.OPTIMIZERS:
+            raise ValueError(f"GptModel: optimizer must be one of {self.OPTIMIZERS}, got {optimizer!r} "
+                             "(the layer-wise fused 8-bit optimizer is not implemented)")
+        if master not in self.MASTERS:
+            raise ValueError(f"GptModel: master must be one of {self.MASTERS}, got {master!r} "
+                             "(BF16-only weights with stochastic rounding are not implemented)")
+        if compute_dtype != "bf16":
+            raise ValueError("GptModel computes in BF16; FP16 with a dynamic loss scale is not implemented "
+                             "(the attention kernels take BF16 only)")
+        if recompute == "every_k" and recompute_every < 1:
+            raise ValueError("GptModel: recompute_every must be >= 1")
+        if optimizer == "zero_offload" and master != "fp32":
+            raise ValueError("GptModel: zero_offload keeps the FP32 master on the host (master must be 'fp32')")
+        self.recompute, self.recompute_every = recompute, recompute_every
+        self.optimizer_kind, self.master_mode = optimizer, master
+        self.offload_grad_dtype = torch.bfloat16 if offload_grad_dtype == "bf16" else torch.float32
         if config.norm != "layernorm" or config.mlp != "gelu" or config.pos != "learned" or not config.bias:
             raise ValueError("GptModel implements the GPT-2 architecture (LayerNorm, GELU, learned positions, bias)")
         if not config.tie_embeddings:
@@ -79,8 +114,25 @@ class GptModel:
         self.params = torch.zeros(self.num_params, dtype=torch.float32, device=dev)     # FP32 master
         self.params_lp = torch.zeros(self.num_params, dtype=torch.bfloat16, device=dev)  # BF16 shadow
         self.grads = torch.zeros(self.num_params, dtype=torch.float32, device=dev)
-        self.m = torch.zeros(self.num_params, dtype=torch.float32, device=dev)
-        self.v = torch.zeros(self.num_params, dtype=torch.float32, device=dev)
+        self._tail = self.offsets["ln1_w"]      # matrices (and embeddings) before, 1-D parameters after
+        self._q8 = None
+        self._host = None
+        if optimizer == "adamw":
+            self.m = torch.zeros(self.num_params, dtype=torch.float32, device=dev)
+            self.v = torch.zeros(self.num_params, dtype=torch.float32, device=dev)
+        elif optimizer == "adamw8bit":
+            from ..ops import _lowp
+            self._q8 = _lowp.AdamW8bitState(self._tail, dev)                 # 8-bit moments of the matrices
+            self.m = torch.zeros(self.num_params - self._tail, dtype=torch.float32, device=dev)   # FP32 for the 1-D tail
+            self.v = torch.zeros(self.num_params - self._tail, dtype=torch.float32, device=dev)
+        else:  # zero_offload: master, moments and the gradient landing buffer live in pinned host memory
+            self.m = self.v = None
+            self._host = {"p": torch.zeros(self.num_params, dtype=torch.float32).pin_memory(),
+                          "m": torch.zeros(self.num_params, dtype=torch.float32).pin_memory(),
+                          "v": torch.zeros(self.num_params, dtype=torch.float32).pin_memory(),
+                          "g": torch.zeros(self.num_params, dtype=self.offload_grad_dtype).pin_memory(),
+                          "lp": torch.zeros(self.num_params, dtype=torch.bfloat16).pin_memory()}
+            self.last_cpu_update_ms = 0.0
         self.p = {n: self._view(self.params, n) for n in PARAM_ORDER}
         self.w = {n: self._view(self.params_lp, n) for n in PARAM_ORDER}
         self.g = {n: self._view(self.grads, n) for n in PARAM_ORDER}
@@ -90,6 +142,9 @@ class GptModel:
         self.chunks = K.make_chunks(
             [(self.offsets[n], math.prod(shapes[n]), 1.0 if n in DECAY else 0.0, 1.0) for n in PARAM_ORDER],
             device=dev)
+        self._tail_chunks = K.make_chunks(
+            [(self.offsets[n] - self._tail, math.prod(shapes[n]), 0.0, 1.0) for n in PARAM_ORDER
+             if self.offsets[n] >= self._tail], device=dev)
         self.loss_buf = torch.zeros(1, dtype=torch.float32, device=dev)
         self._acts = None
         self._acts_key = None
@@ -114,6 +169,8 @@ class GptModel:
         self.p["wte"][self.V:].zero_()  # padded vocabulary rows stay zero (their gradient is zero)
         for name in ("ln1_w", "ln2_w", "lnf_w"):
             self.p[name].fill_(1.0)
+        if self._host is not None:
+            self._host["p"].copy_(self.params)
         self.refresh_shadow()
 
     def rebind_buffers(self, params_lp: Optional[torch.Tensor] = None, grads: Optional[torch.Tensor] = None) -> None:
@@ -150,6 +207,36 @@ class GptModel:
         return sum(math.prod(self.shapes[n]) for n in PARAM_ORDER) - (self.Vp - self.V) * self.C
 
     # ------------------------------------------------------------------------------------ buffers
+    _LAYER_KEYS = ("ln1", "qkv", "atty", "lse", "ln2", "fch_pre", "fch")
+    _KEPT = {"none": set(_LAYER_KEYS), "selective": {"qkv", "atty", "lse", "fch_pre"}, "full": set()}
+
+    def layer_mode(self, l: int) -> str:
+        """How layer ``l`` treats its activations: "none" (kept), "selective" or "full" (recomputed)."""
+        if self.recompute == "every_k":
+            return "full" if l % self.recompute_every == 0 else "none"
+        return self.recompute
+
+    def _plan_slots(self):
+        """Per activation kind: the buffer index of every layer.  Kept activations get an index of their own; the
+        ones a layer recomputes share one scratch index."""
+        slots, counts = {}, {}
+        for key in self._LAYER_KEYS:
+            idx, nxt = [], 0
+            for l in range(self.L):
+                if key in self._KEPT[self.layer_mode(l)]:
+                    idx.append(nxt)
+                    nxt += 1
+                else:
+                    idx.append(-1)
+            shared = nxt if any(i < 0 for i in idx) else -1
+            slots[key] = [shared if i < 0 else i for i in idx]
+            counts[key] = nxt + (1 if shared >= 0 else 0)
+        return slots, counts
+
+    def activation_bytes(self) -> int:
+        a = self._acts or {}
+        return sum(t.numel() * t.element_size() for t in a.values() if isinstance(t, torch.Tensor))
+
     def _alloc_acts(self, B: int, T: int):
         key = (B, T)
         if self._acts_key == key:
@@ -157,17 +244,18 @@ class GptModel:
         dev, L, C, F, H = self.device, self.L, self.C, self.F, self.H
         N = B * T
         bf, f32 = torch.bfloat16, torch.float32
+        self._slots, cnt = self._plan_slots()
         a = {
             "res": torch.empty((2 * L + 1, N, C), dtype=f32, device=dev),   # residual stream checkpoints
-            "ln1": torch.empty((L, N, C), dtype=bf, device=dev),
+            "ln1": torch.empty((cnt["ln1"], N, C), dtype=bf, device=dev),
             "ln1_mean": torch.empty((L, N), dtype=f32, device=dev), "ln1_rstd": torch.empty((L, N), dtype=f32, device=dev),
-            "qkv": torch.empty((L, B, T, 3, H, C // H), dtype=bf, device=dev),
-            "atty": torch.empty((L, B, T, H, C // H), dtype=bf, device=dev),
-            "lse": torch.empty((L, B, H, T), dtype=f32, device=dev),
-            "ln2": torch.empty((L, N, C), dtype=bf, device=dev),
+            "qkv": torch.empty((cnt["qkv"], B, T, 3, H, C // H), dtype=bf, device=dev),
+            "atty": torch.empty((cnt["atty"], B, T, H, C // H), dtype=bf, device=dev),
+            "lse": torch.empty((cnt["lse"], B, H, T), dtype=f32, device=dev),
+            "ln2": torch.empty((cnt["ln2"], N, C), dtype=bf, device=dev),
             "ln2_mean": torch.empty((L, N), dtype=f32, device=dev), "ln2_rstd": torch.empty((L, N), dtype=f32, device=dev),
-            "fch_pre": torch.empty((L, N, F), dtype=bf, device=dev),
-            "fch": torch.empty((L, N, F), dtype=bf, device=dev),
+            "fch_pre": torch.empty((cnt["fch_pre"], N, F), dtype=bf, device=dev),
+            "fch": torch.empty((cnt["fch"], N, F), dtype=bf, device=dev),
             "lnf": torch.empty((N, C), dtype=bf, device=dev),
             "lnf_mean": torch.empty(N, dtype=f32, device=dev), "lnf_rstd": torch.empty(N, dtype=f32, device=dev),
             "logits": torch.empty((N, self.Vp), dtype=bf, device=dev),
@@ -190,22 +278,45 @@ class GptModel:
         a = self._alloc_acts(B, T)
         w, L, C = self.w, self.L, self.C
         N = B * T
+        if self.master_mode == "cast_per_forward":
+            self.refresh_shadow()
         res = a["res"]
         _embedding_into(res[0], tokens, w["wte"], w["wpe"], T)
         for l in range(L):
-            x_in, x_mid, x_out = res[2 * l], res[2 * l + 1], res[2 * l + 2]
-            _norm_into(a["ln1"][l], a["ln1_mean"][l], a["ln1_rstd"][l], x_in, self.p["ln1_w"][l], self.p["ln1_b"][l])
-            qkv = a["qkv"][l]
-            K.gemm(a["ln1"][l], w["qkv_w"][l], bias=w["qkv_b"][l], out=qkv.view(N, 3 * C))
-            _attn_fwd_into(a["atty"][l], a["lse"][l], qkv)
-            K.gemm(a["atty"][l].view(N, C), w["attproj_w"][l], bias=w["attproj_b"][l], residual=x_in, out=x_mid)
-            _norm_into(a["ln2"][l], a["ln2_mean"][l], a["ln2_rstd"][l], x_mid, self.p["ln2_w"][l], self.p["ln2_b"][l])
-            K.gemm(a["ln2"][l], w["fc_w"][l], bias=w["fc_b"][l], act="gelu", aux_out=a["fch_pre"][l], out=a["fch"][l])
-            K.gemm(a["fch"][l], w["fcproj_w"][l], bias=w["fcproj_b"][l], residual=x_mid, out=x_out)
+            self._layer_forward(a, l, B, T, output=True)
         _norm_into(a["lnf"], a["lnf_mean"], a["lnf_rstd"], res[2 * L], self.p["lnf_w"], self.p["lnf_b"])
         if want_logits:
             K.gemm(a["lnf"], w["wte"], out=a["logits"])
         return a["logits"]
+
+    def _layer_forward(self, a, l: int, B: int, T: int, output: bool, only: Optional[set] = None) -> None:
+        """Forward of layer ``l`` into its activation buffers.  ``output``: also form the residual outputs (the
+        forward pass); the recomputation of the backward pass only refills the activations named in ``only``."""
+        w, C = self.w, self.C
+        N = B * T
+        S = self._slots
+        res = a["res"]
+        x_in, x_mid, x_out = res[2 * l], res[2 * l + 1], res[2 * l + 2]
+        want = (lambda k: True) if only is None else (lambda k: k in only)
+        ln1, qkv, atty, lse = a["ln1"][S["ln1"][l]], a["qkv"][S["qkv"][l]], a["atty"][S["atty"][l]], a["lse"][S["lse"][l]]
+        ln2, fch_pre, fch = a["ln2"][S["ln2"][l]], a["fch_pre"][S["fch_pre"][l]], a["fch"][S["fch"][l]]
+        if want("ln1"):
+            _norm_into(ln1, a["ln1_mean"][l], a["ln1_rstd"][l], x_in, self.p["ln1_w"][l], self.p["ln1_b"][l])
+        if want("qkv"):
+            K.gemm(ln1, w["qkv_w"][l], bias=w["qkv_b"][l], out=qkv.view(N, 3 * C))
+        if want("atty"):
+            _attn_fwd_into(atty, lse, qkv)
+        if output:
+            K.gemm(atty.view(N, C), w["attproj_w"][l], bias=w["attproj_b"][l], residual=x_in, out=x_mid)
+        if want("ln2"):
+            _norm_into(ln2, a["ln2_mean"][l], a["ln2_rstd"][l], x_mid, self.p["ln2_w"][l], self.p["ln2_b"][l])
+        if want("fch_pre"):
+            K.gemm(ln2, w["fc_w"][l], bias=w["fc_b"][l], act="gelu", aux_out=fch_pre, out=fch)
+        elif want("fch"):   # the pre-activation was kept: only the GELU is redone
+            K._check(K.lib().nx_gelu(K._p(fch_pre), K._p(None), K._p(fch), _C.c_int(K._DT[fch.dtype]),
+                                     _C.c_int64(fch.numel()), K._stream()), "nx_gelu")
+        if output:
+            K.gemm(fch, w["fcproj_w"][l], bias=w["fcproj_b"][l], residual=x_mid, out=x_out)
 
     # --------------------------------------------------------------------------- forward + backward
     def forward_backward(self, tokens: torch.Tensor, grad_scale: float = 1.0, accumulate_loss: bool = False,
@@ -229,13 +340,19 @@ class GptModel:
         # each norm backward also sums the columns of its BF16 dx: the bias gradient of the projection that follows
         K.norm_bwd(a["dlnf"], res[2 * L], self.p["lnf_w"], a["lnf_mean"], a["lnf_rstd"], dx=dres, dx_lp=dres_lp,
                    dgamma=g["lnf_w"], dbeta=g["lnf_b"], accumulate_params=True, dx_colsum=g["fcproj_b"][L - 1])
+        S = self._slots
         for l in range(L - 1, -1, -1):
             x_in, x_mid = res[2 * l], res[2 * l + 1]
+            mode = self.layer_mode(l)
+            if mode != "none":   # refill what this layer did not keep (the residual stream is always kept)
+                self._layer_forward(a, l, B, T, output=False, only=set(self._LAYER_KEYS) - self._KEPT[mode])
+            ln1_l, qkv_l, atty_l, lse_l = (a[k][S[k][l]] for k in ("ln1", "qkv", "atty", "lse"))
+            ln2_l, fch_pre_l, fch_l = (a[k][S[k][l]] for k in ("ln2", "fch_pre", "fch"))
             # ---- MLP
-            K.gemm(dres_lp, w["fcproj_w"][l], b_mn=True, act="dgelu", aux_in=a["fch_pre"][l], out=a["dfch"])
-            K.gemm(dres_lp, a["fch"][l], a_mn=True, b_mn=True, out=g["fcproj_w"][l], accumulate=True, split_k=0)
+            K.gemm(dres_lp, w["fcproj_w"][l], b_mn=True, act="dgelu", aux_in=fch_pre_l, out=a["dfch"])
+            K.gemm(dres_lp, fch_l, a_mn=True, b_mn=True, out=g["fcproj_w"][l], accumulate=True, split_k=0)
             K.gemm(a["dfch"], w["fc_w"][l], b_mn=True, out=a["dln"])
-            K.gemm(a["dfch"], a["ln2"][l], a_mn=True, b_mn=True, out=g["fc_w"][l], accumulate=True, split_k=0)
+            K.gemm(a["dfch"], ln2_l, a_mn=True, b_mn=True, out=g["fc_w"][l], accumulate=True, split_k=0)
             K.colsum(a["dfch"], out=g["fc_b"][l], accumulate=True)
             K.norm_bwd(a["dln"], x_mid, self.p["ln2_w"][l], a["ln2_mean"][l], a["ln2_rstd"][l], add=dres,
                        dx=dres_other, dx_lp=dres_lp, dgamma=g["ln2_w"][l], dbeta=g["ln2_b"][l], accumulate_params=True,
@@ -243,14 +360,14 @@ class GptModel:
             dres, dres_other = dres_other, dres
             # ---- attention
             K.gemm(dres_lp, w["attproj_w"][l], b_mn=True, out=a["datty"].view(N, C))
-            K.gemm(dres_lp, a["atty"][l].view(N, C), a_mn=True, b_mn=True, out=g["attproj_w"][l], accumulate=True,
+            K.gemm(dres_lp, atty_l.view(N, C), a_mn=True, b_mn=True, out=g["attproj_w"][l], accumulate=True,
                    split_k=0)
-            qkv, dqkv = a["qkv"][l], a["dqkv"]
-            K.attention_bwd(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], a["atty"][l], a["lse"][l], a["datty"],
+            qkv, dqkv = qkv_l, a["dqkv"]
+            K.attention_bwd(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], atty_l, lse_l, a["datty"],
                             causal=True, dq=dqkv[:, :, 0], dk=dqkv[:, :, 1], dv=dqkv[:, :, 2])
             dq2 = dqkv.view(N, 3 * C)
             K.gemm(dq2, w["qkv_w"][l], b_mn=True, out=a["dln"])
-            K.gemm(dq2, a["ln1"][l], a_mn=True, b_mn=True, out=g["qkv_w"][l], accumulate=True, split_k=0)
+            K.gemm(dq2, ln1_l, a_mn=True, b_mn=True, out=g["qkv_w"][l], accumulate=True, split_k=0)
             K.colsum(dq2, out=g["qkv_b"][l], accumulate=True)
             K.norm_bwd(a["dln"], x_in, self.p["ln1_w"][l], a["ln1_mean"][l], a["ln1_rstd"][l], add=dres,
                        dx=dres_other, dx_lp=dres_lp, dgamma=g["ln1_w"][l], dbeta=g["ln1_b"][l], accumulate_params=True,
@@ -280,8 +397,78 @@ class GptModel:
     def optimizer_step(self) -> None:
         """Global-norm clip + AdamW on the flat buffers, refreshes the BF16 shadow, zeroes the gradients."""
         K.grad_norm(self.grads, self.opt_state)
-        K.adamw(self.params, self.grads, self.m, self.v, self.params_lp, self.chunks, self.opt_state, zero_grad=True)
+        shadow = None if self.master_mode == "cast_per_forward" else self.params_lp
+        if self.optimizer_kind == "adamw":
+            K.adamw(self.params, self.grads, self.m, self.v, shadow, self.chunks, self.opt_state, zero_grad=True)
+        elif self.optimizer_kind == "adamw8bit":
+            from ..ops import _lowp
+            t = self._tail
+            _lowp.adamw8(self.params[:t], shadow[:t] if shadow is not None else None, self.grads[:t], self._q8,
+                         self.opt_state, wd_scale=1.0, lr_scale=1.0, zero_grad=True)
+            K.adamw(self.params[t:], self.grads[t:], self.m, self.v, shadow[t:] if shadow is not None else None,
+                    self._tail_chunks, self.opt_state, zero_grad=True)
+        else:
+            self._offload_step()
         self.step_count += 1
+
+    def _offload_step(self) -> None:
+        """ZeRO-Offload: gradients -> pinned host memory (BF16 by default), AdamW on the CPU with the device's clip
+        factor and bias corrections, BF16 weights -> device.  One synchronisation per step."""
+        import time
+        import numpy as np
+        from .. import _native
+        h = self._host
+        h["g"].copy_(self.grads.to(h["g"].dtype), non_blocking=True)
+        st_host = self.opt_state.cpu()          # synchronises: the gradient copy and the norm are complete
+        st = K.unpack_opt_state(bytes(st_host.numpy().tobytes()))
+        self.grads.zero_()
+        if st.found_inf:
+            return
+        t0 = time.perf_counter()
+        g32 = h["g"].float().numpy() if h["g"].dtype != torch.float32 else h["g"].numpy()
+        pn, mn, vn = h["p"].numpy(), h["m"].numpy(), h["v"].numpy()
+        for name in PARAM_ORDER:
+            lo = self.offsets[name]
+            hi = lo + math.prod(self.shapes[name])
+            wd = st.weight_decay if name in DECAY else 0.0
+            _native.adamw_range(pn[lo:hi], np.ascontiguousarray(g32[lo:hi]), mn[lo:hi], vn[lo:hi], st.lr, wd, st.beta1,
+                                st.beta2, st.eps, st.inv_bias1, st.inv_bias2, st.clip_coef)
+        h["lp"].copy_(h["p"])
+        self.last_cpu_update_ms = (time.perf_counter() - t0) * 1e3
+        self.params_lp.copy_(h["lp"], non_blocking=True)
+        self.params[self._tail:].copy_(h["p"][self._tail:], non_blocking=True)   # the kernels read norms / biases in FP32
+
+    def optimizer_tensors(self) -> Dict[str, torch.Tensor]:
+        """Every tensor that, with the device optimizer state, makes up the training state (host copies)."""
+        if self.optimizer_kind == "adamw":
+            return {"params": self.params.cpu(), "m": self.m.cpu(), "v": self.v.cpu()}
+        if self.optimizer_kind == "adamw8bit":
+            q = self._q8
+            return {"params": self.params.cpu(), "m_tail": self.m.cpu(), "v_tail": self.v.cpu(), "qm": q.qm.cpu(),
+                    "qv": q.qv.cpu(), "absmax_m": q.absmax_m.cpu(), "absmax_v": q.absmax_v.cpu()}
+        h = self._host
+        return {"params": h["p"].clone(), "m": h["m"].clone(), "v": h["v"].clone()}
+
+    def load_optimizer_tensors(self, d: Dict[str, torch.Tensor]) -> None:
+        if self.optimizer_kind == "adamw":
+            self.params.copy_(d["params"]); self.m.copy_(d["m"]); self.v.copy_(d["v"])
+        elif self.optimizer_kind == "adamw8bit":
+            q = self._q8
+            self.params.copy_(d["params"]); self.m.copy_(d["m_tail"]); self.v.copy_(d["v_tail"])
+            q.qm.copy_(d["qm"]); q.qv.copy_(d["qv"]); q.absmax_m.copy_(d["absmax_m"]); q.absmax_v.copy_(d["absmax_v"])
+        else:
+            h = self._host
+            h["p"].copy_(d["params"]); h["m"].copy_(d["m"]); h["v"].copy_(d["v"])
+            self.params.copy_(h["p"])
+        self.refresh_shadow()
+
+    def optimizer_state_bytes(self) -> Tuple[int, int]:
+        """(device bytes, host bytes) of master weights + moments (the working copy and gradients excluded)."""
+        if self.optimizer_kind == "adamw":
+            return 12 * self.num_params, 0
+        if self.optimizer_kind == "adamw8bit":
+            return 4 * self.num_params + self._q8.nbytes() + 8 * (self.num_params - self._tail), 0
+        return 4 * self.num_params, 12 * self.num_params + self._host["g"].numel() * self._host["g"].element_size()
 
     def read_opt_state(self) -> "K.OptState":
         return K.unpack_opt_state(bytes(self.opt_state.cpu().numpy().tobytes()))

@@ -298,7 +298,7 @@ class LlamaTpModel:
         self.ws.barrier()   # the owners have consumed the previous contents of their slots
         gemm_rs(self.ws, a_mat, w, A["partial"], A["slots_sym"], A["rs_done"], b_mn=b_mn, copier_ctas=self.copier_ctas)
         self.ws.barrier()   # every rank's partial blocks have landed
-        sum_slots(A["slots"], n, Ml, d, out, residual=residual, out_lp=out_lp)
+        sum_slots(A["slots"], n, Ml, d, out, residual=residual, out_lp=out_lp, own=self._own(A["partial"]), own_rank=self.r)
 
     def _own(self, full_rows):
         """This rank's row block of a gathered [M, d] buffer."""

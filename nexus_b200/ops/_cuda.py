@@ -8,6 +8,7 @@ through a per-device status word, read with :func:`check_status`.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 from typing import Dict, Tuple, Optional
 
@@ -84,11 +85,14 @@ def lib():
     """Load the kernel library (once).  Raises when it has not been built."""
     global _lib
     if _lib is None:
-        if not _LIB_PATH.exists():
+        path = _LIB_PATH
+        if os.environ.get("NEXUS_B200_DEBUG_BOUNDS", "0") == "1":   # kernels with the index checks compiled in
+            path = _LIB_PATH.with_name("libnexus_b200_cuda_dbg.so")
+        if not path.exists():
             raise RuntimeError(
-                f"{_LIB_PATH} is missing: build it with `python -m nexus_b200._build` "
+                f"{path} is missing: build it with `python -m nexus_b200._build` "
                 "(the sm_100a kernels are required on a GPU machine; there is no fallback)")
-        _lib = C.CDLL(str(_LIB_PATH))
+        _lib = C.CDLL(str(path))
         _lib.nx_gemm_workspace_bytes.restype = C.c_size_t
         _lib.nx_norm_bwd_scratch_bytes.restype = C.c_size_t
         _lib.nx_ce_state_bytes.restype = C.c_size_t
@@ -131,7 +135,8 @@ def check_status(device=None) -> None:
     code = int(status_word(device).item())
     if code != 0:
         status_word(device).zero_()
-        names = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "peer", 5: "bad argument"}
+        names = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "peer", 5: "bad argument",
+                 6: "tile index out of range (debug-build bounds check)"}
         raise RuntimeError(f"kernel wait timed out / failed in role: {names.get(code, code)}")
 
 

@@ -323,15 +323,17 @@ def gemm_ag(site: GatherSite, gather: SymmetricBuffer, b: torch.Tensor, out: tor
 
 class GemmRs(C.Structure):
     _fields_ = [("slots", C.c_void_p * MAX_PEERS), ("done", C.c_void_p), ("n_ranks", C.c_int32), ("rank", C.c_int32),
-                ("copier_ctas", C.c_int32)]
+                ("copier_ctas", C.c_int32), ("copy_own", C.c_int32)]
 
 
 def gemm_rs(ws: SymmetricWorkspace, a: torch.Tensor, b: torch.Tensor, partial: torch.Tensor, slots: SymmetricBuffer,
-            done: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, copier_ctas: int = 8) -> None:
+            done: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, copier_ctas: int = 8,
+            copy_own: bool = False) -> None:
     """GEMM -> reduce-scatter as ONE kernel: ``partial[M, N] = a @ b^T`` (BF16, local scratch) on the CTA-pair kernel,
     whose copier CTAs push every finished 256-row block into slot ``rank`` of the owner's ``slots`` buffer
     ([n][M/n][N] BF16).  ``done``: int32 [M / 256] scratch.  Follow with ``ws.barrier()`` and `sum_slots`; precede
-    with ``ws.barrier()`` when the owners may still be reading the previous contents of their slots."""
+    with ``ws.barrier()`` when the owners may still be reading the previous contents of their slots.  Unless
+    ``copy_own``, the block this rank owns stays in ``partial`` only: pass `sum_slots` ``own=partial[rank block]``."""
     M = a.shape[1] if a_mn else a.shape[0]
     g = K.GemmArgs()
     g.a, g.b, g.out = a.data_ptr(), b.data_ptr(), partial.data_ptr()
@@ -345,20 +347,22 @@ def gemm_rs(ws: SymmetricWorkspace, a: torch.Tensor, b: torch.Tensor, partial: t
     for q in range(ws.n):
         d.slots[q] = slots.ptrs[q]
     d.done = done.data_ptr()
-    d.n_ranks, d.rank, d.copier_ctas = ws.n, ws.rank, copier_ctas
+    d.n_ranks, d.rank, d.copier_ctas, d.copy_own = ws.n, ws.rank, copier_ctas, int(copy_own)
     done.zero_()
     K._check(K.lib().nx_gemm_rs(C.byref(g), C.byref(d), K._stream()), "nx_gemm_rs")
 
 
 def sum_slots(slots: torch.Tensor, n: int, rows: int, cols: int, out: torch.Tensor, *, residual=None,
-              out_lp: Optional[torch.Tensor] = None) -> torch.Tensor:
+              out_lp: Optional[torch.Tensor] = None, own: Optional[torch.Tensor] = None, own_rank: int = 0) -> torch.Tensor:
     """out = residual + sum of the n BF16 slots ``slots[q][rows][cols]`` in rank order (the owner's half of the slot
-    form of GEMM -> reduce-scatter); ``out_lp`` receives a BF16 copy."""
+    form of GEMM -> reduce-scatter); ``out_lp`` receives a BF16 copy.  ``own`` ([rows, cols] BF16) stands in for slot
+    ``own_rank`` (this rank's own partial sums, which never left its memory)."""
     K._check(K.lib().nx_comm_sum_slots(K._p(slots), C.c_int(n), C.c_int(rows), C.c_int(cols), C.c_int64(cols),
                                        K._p(residual), C.c_int(K._DT[residual.dtype] if residual is not None else 0),
                                        C.c_int64(residual.stride(0) if residual is not None else 0), K._p(out),
                                        C.c_int(K._DT[out.dtype]), C.c_int64(out.stride(0)), K._p(out_lp),
-                                       C.c_int64(out_lp.stride(0) if out_lp is not None else 0), K._stream()),
+                                       C.c_int64(out_lp.stride(0) if out_lp is not None else 0), K._p(own),
+                                       C.c_int(own_rank), K._stream()),
              "nx_comm_sum_slots")
     return out
 

@@ -7,3 +7,5 @@ from .loggers import (ConsoleLogger, CsvLogger, JsonlLogger, TensorBoardLogger, 
 from .schedule import ConstantLr, InverseSqrt, LinearLr, LrSchedule, WarmupCosine, WSD  # noqa: F401
 from .trainer import EpochStats, LossScaler, Trainer, TrainerBuilder  # noqa: F401
 from . import callbacks  # noqa: F401
+from .distributed import (DataParallelStep, DataParallelTrainer, LoopProfile, all_reduce_mean,  # noqa: F401
+                          allreduce_mean_gradients, broadcast_parameters)

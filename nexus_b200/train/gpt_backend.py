@@ -26,12 +26,15 @@ PEAK_BF16_FLOPS = {10: 2.25e15, 9: 0.989e15, 8: 0.312e15}
 
 class GptLmBackend(LmBackend):
     def __init__(self, config: LmConfig, micro_batch: int, seq_len: int, device="cuda", seed: int = 1234,
-                 deterministic: bool = False):
+                 deterministic: bool = False, recompute: str = "none", recompute_every: int = 2,
+                 optimizer: str = "adamw", master: str = "fp32", compute_dtype: str = "bf16"):
         self.dev = torch.device(device)
         if self.dev.index is None:
             self.dev = torch.device("cuda", torch.cuda.current_device())
         torch.cuda.set_device(self.dev)
-        self.model = GptModel(config, device=self.dev, seed=seed)
+        # unknown or unimplemented modes raise inside GptModel: nothing is silently ignored
+        self.model = GptModel(config, device=self.dev, seed=seed, recompute=recompute, recompute_every=recompute_every,
+                              optimizer=optimizer, master=master, compute_dtype=compute_dtype)
         self.model.deterministic_embedding = deterministic
         self.B, self.T = micro_batch, seq_len
         self._host_tokens = [torch.empty((micro_batch, seq_len), dtype=torch.int32).pin_memory() for _ in range(2)]
@@ -137,6 +140,9 @@ class GptLmBackend(LmBackend):
         """Shards master weights, moments and the gradient reduction over ``group`` using the fused
         peer-memory kernels (reduce-scatter + norm exchange + AdamW + all-gather, no NCCL in the step)."""
         from ..parallel.symm import FusedShardedOptimizer, SymmetricWorkspace
+        if self.model.optimizer_kind != "adamw" or self.model.master_mode != "fp32":
+            raise ValueError("the sharded optimizer implements FP32-master AdamW; it cannot be combined with "
+                             f"optimizer='{self.model.optimizer_kind}' / master='{self.model.master_mode}'")
         self._pg_fsdp = group
         group.broadcast_tensor(self.model.params, 0)
         self.model.refresh_shadow()
@@ -258,8 +264,11 @@ class GptLmBackend(LmBackend):
             torch.save({"layout": "fsdp", "world": sh.ws.n, "rank": sh.ws.rank, "off": sh.off, "count": sh.count,
                         "num_params": m.num_params, "master": sh.master.cpu(), "m": sh.m.cpu(), "v": sh.v.cpu(),
                         "opt": m.opt_state.cpu(), "step_count": m.step_count}, buf)
-        else:
+        elif m.optimizer_kind == "adamw":
             torch.save({"layout": "replicated", "params": m.params.cpu(), "m": m.m.cpu(), "v": m.v.cpu(),
+                        "opt": m.opt_state.cpu(), "step_count": m.step_count}, buf)
+        else:
+            torch.save({"layout": "replicated", "kind": m.optimizer_kind, "tensors": m.optimizer_tensors(),
                         "opt": m.opt_state.cpu(), "step_count": m.step_count}, buf)
         return buf.getvalue()
 
@@ -320,6 +329,14 @@ class GptLmBackend(LmBackend):
             m.opt_state.copy_(d["opt"])
             m.step_count = d["step_count"]
             sh.install_weights(sh.gather_master())
+            m.grads.zero_()
+            return
+        if "tensors" in d:
+            if d.get("kind") != m.optimizer_kind:
+                raise ValueError(f"state was written by optimizer '{d.get('kind')}', this model uses '{m.optimizer_kind}'")
+            m.load_optimizer_tensors(d["tensors"])
+            m.opt_state.copy_(d["opt"])
+            m.step_count = d["step_count"]
             m.grads.zero_()
             return
         self._install_full_state(d["params"], d["m"], d["v"], d["opt"], d["step_count"])

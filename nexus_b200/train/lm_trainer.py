@@ -245,6 +245,8 @@ class LanguageTrainerBuilder:
         self._clip = 1.0
         self._precision, self._master = "bf16", "fp32"
         self._recompute = "none"
+        self._recompute_every = 2
+        self._optimizer_kind = "adamw"
         self._eval_every, self._eval_batches, self._log_every = 0, 4, 1
         self._seed = 1234
         self._deterministic = False
@@ -274,7 +276,8 @@ class LanguageTrainerBuilder:
     def seq_len(self, n: int): self._seq_len = n; return self
     def grad_clip(self, c: float): self._clip = c; return self
     def precision(self, p: str, master: str = "fp32"): self._precision, self._master = p.lower(), master.lower(); return self
-    def recompute(self, r: str): self._recompute = r; return self
+    def recompute(self, r: str, every: int = 2): self._recompute, self._recompute_every = r, every; return self
+    def optimizer_kind(self, kind: str): self._optimizer_kind = kind; return self
     def eval_every(self, n: int, batches: int = 4): self._eval_every, self._eval_batches = n, batches; return self
     def log_every(self, n: int): self._log_every = n; return self
     def execution_policy(self, device: str): self._device = device; return self
@@ -330,8 +333,11 @@ def _make_backend(b: LanguageTrainerBuilder) -> LmBackend:
         if use_gpu and cfg.norm == "layernorm" and cfg.mlp == "gelu" and cfg.pos == "learned" and cfg.tie_embeddings \
                 and cfg.bias and b._precision == "bf16":
             from .gpt_backend import GptLmBackend
+            master = {"fp32": "fp32", "cast_per_forward": "cast_per_forward", "castperforward": "cast_per_forward"}.get(
+                b._master, b._master)   # anything else ("none", ...) is refused by the model with a clear message
             return GptLmBackend(cfg, b._micro_batch, b._seq_len, device=b._device, seed=b._seed,
-                                deterministic=b._deterministic)
+                                deterministic=b._deterministic, recompute=b._recompute,
+                                recompute_every=b._recompute_every, optimizer=b._optimizer_kind, master=master)
         from ..lm.model import LanguageModel
         model = LanguageModel(cfg)
     from .torch_backend import TorchLmBackend

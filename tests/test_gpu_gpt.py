@@ -69,3 +69,80 @@ def test_gpt_training_reduces_loss_and_trainer_graph_matches_eager():
     eager, graph = run(False), run(True)
     assert eager[-1] < eager[0]
     assert np.allclose(eager, graph, rtol=2e-3, atol=2e-3)
+
+
+def _tiny_cfg():
+    from nexus_b200.lm.config import preset
+    cfg = preset("gpt2-124m")
+    cfg.n_layer, cfg.d_model, cfg.n_head, cfg.d_ff, cfg.vocab_size, cfg.max_position = 3, 128, 2, 512, 500, 128
+    return cfg
+
+
+@pytest.mark.parametrize("mode,every", [("selective", 2), ("full", 2), ("every_k", 2)])
+def test_recompute_modes_give_the_same_gradients_with_fewer_saved_bytes(mode, every):
+    from nexus_b200.models.gpt import GptModel
+    from nexus_b200.ops import _cuda as K
+    """Every recompute mode re-runs the same kernels on the same inputs: loss and gradients equal the keep-everything
+    run bit for bit (deterministic embedding), and the activation buffers shrink."""
+    cfg = _tiny_cfg()
+    tokens = torch.randint(0, cfg.vocab_size, (2, 128), dtype=torch.int32, device="cuda",
+                           generator=torch.Generator(device="cuda").manual_seed(3))
+    base = GptModel(cfg, device="cuda", seed=5)
+    base.deterministic_embedding = True
+    other = GptModel(cfg, device="cuda", seed=5, recompute=mode, recompute_every=every)
+    other.deterministic_embedding = True
+    l0 = float(base.forward_backward(tokens).item())
+    l1 = float(other.forward_backward(tokens).item())
+    torch.cuda.synchronize()
+    K.check_status()
+    assert l0 == l1
+    rel = (other.grads - base.grads).norm().item() / base.grads.norm().item()
+    assert rel < 1e-3, rel          # split-K reductions add in a free order; everything else is identical
+    assert other.activation_bytes() < base.activation_bytes()
+    assert [other.layer_mode(l) for l in range(3)] == {"selective": ["selective"] * 3, "full": ["full"] * 3,
+                                                       "every_k": ["full", "none", "full"]}[mode]
+
+
+def test_eight_bit_and_offloaded_optimizers_track_fp32_adamw():
+    from nexus_b200.models.gpt import AdamWConfig, GptModel
+    from nexus_b200.ops import _cuda as K
+    """Three optimizer kinds on the same model and data: the CPU (offloaded) AdamW follows the device AdamW closely
+    (same operation order; BF16 gradient transfer), the 8-bit one follows within the quantisation error, and all
+    reduce the loss."""
+    cfg = _tiny_cfg()
+    tokens = torch.randint(0, cfg.vocab_size, (2, 128), dtype=torch.int32, device="cuda",
+                           generator=torch.Generator(device="cuda").manual_seed(4))
+    runs = {}
+    for kind, kw in (("adamw", {}), ("adamw8bit", {}), ("zero_offload", {"offload_grad_dtype": "f32"}),
+                     ("adamw", {"master": "cast_per_forward"})):
+        m = GptModel(cfg, device="cuda", seed=6, optimizer=kind, **kw)
+        m.deterministic_embedding = True
+        m.set_optimizer(AdamWConfig(lr=1e-3))
+        losses = []
+        for _ in range(6):
+            losses.append(float(m.forward_backward(tokens).item()))
+            m.optimizer_step()
+        torch.cuda.synchronize()
+        K.check_status()
+        runs[kind + kw.get("master", "")] = (losses, m.optimizer_tensors()["params"].float().clone())
+        assert losses[-1] < losses[0] - 0.3, (kind, losses)
+    ref_losses, ref_p = runs["adamw"]
+    init = GptModel(cfg, device="cuda", seed=6).params.cpu()
+    upd = (ref_p - init).norm().item()
+    off_losses, off_p = runs["zero_offload"]
+    assert max(abs(a - b) for a, b in zip(ref_losses, off_losses)) < 2e-2
+    assert (off_p - ref_p).norm().item() / upd < 0.1
+    q_losses, q_p = runs["adamw8bit"]
+    assert max(abs(a - b) for a, b in zip(ref_losses, q_losses)) < 0.15
+    c_losses, c_p = runs["adamwcast_per_forward"]
+    assert max(abs(a - b) for a, b in zip(ref_losses, c_losses)) < 2e-2
+    dev_bytes, host_bytes = GptModel(cfg, device="cuda", optimizer="zero_offload").optimizer_state_bytes()
+    assert host_bytes > 0 and dev_bytes < 12 * init.numel()
+
+
+def test_unimplemented_modes_are_refused_not_ignored():
+    from nexus_b200.models.gpt import GptModel
+    cfg = _tiny_cfg()
+    for kw in ({"optimizer": "adamw8bit_fused"}, {"master": "none"}, {"compute_dtype": "f16"}, {"recompute": "sometimes"}):
+        with pytest.raises(ValueError):
+            GptModel(cfg, device="cuda", **kw)

@@ -139,3 +139,41 @@ def test_legacy_language_trainer():
     vals = np.random.default_rng(1).integers(0, 256, size=4 * 16 * 3)
     losses = lt.fit(TokenRows(vals, 4, 16), epochs=3)
     assert len(losses) == 3 and losses[-1] < losses[0]
+
+
+def test_in_process_data_parallel_step_equals_one_replica_on_the_whole_batch():
+    """Three replicas, each on a third of the batch, gradients averaged: the same update as one model on the whole
+    batch (mean loss over rows); the loop profile accounts for the time."""
+    import copy
+    from nexus_b200 import nn as nn_
+    from nexus_b200.loss import CrossEntropy
+    from nexus_b200.optim import SGD
+    from nexus_b200.train import DataParallelStep, DataParallelTrainer, LoopProfile, all_reduce_mean
+    torch.manual_seed(0)
+    base = nn_.Sequential(nn_.Linear(4, 8, True), nn_.ReLU(), nn_.Linear(8, 3, True))
+    single = copy.deepcopy(base)
+    reps = [copy.deepcopy(base), copy.deepcopy(base), copy.deepcopy(base)]
+    with torch.no_grad():                                  # replicas start different: construction must broadcast
+        for p in reps[1].parameters():
+            p.add_(1.0)
+    x, y = torch.randn(6, 4), torch.randint(0, 3, (6,))
+    step = DataParallelStep(reps, CrossEntropy().forward_backward, SGD(list(reps[0].parameters()), lr=0.1))
+    o1 = SGD(list(single.parameters()), lr=0.1)
+    for _ in range(3):
+        got = step.step(x, y)
+        pred = single(x)
+        loss, grad = CrossEntropy().forward_backward(pred, y)
+        o1.zero_grad()
+        pred.backward(grad)
+        o1.step()
+        assert abs(got - float(loss)) < 1e-5
+    for a, b, c in zip(single.parameters(), reps[0].parameters(), reps[2].parameters()):
+        assert torch.allclose(a, b, atol=1e-5) and torch.equal(b, c)
+    pr = step.profile
+    assert pr.steps == 3 and pr.wall_s >= pr.optimizer_s > 0 and "forward_s=" in pr.report() and "%" in pr.report()
+    tr = DataParallelTrainer(reps, CrossEntropy().forward_backward, SGD(list(reps[0].parameters()), lr=0.1))
+    hist = tr.fit([(x, y), (x, y)], epochs=2)
+    assert len(hist) == 2 and hist[1] < hist[0] and tr.profile.batches == 4
+    ranks = [[1.0, 3.0], [3.0, 5.0]]
+    all_reduce_mean(ranks)
+    assert ranks == [[2.0, 4.0], [2.0, 4.0]] and LoopProfile().report().startswith("batches=0")
