@@ -205,8 +205,9 @@ def run_fused(args) -> int:
     loss_log = torch.zeros(args.steps + max(1, args.warmup), dtype=torch.float32, device=dev)
     step_no = [0]
 
-    def step(tokens):
-        refill(tokens)
+    def step(tokens, fresh=True):
+        if fresh:
+            refill(tokens)
         for i, t in enumerate(tokens):
             model.forward_backward(t, grad_scale=1.0 / n_micro, accumulate_loss=i > 0, loss_weight=1.0 / n_micro)
         model.optimizer_step()
@@ -225,13 +226,14 @@ def run_fused(args) -> int:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            step(sets[0])
+            step(sets[0], fresh=False)     # the token buffers are refilled outside the graph, before every replay
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = K.launch_count
     e0.record()
     for i in range(args.steps):
         if graph is not None:
+            refill(sets[0])
             graph.replay()
         else:
             step(sets[i % 2])

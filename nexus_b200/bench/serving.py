@@ -28,7 +28,9 @@ def main(argv=None) -> int:
     ap.add_argument("--max-new", type=int, default=256)
     ap.add_argument("--prompt-min", type=int, default=128)
     ap.add_argument("--prompt-max", type=int, default=1024)
-    ap.add_argument("--quant", default="bf16", help="weights: bf16 | w8a8 | w4a16")
+    ap.add_argument("--quant", default="bf16", help="weights: bf16 | fp8 | w8a8 | w4a16")
+    ap.add_argument("--tp-comm", default="fused", choices=["fused", "nccl"],
+                    help="tensor-parallel all-reduce: the peer-memory kernel (default) or NCCL")
     ap.add_argument("--kv", default="bf16", help="KV cache: bf16 | int8 | fp8")
     ap.add_argument("--batch-tokens", type=int, default=8192)
     ap.add_argument("--kv-gb", type=float, default=0.0, help="KV pool per GPU in GiB (0: sized for the workload)")
@@ -63,7 +65,7 @@ def main(argv=None) -> int:
     kv_bytes = int(args.kv_gb * 2 ** 30) if args.kv_gb > 0 else int(kv_need * 1.15) + (1 << 28)
     eng = Engine(w, EngineConfig(device=dev, precision="bf16" if cuda else "fp32", max_seqs=args.requests,
                                  max_tokens=args.batch_tokens, block_size=16, kv_bytes=kv_bytes,
-                                 quant=QuantOptions(weights=args.quant, kv=args.kv), tp_graphs=bool(args.tp_graphs)),
+                                 quant=QuantOptions(weights=args.quant, kv=args.kv), tp_graphs=bool(args.tp_graphs), tp_comm=args.tp_comm),
                  group=group)
     greedy = SamplingParams(temperature=0.0)
 

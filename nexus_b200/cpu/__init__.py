@@ -35,6 +35,29 @@ def gemm_nt(x, w, bias=None, threads: int = 0) -> np.ndarray:
     return N.cpu_gemm_nt(pool(threads), np.ascontiguousarray(x, np.float32), np.ascontiguousarray(w, np.float32), bias)
 
 
+def to_bf16_bits(w) -> np.ndarray:
+    """FP32 -> BF16 bit patterns (uint16, round to nearest even)."""
+    u = np.ascontiguousarray(w, np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def gemm_nt_bf16(x, w_bits, bias=None, threads: int = 0) -> np.ndarray:
+    """x [m, k] @ w[n, k]^T (+ bias) with the weights stored as BF16 bit patterns (`to_bf16_bits`)."""
+    return N.cpu_gemm_nt_bf16(pool(threads), np.ascontiguousarray(x, np.float32), np.ascontiguousarray(w_bits, np.uint16), bias)
+
+
+def flash_attention(q, k, v, causal=True, window=0, scale=None, softcap=0.0, alibi=None, threads: int = 0):
+    """Blocked attention on the CPU (online softmax over 64-key blocks, no [Tq, Tk] matrix): q [B, Tq, H, D],
+    k / v [B, Tk, Hkv, D] FP32; causal with the last query aligned to the last key, sliding window, soft-capping,
+    ALiBi slopes, grouped-query heads.  Returns (o [B, Tq, H, D], lse [B, H, Tq]).
+    Parity: include/nexus/attention/cpu.hpp:42-47 of the reference (`flash_attention_forward` with `AttentionParams`)."""
+    q = np.ascontiguousarray(q, np.float32)
+    sc = float(scale) if scale is not None else q.shape[-1] ** -0.5
+    al = np.zeros(0, np.float32) if alibi is None else np.ascontiguousarray(alibi, np.float32)
+    return N.cpu_flash_attention(pool(threads), q, np.ascontiguousarray(k, np.float32), np.ascontiguousarray(v, np.float32),
+                                 bool(causal), int(window), sc, float(softcap), al)
+
+
 def pack_weights(w, bits: int = 8, group: int = 32) -> PackedWeights:
     return N.pack_weights(np.ascontiguousarray(w, np.float32), bits, group)
 

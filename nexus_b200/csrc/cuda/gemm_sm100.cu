@@ -522,8 +522,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const int k0 = kb * p.bk_elems;
           // debug builds: the tile must start inside the operands (partial tiles are zero-filled by TMA, but a tile
           // that starts outside means the unit decoding went wrong) and x must be 16-byte aligned
-          if (!NX_INDEX_OK(w.m0 >= 0 && w.m0 < p.m && n0 >= 0 && n0 < p.n && k0 >= 0 && k0 < p.k && (k0 & 7) == 0 &&
-                           w.batch >= 0 && w.batch < p.batch, p.status)) {
+          if (!NX_INDEX_OK(w.m0 - m_off >= 0 && w.m0 - m_off < p.m && n0 >= 0 && n0 < p.n && k0 >= 0 && k0 < p.k &&
+                           (k0 & 7) == 0 && w.batch >= 0 && w.batch < p.batch, p.status)) {
             ok = false;
             *abort_flag = 1;
             break;

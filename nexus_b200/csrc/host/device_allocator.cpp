@@ -549,6 +549,142 @@ py::array_t<float> cpu_gemm_nt(ThreadPool& pool, FArr x, FArr w, py::object bias
   return y;
 }
 
+// The same product with the weights held as BF16 bit patterns (uint16, upper half of the FP32 word): half the
+// weight bytes of cpu_gemm_nt, FP32 accumulation in the same index order.
+py::array_t<float> cpu_gemm_nt_bf16(ThreadPool& pool, FArr x,
+                                    py::array_t<uint16_t, py::array::c_style | py::array::forcecast> w, py::object bias) {
+  if (x.ndim() != 2 || w.ndim() != 2 || x.shape(1) != w.shape(1)) throw std::invalid_argument("gemm_nt_bf16: shapes");
+  const int64_t M = x.shape(0), K = x.shape(1), N = w.shape(0);
+  py::array_t<float> y({M, N});
+  const float* xp = x.data();
+  const uint16_t* wp = w.data();
+  const float* bp = nullptr;
+  FArr b;
+  if (!bias.is_none()) {
+    b = bias.cast<FArr>();
+    bp = b.data();
+  }
+  float* yp = y.mutable_data();
+  {
+    py::gil_scoped_release rel;
+    pool.run(N, [&](int, int64_t n0, int64_t n1) {
+      for (int64_t n = n0; n < n1; ++n)
+        for (int64_t m = 0; m < M; ++m) {
+          const float* xr = xp + m * K;
+          const uint16_t* wr = wp + n * K;
+          float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          int64_t k = 0;
+          for (; k + 8 <= K; k += 8)
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t bits = static_cast<uint32_t>(wr[k + j]) << 16;
+              float wv;
+              std::memcpy(&wv, &bits, 4);
+              acc[j] += xr[k + j] * wv;
+            }
+          float s = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
+          for (; k < K; ++k) {
+            const uint32_t bits = static_cast<uint32_t>(wr[k]) << 16;
+            float wv;
+            std::memcpy(&wv, &bits, 4);
+            s += xr[k] * wv;
+          }
+          yp[m * N + n] = s + (bp ? bp[n] : 0.0f);
+        }
+    });
+  }
+  return y;
+}
+
+// Blocked ("flash") attention on the CPU, FP32: q [B, Tq, H, D], k / v [B, Tk, Hkv, D] (GQA: H a multiple of Hkv).
+// One (batch, head, 64-row query block) per work item; key blocks of 64 with the online-softmax recurrence, so the
+// [Tq, Tk] score matrix never exists.  Causal masking aligns the last query with the last key (Tq <= Tk), `window`
+// > 0 limits each query to its last `window` keys, `softcap` > 0 passes scores through softcap * tanh(s / softcap),
+// `alibi` (H slopes, may be empty) adds slope * (key - query position).  Returns (o [B, Tq, H, D], lse [B, H, Tq]).
+py::tuple cpu_flash_attention(ThreadPool& pool, FArr q, FArr k, FArr v, bool causal, int window, double scale,
+                              double softcap, FArr alibi) {
+  if (q.ndim() != 4 || k.ndim() != 4 || v.ndim() != 4) throw std::invalid_argument("flash_attention: [B, T, H, D] tensors");
+  const int64_t B = q.shape(0), Tq = q.shape(1), H = q.shape(2), D = q.shape(3);
+  const int64_t Tk = k.shape(1), Hkv = k.shape(2);
+  if (k.shape(0) != B || v.shape(0) != B || k.shape(3) != D || v.shape(3) != D || v.shape(1) != Tk || v.shape(2) != Hkv ||
+      Hkv < 1 || H % Hkv)
+    throw std::invalid_argument("flash_attention: shapes");
+  if (alibi.size() != 0 && alibi.size() != H) throw std::invalid_argument("flash_attention: alibi needs one slope per head");
+  py::array_t<float> o({B, Tq, H, D});
+  py::array_t<float> lse({B, H, Tq});
+  const float *qp = q.data(), *kp = k.data(), *vp = v.data();
+  const float* ap = alibi.size() ? alibi.data() : nullptr;
+  float* op = o.mutable_data();
+  float* lp = lse.mutable_data();
+  constexpr int64_t BQ = 64, BK = 64;
+  const int64_t nqb = (Tq + BQ - 1) / BQ;
+  const int64_t items = B * H * nqb;
+  const int64_t shift = Tk - Tq;  // query i sits at key position i + shift
+  {
+    py::gil_scoped_release rel;
+    pool.run(items, [&](int, int64_t i0, int64_t i1) {
+      std::vector<float> s(BQ * BK), acc(BQ * D), mrow(BQ), lrow(BQ);
+      for (int64_t it = i0; it < i1; ++it) {
+        const int64_t qb = it % nqb, h = (it / nqb) % H, b = it / (nqb * H);
+        const int64_t hk = h / (H / Hkv);
+        const int64_t q0 = qb * BQ, rows = std::min(BQ, Tq - q0);
+        std::fill(acc.begin(), acc.end(), 0.0f);
+        std::fill(mrow.begin(), mrow.end(), -INFINITY);
+        std::fill(lrow.begin(), lrow.end(), 0.0f);
+        int64_t k_hi = Tk;
+        if (causal) k_hi = std::min(Tk, q0 + rows + shift);
+        int64_t k_lo = 0;
+        if (window > 0) k_lo = std::max<int64_t>(0, q0 + shift - window + 1);
+        for (int64_t k0 = (k_lo / BK) * BK; k0 < k_hi; k0 += BK) {
+          const int64_t cols = std::min(BK, Tk - k0);
+          for (int64_t r = 0; r < rows; ++r) {
+            const float* qr = qp + ((b * Tq + q0 + r) * H + h) * D;
+            const int64_t qpos = q0 + r + shift;
+            for (int64_t c = 0; c < cols; ++c) {
+              const int64_t kpos = k0 + c;
+              float val = -INFINITY;
+              const bool masked = (causal && kpos > qpos) || (window > 0 && kpos < qpos - window + 1);
+              if (!masked) {
+                const float* kr = kp + ((b * Tk + kpos) * Hkv + hk) * D;
+                float d0 = 0.0f;
+                for (int64_t e = 0; e < D; ++e) d0 += qr[e] * kr[e];
+                val = d0 * static_cast<float>(scale);
+                if (softcap > 0.0) val = static_cast<float>(softcap) * std::tanh(val / static_cast<float>(softcap));
+                if (ap) val += ap[h] * static_cast<float>(kpos - qpos);
+              }
+              s[r * BK + c] = val;
+            }
+          }
+          for (int64_t r = 0; r < rows; ++r) {
+            float mx = mrow[r];
+            for (int64_t c = 0; c < cols; ++c) mx = std::max(mx, s[r * BK + c]);
+            if (mx == -INFINITY) continue;  // nothing visible in this block yet
+            const float corr = std::exp(mrow[r] - mx);
+            float sum = 0.0f;
+            float* ar = acc.data() + r * D;
+            for (int64_t e = 0; e < D; ++e) ar[e] *= corr;
+            for (int64_t c = 0; c < cols; ++c) {
+              const float pval = std::exp(s[r * BK + c] - mx);
+              if (pval == 0.0f) continue;
+              sum += pval;
+              const float* vr = vp + ((b * Tk + k0 + c) * Hkv + hk) * D;
+              for (int64_t e = 0; e < D; ++e) ar[e] += pval * vr[e];
+            }
+            lrow[r] = lrow[r] * corr + sum;
+            mrow[r] = mx;
+          }
+        }
+        for (int64_t r = 0; r < rows; ++r) {
+          float* orow = op + ((b * Tq + q0 + r) * H + h) * D;
+          const float inv = lrow[r] > 0.0f ? 1.0f / lrow[r] : 0.0f;
+          for (int64_t e = 0; e < D; ++e) orow[e] = acc[r * D + e] * inv;
+          lp[(b * H + h) * Tq + q0 + r] = lrow[r] > 0.0f ? mrow[r] + std::log(lrow[r]) : -INFINITY;
+        }
+      }
+    });
+  }
+  return py::make_tuple(o, lse);
+}
+
 // INT8 weights with one scale per output row, or INT4 (two nibbles per byte, value = nibble - 8) with one
 // scale per group; activations are quantised per row to INT8 first (integer dot products, exact).
 struct PackedWeights {
@@ -679,4 +815,8 @@ void bind_device_allocator(py::module_& m) {
   m.def("pack_weights", &pack_weights, py::arg("w"), py::arg("bits") = 8, py::arg("group") = 32);
   m.def("cpu_gemm_nt", &cpu_gemm_nt, py::arg("pool"), py::arg("x"), py::arg("w"), py::arg("bias") = py::none());
   m.def("cpu_quant_gemm", &cpu_quant_gemm);
+  m.def("cpu_gemm_nt_bf16", &cpu_gemm_nt_bf16, py::arg("pool"), py::arg("x"), py::arg("w"), py::arg("bias") = py::none());
+  m.def("cpu_flash_attention", &cpu_flash_attention, py::arg("pool"), py::arg("q"), py::arg("k"), py::arg("v"),
+        py::arg("causal") = true, py::arg("window") = 0, py::arg("scale") = 1.0, py::arg("softcap") = 0.0,
+        py::arg("alibi") = FArr(0));
 }

@@ -310,6 +310,14 @@ def attention(q, k, v, causal=True, window=0, scale=None, softcap=0.0, alibi_slo
         slopes = None if alibi_slopes is None else alibi_slopes.detach().float().contiguous().to(q.device)
         return _FlashAttention.apply(q, k, v, causal, window, scale, float(softcap), slopes,
                                      (float(dropout_p), int(dropout_seed), int(dropout_offset)))
+    if not q.is_cuda and q.dtype == torch.float32 and dropout_p == 0.0 and \
+            not (torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)):
+        # CPU inference: the blocked native kernel (no [Tq, Tk] score matrix)
+        from .. import cpu as _cpu
+        o, _ = _cpu.flash_attention(q.detach().contiguous().numpy(), k.detach().contiguous().numpy(),
+                                    v.detach().contiguous().numpy(), causal=causal, window=window, scale=scale,
+                                    softcap=softcap, alibi=None if alibi_slopes is None else alibi_slopes.detach().float().numpy())
+        return torch.from_numpy(o)
     return attention_reference(q, k, v, causal, window, scale, softcap, alibi_slopes, dropout_p, dropout_seed,
                                dropout_offset)
 

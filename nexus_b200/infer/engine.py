@@ -131,8 +131,10 @@ class EngineConfig:
     quant: QuantOptions = field(default_factory=QuantOptions)
     device: str = "cuda"
     decode_splits: int = 0       # 0: chosen per step from the batch size and context length
-    tp_graphs: bool = False      # decode CUDA graphs of a tensor-parallel engine (its NCCL all-reduces are captured too);
+    tp_graphs: bool = False      # decode CUDA graphs of a tensor-parallel engine (its all-reduces are captured too);
                                  # call Engine.release_graphs() before the process group is destroyed
+    tp_comm: str = "nccl"        # "nccl" | "fused": the tensor-parallel all-reduces run as the peer-memory kernel
+                                 # (symmetric buffers, flag barriers with a device-resident generation: graph safe)
 
 
 @dataclass
@@ -189,6 +191,16 @@ class _Linear:
             self.nbytes = self.w.numel() * self.w.element_size()
             return
         wf = w.float()
+        if quant == "fp8":
+            if not fast:
+                raise ValueError("fp8 weights need the kernel path (CUDA, bf16 precision)")
+            # E4M3 codes with one scale per output row; activations are quantised per row at run time
+            scale = wf.abs().amax(dim=1).clamp_min(1e-12) / 448.0
+            self.wq = (wf / scale[:, None]).to(dev).to(torch.float8_e4m3fn).contiguous()
+            self.scales = scale.to(dev, torch.float32).contiguous()
+            self.nbytes = self.wq.numel() + self.scales.numel() * 4
+            self._dense = None
+            return
         if quant == "w8a8":
             if smooth is not None:  # x' = x / s, w' = w * s
                 wf = wf * smooth[None, :]
@@ -213,6 +225,9 @@ class _Linear:
         """Dequantised weights (BF16 on the kernel path, FP32 otherwise)."""
         if self.quant == "bf16":
             return self.w
+        if self.quant == "fp8":
+            from ..ops import _lowp as LP
+            return LP.fp8_dequantize(self.wq, None).float().mul_(self.scales[:, None]).to(torch.bfloat16)
         if self.fast:
             from ..ops import _infer as I
             return I.wq_dequant(self.wq, self.scales, bits=8 if self.quant == "w8a8" else 4, group=self.group, k=self.k)
@@ -267,6 +282,16 @@ class Engine:
         self._static: Dict[int, dict] = {}
         self._pin = None
         self._capture = None
+        self._fused_ar = None
+        if self.tp > 1 and cfg.tp_comm == "fused":
+            if not self.fast:
+                raise ValueError("tp_comm='fused' needs the kernel path (CUDA, bf16 precision)")
+            from ..parallel.symm import SymmetricWorkspace
+            ws = SymmetricWorkspace(group)
+            n = (cfg.max_tokens * self.d + 7) // 8 * 8
+            self._fused_ar = (ws, ws.alloc(n, torch.float32), ws.alloc(n, torch.float32))
+        elif cfg.tp_comm not in ("nccl", "fused"):
+            raise ValueError("tp_comm must be 'nccl' or 'fused'")
 
     # ----------------------------------------------------------------------------- weights / KV pool
     def _load(self, w: Gpt2Weights) -> None:
@@ -501,9 +526,15 @@ class Engine:
         from ..ops import _infer as I
         n = x.shape[0]
         od = torch.float32 if residual is not None else (out_dtype or torch.bfloat16)
+        if lin.quant == "fp8" and n > self._skinny and lin.k % 16 == 0:
+            # FP8 tensor-core GEMM: half the weight bytes of BF16 (decode is bound by reading the weights)
+            from ..ops import _lowp as LP
+            y = LP.fp8_linear(x.to(torch.bfloat16), lin.wq, lin.scales, bias=lin.bias, act=act,
+                              out_dtype=torch.float32 if residual is not None else od)
+            return residual.add_(y) if residual is not None else y
         if lin.quant == "w8a8":
             _, x, _ = I.quant_rows(x, lin.inv_smooth, want_codes=False, want_fake=True)
-        if lin.quant != "bf16" and n <= self._skinny:   # weights stay packed: the GEMV dequantises on the fly
+        if lin.quant not in ("bf16", "fp8") and n <= self._skinny:   # weights stay packed: the GEMV dequantises on the fly
             y = I.wq_gemv(x, lin.wq, lin.scales, bits=8 if lin.quant == "w8a8" else 4, group=lin.group, bias=lin.bias)
             if act == "gelu":
                 y = torch.nn.functional.gelu(y, approximate="tanh")
@@ -526,9 +557,18 @@ class Engine:
         return K.norm_fwd(x, w, b, out_dtype=torch.bfloat16, want_stats=False)[0]
 
     def _all_reduce(self, t):
-        if self.tp > 1:
+        """Sum of ``t`` [n, d] FP32 over the tensor-parallel group."""
+        if self.tp == 1:
+            return t
+        if self._fused_ar is None:
             self.group.all_reduce_tensor(t, "sum")
-        return t
+            return t
+        from ..parallel.symm import fused_all_reduce
+        ws, src, dst = self._fused_ar
+        count = (t.numel() + 7) // 8 * 8
+        src.local[: t.numel()].copy_(t.reshape(-1))
+        fused_all_reduce(ws, src, dst, count)
+        return dst.local[: t.numel()].view(t.shape)
 
     # ----------------------------------------------------------------------------- forward
     def forward(self, chunks: Sequence[Chunk], layers: int = -1) -> torch.Tensor:

@@ -48,13 +48,53 @@ class Norm(nn.Module):
         return F_.fused_layernorm(x, self.weight, self.bias, self.eps)
 
 
+CPU_WEIGHT_MODES = ("auto", "f32", "bf16", "int8", "int4")
+
+
 class Linear(nn.Module):
     def __init__(self, d_in: int, d_out: int, bias: bool):
         super().__init__()
         self.weight = nn.Parameter(torch.empty(d_out, d_in))
         self.bias = nn.Parameter(torch.zeros(d_out)) if bias else None
+        self._cpu_pack = None      # (mode, packed weights) after LanguageModel.prepare_cpu_inference
+
+    def pack_for_cpu(self, mode: str) -> int:
+        """Prepares the inference form of the weights on the CPU; returns the bytes it occupies."""
+        from .. import cpu as _cpu
+        w = self.weight.detach().float().cpu().numpy()
+        if mode in ("auto", "f32"):
+            self._cpu_pack = ("f32", w.copy())
+            return w.nbytes
+        if mode == "bf16":
+            bits = _cpu.to_bf16_bits(w)
+            self._cpu_pack = ("bf16", bits)
+            return bits.nbytes
+        bits_n = 8 if mode == "int8" else 4
+        group = 32 if w.shape[1] % 32 == 0 else 0
+        if bits_n == 4 and not group:
+            raise ValueError("int4 CPU inference needs in-features divisible by 32")
+        self._cpu_pack = (mode, _cpu.pack_weights(w, bits_n, group or 32))
+        return w.size * bits_n // 8 + w.shape[0] * 4 * (1 if bits_n == 8 else w.shape[1] // 32)
+
+    def _cpu_fast(self, x, act: str):
+        from .. import cpu as _cpu
+        mode, pack = self._cpu_pack
+        x2 = x.detach().reshape(-1, x.shape[-1]).float().numpy()
+        bias = None if self.bias is None else self.bias.detach().float().numpy()
+        if mode == "f32":
+            y = _cpu.gemm_nt(x2, pack, bias)
+        elif mode == "bf16":
+            y = _cpu.gemm_nt_bf16(x2, pack, bias)
+        else:
+            y = _cpu.quant_gemm(x2, pack)
+            if bias is not None:
+                y = y + bias
+        out = torch.from_numpy(y).view(*x.shape[:-1], y.shape[-1])
+        return F_._act_fwd(out, act) if act != "identity" else out
 
     def forward(self, x, act: str = "identity"):
+        if self._cpu_pack is not None and not x.is_cuda and not torch.is_grad_enabled():
+            return self._cpu_fast(x, act)
         return F_.fused_linear(x, self.weight, self.bias, act)
 
 
@@ -226,6 +266,29 @@ class LanguageModel(nn.Module):
         if self.rope is not None:
             self.rope.to(self.wte.device)
         return out
+
+    # ---------------------------------------------------------------------------- CPU inference weight modes
+    def prepare_cpu_inference(self, mode: str = "f32") -> None:
+        """Packs every projection for inference on the CPU: "f32" (contiguous FP32 GEMM), "bf16" (BF16 weight bits,
+        FP32 accumulation: half the weight bytes), "int8" (per-output-row symmetric INT8, activations quantised per row,
+        integer dot products), "int4" (nibbles with one scale per 32 inputs).  Only no-grad forward passes on CPU
+        tensors use the packed form (generation, evaluation); training keeps the FP32 parameters.  Attention on that
+        path is the blocked native kernel.  Parity: `LanguageModel::prepare_cpu_inference(CpuWeightMode)` of the
+        reference (include/nexus/lm/model.hpp:56-61,151)."""
+        mode = mode.lower()
+        if mode not in CPU_WEIGHT_MODES:
+            raise ValueError(f"cpu weight mode must be one of {CPU_WEIGHT_MODES}")
+        total = 0
+        for m in self.modules():
+            if isinstance(m, Linear):
+                total += m.pack_for_cpu(mode)
+        self._cpu_mode, self._cpu_bytes = ("f32" if mode == "auto" else mode), total
+
+    def cpu_weight_mode(self) -> str:
+        return getattr(self, "_cpu_mode", "auto")
+
+    def cpu_inference_weight_bytes(self) -> int:
+        return getattr(self, "_cpu_bytes", 0)
 
     def set_rng(self, seed: int, offset: int) -> None:
         self.rng_state = (seed, offset)

@@ -238,7 +238,7 @@ def test_engine_generate_speculative_graphs_and_server():
     K.check_status()
 
 
-@pytest.mark.parametrize("weights,kv", [("w8a8", "bf16"), ("w4a16", "int8"), ("bf16", "fp8")])
+@pytest.mark.parametrize("weights,kv", [("w8a8", "bf16"), ("w4a16", "int8"), ("bf16", "fp8"), ("fp8", "bf16")])
 def test_engine_quantised_modes(weights, kv):
     from nexus_b200.infer import Chunk, Engine, EngineConfig, QuantOptions, generate
     w = _weights(layers=2)
@@ -249,7 +249,7 @@ def test_engine_quantised_modes(weights, kv):
     s0, sq = e0.add_sequence(), eq.add_sequence()
     a = e0.forward([Chunk(s0, toks, 8)]).float().cpu()[:, :1000]
     b = eq.forward([Chunk(sq, toks, 8)]).float().cpu()[:, :1000]
-    tol = 0.5 if weights == "w4a16" else 0.3   # 4-bit Gaussian weights: ~14 % error per layer
+    tol = 0.5 if weights == "w4a16" else (0.15 if weights == "fp8" else 0.3)   # 4-bit Gaussian weights: ~14 % error per layer
     assert (a - b).norm() / a.norm() < tol
     a = e0.forward([Chunk(s0, [5], 1, True)]).float().cpu()[:, :1000]
     b = eq.forward([Chunk(sq, [5], 1, True)]).float().cpu()[:, :1000]

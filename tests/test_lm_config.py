@@ -42,3 +42,54 @@ def test_moe_validation():
     c.moe_top_k = 99
     with pytest.raises(C.ConfigError):
         C.validate(c)
+
+
+def test_cpu_inference_weight_modes_and_native_attention():
+    """`prepare_cpu_inference`: the packed no-grad forward (native GEMMs + blocked attention) follows the autograd
+    forward; BF16 / INT8 / INT4 shrink the weights and stay within their quantisation error; generation runs."""
+    import torch
+    from nexus_b200.lm.config import preset
+    from nexus_b200.lm.model import LanguageModel
+    cfg = preset("nano")
+    m = LanguageModel(cfg)
+    toks = torch.randint(0, cfg.vocab_size, (2, 24), generator=torch.Generator().manual_seed(0))
+    with torch.enable_grad():
+        ref = m.logits(toks).detach()
+    sizes = {}
+    for mode, tol in (("f32", 2e-4), ("bf16", 2e-2), ("int8", 6e-2), ("int4", 0.5)):
+        m.prepare_cpu_inference(mode)
+        assert m.cpu_weight_mode() == mode
+        sizes[mode] = m.cpu_inference_weight_bytes()
+        with torch.no_grad():
+            got = m.logits(toks)
+        rel = ((got - ref).norm() / ref.norm()).item()
+        assert rel < tol, (mode, rel)
+    assert sizes["f32"] > sizes["bf16"] > sizes["int8"] > sizes["int4"] > 0
+    with torch.no_grad():
+        out = m.generate(toks[:1, :4], 5)
+    assert out.shape[-1] == 9
+    with pytest.raises(ValueError):
+        m.prepare_cpu_inference("fp4")
+
+
+def test_cpu_flash_attention_matches_math_attention_with_every_option():
+    import numpy as np
+    import torch
+    from nexus_b200 import cpu
+    from nexus_b200.fused.ops import attention_reference
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(2, 70, 4, 16, generator=g)
+    k = torch.randn(2, 100, 2, 16, generator=g)
+    v = torch.randn(2, 100, 2, 16, generator=g)
+    slopes = torch.tensor([0.1, 0.2, 0.3, 0.4])
+    for kw in ({"causal": True}, {"causal": False}, {"causal": True, "window": 33}, {"causal": True, "softcap": 20.0},
+               {"causal": True, "alibi_slopes": slopes}):
+        want = attention_reference(q, k, v, **kw)
+        got, lse = cpu.flash_attention(q.numpy(), k.numpy(), v.numpy(), causal=kw.get("causal", True),
+                                       window=kw.get("window", 0), softcap=kw.get("softcap", 0.0),
+                                       alibi=None if "alibi_slopes" not in kw else slopes.numpy())
+        assert np.abs(got - want.numpy()).max() < 1e-4, kw
+        assert lse.shape == (2, 4, 70) and np.isfinite(lse).all()
+    a = cpu.flash_attention(q.numpy(), k.numpy(), v.numpy(), threads=1)[0]
+    b = cpu.flash_attention(q.numpy(), k.numpy(), v.numpy(), threads=4)[0]
+    assert np.array_equal(a, b)           # the work split does not change a single bit
