@@ -35,6 +35,10 @@ def main(argv=None) -> int:
     ap.add_argument("--check", action="store_true")
     ap.add_argument("--copiers", type=int, default=8, help="copier CTAs of the all-gather GEMM")
     ap.add_argument("--pull", action="store_true", help="also time the pull forms (remote tiles re-read per column tile)")
+    ap.add_argument("--loopback", action="store_true",
+                    help="one GPU: run the fused kernels as rank 0 of 2 with the 'peer' buffers in this GPU's own memory and "
+                         "the arrival flags pre-set (for profiler captures, which must be single-process: the copier CTAs "
+                         "and the flag waits run as they do over NVLink, the pushed bytes land in local HBM)")
     ap.add_argument("--peak-tflops", type=float, default=0.0, help="GEMM peak for the roofline (default: MEASURED_PEAKS.json)")
     args = ap.parse_args(argv)
 
@@ -45,6 +49,8 @@ def main(argv=None) -> int:
     world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    if args.loopback:
+        return _loopback(args, dev)
     pg = init_process_group("nccl", f"cuda:{local}")
     ws = SymmetricWorkspace(pg)
     n = world
@@ -194,6 +200,57 @@ def main(argv=None) -> int:
     report("wgrad_k[qkv]", [n_loc, d, M], 2.0 * M * n_loc * d, (n - 1) * Ml * d * 2, fused, base, err)
 
     return _finish(rank, n, M, d, peak, link, rows, pg)
+
+
+def _loopback(args, dev) -> int:
+    """Rank 0 of an emulated 2-rank group on ONE GPU (see --loopback)."""
+    import types
+    from ..ops import _cuda as K
+    from ..parallel.symm import SymmetricBuffer, gemm_ag, gemm_rs, sum_slots
+    n, M, d = 2, args.tokens, args.d
+    Ml = M // n
+    bf = torch.bfloat16
+    ff_loc = (args.ff // n + 127) // 128 * 128
+    ws = types.SimpleNamespace(n=n, rank=0, device=dev)
+
+    def pair(numel, dtype, fill=None):
+        a, b = torch.zeros(numel, dtype=dtype, device=dev), torch.zeros(numel, dtype=dtype, device=dev)
+        if fill is not None:
+            a.fill_(fill)
+        return SymmetricBuffer(a, [a.data_ptr(), b.data_ptr()])
+
+    site = types.SimpleNamespace(ws=ws, rows=Ml, flags=pair(n * (Ml // 128), torch.int32, fill=1 << 30),
+                                 counter=torch.zeros(1, dtype=torch.int32, device=dev))
+    xg = pair(M * d, bf)
+    xg.local.copy_(torch.randn(M * d, device=dev).to(bf))
+    w = (torch.randn(2 * ff_loc, d, device=dev) * 0.02).to(bf)
+    y = torch.empty(M, 2 * ff_loc, dtype=bf, device=dev)
+    a = torch.randn(M, ff_loc, device=dev).to(bf)
+    wd = (torch.randn(d, ff_loc, device=dev) * 0.02).to(bf)
+    slots = pair(n * Ml * d, bf)
+    partial = torch.empty(M, d, dtype=bf, device=dev)
+    done = torch.zeros(M // 256, dtype=torch.int32, device=dev)
+    z = torch.empty(Ml, d, dtype=torch.float32, device=dev)
+    out = {}
+    for name, fn in (("ag_gemm[up]", lambda: gemm_ag(site, xg, w, y, k=d, copier_ctas=args.copiers)),
+                     ("gemm_rs[down]", lambda: (gemm_rs(ws, a, wd, partial, slots, done, copier_ctas=args.copiers),
+                                                sum_slots(slots.local, n, Ml, d, z, own=partial[:Ml], own_rank=0)))):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        K.check_status(dev)
+        out[name] = round(e0.elapsed_time(e1) / args.iters, 4)
+    ref = xg.local.view(M, d)[:512].float() @ w.float().t()
+    err = float((y[:512].float() - ref).abs().max() / ref.abs().max())
+    print(json.dumps({"bench": "fused_comm loopback (1 GPU as rank 0 of 2; pushed bytes land in local HBM)", "tokens": M,
+                      "d": d, "copiers": args.copiers, "ms": out, "ag_gemm_max_rel_err": err}))
+    return 0
 
 
 def _finish(rank, n, M, d, peak, link, rows, pg) -> int:

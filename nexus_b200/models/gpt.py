@@ -149,6 +149,7 @@ class GptModel:
         self._acts = None
         self._acts_key = None
         self.step_count = 0
+        self.backward_hook = None     # callable(stage): see set_backward_hook
         self.deterministic_embedding = False
         self.init_weights(config.seed if seed is None else seed)
 
@@ -289,6 +290,27 @@ class GptModel:
             K.gemm(a["lnf"], w["wte"], out=a["logits"])
         return a["logits"]
 
+    STAGE_HEAD, STAGE_EMBEDDING = -1, -2
+
+    def set_backward_hook(self, hook) -> None:
+        """``hook(stage)`` is called on the host while the backward pass is being enqueued, right after the kernels
+        that complete a stage's gradients: STAGE_HEAD (final norm), then layer L-1 ... 0 (every per-layer slice of
+        that layer), then STAGE_EMBEDDING (wte, wpe).  A data-parallel backend records an event there and starts
+        reducing the stage's gradients on another stream.  Parity: GptModel::set_backward_hook of the reference
+        (include/nexus/cuda/gpt.hpp, kStageHead / kStageEmbedding)."""
+        self.backward_hook = hook
+
+    def layer_grad_ranges(self, l0: int, l1: int):
+        """(offset, count) of the gradient slices of layers [l0, l1) in the flat buffer, one per per-layer tensor."""
+        out = []
+        for name in PARAM_ORDER:
+            shp = self.shapes[name]
+            if name in ("wte", "wpe", "lnf_w", "lnf_b"):
+                continue
+            per = math.prod(shp[1:])
+            out.append((self.offsets[name] + l0 * per, (l1 - l0) * per))
+        return out
+
     def _layer_forward(self, a, l: int, B: int, T: int, output: bool, only: Optional[set] = None) -> None:
         """Forward of layer ``l`` into its activation buffers.  ``output``: also form the residual outputs (the
         forward pass); the recomputation of the backward pass only refills the activations named in ``only``."""
@@ -373,8 +395,12 @@ class GptModel:
                        dx=dres_other, dx_lp=dres_lp, dgamma=g["ln1_w"][l], dbeta=g["ln1_b"][l], accumulate_params=True,
                        dx_colsum=g["fcproj_b"][l - 1] if l > 0 else None)
             dres, dres_other = dres_other, dres
+            if hook is not None:
+                hook(l)
         K.embedding_bwd(tokens, dres.view(B, T, C), g["wte"], g["wpe"][:T], B, T,
                         deterministic=self.deterministic_embedding)
+        if hook is not None:
+            hook(self.STAGE_EMBEDDING)
         return self.loss_buf
 
     # ---------------------------------------------------------------------------------- optimizer

@@ -10,6 +10,7 @@ on the device (NCCL / NVLink).
 from __future__ import annotations
 
 import io
+import os
 from typing import List, Optional
 
 import numpy as np
@@ -110,10 +111,11 @@ class GptLmBackend(LmBackend):
             if index == count - 1:
                 self._count = count
             return
+        self._ddp_arm(index == count - 1)
         self.model.forward_backward(dev_tokens, grad_scale=grad_weight, accumulate_loss=index > 0,
                                     loss_weight=grad_weight)
-        if index == count - 1 and self._pg is not None and self._sharded is None:
-            self._pg.all_reduce_tensor(self.model.grads, "sum")
+        if index == count - 1:
+            self._ddp_finish()
 
     def optimizer_step(self, optimizer: AdamW, lr: float, clip: float) -> None:
         cfg = AdamWConfig(lr=lr, beta1=optimizer.beta1, beta2=optimizer.beta2, eps=optimizer.eps,
@@ -129,6 +131,23 @@ class GptLmBackend(LmBackend):
             self._run_graph()
             return
         self._opt_step()
+
+    def _ddp_arm(self, last_micro_step: bool) -> None:
+        """Buckets are reduced only during the last micro-step of an accumulation window."""
+        if getattr(self, "_ddp", None) is not None:
+            self._ddp["armed"] = bool(last_micro_step)
+
+    def _ddp_finish(self) -> None:
+        """After the last backward pass: the optimizer's stream waits for the last bucket (bucketed form), or the
+        whole gradient buffer is all-reduced at once (NCCL form)."""
+        if self._pg is None or self._sharded is not None:
+            return
+        d = getattr(self, "_ddp", None)
+        if d is not None:
+            torch.cuda.current_stream().wait_event(d["done"])
+            d["armed"] = False
+            return
+        self._pg.all_reduce_tensor(self.model.grads, "sum")
 
     def _opt_step(self) -> None:
         if self._sharded is not None:
@@ -175,9 +194,9 @@ class GptLmBackend(LmBackend):
             self._opt_cfg = AdamWConfig(lr=lr)
             m.set_optimizer(self._opt_cfg)
         world = self._ws.n if self._sharded is not None else (self._pg.size() if self._pg is not None else 1)
+        self._ddp_arm(True)
         m.forward_backward(tokens_dev, grad_scale=1.0 / world)
-        if self._pg is not None and self._sharded is None:
-            self._pg.all_reduce_tensor(m.grads, "sum")
+        self._ddp_finish()
         self._opt_step()
 
     # ------------------------------------------------------------------------------- CUDA graph
@@ -211,10 +230,10 @@ class GptLmBackend(LmBackend):
     def _graph_body(self, count: int, weights) -> None:
         m = self.model
         for i in range(count):
+            self._ddp_arm(i == count - 1)
             m.forward_backward(self._dev_tokens[i], grad_scale=weights[i], accumulate_loss=i > 0,
                                loss_weight=weights[i])
-        if self._pg is not None and self._sharded is None:
-            self._pg.all_reduce_tensor(m.grads, "sum")
+        self._ddp_finish()
         self._opt_step()
 
     # ------------------------------------------------------------------------------- evaluation
@@ -358,7 +377,77 @@ class GptLmBackend(LmBackend):
 
     # ------------------------------------------------------------------------------ data parallel
     def attach_process_group(self, group, options=None) -> None:
+        """Data-parallel gradient averaging over ``group``.  With ``options.bucketed`` (default when the group has
+        peer-mapped memory) the gradients live in a symmetric buffer and are reduced bucket by bucket while the
+        backward pass is still being executed: the model's backward hook fires after the head, after every layer and
+        after the embedding; every ``options.bucket_layers`` layers the finished gradient ranges are all-reduced in
+        place by the peer-memory kernel (two-shot, FP32) on a second stream that waits on an event of the compute
+        stream; the optimizer waits for the last bucket.  Otherwise one NCCL all-reduce of the whole buffer follows the
+        backward pass.  Parity: the staged, bucketed DDP of the reference's GPU backend
+        (src/cuda/lm_backend.cpp:211-290, include/nexus/dist/ddp.hpp:36-110), which moves buckets through host memory."""
         self._pg = group
+        self._ddp = None
+        bucketed = getattr(options, "bucketed", None)
+        if bucketed is None:
+            bucketed = group.size() > 1 and str(self.dev).startswith("cuda") and getattr(group, "group", None) is not None \
+                and os.environ.get("NEXUS_DDP_BUCKETED", "1") == "1"
+        if not bucketed or group.size() == 1:
+            return
+        from ..parallel.symm import SymmetricWorkspace
+        m = self.model
+        ws = SymmetricWorkspace(group)
+        gsym = ws.alloc(m.num_params, torch.float32)
+        gsym.local.zero_()
+        m.rebind_buffers(grads=gsym.local)
+        self._ddp = {"ws": ws, "grads": gsym, "stream": torch.cuda.Stream(device=self.dev),
+                     "bucket_layers": max(1, int(getattr(options, "bucket_layers", 4) or 4)), "pending": None,
+                     "done": torch.cuda.Event(), "buckets": 0}
+        m.set_backward_hook(self._ddp_hook)
+        torch.cuda.synchronize()
+        group.barrier()
+
+    def _ddp_ranges(self, stage: int):
+        """Gradient ranges (offset, count) that are complete once ``stage`` has been enqueued and belong to its bucket."""
+        m, d = self.model, self._ddp
+        bl = d["bucket_layers"]
+        if stage == m.STAGE_HEAD:
+            lo = m.offsets["lnf_w"]
+            return [(lo, m.num_params - lo)]                       # lnf_w, lnf_b (and the padding after them)
+        if stage == m.STAGE_EMBEDDING:
+            return [(m.offsets["wte"], m.offsets["qkv_w"] - m.offsets["wte"])]   # wte, wpe
+        if stage % bl == 0:                                         # layers [stage, min(stage + bl, L)) are complete
+            return m.layer_grad_ranges(stage, min(stage + bl, m.L))
+        return []
+
+    def _ddp_hook(self, stage: int) -> None:
+        d = self._ddp
+        if not d.get("armed", False):
+            return
+        ranges = self._ddp_ranges(stage)
+        if not ranges:
+            return
+        from ..parallel.symm import _table
+        import ctypes as C
+        ws, g = d["ws"], d["grads"]
+        n, r = ws.n, ws.rank
+        ev = torch.cuda.Event()
+        ev.record()                                   # the stage's gradient kernels are in the compute stream
+        with torch.cuda.stream(d["stream"]):
+            d["stream"].wait_event(ev)
+            ws.barrier()                              # every rank has produced this bucket
+            for off, cnt in ranges:
+                cnt8 = cnt // 8 * 8
+                per = (-(-cnt8 // n) + 7) // 8 * 8
+                lo = min(cnt8, r * per)
+                mine = max(0, min(per, cnt8 - lo))
+                if mine > 0:
+                    K._check(K.lib().nx_comm_allreduce_shard(C.byref(g.table), C.c_int(K._DT[torch.float32]), C.c_int(n),
+                                                             C.byref(g.table), C.c_int(K._DT[torch.float32]), C.c_int(n),
+                                                             C.c_int64(off + lo), C.c_int64(mine), C.c_float(1.0),
+                                                             K._stream()), "nx_comm_allreduce_shard")
+            ws.barrier()                              # the sums are in every rank's buffer
+            d["done"].record()
+        d["buckets"] += 1
 
     def broadcast_parameters(self) -> None:
         if self._pg is not None:

@@ -120,6 +120,23 @@ def main():
     check(f"graph-captured sharded step == eager sharded step (max loss diff {dl:.2e}, master rel diff {dm:.2e})",
           dl < 5e-3 and dm < 1e-3)
 
+    # ---- data parallel: buckets reduced by the peer-memory kernel during the backward pass == one NCCL all-reduce
+    import types
+    finals = {}
+    for bucketed in (False, True):
+        b = GptLmBackend(cfg, 2, 128, device=dev, seed=11)
+        b.attach_process_group(pg, types.SimpleNamespace(bucketed=bucketed, bucket_layers=1))
+        for step in range(3):
+            b.device_step(tokens[rank], lr=1e-3)
+        torch.cuda.synchronize(); K.check_status()
+        finals[bucketed] = (b.model.params.clone(), b.model.read_opt_state().grad_norm,
+                            0 if b._ddp is None else b._ddp["buckets"])
+    upd = (finals[False][0] - init).norm().item()
+    dd = (finals[True][0] - finals[False][0]).norm().item() / upd
+    check(f"bucketed overlapped DDP == flat all-reduce (rel diff of the update {dd:.2e}, grad norm "
+          f"{finals[True][1]:.5f} vs {finals[False][1]:.5f}, {finals[True][2]} buckets)",
+          dd < 5e-2 and abs(finals[True][1] - finals[False][1]) < 1e-3 * finals[False][1] and finals[True][2] == 3 * 4)
+
     # ---- all-reduce with the cast fused in (BF16 in -> FP32 out), two-shot and one-shot
     for count, one_shot in ((1 << 20, False), (4096, True), (1000 * 8, False)):
         src = ws.alloc(count, torch.bfloat16)
