@@ -5,7 +5,11 @@ buffer larger than the L2 cache is rewritten so that every launch starts cold.  
 algorithmic FLOPs (or bytes) of the case divided by the median time, and is reported as a fraction of
 the measured cuBLAS BF16 / device-copy peaks when a peaks file is given.
 
-    python -m nexus_b200.bench.kernels [--only REGEX] [--small] [--iters N] [--peaks FILE] [--json OUT]
+    python -m nexus_b200.bench.kernels [--only REGEX] [--small] [--iters N] [--peaks FILE] [--json OUT] [--library]
+
+``--library`` adds, after each GEMM case, the same shape and operand layouts through ``torch.matmul`` /
+``torch.addmm`` (cuBLASLt; BF16 output, bias in the library epilogue, no activation), so the distance
+between this package's tcgen05 kernel and the vendor library is read off per shape.
 
 ``--small`` shrinks every case to a few hundred MB (still larger than L2) with one warm-up launch: the
 form to run under a profiler.
@@ -38,7 +42,7 @@ def _time(fn: Callable[[], None], iters: int, warmup: int, flush: torch.Tensor) 
     return statistics.median(times), min(times)
 
 
-def build_cases(small: bool) -> Dict[str, Tuple[Callable[[], None], float, float]]:
+def build_cases(small: bool, library: bool = False) -> Dict[str, Tuple[Callable[[], None], float, float]]:
     """name -> (launch, flops, bytes); exactly one of flops / bytes drives the roofline."""
     from ..ops import _cuda as K
     from ..ops import _infer as I
@@ -66,6 +70,19 @@ def build_cases(small: bool) -> Dict[str, Tuple[Callable[[], None], float, float
         if kw.get("acc"):
             extra.update(accumulate=True, split_k=kw.get("split_k", 1))
         cases[name] = (lambda: K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, **extra), 2.0 * m * n * k, 0.0)
+        if library and not kw.get("acc"):
+            # the same contraction through torch (cuBLASLt), bias in its epilogue, activation left out
+            at, bt = (a.t() if a_mn else a), (b if b_mn else b.t())
+            lib_out = torch.empty((m, n), dtype=bf, device=dev)
+            bias = extra.get("bias")
+            if bias is not None:
+                cases[name + "@cublaslt"] = (lambda: torch.addmm(bias, at, bt, out=lib_out), 2.0 * m * n * k, 0.0)
+            else:
+                cases[name + "@cublaslt"] = (lambda: torch.matmul(at, bt, out=lib_out), 2.0 * m * n * k, 0.0)
+        elif library:
+            at, bt = (a.t() if a_mn else a), (b if b_mn else b.t())
+            lib_acc = torch.zeros((m, n), dtype=bf, device=dev)
+            cases[name + "@cublaslt"] = (lambda: torch.addmm(lib_acc, at, bt, out=lib_acc), 2.0 * m * n * k, 0.0)
 
     add_gemm("gemm_qkv_fwd", M, 3 * C, C, bias=True)
     add_gemm("gemm_fc_fwd_gelu", M, F, C, bias=True, act="gelu")
@@ -104,6 +121,16 @@ def build_cases(small: bool) -> Dict[str, Tuple[Callable[[], None], float, float
     fl = 4.0 * B * H * T * T * D / 2
     cases["attention_fwd_causal"] = (lambda: K.attention_fwd(q, k, v, causal=True, out=o), fl, 0.0)
     cases["attention_bwd_causal"] = (lambda: K.attention_bwd(q, k, v, o, lse, do, causal=True), 2.5 * fl, 0.0)
+
+    # Llama-7B attention shape: head_dim 128, 4096 tokens
+    B2, H2, T2, D2 = (1 if small else 2), 32, 4096, 128
+    qkv2 = rn(B2, T2, 3, H2, D2)
+    q2, k2, v2 = qkv2[:, :, 0], qkv2[:, :, 1], qkv2[:, :, 2]
+    o2, lse2 = K.attention_fwd(q2, k2, v2, causal=True)
+    do2 = rn(B2, T2, H2, D2)
+    fl2 = 4.0 * B2 * H2 * T2 * T2 * D2 / 2
+    cases["attention_fwd_causal_d128_t4096"] = (lambda: K.attention_fwd(q2, k2, v2, causal=True, out=o2), fl2, 0.0)
+    cases["attention_bwd_causal_d128_t4096"] = (lambda: K.attention_bwd(q2, k2, v2, o2, lse2, do2, causal=True), 2.5 * fl2, 0.0)
 
     N = M
     x = rn(N, C, dtype=torch.float32)
@@ -164,6 +191,8 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--peaks", default="MEASURED_PEAKS.json")
     ap.add_argument("--json", default="")
+    ap.add_argument("--library", action="store_true",
+                    help="also time every GEMM shape through torch.matmul / addmm (cuBLASLt) as '<case>@cublaslt'")
     args = ap.parse_args(argv)
     peak_tf, peak_gb = None, None
     try:
@@ -175,7 +204,7 @@ def main(argv=None) -> int:
     pat = re.compile(args.only)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     rows: List[dict] = []
-    for name, (fn, flops, nbytes) in build_cases(args.small).items():
+    for name, (fn, flops, nbytes) in build_cases(args.small, args.library).items():
         if not pat.search(name):
             continue
         med, best = _time(fn, 1 if args.small else args.iters, 1 if args.small else args.warmup, flush)

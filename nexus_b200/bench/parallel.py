@@ -88,7 +88,8 @@ def main(argv=None) -> int:
                     help="fused: models.llama_tp.LlamaTpModel (all-gather -> GEMM / GEMM -> reduce-scatter inside the "
                          "tcgen05 kernels over peer memory, hand-scheduled backward); nccl: parallel.ParallelLm "
                          "(autograd, NCCL all-reduces at the region boundaries) - the same-box baseline")
-    ap.add_argument("--copiers", type=int, default=8, help="copier CTAs of the fused GEMM kernels")
+    ap.add_argument("--copiers", type=int, default=0,
+                    help="copier CTAs of the fused GEMM kernels (0: 8 up to two ranks, 16 beyond, where the link binds)")
     ap.add_argument("--graph", type=int, default=0, help="fused: replay the whole step as one CUDA graph")
     args = ap.parse_args(argv)
     if args.comm == "fused" and args.precision == "bf16" and not args.check:
@@ -192,6 +193,7 @@ def run_fused(args) -> int:
         cfg.n_layer = args.layers
     cfg.max_position = max(cfg.max_position, args.seq_len)
     model = LlamaTpModel(cfg, pg, device=dev, copier_ctas=args.copiers)
+    args.copiers = model.copier_ctas
     model.set_optimizer(AdamWConfig(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, grad_clip=1.0))
     n_micro = max(1, args.global_batch // args.micro_batch)
     gen = torch.Generator(device=dev).manual_seed(1234)

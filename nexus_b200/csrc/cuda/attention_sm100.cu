@@ -19,6 +19,7 @@
 #include "sm100_ptx.cuh"
 #include "tensor_map.h"
 #include <algorithm>
+#include <cstdlib>
 #include <type_traits>
 
 namespace {
@@ -154,6 +155,12 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t tile_addr, int k_rows,
   const uint32_t a = tile_addr + static_cast<uint32_t>(ks * 2048);
   return make_smem_desc_sw128(a, static_cast<uint32_t>(k_rows * 128), 1024);
 }
+
+// what k-step `ks` adds to the address field (bytes >> 4) of a K-major / MN-major descriptor built for k-step 0
+__device__ __forceinline__ uint64_t kstep_kmajor(int rows, int ks) {
+  return static_cast<uint64_t>((ks >> 2) * rows * 8 + (ks & 3) * 2);
+}
+__device__ __forceinline__ uint64_t kstep_mnmajor(int ks) { return static_cast<uint64_t>(ks * 128); }
 
 __device__ __forceinline__ float ex2f(float x) {
   float y;
@@ -385,9 +392,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
   } else if (warp == 9) {
-    if (lane == 0) {
+    // the whole warp walks the loop (descriptors stay in uniform registers); one elected lane issues
+    {
+      const bool leader = elect_one();
       const uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, false, false, 128, 128);
       const uint32_t idesc_o = make_idesc(kFmtBF16, kFmtBF16, false, true, 128, HD);
+      const uint64_t dQ = desc_kmajor(smem_u32(sQ), 128, 0), dP = desc_kmajor(smem_u32(sP), 128, 0);
       int n_item = 0, n_kv = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < p.items && ok; item += gridDim.x, ++n_item) {
@@ -397,38 +407,45 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         int kv_lo, kv_hi;
         kv_range(p, q0, min(128, p.Tq - q0), kv_lo, kv_hi);
         const int jb = kv_lo / 128, je = (kv_hi + 127) / 128;
-        if (!mbar_wait_bounded(q_full, n_item & 1, abort_flag)) {
-          atomicCAS(p.status, 0, kStatusTimeoutMma);
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(q_full, n_item & 1, abort_flag))) {
+          if (leader) atomicCAS(p.status, 0, kStatusTimeoutMma);
           break;
         }
         for (int j = jb; j < je; ++j, ++n_kv) {
           const int s = n_kv & 1;
-          if (!mbar_wait_bounded(&kv_full[s], (n_kv >> 1) & 1, abort_flag)) {
-            atomicCAS(p.status, 0, kStatusTimeoutMma);
+          if (!__all_sync(0xffffffffu, mbar_wait_bounded(&kv_full[s], (n_kv >> 1) & 1, abort_flag))) {
+            if (leader) atomicCAS(p.status, 0, kStatusTimeoutMma);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK + s * C::kKVBytes), aV = smem_u32(sV + s * C::kKVBytes);
+          const uint64_t dK = desc_kmajor(smem_u32(sK + s * C::kKVBytes), 128, 0);
+          const uint64_t dV = desc_mnmajor(smem_u32(sV + s * C::kKVBytes), 128, 0);
+          if (leader) {
 #pragma unroll
-          for (int ks = 0; ks < HD / 16; ++ks)
-            umma_f16_ss(tmem_s, desc_kmajor(aQ, 128, ks), desc_kmajor(aK, 128, ks), idesc_s, ks > 0 ? 1u : 0u);
-          umma_commit(s_full);
-          if (j + 1 == je) umma_commit(q_empty);  // the Q tile may be replaced once these MMAs have read it
-          if (!mbar_wait_bounded(p_full, n_kv & 1, abort_flag)) {
-            atomicCAS(p.status, 0, kStatusTimeoutMma);
+            for (int ks = 0; ks < HD / 16; ++ks)
+              umma_f16_ss(tmem_s, dQ + kstep_kmajor(128, ks), dK + kstep_kmajor(128, ks), idesc_s, ks > 0 ? 1u : 0u);
+            umma_commit(s_full);
+            if (j + 1 == je) umma_commit(q_empty);  // the Q tile may be replaced once these MMAs have read it
+          }
+          __syncwarp();
+          if (!__all_sync(0xffffffffu, mbar_wait_bounded(p_full, n_kv & 1, abort_flag))) {
+            if (leader) atomicCAS(p.status, 0, kStatusTimeoutMma);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t aP = smem_u32(sP);
+          if (leader) {
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks)
-            umma_f16_ss(tmem_o, desc_kmajor(aP, 128, ks), desc_mnmajor(aV, 128, ks), idesc_o, ks > 0 ? 1u : 0u);
-          umma_commit(o_full);
-          umma_commit(&kv_empty[s]);
+            for (int ks = 0; ks < 8; ++ks)
+              umma_f16_ss(tmem_o, dP + kstep_kmajor(128, ks), dV + kstep_mnmajor(ks), idesc_o, ks > 0 ? 1u : 0u);
+            umma_commit(o_full);
+            umma_commit(&kv_empty[s]);
+          }
+          __syncwarp();
         }
-        if (jb >= je) umma_commit(q_empty);  // nothing visible: release Q at once
+        if (jb >= je && leader) umma_commit(q_empty);  // nothing visible: release Q at once
+        __syncwarp();
       }
     }
   } else {
@@ -597,6 +614,462 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }
 
 // ================================================================================================
+// forward with two q tiles in flight.  One persistent CTA per SM works on 256 query rows of one
+// (head, batch) at a time: softmax group A (warps 0-3) owns rows 0-127, group B (warps 4-7) rows
+// 128-255, and both walk the same key/value tiles, which are loaded once.  The MMA warp interleaves
+//   PV_A(j-1), QK_A(j), PV_B(j-1), QK_B(j)
+// so the tensor core works on one tile while the other tile's exponentials run.  Each softmax thread
+// owns a whole score row (its TMEM lane), so no row statistic crosses threads.  The output tile
+// accumulates in TMEM across key tiles; it is rescaled (by the row's own thread) only when the running
+// maximum has grown by more than 2^8, otherwise the stale maximum stays the reference of the
+// exponentials, and the last step divides by the matching row sum.
+// TMEM (512 columns): S_A 0-127, S_B 128-255, O_A 256.., O_B 384..
+// Probabilities go back as BF16 into the first 64 columns of the score tile itself, two per column, and the
+// P V MMA reads them from TMEM as its A operand, so they never touch shared memory.  (A variant that wrote P
+// to swizzled shared memory and issued the next Q K^T as soon as the scores were in registers measured slower,
+// 105 us against 93 us on 16 x 12 x 1024 x 64, as did four softmax warps more per tile, 118 us.)
+// ================================================================================================
+template <int HD>
+struct Fwd2Cfg {
+  static constexpr int kStages = (HD == 64) ? 3 : 2;
+  static constexpr int kQBytes = 128 * HD * 2;
+  static constexpr int kKVBytes = 128 * HD * 2;
+  static constexpr int kSmem = 2 * kQBytes + kStages * 2 * kKVBytes + 256;
+  static constexpr int kTmemCols = 512;
+};
+constexpr int kFwd2Threads = 320;  // warps 0-3: softmax A, 4-7: softmax B, 8: TMA, 9: MMA
+constexpr float kRescaleStep = 8.0f;  // log2 of the growth of the row maximum that forces a rescale
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows on the lanes, two BF16 per column along K) is read from TMEM
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Work of one round of the persistent loop: CTA c takes item round * grid + c in even rounds and
+// round * grid + (grid - 1 - c) in odd ones, and the items are sorted by cost (late q blocks first under a causal
+// mask), so that the CTAs' totals stay close.  Key tile ranges [jb, je) are per q tile; an absent tile has jb == je.
+struct PairWork {
+  int q0, h, b;
+  int jbA, jeA, jbB, jeB, jb, je;
+};
+__device__ __forceinline__ bool pair_work(const AttnDev& p, int round, PairWork& w) {
+  const int G = static_cast<int>(gridDim.x), c = static_cast<int>(blockIdx.x);
+  const int item = round * G + ((round & 1) ? (G - 1 - c) : c);
+  if (item >= p.items) return false;
+  const int per = p.H * p.B;
+  const int qb = p.nqb - 1 - item / per;
+  const int rem = item % per;
+  w.h = rem % p.H;
+  w.b = rem / p.H;
+  w.q0 = qb * 256;
+  int lo, hi;
+  kv_range(p, w.q0, min(128, p.Tq - w.q0), lo, hi);
+  w.jbA = lo / 128;
+  w.jeA = (hi + 127) / 128;
+  if (w.jeA <= w.jbA) w.jbA = w.jeA = 0;
+  w.jbB = w.jeB = 0;
+  if (w.q0 + 128 < p.Tq) {
+    kv_range(p, w.q0 + 128, min(128, p.Tq - w.q0 - 128), lo, hi);
+    w.jbB = lo / 128;
+    w.jeB = (hi + 127) / 128;
+    if (w.jeB <= w.jbB) w.jbB = w.jeB = 0;
+  }
+  const bool a = w.jeA > w.jbA, bb = w.jeB > w.jbB;
+  w.jb = a ? (bb ? min(w.jbA, w.jbB) : w.jbA) : w.jbB;
+  w.je = a ? (bb ? max(w.jeA, w.jeB) : w.jeA) : w.jeB;
+  if (!a && !bb) w.jb = w.je = 0;
+  return true;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kFwd2Threads, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const AttnDev p) {
+  pdl_launch_dependents();
+  using C = Fwd2Cfg<HD>;
+  constexpr int S = C::kStages;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {  // the swizzled tiles need a 1 KiB aligned base; uniform early exit
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, kStatusBadArgument);
+    return;
+  }
+  uint8_t* sQ = smem;                             // [2] q tiles
+  uint8_t* sK = sQ + 2 * C::kQBytes;              // [S]
+  uint8_t* sV = sK + S * C::kKVBytes;             // [S]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + S * C::kKVBytes);
+  uint64_t* q_full = bars;         // [2]
+  uint64_t* q_empty = bars + 2;    // [2]
+  uint64_t* kv_full = bars + 4;    // [S]
+  uint64_t* kv_empty = bars + 7;   // [S]
+  uint64_t* s_full = bars + 10;    // [2]
+  uint64_t* p_full = bars + 12;    // [2]
+  uint64_t* o_done = bars + 14;    // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(&q_full[x], 1);
+      mbar_init(&q_empty[x], 1);
+      mbar_init(&s_full[x], 1);
+      mbar_init(&p_full[x], 4);  // one arrival per softmax warp of the group
+      mbar_init(&o_done[x], 1);
+    }
+    for (int s = 0; s < S; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      int nq[2] = {0, 0}, n_kv = 0;
+      bool ok = true;
+      PairWork w;
+      for (int round = 0; ok && pair_work(p, round, w); ++round) {
+        const int hk = w.h / (p.H / p.Hkv);
+        if (!NX_INDEX_OK(w.q0 >= 0 && w.q0 < p.Tq && w.h < p.H && hk < p.Hkv && w.b < p.B && w.jb >= 0 &&
+                         (w.je == w.jb || (w.je - 1) * 128 < p.Tk), p.status)) {
+          *abort_flag = 1;
+          break;
+        }
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const bool active = x == 0 ? (w.jeA > w.jbA) : (w.jeB > w.jbB);
+          if (!active) continue;
+          if (!mbar_wait_bounded(&q_empty[x], (nq[x] & 1) ^ 1u, abort_flag)) {  // the previous item's QK^T are done
+            atomicCAS(p.status, 0, kStatusTimeoutProducer);
+            ok = false;
+            break;
+          }
+          ++nq[x];
+          mbar_arrive_expect_tx(&q_full[x], C::kQBytes);
+          load_tile<HD>(sQ + x * C::kQBytes, &tm_q, &q_full[x], 128, w.q0 + x * 128, w.h, w.b, p.hfirst);
+        }
+        for (int j = w.jb; ok && j < w.je; ++j, ++n_kv) {
+          const int s = n_kv % S;
+          if (!mbar_wait_bounded(&kv_empty[s], ((n_kv / S) & 1) ^ 1u, abort_flag)) {
+            atomicCAS(p.status, 0, kStatusTimeoutProducer);
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&kv_full[s], 2 * C::kKVBytes);
+          load_tile<HD>(sK + s * C::kKVBytes, &tm_k, &kv_full[s], 128, j * 128, hk, w.b, p.hfirst);
+          load_tile<HD>(sV + s * C::kKVBytes, &tm_v, &kv_full[s], 128, j * 128, hk, w.b, p.hfirst);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // Every lane walks the loop (uniform control flow keeps the descriptors in uniform registers); one elected lane
+    // issues the MMAs and commits.
+    const bool leader = elect_one();
+    const uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, false, false, 128, 128);
+    const uint32_t idesc_o = make_idesc(kFmtBF16, kFmtBF16, false, true, 128, HD);
+    int nqA = 0, nqB = 0, npA = 0, npB = 0, n_kv = 0;
+    bool ok = true;
+    PairWork w;
+    for (int round = 0; ok && pair_work(p, round, w); ++round) {
+      if (w.jeA > w.jbA) {
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&q_full[0], nqA & 1, abort_flag));
+        ++nqA;
+      }
+      if (ok && w.jeB > w.jbB) {
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&q_full[1], nqB & 1, abort_flag));
+        ++nqB;
+      }
+      if (!ok) {
+        if (leader) atomicCAS(p.status, 0, kStatusTimeoutMma);
+        break;
+      }
+      const int kv0 = n_kv;  // key tile j of this item sits in stage (kv0 + j - jb) % S
+      for (int j = w.jb; ok && j <= w.je; ++j) {
+        if (j < w.je) {
+          const int n = kv0 + (j - w.jb);
+          ok = __all_sync(0xffffffffu, mbar_wait_bounded(&kv_full[n % S], (n / S) & 1, abort_flag));
+          if (!ok) {
+            if (leader) atomicCAS(p.status, 0, kStatusTimeoutMma);
+            break;
+          }
+        }
+        const int sj = (kv0 + (j - w.jb)) % S, sjm = (kv0 + (j - w.jb) + S - 1) % S;
+        const uint64_t dK = desc_kmajor(smem_u32(sK + sj * C::kKVBytes), 128, 0);
+        const uint64_t dV = desc_mnmajor(smem_u32(sV + sjm * C::kKVBytes), 128, 0);
+        // P aliases S, so per tile the order is P V (j-1), then Q K^T (j); the two tiles alternate
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const int jbx = x == 0 ? w.jbA : w.jbB, jex = x == 0 ? w.jeA : w.jeB;
+          const uint32_t tmem_s = tmem_base + x * 128, tmem_o = tmem_base + 256 + x * 128;
+          if (ok && j - 1 >= jbx && j - 1 < jex) {  // P_x(j-1) @ V(j-1)
+            const int np = x == 0 ? npA : npB;
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&p_full[x], np & 1, abort_flag));
+            if (!ok) {
+              if (leader) atomicCAS(p.status, 0, kStatusTimeoutMma);
+            } else {
+              if (x == 0) ++npA;
+              else ++npB;
+              tc_fence_after_sync();
+              const uint32_t acc0 = (j - 1 > jbx) ? 1u : 0u;
+              if (leader) {
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks)  // one k-step = 16 keys = 8 TMEM columns of packed P, 2 KiB of the V tile
+                  umma_f16_ts(tmem_o, tmem_s + ks * 8, dV + kstep_mnmajor(ks), idesc_o, (ks > 0) ? 1u : acc0);
+                umma_commit(&o_done[x]);
+              }
+            }
+          }
+          if (ok && j >= jbx && j < jex) {  // S_x(j) = Q_x K(j)^T
+            tc_fence_after_sync();
+            const uint64_t dQ = desc_kmajor(smem_u32(sQ + x * C::kQBytes), 128, 0);
+            if (leader) {
+#pragma unroll
+              for (int ks = 0; ks < HD / 16; ++ks)
+                umma_f16_ss(tmem_s, dQ + kstep_kmajor(128, ks), dK + kstep_kmajor(128, ks), idesc_s, ks > 0 ? 1u : 0u);
+              umma_commit(&s_full[x]);
+              if (j + 1 == jex) umma_commit(&q_empty[x]);  // the Q tile may be replaced once these MMAs have read it
+            }
+          }
+        }
+        if (ok && j > w.jb && leader) umma_commit(&kv_empty[sjm]);  // both tiles are done with key tile j - 1
+        __syncwarp();
+      }
+      n_kv = kv0 + (w.je - w.jb);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + output rows
+    const int x = warp >> 2;                      // q tile of this group
+    const int r = (warp & 3) * 32 + lane;         // row inside the q tile == TMEM lane
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tmem_s = tmem_base + x * 128 + lane_addr, tmem_o = tmem_base + 256 + x * 128 + lane_addr;
+    const float sc = p.scale * kLog2e;
+    const int off = p.Tk - p.Tq;
+    int cnt = 0;  // key tiles this group has processed: phase counter of s_full / o_done
+    bool ok = true;
+    PairWork w;
+    for (int round = 0; ok && pair_work(p, round, w); ++round) {
+      const int jbx = x == 0 ? w.jbA : w.jbB, jex = x == 0 ? w.jeA : w.jeB;
+      if (jex <= jbx) {
+        // no visible key for any row of this tile: rows that exist get zeros and -inf (nothing to merge either)
+        const int q0x = w.q0 + x * 128, q = q0x + r;
+        if (q < p.Tq && q0x < p.Tq) {
+          __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(w.b) * p.o_batch +
+                                static_cast<int64_t>(q) * p.o_row + static_cast<int64_t>(w.h) * p.o_head;
+          const int64_t li = (static_cast<int64_t>(w.b) * p.H + w.h) * p.Tq + q;
+          if (p.merge_o == nullptr) {
+#pragma unroll
+            for (int g = 0; g < HD / 8; ++g) reinterpret_cast<uint4*>(orow)[g] = make_uint4(0u, 0u, 0u, 0u);
+            if (p.lse) p.lse[li] = -INFINITY;
+          } else {
+            const float* mo = p.merge_o + ((static_cast<int64_t>(w.b) * p.Tq + q) * p.H + w.h) * HD;
+#pragma unroll
+            for (int g = 0; g < HD / 8; ++g) {
+              const float4 u0 = reinterpret_cast<const float4*>(mo)[2 * g], u1 = reinterpret_cast<const float4*>(mo)[2 * g + 1];
+              uint4 wv;
+              wv.x = pack_bf16x2(u0.x, u0.y);
+              wv.y = pack_bf16x2(u0.z, u0.w);
+              wv.z = pack_bf16x2(u1.x, u1.y);
+              wv.w = pack_bf16x2(u1.z, u1.w);
+              reinterpret_cast<uint4*>(orow)[g] = wv;
+            }
+            if (p.lse) p.lse[li] = p.merge_lse[li];
+          }
+        }
+        continue;
+      }
+      const int q0 = w.q0 + x * 128;
+      const int q = q0 + r;
+      int row_lo, row_hi;
+      row_limits(p, q, row_lo, row_hi);
+      float m_ref = -INFINITY, l_run = 0.0f;
+      for (int j = jbx; j < jex; ++j, ++cnt) {
+        const int k0 = j * 128;
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&s_full[x], cnt & 1, abort_flag));
+        if (!ok) {
+          if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+          break;
+        }
+        tc_fence_after_sync();
+        // the whole row in registers with one wait: a TMEM load takes several hundred cycles to come back, so the
+        // row is read once
+        uint32_t sv[4][32];
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) tmem_ld_32x32b_x32(tmem_s + cc * 32, sv[cc]);
+        tmem_ld_wait();
+        const bool need_mask = (k0 + 128 > p.Tk) || (p.causal && (k0 + 127 > q0 + off)) ||
+                               (p.window > 0 && (k0 < q0 + 127 + off - p.window + 1));
+        const int clo = row_lo - k0, chi = row_hi - k0;  // column c is visible iff clo <= c <= chi
+        if (need_mask) {
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+              if (cc * 32 + c < clo || cc * 32 + c > chi) sv[cc][c] = 0xff800000u;  // -inf
+        }
+        float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+          for (int c = 0; c < 32; c += 4) {
+            m0 = fmaxf(m0, __uint_as_float(sv[cc][c]));
+            m1 = fmaxf(m1, __uint_as_float(sv[cc][c + 1]));
+            m2 = fmaxf(m2, __uint_as_float(sv[cc][c + 2]));
+            m3 = fmaxf(m3, __uint_as_float(sv[cc][c + 3]));
+          }
+        const float m_new = fmaxf(m_ref, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * sc);
+        // rescale only when the maximum has moved far: a warp-uniform decision, every lane uses its own factor
+        const bool grow = m_new - kRescaleStep > m_ref;
+        if (__any_sync(0xffffffffu, grow)) {
+          const float alpha = grow ? ex2f(m_ref - m_new) : 1.0f;  // m_ref == -inf -> 0
+          if (grow) {
+            l_run *= alpha;
+            m_ref = m_new;
+          }
+          if (j > jbx) {  // the output tile holds the sums of the earlier key tiles
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&o_done[x], (cnt - 1) & 1, abort_flag));
+            if (!ok) {
+              if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+              break;
+            }
+            tc_fence_after_sync();
+#pragma unroll
+            for (int cc = 0; cc < HD / 32; ++cc) {
+              uint32_t ov[32];
+              tmem_ld_32x32b_x32(tmem_o + cc * 32, ov);
+              tmem_ld_wait();
+#pragma unroll
+              for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * alpha);
+              tmem_st_32x32b_x32(tmem_o + cc * 32, ov);
+            }
+            tmem_st_wait();
+          }
+        }
+        const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
+        float r0 = 0.0f, r1 = 0.0f, r2 = 0.0f, r3 = 0.0f;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float e[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) e[i] = ex2f(fmaf(__uint_as_float(sv[cc][8 * g + i]), sc, -m_use));  // -inf -> 0
+            r0 += e[0] + e[4];
+            r1 += e[1] + e[5];
+            r2 += e[2] + e[6];
+            r3 += e[3] + e[7];
+            pk[4 * g + 0] = pack_bf16x2(e[0], e[1]);
+            pk[4 * g + 1] = pack_bf16x2(e[2], e[3]);
+            pk[4 * g + 2] = pack_bf16x2(e[4], e[5]);
+            pk[4 * g + 3] = pack_bf16x2(e[6], e[7]);
+          }
+          tmem_st_32x32b_x16(tmem_s + cc * 16, pk);  // two probabilities per column
+        }
+        l_run += (r0 + r1) + (r2 + r3);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[x]);
+      }
+      if (!ok) break;
+      // ---- the last P V has retired: normalise (and merge) the output rows
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(&o_done[x], (cnt - 1) & 1, abort_flag));
+      if (!ok) {
+        if (lane == 0) atomicCAS(p.status, 0, kStatusTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after_sync();
+      float o_acc[HD];
+#pragma unroll
+      for (int cc = 0; cc < HD / 32; ++cc) {
+        uint32_t ov[32];
+        tmem_ld_32x32b_x32(tmem_o + cc * 32, ov);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) o_acc[cc * 32 + c] = __uint_as_float(ov[c]);
+      }
+      tc_fence_before_sync();
+      if (q < p.Tq) {
+        const int64_t li = (static_cast<int64_t>(w.b) * p.H + w.h) * p.Tq + q;
+        float m_fin = m_ref;
+        if (p.merge_o != nullptr) {
+          // merge with the result of earlier key/value chunks: softmax over the union of the key sets
+          float* mo = p.merge_o + ((static_cast<int64_t>(w.b) * p.Tq + q) * p.H + w.h) * HD;
+          const float lse_new = l_run > 0.0f ? (m_ref / kLog2e + logf(l_run)) : -INFINITY;
+          const float lse_old = p.merge_lse[li];
+          const float mm = fmaxf(lse_new, lse_old);
+          const float w_new = (lse_new == -INFINITY) ? 0.0f : __expf(lse_new - mm);
+          const float w_old = (lse_old == -INFINITY) ? 0.0f : __expf(lse_old - mm);
+          const float den = w_new + w_old;
+          const float c_new = den > 0.0f ? w_new / den / (l_run > 0.0f ? l_run : 1.0f) : 0.0f;
+          const float c_old = den > 0.0f ? w_old / den : 0.0f;
+#pragma unroll
+          for (int g = 0; g < HD / 4; ++g) {
+            float4 prev = reinterpret_cast<const float4*>(mo)[g];
+            prev.x = prev.x * c_old + o_acc[4 * g + 0] * c_new;
+            prev.y = prev.y * c_old + o_acc[4 * g + 1] * c_new;
+            prev.z = prev.z * c_old + o_acc[4 * g + 2] * c_new;
+            prev.w = prev.w * c_old + o_acc[4 * g + 3] * c_new;
+            reinterpret_cast<float4*>(mo)[g] = prev;
+            o_acc[4 * g + 0] = prev.x;
+            o_acc[4 * g + 1] = prev.y;
+            o_acc[4 * g + 2] = prev.z;
+            o_acc[4 * g + 3] = prev.w;
+          }
+          l_run = den > 0.0f ? 1.0f : 0.0f;  // o_acc now holds the normalised merged output
+          m_fin = (den > 0.0f ? mm + logf(den) : -INFINITY) * kLog2e;
+        }
+        const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<int64_t>(w.b) * p.o_batch +
+                              static_cast<int64_t>(q) * p.o_row + static_cast<int64_t>(w.h) * p.o_head;
+#pragma unroll
+        for (int g = 0; g < HD / 8; ++g) {
+          uint4 wv;
+          wv.x = pack_bf16x2(o_acc[8 * g + 0] * inv, o_acc[8 * g + 1] * inv);
+          wv.y = pack_bf16x2(o_acc[8 * g + 2] * inv, o_acc[8 * g + 3] * inv);
+          wv.z = pack_bf16x2(o_acc[8 * g + 4] * inv, o_acc[8 * g + 5] * inv);
+          wv.w = pack_bf16x2(o_acc[8 * g + 6] * inv, o_acc[8 * g + 7] * inv);
+          reinterpret_cast<uint4*>(orow)[g] = wv;
+        }
+        const float lse = l_run > 0.0f ? (m_fin / kLog2e + logf(l_run)) : -INFINITY;
+        if (p.lse) p.lse[li] = lse;
+        if (p.merge_lse) p.merge_lse[li] = lse;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(2000);
+    __syncthreads();
+  }
+  if (warp == 9) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// ================================================================================================
 // backward, part 1: dK / dV.  One CTA per (kv block of 128, kv head, batch); loops over the q heads
 // of the group and over q chunks of 64 rows.  TMEM: S^T [128 kv][64 q], dP^T [128][64], dV [128][HD],
 // dK [128][HD].  Thread r owns kv row r.
@@ -705,43 +1178,54 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       }
     }
   } else if (warp == 5) {
-    if (lane == 0) {
+    // the whole warp walks the loop (descriptors stay in uniform registers); one elected lane issues
+    {
+      const bool leader = elect_one();
       const uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, false, false, 128, 64);   // K Q^T, V dO^T
       const uint32_t idesc_g = make_idesc(kFmtBF16, kFmtBF16, false, true, 128, HD);    // P^T dO, dS^T Q
-      bool ok = mbar_wait_bounded(kv_full, 0, abort_flag);
-      if (!ok) atomicCAS(p.status, 0, kStatusTimeoutMma);
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aPT = smem_u32(sPT), aDST = smem_u32(sDST);
+      bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(kv_full, 0, abort_flag));
+      if (!ok && leader) atomicCAS(p.status, 0, kStatusTimeoutMma);
+      const uint64_t dK = desc_kmajor(smem_u32(sK), 128, 0), dV = desc_kmajor(smem_u32(sV), 128, 0);
+      const uint64_t dPT = desc_kmajor(smem_u32(sPT), 128, 0), dDST = desc_kmajor(smem_u32(sDST), 128, 0);
       for (int it = 0; it < iters && ok; ++it) {
         const int s = it & 1;
-        if (!mbar_wait_bounded(&q_full[s], (it >> 1) & 1, abort_flag)) {
-          atomicCAS(p.status, 0, kStatusTimeoutMma);
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&q_full[s], (it >> 1) & 1, abort_flag))) {
+          if (leader) atomicCAS(p.status, 0, kStatusTimeoutMma);
           break;
         }
         tc_fence_after_sync();
         const uint32_t aQ = smem_u32(sQ + s * C::kQBytes), aDO = smem_u32(sDO + s * C::kQBytes);
+        const uint64_t dQk = desc_kmajor(aQ, 64, 0), dDOk = desc_kmajor(aDO, 64, 0);
+        const uint64_t dQm = desc_mnmajor(aQ, 64, 0), dDOm = desc_mnmajor(aDO, 64, 0);
+        if (leader) {
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks)
-          umma_f16_ss(tmem_st, desc_kmajor(aK, 128, ks), desc_kmajor(aQ, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
+          for (int ks = 0; ks < HD / 16; ++ks)
+            umma_f16_ss(tmem_st, dK + kstep_kmajor(128, ks), dQk + kstep_kmajor(64, ks), idesc_s, ks > 0 ? 1u : 0u);
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks)
-          umma_f16_ss(tmem_dpt, desc_kmajor(aV, 128, ks), desc_kmajor(aDO, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
-        umma_commit(s_full);
-        if (!mbar_wait_bounded(p_full, it & 1, abort_flag)) {
-          atomicCAS(p.status, 0, kStatusTimeoutMma);
+          for (int ks = 0; ks < HD / 16; ++ks)
+            umma_f16_ss(tmem_dpt, dV + kstep_kmajor(128, ks), dDOk + kstep_kmajor(64, ks), idesc_s, ks > 0 ? 1u : 0u);
+          umma_commit(s_full);
+        }
+        __syncwarp();
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(p_full, it & 1, abort_flag))) {
+          if (leader) atomicCAS(p.status, 0, kStatusTimeoutMma);
           break;
         }
         tc_fence_after_sync();
         // dV += P^T dO ; dK += dS^T Q   (reduction over the 64 q rows of the chunk: 4 k-steps)
+        if (leader) {
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_f16_ss(tmem_dv, desc_kmajor(aPT, 128, ks), desc_mnmajor(aDO, 64, ks), idesc_g,
-                      (it > 0 || ks > 0) ? 1u : 0u);
+          for (int ks = 0; ks < 4; ++ks)
+            umma_f16_ss(tmem_dv, dPT + kstep_kmajor(128, ks), dDOm + kstep_mnmajor(ks), idesc_g,
+                        (it > 0 || ks > 0) ? 1u : 0u);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_f16_ss(tmem_dk, desc_kmajor(aDST, 128, ks), desc_mnmajor(aQ, 64, ks), idesc_g,
-                      (it > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(&q_empty[s]);
-        umma_commit(acc_done);
+          for (int ks = 0; ks < 4; ++ks)
+            umma_f16_ss(tmem_dk, dDST + kstep_kmajor(128, ks), dQm + kstep_mnmajor(ks), idesc_g,
+                        (it > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(&q_empty[s]);
+          umma_commit(acc_done);
+        }
+        __syncwarp();
       }
     }
   } else {
@@ -995,38 +1479,48 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
       }
     }
   } else if (warp == 5) {
-    if (lane == 0) {
+    // the whole warp walks the loop (descriptors stay in uniform registers); one elected lane issues
+    {
+      const bool leader = elect_one();
       const uint32_t idesc_s = make_idesc(kFmtBF16, kFmtBF16, false, false, 128, 64);  // Q K^T, dO V^T
       const uint32_t idesc_g = make_idesc(kFmtBF16, kFmtBF16, false, true, 128, HD);   // dS K
-      bool ok = mbar_wait_bounded(q_full, 0, abort_flag);
-      if (!ok) atomicCAS(p.status, 0, kStatusTimeoutMma);
-      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
+      bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(q_full, 0, abort_flag));
+      if (!ok && leader) atomicCAS(p.status, 0, kStatusTimeoutMma);
+      const uint64_t dQ = desc_kmajor(smem_u32(sQ), 128, 0), dDO = desc_kmajor(smem_u32(sDO), 128, 0);
+      const uint64_t dDS = desc_kmajor(smem_u32(sDS), 128, 0);
       for (int it = 0; it < iters && ok; ++it) {
         const int s = it % NS;
-        if (!mbar_wait_bounded(&kv_full[s], (it / NS) & 1, abort_flag)) {
-          atomicCAS(p.status, 0, kStatusTimeoutMma);
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&kv_full[s], (it / NS) & 1, abort_flag))) {
+          if (leader) atomicCAS(p.status, 0, kStatusTimeoutMma);
           break;
         }
         tc_fence_after_sync();
         const uint32_t aK = smem_u32(sK + s * C::kKVBytes), aV = smem_u32(sV + s * C::kKVBytes);
+        const uint64_t dKk = desc_kmajor(aK, 64, 0), dVk = desc_kmajor(aV, 64, 0), dKm = desc_mnmajor(aK, 64, 0);
+        if (leader) {
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks)
-          umma_f16_ss(tmem_s, desc_kmajor(aQ, 128, ks), desc_kmajor(aK, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
+          for (int ks = 0; ks < HD / 16; ++ks)
+            umma_f16_ss(tmem_s, dQ + kstep_kmajor(128, ks), dKk + kstep_kmajor(64, ks), idesc_s, ks > 0 ? 1u : 0u);
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks)
-          umma_f16_ss(tmem_dp, desc_kmajor(aDO, 128, ks), desc_kmajor(aV, 64, ks), idesc_s, ks > 0 ? 1u : 0u);
-        umma_commit(s_full);
-        if (!mbar_wait_bounded(p_full, it & 1, abort_flag)) {
-          atomicCAS(p.status, 0, kStatusTimeoutMma);
+          for (int ks = 0; ks < HD / 16; ++ks)
+            umma_f16_ss(tmem_dp, dDO + kstep_kmajor(128, ks), dVk + kstep_kmajor(64, ks), idesc_s, ks > 0 ? 1u : 0u);
+          umma_commit(s_full);
+        }
+        __syncwarp();
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(p_full, it & 1, abort_flag))) {
+          if (leader) atomicCAS(p.status, 0, kStatusTimeoutMma);
           break;
         }
         tc_fence_after_sync();
+        if (leader) {
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_f16_ss(tmem_dq, desc_kmajor(aDS, 128, ks), desc_mnmajor(aK, 64, ks), idesc_g,
-                      (it > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(&kv_empty[s]);
-        umma_commit(acc_done);
+          for (int ks = 0; ks < 4; ++ks)
+            umma_f16_ss(tmem_dq, dDS + kstep_kmajor(128, ks), dKm + kstep_mnmajor(ks), idesc_g,
+                        (it > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(&kv_empty[s]);
+          umma_commit(acc_done);
+        }
+        __syncwarp();
       }
     }
   } else {
@@ -1257,6 +1751,31 @@ extern "C" int nx_attention_fwd(const NxAttnArgs* a, nx_stream_t stream_) {
   // one persistent CTA per slot: two per SM for head_dim 64 (registers / shared memory allow it), one otherwise
   const int grid = std::min(p.items, sms * (HD == 64 ? 2 : 1));
   const bool ext = p.softcap > 0.0f || p.alibi != nullptr || p.dropout_p > 0.0f;
+  // The two-tile kernel serves the plain softmax (no soft-capping / ALiBi / dropout).  It is the default for
+  // head_dim 128 (369 us against 499 us on 2 x 32 x 4096 x 128, causal); at head_dim 64 the two forms time alike
+  // and the one-tile kernel below stays.  NEXUS_B200_ATTN_FWD=1 / =2 forces the one-tile / two-tile form.
+  static const int fwd_mode = [] {
+    const char* e = std::getenv("NEXUS_B200_ATTN_FWD");
+    return e != nullptr ? std::atoi(e) : 0;
+  }();
+  if (!ext && (fwd_mode == 2 || (fwd_mode == 0 && HD == 128))) {
+    p.nqb = (a->tq + 255) / 256;
+    p.items = p.nqb * a->heads * a->batch;
+    const int grid2 = std::min(p.items, sms);
+#define NX_FWD2(HD_)                                                                                \
+  do {                                                                                              \
+    static bool once = false;                                                                       \
+    if (!once) {                                                                                    \
+      if (set_smem(attn_fwd2_kernel<HD_>, Fwd2Cfg<HD_>::kSmem)) return -2;                          \
+      once = true;                                                                                  \
+    }                                                                                               \
+    attn_fwd2_kernel<HD_><<<grid2, kFwd2Threads, Fwd2Cfg<HD_>::kSmem, st>>>(tq, tk, tv, p);         \
+  } while (0)
+    if (HD == 64) NX_FWD2(64);
+    else NX_FWD2(128);
+#undef NX_FWD2
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
 #define NX_FWD(HD_, EXT_)                                                                           \
   do {                                                                                              \
     static bool once = false;                                                                       \

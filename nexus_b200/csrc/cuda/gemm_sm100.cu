@@ -612,7 +612,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer
-    if (lane == 0 && cta_rank == 0) {
+    // The whole warp walks the loop so that addresses and descriptors stay in uniform registers; one elected lane
+    // issues the MMAs and the commits (issuing from a lone lane of a diverged warp costs ~100 cycles per MMA in
+    // register-to-uniform moves).
+    if (cta_rank == 0) {
+      const bool leader = elect_one();
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -623,8 +627,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       for (int u = unit_first; u < p.num_units && ok; u += unit_step) {
         Unit w = decode_unit<kTileM>(p, u);
         NX_PROF(const long long c0 = clock64();)
-        if (!mbar_wait_bounded(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) {
-          atomicCAS(p.status, 0, kStatusTimeoutMma);
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&tempty_bar[acc], acc_phase ^ 1u, abort_flag))) {
+          if (leader) atomicCAS(p.status, 0, kStatusTimeoutMma);
           break;
         }
         NX_PROF(t_acc += clock64() - c0; ++n_tiles;)
@@ -632,32 +636,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = w.kb_begin; kb < w.kb_end; ++kb) {
           NX_PROF(const long long c1 = clock64();)
-          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+          if (!__all_sync(0xffffffffu, mbar_wait_bounded(&full_bar[stage], phase, abort_flag))) {
             ok = false;
-            atomicCAS(p.status, 0, kStatusTimeoutMma);
+            if (leader) atomicCAS(p.status, 0, kStatusTimeoutMma);
             break;
           }
           NX_PROF(const long long c2 = clock64(); t_tma += c2 - c1; ++n_kb;)
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(stage_base + stage * C::kStageBytes);
           const uint32_t sb = sa + C::kABytes;
+          const uint64_t da0 = make_smem_desc_sw128(sa, A_MN ? 64 * kBK * 2 : 16, 1024);
+          const uint64_t db0 = make_smem_desc_sw128(sb, B_MN ? 64 * kBK * 2 : 16, 1024);
+          if (leader) {
 #pragma unroll
-          for (int ks = 0; ks < kBK / 16; ++ks) {
-            // K-major: 16 elements = 32 bytes inside the swizzled row.  MN-major: 16 k-rows = 2 KiB.
-            const uint32_t a_addr = A_MN ? sa + ks * 2048 : sa + ks * 32;
-            const uint32_t b_addr = B_MN ? sb + ks * 2048 : sb + ks * 32;
-            const uint64_t da = make_smem_desc_sw128(a_addr, A_MN ? 64 * kBK * 2 : 16, 1024);
-            const uint64_t db = make_smem_desc_sw128(b_addr, B_MN ? 64 * kBK * 2 : 16, 1024);
-            if constexpr (PAIR)
-              umma_f16_ss_pair(tmem_d, da, db, idesc, (kb > w.kb_begin || ks > 0) ? 1u : 0u);
-            else if (p.fp8)
-              umma_f8_ss(tmem_d, da, db, idesc, (kb > w.kb_begin || ks > 0) ? 1u : 0u);
-            else
-              umma_f16_ss(tmem_d, da, db, idesc, (kb > w.kb_begin || ks > 0) ? 1u : 0u);
+            for (int ks = 0; ks < kBK / 16; ++ks) {
+              // K-major: 16 elements = 32 bytes inside the swizzled row.  MN-major: 16 k-rows = 2 KiB.  (address field: >> 4)
+              const uint64_t da = da0 + static_cast<uint64_t>(A_MN ? ks * 128 : ks * 2);
+              const uint64_t db = db0 + static_cast<uint64_t>(B_MN ? ks * 128 : ks * 2);
+              if constexpr (PAIR)
+                umma_f16_ss_pair(tmem_d, da, db, idesc, (kb > w.kb_begin || ks > 0) ? 1u : 0u);
+              else if (p.fp8)
+                umma_f8_ss(tmem_d, da, db, idesc, (kb > w.kb_begin || ks > 0) ? 1u : 0u);
+              else
+                umma_f16_ss(tmem_d, da, db, idesc, (kb > w.kb_begin || ks > 0) ? 1u : 0u);
+            }
+            // frees the stage (in both CTAs of a pair) once these MMAs have read it
+            if constexpr (PAIR) umma_commit_pair(&empty_bar[stage], 3);
+            else umma_commit(&empty_bar[stage]);
           }
-          // frees the stage (in both CTAs of a pair) once these MMAs have read it
-          if constexpr (PAIR) umma_commit_pair(&empty_bar[stage], 3);
-          else umma_commit(&empty_bar[stage]);
+          __syncwarp();
           NX_PROF(t_issue += clock64() - c2;)
           if (++stage == C::kStages) {
             stage = 0;
@@ -666,14 +673,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         if (!ok) break;
         // accumulator complete (each CTA of a pair holds its 128 rows)
-        if constexpr (PAIR) umma_commit_pair(&tfull_bar[acc], 3);
-        else umma_commit(&tfull_bar[acc]);
+        if (leader) {
+          if constexpr (PAIR) umma_commit_pair(&tfull_bar[acc], 3);
+          else umma_commit(&tfull_bar[acc]);
+        }
+        __syncwarp();
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1u;
         }
       }
-      NX_PROF(if (blockIdx.x < 148) {
+      NX_PROF(if (blockIdx.x < 148 && leader) {
         long long* o = g_mma_prof + (PAIR ? blockIdx.x >> 1 : blockIdx.x) * 8;
         o[0] = clock64() - t_begin; o[1] = t_acc; o[2] = t_tma; o[3] = t_issue; o[4] = n_kb; o[5] = n_tiles;
       })

@@ -369,7 +369,9 @@ class Engine:
         if not self.fast and self.kv_kind == 2:
             raise ValueError("FP8 KV needs the kernel path")
         elem = (2 if self.fast else 4) if self.kv_kind == 0 else 1
-        per_tok = self.L * 2 * self.Hl * self.D * elem + (self.L * 2 * self.Hl * 4 if self.kv_kind else 0)
+        # sized by the heads of the fullest rank, so that every rank of a tensor-parallel group owns the same number of
+        # blocks (the scheduler runs replicated) even when the heads do not divide evenly or a rank holds none
+        per_tok = self.L * 2 * self.Hp * self.D * elem + (self.L * 2 * self.Hp * 4 if self.kv_kind else 0)
         self._kv_tok_bytes = per_tok
         self.n_blocks = max(2, int(cfg.kv_bytes // max(1, per_tok * cfg.block_size)))
         self.max_blocks = -(-self.ctx // cfg.block_size)

@@ -362,6 +362,9 @@ class GptModel:
         # each norm backward also sums the columns of its BF16 dx: the bias gradient of the projection that follows
         K.norm_bwd(a["dlnf"], res[2 * L], self.p["lnf_w"], a["lnf_mean"], a["lnf_rstd"], dx=dres, dx_lp=dres_lp,
                    dgamma=g["lnf_w"], dbeta=g["lnf_b"], accumulate_params=True, dx_colsum=g["fcproj_b"][L - 1])
+        hook = self.backward_hook
+        if hook is not None:
+            hook(self.STAGE_HEAD)
         S = self._slots
         for l in range(L - 1, -1, -1):
             x_in, x_mid = res[2 * l], res[2 * l + 1]

@@ -88,6 +88,8 @@ def lib():
         path = _LIB_PATH
         if os.environ.get("NEXUS_B200_DEBUG_BOUNDS", "0") == "1":   # kernels with the index checks compiled in
             path = _LIB_PATH.with_name("libnexus_b200_cuda_dbg.so")
+        if os.environ.get("NEXUS_B200_CUDA_LIB"):                   # another build of the same library (A/B timing)
+            path = Path(os.environ["NEXUS_B200_CUDA_LIB"])
         if not path.exists():
             raise RuntimeError(
                 f"{path} is missing: build it with `python -m nexus_b200._build` "

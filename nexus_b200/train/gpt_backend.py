@@ -436,7 +436,10 @@ class GptLmBackend(LmBackend):
             d["stream"].wait_event(ev)
             ws.barrier()                              # every rank has produced this bucket
             for off, cnt in ranges:
-                cnt8 = cnt // 8 * 8
+                if cnt % 8 != 0 or off % 4 != 0:
+                    raise ValueError("bucketed data parallelism needs gradient slices of a multiple of 8 elements "
+                                     "that start on a 16-byte boundary; set NEXUS_DDP_BUCKETED=0 for this model")
+                cnt8 = cnt
                 per = (-(-cnt8 // n) + 7) // 8 * 8
                 lo = min(cnt8, r * per)
                 mine = max(0, min(per, cnt8 - lo))

@@ -34,6 +34,12 @@ CASES = [
     (1, 512, 512, 2, 2, 64, True, 100, False),
     (1, 256, 256, 2, 1, 128, True, 0, False),
     (1, 384, 384, 2, 2, 128, False, 0, False),
+    # head_dim 128 runs the two-q-tile forward: several 256-row items per head, ragged ends, window, Tq != Tk
+    (2, 1024, 1024, 3, 3, 128, True, 0, True),
+    (1, 700, 700, 2, 1, 128, True, 0, False),
+    (1, 640, 640, 2, 2, 128, True, 200, False),
+    (1, 300, 900, 4, 2, 128, True, 0, False),
+    (1, 900, 300, 2, 2, 128, True, 0, False),
 ]
 
 
@@ -153,3 +159,47 @@ def test_attention_dropout_in_kernels(Tq, Tk, H, Hkv, D, causal):
     assert abs(keep - (1 - p)) < 5e-3
     o0 = F.attention(q, k, v, causal, 0, None, 0.0, None, 0.0)
     assert (o0.float() - o.float()).abs().max() > 1e-2          # dropout did change the result
+
+
+def test_two_tile_forward_merges_key_chunks():
+    """The two-q-tile forward (head_dim 128) with a running (output, log-sum-exp) pair: three key/value chunks merged one
+    launch at a time equal one softmax over all keys."""
+    from nexus_b200.ops import _cuda as K
+    torch.manual_seed(7)
+    dev = "cuda"
+    B, Tq, Tk, H, D = 1, 384, 768, 2, 128
+    q = torch.randn(B, Tq, H, D, device=dev).bfloat16()
+    k = torch.randn(B, Tk, H, D, device=dev).bfloat16()
+    v = torch.randn(B, Tk, H, D, device=dev).bfloat16()
+    mo = torch.zeros(B, Tq, H, D, device=dev)
+    ml = torch.full((B, H, Tq), float("-inf"), device=dev)
+    for c in range(3):
+        o, lse = K.attention_fwd(q, k[:, c * 256:(c + 1) * 256], v[:, c * 256:(c + 1) * 256], causal=False,
+                                 merge_o=mo, merge_lse=ml)
+    K.check_status()
+    oref, lref = _ref(q.float(), k.float(), v.float(), False, 0, D ** -0.5)
+    assert (o.float() - oref).abs().max() < 2e-2
+    assert (lse - lref).abs().max() < 2e-2
+    assert (mo - oref).abs().max() < 2e-2
+
+
+def test_two_tile_forward_forced_at_head_dim_64():
+    """NEXUS_B200_ATTN_FWD=2 routes head_dim 64 through the two-q-tile kernel as well (the choice is read once per
+    process, so the check runs in a child)."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import torch\n"
+        "from nexus_b200.ops import _cuda as K\n"
+        "torch.manual_seed(0)\n"
+        "q, k, v = [torch.randn(2, 600, 4, 64, device='cuda').bfloat16() for _ in range(3)]\n"
+        "o, lse = K.attention_fwd(q, k, v, causal=True)\n"
+        "K.check_status()\n"
+        "ref = torch.nn.functional.scaled_dot_product_attention(*[t.float().transpose(1, 2) for t in (q, k, v)],"
+        " is_causal=True).transpose(1, 2)\n"
+        "assert (o.float() - ref).abs().max() < 2e-2, float((o.float() - ref).abs().max())\n"
+        "print('ok')\n")
+    env = dict(os.environ, NEXUS_B200_ATTN_FWD="2")
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "ok" in out.stdout, out.stderr[-2000:]

@@ -219,3 +219,27 @@ def test_int8_kv_close_to_fp():
     a = e0.forward([Chunk(s0, [40], 1)])[0, :97]
     b = e8.forward([Chunk(s8, [40], 1)])[0, :97]
     assert (a - b).norm() / a.norm() < 0.02
+
+
+@pytest.mark.parametrize("ranks,heads", [(2, 4), (3, 4), (4, 2)])
+def test_tensor_parallel_engine_with_uneven_heads_matches_one_rank(ranks, heads):
+    """Heads and MLP columns sharded over a group, also when the heads do not divide evenly (the last ranks hold fewer
+    heads or none and only take part in the all-reduce): every rank owns the same number of KV blocks and produces the
+    tokens of the single-rank engine."""
+    from nexus_b200.parallel.process_group import ThreadWorld
+    w = Gpt2Weights.random(2, heads, 48, 97, 64, seed=3)
+    for lw in w.h:
+        for k in ("attn_w", "fc_w", "proj_w", "fc2_w"):
+            lw[k] *= 4.0
+    cfg = dict(precision="fp32", device="cpu", max_seqs=4, max_tokens=128, block_size=4, kv_bytes=1 << 20)
+    prompt = [5, 17, 3, 44, 9, 60, 2]
+    want = generate(Engine(w, EngineConfig(**cfg)), prompt, 12, SamplingParams(temperature=0.0))
+
+    def run(pg):
+        eng = Engine(w, EngineConfig(tp_comm="nccl", **cfg), group=pg)
+        return eng.n_blocks, generate(eng, prompt, 12, SamplingParams(temperature=0.0))
+
+    out = ThreadWorld(ranks).run(run)
+    assert len({nb for nb, _ in out}) == 1
+    for _, toks in out:
+        assert toks == want
