@@ -183,6 +183,30 @@ def main(argv=None) -> int:
     report("dgrad_ag[down]", [M, k_loc, d], 2.0 * M * k_loc * d, (n - 1) * Ml * d * 2, fused, base, err)
     del w, da, da2
 
+    # ------------------------------------------------------------------ all-reduce: in-switch, peer loads, NCCL
+    from ..parallel.symm import fused_all_reduce, multimem_all_reduce
+    ar_rows = []
+    for numel in (256 * 1600, 16 << 20, 64 << 20):                     # FP32: a decode step's activations ... a gradient bucket
+        buf = ws.alloc(numel, torch.float32)
+        dst = ws.alloc(numel, torch.float32)
+        buf.local.normal_()
+        ref = buf.local.clone()
+        t_mm = timed(lambda: multimem_all_reduce(ws, buf, numel, scale=1.0 / n)) if buf.multicast else None
+        t_pl = timed(lambda: fused_all_reduce(ws, buf, dst, numel, scale=1.0 / n, multimem=False))
+        t_nc = timed(lambda: pg.all_reduce_tensor(ref, "sum"))
+        bus = 2.0 * (n - 1) / n * numel * 4                            # bytes per GPU of a ring all-reduce (bus bandwidth)
+        ar_rows.append({"op": "all_reduce[fp32]", "mbytes": round(numel * 4 / 2 ** 20, 1),
+                        "multimem_ms": None if t_mm is None else round(t_mm, 4), "peer_load_ms": round(t_pl, 4),
+                        "nccl_ms": round(t_nc, 4),
+                        "multimem_busbw_GBps": None if t_mm is None else round(bus / t_mm / 1e6, 1),
+                        "peer_load_busbw_GBps": round(bus / t_pl / 1e6, 1), "nccl_busbw_GBps": round(bus / t_nc / 1e6, 1)})
+    if rank == 0:
+        for r in ar_rows:
+            print("all_reduce fp32 %7.1f MiB   in-switch %s ms (%s GB/s bus)   peer loads %.4f ms (%.1f)   NCCL %.4f ms (%.1f)"
+                  % (r["mbytes"], r["multimem_ms"], r["multimem_busbw_GBps"], r["peer_load_ms"], r["peer_load_busbw_GBps"],
+                     r["nccl_ms"], r["nccl_busbw_GBps"]), flush=True)
+    rows.extend(ar_rows)
+
     # ------------------------------------------------------------------ wgrad over the sharded rows (pull form)
     if not args.pull:
         return _finish(rank, n, M, d, peak, link, rows, pg)
@@ -258,6 +282,8 @@ def _finish(rank, n, M, d, peak, link, rows, pg) -> int:
         print(json.dumps({"bench": "fused_comm", "n_gpus": n, "tokens": M, "d": d, "peak_tflops": peak,
                           "nvlink_GBps": link / 1e9, "rows": rows}))
         for r in rows:
+            if "fused_ms" not in r:
+                continue
             print("%-16s %-22s fused %8.3f ms  nccl+gemm %8.3f ms  x%.2f  %7.1f TFLOP/s  roofline %.3f ms -> %.2f"
                   % (r["op"], r["shape"], r["fused_ms"], r["nccl_plus_gemm_ms"], r["speedup"], r["tflops"],
                      r["roofline_ms"], r["fraction_of_roofline"]) + (f"  err {r['max_rel_err']:.1e}" if r["max_rel_err"] is not None else "")

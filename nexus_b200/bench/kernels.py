@@ -171,6 +171,16 @@ def build_cases(small: bool, library: bool = False) -> Dict[str, Tuple[Callable[
         cases[f"paged_decode_attention_split{sp}"] = (
             lambda sp=sp: I.paged_attention(qd, kc, vc, table, rs, cl, od, block_size=bs, kv_heads=H, splits=sp),
             0.0, 2.0 * nseq * ctx * H * D * 2)
+    # the same bytes with one head per cache row, i.e. every 16-token page of a head is one contiguous 2 KiB block
+    nb1 = nseq * H * ctx // bs
+    kc1, vc1 = rn(nb1, bs, 1, D), rn(nb1, bs, 1, D)
+    table1 = torch.randperm(nb1, device=dev, generator=g).to(torch.int32).view(nseq * H, ctx // bs)
+    qd1, od1 = rn(nseq * H, 1, D), torch.empty(nseq * H, 1, D, dtype=bf, device=dev)
+    rs1 = torch.arange(nseq * H, dtype=torch.int32, device=dev)
+    cl1 = torch.full((nseq * H,), ctx, dtype=torch.int32, device=dev)
+    cases["paged_decode_attention_contiguous_pages"] = (
+        lambda: I.paged_attention(qd1, kc1, vc1, table1, rs1, cl1, od1, block_size=bs, kv_heads=1, splits=1),
+        0.0, 2.0 * nseq * ctx * H * D * 2)
     xs, ws, bsk = rn(8, C), rn(F, C, scale=0.05), rn(F)
     cases["skinny_gemm_m8"] = (lambda: I.skinny_gemm(xs, ws, bsk, act="gelu"), 0.0, F * C * 2)
     wh = rn(V, C, scale=0.05)

@@ -89,7 +89,7 @@ def main(argv=None) -> int:
                          "tcgen05 kernels over peer memory, hand-scheduled backward); nccl: parallel.ParallelLm "
                          "(autograd, NCCL all-reduces at the region boundaries) - the same-box baseline")
     ap.add_argument("--copiers", type=int, default=0,
-                    help="copier CTAs of the fused GEMM kernels (0: 8 up to two ranks, 16 beyond, where the link binds)")
+                    help="copier CTAs of the fused GEMM kernels (0: 8 up to two ranks, 32 beyond, where the link binds)")
     ap.add_argument("--graph", type=int, default=0, help="fused: replay the whole step as one CUDA graph")
     args = ap.parse_args(argv)
     if args.comm == "fused" and args.precision == "bf16" and not args.check:

@@ -34,6 +34,8 @@ def main(argv=None) -> int:
     ap.add_argument("--kv", default="bf16", help="KV cache: bf16 | int8 | fp8")
     ap.add_argument("--batch-tokens", type=int, default=8192)
     ap.add_argument("--kv-gb", type=float, default=0.0, help="KV pool per GPU in GiB (0: sized for the workload)")
+    ap.add_argument("--pipeline", type=int, default=1,
+                    help="1: launch decode step n + 1 before the tokens of step n are read (device-fed tokens)")
     ap.add_argument("--tp-graphs", type=int, default=0, help="1: capture the decode steps of a tensor-parallel engine too")
     args = ap.parse_args(argv)
 
@@ -70,7 +72,8 @@ def main(argv=None) -> int:
     greedy = SamplingParams(temperature=0.0)
 
     def serve(reqs, new):
-        srv = Server(eng, Config(max_batch_tokens=args.batch_tokens, max_running=args.requests))
+        srv = Server(eng, Config(max_batch_tokens=args.batch_tokens, max_running=args.requests,
+                                 pipeline_decode=bool(args.pipeline)))
         futs = [srv.submit(Request(p, new, sampling=greedy)) for p in reqs]
         if group is not None:
             group.barrier()
@@ -98,7 +101,7 @@ def main(argv=None) -> int:
             "config": {"model": args.model, "tp": world, "requests": args.requests, "prompt_len": [args.prompt_min, args.prompt_max],
                        "max_new": args.max_new, "page_size": 16, "weights": args.quant, "kv": args.kv,
                        "kv_pool_gib": round(kv_bytes / 2 ** 30, 1), "batch_tokens": args.batch_tokens,
-                       "tp_graphs": bool(args.tp_graphs)},
+                       "tp_graphs": bool(args.tp_graphs), "pipelined_decode_steps": m.pipelined_steps},
             "data": "random prompts from seed 0, random-init weights"}), flush=True)
     if group is not None:
         if args.tp_graphs:

@@ -564,6 +564,85 @@ extern "C" int nx_comm_allreduce_shard(const NxPeerTable* in, int in_dtype, int 
   return launch_status();
 }
 
+// ---------------------------------------------------------------------------------------------
+// In-switch all-reduce (NVLS): `mc` is the multicast address of a symmetric buffer, i.e. one address that stands for
+// the same offset in every rank's copy.  `multimem.ld_reduce` makes NVSwitch read the 16 bytes from every rank and
+// return their sum (FP32 accumulation), `multimem.st` writes the result into every rank's copy: a rank moves its
+// slice over its own links once in each direction, whatever the number of ranks.
+// ---------------------------------------------------------------------------------------------
+template <bool BF16>
+__device__ __forceinline__ void multimem_ld_reduce(uint64_t addr, uint32_t (&r)[4]) {
+  if (BF16)
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "l"(addr)
+                 : "memory");
+  else
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "l"(addr)
+                 : "memory");
+}
+template <bool BF16>
+__device__ __forceinline__ void multimem_st(uint64_t addr, const uint32_t (&r)[4]) {
+  if (BF16)
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(r[0]), "r"(r[1]),
+                 "r"(r[2]), "r"(r[3])
+                 : "memory");
+  else
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(r[0]), "r"(r[1]),
+                 "r"(r[2]), "r"(r[3])
+                 : "memory");
+}
+template <bool BF16>
+__device__ __forceinline__ void multimem_scale(uint32_t (&r)[4], float scale) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (BF16) {
+      float lo, hi;
+      nx::unpack_bf16x2(r[j], lo, hi);
+      r[j] = nx::pack_bf16x2(lo * scale, hi * scale);
+    } else {
+      r[j] = __float_as_uint(__uint_as_float(r[j]) * scale);
+    }
+  }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(256) allreduce_multimem_kernel(uint8_t* mc, int64_t off_bytes, int64_t vecs, float scale) {
+  constexpr int U = 4;  // reductions in flight per thread
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const uint64_t base = reinterpret_cast<uint64_t>(mc) + static_cast<uint64_t>(off_bytes);
+  for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < vecs; i0 += stride * U) {
+    uint32_t r[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (i0 + u * stride < vecs) multimem_ld_reduce<BF16>(base + static_cast<uint64_t>(i0 + u * stride) * 16, r[u]);
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (i0 + u * stride < vecs) {
+        if (scale != 1.0f) multimem_scale<BF16>(r[u], scale);
+        multimem_st<BF16>(base + static_cast<uint64_t>(i0 + u * stride) * 16, r[u]);
+      }
+  }
+  __threadfence_system();  // the stores are out before the barrier kernel that follows signals the peers
+}
+
+extern "C" int nx_comm_allreduce_multimem(void* multicast_ptr, int dtype, int64_t shard_off, int64_t count, float scale,
+                                          nx_stream_t stream) {
+  if (multicast_ptr == nullptr || (dtype != NX_F32 && dtype != NX_BF16)) return -1;
+  if (count <= 0) return 0;
+  const int per_vec = dtype == NX_F32 ? 4 : 8;
+  if ((shard_off % per_vec) || (count % per_vec)) return -1;
+  const int64_t vecs = count / per_vec;
+  const int64_t off_bytes = shard_off * (dtype == NX_F32 ? 4 : 2);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int blocks = blocks_for(vecs, 256, 148 * 4);
+  if (dtype == NX_F32) allreduce_multimem_kernel<false><<<blocks, 256, 0, st>>>(static_cast<uint8_t*>(multicast_ptr), off_bytes, vecs, scale);
+  else allreduce_multimem_kernel<true><<<blocks, 256, 0, st>>>(static_cast<uint8_t*>(multicast_ptr), off_bytes, vecs, scale);
+  return launch_status();
+}
+
 extern "C" int nx_comm_a2a_heads(const void* x, const NxPeerTable* out, int B, int Tl, int H, int D, int rank, int n,
                                  int mode, nx_stream_t stream) {
   if (out == nullptr || n < 1 || n > NX_MAX_PEERS || H % n || (D & 7) || mode < 0 || mode > 1) return -1;

@@ -8,6 +8,8 @@
 #include "common.cuh"
 #include "nx_api_infer.h"
 #include "sm100_ptx.cuh"
+#include "tensor_map.h"
+#include <cstdlib>
 
 #include <cuda_fp8.h>
 
@@ -198,6 +200,130 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_row_stride, c
     for (int i = 0; i < 4 * TPW; ++i) gm = fmaxf(gm, s_m[i]);
     float gl = 0.0f, go = 0.0f;
     for (int i = 0; i < 4 * TPW; ++i) {
+      const float w = (s_m[i] == -INFINITY) ? 0.0f : exp2f(s_m[i] - gm);
+      gl += s_l[i] * w;
+      go += s_acc[i][d] * w;
+    }
+    if (splits == 1) {
+      out[row * o_row_stride + h * D + d] = __float2bfloat16_rn(gl > 0.0f ? go / gl : 0.0f);
+    } else {
+      const int64_t pi = (static_cast<int64_t>(row) * heads + h) * splits + split;
+      part_o[pi * D + d] = go;
+      if (d == 0) {
+        part_ml[pi * 2] = gm;
+        part_ml[pi * 2 + 1] = gl;
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// paged attention, decode, BF16 cache with 16-token pages: the K and V page of a head ([16][D], rows
+// kv_heads * D apart) arrive by one tiled TMA copy each into a ring of kStages shared-memory stages,
+// issued by one thread as soon as a stage has been consumed; with several resident CTAs an SM keeps
+// 100-200 KiB of cache reads in flight, which is what a bandwidth-bound kernel needs.  Scoring and
+// the running softmax are those of the kernel above: 128 threads, D / 8 lanes per cached token,
+// every lane group keeps its own (max, sum, 8 output columns) and the groups merge at the end.
+// grid (heads, rows, splits).
+// ------------------------------------------------------------------------------------------------
+constexpr int kPagedStages = 6;
+constexpr int kPagedWaitStatus = 7;  // status-word value: a page did not arrive within the wait limit
+
+template <int D>
+__global__ void __launch_bounds__(128)
+paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                        const __nv_bfloat16* __restrict__ q, int64_t q_row_stride,
+                        const int32_t* __restrict__ block_table, int max_blocks, const int32_t* __restrict__ row_seq,
+                        const int32_t* __restrict__ ctx_len, int heads, int kv_heads, float scale, int splits,
+                        __nv_bfloat16* __restrict__ out, int64_t o_row_stride, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, int* __restrict__ status) {
+  constexpr int LPT = D / 8;          // lanes per token
+  constexpr int TPP = 128 / LPT;      // tokens per pass of the block (16 at D = 64, 8 at D = 128)
+  constexpr int kPage = 16;
+  constexpr int kPageBytes = kPage * D * 2;
+  extern __shared__ __align__(128) uint8_t pd_smem[];
+  uint8_t* sK = pd_smem;                               // [kStages][16][D]
+  uint8_t* sV = sK + kPagedStages * kPageBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(sV + kPagedStages * kPageBytes);
+  __shared__ int s_abort;
+  const int h = blockIdx.x, row = blockIdx.y, split = blockIdx.z;
+  const int hk = h / (heads / kv_heads);
+  const int seq = row_seq[row];
+  const int ctx = ctx_len[row];
+  const int tid = threadIdx.x;
+  const int grp = tid / LPT, sub = tid % LPT;
+  const int per = (ctx + splits - 1) / splits;
+  const int t_begin = split * per, t_end = min(ctx, t_begin + per);
+  const int p_begin = t_begin / kPage, p_end = t_end > t_begin ? (t_end + kPage - 1) / kPage : p_begin;
+  const int32_t* bt = block_table + static_cast<int64_t>(seq) * max_blocks;
+  if (tid == 0) {
+    for (int s = 0; s < kPagedStages; ++s) nx::mbar_init(&full[s], 1);
+    s_abort = 0;
+    nx::fence_mbar_init();
+  }
+  __syncthreads();
+  auto issue = [&](int page) {   // thread 0: K and V page `page` of this head into stage (page - p_begin) % kStages
+    const int s = (page - p_begin) % kPagedStages;
+    const int blk = bt[page];
+    nx::mbar_arrive_expect_tx(&full[s], 2 * kPageBytes);
+    nx::tma_load_3d(sK + s * kPageBytes, &tm_k, &full[s], hk * D, blk * kPage, 0);
+    nx::tma_load_3d(sV + s * kPageBytes, &tm_v, &full[s], hk * D, blk * kPage, 0);
+  };
+  if (tid == 0)
+    for (int pg = p_begin; pg < min(p_end, p_begin + kPagedStages); ++pg) issue(pg);
+  float qv[8];
+  unpack8(*reinterpret_cast<const uint4*>(q + row * q_row_stride + h * D + sub * 8), qv);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) qv[j] *= scale * 1.4426950408889634f;
+  float m = -INFINITY, l = 0.0f, acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+  for (int pg = p_begin; pg < p_end; ++pg) {
+    const int n = pg - p_begin;
+    const int s = n % kPagedStages;
+    const bool arrived = nx::mbar_wait_bounded(&full[s], (n / kPagedStages) & 1, &s_abort);
+    if (!arrived) atomicCAS(status, 0, kPagedWaitStatus);
+#pragma unroll
+    for (int pass = 0; arrived && pass < kPage / TPP; ++pass) {
+      const int tok = pg * kPage + pass * TPP + grp;
+      const bool valid = tok >= t_begin && tok < t_end;
+      float kv[8], vv[8];
+      unpack8(*reinterpret_cast<const uint4*>(sK + s * kPageBytes + ((pass * TPP + grp) * D + sub * 8) * 2), kv);
+      unpack8(*reinterpret_cast<const uint4*>(sV + s * kPageBytes + ((pass * TPP + grp) * D + sub * 8) * 2), vv);
+      float t = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) t += qv[j] * kv[j];
+#pragma unroll
+      for (int o = LPT / 2; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+      if (valid) {
+        const float mn = fmaxf(m, t);
+        const float alpha = exp2f(m - mn);   // m == -inf: 0
+        const float pw = exp2f(t - mn);
+        l = l * alpha + pw;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = acc[j] * alpha + pw * vv[j];
+        m = mn;
+      }
+    }
+    // every thread has read stage s; a page that did not arrive ends the loop for the whole block (status is set)
+    if (__syncthreads_or(arrived ? 0 : 1)) break;
+    if (tid == 0 && pg + kPagedStages < p_end) issue(pg + kPagedStages);
+  }
+  // merge the lane groups of the block
+  __shared__ float s_m[TPP], s_l[TPP], s_acc[TPP][D];
+  if (sub == 0) {
+    s_m[grp] = m;
+    s_l[grp] = l;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s_acc[grp][sub * 8 + j] = acc[j];
+  __syncthreads();
+  if (tid < D) {
+    const int d = tid;
+    float gm = -INFINITY;
+    for (int i = 0; i < TPP; ++i) gm = fmaxf(gm, s_m[i]);
+    float gl = 0.0f, go = 0.0f;
+    for (int i = 0; i < TPP; ++i) {
       const float w = (s_m[i] == -INFINITY) ? 0.0f : exp2f(s_m[i] - gm);
       gl += s_l[i] * w;
       go += s_acc[i][d] * w;
@@ -651,6 +777,46 @@ extern "C" int nx_paged_attention_decode(const NxPagedArgs* a, nx_stream_t strea
   if (splits > 1 && (a->part_o == nullptr || a->part_ml == nullptr)) return -1;
   if (a->rows > 65535) return -1;
   dim3 grid(a->heads, a->rows, splits);
+  // BF16 cache, 16-token pages, known pool size: pages come in by TMA (NEXUS_B200_PAGED_TMA=0 keeps the plain loads)
+  static const bool tma_on = [] {
+    const char* e = std::getenv("NEXUS_B200_PAGED_TMA");
+    return e == nullptr || std::atoi(e) != 0;
+  }();
+  if (tma_on && a->kv_kind == 0 && a->block_size == 16 && a->num_blocks > 0 && a->status != nullptr) {
+    const int D = a->head_dim;
+    CUtensorMap tk, tv;
+    const uint64_t cols = static_cast<uint64_t>(a->kv_heads) * D, rows_total = static_cast<uint64_t>(a->num_blocks) * 16;
+    if (nx::make_tensor_map_3d(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->k_cache, cols, rows_total, 1, cols, 0, D, 16,
+                               CU_TENSOR_MAP_SWIZZLE_NONE) ||
+        nx::make_tensor_map_3d(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a->v_cache, cols, rows_total, 1, cols, 0, D, 16,
+                               CU_TENSOR_MAP_SWIZZLE_NONE))
+      return -3;
+    const int smem = 2 * kPagedStages * 16 * D * 2 + kPagedStages * 8;
+    if (D == 64)
+      paged_decode_tma_kernel<64><<<grid, 128, smem, st>>>(tk, tv, (const __nv_bfloat16*)a->q, a->q_row_stride, a->block_table,
+          a->max_blocks, a->row_seq, a->ctx_len, a->heads, a->kv_heads, a->scale, splits, (__nv_bfloat16*)a->out,
+          a->o_row_stride, a->part_o, a->part_ml, a->status);
+    else {
+      static bool once = false;
+      if (!once) {
+        if (cudaFuncSetAttribute(paged_decode_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+          return -2;
+        once = true;
+      }
+      paged_decode_tma_kernel<128><<<grid, 128, smem, st>>>(tk, tv, (const __nv_bfloat16*)a->q, a->q_row_stride, a->block_table,
+          a->max_blocks, a->row_seq, a->ctx_len, a->heads, a->kv_heads, a->scale, splits, (__nv_bfloat16*)a->out,
+          a->o_row_stride, a->part_o, a->part_ml, a->status);
+    }
+    if (launch_status() != 0) return -2;
+    if (splits > 1) {
+      dim3 g2(a->rows, a->heads);
+      if (D == 64)
+        paged_combine_kernel<64><<<g2, 64, 0, st>>>(a->part_o, a->part_ml, splits, a->heads, (__nv_bfloat16*)a->out, a->o_row_stride);
+      else
+        paged_combine_kernel<128><<<g2, 128, 0, st>>>(a->part_o, a->part_ml, splits, a->heads, (__nv_bfloat16*)a->out, a->o_row_stride);
+    }
+    return launch_status();
+  }
 #define NX_PD(D_, KV_)                                                                                              \
   paged_decode_kernel<D_, KV_><<<grid, 128, 0, st>>>((const __nv_bfloat16*)a->q, a->q_row_stride, a->k_cache, a->v_cache, \
       a->k_scale, a->v_scale, a->block_table, a->max_blocks, a->row_seq, a->ctx_len, a->block_size, a->heads,        \

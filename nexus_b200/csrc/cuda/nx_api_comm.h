@@ -45,6 +45,14 @@ int nx_comm_adamw_allgather(float* master, const float* grad, float* m, float* v
 int nx_comm_allreduce_shard(const NxPeerTable* in, int in_dtype, int n_in, const NxPeerTable* out, int out_dtype,
                             int n_out, int64_t shard_off, int64_t count, float scale, nx_stream_t stream);
 
+// The same all-reduce done by NVSwitch (NVLS): `multicast_ptr` is the multicast address of a symmetric buffer (one
+// address for the same offset in every rank's copy; from the symmetric-memory rendezvous, null when the fabric has no
+// multicast).  The caller owns [shard_off, shard_off + count) elements (FP32: multiples of 4, BF16: of 8): the switch
+// sums that range over all ranks (FP32 accumulation), the result times `scale` is stored into every rank's copy, in
+// place.  Bracket with nx_comm_barrier like the peer-load form.
+int nx_comm_allreduce_multimem(void* multicast_ptr, int dtype, int64_t shard_off, int64_t count, float scale,
+                               nx_stream_t stream);
+
 // Ulysses all-to-all by peer stores (BF16, D % 8 == 0, H % n == 0).  mode 0: x [B, Tl, H, D] ->
 // out[q] [B, n*Tl, H/n, D] (heads scattered, sequence gathered); mode 1: the inverse.  Bracket with barriers.
 int nx_comm_a2a_heads(const void* x, const NxPeerTable* out, int B, int Tl, int H, int D, int rank, int n, int mode,

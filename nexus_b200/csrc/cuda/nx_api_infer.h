@@ -30,6 +30,9 @@ typedef struct NxPagedArgs {
   float* part_ml;           // splits > 1: [rows, heads, splits, 2]
   float scale;
   int rows, heads, kv_heads, head_dim, block_size, max_blocks, splits, kv_kind;
+  int num_blocks;           // blocks in the pool (0: unknown).  With a BF16 cache, 16-token pages and a status word the
+                            // pages are fetched by TMA into a shared-memory ring; otherwise by plain loads
+  int* status;              // device status word for the bounded waits of the TMA form (may be null: plain loads)
 } NxPagedArgs;
 
 // One query row per (sequence, position): decode steps and speculative verification rows alike.

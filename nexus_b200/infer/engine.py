@@ -158,6 +158,15 @@ class Chunk:
 
 
 @dataclass
+class PendingTokens:
+    """Tokens of one ``Engine.sample(..., pending=True)`` call on their way to the host."""
+    event: object
+    pinned: torch.Tensor
+    rows: int
+    seqs: List[int]
+
+
+@dataclass
 class StepStats:
     tokens: int = 0
     prefill_tokens: int = 0
@@ -272,6 +281,12 @@ class Engine:
         self.counts_all = torch.zeros((cfg.max_seqs, self.V), dtype=torch.int32, device=self.dev)
         self.counts_out = torch.zeros((cfg.max_seqs, self.V), dtype=torch.int32, device=self.dev)
         self._ones = torch.ones(cfg.max_tokens, dtype=torch.int32, device=self.dev)
+        # pipelined decode: last sampled token per sequence (device), pinned landing buffers, host positions to complete
+        self._last_tok = torch.zeros(cfg.max_seqs, dtype=torch.int32, device=self.dev)
+        self._tok_pins = [torch.zeros(cfg.max_seqs, dtype=torch.int32).pin_memory() for _ in range(3)] \
+            if self.dev.type == "cuda" else []
+        self._tok_pin_next = 0
+        self._patch: Dict[int, int] = {}
         self._stage_bufs: Dict[int, torch.Tensor] = {}
         self._stage_evt: dict = {}
         self._sample_cache: dict = {}
@@ -573,8 +588,13 @@ class Engine:
         return dst.local[: t.numel()].view(t.shape)
 
     # ----------------------------------------------------------------------------- forward
-    def forward(self, chunks: Sequence[Chunk], layers: int = -1) -> torch.Tensor:
-        """Runs the packed batch; returns FP32 logits ``[logit_rows, vocab_padded]`` on the device."""
+    def forward(self, chunks: Sequence[Chunk], layers: int = -1, device_tokens: bool = False) -> torch.Tensor:
+        """Runs the packed batch; returns FP32 logits ``[logit_rows, vocab_padded]`` on the device.
+
+        ``device_tokens`` (one-token chunks): the token of every chunk is the one the last ``sample`` drew
+        for its sequence, taken from the device-resident table without the host having read it yet; the chunk's own
+        token value is ignored and the host-side token list is completed by ``collect``.  This is what lets a server
+        launch decode step n + 1 before it has read the tokens of step n."""
         t0 = time.perf_counter()
         cfg = self.cfg
         nl = self.L if layers < 0 else min(layers, self.L)
@@ -595,7 +615,12 @@ class Engine:
             slots = self._reserve(c.seq, n)
             r0 = len(tok)
             fresh = s.length == 0 and n > 1
-            tok.extend(int(t) for t in c.tokens)
+            if device_tokens:
+                if n != 1:
+                    raise ValueError("device_tokens needs one-token chunks")
+                tok.append(0)
+            else:
+                tok.extend(int(t) for t in c.tokens)
             pos.extend(range(s.length, s.length + n))
             slot.extend(slots)
             rseq.extend([c.seq] * n)
@@ -618,7 +643,11 @@ class Engine:
             self._logit_seq.extend([c.seq] * k)
             if not c.output and s.length == s.n_prompt:
                 s.n_prompt += n
-            s.tokens.extend(int(t) for t in c.tokens)
+            if device_tokens:
+                self._patch[c.seq] = len(s.tokens)      # filled in by collect() once the token has been read
+                s.tokens.append(-1)
+            else:
+                s.tokens.extend(int(t) for t in c.tokens)
             s.length += n
         N = len(tok)
         stats.tokens = N
@@ -645,11 +674,13 @@ class Engine:
         h[5, :R] = logit_rows
         h[5, R:] = 0
         if use_graph:
-            logits = self._decode_graph(bucket, ints)[:R]
+            logits = self._decode_graph(bucket, ints, N if device_tokens else 0)[:R]
             dv = self._static[bucket]["ints"]
             stats.graph = True
         else:
             dv = ints.to(self.dev, non_blocking=True)
+            if device_tokens:
+                dv[0, :N] = self._last_tok[dv[3, :N].long()]
             logits = self._body(dv[0], dv[1], dv[2], dv[3], dv[4], dv[5][:R], runs, nl)
         if self.dev.type == "cuda":
             ev = self._stage_evt.get(bucket)
@@ -790,7 +821,7 @@ class Engine:
         return t
 
     # ----------------------------------------------------------------------------- decode graphs
-    def _decode_graph(self, bucket: int, ints: torch.Tensor) -> torch.Tensor:
+    def _decode_graph(self, bucket: int, ints: torch.Tensor, device_rows: int = 0) -> torch.Tensor:
         st = self._static.get(bucket)
         if st is None:
             st = {"ints": torch.zeros((6, bucket), dtype=torch.int32, device=self.dev)}
@@ -811,6 +842,8 @@ class Engine:
                 st["logits"] = self._body(i[0], i[1], i[2], i[3], i[4], i[5], runs, self.L)
             self._graphs[bucket] = g
         st["ints"].copy_(ints, non_blocking=True)
+        if device_rows:   # tokens drawn by the previous step, still only on the device
+            st["ints"][0, :device_rows] = self._last_tok[st["ints"][3, :device_rows].long()]
         self._graphs[bucket].replay()
         return st["logits"]
 
@@ -838,9 +871,14 @@ class Engine:
     def logits_host(self, row: int) -> torch.Tensor:
         return self._logits[row, : self.V].float().cpu()
 
-    def sample(self, params: Sequence[SamplingParams], seqs: Optional[Sequence[int]] = None, offsets=0) -> List[int]:
+    def sample(self, params: Sequence[SamplingParams], seqs: Optional[Sequence[int]] = None, offsets=0,
+               pending: bool = False):
         """One token per logit row.  ``offsets``: Philox counter per row (or one value for all rows);
-        using the request's own token index makes a request's draws independent of the batch."""
+        using the request's own token index makes a request's draws independent of the batch.
+
+        ``pending``: nothing is read back; the tokens stay in the device table that
+        ``forward(device_tokens=True)`` reads, an asynchronous copy into pinned memory is started, and the returned
+        ``PendingTokens`` is turned into the list by ``collect`` later."""
         R = self.logit_rows()
         if len(params) != R:
             raise ValueError(f"sample: {len(params)} parameter sets for {R} logit rows")
@@ -870,10 +908,37 @@ class Engine:
             od, rows = dvs[: 2 * R].view(torch.int64), dvs[2 * R:]
             out = I.sample(self._logits, pd, od, vocab=self.V, counts_all=self.counts_all if need_counts else None,
                            counts_out=self.counts_out if need_counts else None, count_row=rows)
+            o32 = out.to(torch.int32)
+            self._last_tok.index_copy_(0, rows.long(), o32)      # the table forward(device_tokens=True) reads
+            if pending:
+                pin = self._tok_pins[self._tok_pin_next % len(self._tok_pins)]
+                self._tok_pin_next += 1
+                pin[:R].copy_(o32, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record()
+                return PendingTokens(ev, pin, R, seqs)
             return out.cpu().tolist()
         from .sampling import sample_reference
-        return [sample_reference(self._logits[r, : self.V].float().cpu(), params[r], self.counts_all[seqs[r]].cpu(),
+        toks = [sample_reference(self._logits[r, : self.V].float().cpu(), params[r], self.counts_all[seqs[r]].cpu(),
                                  self.counts_out[seqs[r]].cpu(), offs[r]) for r in range(R)]
+        t32 = torch.tensor(toks, dtype=torch.int32, device=self.dev)
+        self._last_tok.index_copy_(0, torch.tensor(seqs, dtype=torch.long, device=self.dev), t32)
+        if pending:   # reference path: nothing is asynchronous, the handle only defers the hand-over
+            return PendingTokens(None, t32.cpu(), R, seqs)
+        return toks
+
+    def collect(self, pending: "PendingTokens") -> List[int]:
+        """Waits for the tokens of a ``sample(..., pending=True)`` call and completes the host-side token lists of the
+        sequences that were fed from the device table since."""
+        if pending.event is not None:
+            pending.event.synchronize()
+        toks = [int(t) for t in pending.pinned[: pending.rows].tolist()]
+        for seq, t in zip(pending.seqs, toks):
+            idx = self._patch.pop(seq, None)
+            s = self.seqs.get(seq)
+            if idx is not None and s is not None and idx < len(s.tokens) and s.tokens[idx] == -1:
+                s.tokens[idx] = t
+        return toks
 
     def nll(self, targets: Sequence[int]) -> List[float]:
         t = torch.tensor(list(targets), dtype=torch.int32, device=self.dev)

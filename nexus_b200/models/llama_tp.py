@@ -68,8 +68,9 @@ class LlamaTpModel:
         self.v0 = self.r * self.Vl
         self.Nqkv = (self.Hl + 2 * self.Hkvl) * self.D
         # copier CTAs of the fused GEMMs: 8 fill the link between two ranks; at more ranks every projection is
-        # link-bound and 16 measured 1.28 x faster (Llama-7B, 8 ranks)
-        self.copier_ctas = copier_ctas if copier_ctas > 0 else (16 if (pg.size() if pg is not None else 1) > 2 else 8)
+        # link-bound and more copiers win although they take CTAs from the GEMM (Llama-7B, 8 ranks: 357 / 280 / 257 ms
+        # per step with 8 / 16 / 32)
+        self.copier_ctas = copier_ctas if copier_ctas > 0 else (32 if (pg.size() if pg is not None else 1) > 2 else 8)
         L, d, D = self.L, self.d, self.D
         shapes = {"wte": (self.Vl, d), "head": (self.Vl, d), "qkv_w": (L, self.Nqkv, d), "o_w": (L, d, self.Hl * D),
                   "up_w": (L, 2 * self.Fl, d), "down_w": (L, d, self.Fl),

@@ -19,7 +19,8 @@ class PagedArgs(C.Structure):
                 ("row_seq", C.c_void_p), ("ctx_len", C.c_void_p), ("out", C.c_void_p), ("o_row_stride", C.c_int64),
                 ("part_o", C.c_void_p), ("part_ml", C.c_void_p), ("scale", C.c_float), ("rows", C.c_int),
                 ("heads", C.c_int), ("kv_heads", C.c_int), ("head_dim", C.c_int), ("block_size", C.c_int),
-                ("max_blocks", C.c_int), ("splits", C.c_int), ("kv_kind", C.c_int)]
+                ("max_blocks", C.c_int), ("splits", C.c_int), ("kv_kind", C.c_int), ("num_blocks", C.c_int),
+                ("status", C.c_void_p)]
 
 
 class SampleParams(C.Structure):
@@ -55,6 +56,8 @@ def paged_attention(q, k_cache, v_cache, block_table, row_seq, ctx_len, out, *, 
     a.scale = scale if scale is not None else d ** -0.5
     a.rows, a.heads, a.kv_heads, a.head_dim = rows, heads, kv_heads, d
     a.block_size, a.max_blocks, a.splits, a.kv_kind = block_size, block_table.shape[1], splits, kv_kind
+    a.num_blocks = k_cache.shape[0] if k_cache.dim() == 4 and k_cache.is_contiguous() and v_cache.is_contiguous() else 0
+    a.status = K.status_word(q.device).data_ptr()
     if splits > 1:
         po = K.scratch(rows * heads * splits * d * 4, "paged_o", q.device)
         pm = K.scratch(rows * heads * splits * 8, "paged_ml", q.device)

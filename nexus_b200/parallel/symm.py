@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from typing import List, Optional
 
 import numpy as np
@@ -46,9 +47,12 @@ def _table(ptrs: List[int]) -> PeerTable:
 class SymmetricBuffer:
     """One symmetric allocation: ``local`` is this rank's tensor, ``ptrs[q]`` rank q's device address."""
 
-    def __init__(self, local: torch.Tensor, ptrs: List[int]):
+    def __init__(self, local: torch.Tensor, ptrs: List[int], multicast: int = 0):
         self.local, self.ptrs = local, ptrs
         self.table = _table(ptrs)
+        # NVSwitch multicast address of the allocation (0: the fabric or the driver offers none): one address that
+        # stands for the same offset in every rank's copy, for the in-switch reductions (`multimem_all_reduce`)
+        self.multicast = int(multicast)
 
     def offset_table(self, byte_offset: int) -> PeerTable:
         return _table([p + byte_offset for p in self.ptrs])
@@ -83,7 +87,13 @@ class SymmetricWorkspace:
         t = self.symm_mem.empty(int(numel), dtype=dtype, device=self.device)
         hdl = self.symm_mem.rendezvous(t, self.group)
         ptrs = [int(p) for p in hdl.buffer_ptrs]
-        return SymmetricBuffer(t, ptrs)
+        mc = 0
+        if os.environ.get("NEXUS_B200_MULTIMEM", "1") != "0":
+            try:
+                mc = int(hdl.multicast_ptr) if getattr(hdl, "multicast_ptr", None) else 0
+            except Exception:
+                mc = 0
+        return SymmetricBuffer(t, ptrs, mc)
 
     def barrier(self) -> None:
         """Device-side barrier over the group on the current stream (bounded wait)."""
@@ -183,16 +193,28 @@ class FusedShardedOptimizer:
 
 
 def fused_all_reduce(ws: SymmetricWorkspace, src: SymmetricBuffer, dst: SymmetricBuffer, count: int, *,
-                     scale: float = 1.0, one_shot: Optional[bool] = None) -> None:
+                     scale: float = 1.0, one_shot: Optional[bool] = None, multimem: Optional[bool] = None) -> None:
     """All-reduce (sum * scale) of ``src`` over the group into ``dst`` on every rank, with the dtype
     conversion fused into the reduction (e.g. BF16-compressed gradients in, FP32 out).  Two-shot
     (each rank reduces one slice and stores it to every rank) for large buffers, one-shot (each rank
-    reduces the whole buffer for itself) for small ones.  ``count`` must be a multiple of 8."""
+    reduces the whole buffer for itself) for small ones; when both sides have one dtype and the allocation has an
+    NVSwitch multicast address, the large form is reduced inside the switch (`multimem_all_reduce`; ``multimem=False``
+    keeps the peer-load kernel).  ``count`` must be a multiple of 8."""
     n, r = ws.n, ws.rank
     if count % 8:
         raise ValueError("fused_all_reduce: count must be a multiple of 8 elements")
     if one_shot is None:
         one_shot = count * src.local.element_size() <= (256 << 10)
+    # same dtype on both sides and a multicast address: let NVSwitch do the sum (in place in `src`, then one local
+    # copy when the result is wanted elsewhere); small buffers keep the one-shot form, which needs no second hop
+    if multimem is None:
+        multimem = not one_shot
+    if multimem and src.multicast and src.local.dtype == dst.local.dtype and \
+            src.local.dtype in (torch.float32, torch.bfloat16):
+        multimem_all_reduce(ws, src, count, scale=scale)
+        if dst is not src:
+            dst.local[:count].copy_(src.local[:count])
+        return
     dt_in, dt_out = K._DT[src.local.dtype], K._DT[dst.local.dtype]
     L = K.lib()
     ws.barrier()
@@ -210,6 +232,30 @@ def fused_all_reduce(ws: SymmetricWorkspace, src: SymmetricBuffer, dst: Symmetri
                                                C.c_int(dt_out), C.c_int(n), C.c_int64(off), C.c_int64(cnt),
                                                C.c_float(scale), K._stream()), "nx_comm_allreduce_shard")
     ws.barrier()
+
+
+def multimem_all_reduce(ws: SymmetricWorkspace, buf: SymmetricBuffer, count: int, *, offset: int = 0,
+                        scale: float = 1.0) -> bool:
+    """In-place all-reduce (sum * scale) of ``buf.local[offset : offset + count]`` over the group, reduced inside
+    NVSwitch: every rank asks the switch for the sum of its slice (``multimem.ld_reduce``) and stores it into every
+    rank's copy (``multimem.st``), so each byte crosses a GPU's links once per direction whatever the group size.
+    FP32 or BF16 buffers; ``offset`` and ``count`` multiples of 8 elements.  Returns False (nothing done) when the
+    allocation has no multicast address; the caller then uses ``fused_all_reduce``."""
+    if not buf.multicast:
+        return False
+    if offset % 8 or count % 8:
+        raise ValueError("multimem_all_reduce: offset and count must be multiples of 8 elements")
+    n, r = ws.n, ws.rank
+    per = (-(-count // n) + 7) // 8 * 8
+    lo = min(count, r * per)
+    mine = max(0, min(per, count - lo))
+    ws.barrier()                                   # every rank's values are in its copy
+    if mine > 0:
+        K._check(K.lib().nx_comm_allreduce_multimem(C.c_void_p(buf.multicast), C.c_int(K._DT[buf.local.dtype]),
+                                                    C.c_int64(offset + lo), C.c_int64(mine), C.c_float(scale),
+                                                    K._stream()), "nx_comm_allreduce_multimem")
+    ws.barrier()                                   # every slice has been written everywhere
+    return True
 
 
 def gemm_dist(ws: SymmetricWorkspace, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *,

@@ -7,6 +7,12 @@ and the free-block count, (3) runs ONE engine forward over [one decode token per
 request's own token index, so draws do not depend on the batch), (5) streams tokens, finishes requests
 on a stop token / ``max_new`` and records TTFT / TPOT / latency.
 
+Pipelined decode (``Config.pipeline_decode``, on by default on the kernel path): while nothing can be admitted and nothing has to be
+preempted, step n + 1 is launched before the tokens of step n have been read.  The engine feeds each sequence the token
+its last sampling call left on the device, the host reads the tokens one step late (streaming callbacks, stop tokens,
+statistics), and a request that turns out to have stopped at step n has its step n + 1 token dropped.  The host-side
+scheduling of a step then overlaps the device's work on the previous one.
+
 Parity: include/nexus/cuda/serve.hpp:39-97 and src/cuda/serve.cpp (`Server::step`) of the reference.
 """
 from __future__ import annotations
@@ -27,6 +33,8 @@ __all__ = ["Config", "Request", "Result", "Metrics", "Server"]
 class Config:
     max_batch_tokens: int = 2048
     max_running: int = 64
+    pipeline_decode: Optional[bool] = None   # launch the next decode step before reading this one's tokens
+                                             # (None: on the kernel path only; True also on the reference path)
 
 
 @dataclass
@@ -59,6 +67,7 @@ class Metrics:
     tpot_ms_sum: float = 0.0
     latency_ms_sum: float = 0.0
     busy_ms: float = 0.0
+    pipelined_steps: int = 0     # decode steps launched before the previous step's tokens were read
 
     def mean_ttft_ms(self) -> float:
         return self.ttft_ms_sum / max(1, self.completed)
@@ -71,7 +80,8 @@ class Metrics:
 
 
 class _Live:
-    __slots__ = ("id", "req", "future", "seq", "out", "t_submit", "t_first", "t_last", "preemptions", "next_token")
+    __slots__ = ("id", "req", "future", "seq", "out", "t_submit", "t_first", "t_last", "preemptions", "next_token",
+                 "launched", "zombie")
 
     def __init__(self, rid: int, req: Request):
         self.id, self.req, self.future = rid, req, Future()
@@ -81,6 +91,8 @@ class _Live:
         self.t_first = self.t_last = 0.0
         self.preemptions = 0
         self.next_token: Optional[int] = None   # sampled, not yet in the KV cache
+        self.launched = 0      # tokens sampled or being sampled by a step in flight
+        self.zombie = False    # finished while a later step that still contains it was in flight
 
 
 class Server:
@@ -97,6 +109,7 @@ class Server:
         self._wake = threading.Condition(self._lock)
         self._thread: Optional[threading.Thread] = None
         self._stop = False
+        self._inflight = None      # (PendingTokens, [requests]) of the decode step whose tokens have not been read
 
     # ------------------------------------------------------------------ submission
     def submit(self, req: Request) -> Future:
@@ -116,7 +129,7 @@ class Server:
 
     def pending(self) -> int:
         with self._lock:
-            return len(self.waiting) + len(self.running)
+            return len(self.waiting) + len(self.running) + (1 if self._inflight is not None else 0)
 
     # ------------------------------------------------------------------ one scheduling step
     def step(self) -> int:
@@ -124,6 +137,10 @@ class Server:
         eng, cfg = self.engine, self.cfg
         t0 = time.perf_counter()
         with self._lock:
+            n_pipe = self._pipelined_step()
+            if n_pipe is not None:
+                return n_pipe
+            self._drain()
             # 1. every running request needs room for one more token: preempt the newest while short
             def decode_need() -> int:
                 return sum(eng.blocks_needed(r.seq, 1) for r in self.running)
@@ -178,36 +195,91 @@ class Server:
             params = [r.req.sampling for r in order]
             offsets = [len(r.req.prompt) + len(r.out) for r in order]
             toks = eng.sample(params, [r.seq for r in order], offsets)
-            now = time.perf_counter()
             self.running.extend(admitted)
-            done: List[_Live] = []
-            for r, t in zip(order, toks):
-                r.out.append(t)
-                r.next_token = t
-                if r.t_first == 0.0:
-                    r.t_first = now
-                r.t_last = now
-                self.metrics.output_tokens += 1
-                if r.req.on_token is not None:
-                    r.req.on_token(r.id, t)
-                full = eng.length(r.seq) + 1 >= eng.ctx
-                if len(r.out) >= r.req.max_new or t == r.req.stop_token or full:
-                    done.append(r)
-            for r in done:
-                self.running.remove(r)
-                eng.free_sequence(r.seq)
-                res = Result(r.id, list(r.out), (r.t_first - r.t_submit) * 1e3,
-                             (r.t_last - r.t_first) * 1e3 / max(1, len(r.out) - 1), (now - r.t_submit) * 1e3,
-                             r.preemptions)
-                m = self.metrics
-                m.completed += 1
-                m.ttft_ms_sum += res.ttft_ms
-                m.tpot_ms_sum += res.tpot_ms
-                m.latency_ms_sum += res.latency_ms
-                r.future.set_result(res)
+            for r in order:
+                r.launched = len(r.out) + 1
+            self._consume(order, toks)
             self.metrics.steps += 1
             self.metrics.busy_ms += (time.perf_counter() - t0) * 1e3
             return eng.last_step().tokens
+
+    def _consume(self, order: List[_Live], toks: List[int]) -> None:
+        """Books one sampled token per request of ``order``: streaming, stop conditions, results."""
+        eng = self.engine
+        now = time.perf_counter()
+        done: List[_Live] = []
+        for r, t in zip(order, toks):
+            if r.zombie:                 # stopped one step earlier; this token was drawn past its end
+                eng.free_sequence(r.seq)
+                r.seq = -1
+                continue
+            r.out.append(t)
+            r.next_token = t
+            if r.t_first == 0.0:
+                r.t_first = now
+            r.t_last = now
+            self.metrics.output_tokens += 1
+            if r.req.on_token is not None:
+                r.req.on_token(r.id, t)
+            full = len(r.req.prompt) + len(r.out) >= eng.ctx
+            if len(r.out) >= r.req.max_new or t == r.req.stop_token or full:
+                done.append(r)
+        for r in done:
+            self.running.remove(r)
+            if r.launched > len(r.out):  # a step in flight still works on this sequence: free it when that step is read
+                r.zombie = True
+            else:
+                eng.free_sequence(r.seq)
+            res = Result(r.id, list(r.out), (r.t_first - r.t_submit) * 1e3,
+                         (r.t_last - r.t_first) * 1e3 / max(1, len(r.out) - 1), (now - r.t_submit) * 1e3,
+                         r.preemptions)
+            m = self.metrics
+            m.completed += 1
+            m.ttft_ms_sum += res.ttft_ms
+            m.tpot_ms_sum += res.tpot_ms
+            m.latency_ms_sum += res.latency_ms
+            r.future.set_result(res)
+
+    def _drain(self) -> None:
+        """Reads the tokens of the step in flight, if any."""
+        if self._inflight is not None:
+            pend, order = self._inflight
+            self._inflight = None
+            self._consume(order, self.engine.collect(pend))
+
+    def _pipelined_step(self) -> Optional[int]:
+        """Launches the next decode step before the tokens of the one in flight are read.  Returns None when the
+        situation needs the ordinary step (something to admit, blocks short, nothing to continue)."""
+        eng, cfg = self.engine, self.cfg
+        on = getattr(eng, "fast", False) if cfg.pipeline_decode is None else cfg.pipeline_decode
+        if not (on and self.running):
+            return None
+        bs = eng.block_size()
+        if self.waiting and len(self.running) < cfg.max_running:
+            cand = self.waiting[0]
+            n = len(cand.req.prompt) + len(cand.out)
+            if n <= cfg.max_batch_tokens - len(self.running) and -(-(n + 1) // bs) <= eng.free_blocks():
+                return None                                   # the head of the queue can be admitted: ordinary step
+        cont = [r for r in self.running
+                if r.launched < r.req.max_new and len(r.req.prompt) + r.launched < eng.ctx]
+        if not cont:
+            return None
+        if sum(eng.blocks_needed(r.seq, 1) for r in cont) > eng.free_blocks():
+            return None                                       # preemption is decided with every token known
+        t0 = time.perf_counter()
+        chunks = [Chunk(r.seq, [0], 1, True) for r in cont]
+        eng.forward(chunks, device_tokens=True)
+        offsets = [len(r.req.prompt) + r.launched for r in cont]
+        pend = eng.sample([r.req.sampling for r in cont], [r.seq for r in cont], offsets, pending=True)
+        for r in cont:
+            r.launched += 1
+        prev, self._inflight = self._inflight, (pend, cont)
+        if prev is not None:
+            self._consume(prev[1], eng.collect(prev[0]))
+        self.metrics.steps += 1
+        self.metrics.pipelined_steps += 1
+        self.metrics.busy_ms += (time.perf_counter() - t0) * 1e3
+        return len(cont)
 
     def run_until_idle(self, max_steps: int = 1 << 30) -> None:
         for _ in range(max_steps):

@@ -443,7 +443,11 @@ class GptLmBackend(LmBackend):
                 per = (-(-cnt8 // n) + 7) // 8 * 8
                 lo = min(cnt8, r * per)
                 mine = max(0, min(per, cnt8 - lo))
-                if mine > 0:
+                if mine > 0 and g.multicast:      # the sum is formed inside NVSwitch
+                    K._check(K.lib().nx_comm_allreduce_multimem(C.c_void_p(g.multicast), C.c_int(K._DT[torch.float32]),
+                                                                C.c_int64(off + lo), C.c_int64(mine), C.c_float(1.0),
+                                                                K._stream()), "nx_comm_allreduce_multimem")
+                elif mine > 0:
                     K._check(K.lib().nx_comm_allreduce_shard(C.byref(g.table), C.c_int(K._DT[torch.float32]), C.c_int(n),
                                                              C.byref(g.table), C.c_int(K._DT[torch.float32]), C.c_int(n),
                                                              C.c_int64(off + lo), C.c_int64(mine), C.c_float(1.0),

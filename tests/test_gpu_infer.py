@@ -238,6 +238,34 @@ def test_engine_generate_speculative_graphs_and_server():
     K.check_status()
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+def test_server_pipelined_decode_equals_step_by_step(graphs):
+    """Decode step n + 1 launched before the tokens of step n are read (tokens fed from the device table, read back one
+    step late through pinned memory) against the ordinary loop: same tokens with stop tokens, seeds, penalties,
+    admission in the middle of decoding, eager and with captured decode graphs."""
+    from nexus_b200.infer import Engine, EngineConfig, SamplingParams
+    from nexus_b200.serve import Config, Request, Server
+    from nexus_b200.ops import _cuda as K
+    w = _weights()
+    outs = {}
+    for pipe in (False, True):
+        e = Engine(w, EngineConfig(max_seqs=8, max_tokens=512, kv_bytes=64 << 20, cuda_graphs=graphs))
+        srv = Server(e, Config(max_batch_tokens=128, max_running=4, pipeline_decode=pipe))
+        g = torch.Generator().manual_seed(9)
+        futs = []
+        for i in range(9):
+            prompt = torch.randint(0, 1000, (int(torch.randint(3, 40, (1,), generator=g)),), generator=g).tolist()
+            sp = SamplingParams(temperature=0.0) if i % 2 == 0 else \
+                SamplingParams(temperature=0.8, top_k=40, top_p=0.9, seed=50 + i, repetition_penalty=1.2)
+            futs.append(srv.submit(Request(prompt, 6 + 4 * i, sampling=sp, stop_token=17 if i % 3 == 0 else None)))
+        srv.run_until_idle(2000)
+        outs[pipe] = [f.result(timeout=1).tokens for f in futs]
+        assert (srv.metrics.pipelined_steps > 0) == pipe
+        assert e.free_blocks() == e.total_blocks()
+        K.check_status()
+    assert outs[True] == outs[False]
+
+
 @pytest.mark.parametrize("weights,kv", [("w8a8", "bf16"), ("w4a16", "int8"), ("bf16", "fp8"), ("fp8", "bf16")])
 def test_engine_quantised_modes(weights, kv):
     from nexus_b200.infer import Chunk, Engine, EngineConfig, QuantOptions, generate

@@ -243,3 +243,30 @@ def test_tensor_parallel_engine_with_uneven_heads_matches_one_rank(ranks, heads)
     assert len({nb for nb, _ in out}) == 1
     for _, toks in out:
         assert toks == want
+
+
+@pytest.mark.parametrize("kv_bytes,max_running", [(1 << 20, 8), (1 << 20, 3), (40 * 1024, 8)])
+def test_pipelined_decode_equals_step_by_step(kv_bytes, max_running):
+    """Launching decode step n + 1 before the tokens of step n are read (device-fed tokens, tokens consumed one step
+    late, zombie steps of requests that hit their stop token) produces exactly the tokens, stop points and engine-side
+    token lists of the ordinary loop: with admission in the middle of decoding, with preemption by recompute when
+    blocks run out, with stop tokens, seeds and penalties."""
+    outs = {}
+    for pipe in (False, True):
+        w, eng = make(layers=2, heads=2, d=32, vocab=97, ctx=64, kv_bytes=kv_bytes)
+        srv = Server(eng, Config(max_batch_tokens=64, max_running=max_running, pipeline_decode=pipe))
+        g = torch.Generator().manual_seed(5)
+        futs, streamed = [], {}
+        for i in range(7):
+            prompt = torch.randint(0, 97, (int(torch.randint(3, 14, (1,), generator=g)),), generator=g).tolist()
+            sp = SamplingParams(temperature=0.0) if i % 2 == 0 else \
+                SamplingParams(temperature=0.9, top_k=20, top_p=0.95, seed=100 + i, repetition_penalty=1.1)
+            futs.append(srv.submit(Request(prompt, 5 + 3 * i, sampling=sp, stop_token=11 if i % 3 == 0 else None,
+                                           on_token=lambda rid, t, d=streamed: d.setdefault(rid, []).append(t))))
+        srv.run_until_idle()
+        res = [f.result() for f in futs]
+        assert all(streamed[r.id] == r.tokens for r in res)
+        assert eng.free_blocks() == eng.total_blocks()            # every sequence (zombies included) was released
+        assert (srv.metrics.pipelined_steps > 0) == pipe
+        outs[pipe] = [(r.tokens, r.preemptions) for r in res]
+    assert outs[True] == outs[False]

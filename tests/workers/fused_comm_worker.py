@@ -150,6 +150,27 @@ def main():
         check(f"fused all-reduce bf16->fp32 n={count} one_shot={one_shot}",
               (dst.local - 0.5 * want).abs().max().item() < 1e-5)
 
+    # ---- the same sum formed inside NVSwitch (multimem), in place, FP32 and BF16; skipped where the allocation has no
+    # multicast address
+    from nexus_b200.parallel.symm import multimem_all_reduce
+    for dt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+        count = (1 << 20) + 64
+        buf = ws.alloc(count, dt)
+        gen = torch.Generator(device=dev).manual_seed(200 + rank)
+        buf.local.copy_(torch.randn(count, device=dev, generator=gen).to(dt))
+        want = buf.local.float().clone()
+        pg.all_reduce_tensor(want)
+        head = buf.local[:64].clone()
+        done = multimem_all_reduce(ws, buf, count - 64, offset=64, scale=0.5)
+        torch.cuda.synchronize()
+        K.check_status(dev)
+        if done:
+            check(f"in-switch all-reduce {str(dt)[6:]} n={count - 64}",
+                  (buf.local[64:].float() - 0.5 * want[64:]).abs().max().item() < tol * max(1.0, want.abs().max().item())
+                  and torch.equal(buf.local[:64], head))
+        elif rank == 0:
+            print("--  in-switch all-reduce: no multicast address on this fabric, peer-load kernel stays", flush=True)
+
     # ---- context parallelism: ring attention (contiguous + zigzag) and Ulysses vs full attention
     Bc, Tl, Hc, Dc = 2, 256, 4, 64
     Tfull = Tl * world
