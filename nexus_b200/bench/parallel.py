@@ -76,6 +76,11 @@ def main(argv=None) -> int:
     ap.add_argument("--model", default="llama2-7b")
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0: the preset's)")
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel degree (0: all ranks)")
+    ap.add_argument("--cp", type=int, default=1, help="context-parallel degree (the `ParallelLm` path, --comm nccl)")
+    ap.add_argument("--cp-algorithm", default="ring", choices=["ring", "ulysses"])
+    ap.add_argument("--cp-layout", default="zigzag", choices=["zigzag", "contiguous"])
+    ap.add_argument("--cp-comm", default="fused", choices=["fused", "nccl"],
+                    help="context-parallel attention over peer memory (fused) or send_recv through NCCL")
     ap.add_argument("--sp", type=int, default=0, help="1: sequence-parallel norm / residual regions")
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--global-batch", type=int, default=8, help="sequences per optimizer step (over all dp replicas)")
@@ -92,7 +97,7 @@ def main(argv=None) -> int:
                     help="copier CTAs of the fused GEMM kernels (0: 8 up to two ranks, 32 beyond, where the link binds)")
     ap.add_argument("--graph", type=int, default=0, help="fused: replay the whole step as one CUDA graph")
     args = ap.parse_args(argv)
-    if args.comm == "fused" and args.precision == "bf16" and not args.check:
+    if args.comm == "fused" and args.precision == "bf16" and not args.check and args.cp == 1:
         return run_fused(args)
 
     from ..fused.ops import linear_precision
@@ -108,21 +113,23 @@ def main(argv=None) -> int:
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     pg = init_process_group(backend="nccl", device=f"cuda:{local}")
-    tp = args.tp or world
-    dp = world // tp
+    tp = args.tp or max(1, world // args.cp)
+    dp = world // (tp * args.cp)
     cfg = preset(args.model)
     if args.layers > 0:
         cfg.n_layer = args.layers
     cfg.max_position = max(cfg.max_position, args.seq_len)
     source = build(cfg) if args.check else _RandomWeights(cfg, dev)
-    plm = ParallelLm(source, pg, ParallelConfig(dp=dp, tp=tp, sp=bool(args.sp)), device=dev, compute_dtype=torch.bfloat16)
+    plm = ParallelLm(source, pg, ParallelConfig(dp=dp, tp=tp, cp=args.cp, sp=bool(args.sp), cp_algorithm=args.cp_algorithm,
+                                                cp_layout=args.cp_layout, cp_comm=args.cp_comm),
+                     device=dev, compute_dtype=torch.bfloat16)
     if not args.check:
         del source
     torch.cuda.empty_cache()
     opt = types.SimpleNamespace(beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1)
     per_replica = args.global_batch // dp
     n_micro = per_replica // args.micro_batch
-    gen = torch.Generator(device=dev).manual_seed(1234 + rank // tp)
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank // (tp * args.cp))
 
     def batch():
         return [torch.randint(0, cfg.vocab_size, (args.micro_batch, args.seq_len), device=dev, generator=gen)
@@ -163,7 +170,9 @@ def main(argv=None) -> int:
         print(json.dumps({
             "metric": f"train tokens/s {args.model} tensor-parallel", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "ms_per_step": ms, "steps": args.steps, "warmup": max(1, args.warmup),
-            "config": {"model": args.model, "layers": cfg.n_layer, "tp": tp, "dp": dp, "sp": bool(args.sp),
+            "config": {"model": args.model, "layers": cfg.n_layer, "tp": tp, "dp": dp, "cp": args.cp,
+                       "cp_attention": (f"{args.cp_algorithm}/{args.cp_layout}/{args.cp_comm}" if args.cp > 1 else None),
+                       "sp": bool(args.sp),
                        "seq_len": args.seq_len, "global_batch": args.global_batch, "micro_batch": args.micro_batch,
                        "linear_precision": args.precision, "compute_dtype": "bf16", "master": "fp32 AdamW, clip 1.0"},
             "losses": [round(x, 4) for x in losses],

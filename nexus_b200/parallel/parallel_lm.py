@@ -49,6 +49,8 @@ class ParallelConfig:
     pp_schedule: str = "1f1b"
     virtual_stages: int = 1
     cp_algorithm: str = "ring"     # "ring" | "ulysses"
+    cp_comm: str = "fused"         # on GPUs: "fused" = ring / Ulysses over peer memory (the attention kernels read the
+                                   # owners' K / V by TMA, head <-> sequence exchange by peer stores); "nccl" = send_recv
     cp_layout: str = "zigzag"      # "zigzag" | "contiguous"
 
     def world(self) -> int:
@@ -193,6 +195,12 @@ class ParallelLm:
         self.tppp_g = self.mesh.flatten(["pp", "tp"])
         self.tp_r, self.cp_r, self.pp_r, self.dp_r = (self.mesh.index(n) for n in ("tp", "cp", "pp", "dp"))
         self.pp_g = self.mesh.group("pp")
+        # context parallelism on GPUs: symmetric workspace over the cp group for the peer-memory attention paths
+        self._cp_ws = None
+        if cfg.cp > 1 and self.device.type == "cuda" and cfg.cp_comm == "fused" and mc.window <= 0 and \
+                self.cd == torch.bfloat16 and getattr(self.cp_g, "group", None) is not None:
+            from .symm import SymmetricWorkspace
+            self._cp_ws = SymmetricWorkspace(self.cp_g)
         # embedding group {first, last} pipeline stage for the tied weight
         self.tie_g = None
         if cfg.pp > 1 and mc.tie_embeddings:
@@ -330,7 +338,13 @@ class ParallelLm:
         if self.rope is not None:
             q = apply_rope(q, self.rope.cos, self.rope.sin, positions)
             k = apply_rope(k, self.rope.cos, self.rope.sin, positions)
-        if self.cfg.cp > 1:
+        if self.cfg.cp > 1 and self._cp_ws is not None:
+            from . import symm
+            if self.cfg.cp_algorithm == "ulysses":
+                a = symm.ulysses_attention(self._cp_ws, q, k, v, causal=True)
+            else:
+                a = symm.ring_attention_autograd(self._cp_ws, q, k, v, layout=self.cfg.cp_layout, causal=True)
+        elif self.cfg.cp > 1:
             if self.cfg.cp_algorithm == "ulysses":
                 a = ulysses_attention(q, k, v, self.cp_g)
             else:

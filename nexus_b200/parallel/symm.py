@@ -557,6 +557,35 @@ class RingAttention:
         return dq_acc.to(q.dtype), dkv[0], dkv[1]
 
 
+class _RingAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, ring, causal):
+        o, lse = ring.forward(q, k, v, causal)
+        ctx.ring, ctx.causal = ring, causal
+        ctx.save_for_backward(q, k, v, o, lse)
+        return o
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = ctx.ring.backward(q, k, v, o, lse, d_o.contiguous(), ctx.causal)
+        return dq, dk, dv, None, None
+
+
+def ring_attention_autograd(ws: SymmetricWorkspace, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                            layout: str = "contiguous", causal: bool = True) -> torch.Tensor:
+    """Differentiable ring attention over the group of ``ws`` (q [B, Tl, H, D], k / v [B, Tl, Hkv, D], BF16, this rank's
+    tokens in the given layout): `RingAttention.forward` / `.backward` under one autograd node.  The symmetric K / V
+    and gradient buffers are kept per shape on the workspace.  Used by `ParallelLm` on GPUs when cp > 1."""
+    B, Tl, Hkv, D = k.shape
+    cache = ws.__dict__.setdefault("_rings", {})
+    key = (B, Tl, Hkv, D, layout)
+    ring = cache.get(key)
+    if ring is None:
+        ring = cache[key] = RingAttention(ws, B, Tl, Hkv, D, layout)
+    return _RingAttnFn.apply(q.contiguous(), k.contiguous(), v.contiguous(), ring, causal)
+
+
 class _VocabParallelCE(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, targets, ws, vocab_start, ignore_index):
@@ -605,28 +634,79 @@ def vocab_parallel_cross_entropy(ws: SymmetricWorkspace, logits: torch.Tensor, t
     return _VocabParallelCE.apply(logits, targets, ws, int(vocab_start), int(ignore_index))
 
 
+def _a2a_heads(ws: SymmetricWorkspace, x: torch.Tensor, buf: SymmetricBuffer, mode: int) -> None:
+    """mode 0: [B, Tl, H, D] of every rank -> [B, n * Tl, H / n, D] in each rank's ``buf``; mode 1: the way back."""
+    if mode == 0:
+        B, Tl, H, D = x.shape
+    else:
+        B, T, Hl, D = x.shape
+        Tl, H = T // ws.n, Hl * ws.n
+    K._check(K.lib().nx_comm_a2a_heads(K._p(x.contiguous()), C.byref(buf.table), C.c_int(B), C.c_int(Tl), C.c_int(H),
+                                       C.c_int(D), C.c_int(ws.rank), C.c_int(ws.n), C.c_int(mode), K._stream()),
+             "nx_comm_a2a_heads")
+
+
+def _ulysses_bufs(ws: SymmetricWorkspace, tag: str, numel: int, count: int) -> List[SymmetricBuffer]:
+    cache = ws.__dict__.setdefault("_ulysses", {})
+    bufs = cache.setdefault((tag, numel), [])
+    while len(bufs) < count:
+        bufs.append(ws.alloc(numel, torch.bfloat16))
+    return bufs
+
+
+class _UlyssesFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, ws, causal):
+        n = ws.n
+        B, Tl, H, D = q.shape
+        Hkv = k.shape[2]
+        gq_b, back_b = _ulysses_bufs(ws, "q", q.numel(), 2)
+        gk_b, gv_b = _ulysses_bufs(ws, "kv", k.numel(), 2)
+        ws.barrier()                                   # the previous call's readers are done
+        _a2a_heads(ws, q, gq_b, 0)
+        _a2a_heads(ws, k, gk_b, 0)
+        _a2a_heads(ws, v, gv_b, 0)
+        ws.barrier()
+        gq = gq_b.local.view(B, n * Tl, H // n, D).clone()
+        gk = gk_b.local.view(B, n * Tl, Hkv // n, D).clone()
+        gv = gv_b.local.view(B, n * Tl, Hkv // n, D).clone()
+        o, lse = K.attention_fwd(gq, gk, gv, causal=causal)
+        _a2a_heads(ws, o, back_b, 1)
+        ws.barrier()
+        out = back_b.local.view(B, Tl, H, D).clone()
+        ctx.ws, ctx.causal = ws, causal
+        ctx.save_for_backward(gq, gk, gv, o, lse)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        ws, n = ctx.ws, ctx.ws.n
+        gq, gk, gv, o, lse = ctx.saved_tensors
+        B, T, Hl, D = gq.shape
+        Tl, Hkvl = T // n, gk.shape[2]
+        bq0, bq1 = _ulysses_bufs(ws, "q", gq.numel(), 2)
+        bk0, bk1 = _ulysses_bufs(ws, "kv", gk.numel(), 2)
+        ws.barrier()
+        _a2a_heads(ws, d_out, bq0, 0)                  # dO: sequence shards -> head shards
+        ws.barrier()
+        g_do = bq0.local.view(B, T, Hl, D).clone()
+        dq, dk, dv = K.attention_bwd(gq, gk, gv, o, lse, g_do, causal=ctx.causal)
+        ws.barrier()                                   # every rank has taken its dO out of the buffer
+        _a2a_heads(ws, dq, bq1, 1)
+        _a2a_heads(ws, dk, bk0, 1)
+        _a2a_heads(ws, dv, bk1, 1)
+        ws.barrier()
+        gdq = bq1.local.view(B, Tl, Hl * n, D).clone()
+        gdk = bk0.local.view(B, Tl, Hkvl * n, D).clone()
+        gdv = bk1.local.view(B, Tl, Hkvl * n, D).clone()
+        return gdq, gdk, gdv, None, None
+
+
 def ulysses_attention(ws: SymmetricWorkspace, q, k, v, causal: bool = True):
     """DeepSpeed-Ulysses attention over symmetric memory: heads <-> sequence all-to-all by peer stores,
     local causal flash attention over the full sequence on H/n heads, all-to-all back.
-    q/k/v: [B, Tl, H, D] BF16 with H % n == 0.  Returns o [B, Tl, H, D]."""
-    n, r = ws.n, ws.rank
-    B, Tl, H, D = q.shape
-    Hl = H // n
-    numel = B * Tl * H * D
-    cache = ws.__dict__.setdefault("_ulysses", {})
-    if cache.get("numel") != numel:
-        cache["numel"] = numel
-        cache["bufs"] = [ws.alloc(numel, torch.bfloat16) for _ in range(4)]
-    gq, gk, gv, back = cache["bufs"]
-    L = K.lib()
-    ws.barrier()                                       # the previous call's readers are done
-    for src, dst in ((q, gq), (k, gk), (v, gv)):
-        K._check(L.nx_comm_a2a_heads(K._p(src.contiguous()), C.byref(dst.table), C.c_int(B), C.c_int(Tl), C.c_int(H),
-                                     C.c_int(D), C.c_int(r), C.c_int(n), C.c_int(0), K._stream()), "nx_comm_a2a_heads")
-    ws.barrier()
-    shp = (B, n * Tl, Hl, D)
-    o, _ = K.attention_fwd(gq.local.view(shp), gk.local.view(shp), gv.local.view(shp), causal=causal)
-    K._check(L.nx_comm_a2a_heads(K._p(o), C.byref(back.table), C.c_int(B), C.c_int(Tl), C.c_int(H), C.c_int(D),
-                                 C.c_int(r), C.c_int(n), C.c_int(1), K._stream()), "nx_comm_a2a_heads")
-    ws.barrier()
-    return back.local.view(B, Tl, H, D).clone()
+    q [B, Tl, H, D], k / v [B, Tl, Hkv, D] BF16 with H and Hkv divisible by n.  Returns o [B, Tl, H, D];
+    differentiable (the backward sends dO the same way, runs the local backward kernels and returns dQ, dK, dV)."""
+    if q.shape[2] % ws.n or k.shape[2] % ws.n:
+        raise ValueError("ulysses_attention: heads and kv heads must be divisible by the group size")
+    return _UlyssesFn.apply(q, k, v, ws, causal)

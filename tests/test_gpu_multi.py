@@ -63,3 +63,20 @@ def test_expert_parallel_moe_decoder_matches_single_rank():
            "127.0.0.1", "--master-port", _free_port(), os.path.join(ROOT, "tests", "workers", "moe_ep_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=420, env=env)
     assert "WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("algorithm,layout", [("ring", "zigzag"), ("ring", "contiguous"), ("ulysses", "contiguous")])
+def test_context_parallel_lm_two_gpus_over_peer_memory(algorithm, layout):
+    """`ParallelLm` with cp = 2 on two GPUs: ring attention (the attention kernels read the other rank's K / V from
+    peer memory, dK / dV slots summed by their owners) or Ulysses (head <-> sequence exchange by peer stores) inside
+    every block, forward and backward.  The first loss equals the single-process model's on the same tokens and the
+    training steps that follow run."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", _free_port(), "-m", "nexus_b200.bench.parallel", "--model", "llama2-7b", "--layers", "2",
+           "--tp", "1", "--cp", "2", "--cp-algorithm", algorithm, "--cp-layout", layout, "--seq-len", "512",
+           "--global-batch", "2", "--micro-batch", "1", "--steps", "2", "--warmup", "1", "--check"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert r.returncode == 0 and '"check": "first loss"' in r.stdout and "tokens/s" in r.stdout, \
+        r.stdout[-3000:] + r.stderr[-3000:]
