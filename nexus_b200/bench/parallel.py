@@ -171,7 +171,8 @@ def main(argv=None) -> int:
             "metric": f"train tokens/s {args.model} tensor-parallel", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
             "n_gpus": world, "ms_per_step": ms, "steps": args.steps, "warmup": max(1, args.warmup),
             "config": {"model": args.model, "layers": cfg.n_layer, "tp": tp, "dp": dp, "cp": args.cp,
-                       "cp_attention": (f"{args.cp_algorithm}/{args.cp_layout}/{args.cp_comm}" if args.cp > 1 else None),
+                       "cp_attention": (f"{args.cp_algorithm}/{args.cp_layout}/" + ("peer memory" if plm._cp_ws is not None else "send_recv")
+                                        if args.cp > 1 else None),
                        "sp": bool(args.sp),
                        "seq_len": args.seq_len, "global_batch": args.global_batch, "micro_batch": args.micro_batch,
                        "linear_precision": args.precision, "compute_dtype": "bf16", "master": "fp32 AdamW, clip 1.0"},

@@ -565,6 +565,27 @@ extern "C" int nx_comm_allreduce_shard(const NxPeerTable* in, int in_dtype, int 
 }
 
 // ---------------------------------------------------------------------------------------------
+// All-gather by peer loads: out[q * shard + i] = shards[q][i] for every rank q (16-byte vectors; `shard` counts
+// vectors).  The FullShard engine gathers a unit's parameter shards with it before the unit's forward / backward.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gather_shards_kernel(NxPeerTable shards, int n, int64_t shard_vecs, uint4* __restrict__ out) {
+  const int64_t total = shard_vecs * n;
+  NX_GRID_STRIDE(i, total) {
+    const int q = static_cast<int>(i / shard_vecs);
+    out[i] = reinterpret_cast<const uint4*>(shards.ptr[q])[i - q * shard_vecs];
+  }
+}
+
+extern "C" int nx_comm_gather_shards(const NxPeerTable* shards, int n, int64_t shard_bytes, void* out, nx_stream_t stream) {
+  if (shards == nullptr || out == nullptr || n < 1 || n > NX_MAX_PEERS || shard_bytes < 0 || (shard_bytes & 15)) return -1;
+  if (shard_bytes == 0) return 0;
+  const int64_t vecs = shard_bytes / 16;
+  gather_shards_kernel<<<blocks_for(vecs * n, 256, 148 * 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      *shards, n, vecs, static_cast<uint4*>(out));
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
 // In-switch all-reduce (NVLS): `mc` is the multicast address of a symmetric buffer, i.e. one address that stands for
 // the same offset in every rank's copy.  `multimem.ld_reduce` makes NVSwitch read the 16 bytes from every rank and
 // return their sum (FP32 accumulation), `multimem.st` writes the result into every rank's copy: a rank moves its

@@ -45,6 +45,11 @@ int nx_comm_adamw_allgather(float* master, const float* grad, float* m, float* v
 int nx_comm_allreduce_shard(const NxPeerTable* in, int in_dtype, int n_in, const NxPeerTable* out, int out_dtype,
                             int n_out, int64_t shard_off, int64_t count, float scale, nx_stream_t stream);
 
+// All-gather by peer loads: out[q * shard_bytes + ...] = shards[q][0 .. shard_bytes) for q < n (shard_bytes a multiple of
+// 16; `out` local).  Bracket with nx_comm_barrier: the shards must be written before, and stay untouched until every
+// rank has read them.
+int nx_comm_gather_shards(const NxPeerTable* shards, int n, int64_t shard_bytes, void* out, nx_stream_t stream);
+
 // The same all-reduce done by NVSwitch (NVLS): `multicast_ptr` is the multicast address of a symmetric buffer (one
 // address for the same offset in every rank's copy; from the symmetric-memory rendezvous, null when the fabric has no
 // multicast).  The caller owns [shard_off, shard_off + count) elements (FP32: multiples of 4, BF16: of 8): the switch

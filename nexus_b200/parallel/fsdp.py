@@ -44,6 +44,9 @@ class FsdpOptions:
     mixed_precision: bool = False  # gather / reduce in BF16
     replica_group = None           # HSDP: process group across replicas
     nvme = None                    # NvmeStore for optimizer state offload
+    comm: str = "auto"             # "nccl": collectives of the process group; "fused": on GPUs a unit's shards are
+                                   # gathered by peer loads and its gradients reduce-scattered by an owner pull over
+                                   # symmetric memory (no NCCL call per unit); "auto": fused when that is available
 
 
 class _Unit:
@@ -76,6 +79,8 @@ class FsdpEngine:
         self.events: List[str] = []
         self.steps = 0
         self._build_units()
+        self._ws = None
+        self._setup_fused()
         group.barrier()
         for u in self.units:  # rank 0's initial values everywhere
             full = self._gather_master(u)
@@ -99,6 +104,31 @@ class FsdpEngine:
         if rest:
             self.units.insert(0, _Unit("root", rest, None, self.dp, self.rank))
 
+    def _setup_fused(self) -> None:
+        """Symmetric-memory plumbing of the fused form: one persistent shard slot per unit (1 / dp of the unit, in the
+        gather dtype) and two rotating full-size gradient buffers shared by all units."""
+        dev = self.units[0].master.device if self.units else torch.device("cpu")
+        want = self.o.comm
+        ok = dev.type == "cuda" and self.dp > 1 and hasattr(self.pg, "dist")      # a torch (NCCL) process group
+        if want == "nccl" or (want == "auto" and not ok):
+            return
+        if not ok:
+            raise ValueError("FsdpOptions.comm='fused' needs CUDA parameters and a torch process group")
+        from .symm import SymmetricWorkspace
+        self._ws = SymmetricWorkspace(self.pg)
+        self._gdt = torch.bfloat16 if self.o.mixed_precision else torch.float32
+        for u in self.units:
+            u.S8 = (u.S + 7) // 8 * 8                        # 16-byte vectors in both dtypes
+            u.shard_sym = self._ws.alloc(u.S8, self._gdt)
+            u.shard_sym.local.zero_()
+        big = max(u.S8 for u in self.units) * self.dp
+        self._gsym = [self._ws.alloc(big, self._gdt) for _ in range(2)]
+        self._gnext = 0
+        torch.cuda.synchronize()
+
+    def comm(self) -> str:
+        return "fused" if self._ws is not None else "nccl"
+
     def trace(self) -> List[str]:
         return list(self.events)
 
@@ -107,10 +137,29 @@ class FsdpEngine:
 
     # ---------------------------------------------------------------------------- gather / free
     def _gather_master(self, u: _Unit, dtype=torch.float32) -> torch.Tensor:
+        if self._ws is not None and dtype == self._gdt:
+            return self._gather_fused(u)
         src = u.master.to(dtype) if dtype != torch.float32 else u.master
         out = torch.empty(u.S * self.dp, dtype=dtype, device=src.device)
         self.pg.all_gather_tensor(out, src.contiguous())
         return out
+
+    def _gather_fused(self, u: _Unit) -> torch.Tensor:
+        """This rank's shard goes into its symmetric slot (cast to the gather dtype); after the barrier one kernel
+        reads every rank's slot over peer memory into the unit's full buffer."""
+        import ctypes as C
+        from ..ops import _cuda as K
+        ws = self._ws
+        u.shard_sym.local[: u.S].copy_(u.master)
+        ws.barrier()
+        full = torch.empty(u.S8 * self.dp, dtype=self._gdt, device=u.master.device)
+        K._check(K.lib().nx_comm_gather_shards(C.byref(u.shard_sym.table), C.c_int(self.dp),
+                                               C.c_int64(u.S8 * full.element_size()), K._p(full), K._stream()),
+                 "nx_comm_gather_shards")
+        ws.barrier()                                   # the slots may be rewritten
+        if u.S8 == u.S:
+            return full
+        return full.view(self.dp, u.S8)[:, : u.S].reshape(-1)
 
     def _unpack(self, u: _Unit, full: torch.Tensor) -> None:
         off = 0
@@ -179,8 +228,11 @@ class FsdpEngine:
             if p.grad is not None:
                 flat[off: off + n].copy_(p.grad.reshape(-1).to(dt))
             off += n
-        shard = torch.empty(u.S, dtype=dt, device=flat.device)
-        self.pg.reduce_scatter_tensor(shard, flat, "sum")
+        if self._ws is not None:
+            shard = self._reduce_fused(u, flat)
+        else:
+            shard = torch.empty(u.S, dtype=dt, device=flat.device)
+            self.pg.reduce_scatter_tensor(shard, flat, "sum")
         if self.o.replica_group is not None:
             self.o.replica_group.all_reduce_tensor(shard, "sum")
         u.grad_shard.add_(shard.float())
@@ -188,6 +240,30 @@ class FsdpEngine:
             p.grad = None
         if u.module is not None:
             self._release(u)
+
+    def _reduce_fused(self, u: _Unit, flat: torch.Tensor) -> torch.Tensor:
+        """Reduce-scatter by owner pull: the unit's flat gradients go into one of two rotating symmetric buffers, and
+        after the barrier this rank sums its own shard range over every rank's buffer (rank order, FP32 math)."""
+        import ctypes as C
+        from ..ops import _cuda as K
+        from .symm import _table
+        ws = self._ws
+        g = self._gsym[self._gnext]
+        self._gnext ^= 1
+        ws.barrier()                                   # the readers of this buffer's previous use are done
+        g.local[: flat.numel()].copy_(flat)
+        ws.barrier()                                   # every rank's gradients are in place
+        lo = self.rank * u.S
+        # the kernel works on multiples of 8 elements: widen the range to the enclosing aligned window and cut
+        a0 = lo // 8 * 8
+        cnt = min(((lo + u.S + 7) // 8 * 8), (flat.numel() + 7) // 8 * 8) - a0
+        win = torch.zeros(cnt, dtype=self._gdt, device=flat.device)
+        own = _table([win.data_ptr() - a0 * win.element_size()])   # the kernel indexes outputs by global offset
+        K._check(K.lib().nx_comm_allreduce_shard(C.byref(g.table), C.c_int(K._DT[self._gdt]), C.c_int(self.dp),
+                                                 C.byref(own), C.c_int(K._DT[self._gdt]), C.c_int(1),
+                                                 C.c_int64(a0), C.c_int64(cnt), C.c_float(1.0), K._stream()),
+                 "nx_comm_allreduce_shard")
+        return win[lo - a0: lo - a0 + u.S]
 
     # ------------------------------------------------------------------------------------- step
     def forward_backward(self, loss_fn: Callable[[], torch.Tensor], weight: float, sync: bool = True) -> torch.Tensor:

@@ -198,7 +198,7 @@ class ParallelLm:
         # context parallelism on GPUs: symmetric workspace over the cp group for the peer-memory attention paths
         self._cp_ws = None
         if cfg.cp > 1 and self.device.type == "cuda" and cfg.cp_comm == "fused" and mc.window <= 0 and \
-                self.cd == torch.bfloat16 and getattr(self.cp_g, "group", None) is not None:
+                self.cd == torch.bfloat16 and hasattr(self.cp_g, "dist"):      # a torch (NCCL) process group
             from .symm import SymmetricWorkspace
             self._cp_ws = SymmetricWorkspace(self.cp_g)
         # embedding group {first, last} pipeline stage for the tied weight

@@ -80,3 +80,14 @@ def test_context_parallel_lm_two_gpus_over_peer_memory(algorithm, layout):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert r.returncode == 0 and '"check": "first loss"' in r.stdout and "tokens/s" in r.stdout, \
         r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_full_shard_fsdp_two_gpus_fused_and_nccl_forms():
+    """FullShard (stage 3) of the unit FSDP engine on two GPUs: parameter shards gathered by peer loads, gradients
+    reduce-scattered by owner pull over symmetric memory, against the NCCL form and a single process."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", _free_port(), os.path.join(ROOT, "tests", "workers", "fsdp_gpu_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=420, env=env)
+    assert "WORKER_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
