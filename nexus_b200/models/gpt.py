@@ -15,6 +15,7 @@ Weights are stored [out, in] here (the reference stores [in, out]); archives tra
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
 
@@ -150,6 +151,10 @@ class GptModel:
         self._acts_key = None
         self.step_count = 0
         self.backward_hook = None     # callable(stage): see set_backward_hook
+        # the bias-gradient column sums of fc / qkv are bandwidth-bound side work: they run on a second stream under the
+        # two GEMMs that follow them (NEXUS_B200_OVERLAP_COLSUM=0 keeps them in line)
+        self.overlap_colsum = os.environ.get("NEXUS_B200_OVERLAP_COLSUM", "1") != "0" and torch.device(device).type == "cuda"
+        self._side = None
         self.deterministic_embedding = False
         self.init_weights(config.seed if seed is None else seed)
 
@@ -366,6 +371,30 @@ class GptModel:
         if hook is not None:
             hook(self.STAGE_HEAD)
         S = self._slots
+        side = None
+        if self.overlap_colsum:
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=self.device)
+                self._side_evt = [torch.cuda.Event() for _ in range(4)]   # fork / join, for dfch and dqkv
+            side = self._side
+        main = torch.cuda.current_stream() if side is not None else None
+        pending = [False, False]      # a column sum of dfch / dqkv is still running on the side stream
+
+        def side_colsum(which, src, dst):
+            """Column sums of ``src`` into ``dst`` on the side stream, ordered after what the main stream has enqueued."""
+            fork = self._side_evt[2 * which]
+            fork.record(main)
+            side.wait_event(fork)
+            with torch.cuda.stream(side):
+                K.colsum(src, out=dst, accumulate=True)
+                self._side_evt[2 * which + 1].record(side)
+            pending[which] = True
+
+        def side_join(which):
+            """The main stream waits for the side stream's last use of dfch / dqkv (before the buffer is overwritten)."""
+            if side is not None and pending[which]:
+                main.wait_event(self._side_evt[2 * which + 1])
+                pending[which] = False
         for l in range(L - 1, -1, -1):
             x_in, x_mid = res[2 * l], res[2 * l + 1]
             mode = self.layer_mode(l)
@@ -374,11 +403,15 @@ class GptModel:
             ln1_l, qkv_l, atty_l, lse_l = (a[k][S[k][l]] for k in ("ln1", "qkv", "atty", "lse"))
             ln2_l, fch_pre_l, fch_l = (a[k][S[k][l]] for k in ("ln2", "fch_pre", "fch"))
             # ---- MLP
+            side_join(0)
             K.gemm(dres_lp, w["fcproj_w"][l], b_mn=True, act="dgelu", aux_in=fch_pre_l, out=a["dfch"])
             K.gemm(dres_lp, fch_l, a_mn=True, b_mn=True, out=g["fcproj_w"][l], accumulate=True, split_k=0)
             K.gemm(a["dfch"], w["fc_w"][l], b_mn=True, out=a["dln"])
             K.gemm(a["dfch"], ln2_l, a_mn=True, b_mn=True, out=g["fc_w"][l], accumulate=True, split_k=0)
-            K.colsum(a["dfch"], out=g["fc_b"][l], accumulate=True)
+            if side is not None:
+                side_colsum(0, a["dfch"], g["fc_b"][l])
+            else:
+                K.colsum(a["dfch"], out=g["fc_b"][l], accumulate=True)
             K.norm_bwd(a["dln"], x_mid, self.p["ln2_w"][l], a["ln2_mean"][l], a["ln2_rstd"][l], add=dres,
                        dx=dres_other, dx_lp=dres_lp, dgamma=g["ln2_w"][l], dbeta=g["ln2_b"][l], accumulate_params=True,
                        dx_colsum=g["attproj_b"][l])
@@ -388,18 +421,26 @@ class GptModel:
             K.gemm(dres_lp, atty_l.view(N, C), a_mn=True, b_mn=True, out=g["attproj_w"][l], accumulate=True,
                    split_k=0)
             qkv, dqkv = qkv_l, a["dqkv"]
+            side_join(1)
             K.attention_bwd(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], atty_l, lse_l, a["datty"],
                             causal=True, dq=dqkv[:, :, 0], dk=dqkv[:, :, 1], dv=dqkv[:, :, 2])
             dq2 = dqkv.view(N, 3 * C)
             K.gemm(dq2, w["qkv_w"][l], b_mn=True, out=a["dln"])
             K.gemm(dq2, ln1_l, a_mn=True, b_mn=True, out=g["qkv_w"][l], accumulate=True, split_k=0)
-            K.colsum(dq2, out=g["qkv_b"][l], accumulate=True)
+            if side is not None:
+                side_colsum(1, dq2, g["qkv_b"][l])
+            else:
+                K.colsum(dq2, out=g["qkv_b"][l], accumulate=True)
             K.norm_bwd(a["dln"], x_in, self.p["ln1_w"][l], a["ln1_mean"][l], a["ln1_rstd"][l], add=dres,
                        dx=dres_other, dx_lp=dres_lp, dgamma=g["ln1_w"][l], dbeta=g["ln1_b"][l], accumulate_params=True,
                        dx_colsum=g["fcproj_b"][l - 1] if l > 0 else None)
             dres, dres_other = dres_other, dres
             if hook is not None:
+                side_join(0)          # the stage's bias gradients are complete before the hook looks at them
+                side_join(1)
                 hook(l)
+        side_join(0)
+        side_join(1)
         K.embedding_bwd(tokens, dres.view(B, T, C), g["wte"], g["wpe"][:T], B, T,
                         deterministic=self.deterministic_embedding)
         if hook is not None:
