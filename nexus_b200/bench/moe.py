@@ -32,9 +32,13 @@ def main(argv=None) -> int:
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--capacity-factor", type=float, default=1.25)
     ap.add_argument("--aux", type=float, default=0.01)
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
+                    help="row exchange of the expert-parallel layers: peer-memory dispatch / combine kernels, or NCCL "
+                         "variable-split all-to-alls (the same-box comparison)")
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=2)
     args = ap.parse_args(argv)
+    os.environ["NEXUS_B200_EP_COMM"] = args.comm
 
     from ..lm.config import LmConfig
     from ..models.gpt import AdamWConfig
@@ -94,7 +98,8 @@ def main(argv=None) -> int:
                        "seqs_per_gpu": args.seqs_per_gpu, "micro_batch": args.micro_batch, "ep": world,
                        "capacity_factor": args.capacity_factor, "capacity_rows_per_expert": model.ep.capacity,
                        "aux_alpha": args.aux, "dtype": "bf16", "master": "fp32 AdamW, clip 1.0",
-                       "dispatch": "peer-memory kernels (nx_moe_dispatch / nx_moe_combine)"},
+                       "dispatch": ("peer-memory kernels (nx_moe_dispatch / nx_moe_combine)" if args.comm == "fused"
+                                    else "NCCL all_to_all_single with per-rank splits")},
             "losses": [[round(float(v), 4) for v in l.cpu()] for l in losses],
             "kernel_launches_per_step": (K.launch_count - launches0) // max(args.steps, 1),
             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 2),

@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from typing import Optional
 
 import torch
@@ -38,8 +39,13 @@ class EpContext:
     symmetric workspace (barrier).  One context serves every MoE layer of a model (layers run one after the other)."""
 
     def __init__(self, pg, experts: int, d_model: int, tokens_per_rank: int, top_k: int, capacity_factor: float,
-                 device, min_capacity: int = 8):
+                 device, min_capacity: int = 8, comm: Optional[str] = None):
         self.pg = pg
+        # "fused": rows move by the peer-memory dispatch / combine kernels; "nccl": the same routing and slots, rows
+        # exchanged with variable-split all-to-alls (the library form, kept as the same-box comparison)
+        self.comm = comm or os.environ.get("NEXUS_B200_EP_COMM", "fused")
+        if self.comm not in ("fused", "nccl"):
+            raise ValueError("EpContext.comm must be 'fused' or 'nccl'")
         self.n = pg.size() if pg is not None else 1
         self.rank = pg.rank() if pg is not None else 0
         if experts % self.n:
@@ -50,7 +56,13 @@ class EpContext:
         self.capacity = (cap + 7) // 8 * 8
         self.device = torch.device(device)
         numel = self.le * self.capacity * d_model
-        if self.n > 1:
+        if self.n > 1 and self.comm == "nccl":
+            from ..parallel.symm import SymmetricWorkspace
+            self.ws = SymmetricWorkspace(pg)             # the trainer's gradient reductions still use it
+            self.in_local = torch.zeros(numel, dtype=torch.bfloat16, device=self.device)
+            self.out_local = torch.zeros(numel, dtype=torch.bfloat16, device=self.device)
+            self.in_table = self.out_table = None
+        elif self.n > 1:
             from ..parallel.symm import SymmetricWorkspace
             self.ws = SymmetricWorkspace(pg)
             self.inbuf = self.ws.alloc(numel, torch.bfloat16)
@@ -115,6 +127,100 @@ def route_global(ctx: EpContext, logits: torch.Tensor):
         total = counts
     slot = torch.where(slot < ctx.capacity, slot, torch.full_like(slot, -1))
     return expert, gate, slot.contiguous(), total
+
+
+class _A2aPlan:
+    """Row exchange of one routing decision through NCCL all-to-alls: which (token, choice) rows go to which rank, in
+    (destination rank, expert, slot) order, and where the rows this rank receives sit in its capacity buffer."""
+
+    def __init__(self, ep: EpContext, expert: torch.Tensor, slot: torch.Tensor):
+        import torch.distributed as dist
+        self.ep, self.dist = ep, dist
+        n, le, cap = ep.n, ep.le, ep.capacity
+        flat_e, flat_s = expert.reshape(-1).long(), slot.reshape(-1).long()
+        keep = flat_s >= 0
+        key = torch.where(keep, flat_e * cap + flat_s, torch.full_like(flat_e, ep.E * cap))
+        order = torch.argsort(key, stable=True)
+        self.nkeep = int(keep.sum())
+        self.rows = order[: self.nkeep]                               # flat (token * k + choice) indices, sorted
+        self.pos = key[self.rows]                                     # global (expert * cap + slot)
+        dst = self.pos // (le * cap)
+        send = torch.bincount(dst, minlength=n).to(torch.int64)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=ep.pg.group)
+        self.send, self.recv = [int(v) for v in send.cpu()], [int(v) for v in recv.cpu()]
+        self.nrecv = sum(self.recv)
+        meta = (self.pos - dst * (le * cap)).to(torch.int64)          # position inside the owner's buffer
+        self.rpos = torch.empty(self.nrecv, dtype=torch.int64, device=expert.device)
+        dist.all_to_all_single(self.rpos, meta, self.recv, self.send, group=ep.pg.group)
+
+    def to_owners(self, rows: torch.Tensor, buf: torch.Tensor) -> None:
+        """rows [nkeep, d] (in plan order) -> every owner's capacity buffer ``buf`` [le * cap, d] (zeroed first)."""
+        got = torch.empty((self.nrecv, rows.shape[1]), dtype=rows.dtype, device=rows.device)
+        self.dist.all_to_all_single(got, rows.contiguous(), self.recv, self.send, group=self.ep.pg.group)
+        buf.zero_()
+        buf.index_copy_(0, self.rpos, got)
+
+    def from_owners(self, buf: torch.Tensor) -> torch.Tensor:
+        """The rows of ``buf`` [le * cap, d] that belong to this rank's assignments, back in plan order [nkeep, d]."""
+        back = buf.index_select(0, self.rpos)
+        out = torch.empty((self.nkeep, buf.shape[1]), dtype=buf.dtype, device=buf.device)
+        self.dist.all_to_all_single(out, back, self.send, self.recv, group=self.ep.pg.group)
+        return out
+
+
+class _MoeEpNcclFn(torch.autograd.Function):
+    """The layer of `_MoeEpFn` with the row movement done by NCCL all-to-alls (same routing, slots, expert GEMMs)."""
+
+    @staticmethod
+    def forward(ctx, x, logits, up, down, ep: EpContext):
+        le, cap, d, k = ep.le, ep.capacity, ep.d, ep.k
+        F2 = up.shape[1]
+        expert, gate, slot, total = route_global(ep, logits.detach())
+        plan = _A2aPlan(ep, expert, slot)
+        tok = plan.rows // k
+        inb = ep.in_local.view(le * cap, d)
+        plan.to_owners(x.index_select(0, tok), inb)
+        buf = ep.view(ep.in_local).clone()
+        h = K.gemm(buf, up)
+        act = I.gated_fwd(h.view(le * cap, F2), "silu").view(le, cap, F2 // 2)
+        K.gemm(act, down, out=ep.view(ep.out_local))
+        rows_out = plan.from_owners(ep.out_local.view(le * cap, d))              # [nkeep, d] expert outputs of my rows
+        g = gate.reshape(-1)[plan.rows].to(torch.float32)
+        y = torch.zeros((x.shape[0], d), dtype=torch.float32, device=x.device)
+        y.index_add_(0, tok, rows_out.float() * g[:, None])
+        ctx.ep, ctx.plan = ep, plan
+        ctx.save_for_backward(x, up, down, expert, gate, buf, h, act, rows_out)
+        ctx.mark_non_differentiable(total)
+        return y.to(torch.bfloat16), total
+
+    @staticmethod
+    def backward(ctx, dy, _t):
+        x, up, down, expert, gate, buf, h, act, rows_out = ctx.saved_tensors
+        ep, plan = ctx.ep, ctx.plan
+        le, cap, d, k = ep.le, ep.capacity, ep.d, ep.k
+        N, F2 = x.shape[0], up.shape[1]
+        dy = dy.contiguous().to(torch.bfloat16)
+        tok = plan.rows // k
+        dyr = dy.index_select(0, tok)
+        dgate = torch.zeros(N * k, dtype=torch.float32, device=x.device)
+        dgate[plan.rows] = (dyr.float() * rows_out.float()).sum(-1)
+        dgate = dgate.view(N, k)
+        g = gate.reshape(-1)[plan.rows].to(torch.float32)
+        plan.to_owners((dyr.float() * g[:, None]).to(torch.bfloat16), ep.in_local.view(le * cap, d))
+        dout = ep.view(ep.in_local)
+        dact = K.gemm(dout, down, b_mn=True)
+        ddown = K.gemm(dout, act, a_mn=True, b_mn=True, out_dtype=torch.float32)
+        dh = I.gated_bwd(h.view(le * cap, F2), dact.view(le * cap, F2 // 2), "silu").view(le, cap, F2)
+        K.gemm(dh, up, b_mn=True, out=ep.view(ep.out_local))
+        dup = K.gemm(dh, buf, a_mn=True, b_mn=True, out_dtype=torch.float32)
+        dxr = plan.from_owners(ep.out_local.view(le * cap, d))
+        dx = torch.zeros((N, d), dtype=torch.float32, device=x.device)
+        dx.index_add_(0, tok, dxr.float())
+        inner = (gate * dgate).sum(-1, keepdim=True)
+        dsel = gate * (dgate - inner)
+        dlogits = torch.zeros((N, ep.E), dtype=torch.float32, device=x.device).scatter_add_(1, expert.long(), dsel)
+        return dx.to(torch.bfloat16), dlogits, dup.to(up.dtype), ddown.to(down.dtype), None
 
 
 class _MoeEpFn(torch.autograd.Function):
@@ -199,7 +305,8 @@ class MoeEpLayer(torch.nn.Module):
     def forward(self, x: torch.Tensor):
         ep = self.ep
         logits = x.float() @ self.router.float().t()
-        y, total = _MoeEpFn.apply(x, logits, self.up, self.down, ep)
+        fn = _MoeEpNcclFn if (ep.comm == "nccl" and ep.n > 1) else _MoeEpFn
+        y, total = fn.apply(x, logits, self.up, self.down, ep)
         self.last_counts = total
         probs = torch.softmax(logits, dim=-1).mean(0)                       # P_e over this rank's tokens
         frac = total.float() / max(float(x.shape[0] * ep.n * ep.k), 1.0)    # f_e over all ranks (no gradient)

@@ -55,10 +55,12 @@ def test_tensor_parallel_llama_on_fused_kernels_matches_single_rank():
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_expert_parallel_moe_decoder_matches_single_rank():
-    """`models.moe_ep` over 2 GPUs (experts split over the ranks, rows dispatched / combined through peer memory,
-    fused all-reduce of the replicated gradients) against one rank holding all experts and sequences."""
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+@pytest.mark.parametrize("comm", ["fused", "nccl"])
+def test_expert_parallel_moe_decoder_matches_single_rank(comm):
+    """`models.moe_ep` over 2 GPUs (experts split over the ranks, rows dispatched / combined through peer memory, or
+    exchanged with NCCL all-to-alls in the comparison form; fused all-reduce of the replicated gradients) against one
+    rank holding all experts and sequences."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT, NEXUS_B200_EP_COMM=comm)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", _free_port(), os.path.join(ROOT, "tests", "workers", "moe_ep_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=420, env=env)
