@@ -1,5 +1,5 @@
 // `nexus_b200._native`: the host-side native runtime (archive codecs, checksums, allocator and
-// planner, profiler, CPU oracles, environments).  Each translation unit registers its own bindings.
+// planner, profiler, CPU oracles, environments, the rendezvous store and the watchdog scan).  Each translation unit registers its own bindings.
 #include <pybind11/pybind11.h>
 
 namespace py = pybind11;
@@ -10,6 +10,7 @@ void bind_runtime(py::module_& m);
 void bind_cpu_kernels(py::module_& m);
 void bind_envs(py::module_& m);
 void bind_device_allocator(py::module_& m);
+void bind_store(py::module_& m);
 
 PYBIND11_MODULE(_native, m) {
   m.doc() = "nexus_b200 native host runtime";
@@ -19,4 +20,5 @@ PYBIND11_MODULE(_native, m) {
   bind_cpu_kernels(m);
   bind_envs(m);
   bind_device_allocator(m);
+  bind_store(m);
 }

@@ -7,7 +7,6 @@ Parity: include/nexus/dist/watchdog.hpp:37-125 and src/dist/watchdog.cpp of the 
 from __future__ import annotations
 
 import json
-import statistics
 import threading
 import time
 from dataclasses import dataclass, field
@@ -94,32 +93,14 @@ class Watchdog:
             self.on_event(ev)
 
     def check_once(self, now: Optional[float] = None) -> None:
+        """One pass over the board; the comparison of the ranks' heartbeats is native (`_native.watchdog_scan`)."""
+        from .. import _native
         now = time.time() if now is None else now
-        recs = {r: self.board.read(r) for r in range(self.world)}
-        live = {r: v for r, v in recs.items() if v is not None}
-        if not live:
-            return
-        leader = max(v["step"] for v in live.values())
-        for r in range(self.world):
-            v = recs.get(r)
-            last_t = v["t"] if v else None
-            step = v["step"] if v else -1
-            if step < leader and (last_t is None or now - last_t > self.o.stall_timeout_s):
-                self._emit(WatchdogEvent("stalled", r, step, now - (last_t or now)))
-        for r, v in live.items():
-            self._arrivals.setdefault(v["step"], {})[r] = v["t"]
-        for step, arr in sorted(self._arrivals.items()):
-            if len(arr) < self.world:
-                continue
-            first = min(arr.values())
-            durations = [x["ms"] / 1e3 for x in live.values() if x["ms"] > 0]
-            med = statistics.median(durations) if durations else 0.0
-            thr = max(self.o.min_lag_s, self.o.straggler_fraction * med)
-            for r, t in arr.items():
-                if t - first > thr:
-                    self._emit(WatchdogEvent("straggler", r, step, t - first))
-        for step in sorted(self._arrivals)[: max(0, len(self._arrivals) - self.o.window)]:
-            del self._arrivals[step]
+        recs = [self.board.read(r) for r in range(self.world)]
+        for kind, rank, step, detail in _native.watchdog_scan(recs, float(now), float(self.o.stall_timeout_s),
+                                                              float(self.o.straggler_fraction), float(self.o.min_lag_s),
+                                                              self._arrivals, int(self.o.window)):
+            self._emit(WatchdogEvent(kind, int(rank), int(step), float(detail)))
 
     def _loop(self) -> None:
         while not self._stop.wait(self.o.poll_s):
