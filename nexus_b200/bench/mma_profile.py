@@ -52,16 +52,16 @@ def main() -> int:
         K.gemm(a, b, bias=bias)
         e1.record()
         torch.cuda.synchronize()
-        buf = (C.c_longlong * (148 * 8))()
+        buf = (C.c_longlong * (256 * 8))()
         lib.nx_gemm_prof_read(buf)
-        r = np.array(buf[:], dtype=np.int64).reshape(148, 8)
+        r = np.array(buf[:], dtype=np.int64).reshape(256, 8)
         r = r[r[:, 4] > 0]
         tot, acc, tma, issue, nkb, nt = (r[:, i].mean() for i in range(6))
         print(f"{m}x{n}x{k}: {e0.elapsed_time(e1) * 1e3:8.1f} us | accumulator wait {acc / tot * 100:4.1f} % | "
               f"TMA wait {tma / tot * 100:4.1f} % | issue-to-commit {issue / tot * 100:4.1f} % | "
               f"{tot / nkb:6.0f} cycles per k-block ({nt:.1f} tiles, {nkb:.0f} k-blocks per CTA)", flush=True)
         lib.nx_gemm_prof_read_epilogue(buf)
-        e = np.array(buf[:], dtype=np.int64).reshape(148, 8)
+        e = np.array(buf[:], dtype=np.int64).reshape(256, 8)
         e = e[e[:, 3] > 0]
         busy, ld, slot, tiles, bias_c, stage, fence, issue = (e[:, i].sum() for i in range(8))
         print(f"    first epilogue warp: {busy / tiles:6.0f} cycles per tile, of which TMEM-load wait {ld / tiles:5.0f}, "

@@ -242,8 +242,10 @@ __device__ __forceinline__ void load_any32(const void* base, int dtype, int64_t 
 // Profiling build only (-DNX_PROFILE_MMA): per CTA, cycles the MMA-issuing thread spent in total, waiting for a
 // free accumulator, waiting for TMA data, and between a stage's arrival and the commit of its MMAs (which blocks
 // while the tensor-core queue is full), plus k-block and tile counts.  Read back with nx_gemm_prof_read.
-__device__ long long g_mma_prof[148 * 8];
-__device__ long long g_epi_prof[148 * 8];  // first epilogue warp: busy cycles per tile, TMEM-load wait, store-slot wait, tiles
+// counters of the profiling build: one row of 8 per CTA (or CTA pair), for grids of up to kProfRows CTAs
+constexpr int kProfRows = 256;
+__device__ long long g_mma_prof[kProfRows * 8];
+__device__ long long g_epi_prof[kProfRows * 8];  // first epilogue warp: busy cycles per tile, TMEM-load wait, store-slot wait, tiles
 #define NX_PROF(x) x
 #else
 #define NX_PROF(x)
@@ -683,7 +685,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           acc_phase ^= 1u;
         }
       }
-      NX_PROF(if (blockIdx.x < 148 && leader) {
+      NX_PROF(if (blockIdx.x < kProfRows && leader) {
         long long* o = g_mma_prof + (PAIR ? blockIdx.x >> 1 : blockIdx.x) * 8;
         o[0] = clock64() - t_begin; o[1] = t_acc; o[2] = t_tma; o[3] = t_issue; o[4] = n_kb; o[5] = n_tiles;
       })
@@ -1093,7 +1095,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         acc_phase ^= 1u;
       }
     }
-    NX_PROF(if (warp == 2 && lane == 0 && blockIdx.x < 148) {
+    NX_PROF(if (warp == 2 && lane == 0 && blockIdx.x < kProfRows) {
       long long* o = g_epi_prof + blockIdx.x * 8;
       o[0] = e_busy; o[1] = e_ld; o[2] = e_slot; o[3] = e_tiles;
       o[4] = e_bias; o[5] = e_stage; o[6] = e_fence; o[7] = e_issue;
@@ -1596,9 +1598,9 @@ extern "C" int nx_gemm_dist(const NxGemmArgs* a, const NxGemmDist* d, nx_stream_
 
 #ifdef NX_PROFILE_MMA
 extern "C" int nx_gemm_prof_read(long long* out) {
-  return cudaMemcpyFromSymbol(out, g_mma_prof, sizeof(long long) * 148 * 8) == cudaSuccess ? 0 : -1;
+  return cudaMemcpyFromSymbol(out, g_mma_prof, sizeof(long long) * kProfRows * 8) == cudaSuccess ? 0 : -1;
 }
 extern "C" int nx_gemm_prof_read_epilogue(long long* out) {
-  return cudaMemcpyFromSymbol(out, g_epi_prof, sizeof(long long) * 148 * 8) == cudaSuccess ? 0 : -1;
+  return cudaMemcpyFromSymbol(out, g_epi_prof, sizeof(long long) * kProfRows * 8) == cudaSuccess ? 0 : -1;
 }
 #endif

@@ -68,6 +68,13 @@ int nx_cross_entropy_shifted(void* logits, int logits_dtype, const int32_t* toke
                              float* row_loss, void* ce_state, float* loss_out, float loss_weight,
                              int accumulate_loss, int64_t rows, int seq_len, int vocab, int64_t ld, int ignore_index,
                              float smoothing, float z_loss, float grad_scale, int write_grad, nx_stream_t stream);
+// The same with a second, device-resident gradient multiplier (`grad_scale_dev`, may be null): the dynamic loss scale
+// of the optimizer state, read on the device so that a captured step follows its changes.
+int nx_cross_entropy_shifted_scaled(void* logits, int logits_dtype, const int32_t* tokens, const int32_t* targets,
+                                    float* row_loss, void* ce_state, float* loss_out, float loss_weight,
+                                    int accumulate_loss, int64_t rows, int seq_len, int vocab, int64_t ld,
+                                    int ignore_index, float smoothing, float z_loss, float grad_scale,
+                                    const float* grad_scale_dev, int write_grad, nx_stream_t stream);
 
 // ---- dropout / rng -----------------------------------------------------------------------------
 int nx_dropout(const void* in, void* out, int dtype, int64_t n, float p, uint64_t seed, uint64_t offset,

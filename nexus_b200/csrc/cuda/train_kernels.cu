@@ -84,6 +84,7 @@ struct CeState {        // device-resident, 4 floats + 2 ints
   float loss;           // mean loss over valid targets
   int valid;            // number of valid targets
   int bad_target;       // 1 when a target is outside [0, vocab) and is not ignore_index
+  float grad_mul;       // device-resident multiplier of the gradient (dynamic loss scale), 1 when none is given
 };
 
 __device__ __forceinline__ int ce_target(const int32_t* tokens, const int32_t* targets, int64_t row, int seq_len) {
@@ -93,7 +94,8 @@ __device__ __forceinline__ int ce_target(const int32_t* tokens, const int32_t* t
 }
 
 __global__ void ce_count_kernel(const int32_t* __restrict__ tokens, const int32_t* __restrict__ targets,
-                                int64_t rows, int seq_len, int vocab, int ignore_index, CeState* st) {
+                                int64_t rows, int seq_len, int vocab, int ignore_index, CeState* st,
+                                const float* __restrict__ grad_mul) {
   __shared__ int s_scratch[32];
   int count = 0, bad = 0;
   for (int64_t r = threadIdx.x; r < rows; r += blockDim.x) {
@@ -108,6 +110,7 @@ __global__ void ce_count_kernel(const int32_t* __restrict__ tokens, const int32_
     st->valid = count;
     st->inv_valid = count > 0 ? 1.0f / static_cast<float>(count) : 0.0f;
     st->bad_target = bad ? 1 : 0;
+    st->grad_mul = grad_mul != nullptr ? *grad_mul : 1.0f;
   }
 }
 
@@ -151,7 +154,7 @@ __global__ void ce_row_kernel(LT* __restrict__ logits, const int32_t* __restrict
   if (threadIdx.x == 0) row_loss[row] = loss;
   if (!write_grad) return;
   __syncthreads();  // every thread has read lr[tg] before anyone overwrites it
-  const float k = grad_scale * st->inv_valid;
+  const float k = grad_scale * st->inv_valid * st->grad_mul;
   const float pz = 1.0f + 2.0f * z_loss * lse;
   const float sv = smoothing / vocab;
   for (int c = threadIdx.x; c < vocab; c += blockDim.x) {
@@ -278,7 +281,7 @@ __global__ void __launch_bounds__(512) ce_row_vec_kernel(LT* __restrict__ logits
   if (threadIdx.x == 0) row_loss[row] = loss;
   if (!write_grad) return;
   __syncthreads();  // every thread has read lr[tg] before anyone overwrites it
-  const float k = grad_scale * st->inv_valid;
+  const float k = grad_scale * st->inv_valid * st->grad_mul;
   const float pz = (1.0f + 2.0f * z_loss * lse) * k;
   const float sv = smoothing / vocab * k;
   const float onehot = (1.0f - smoothing) * k;
@@ -439,8 +442,14 @@ template <typename GT, typename ST>
 __global__ void adamw_kernel(float* __restrict__ master, const GT* __restrict__ grad, float* __restrict__ m,
                              float* __restrict__ v, ST* __restrict__ shadow, const NxAdamChunk* __restrict__ chunks,
                              const NxOptState* __restrict__ st, int zero_grad, uint64_t sr_seed) {
-  if (st->found_inf) return;
   const NxAdamChunk ch = chunks[blockIdx.x];
+  if (st->found_inf) {  // skipped step: the weights stay, the (non-finite) gradients still go
+    if (zero_grad) {
+      GT* gw = const_cast<GT*>(grad);
+      for (int64_t i = ch.offset + threadIdx.x; i < ch.offset + ch.count; i += blockDim.x) Num<GT>::store(gw + i, 0.0f);
+    }
+    return;
+  }
   const float lr = __fmul_rn(st->lr, ch.lr_scale);
   const float wd = __fmul_rn(st->weight_decay, ch.wd_scale);
   const float b1 = st->beta1, b2 = st->beta2, omb1 = __fsub_rn(1.0f, b1), omb2 = __fsub_rn(1.0f, b2);
@@ -669,15 +678,33 @@ extern "C" int nx_embedding_bwd(const int32_t* tokens, const int32_t* sorted_tok
 
 extern "C" size_t nx_ce_state_bytes(void) { return sizeof(CeState); }
 
+extern "C" int nx_cross_entropy_shifted_scaled(void* logits, int logits_dtype, const int32_t* tokens,
+                                               const int32_t* targets, float* row_loss, void* ce_state, float* loss_out,
+                                               float loss_weight, int accumulate_loss, int64_t rows, int seq_len,
+                                               int vocab, int64_t ld, int ignore_index, float smoothing, float z_loss,
+                                               float grad_scale, const float* grad_scale_dev, int write_grad,
+                                               nx_stream_t stream);
+
 extern "C" int nx_cross_entropy_shifted(void* logits, int logits_dtype, const int32_t* tokens,
                                         const int32_t* targets, float* row_loss, void* ce_state, float* loss_out,
                                         float loss_weight, int accumulate_loss, int64_t rows, int seq_len, int vocab,
                                         int64_t ld, int ignore_index, float smoothing, float z_loss, float grad_scale,
                                         int write_grad, nx_stream_t stream) {
+  return nx_cross_entropy_shifted_scaled(logits, logits_dtype, tokens, targets, row_loss, ce_state, loss_out, loss_weight,
+                                         accumulate_loss, rows, seq_len, vocab, ld, ignore_index, smoothing, z_loss,
+                                         grad_scale, nullptr, write_grad, stream);
+}
+
+extern "C" int nx_cross_entropy_shifted_scaled(void* logits, int logits_dtype, const int32_t* tokens,
+                                               const int32_t* targets, float* row_loss, void* ce_state, float* loss_out,
+                                               float loss_weight, int accumulate_loss, int64_t rows, int seq_len,
+                                               int vocab, int64_t ld, int ignore_index, float smoothing, float z_loss,
+                                               float grad_scale, const float* grad_scale_dev, int write_grad,
+                                               nx_stream_t stream) {
   if (rows <= 0 || vocab <= 0 || ld < vocab || seq_len <= 0) return -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CeState* cs = static_cast<CeState*>(ce_state);
-  ce_count_kernel<<<1, 1024, 0, st>>>(tokens, targets, rows, seq_len, vocab, ignore_index, cs);
+  ce_count_kernel<<<1, 1024, 0, st>>>(tokens, targets, rows, seq_len, vocab, ignore_index, cs, grad_scale_dev);
   const bool aligned = (reinterpret_cast<uintptr_t>(logits) & 15) == 0;
   if (logits_dtype == NX_F32 && aligned && (ld % 4) == 0)
     ce_row_vec_kernel<float><<<static_cast<unsigned>(rows), 512, 0, st>>>((float*)logits, tokens, targets, row_loss, rows, seq_len, vocab, ld, ignore_index, smoothing, z_loss, grad_scale, cs, write_grad);

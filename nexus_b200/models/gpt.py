@@ -52,7 +52,8 @@ class GptModel:
 
     def __init__(self, config: LmConfig, device="cuda", seed: Optional[int] = None, vocab_pad: int = 128,
                  recompute: str = "none", recompute_every: int = 2, optimizer: str = "adamw", master: str = "fp32",
-                 compute_dtype: str = "bf16", offload_grad_dtype: str = "bf16"):
+                 compute_dtype: str = "bf16", offload_grad_dtype: str = "bf16", dynamic_loss_scale: bool = False,
+                 loss_scale_init: float = 65536.0, loss_scale_growth_interval: int = 2000):
         """``recompute`` (activation memory against recomputation in the backward pass; include/nexus/cuda/gpt.hpp:66 of
         the reference): "none" keeps every activation; "selective" keeps the GEMM outputs (qkv, attention output,
         MLP pre-activation) and recomputes the norm outputs and the GELU output; "full" keeps only the residual stream
@@ -138,6 +139,8 @@ class GptModel:
         self.w = {n: self._view(self.params_lp, n) for n in PARAM_ORDER}
         self.g = {n: self._view(self.grads, n) for n in PARAM_ORDER}
         self.opt_state = K.opt_state_tensor(dev)
+        off = K.OptState.loss_scale.offset             # the loss-scale field, as the 1-element tensor the CE kernel reads
+        self._loss_scale_dev = self.opt_state[off: off + 4].view(torch.float32)
         self._opt_host = torch.zeros(self.opt_state.numel(), dtype=torch.uint8).pin_memory()
         self._lr_host = torch.zeros(1, dtype=torch.float32).pin_memory()
         self.chunks = K.make_chunks(
@@ -150,6 +153,14 @@ class GptModel:
         self._acts = None
         self._acts_key = None
         self.step_count = 0
+        # Dynamic loss scale (include/nexus/cuda/gpt.hpp:30,91 of the reference): the scale lives in the device-resident
+        # optimizer state; the loss gradient is multiplied by it on the device, the norm kernel unscales and flags
+        # non-finite gradients, AdamW skips such a step, and one tiny kernel halves / doubles the scale.  No host read.
+        self.dynamic_loss_scale = bool(dynamic_loss_scale)
+        self.loss_scale_init = float(loss_scale_init)
+        self.loss_scale_growth_interval = int(loss_scale_growth_interval)
+        if self.dynamic_loss_scale and optimizer != "adamw":
+            raise ValueError("dynamic_loss_scale is implemented for optimizer='adamw'")
         self.backward_hook = None     # callable(stage): see set_backward_hook
         # the bias-gradient column sums of fc / qkv are bandwidth-bound side work: they run on a second stream under the
         # two GEMMs that follow them (NEXUS_B200_OVERLAP_COLSUM=0 keeps them in line)
@@ -357,7 +368,8 @@ class GptModel:
         logits = self.forward(tokens)
         K.cross_entropy_shifted(logits, tokens, vocab=self.V, smoothing=smoothing, z_loss=z_loss,
                                 grad_scale=grad_scale, loss_out=self.loss_buf, loss_weight=loss_weight,
-                                accumulate_loss=accumulate_loss, seq_len=T)
+                                accumulate_loss=accumulate_loss, seq_len=T,
+                                grad_scale_dev=self._loss_scale_dev if self.dynamic_loss_scale else None)
         dlogits = logits
         res = a["res"]
         # head: dlnf = dlogits @ wte ; dwte += dlogits^T @ lnf
@@ -448,9 +460,16 @@ class GptModel:
         return self.loss_buf
 
     # ---------------------------------------------------------------------------------- optimizer
-    def set_optimizer(self, cfg: AdamWConfig, lr: Optional[float] = None, loss_scale: float = 1.0) -> None:
-        """Writes hyper-parameters into the device-resident optimizer state (keeps step counters)."""
+    def set_optimizer(self, cfg: AdamWConfig, lr: Optional[float] = None, loss_scale: Optional[float] = None) -> None:
+        """Writes hyper-parameters into the device-resident optimizer state (keeps step counters and, under
+        ``dynamic_loss_scale``, the current scale)."""
         cur = K.unpack_opt_state(bytes(self.opt_state.cpu().numpy().tobytes()))
+        if loss_scale is None:
+            if not self.dynamic_loss_scale:
+                loss_scale = 1.0
+            else:
+                loss_scale = cur.loss_scale if getattr(self, "_loss_scale_set", False) else self.loss_scale_init
+        self._loss_scale_set = True
         raw = K.pack_opt_state(lr=cfg.lr if lr is None else lr, weight_decay=cfg.weight_decay, beta1=cfg.beta1,
                                beta2=cfg.beta2, eps=cfg.eps, max_grad_norm=cfg.grad_clip, loss_scale=loss_scale,
                                step=cur.step, skipped=cur.skipped, good_steps=cur.good_steps,
@@ -470,6 +489,8 @@ class GptModel:
         shadow = None if self.master_mode == "cast_per_forward" else self.params_lp
         if self.optimizer_kind == "adamw":
             K.adamw(self.params, self.grads, self.m, self.v, shadow, self.chunks, self.opt_state, zero_grad=True)
+            if self.dynamic_loss_scale:
+                K.loss_scale_update(self.opt_state, interval=self.loss_scale_growth_interval)
         elif self.optimizer_kind == "adamw8bit":
             from ..ops import _lowp
             t = self._tail

@@ -352,9 +352,10 @@ def embedding_bwd(tokens, dx, dwte, dwpe, batch, seq_len, deterministic=True):
 # ------------------------------------------------------------------------------------ cross-entropy
 def cross_entropy_shifted(logits, tokens, *, targets=None, vocab=None, ignore_index=-100, smoothing=0.0,
                           z_loss=0.0, grad_scale=1.0, write_grad=True, loss_out=None, loss_weight=1.0,
-                          accumulate_loss=False, seq_len=None):
+                          accumulate_loss=False, seq_len=None, grad_scale_dev=None):
     """In-place fused CE.  ``logits`` [rows, ld] becomes d(loss*grad_scale)/dlogits.  Returns the loss
-    tensor (1 element, device)."""
+    tensor (1 element, device).  ``grad_scale_dev``: a 1-element FP32 device tensor that multiplies the gradient too
+    (the dynamic loss scale inside the optimizer state)."""
     L = lib()
     rows, ld = logits.shape[0], logits.stride(0)
     vocab = vocab or logits.shape[1]
@@ -363,11 +364,12 @@ def cross_entropy_shifted(logits, tokens, *, targets=None, vocab=None, ignore_in
     state = scratch(int(L.nx_ce_state_bytes()), "ce_state", logits.device)
     if loss_out is None:
         loss_out = torch.empty(1, dtype=torch.float32, device=logits.device)
-    _check(L.nx_cross_entropy_shifted(_p(logits), C.c_int(_DT[logits.dtype]), _p(tokens), _p(targets), _p(row_loss),
-                                      _p(state), _p(loss_out), C.c_float(loss_weight), C.c_int(int(accumulate_loss)),
-                                      C.c_int64(rows), C.c_int(T), C.c_int(vocab), C.c_int64(ld),
-                                      C.c_int(ignore_index), C.c_float(smoothing), C.c_float(z_loss),
-                                      C.c_float(grad_scale), C.c_int(int(write_grad)), _stream()),
+    _check(L.nx_cross_entropy_shifted_scaled(_p(logits), C.c_int(_DT[logits.dtype]), _p(tokens), _p(targets),
+                                             _p(row_loss), _p(state), _p(loss_out), C.c_float(loss_weight),
+                                             C.c_int(int(accumulate_loss)), C.c_int64(rows), C.c_int(T), C.c_int(vocab),
+                                             C.c_int64(ld), C.c_int(ignore_index), C.c_float(smoothing),
+                                             C.c_float(z_loss), C.c_float(grad_scale), _p(grad_scale_dev),
+                                             C.c_int(int(write_grad)), _stream()),
            "nx_cross_entropy_shifted")
     return loss_out
 

@@ -142,6 +142,50 @@ def test_eight_bit_and_offloaded_optimizers_track_fp32_adamw():
     assert host_bytes > 0 and dev_bytes < 12 * init.numel()
 
 
+def test_dynamic_loss_scale_on_the_device():
+    """The loss scale lives in the device-resident optimizer state: the loss gradient is multiplied by it inside the
+    cross-entropy kernel, the norm kernel unscales and flags non-finite gradients, AdamW skips such a step (and still
+    clears the gradients), and the update kernel halves the scale after an overflow and doubles it after
+    `growth_interval` clean steps.  No host read takes part."""
+    from nexus_b200.models.gpt import AdamWConfig, GptModel
+    from nexus_b200.ops import _cuda as K
+    cfg = _tiny_cfg()
+    tokens = torch.randint(0, cfg.vocab_size, (2, 128), dtype=torch.int32, device="cuda",
+                           generator=torch.Generator(device="cuda").manual_seed(4))
+
+    def state(m):
+        return K.unpack_opt_state(bytes(m.opt_state.cpu().numpy().tobytes()))
+
+    # a power-of-two scale changes nothing but the exponent of the BF16 gradients: same training as without it
+    ref = GptModel(cfg, device="cuda", seed=6)
+    dyn = GptModel(cfg, device="cuda", seed=6, dynamic_loss_scale=True, loss_scale_init=1024.0, loss_scale_growth_interval=3)
+    for m in (ref, dyn):
+        m.deterministic_embedding = True
+        m.set_optimizer(AdamWConfig(lr=1e-3))
+    la, lb = [], []
+    for _ in range(4):
+        la.append(float(ref.forward_backward(tokens).item())); ref.optimizer_step()
+        lb.append(float(dyn.forward_backward(tokens).item())); dyn.optimizer_step()
+    assert max(abs(a - b) for a, b in zip(la, lb)) < 2e-2
+    upd = (ref.params - GptModel(cfg, device="cuda", seed=6).params).norm().item()
+    assert (ref.params - dyn.params).norm().item() / upd < 5e-2
+    st = state(dyn)
+    assert st.skipped == 0 and st.step == 4 and st.loss_scale == 2048.0       # doubled once after three clean steps
+
+    # an absurd scale overflows the gradients: the step is skipped, the weights stay, the scale is halved, the
+    # gradients are cleared, and training goes on once the scale is small enough
+    big = GptModel(cfg, device="cuda", seed=6, dynamic_loss_scale=True, loss_scale_init=2.0 ** 126)
+    big.set_optimizer(AdamWConfig(lr=1e-3))
+    before = big.params.clone()
+    big.forward_backward(tokens, grad_scale=2.0 ** 12)      # scale x weight is past the FP32 range: infinite gradients
+    big.optimizer_step()
+    st = state(big)
+    assert st.found_inf == 1 and st.skipped == 1 and st.step == 0 and st.loss_scale == 2.0 ** 125
+    assert torch.equal(big.params, before) and float(big.grads.abs().max()) == 0.0
+    torch.cuda.synchronize()
+    K.check_status()
+
+
 def test_unimplemented_modes_are_refused_not_ignored():
     from nexus_b200.models.gpt import GptModel
     cfg = _tiny_cfg()
