@@ -28,14 +28,17 @@ PEAK_BF16_FLOPS = {10: 2.25e15, 9: 0.989e15, 8: 0.312e15}
 class GptLmBackend(LmBackend):
     def __init__(self, config: LmConfig, micro_batch: int, seq_len: int, device="cuda", seed: int = 1234,
                  deterministic: bool = False, recompute: str = "none", recompute_every: int = 2,
-                 optimizer: str = "adamw", master: str = "fp32", compute_dtype: str = "bf16"):
+                 optimizer: str = "adamw", master: str = "fp32", compute_dtype: str = "bf16",
+                 dynamic_loss_scale=(False, 65536.0, 2000)):
         self.dev = torch.device(device)
         if self.dev.index is None:
             self.dev = torch.device("cuda", torch.cuda.current_device())
         torch.cuda.set_device(self.dev)
         # unknown or unimplemented modes raise inside GptModel: nothing is silently ignored
         self.model = GptModel(config, device=self.dev, seed=seed, recompute=recompute, recompute_every=recompute_every,
-                              optimizer=optimizer, master=master, compute_dtype=compute_dtype)
+                              optimizer=optimizer, master=master, compute_dtype=compute_dtype,
+                              dynamic_loss_scale=dynamic_loss_scale[0], loss_scale_init=dynamic_loss_scale[1],
+                              loss_scale_growth_interval=dynamic_loss_scale[2])
         self.model.deterministic_embedding = deterministic
         self.B, self.T = micro_batch, seq_len
         self._host_tokens = [torch.empty((micro_batch, seq_len), dtype=torch.int32).pin_memory() for _ in range(2)]
@@ -162,6 +165,9 @@ class GptLmBackend(LmBackend):
         if self.model.optimizer_kind != "adamw" or self.model.master_mode != "fp32":
             raise ValueError("the sharded optimizer implements FP32-master AdamW; it cannot be combined with "
                              f"optimizer='{self.model.optimizer_kind}' / master='{self.model.master_mode}'")
+        if self.model.dynamic_loss_scale:
+            raise ValueError("the sharded optimizer does not run the loss-scale update; use dynamic_loss_scale with "
+                             "data parallelism (attach_process_group) or on one GPU")
         self._pg_fsdp = group
         group.broadcast_tensor(self.model.params, 0)
         self.model.refresh_shadow()

@@ -278,6 +278,10 @@ class LanguageTrainerBuilder:
     def precision(self, p: str, master: str = "fp32"): self._precision, self._master = p.lower(), master.lower(); return self
     def recompute(self, r: str, every: int = 2): self._recompute, self._recompute_every = r, every; return self
     def optimizer_kind(self, kind: str): self._optimizer_kind = kind; return self
+    def dynamic_loss_scale(self, enabled: bool = True, init: float = 65536.0, growth_interval: int = 2000):
+        """Device-resident dynamic loss scale of the GPU model backend (off by default; BF16 rarely needs it)."""
+        self._dynamic_loss_scale = (bool(enabled), float(init), int(growth_interval))
+        return self
     def eval_every(self, n: int, batches: int = 4): self._eval_every, self._eval_batches = n, batches; return self
     def log_every(self, n: int): self._log_every = n; return self
     def execution_policy(self, device: str): self._device = device; return self
@@ -337,7 +341,8 @@ def _make_backend(b: LanguageTrainerBuilder) -> LmBackend:
                 b._master, b._master)   # anything else ("none", ...) is refused by the model with a clear message
             return GptLmBackend(cfg, b._micro_batch, b._seq_len, device=b._device, seed=b._seed,
                                 deterministic=b._deterministic, recompute=b._recompute,
-                                recompute_every=b._recompute_every, optimizer=b._optimizer_kind, master=master)
+                                recompute_every=b._recompute_every, optimizer=b._optimizer_kind, master=master,
+                                dynamic_loss_scale=getattr(b, "_dynamic_loss_scale", (False, 65536.0, 2000)))
         from ..lm.model import LanguageModel
         model = LanguageModel(cfg)
     from .torch_backend import TorchLmBackend
