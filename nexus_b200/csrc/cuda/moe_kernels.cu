@@ -98,6 +98,62 @@ moe_assign_kernel(const int32_t* __restrict__ expert, int tokens, int k, int cap
   if (dropped != nullptr && ndrop > 0) atomicAdd(dropped, ndrop);
 }
 
+// Capacity per GROUP of tokens and the Reroute overflow policy.  One warp per group walks the group's assignments in
+// priority order (choice j, then token t) with the per-expert fill counters in shared memory: an assignment whose
+// expert is full is dropped (slot -1) or, with `order` given ([tokens, E]: every token's experts by descending
+// score), moved to the token's best expert that still has room and is not one of the token's own choices; the lanes
+// test 32 candidates per trip.  slot = group * capacity + position inside the group's share of the expert's buffer,
+// so the buffers are [E, groups * capacity, d].  counts[g * E + e] = rows of group g accepted by expert e.
+__global__ void __launch_bounds__(32)
+moe_assign_groups_kernel(int32_t* __restrict__ expert, const int32_t* __restrict__ order, int tokens, int k, int E,
+                         int groups, int capacity, int32_t* __restrict__ slot, int32_t* __restrict__ counts,
+                         int32_t* __restrict__ dropped, int32_t* __restrict__ rerouted) {
+  extern __shared__ int s_fill[];  // [E]
+  const int g = blockIdx.x, lane = threadIdx.x;
+  const int ng = tokens / groups, t0 = g * ng;
+  for (int e = lane; e < E; e += 32) s_fill[e] = 0;
+  __syncwarp();
+  int ndrop = 0, nmove = 0;
+  for (int j = 0; j < k; ++j) {
+    for (int t = t0; t < t0 + ng; ++t) {
+      int e = expert[t * k + j];
+      bool full = s_fill[e] >= capacity;
+      if (full && order != nullptr) {
+        int alt = -1;
+        for (int c0 = 0; c0 < E && alt < 0; c0 += 32) {
+          const int c = c0 + lane;
+          bool ok = false;
+          int cand = -1;
+          if (c < E) {
+            cand = order[static_cast<int64_t>(t) * E + c];
+            ok = s_fill[cand] < capacity;
+            for (int q = 0; q < k; ++q) ok = ok && expert[t * k + q] != cand;
+          }
+          const unsigned b = __ballot_sync(0xffffffffu, ok);
+          if (b != 0u) alt = __shfl_sync(0xffffffffu, cand, __ffs(b) - 1);
+        }
+        if (alt >= 0) {
+          e = alt;
+          full = false;
+          ++nmove;
+          if (lane == 0) expert[t * k + j] = e;
+        }
+      }
+      if (lane == 0) {
+        slot[t * k + j] = full ? -1 : g * capacity + s_fill[e];
+        if (!full) s_fill[e] += 1;
+      }
+      ndrop += full ? 1 : 0;
+      __syncwarp();
+    }
+  }
+  for (int e = lane; e < E; e += 32) counts[g * E + e] = s_fill[e];
+  if (lane == 0) {
+    if (dropped != nullptr && ndrop > 0) atomicAdd(dropped, ndrop);
+    if (rerouted != nullptr && nmove > 0) atomicAdd(rerouted, nmove);
+  }
+}
+
 // dgate[t, j] = dy[t] . expert_out[e_tj][slot_tj]   (0 for dropped assignments); warp per (t, j)
 __global__ void moe_gate_grad_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ buf,
                                      const int32_t* __restrict__ expert, const int32_t* __restrict__ slot,
@@ -133,6 +189,16 @@ extern "C" int nx_moe_assign(const int32_t* expert, int tokens, int k, int exper
   if (tokens <= 0 || experts <= 0) return 0;
   if (capacity < 0) return -1;
   moe_assign_kernel<<<experts, 1024, 0, static_cast<cudaStream_t>(stream)>>>(expert, tokens, k, capacity, slot, counts, dropped);
+  return launch_status();
+}
+
+extern "C" int nx_moe_assign_groups(int32_t* expert, const int32_t* order, int tokens, int k, int experts, int groups,
+                                    int capacity, int32_t* slot, int32_t* counts, int32_t* dropped, int32_t* rerouted,
+                                    nx_stream_t stream) {
+  if (tokens <= 0 || experts <= 0) return 0;
+  if (groups < 1 || tokens % groups || capacity < 0 || k < 1 || k > 8 || experts > 8192) return -1;
+  moe_assign_groups_kernel<<<groups, 32, experts * sizeof(int), static_cast<cudaStream_t>(stream)>>>(
+      expert, order, tokens, k, experts, groups, capacity, slot, counts, dropped, rerouted);
   return launch_status();
 }
 

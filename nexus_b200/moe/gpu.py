@@ -6,6 +6,8 @@ from __future__ import annotations
 
 import ctypes as C
 
+from typing import Optional
+
 import torch
 
 from ..ops import _cuda as K
@@ -105,12 +107,114 @@ class _MoeFn(torch.autograd.Function):
         return dx.to(x.dtype), drouter.to(router_w.dtype), dup.to(up.dtype), ddown.to(down.dtype), None, None
 
 
-def moe_ffn(x: torch.Tensor, router_w: torch.Tensor, up: torch.Tensor, down: torch.Tensor, k: int, capacity: int):
-    """x [N, d] BF16, router_w [E, d], up [E, 2F, d] (gate | up rows), down [E, d, F].
-    Returns (y [N, d] BF16, counts[E], dropped[1])."""
+def route_groups(select: torch.Tensor, k: int, capacity: int, groups: int = 1, reroute: bool = False):
+    """Routing with a capacity per group of tokens and, optionally, the Reroute overflow policy, on selection scores
+    ``select`` FP32 [N, E] (the router logits, or the noisy ones).  Returns (expert_sel [N, k] the top-k before any
+    move, expert [N, k] after rerouting, gate [N, k] = softmax over the selected scores, slot [N, k] into buffers of
+    ``groups * capacity`` rows per expert, counts [groups, E], dropped [1], rerouted [1]).
+    Parity: src/moe/moe.cpp:115-259 of the reference (GShard capacity per group, (choice, token) priority)."""
+    N, E = select.shape
+    dev = select.device
+    order = torch.sort(select.detach(), dim=-1, descending=True, stable=True).indices.to(torch.int32).contiguous()
+    expert_sel = order[:, :k].contiguous()
+    gate = torch.softmax(select.gather(1, expert_sel.long()), -1)
+    expert = expert_sel.clone()
+    slot = torch.empty((N, k), dtype=torch.int32, device=dev)
+    counts = torch.zeros(groups * E, dtype=torch.int32, device=dev)
+    dropped = torch.zeros(1, dtype=torch.int32, device=dev)
+    rerouted = torch.zeros(1, dtype=torch.int32, device=dev)
+    K._check(K.lib().nx_moe_assign_groups(K._p(expert), K._p(order if reroute else None), C.c_int(N), C.c_int(k),
+                                          C.c_int(E), C.c_int(groups), C.c_int(capacity), K._p(slot), K._p(counts),
+                                          K._p(dropped), K._p(rerouted), K._stream()), "nx_moe_assign_groups")
+    return expert_sel, expert, gate, slot, counts.view(groups, E), dropped, rerouted
+
+
+class _MoeGroupsFn(torch.autograd.Function):
+    """`_MoeFn` with group capacities, Reroute and noisy top-k.  The gate of an assignment is the softmax over the
+    scores of the token's ORIGINAL top-k (a rerouted assignment keeps its weight), so the router gradient goes to the
+    originally selected logits while rows travel to the final experts."""
+
+    @staticmethod
+    def forward(ctx, x, router_w, noise_w, up, down, k, capacity, groups, reroute, eps):
+        N, d = x.shape
+        E, F2, _ = up.shape
+        cap = groups * capacity
+        logits = x.float() @ router_w.float().t()
+        nl = None
+        select = logits
+        if noise_w is not None and eps is not None:
+            nl = x.float() @ noise_w.float().t()
+            select = logits + eps * torch.nn.functional.softplus(nl)
+        expert_sel, expert, gate, slot, counts, dropped, rerouted = route_groups(select, k, capacity, groups, reroute)
+        buf = dispatch(x, expert, slot, E, cap)
+        h = K.gemm(buf, up)
+        act = I.gated_fwd(h.view(E * cap, F2), "silu").view(E, cap, F2 // 2)
+        out = K.gemm(act, down)
+        y = combine(out, expert, slot, gate, E, cap)
+        ctx.save_for_backward(x, router_w, noise_w if noise_w is not None else x.new_zeros(0), up, down, expert_sel, expert,
+                              gate, slot, buf, h, act, out, nl if nl is not None else x.new_zeros(0),
+                              eps if eps is not None else x.new_zeros(0))
+        ctx.k, ctx.cap, ctx.noisy = k, cap, nl is not None
+        ctx.mark_non_differentiable(counts, dropped, rerouted)
+        return y, counts, dropped, rerouted
+
+    @staticmethod
+    def backward(ctx, dy, _c, _d, _r):
+        x, router_w, noise_w, up, down, expert_sel, expert, gate, slot, buf, h, act, out, nl, eps = ctx.saved_tensors
+        k, cap = ctx.k, ctx.cap
+        N, d = x.shape
+        E, F2, _ = up.shape
+        dy = dy.contiguous().to(torch.bfloat16)
+        dgate = torch.empty((N, k), dtype=torch.float32, device=x.device)
+        K._check(K.lib().nx_moe_gate_grad(K._p(dy), K._p(out), K._p(expert), K._p(slot), K._p(dgate), C.c_int(N), C.c_int(k),
+                                          C.c_int(d), C.c_int(cap), K._stream()), "nx_moe_gate_grad")
+        dout = dispatch(dy, expert, slot, E, cap, row_scale=gate.contiguous().view(-1))
+        dact = K.gemm(dout, down, b_mn=True)
+        ddown = K.gemm(dout, act, a_mn=True, b_mn=True, out_dtype=torch.float32)
+        dh = I.gated_bwd(h.view(E * cap, F2), dact.view(E * cap, F2 // 2), "silu").view(E, cap, F2)
+        dbuf = K.gemm(dh, up, b_mn=True)
+        dup = K.gemm(dh, buf, a_mn=True, b_mn=True, out_dtype=torch.float32)
+        dx = combine(dbuf, expert, slot, torch.ones_like(gate), E, cap).float()
+        inner = (gate * dgate).sum(-1, keepdim=True)
+        dsel = gate * (dgate - inner)
+        dselect = torch.zeros((N, E), dtype=torch.float32, device=x.device).scatter_add_(1, expert_sel.long(), dsel)
+        drouter = dselect.t() @ x.float()
+        dx = dx + dselect @ router_w.float()
+        dnoise = None
+        if ctx.noisy:
+            dnl = dselect * eps * torch.sigmoid(nl)
+            dnoise = (dnl.t() @ x.float()).to(noise_w.dtype)
+            dx = dx + dnl @ noise_w.float()
+        return (dx.to(x.dtype), drouter.to(router_w.dtype), dnoise, dup.to(up.dtype), ddown.to(down.dtype),
+                None, None, None, None, None)
+
+
+def noise_sample(tokens: int, experts: int, seed: int, device) -> torch.Tensor:
+    """The standard-normal draws of the noisy top-k router: the CPU generator's stream for ``seed`` (the one
+    `moe.route` uses), moved to the device, so both paths select the same experts."""
+    g = torch.Generator(device="cpu").manual_seed(int(seed))
+    return torch.randn((tokens, experts), generator=g).to(device)
+
+
+def moe_ffn(x: torch.Tensor, router_w: torch.Tensor, up: torch.Tensor, down: torch.Tensor, k: int, capacity: int, *,
+            groups: int = 1, overflow: str = "drop", noise_w: Optional[torch.Tensor] = None, noise_seed: int = 0,
+            training: bool = False):
+    """x [N, d] BF16, router_w [E, d], up [E, 2F, d] (gate | up rows), down [E, d, F]; ``capacity`` rows per expert
+    and group.  Returns (y [N, d] BF16, counts, dropped[1]) for the plain policy (one group, drop, no noise), and
+    (y, counts [groups, E], dropped[1], rerouted[1]) when ``groups`` > 1, ``overflow`` = "reroute" or a noisy router
+    (``noise_w`` [E, d], used in training) is asked for."""
     if capacity % 8 or x.shape[1] % 8:
         raise ValueError("capacity and model width must be multiples of 8")
-    return _MoeFn.apply(x, router_w, up, down, k, capacity)
+    if overflow not in ("drop", "reroute"):
+        raise ValueError("overflow must be 'drop' or 'reroute'")
+    noisy = training and noise_w is not None
+    if groups == 1 and overflow == "drop" and not noisy:
+        return _MoeFn.apply(x, router_w, up, down, k, capacity)
+    if x.shape[0] % groups:
+        raise ValueError(f"token count {x.shape[0]} must be divisible by groups {groups}")
+    eps = noise_sample(x.shape[0], up.shape[0], noise_seed, x.device) if noisy else None
+    return _MoeGroupsFn.apply(x, router_w, noise_w if noisy else None, up, down, k, capacity, groups,
+                              overflow == "reroute", eps)
 
 
 def reference(x, router_w, up, down, k: int, capacity: int):
