@@ -75,7 +75,8 @@ def copy_sources(ref: Path) -> dict:
 
 
 def build(ref: Path | None = None, force: bool = False, verbose: bool = True) -> Path:
-    ref = Path(ref or os.environ.get("NEXUS_REFERENCE", "/root/reference"))
+    # the reference checkout: given, or $NEXUS_REFERENCE, or a `reference` directory beside this repository
+    ref = Path(ref or os.environ.get("NEXUS_REFERENCE") or HERE.parent.parent / "reference")
     driver = HERE / "ref_gpt_driver.cpp"
     if LIB.exists() and BIN.exists() and not force and LIB.stat().st_mtime >= driver.stat().st_mtime:
         return LIB
