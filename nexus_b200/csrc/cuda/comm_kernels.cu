@@ -649,6 +649,130 @@ __global__ void __launch_bounds__(256) allreduce_multimem_kernel(uint8_t* mc, in
   __threadfence_system();  // the stores are out before the barrier kernel that follows signals the peers
 }
 
+// ---------------------------------------------------------------------------------------------
+// The sharded optimizer through NVSwitch.  Reduce-scatter: the owner asks the switch for the sum of its shard of the
+// gradients (`multimem.ld_reduce` on the multicast address of the symmetric gradient buffer), so 1 / n of the buffer
+// enters each GPU instead of (n - 1) / n; the square sum for the norm is formed in the same pass.  All-gather: the
+// owner's AdamW writes every updated BF16 weight (and FP32 norm / bias value) once with `multimem.st`, which lands in
+// every rank's copy, instead of once per peer.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+reduce_shard_multimem_kernel(const uint8_t* __restrict__ mc, int64_t shard_off, int64_t count, float scale,
+                             float* __restrict__ out, double* __restrict__ partial) {
+  __shared__ double s_scratch[32];
+  const int64_t begin = static_cast<int64_t>(blockIdx.x) * kReduceChunk;
+  const int64_t end = min(count, begin + kReduceChunk);
+  const uint64_t base = reinterpret_cast<uint64_t>(mc) + static_cast<uint64_t>(shard_off) * 4;
+  double sq = 0.0;
+  for (int64_t i = begin + threadIdx.x * 4; i < end; i += blockDim.x * 4) {
+    if (i + 4 <= end) {
+      uint32_t r[4];
+      multimem_ld_reduce<false>(base + static_cast<uint64_t>(i) * 4, r);
+      float4 acc = make_float4(__uint_as_float(r[0]) * scale, __uint_as_float(r[1]) * scale, __uint_as_float(r[2]) * scale,
+                               __uint_as_float(r[3]) * scale);
+      *reinterpret_cast<float4*>(out + i) = acc;
+      sq += static_cast<double>(acc.x) * acc.x + static_cast<double>(acc.y) * acc.y +
+            static_cast<double>(acc.z) * acc.z + static_cast<double>(acc.w) * acc.w;
+    } else {
+      for (int64_t j = i; j < end; ++j) {
+        float a;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.f32 %0, [%1];" : "=f"(a) : "l"(base + static_cast<uint64_t>(j) * 4) : "memory");
+        a *= scale;
+        out[j] = a;
+        sq += static_cast<double>(a) * a;
+      }
+    }
+  }
+  sq = block_sum<double>(sq, s_scratch);
+  if (threadIdx.x == 0) partial[blockIdx.x] = sq;
+}
+
+// `adamw_shard_allgather_kernel` with the results stored through the multicast addresses of the BF16 shadow and the
+// FP32 tail.  Eight parameters per thread where the global index allows a 16-byte store, one at a time at ragged ends.
+__global__ void __launch_bounds__(256)
+adamw_shard_multimem_kernel(float* __restrict__ master, const float* __restrict__ grad, float* __restrict__ m,
+                            float* __restrict__ v, uint8_t* __restrict__ shadow_mc, uint8_t* __restrict__ tail_mc,
+                            NxPeerTable shadows, int n, int64_t tail_off, int64_t shard_off,
+                            const NxAdamChunk* __restrict__ chunks, const NxOptState* __restrict__ st) {
+  if (st->found_inf) return;
+  const NxAdamChunk ch = chunks[blockIdx.x];
+  const float lr = __fmul_rn(st->lr, ch.lr_scale);
+  const float wd = __fmul_rn(st->weight_decay, ch.wd_scale);
+  const float b1 = st->beta1, b2 = st->beta2, omb1 = __fsub_rn(1.0f, b1), omb2 = __fsub_rn(1.0f, b2);
+  const float i1 = st->inv_bias1, i2 = st->inv_bias2, eps = st->eps, clip = st->clip_coef;
+  const float lrwd = __fmul_rn(lr, wd);
+  auto update = [&](int64_t gi) -> float {   // same operation order as adamw_kernel
+    const int64_t i = gi - shard_off;
+    const float g = __fmul_rn(grad[i], clip);
+    float p = master[i];
+    p = __fsub_rn(p, __fmul_rn(lrwd, p));
+    const float mi = __fadd_rn(__fmul_rn(b1, m[i]), __fmul_rn(omb1, g));
+    const float vi = __fadd_rn(__fmul_rn(b2, v[i]), __fmul_rn(omb2, __fmul_rn(g, g)));
+    p = __fsub_rn(p, __fdiv_rn(__fmul_rn(lr, __fmul_rn(mi, i1)), __fadd_rn(__fsqrt_rn(__fmul_rn(vi, i2)), eps)));
+    master[i] = p;
+    m[i] = mi;
+    v[i] = vi;
+    return p;
+  };
+  auto store_one = [&](int64_t gi, float p) {   // a multicast store is at least 32 bits wide: single BF16 values go peer by peer
+    const __nv_bfloat16 lp = __float2bfloat16_rn(p);
+#pragma unroll 1
+    for (int q = 0; q < n; ++q) reinterpret_cast<__nv_bfloat16*>(shadows.ptr[q])[gi] = lp;
+    if (tail_off >= 0 && gi >= tail_off)
+      asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(tail_mc) + static_cast<uint64_t>(gi - tail_off) * 4), "f"(p) : "memory");
+  };
+  const int64_t lo = ch.offset, hi = ch.offset + ch.count;
+  const int64_t a0 = min(hi, (lo + 7) / 8 * 8), a1 = max(a0, hi / 8 * 8);   // [a0, a1): whole groups of 8 by global index
+  for (int64_t gi = lo + threadIdx.x; gi < a0; gi += blockDim.x) store_one(gi, update(gi));
+  for (int64_t gi = a1 + threadIdx.x; gi < hi; gi += blockDim.x) store_one(gi, update(gi));
+  for (int64_t g8 = a0 + static_cast<int64_t>(threadIdx.x) * 8; g8 < a1; g8 += static_cast<int64_t>(blockDim.x) * 8) {
+    float p[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) p[j] = update(g8 + j);
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) w[j] = nx::pack_bf16x2(p[2 * j], p[2 * j + 1]);
+    multimem_st<false>(reinterpret_cast<uint64_t>(shadow_mc) + static_cast<uint64_t>(g8) * 2, w);
+    if (tail_off >= 0 && g8 + 8 > tail_off) {
+      const int64_t t = g8 - tail_off;
+      if (t >= 0 && (t & 3) == 0) {
+        uint32_t f0[4] = {__float_as_uint(p[0]), __float_as_uint(p[1]), __float_as_uint(p[2]), __float_as_uint(p[3])};
+        uint32_t f1[4] = {__float_as_uint(p[4]), __float_as_uint(p[5]), __float_as_uint(p[6]), __float_as_uint(p[7])};
+        multimem_st<false>(reinterpret_cast<uint64_t>(tail_mc) + static_cast<uint64_t>(t) * 4, f0);
+        multimem_st<false>(reinterpret_cast<uint64_t>(tail_mc) + static_cast<uint64_t>(t + 4) * 4, f1);
+      } else {   // the tail starts inside this group, or on an odd 16-byte phase
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (t + j >= 0)
+            asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(reinterpret_cast<uint64_t>(tail_mc) + static_cast<uint64_t>(t + j) * 4), "f"(p[j]) : "memory");
+      }
+    }
+  }
+  __threadfence_system();
+}
+
+extern "C" int nx_comm_reduce_shard_multimem(void* grads_mc, int64_t shard_off, int64_t count, float scale, float* out,
+                                             double* partial, nx_stream_t stream) {
+  if (grads_mc == nullptr || count <= 0 || (shard_off & 3)) return -1;
+  const int blocks = static_cast<int>((count + kReduceChunk - 1) / kReduceChunk);
+  reduce_shard_multimem_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(grads_mc), shard_off, count, scale, out, partial);
+  return launch_status();
+}
+
+extern "C" int nx_comm_adamw_allgather_multimem(float* master, const float* grad, float* m, float* v, void* shadow_mc,
+                                                void* tail_mc, const NxPeerTable* shadows, int n, int64_t tail_off,
+                                                int64_t shard_off, const NxAdamChunk* chunks, int nchunks,
+                                                const NxOptState* state, nx_stream_t stream) {
+  if (shadow_mc == nullptr || shadows == nullptr || n < 1 || n > NX_MAX_PEERS || nchunks <= 0 ||
+      (tail_mc == nullptr && tail_off >= 0))
+    return -1;
+  adamw_shard_multimem_kernel<<<nchunks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      master, grad, m, v, static_cast<uint8_t*>(shadow_mc), static_cast<uint8_t*>(tail_mc), *shadows, n, tail_off,
+      shard_off, chunks, state);
+  return launch_status();
+}
+
 extern "C" int nx_comm_allreduce_multimem(void* multicast_ptr, int dtype, int64_t shard_off, int64_t count, float scale,
                                           nx_stream_t stream) {
   if (multicast_ptr == nullptr || (dtype != NX_F32 && dtype != NX_BF16)) return -1;

@@ -45,6 +45,18 @@ int nx_comm_adamw_allgather(float* master, const float* grad, float* m, float* v
 int nx_comm_allreduce_shard(const NxPeerTable* in, int in_dtype, int n_in, const NxPeerTable* out, int out_dtype,
                             int n_out, int64_t shard_off, int64_t count, float scale, nx_stream_t stream);
 
+// The two communicating kernels of the sharded optimizer through NVSwitch (`*_mc`: multicast addresses of the
+// symmetric gradient, BF16 shadow and FP32 tail buffers).  Same arguments and results as nx_comm_reduce_shard /
+// nx_comm_adamw_allgather; the reduce reads each element once from the switch (`multimem.ld_reduce`), the update
+// writes each result once for all ranks (`multimem.st`).
+int nx_comm_reduce_shard_multimem(void* grads_mc, int64_t shard_off, int64_t count, float scale, float* out,
+                                  double* partial, nx_stream_t stream);
+// (`shadows`: the peer table of the BF16 shadow, for single values at ragged chunk ends: a multicast store is at least
+// 32 bits wide.)
+int nx_comm_adamw_allgather_multimem(float* master, const float* grad, float* m, float* v, void* shadow_mc, void* tail_mc,
+                                     const NxPeerTable* shadows, int n, int64_t tail_off, int64_t shard_off,
+                                     const NxAdamChunk* chunks, int nchunks, const NxOptState* state, nx_stream_t stream);
+
 // All-gather by peer loads: out[q * shard_bytes + ...] = shards[q][0 .. shard_bytes) for q < n (shard_bytes a multiple of
 // 16; `out` local).  Bracket with nx_comm_barrier: the shards must be written before, and stay untouched until every
 // rank has read them.

@@ -68,6 +68,25 @@ def main():
           err < 0.05 and err_lp < 0.08 and frac < 0.01)
     check(f"grad norm {s1.grad_norm:.5f} vs {s2.grad_norm:.5f}", abs(s1.grad_norm - s2.grad_norm) < 1e-3 * s2.grad_norm)
 
+    # ---- the same three steps with the reduce-scatter and the all-gather going through NVSwitch (opt-in form)
+    if opt.grads.multicast and opt.shadow.multicast and opt.tail.multicast:
+        os.environ["NEXUS_B200_SHARDED_MULTIMEM"] = "1"
+        model_mc = GptModel(cfg, device=dev, seed=11)
+        model_mc.set_optimizer(AdamWConfig(lr=1e-3))
+        opt_mc = FusedShardedOptimizer(model_mc, ws)
+        for step in range(3):
+            model_mc.forward_backward(tokens[rank], grad_scale=1.0 / world, loss_weight=1.0 / world)
+            opt_mc.step()
+        torch.cuda.synchronize()
+        K.check_status()
+        os.environ["NEXUS_B200_SHARDED_MULTIMEM"] = "0"
+        err_mc = (opt_mc.gather_master() - ref.params).norm().item() / upd
+        err_mc_lp = (model_mc.params_lp.float() - ref.params_lp.float()).norm().item() / upd
+        check(f"sharded optimizer through NVSwitch rel-L2 master {err_mc:.2e} shadow {err_mc_lp:.2e}",
+              err_mc < 0.05 and err_mc_lp < 0.08)
+    elif rank == 0:
+        print("--  sharded optimizer through NVSwitch: no multicast address on this fabric", flush=True)
+
     # ---- checkpoint of the sharded state: save -> train -> load -> the same step again gives the same result,
     # ---- and every rank's shard together loads into an unsharded backend (2 -> 1 reshard)
     import torch.distributed as dist
