@@ -69,3 +69,38 @@ def test_graph_merges():
     assert torch.allclose(g(x), torch.relu(a(x) + b(x)))
     gx = g.backward(torch.ones(3, 4))
     assert gx.shape == x.shape
+
+
+def test_functional_forms_match_torch():
+    """`nn.functional`: the stateless operator forms against torch on CPU tensors (the fused ops fall back to their
+    FP32 reference statements there): activations, gated activations, norms, attention in torch's layout with
+    grouped-query heads, embedding, dropout drawn from the Philox stream."""
+    import torch
+    from nexus_b200.nn import functional as F
+    TF = torch.nn.functional
+    torch.manual_seed(0)
+    x = torch.randn(5, 16)
+    assert torch.allclose(F.gelu(x), TF.gelu(x, approximate="tanh"), atol=1e-6)
+    assert torch.allclose(F.gelu(x, approximate="none"), TF.gelu(x), atol=1e-6)
+    h = torch.randn(5, 32)
+    assert torch.allclose(F.swiglu(h), TF.silu(h[:, :16]) * h[:, 16:], atol=1e-6)
+    assert torch.allclose(F.geglu(h), TF.gelu(h[:, :16], approximate="tanh") * h[:, 16:], atol=1e-5)
+    g, b = torch.randn(16), torch.randn(16)
+    assert torch.allclose(F.layer_norm(x, g, b), TF.layer_norm(x, (16,), g, b), atol=1e-5)
+    res = torch.randn(5, 16)
+    out = F.residual_layer_norm(x, res, g, b)
+    y = out[0] if isinstance(out, tuple) else out
+    assert torch.allclose(y, TF.layer_norm(x + res, (16,), g, b), atol=1e-5)
+    assert torch.allclose(F.rms_norm(x, g), x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * g, atol=1e-5)
+    assert torch.allclose(F.softmax(x), torch.softmax(x, -1), atol=1e-6)
+    w, bias = torch.randn(8, 16), torch.randn(8)
+    assert torch.allclose(F.linear(x, w, bias), TF.linear(x, w, bias), atol=1e-5)
+    q, k, v = torch.randn(2, 4, 10, 8), torch.randn(2, 2, 10, 8), torch.randn(2, 2, 10, 8)
+    want = TF.scaled_dot_product_attention(q, k.repeat_interleave(2, 1), v.repeat_interleave(2, 1), is_causal=True)
+    assert torch.allclose(F.scaled_dot_product_attention(q, k, v, is_causal=True), want, atol=1e-5)
+    toks = torch.randint(0, 20, (2, 6))
+    table = torch.randn(20, 12)
+    assert torch.equal(F.embedding(toks, table), table[toks])
+    d1, d2 = F.dropout(x, 0.5, seed=3, offset=10), F.dropout(x, 0.5, seed=3, offset=10)
+    assert torch.equal(d1, d2) and 0 < int((d1 == 0).sum()) < x.numel()
+    assert torch.equal(F.dropout(x, 0.5, seed=3, offset=10, training=False), x)

@@ -148,3 +148,35 @@ def test_token_loader_gpu():
         got = ld.next()
         assert got.is_cuda and np.array_equal(got.cpu().numpy(), np.asarray(ref.next_rows(4, 64), dtype=np.int32))
     ld.close()
+
+
+def test_nvme_store_aligned_direct_io_roundtrip(tmp_path):
+    """Offload store: one header sector + payload padded to sectors, written and read through page-aligned bounce
+    buffers (O_DIRECT where the file system takes it, buffered otherwise); odd sizes, empty payloads, overwrite,
+    asynchronous forms, truncated files are refused."""
+    import os
+    from nexus_b200.parallel.nvme import ALIGN, NvmeStore
+    for direct in (True, False):
+        st = NvmeStore(str(tmp_path / f"d{int(direct)}"), direct=direct)
+        assert isinstance(st.direct, bool) and (st.direct is False or direct)
+        blobs = {"a": b"", "b/c": b"x", "odd": os.urandom(ALIGN + 17), "big": os.urandom(3 * ALIGN)}
+        for k, v in blobs.items():
+            st.write(k, v)
+        for k, v in blobs.items():
+            assert st.read(k) == v
+            assert os.path.getsize(st._path(k)) % ALIGN == 0
+        st.write("odd", b"replaced")
+        assert st.read("odd") == b"replaced"
+        futs = [st.write_async(f"k{i}", bytes([i]) * (100 * i + 1)) for i in range(6)]
+        [f.result() for f in futs]
+        assert [st.read_async(f"k{i}").result() for i in range(6)] == [bytes([i]) * (100 * i + 1) for i in range(6)]
+        assert st.contains("big") and st.bytes_read > 0 and st.bytes_written > 0
+        with open(st._path("big"), "r+b") as f:
+            f.truncate(ALIGN)
+        try:
+            st.read("big")
+            raise AssertionError("a truncated file was accepted")
+        except IOError:
+            pass
+        st.remove("big")
+        assert not st.contains("big")
