@@ -11,6 +11,7 @@ void bind_cpu_kernels(py::module_& m);
 void bind_envs(py::module_& m);
 void bind_device_allocator(py::module_& m);
 void bind_store(py::module_& m);
+void bind_moe_ref(py::module_& m);
 
 PYBIND11_MODULE(_native, m) {
   m.doc() = "nexus_b200 native host runtime";
@@ -21,4 +22,5 @@ PYBIND11_MODULE(_native, m) {
   bind_envs(m);
   bind_device_allocator(m);
   bind_store(m);
+  bind_moe_ref(m);
 }

@@ -230,19 +230,25 @@ def combine(yp: torch.Tensor, r: Routing, like: torch.Tensor) -> torch.Tensor:
 
 
 def reference(x, router_w, up, down, spec: Spec):
-    """FP64 token-by-token oracle (no noise): returns (y, aux, z)."""
-    r = route(x.double(), router_w.double(), None, spec, False, 0)
-    Fd = up.shape[1] // 2
-    y = torch.zeros(x.shape, dtype=torch.float64)
-    for t in range(x.shape[0]):
-        for j in range(spec.top_k):
-            if int(r.row[t, j]) < 0:
-                continue
-            e = int(r.expert[t, j])
-            h = up[e].double() @ x[t].double()
-            a = F.silu(h[:Fd]) * h[Fd:]
-            y[t] += float(r.gate[t, j]) * (down[e].double() @ a)
-    return y, float(r.aux), float(r.z)
+    """FP64 token-by-token oracle (no noise): returns (y, aux, z).  Native and independent of the tensor code above
+    (`csrc/host/moe_ref.cpp`: its own router, top-k, capacity / Drop / Reroute walk and expert MLPs)."""
+    y, aux, z, _dropped, _rerouted = reference_full(x, router_w, up, down, spec)
+    return y, aux, z
+
+
+def reference_full(x, router_w, up, down, spec: Spec):
+    """The oracle with its routing statistics: (y [N, d] FP64, aux, z, dropped, rerouted)."""
+    from .. import _native
+    spec.validate()
+    N = x.shape[0]
+    if N % spec.groups:
+        raise ValueError(f"token count {N} must be divisible by groups {spec.groups}")
+    cap = capacity_of(spec, N // spec.groups)
+    np64 = lambda t: t.detach().double().cpu().contiguous().numpy()
+    y, aux, z, dropped, rerouted = _native.moe_reference(np64(x), np64(router_w), np64(up), np64(down), spec.top_k,
+                                                         spec.groups, cap, spec.overflow == "reroute",
+                                                         float(spec.aux_alpha), float(spec.z_alpha))
+    return torch.from_numpy(y), float(aux), float(z), int(dropped), int(rerouted)
 
 
 def quantize_experts(w: torch.Tensor, kind: str):

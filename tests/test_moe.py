@@ -68,3 +68,21 @@ def test_block_scaled_expert_storage_round_trip():
     q1, s1 = quantize_experts(w, "fp8")
     coarse = (dequantize_experts(q1, s1)[:, :, :32] - w[:, :, :32]).norm() / w[:, :, :32].norm()
     assert coarse > 0.5                                    # per-expert scaling loses those columns
+
+
+@pytest.mark.parametrize("groups,overflow", [(1, "drop"), (2, "drop"), (1, "reroute"), (4, "reroute")])
+def test_tensor_core_agrees_with_the_native_fp64_oracle_under_every_policy(groups, overflow):
+    """The native FP64 oracle (its own router, top-k, capacity walk and expert MLPs) against the tensor implementation
+    under tight capacities: outputs, losses, dropped and rerouted counts, with token groups and both overflow policies."""
+    from nexus_b200.moe.moe import moe_forward, reference_full
+    torch.manual_seed(5)
+    s = Spec(experts=8, top_k=2, d_model=16, d_ff=8, capacity_factor=0.6, min_capacity=1, groups=groups, overflow=overflow)
+    x = torch.randn(64, 16)
+    router = torch.randn(16, 8)
+    router[:, 1] *= 3.0
+    up, down = torch.randn(8, 16, 16) * 0.3, torch.randn(8, 16, 8) * 0.3
+    y, r = moe_forward(x, router, None, up, down, s)
+    yr, aux, z, dropped, rerouted = reference_full(x, router, up, down, s)
+    assert dropped == r.dropped and rerouted == r.rerouted and dropped + (rerouted if overflow == "reroute" else 0) > 0
+    assert (y.double() - yr).abs().max() < 1e-5
+    assert float(r.aux) == pytest.approx(aux, rel=1e-6) and float(r.z) == pytest.approx(z, rel=1e-6)
