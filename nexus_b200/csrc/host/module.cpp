@@ -12,6 +12,7 @@ void bind_envs(py::module_& m);
 void bind_device_allocator(py::module_& m);
 void bind_store(py::module_& m);
 void bind_moe_ref(py::module_& m);
+void bind_estimate(py::module_& m);
 
 PYBIND11_MODULE(_native, m) {
   m.doc() = "nexus_b200 native host runtime";
@@ -23,4 +24,5 @@ PYBIND11_MODULE(_native, m) {
   bind_device_allocator(m);
   bind_store(m);
   bind_moe_ref(m);
+  bind_estimate(m);
 }

@@ -8,6 +8,8 @@ by TP (with sequence parallelism) and CP, 2*s*b*h per layer with full recomputat
 Time model: compute = 6*N*tokens (+ attention) / (peak * mfu); TP / CP / DP communication from ring
 volumes over the intra- or inter-node bandwidth; pipeline bubble (pp-1)/(m+pp-1).
 Defaults describe an 8-GPU B200 node (180 GB, measured cuBLAS BF16 rate, NVLink 5 bus bandwidth).
+The arithmetic and the search run in the native host module (`csrc/host/estimate.cpp`); this file holds the
+dataclasses and the command line.
 
     python -m nexus_b200.tools.estimate --preset gpt2-124m --batch 16 --seq 1024 [--auto-parallel --gpus 8]
 
@@ -18,7 +20,7 @@ import argparse
 import json
 import sys
 from dataclasses import asdict, dataclass, field
-from typing import List, Optional
+from typing import Optional
 
 
 @dataclass
@@ -66,50 +68,22 @@ class Plan:
     sequence_parallel: bool = True
 
 
+def _core():
+    from .. import _native
+    return _native
+
+
 def param_breakdown(m: ModelShape) -> dict:
-    d, hd = m.d_model, m.d_model // m.n_head
-    qkv = d * (m.n_head + 2 * m.n_kv_head) * hd + (((m.n_head + 2 * m.n_kv_head) * hd) if m.bias else 0)
-    proj = d * d + (d if m.bias else 0)
-    ffn = (3 if m.ffn_swiglu else 2) * d * m.d_ff + ((m.d_ff + d) if m.bias else 0)
-    norms = 2 * d * (1 if m.rmsnorm else 2)
-    per_layer = qkv + proj + ffn + norms
-    emb = m.vocab * d + m.learned_pos * d
-    head = 0 if m.tie_head else m.vocab * d
-    final_norm = d * (1 if m.rmsnorm else 2)
-    total = m.n_layer * per_layer + emb + head + final_norm
-    return {"embedding": emb, "per_layer": per_layer, "attention": qkv + proj, "ffn": ffn, "norms": norms,
-            "head": head, "final_norm": final_norm, "total": total}
+    return dict(_core().estimate_params(asdict(m)))
 
 
 def flops_per_token(m: ModelShape, causal: bool = True) -> float:
     """Training FLOPs per token: 6 per matrix parameter plus the attention score / value products."""
-    p = param_breakdown(m)
-    matrix = p["total"] - p["embedding"] + (m.vocab * m.d_model if m.tie_head else 0)
-    attn = 12 * m.n_layer * m.d_model * m.seq_len * (0.5 if causal else 1.0)
-    return 6.0 * matrix + attn
+    return float(_core().estimate_flops_per_token(asdict(m), causal))
 
 
 def memory_bytes(m: ModelShape, dt: DTypePlan, plan: Plan) -> dict:
-    n = param_breakdown(m)["total"] / (plan.tp * plan.pp)
-    z = plan.zero_stage
-    params = n * dt.param_bytes / (plan.dp if z >= 3 else 1)
-    grads = n * dt.grad_bytes / (plan.dp if z >= 2 else 1)
-    optim = n * (dt.optim_bytes + dt.master_bytes) / (plan.dp if z >= 1 else 1)
-    s, b, h, a = m.seq_len / plan.cp, m.micro_batch, m.d_model, m.n_head
-    e = dt.activation_elem_bytes / 2.0
-    if plan.full_recompute:
-        per_layer = 2 * s * b * h * e
-    else:
-        per_layer = s * b * h * (34 + (0 if plan.flash_attention else 5 * a * s * plan.cp / h)) * e
-        if plan.tp > 1:
-            per_layer = per_layer / plan.tp if plan.sequence_parallel else (10 + 24 / plan.tp) / 34 * per_layer
-    layers = m.n_layer / plan.pp
-    in_flight = min(plan.pp, max(1, m.gradient_accum)) if plan.pp > 1 else 1     # 1F1B keeps pp micro-batches alive
-    acts = per_layer * layers * in_flight
-    logits = s * b * (m.vocab / plan.tp) * (dt.activation_elem_bytes + 4)
-    total = params + grads + optim + acts + logits
-    return {"params": params, "grads": grads, "optimizer": optim, "activations": acts, "logits": logits,
-            "static": params + grads + optim, "total": total}
+    return dict(_core().estimate_memory(asdict(m), asdict(dt), asdict(plan)))
 
 
 @dataclass
@@ -126,32 +100,7 @@ class Cluster:
 
 
 def step_time(m: ModelShape, plan: Plan, cl: Cluster, dt: DTypePlan = DTypePlan()) -> dict:
-    tokens = m.micro_batch * m.seq_len * m.gradient_accum * plan.dp
-    model_flops = flops_per_token(m) * tokens
-    gpus = plan.dp * plan.tp * plan.pp * plan.cp
-    recompute = 4.0 / 3.0 if plan.full_recompute else 1.0
-    compute = model_flops * recompute / (gpus * cl.peak_tflops * 1e12 * cl.mfu)
-    def bw(group: int) -> float:
-        return (cl.intra_gbps if group <= cl.gpus_per_node else cl.inter_gbps) * 1e9
-    per_rank_tokens = m.micro_batch * m.seq_len / plan.cp * m.gradient_accum
-    tp_comm = 0.0
-    if plan.tp > 1:   # 4 all-reduces (or AG+RS pairs) of [tokens, h] per layer per direction
-        vol = 4 * 2 * (m.n_layer / plan.pp) * per_rank_tokens * m.d_model * dt.activation_elem_bytes
-        tp_comm = vol * 2 * (plan.tp - 1) / plan.tp / bw(plan.tp)
-    cp_comm = 0.0
-    if plan.cp > 1:   # K/V blocks travel around the ring once per layer, forward and backward
-        kv = 2 * per_rank_tokens * (m.d_model * m.n_kv_head / m.n_head) * dt.activation_elem_bytes
-        cp_comm = 0.3 * 3 * (m.n_layer / plan.pp) * kv * (plan.cp - 1) / bw(plan.tp * plan.cp)
-    dp_comm = 0.0
-    if plan.dp > 1:
-        n = param_breakdown(m)["total"] / (plan.tp * plan.pp)
-        vol = n * dt.grad_bytes * 2 * (plan.dp - 1) / plan.dp + (n * dt.param_bytes if plan.zero_stage >= 3 else 0)
-        dp_comm = (1 - cl.dp_overlap) * vol / bw(gpus)
-    bubble = (plan.pp - 1) / (m.gradient_accum + plan.pp - 1) if plan.pp > 1 else 0.0
-    step = (compute + tp_comm + cp_comm) / (1 - bubble) + dp_comm
-    return {"tokens": tokens, "model_flops": model_flops, "compute_s": compute, "tp_comm_s": tp_comm, "cp_comm_s": cp_comm,
-            "dp_comm_s": dp_comm, "bubble": bubble, "step_s": step, "tokens_per_s": tokens / step,
-            "mfu": model_flops / (step * gpus * cl.peak_tflops * 1e12)}
+    return dict(_core().estimate_step_time(asdict(m), asdict(plan), asdict(cl), asdict(dt)))
 
 
 @dataclass
@@ -190,43 +139,15 @@ class Candidate:
 
 def evaluate(m: ModelShape, cl: Cluster, dp, tp, pp, cp, zero, micro, accum, recompute=False,
              dt: DTypePlan = DTypePlan()) -> Candidate:
-    shape = ModelShape(**{**asdict(m), "micro_batch": micro, "gradient_accum": accum})
-    plan = Plan(dp, tp, pp, cp, zero, recompute)
-    mem = memory_bytes(shape, dt, plan)
-    t = step_time(shape, plan, cl, dt)
-    gib = 1 << 30
-    c = Candidate(dp, tp, pp, cp, zero, micro, accum, mem["total"] / gib, mem["static"] / gib, mem["activations"] / gib,
-                  mem["logits"] / gib, t["compute_s"], t["tp_comm_s"], t["cp_comm_s"], t["dp_comm_s"], t["bubble"],
-                  t["step_s"], t["mfu"], recompute=recompute)
-    c.fits = c.memory_gib + cl.reserve_gib <= cl.mem_gib
-    return c
+    return Candidate(**_core().estimate_evaluate(asdict(m), asdict(cl), dp, tp, pp, cp, zero, micro, accum, bool(recompute),
+                                                 asdict(dt)))
 
 
-def auto_parallel(m: ModelShape, cl: Cluster, opt: AutoOptions = AutoOptions()) -> dict:
+def auto_parallel(m: ModelShape, cl: Cluster, opt: AutoOptions = AutoOptions(), dt: DTypePlan = DTypePlan()) -> dict:
     """Exhaustive search over factorizations of the GPU count; ranks the layouts that fit by step time."""
-    def divisors(n):
-        return [i for i in range(1, n + 1) if n % i == 0]
-    cands: List[Candidate] = []
-    tried = 0
-    for tp in [t for t in divisors(cl.gpus) if t <= opt.max_tp and m.n_head % t == 0 and t <= cl.gpus_per_node]:
-        for pp in [p for p in divisors(cl.gpus // tp) if p <= opt.max_pp and m.n_layer % p == 0]:
-            for cp in [c for c in divisors(cl.gpus // (tp * pp)) if c <= opt.max_cp and m.seq_len % (2 * c) == 0]:
-                dp = cl.gpus // (tp * pp * cp)
-                if opt.global_batch % dp:
-                    continue
-                per_dp = opt.global_batch // dp
-                for micro in opt.micro_batches:
-                    if per_dp % micro:
-                        continue
-                    accum = per_dp // micro
-                    for zero in ((0, 1, 2, 3) if dp > 1 else (0,)):
-                        for rec in (False, True):
-                            tried += 1
-                            c = evaluate(m, cl, dp, tp, pp, cp, zero, micro, accum, rec)
-                            if c.fits:
-                                cands.append(c)
-    cands.sort(key=lambda c: (c.step_s, c.tp * c.pp * c.cp, c.zero))
-    return {"tried": tried, "feasible": len(cands), "best": [asdict(c) for c in cands[: opt.top]]}
+    r = _core().estimate_auto_parallel(asdict(m), asdict(cl), opt.global_batch, opt.max_tp, opt.max_pp, opt.max_cp, opt.top,
+                                       [int(x) for x in opt.micro_batches], asdict(dt))
+    return {"tried": int(r["tried"]), "feasible": int(r["feasible"]), "best": [dict(c) for c in r["best"]]}
 
 
 def main(argv=None) -> int:

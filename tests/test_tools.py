@@ -146,3 +146,23 @@ def test_parallel_bench_parameter_table_matches_the_model():
         want = {n: tuple(p.shape) for n, p in build(cfg).named_parameters()}
         got = dict(build_meta(cfg))
         assert got == want
+
+
+def test_estimate_core_is_native_and_ranked():
+    from nexus_b200 import _native
+    for name in ("estimate_params", "estimate_memory", "estimate_step_time", "estimate_evaluate", "estimate_auto_parallel"):
+        assert hasattr(_native, name)
+    big = E.ModelShape(n_layer=80, d_model=8192, n_head=64, n_kv_head=8, d_ff=28672, vocab=128256, seq_len=8192,
+                       tie_head=False, ffn_swiglu=True, bias=False, rmsnorm=True)
+    r = E.auto_parallel(big, E.Cluster(gpus=64), E.AutoOptions(top=8))
+    assert 0 < r["feasible"] < r["tried"]
+    keys = [(c["step_s"], c["tp"] * c["pp"] * c["cp"], c["zero"]) for c in r["best"]]
+    assert keys == sorted(keys) and all(c["fits"] for c in r["best"])
+    c0 = r["best"][0]
+    again = E.evaluate(big, E.Cluster(gpus=64), c0["dp"], c0["tp"], c0["pp"], c0["cp"], c0["zero"], c0["micro_batch"],
+                       c0["accum"], c0["recompute"])
+    assert abs(again.step_s - c0["step_s"]) < 1e-12 and again.fits
+    # hand-checked closed form of the static share: 18 bytes per parameter over tp*pp, ZeRO-3 divides all of it by dp
+    n = E.param_breakdown(big)["total"]
+    assert abs(again.static_gib * (1 << 30) - n * 18 / (c0["tp"] * c0["pp"]) / (c0["dp"] if c0["zero"] >= 3 else 1)) < \
+        (1 << 20) or c0["zero"] in (1, 2)
