@@ -53,7 +53,7 @@ class GptModel:
     def __init__(self, config: LmConfig, device="cuda", seed: Optional[int] = None, vocab_pad: int = 128,
                  recompute: str = "none", recompute_every: int = 2, optimizer: str = "adamw", master: str = "fp32",
                  compute_dtype: str = "bf16", offload_grad_dtype: str = "bf16", dynamic_loss_scale: bool = False,
-                 loss_scale_init: float = 65536.0, loss_scale_growth_interval: int = 2000):
+                 loss_scale_init: float = 65536.0, loss_scale_growth_interval: int = 2000, ce_chunk_rows: Optional[int] = None):
         """``recompute`` (activation memory against recomputation in the backward pass; include/nexus/cuda/gpt.hpp:66 of
         the reference): "none" keeps every activation; "selective" keeps the GEMM outputs (qkv, attention output,
         MLP pre-activation) and recomputes the norm outputs and the GELU output; "full" keeps only the residual stream
@@ -64,7 +64,11 @@ class GptModel:
         by the optimizer kernel) or "cast_per_forward" (the working copy is re-cast from the FP32 parameters at the
         start of every forward pass).  Anything else the reference's model offers (FP16 with a loss scale, BF16-only
         weights with stochastic rounding, the 8-bit optimizer applied layer by layer inside the backward pass) is
-        refused here with an error rather than ignored."""
+        refused here with an error rather than ignored.
+        ``ce_chunk_rows`` (`GptConfig::ce_chunk_rows` of include/nexus/cuda/gpt.hpp; default from
+        ``NEXUS_B200_CE_CHUNK_ROWS``, else 0): 0 keeps one [B*T, V] logits
+        buffer; a positive value runs the LM head, the fused cross-entropy and the head's two backward GEMMs over
+        groups of whole sequences of at most that many rows, so that only one group's logits exist at a time."""
         if recompute not in self.RECOMPUTE:
             raise ValueError(f"GptModel: recompute must be one of {self.RECOMPUTE}, got {recompute!r}")
         if optimizer not in self.OPTIMIZERS:
@@ -80,6 +84,11 @@ class GptModel:
             raise ValueError("GptModel: recompute_every must be >= 1")
         if optimizer == "zero_offload" and master != "fp32":
             raise ValueError("GptModel: zero_offload keeps the FP32 master on the host (master must be 'fp32')")
+        if ce_chunk_rows is None:
+            ce_chunk_rows = int(os.environ.get("NEXUS_B200_CE_CHUNK_ROWS", "0"))
+        if ce_chunk_rows < 0:
+            raise ValueError("GptModel: ce_chunk_rows must be >= 0")
+        self.ce_chunk_rows = int(ce_chunk_rows)
         self.recompute, self.recompute_every = recompute, recompute_every
         self.optimizer_kind, self.master_mode = optimizer, master
         self.offload_grad_dtype = torch.bfloat16 if offload_grad_dtype == "bf16" else torch.float32
@@ -275,7 +284,7 @@ class GptModel:
             "fch": torch.empty((cnt["fch"], N, F), dtype=bf, device=dev),
             "lnf": torch.empty((N, C), dtype=bf, device=dev),
             "lnf_mean": torch.empty(N, dtype=f32, device=dev), "lnf_rstd": torch.empty(N, dtype=f32, device=dev),
-            "logits": torch.empty((N, self.Vp), dtype=bf, device=dev),
+            "logits": torch.empty((self._head_group(B, T) * T, self.Vp), dtype=bf, device=dev),
             # backward scratch (reused by every layer)
             "dres_a": torch.empty((N, C), dtype=f32, device=dev), "dres_b": torch.empty((N, C), dtype=f32, device=dev),
             "dres_lp": torch.empty((N, C), dtype=bf, device=dev),
@@ -287,6 +296,16 @@ class GptModel:
         }
         self._acts, self._acts_key = a, key
         return a
+
+    def _head_group(self, B: int, T: int) -> int:
+        """Sequences per pass of the LM head and the loss: all of them unless ``ce_chunk_rows`` asks for less; always a
+        divisor of B, so that every group has the same number of targets and the mean of the group means is the mean."""
+        if self.ce_chunk_rows <= 0 or self.ce_chunk_rows >= B * T:
+            return B
+        k = max(1, self.ce_chunk_rows // T)
+        while B % k:
+            k -= 1
+        return k
 
     # ------------------------------------------------------------------------------------ forward
     def forward(self, tokens: torch.Tensor, *, want_logits: bool = True):
@@ -302,8 +321,15 @@ class GptModel:
         for l in range(L):
             self._layer_forward(a, l, B, T, output=True)
         _norm_into(a["lnf"], a["lnf_mean"], a["lnf_rstd"], res[2 * L], self.p["lnf_w"], self.p["lnf_b"])
-        if want_logits:
-            K.gemm(a["lnf"], w["wte"], out=a["logits"])
+        if not want_logits:
+            return None
+        if a["logits"].shape[0] != N:     # the training buffer holds one group only: whole logits on request
+            full = a.get("logits_full")
+            if full is None:
+                full = a["logits_full"] = torch.empty((N, self.Vp), dtype=torch.bfloat16, device=self.device)
+            K.gemm(a["lnf"], w["wte"], out=full)
+            return full
+        K.gemm(a["lnf"], w["wte"], out=a["logits"])
         return a["logits"]
 
     STAGE_HEAD, STAGE_EMBEDDING = -1, -2
@@ -365,16 +391,23 @@ class GptModel:
         N = B * T
         a = self._alloc_acts(B, T)
         w, g, L, C, F = self.w, self.g, self.L, self.C, self.F
-        logits = self.forward(tokens)
-        K.cross_entropy_shifted(logits, tokens, vocab=self.V, smoothing=smoothing, z_loss=z_loss,
-                                grad_scale=grad_scale, loss_out=self.loss_buf, loss_weight=loss_weight,
-                                accumulate_loss=accumulate_loss, seq_len=T,
-                                grad_scale_dev=self._loss_scale_dev if self.dynamic_loss_scale else None)
-        dlogits = logits
+        self.forward(tokens, want_logits=False)
         res = a["res"]
-        # head: dlnf = dlogits @ wte ; dwte += dlogits^T @ lnf
-        K.gemm(dlogits, w["wte"], b_mn=True, out=a["dlnf"])
-        K.gemm(dlogits, a["lnf"], a_mn=True, b_mn=True, out=g["wte"], accumulate=True)
+        # head, per group of whole sequences (one group unless ce_chunk_rows is set):
+        # logits = lnf @ wte^T ; CE turns them into dlogits ; dlnf = dlogits @ wte ; dwte += dlogits^T @ lnf
+        k = self._head_group(B, T)
+        groups, rows = B // k, k * T
+        dlogits = a["logits"]
+        for c in range(groups):
+            r0 = c * rows
+            lnf_c = a["lnf"][r0:r0 + rows]
+            K.gemm(lnf_c, w["wte"], out=dlogits)
+            K.cross_entropy_shifted(dlogits, tokens[c * k:(c + 1) * k], vocab=self.V, smoothing=smoothing, z_loss=z_loss,
+                                    grad_scale=grad_scale / groups, loss_out=self.loss_buf,
+                                    loss_weight=loss_weight / groups, accumulate_loss=accumulate_loss or c > 0, seq_len=T,
+                                    grad_scale_dev=self._loss_scale_dev if self.dynamic_loss_scale else None)
+            K.gemm(dlogits, w["wte"], b_mn=True, out=a["dlnf"][r0:r0 + rows])
+            K.gemm(dlogits, lnf_c, a_mn=True, b_mn=True, out=g["wte"], accumulate=True)
         dres, dres_other, dres_lp = a["dres_a"], a["dres_b"], a["dres_lp"]
         # each norm backward also sums the columns of its BF16 dx: the bias gradient of the projection that follows
         K.norm_bwd(a["dlnf"], res[2 * L], self.p["lnf_w"], a["lnf_mean"], a["lnf_rstd"], dx=dres, dx_lp=dres_lp,
@@ -566,10 +599,16 @@ class GptModel:
 
     # ---------------------------------------------------------------------------------- utilities
     def loss(self, tokens: torch.Tensor) -> float:
-        logits = self.forward(tokens)
+        self.forward(tokens, want_logits=False)
         B, T = tokens.shape
+        a = self._acts
+        k = self._head_group(B, T)
+        groups, rows = B // k, k * T
         out = torch.zeros(1, dtype=torch.float32, device=self.device)
-        K.cross_entropy_shifted(logits, tokens, vocab=self.V, write_grad=False, loss_out=out, seq_len=T)
+        for c in range(groups):
+            K.gemm(a["lnf"][c * rows:(c + 1) * rows], self.w["wte"], out=a["logits"])
+            K.cross_entropy_shifted(a["logits"], tokens[c * k:(c + 1) * k], vocab=self.V, write_grad=False, loss_out=out,
+                                    loss_weight=1.0 / groups, accumulate_loss=c > 0, seq_len=T)
         return float(out.item())
 
     def state_dict(self) -> Dict[str, torch.Tensor]:

@@ -29,7 +29,7 @@ class GptLmBackend(LmBackend):
     def __init__(self, config: LmConfig, micro_batch: int, seq_len: int, device="cuda", seed: int = 1234,
                  deterministic: bool = False, recompute: str = "none", recompute_every: int = 2,
                  optimizer: str = "adamw", master: str = "fp32", compute_dtype: str = "bf16",
-                 dynamic_loss_scale=(False, 65536.0, 2000)):
+                 dynamic_loss_scale=(False, 65536.0, 2000), ce_chunk_rows: Optional[int] = None):
         self.dev = torch.device(device)
         if self.dev.index is None:
             self.dev = torch.device("cuda", torch.cuda.current_device())
@@ -38,7 +38,7 @@ class GptLmBackend(LmBackend):
         self.model = GptModel(config, device=self.dev, seed=seed, recompute=recompute, recompute_every=recompute_every,
                               optimizer=optimizer, master=master, compute_dtype=compute_dtype,
                               dynamic_loss_scale=dynamic_loss_scale[0], loss_scale_init=dynamic_loss_scale[1],
-                              loss_scale_growth_interval=dynamic_loss_scale[2])
+                              loss_scale_growth_interval=dynamic_loss_scale[2], ce_chunk_rows=ce_chunk_rows)
         self.model.deterministic_embedding = deterministic
         self.B, self.T = micro_batch, seq_len
         self._host_tokens = [torch.empty((micro_batch, seq_len), dtype=torch.int32).pin_memory() for _ in range(2)]

@@ -246,6 +246,7 @@ class LanguageTrainerBuilder:
         self._precision, self._master = "bf16", "fp32"
         self._recompute = "none"
         self._recompute_every = 2
+        self._ce_chunk_rows = None
         self._optimizer_kind = "adamw"
         self._eval_every, self._eval_batches, self._log_every = 0, 4, 1
         self._seed = 1234
@@ -278,6 +279,10 @@ class LanguageTrainerBuilder:
     def precision(self, p: str, master: str = "fp32"): self._precision, self._master = p.lower(), master.lower(); return self
     def recompute(self, r: str, every: int = 2): self._recompute, self._recompute_every = r, every; return self
     def optimizer_kind(self, kind: str): self._optimizer_kind = kind; return self
+    def ce_chunk_rows(self, rows: int):
+        """GPU model backend: run the LM head and the loss over groups of whole sequences of at most ``rows`` rows
+        (0: one pass), so that only one group's logits are alive."""
+        self._ce_chunk_rows = int(rows); return self
     def dynamic_loss_scale(self, enabled: bool = True, init: float = 65536.0, growth_interval: int = 2000):
         """Device-resident dynamic loss scale of the GPU model backend (off by default; BF16 rarely needs it)."""
         self._dynamic_loss_scale = (bool(enabled), float(init), int(growth_interval))
@@ -342,7 +347,8 @@ def _make_backend(b: LanguageTrainerBuilder) -> LmBackend:
             return GptLmBackend(cfg, b._micro_batch, b._seq_len, device=b._device, seed=b._seed,
                                 deterministic=b._deterministic, recompute=b._recompute,
                                 recompute_every=b._recompute_every, optimizer=b._optimizer_kind, master=master,
-                                dynamic_loss_scale=getattr(b, "_dynamic_loss_scale", (False, 65536.0, 2000)))
+                                dynamic_loss_scale=getattr(b, "_dynamic_loss_scale", (False, 65536.0, 2000)),
+                                ce_chunk_rows=b._ce_chunk_rows)
         from ..lm.model import LanguageModel
         model = LanguageModel(cfg)
     from .torch_backend import TorchLmBackend

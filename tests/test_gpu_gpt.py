@@ -192,3 +192,35 @@ def test_unimplemented_modes_are_refused_not_ignored():
     for kw in ({"optimizer": "adamw8bit_fused"}, {"master": "none"}, {"compute_dtype": "f16"}, {"recompute": "sometimes"}):
         with pytest.raises(ValueError):
             GptModel(cfg, device="cuda", **kw)
+
+
+@pytest.mark.parametrize("chunk_rows", [128, 256, 300])
+def test_chunked_head_and_loss_match_the_single_pass(chunk_rows):
+    from nexus_b200.models.gpt import GptModel
+    from nexus_b200.ops import _cuda as K
+    """LM head + cross-entropy + head backward over groups of whole sequences: same loss and gradients as one pass over
+    all rows (only the summation order of the embedding gradient and of the loss differs), a smaller logits buffer,
+    and `loss()` / `forward()` still see every row."""
+    cfg = _tiny_cfg()
+    tokens = torch.randint(0, cfg.vocab_size, (4, 128), dtype=torch.int32, device="cuda",
+                           generator=torch.Generator(device="cuda").manual_seed(11))
+    base = GptModel(cfg, device="cuda", seed=5, ce_chunk_rows=0)
+    base.deterministic_embedding = True
+    other = GptModel(cfg, device="cuda", seed=5, ce_chunk_rows=chunk_rows)
+    other.deterministic_embedding = True
+    assert other._head_group(4, 128) == {128: 1, 256: 2, 300: 2}[chunk_rows]
+    l0 = float(base.forward_backward(tokens).item())
+    l1 = float(other.forward_backward(tokens).item())
+    torch.cuda.synchronize()
+    K.check_status()
+    assert abs(l0 - l1) < 1e-5 * abs(l0), (l0, l1)
+    rel = (other.grads - base.grads).norm().item() / base.grads.norm().item()
+    assert rel < 2e-3, rel
+    assert other._acts["logits"].shape[0] == other._head_group(4, 128) * 128 < base._acts["logits"].shape[0]
+    assert abs(other.loss(tokens) - base.loss(tokens)) < 1e-5 * abs(l0)
+    full, ref = other.forward(tokens), base.forward(tokens)
+    assert full.shape == ref.shape and torch.allclose(full.float(), ref.float(), atol=1e-2, rtol=1e-2)
+    # a second micro-step accumulates the loss like the single pass does
+    a0 = float(base.forward_backward(tokens, accumulate_loss=True, loss_weight=0.5).item())
+    a1 = float(other.forward_backward(tokens, accumulate_loss=True, loss_weight=0.5).item())
+    assert abs(a0 - a1) < 1e-5 * abs(a0)
