@@ -13,6 +13,7 @@ void bind_device_allocator(py::module_& m);
 void bind_store(py::module_& m);
 void bind_moe_ref(py::module_& m);
 void bind_estimate(py::module_& m);
+void bind_dlpack(py::module_& m);
 
 PYBIND11_MODULE(_native, m) {
   m.doc() = "nexus_b200 native host runtime";
@@ -25,4 +26,5 @@ PYBIND11_MODULE(_native, m) {
   bind_store(m);
   bind_moe_ref(m);
   bind_estimate(m);
+  bind_dlpack(m);
 }

@@ -162,3 +162,22 @@ def test_gated_activation_autograd_matches_fp32_formula(kind):
     (ref * t).sum().backward()
     assert (y.float() - ref).abs().max() < 2e-2 * ref.abs().max()
     assert (h.grad.float() - h2.grad).abs().max() < 2e-2 * h2.grad.abs().max()
+
+
+def test_dlpack_exchange_on_the_device_and_pinned_host():
+    """The native DLPack producer / consumer on CUDA memory and pinned host memory: zero copy in both directions."""
+    from nexus_b200.interop import dlpack
+    t = torch.arange(24, dtype=torch.float32, device="cuda").reshape(4, 6)
+    assert dlpack.device_type(t) == dlpack.K_CUDA
+    u = torch.from_dlpack(dlpack.to_dlpack(t))
+    assert u.is_cuda and u.data_ptr() == t.data_ptr()
+    v = dlpack.from_dlpack(torch.utils.dlpack.to_dlpack(t))
+    v[0, 0] = 5.0
+    assert v.is_cuda and v.device == t.device and float(t[0, 0]) == 5.0
+    w = dlpack.from_dlpack(dlpack.to_dlpack(t.t()))
+    assert tuple(w.shape) == (6, 4) and torch.equal(w, t.t())
+    h = torch.ones(8, dtype=torch.float32).pin_memory()
+    assert dlpack.device_type(h) == dlpack.K_CUDA_HOST
+    g = dlpack.from_dlpack(dlpack.to_dlpack(h))
+    g[3] = 2.0
+    assert float(h[3]) == 2.0 and not g.is_cuda

@@ -123,6 +123,77 @@ def test_dlpack_zero_copy():
         dlpack.to_dlpack(t.half())
 
 
+def test_dlpack_native_capsules_interoperate_with_torch_and_numpy():
+    """Capsules made by the native producer are consumed by torch; capsules made by torch and numpy are consumed by the
+    native reader; strided views keep their geometry; a capsule is consumed once; anything but FP32 is refused and
+    stays with its producer."""
+    import numpy as np
+    t = torch.arange(12, dtype=torch.float32).reshape(3, 4)
+    cap = dlpack.to_dlpack(t)
+    u = torch.from_dlpack(cap)
+    u[0, 0] = 42.0
+    assert t[0, 0] == 42.0
+    with pytest.raises(ValueError, match="already consumed"):
+        dlpack.from_dlpack(cap)
+    v = dlpack.from_dlpack(torch.utils.dlpack.to_dlpack(t))
+    v[1, 1] = 7.0
+    assert t[1, 1] == 7.0 and tuple(v.shape) == (3, 4)
+    w = dlpack.from_dlpack(dlpack.to_dlpack(t.t()[1:]))
+    assert tuple(w.shape) == (3, 3) and w.stride() == (1, 4) and torch.equal(w, t.t()[1:])
+    a = np.ones((2, 5), dtype=np.float32)
+    x = dlpack.from_dlpack(a)
+    x[0, 0] = 3.0
+    assert a[0, 0] == 3.0
+    with pytest.raises(ValueError, match="FP32"):
+        dlpack.from_dlpack(np.ones(3))
+    with pytest.raises(ValueError, match="capsule"):
+        dlpack.from_dlpack(object())
+    assert tuple(dlpack.from_dlpack(dlpack.to_dlpack(torch.empty(0, 3))).shape) == (0, 3)
+    from nexus_b200.core.tensor import Tensor
+    z = dlpack.from_dlpack(dlpack.to_dlpack(Tensor.from_torch(t)), as_tensor=True)
+    assert isinstance(z, Tensor) and z.torch().data_ptr() == t.data_ptr()
+
+
+def test_dlpack_owner_lives_exactly_as_long_as_the_consumer():
+    import gc
+    import weakref
+
+    import numpy as np
+    from nexus_b200 import _native
+
+    class Owner:
+        def __init__(self):
+            self.mem = np.full(6, 2.0, dtype=np.float32)
+
+    # consumed capsule: the owner dies when the imported view dies, not when the capsule does
+    o = Owner()
+    alive = weakref.ref(o)
+    cap = _native.dlpack_export(o.mem.ctypes.data, [2, 3], [], 32, dlpack.K_CPU, 0, o)
+    del o
+    gc.collect()
+    assert alive() is not None
+    y = dlpack.from_dlpack(cap)
+    del cap
+    gc.collect()
+    assert alive() is not None and float(y.sum()) == 12.0
+    del y
+    gc.collect()
+    assert alive() is None
+    # capsule nobody consumed: dropping it releases the owner
+    o = Owner()
+    alive = weakref.ref(o)
+    cap = _native.dlpack_export(o.mem.ctypes.data, [6], [], 32, dlpack.K_CPU, 0, o)
+    del o, cap
+    gc.collect()
+    assert alive() is None
+    with pytest.raises(ValueError):
+        _native.dlpack_export(0, [4], [], 32, dlpack.K_CPU, 0, None)
+    with pytest.raises(ValueError):
+        _native.dlpack_export(8, [4], [], 16, dlpack.K_CPU, 0, None)
+    with pytest.raises(ValueError):
+        _native.dlpack_export(8, [4], [], 32, 7, 0, None)
+
+
 def test_onnx_export_structure(tmp_path):
     from nexus_b200.interop import onnx as O
     from nexus_b200.lm.config import preset
