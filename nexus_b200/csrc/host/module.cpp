@@ -14,6 +14,7 @@ void bind_store(py::module_& m);
 void bind_moe_ref(py::module_& m);
 void bind_estimate(py::module_& m);
 void bind_dlpack(py::module_& m);
+void bind_token_data(py::module_& m);
 
 PYBIND11_MODULE(_native, m) {
   m.doc() = "nexus_b200 native host runtime";
@@ -27,4 +28,5 @@ PYBIND11_MODULE(_native, m) {
   bind_moe_ref(m);
   bind_estimate(m);
   bind_dlpack(m);
+  bind_token_data(m);
 }

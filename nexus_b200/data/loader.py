@@ -38,8 +38,11 @@ class GpuTokenLoader:
                 host, dev = self._free.get()
                 if self._stop:
                     return
-                rows = self.source.next_rows(self.B, self.T)
-                host.copy_(torch.from_numpy(np.asarray(rows, dtype=np.int32)))
+                if hasattr(self.source, "next_into"):     # native reader: decode straight into the pinned buffer
+                    self.source.next_into(host.data_ptr(), self.B, self.T)
+                else:
+                    rows = self.source.next_rows(self.B, self.T)
+                    host.copy_(torch.from_numpy(np.asarray(rows, dtype=np.int32)))
                 ev = None
                 if self.cuda:
                     with torch.cuda.stream(self._stream):

@@ -1,6 +1,6 @@
 from .language import LanguageTrainer, TokenRows  # noqa: F401
 from .lm_trainer import (AdamW, ArrayTokens, LanguageModelTrainer, LanguageTrainerBuilder, LmBackend, LmParamInfo,  # noqa: F401
-                         LmStepResult, NanOptions, ParamGroupPolicy, ParamGroupRule, SpikeOptions, StepRecord,
+                         LmStepResult, NanOptions, ParamGroupPolicy, ParamGroupRule, ShardTokens, SpikeOptions, StepRecord,
                          SyntheticTokens, TokenSource, TrainSummary)
 from .loggers import (ConsoleLogger, CsvLogger, JsonlLogger, TensorBoardLogger, WandbOfflineLogger,  # noqa: F401
                       read_tensorboard_scalars)

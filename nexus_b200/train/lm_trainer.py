@@ -194,6 +194,43 @@ class ArrayTokens(TokenSource):
         self.cursor = cursor // self.world
 
 
+class ShardTokens(TokenSource):
+    """Token shards written by ``nexus_b200.tools.tokenize`` (NXTK files), memory-mapped and read by the native
+    reader (`csrc/host/token_data.cpp`): windows of ``seq_len`` tokens numbered across the shards, optionally in a
+    keyed per-epoch permutation, rank ``r`` of ``w`` taking the rows ``cursor * w + r``; a worker thread keeps
+    ``prefetch`` batches decoded ahead.  The global cursor is the whole state (resume, resharding)."""
+
+    def __init__(self, paths, seq_len: int, rank: int = 0, world: int = 1, seed: int = 0, shuffle: bool = False,
+                 prefetch: int = 2):
+        from .. import _native
+        if isinstance(paths, (str, bytes)) or hasattr(paths, "__fspath__"):
+            paths = [paths]
+        self.paths = [str(p) for p in paths]
+        self.seq_len = seq_len
+        self._r = _native.TokenShards(self.paths, seq_len, rank, world, seed, shuffle, prefetch)
+
+    def next_rows(self, rows: int, seq_len: int) -> np.ndarray:
+        return self._r.next_rows(rows, seq_len)
+
+    def next_into(self, ptr: int, rows: int, seq_len: int) -> None:
+        """Decodes the next ``rows`` rows straight into caller memory (``rows * seq_len`` int32 at ``ptr``)."""
+        if seq_len != self.seq_len:
+            raise ValueError("ShardTokens: seq_len differs from the one the windows were cut for")
+        self._r.next_into(ptr, rows)
+
+    def global_cursor(self) -> int:
+        return self._r.global_cursor()
+
+    def seek(self, cursor: int) -> None:
+        self._r.seek(cursor)
+
+    def windows(self) -> int:
+        return self._r.windows()
+
+    def vocab(self) -> int:
+        return self._r.vocab()
+
+
 # ------------------------------------------------------------------------------------------ backend
 class LmBackend:
     """What the trainer needs from a model + optimizer implementation."""
