@@ -15,6 +15,7 @@ void bind_moe_ref(py::module_& m);
 void bind_estimate(py::module_& m);
 void bind_dlpack(py::module_& m);
 void bind_token_data(py::module_& m);
+void bind_kv_sched(py::module_& m);
 
 PYBIND11_MODULE(_native, m) {
   m.doc() = "nexus_b200 native host runtime";
@@ -29,4 +30,5 @@ PYBIND11_MODULE(_native, m) {
   bind_estimate(m);
   bind_dlpack(m);
   bind_token_data(m);
+  bind_kv_sched(m);
 }

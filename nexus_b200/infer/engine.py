@@ -27,6 +27,8 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
+from .. import _native
+
 __all__ = ["Gpt2Weights", "QuantOptions", "EngineConfig", "SamplingParams", "Chunk", "StepStats", "Engine",
            "GenerateStats", "SpecStats", "generate", "speculative_generate", "load_gpt2"]
 
@@ -175,16 +177,6 @@ class StepStats:
     ms: float = 0.0
 
 
-class _Seq:
-    __slots__ = ("blocks", "length", "tokens", "n_prompt")
-
-    def __init__(self):
-        self.blocks: List[int] = []
-        self.length = 0
-        self.tokens: List[int] = []
-        self.n_prompt = 0
-
-
 # ------------------------------------------------------------------------------------------ linear layers
 class _Linear:
     """One linear layer in the engine's storage format (dense BF16/FP32, INT8 or INT4)."""
@@ -275,8 +267,8 @@ class Engine:
         self.wdt = torch.bfloat16 if self.fast else torch.float32
         self._load(weights)
         self._alloc_kv()
-        self.seqs: Dict[int, _Seq] = {}
-        self._free_ids = list(range(cfg.max_seqs - 1, -1, -1))
+        # sequences, block lists, reference counts and batch packing live in the native scheduler
+        self.sched = _native.KvScheduler(self.n_blocks, cfg.block_size, cfg.max_seqs, self.ctx)
         self.block_table = torch.zeros((cfg.max_seqs, self.max_blocks), dtype=torch.int32, device=self.dev)
         self.counts_all = torch.zeros((cfg.max_seqs, self.V), dtype=torch.int32, device=self.dev)
         self.counts_out = torch.zeros((cfg.max_seqs, self.V), dtype=torch.int32, device=self.dev)
@@ -399,69 +391,46 @@ class Engine:
             self.v_scale = [torch.ones((self.n_blocks * bs, Hl), dtype=torch.float32, device=self.dev) for _ in range(self.L)]
         else:
             self.k_scale = self.v_scale = [None] * self.L
-        self.refcount = [0] * self.n_blocks
-        self.free_list = list(range(self.n_blocks - 1, -1, -1))
 
     # ----------------------------------------------------------------------------- sequences / blocks
     def add_sequence(self) -> int:
-        if not self._free_ids:
-            raise RuntimeError("no free sequence slot (max_seqs reached)")
-        sid = self._free_ids.pop()
-        self.seqs[sid] = _Seq()
+        sid = self.sched.add()
         self.counts_all[sid].zero_()
         self.counts_out[sid].zero_()
         return sid
 
     def fork_sequence(self, src: int) -> int:
         """New sequence sharing every block of ``src`` (copy-on-write on the next append)."""
-        s = self.seqs[src]
-        sid = self.add_sequence()
-        n = self.seqs[sid]
-        n.blocks, n.length, n.tokens, n.n_prompt = list(s.blocks), s.length, list(s.tokens), s.n_prompt
-        for b in n.blocks:
-            self.refcount[b] += 1
+        sid = self.sched.fork(src)
         self.counts_all[sid].copy_(self.counts_all[src])
         self.counts_out[sid].copy_(self.counts_out[src])
         self._write_table(sid)
         return sid
 
     def free_sequence(self, seq: int) -> None:
-        s = self.seqs.pop(seq)
-        for b in s.blocks:
-            self._release(b)
-        self._free_ids.append(seq)
+        self.sched.free(seq)
 
     def truncate(self, seq: int, length: int) -> None:
-        s = self.seqs[seq]
-        if length < 0 or length > s.length:
-            raise ValueError("truncate: bad length")
-        if length == s.length:
+        removed, n_out = self.sched.truncate(seq, length)
+        if not removed:
             return
-        keep = -(-length // self.cfg.block_size)
-        for b in s.blocks[keep:]:
-            self._release(b)
-        removed = s.tokens[length:]
-        s.blocks, s.length, s.tokens = s.blocks[:keep], length, s.tokens[:length]
         # counters: remove the dropped tokens (host list -> one small device update)
-        if removed:
-            t = torch.tensor(removed, dtype=torch.long, device=self.dev)
-            ones = torch.ones_like(t, dtype=torch.int32)
-            self.counts_all[seq].index_add_(0, t, -ones)
-            n_out = s.length + len(removed) - max(s.n_prompt, length)
-            if n_out > 0:
-                t2 = t[len(removed) - n_out:]
-                self.counts_out[seq].index_add_(0, t2, -ones[: t2.numel()])
-        s.n_prompt = min(s.n_prompt, length)
+        t = torch.tensor(removed, dtype=torch.long, device=self.dev)
+        ones = torch.ones_like(t, dtype=torch.int32)
+        self.counts_all[seq].index_add_(0, t, -ones)
+        if n_out > 0:
+            t2 = t[len(removed) - n_out:]
+            self.counts_out[seq].index_add_(0, t2, -ones[: t2.numel()])
         self._write_table(seq)
 
     def length(self, seq: int) -> int:
-        return self.seqs[seq].length
+        return self.sched.length(seq)
 
     def tokens(self, seq: int) -> List[int]:
-        return self.seqs[seq].tokens
+        return self.sched.tokens(seq)
 
     def free_blocks(self) -> int:
-        return len(self.free_list)
+        return self.sched.free_blocks()
 
     def total_blocks(self) -> int:
         return self.n_blocks
@@ -471,56 +440,23 @@ class Engine:
 
     def blocks_needed(self, seq: int, new_tokens: int) -> int:
         """Blocks that appending ``new_tokens`` would take from the free list (copy-on-write included)."""
-        s = self.seqs[seq]
-        bs = self.cfg.block_size
-        need = -(-(s.length + new_tokens) // bs) - len(s.blocks)
-        if new_tokens > 0 and s.length % bs and s.blocks and self.refcount[s.blocks[s.length // bs]] > 1:
-            need += 1
-        return max(0, need)
-
-    def _release(self, b: int) -> None:
-        self.refcount[b] -= 1
-        if self.refcount[b] == 0:
-            self.free_list.append(b)
-
-    def _take(self) -> int:
-        if not self.free_list:
-            raise RuntimeError("KV cache exhausted")
-        b = self.free_list.pop()
-        self.refcount[b] = 1
-        return b
+        return self.sched.blocks_needed(seq, new_tokens)
 
     def _write_table(self, seq: int) -> None:
-        s = self.seqs[seq]
-        if s.blocks:
-            row = torch.tensor(s.blocks, dtype=torch.int32)
-            self.block_table[seq, : len(s.blocks)].copy_(row.to(self.dev), non_blocking=True)
+        blocks = self.sched.blocks(seq)
+        if blocks:
+            row = torch.tensor(blocks, dtype=torch.int32)
+            self.block_table[seq, : len(blocks)].copy_(row.to(self.dev), non_blocking=True)
 
-    def _reserve(self, seq: int, new_tokens: int) -> List[int]:
-        """Makes positions [length, length + new_tokens) writable; returns their slots."""
-        s = self.seqs[seq]
+    def _copy_block(self, old: int, nb: int) -> None:
+        """Copy-on-write of a shared partial block: every layer's K and V page (and scales) from ``old`` to ``nb``."""
         bs = self.cfg.block_size
-        if s.length + new_tokens > self.ctx:
-            raise ValueError(f"sequence {seq} would exceed the context length {self.ctx}")
-        changed = False
-        if new_tokens > 0 and s.length % bs and self.refcount[s.blocks[s.length // bs]] > 1:
-            old = s.blocks[s.length // bs]          # shared partial block: copy before writing
-            nb = self._take()
-            for l in range(self.L):
-                self.k_cache[l][nb].copy_(self.k_cache[l][old])
-                self.v_cache[l][nb].copy_(self.v_cache[l][old])
-                if self.kv_kind:
-                    self.k_scale[l][nb * bs: (nb + 1) * bs].copy_(self.k_scale[l][old * bs: (old + 1) * bs])
-                    self.v_scale[l][nb * bs: (nb + 1) * bs].copy_(self.v_scale[l][old * bs: (old + 1) * bs])
-            self._release(old)
-            s.blocks[s.length // bs] = nb
-            changed = True
-        while len(s.blocks) * bs < s.length + new_tokens:
-            s.blocks.append(self._take())
-            changed = True
-        if changed:
-            self._write_table(seq)
-        return [s.blocks[p // bs] * bs + p % bs for p in range(s.length, s.length + new_tokens)]
+        for l in range(self.L):
+            self.k_cache[l][nb].copy_(self.k_cache[l][old])
+            self.v_cache[l][nb].copy_(self.v_cache[l][old])
+            if self.kv_kind:
+                self.k_scale[l][nb * bs: (nb + 1) * bs].copy_(self.k_scale[l][old * bs: (old + 1) * bs])
+                self.v_scale[l][nb * bs: (nb + 1) * bs].copy_(self.v_scale[l][old * bs: (old + 1) * bs])
 
     # ----------------------------------------------------------------------------- math helpers
     def _linear(self, x, lin: _Linear, *, act=None, residual=None, out_dtype=None):
@@ -598,81 +534,40 @@ class Engine:
         t0 = time.perf_counter()
         cfg = self.cfg
         nl = self.L if layers < 0 else min(layers, self.L)
-        tok: List[int] = []
-        pos: List[int] = []
-        slot: List[int] = []
-        rseq: List[int] = []
-        logit_rows: List[int] = []
-        out_rows: List[int] = []      # rows whose token is model output (output counters)
-        self._logit_seq = []
-        runs = []                      # (kind, row0, row1, seq) kind: "flash" | "paged"
         stats = StepStats()
-        for c in chunks:
-            n = len(c.tokens)
-            if n == 0:
-                continue
-            s = self.seqs[c.seq]
-            slots = self._reserve(c.seq, n)
-            r0 = len(tok)
-            fresh = s.length == 0 and n > 1
-            if device_tokens:
-                if n != 1:
-                    raise ValueError("device_tokens needs one-token chunks")
-                tok.append(0)
-            else:
-                tok.extend(int(t) for t in c.tokens)
-            pos.extend(range(s.length, s.length + n))
-            slot.extend(slots)
-            rseq.extend([c.seq] * n)
-            if c.output:
-                out_rows.extend(range(r0, r0 + n))
-            if fresh:
-                runs.append(("flash", r0, r0 + n, c.seq))
-                stats.prefill_tokens += n
-            else:
-                if runs and runs[-1][0] == "paged" and runs[-1][2] == r0:
-                    runs[-1] = ("paged", runs[-1][1], r0 + n, -1)
-                else:
-                    runs.append(("paged", r0, r0 + n, -1))
-                if s.length == 0 or n > 1:
-                    stats.prefill_tokens += n
-                else:
-                    stats.decode_tokens += n
-            k = min(c.logits, n)
-            logit_rows.extend(range(r0 + n - k, r0 + n))
-            self._logit_seq.extend([c.seq] * k)
-            if not c.output and s.length == s.n_prompt:
-                s.n_prompt += n
-            if device_tokens:
-                self._patch[c.seq] = len(s.tokens)      # filled in by collect() once the token has been read
-                s.tokens.append(-1)
-            else:
-                s.tokens.extend(int(t) for t in c.tokens)
-            s.length += n
-        N = len(tok)
+        live = [c for c in chunks if len(c.tokens)]
+        flat: List[int] = []
+        if not device_tokens:
+            for c in live:
+                flat.extend(int(t) for t in c.tokens)
+        else:
+            flat = [0] * len(live)
+        plan = self.sched.plan([c.seq for c in live], [len(c.tokens) for c in live], flat, [c.logits for c in live],
+                               [int(bool(c.output)) for c in live], device_tokens, cfg.max_tokens)
+        for old, nb in plan["cows"]:
+            self._copy_block(old, nb)
+        for sid in plan["tables"]:
+            self._write_table(sid)
+        for sid, idx in plan["patches"]:
+            self._patch[sid] = idx          # filled in by collect() once the token has been read
+        N, R = plan["tokens"], plan["logit_rows"]
+        runs, out_rows = plan["runs"], plan["out_rows"]
+        self._logit_seq = plan["logit_seq"]
+        stats.prefill_tokens, stats.decode_tokens = plan["prefill_tokens"], plan["decode_tokens"]
         stats.tokens = N
         if N == 0:
             self._logits = torch.zeros((0, self.Vp), dtype=torch.float32, device=self.dev)
             self._stats = stats
             return self._logits
-        if N > cfg.max_tokens:
-            raise ValueError(f"{N} tokens exceed max_tokens {cfg.max_tokens}")
         self._skinny = 16
-        decode_only = all(k == "paged" for k, *_ in runs) and N == len(logit_rows) == stats.decode_tokens
+        decode_only = all(k == "paged" for k, *_ in runs) and N == R == stats.decode_tokens
         # tensor-parallel ranks run the same schedule, so with tp_graphs every rank captures and replays the same buckets
         # in the same order, the all-reduces of the layer loop captured with the kernels around them
         use_graph = self.fast and cfg.cuda_graphs and decode_only and nl == self.L and (self.tp == 1 or cfg.tp_graphs)
-        R = len(logit_rows)
         bucket = 1 << (N - 1).bit_length() if use_graph else N
         # one staging buffer in pinned memory, reused every step, and ONE host-to-device copy for all index arrays
         ints = self._stage(bucket)
-        h = ints.numpy()
-        h[:, N:] = 0
-        h[2, N:] = -1
-        h[0, :N], h[1, :N], h[2, :N], h[3, :N] = tok, pos, slot, rseq
-        h[4, :N] = h[1, :N] + 1
-        h[5, :R] = logit_rows
-        h[5, R:] = 0
+        self.sched.write(ints.data_ptr(), bucket)
         if use_graph:
             logits = self._decode_graph(bucket, ints, N if device_tokens else 0)[:R]
             dv = self._static[bucket]["ints"]
@@ -935,9 +830,8 @@ class Engine:
         toks = [int(t) for t in pending.pinned[: pending.rows].tolist()]
         for seq, t in zip(pending.seqs, toks):
             idx = self._patch.pop(seq, None)
-            s = self.seqs.get(seq)
-            if idx is not None and s is not None and idx < len(s.tokens) and s.tokens[idx] == -1:
-                s.tokens[idx] = t
+            if idx is not None:
+                self.sched.patch(seq, idx, t)       # no-op when the sequence is gone or the slot was filled already
         return toks
 
     def nll(self, targets: Sequence[int]) -> List[float]:
