@@ -39,8 +39,6 @@ _TORCH = {DType.F32: torch.float32, DType.F16: torch.float16, DType.BF16: torch.
           DType.I32: torch.int32, DType.I64: torch.int64, DType.I8: torch.int8, DType.U8: torch.uint8,
           DType.Bool: torch.bool, DType.F8E4M3: torch.float8_e4m3fn, DType.F8E5M2: torch.float8_e5m2}
 _FROM_TORCH = {v: k for k, v in _TORCH.items()}
-_FLOAT_RANK = {DType.F16: 1, DType.BF16: 1, DType.F32: 2, DType.F64: 3}
-_INT_RANK = {DType.U8: 1, DType.I8: 1, DType.I32: 2, DType.I64: 3}
 
 
 class TensorError(RuntimeError):
@@ -67,11 +65,11 @@ def is_float8(d: DType) -> bool:
 
 
 def is_floating(d: DType) -> bool:
-    return d in _FLOAT_RANK or is_float8(d)
+    return d in (DType.F16, DType.BF16, DType.F32, DType.F64) or is_float8(d)
 
 
 def is_integral(d: DType) -> bool:
-    return d in _INT_RANK
+    return d in (DType.U8, DType.I8, DType.I32, DType.I64)
 
 
 def to_torch(d: DType) -> torch.dtype:
@@ -82,98 +80,51 @@ def from_torch(t: torch.dtype) -> DType:
     return _FROM_TORCH[t]
 
 
+def _core():
+    from .. import _native
+    return _native
+
+
 def promote(a: DType, b: DType) -> DType:
+    """Result dtype of a binary op: torch-like, except U8 + I8 -> I32 (PyTorch gives int16) and FP8 never promotes
+    implicitly.  The table lives in the native host module (`csrc/host/lowp.cpp`)."""
     a, b = DType(a), DType(b)
-    if a == b:
-        return a
-    if is_float8(a) or is_float8(b):
-        raise TensorError(f"{to_string(a)} and {to_string(b)} do not promote implicitly; convert FP8 explicitly")
-    if a == DType.Bool:
-        return b
-    if b == DType.Bool:
-        return a
-    fa, fb = a in _FLOAT_RANK, b in _FLOAT_RANK
-    if fa != fb:
-        return a if fa else b
-    if fa:
-        ra, rb = _FLOAT_RANK[a], _FLOAT_RANK[b]
-        if ra == rb:
-            return DType.F32            # F16 + BF16
-        return a if ra > rb else b
-    if {a, b} == {DType.U8, DType.I8}:
-        return DType.I32                # documented deviation: PyTorch gives int16
-    return a if _INT_RANK[a] >= _INT_RANK[b] else b
+    try:
+        return DType(_core().dtype_promote(int(a), int(b)))
+    except ValueError:
+        raise TensorError(f"{to_string(a)} and {to_string(b)} do not promote implicitly; convert FP8 explicitly") from None
 
 
 # ------------------------------------------------------------------------------------- host conversions
+# Bit-level round-to-nearest-even conversions in the native host module; arrays of any shape.
 def float_to_bf16_bits(x) -> np.ndarray:
-    """Round-to-nearest-even float32 -> bfloat16 bit patterns (uint16); NaN stays NaN."""
-    u = np.asarray(x, dtype=np.float32).view(np.uint32)
-    nan = (u & 0x7FFFFFFF) > 0x7F800000
-    r = ((u + (0x7FFF + ((u >> 16) & 1))) >> 16).astype(np.uint16)
-    return np.where(nan, np.uint16(0x7FC0), r)
+    """float32 -> bfloat16 bit patterns (uint16); NaN stays NaN."""
+    return _core().f32_to_bf16_bits(np.asarray(x, dtype=np.float32))
 
 
 def bf16_bits_to_float(b) -> np.ndarray:
-    return (np.asarray(b, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+    return _core().bf16_bits_to_f32(np.asarray(b, dtype=np.uint16))
 
 
 def float_to_half_bits(x) -> np.ndarray:
-    return np.asarray(x, dtype=np.float32).astype(np.float16).view(np.uint16)
+    return _core().f32_to_f16_bits(np.asarray(x, dtype=np.float32))
 
 
 def half_bits_to_float(b) -> np.ndarray:
-    return np.asarray(b, dtype=np.uint16).view(np.float16).astype(np.float32)
+    return _core().f16_bits_to_f32(np.asarray(b, dtype=np.uint16))
 
 
 FP8_MAX = {DType.F8E4M3: 448.0, DType.F8E5M2: 57344.0}
 
 
-def _fp8_table(fmt: DType) -> np.ndarray:
-    """Decode table of all 256 bit patterns."""
-    out = np.zeros(256, dtype=np.float32)
-    e_bits, m_bits, bias = (4, 3, 7) if fmt == DType.F8E4M3 else (5, 2, 15)
-    for code in range(256):
-        s = -1.0 if code & 0x80 else 1.0
-        e = (code >> m_bits) & ((1 << e_bits) - 1)
-        m = code & ((1 << m_bits) - 1)
-        if fmt == DType.F8E4M3:
-            if e == 15 and m == 7:
-                out[code] = np.nan           # E4M3fn: only S.1111.111 is NaN, no infinity
-                continue
-        elif e == 31:
-            out[code] = s * np.inf if m == 0 else np.nan
-            continue
-        if e == 0:
-            out[code] = s * m * 2.0 ** (1 - bias - m_bits)
-        else:
-            out[code] = s * (1 + m / (1 << m_bits)) * 2.0 ** (e - bias)
-    return out
-
-
-_FP8_DECODE = {DType.F8E4M3: _fp8_table(DType.F8E4M3), DType.F8E5M2: _fp8_table(DType.F8E5M2)}
-
-
 def fp8_decode(codes, fmt: DType) -> np.ndarray:
-    return _FP8_DECODE[DType(fmt)][np.asarray(codes, dtype=np.uint8)]
+    """FP8 bit patterns -> float32.  E4M3fn: only S.1111.111 is NaN, no infinity; E5M2: IEEE-like."""
+    return _core().fp8_bits_to_f32(np.asarray(codes, dtype=np.uint8), DType(fmt) == DType.F8E5M2)
 
 
 def fp8_encode(x, fmt: DType) -> np.ndarray:
-    """float32 -> FP8 bit patterns, RNE, saturating to +-max (NaN -> NaN code)."""
-    fmt = DType(fmt)
-    x = np.asarray(x, dtype=np.float32)
-    table = _FP8_DECODE[fmt]
-    pos_codes = np.array([c for c in range(128) if np.isfinite(table[c])], dtype=np.uint8)
-    vals = table[pos_codes]                     # ascending
-    a = np.minimum(np.abs(x), FP8_MAX[fmt])
-    hi = np.clip(np.searchsorted(vals, a, side="left"), 0, len(vals) - 1)
-    lo = np.clip(hi - 1, 0, len(vals) - 1)
-    dlo, dhi = np.abs(a - vals[lo]), np.abs(vals[hi] - a)
-    pick_hi = (dhi < dlo) | ((dhi == dlo) & ((pos_codes[hi] & 1) == 0))   # ties -> even mantissa
-    code = np.where(pick_hi, pos_codes[hi], pos_codes[lo]).astype(np.uint8)
-    code = np.where(np.signbit(x), code | 0x80, code).astype(np.uint8)
-    nan_code = 0x7F if fmt == DType.F8E4M3 else 0x7E
-    return np.where(np.isnan(x), np.uint8(nan_code), code)
+    """float32 -> FP8 bit patterns, RNE, saturating to +-max (NaN -> the format's NaN code)."""
+    return _core().f32_to_fp8_bits(np.asarray(x, dtype=np.float32), DType(fmt) == DType.F8E5M2)
 
 
 class Fp8DelayedScaling:

@@ -16,6 +16,7 @@ void bind_estimate(py::module_& m);
 void bind_dlpack(py::module_& m);
 void bind_token_data(py::module_& m);
 void bind_kv_sched(py::module_& m);
+void bind_lowp(py::module_& m);
 
 PYBIND11_MODULE(_native, m) {
   m.doc() = "nexus_b200 native host runtime";
@@ -31,4 +32,5 @@ PYBIND11_MODULE(_native, m) {
   bind_dlpack(m);
   bind_token_data(m);
   bind_kv_sched(m);
+  bind_lowp(m);
 }

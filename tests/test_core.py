@@ -161,3 +161,44 @@ def test_autocast_table():
     assert not amp.autocast_state()[0]
     with pytest.raises(core.TensorError):
         AutocastGuard(dtype=DType.F32)
+
+
+def test_native_low_precision_conversions_match_numpy_and_torch():
+    """Bit-level float32 -> BF16 / F16 / FP8 conversions of the native host module against numpy (F16), torch (BF16,
+    FP8 in range) and exhaustive midpoints (ties go to the even mantissa); FP8 saturates and has one NaN code."""
+    import numpy as np
+    import torch
+    from nexus_b200.core import dtype as D
+    rng = np.random.default_rng(0)
+    x = rng.integers(0, 2 ** 32, size=200_000, dtype=np.uint64).astype(np.uint32).view(np.float32)
+    sp = np.array([0.0, np.inf, np.nan, 1e-45, 1.17549435e-38, 6.1e-5, 5.96e-8, 2.98e-8, 65504, 65519.99, 65520, 70000, 448,
+                   449, 464, 465, 480, 1e9, 57344, 61440, 61439, 2.0 ** -9, 2.0 ** -10, 2.0 ** -17, 2.0 ** -16], dtype=np.float32)
+    x = np.concatenate([x, sp, -sp])
+    nan = np.isnan(x)
+    with np.errstate(over="ignore", invalid="ignore"):
+        f16 = x.astype(np.float16).view(np.uint16)
+    got = D.float_to_half_bits(x)
+    assert got.dtype == np.uint16 and np.array_equal(got[~nan], f16[~nan]) and np.isnan(got[nan].view(np.float16)).all()
+    codes = np.arange(65536, dtype=np.uint16)
+    back, want = D.half_bits_to_float(codes), codes.view(np.float16).astype(np.float32)
+    assert np.array_equal(np.isnan(back), np.isnan(want)) and np.array_equal(back[~np.isnan(want)], want[~np.isnan(want)])
+    vals = np.arange(0, 0x7C00, dtype=np.uint16).view(np.float16).astype(np.float64)
+    mid = ((vals[:-1] + vals[1:]) / 2).astype(np.float32)
+    assert np.array_equal(D.float_to_half_bits(mid), mid.astype(np.float16).view(np.uint16))
+    bf = torch.from_numpy(x.copy()).to(torch.bfloat16).view(torch.uint16).numpy()
+    assert np.array_equal(D.float_to_bf16_bits(x)[~nan], bf[~nan]) and (D.float_to_bf16_bits(x)[nan] == 0x7FC0).all()
+    assert D.float_to_bf16_bits(x.reshape(5, -1)).shape == (5, x.size // 5)
+    for fmt, tdt, nan_code in ((D.DType.F8E4M3, torch.float8_e4m3fn, 0x7F), (D.DType.F8E5M2, torch.float8_e5m2, 0x7E)):
+        mx = D.FP8_MAX[fmt]
+        got = D.fp8_encode(x, fmt)
+        inr = np.isfinite(x) & (np.abs(x) <= mx)
+        assert np.array_equal(got[inr], torch.from_numpy(x.copy()).to(tdt).view(torch.uint8).numpy()[inr])
+        big = ~nan & (np.abs(x) > mx)
+        dec = D.fp8_decode(got[big], fmt)
+        assert (np.abs(dec) == mx).all() and np.array_equal(np.signbit(dec), np.signbit(x[big])) and (got[nan] == nan_code).all()
+        c8 = np.arange(256, dtype=np.uint8)
+        q, r = torch.from_numpy(c8).view(tdt).float().numpy(), D.fp8_decode(c8, fmt)
+        assert np.array_equal(np.isnan(r), np.isnan(q)) and np.array_equal(r[~np.isnan(q)], q[~np.isnan(q)])
+        fin = np.sort(q[np.isfinite(q) & (q >= 0)]).astype(np.float64)
+        mid = ((fin[:-1] + fin[1:]) / 2).astype(np.float32)
+        assert np.array_equal(D.fp8_encode(mid, fmt), torch.from_numpy(mid).to(tdt).view(torch.uint8).numpy())
