@@ -17,6 +17,7 @@ void bind_dlpack(py::module_& m);
 void bind_token_data(py::module_& m);
 void bind_kv_sched(py::module_& m);
 void bind_lowp(py::module_& m);
+void bind_fused_train_cpu(py::module_& m);
 
 PYBIND11_MODULE(_native, m) {
   m.doc() = "nexus_b200 native host runtime";
@@ -33,4 +34,5 @@ PYBIND11_MODULE(_native, m) {
   bind_token_data(m);
   bind_kv_sched(m);
   bind_lowp(m);
+  bind_fused_train_cpu(m);
 }

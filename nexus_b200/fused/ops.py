@@ -366,8 +366,20 @@ def _ce_reference(logits, targets, ignore_index, smoothing, z_loss):
 
 
 class _FusedCE(torch.autograd.Function):
+    """Loss and gradient in one pass: the gradient overwrites a working copy of the logits, on the device through the
+    CUDA kernel, on the host through the native threaded kernel (`csrc/host/fused_train_cpu.cpp`)."""
+
     @staticmethod
     def forward(ctx, logits, tokens, targets, vocab, ignore_index, smoothing, z_loss):
+        ctx.shape, ctx.dtype = logits.shape, logits.dtype
+        if not logits.is_cuda:
+            from .. import _native
+            work = logits.detach().reshape(-1, logits.shape[-1]).to(torch.float32).clone()
+            tg = (shifted_targets(tokens, ignore_index) if targets is None else targets).reshape(-1)
+            tg = tg.to(torch.int32).contiguous()
+            loss, _ = _native.cpu_cross_entropy(work.numpy(), tg.numpy(), vocab, ignore_index, smoothing, z_loss, 1.0, True)
+            ctx.save_for_backward(work)
+            return torch.tensor(loss, dtype=torch.float32)
         from ..ops import _cuda as K
         work = logits.reshape(-1, logits.shape[-1]).clone()  # gradient is produced in place in this copy
         tk = tokens.to(torch.int32).contiguous() if tokens is not None else None
@@ -376,13 +388,17 @@ class _FusedCE(torch.autograd.Function):
         loss = K.cross_entropy_shifted(work, tk, targets=tg, vocab=vocab, ignore_index=ignore_index,
                                        smoothing=smoothing, z_loss=z_loss, grad_scale=1.0, seq_len=T)
         ctx.save_for_backward(work)
-        ctx.shape = logits.shape
         return loss.reshape(())
 
     @staticmethod
     def backward(ctx, dloss):
         (g,) = ctx.saved_tensors
-        return (g * dloss.to(g.dtype)).view(ctx.shape), None, None, None, None, None, None
+        return (g * dloss.to(g.dtype)).to(ctx.dtype).view(ctx.shape), None, None, None, None, None, None
+
+
+def _host_fused(logits: torch.Tensor) -> bool:
+    """The native host kernel takes 16- and 32-bit floats; FP64 (gradient checks) stays on the torch expression."""
+    return not logits.is_cuda and logits.dtype in (torch.float32, torch.bfloat16, torch.float16)
 
 
 def shifted_targets(tokens: torch.Tensor, ignore_index: int = -100) -> torch.Tensor:
@@ -400,6 +416,8 @@ def cross_entropy_shifted(logits: torch.Tensor, tokens: torch.Tensor, ignore_ind
         from ..ops import _cuda as K
         K.lib()
         return _FusedCE.apply(logits, tokens, None, V, ignore_index, label_smoothing, z_loss)
+    if _host_fused(logits) and logits.shape[-1] >= V:
+        return _FusedCE.apply(logits, tokens, None, V, ignore_index, label_smoothing, z_loss)
     tg = shifted_targets(tokens, ignore_index).reshape(-1)
     return _ce_reference(logits.reshape(-1, logits.shape[-1])[:, :V], tg, ignore_index, label_smoothing, z_loss)
 
@@ -410,6 +428,8 @@ def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, ignore_index: int
     if logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32):
         from ..ops import _cuda as K
         K.lib()
+        return _FusedCE.apply(logits, None, targets, logits.shape[-1], ignore_index, label_smoothing, z_loss)
+    if _host_fused(logits):
         return _FusedCE.apply(logits, None, targets, logits.shape[-1], ignore_index, label_smoothing, z_loss)
     return _ce_reference(logits.reshape(-1, logits.shape[-1]), targets.reshape(-1), ignore_index, label_smoothing,
                          z_loss)
@@ -468,6 +488,9 @@ def _dropout_apply(x, p, seed, offset):
     if x.is_cuda and x.dtype in (torch.bfloat16, torch.float32):
         from ..ops import _cuda as K
         return K.dropout(x.contiguous(), p, seed, offset)
+    if not x.is_cuda and x.dtype == torch.float32:
+        from .. import _native
+        return torch.from_numpy(_native.cpu_dropout_philox(x.detach().contiguous().numpy(), p, seed, offset)).view(x.shape)
     keep = torch.from_numpy(_philox.dropout_mask(x.numel(), p, seed, offset)).view(x.shape).to(x.device)
     return torch.where(keep, x * (1.0 / (1.0 - p)), torch.zeros_like(x))
 

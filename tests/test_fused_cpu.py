@@ -110,3 +110,63 @@ def test_attention_varlen_matches_per_sequence_attention():
         assert torch.allclose(g, r, atol=1e-5)
     with pytest.raises(ValueError):
         F.attention_varlen(q, k, v, torch.tensor([0, 3]), ck)
+
+
+@pytest.mark.parametrize("smoothing,z", [(0.0, 0.0), (0.1, 1e-3)])
+def test_native_host_cross_entropy_matches_the_torch_expression(smoothing, z):
+    """The threaded host kernel (loss + gradient written over a copy of the logits) against autograd through the plain
+    torch expression: shifted and explicit targets, ignored rows, a padded vocabulary, 16-bit logits."""
+    import torch
+    from nexus_b200 import _native
+    from nexus_b200.fused import ops as F
+    g = torch.Generator().manual_seed(0)
+    B, T, V, pad = 3, 17, 37, 3
+    tokens = torch.randint(0, V, (B, T), generator=g)
+    for dtype in (torch.float32, torch.bfloat16):
+        base = torch.randn(B, T, V + pad, generator=g).to(dtype)
+        a = base.clone().requires_grad_(True)
+        la = F.cross_entropy_shifted(a, tokens, label_smoothing=smoothing, z_loss=z, vocab=V)
+        la.backward()
+        b = base.clone().float().requires_grad_(True)
+        lb = F._ce_reference(b.reshape(-1, V + pad)[:, :V], F.shifted_targets(tokens).reshape(-1), -100, smoothing, z)
+        lb.backward()
+        tol = 1e-6 if dtype == torch.float32 else 2e-2
+        assert abs(float(la.detach()) - float(lb.detach())) < 1e-5 and a.grad.dtype == dtype
+        assert torch.allclose(a.grad.float(), b.grad, atol=tol) and float(a.grad[..., V:].abs().max()) == 0.0
+        assert float(a.grad[:, -1].abs().max()) == 0.0                       # last position of a row has no target
+    logits = torch.randn(40, V, generator=g, requires_grad=True)
+    tg = torch.randint(0, V, (40,), generator=g)
+    tg[::5] = -100
+    l1 = F.cross_entropy(logits, tg, label_smoothing=smoothing, z_loss=z)
+    l1.backward(torch.tensor(2.0))
+    ref = logits.detach().clone().requires_grad_(True)
+    (2.0 * F._ce_reference(ref, tg, -100, smoothing, z)).backward()
+    assert abs(float(l1.detach()) - float(F._ce_reference(ref.detach(), tg, -100, smoothing, z))) < 1e-5
+    assert torch.allclose(logits.grad, ref.grad, atol=1e-6)
+    # direct calls: loss only leaves the logits alone; nothing valid gives zero loss and zero gradient; bad target refused
+    x = torch.randn(4, 8)
+    keep = x.clone()
+    loss, valid = _native.cpu_cross_entropy(x.numpy(), torch.tensor([1, 2, -100, 3], dtype=torch.int32).numpy(), 8, -100,
+                                            0.0, 0.0, 1.0, False)
+    assert valid == 3 and torch.equal(x, keep) and loss > 0
+    loss, valid = _native.cpu_cross_entropy(x.numpy(), torch.full((4,), -100, dtype=torch.int32).numpy(), 8)
+    assert (loss, valid) == (0.0, 0) and float(x.abs().max()) == 0.0
+    with pytest.raises(IndexError):
+        _native.cpu_cross_entropy(keep.numpy(), torch.tensor([1, 2, 9, 3], dtype=torch.int32).numpy(), 8)
+    # FP64 logits keep the differentiable torch expression (second derivatives, gradient checks)
+    d = torch.randn(2, 5, 7, dtype=torch.float64, requires_grad=True)
+    assert F.cross_entropy_shifted(d, torch.randint(0, 7, (2, 5))).grad_fn.name() != "_FusedCEBackward"
+
+
+def test_native_host_dropout_matches_the_philox_stream():
+    import numpy as np
+    import torch
+    from nexus_b200.fused import ops as F
+    from nexus_b200.fused import philox
+    x = torch.randn(7, 1001, requires_grad=True)
+    y = F.dropout_philox(x, 0.3, seed=0x1234567890AB, offset=5)
+    keep = torch.from_numpy(philox.dropout_mask(x.numel(), 0.3, 0x1234567890AB, 5)).view(x.shape)
+    assert torch.equal(y.detach(), torch.where(keep, x.detach() * np.float32(1.0 / (1.0 - np.float32(0.3))), torch.zeros(())))
+    y.sum().backward()
+    assert torch.equal(x.grad != 0, keep) and 0.65 < float(keep.float().mean()) < 0.75
+    assert F.dropout_philox(x, 0.3, 1, 0, training=False) is x
