@@ -18,6 +18,7 @@ void bind_token_data(py::module_& m);
 void bind_kv_sched(py::module_& m);
 void bind_lowp(py::module_& m);
 void bind_fused_train_cpu(py::module_& m);
+void bind_moe_route(py::module_& m);
 
 PYBIND11_MODULE(_native, m) {
   m.doc() = "nexus_b200 native host runtime";
@@ -35,4 +36,5 @@ PYBIND11_MODULE(_native, m) {
   bind_kv_sched(m);
   bind_lowp(m);
   bind_fused_train_cpu(m);
+  bind_moe_route(m);
 }

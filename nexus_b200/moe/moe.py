@@ -17,6 +17,7 @@ import math
 from dataclasses import dataclass, field
 from typing import List, Optional
 
+import numpy as np
 import torch
 import torch.nn.functional as F
 
@@ -115,65 +116,15 @@ def route(x: torch.Tensor, router_w: torch.Tensor, noise_w: Optional[torch.Tenso
     C = capacity_of(spec, Ng)
     r.capacity = C
     dev = x.device
-    if spec.overflow == "drop":
-        # assignment order inside a group: (choice j, token t)
-        e_gjt = expert.view(spec.groups, Ng, k).permute(0, 2, 1).reshape(spec.groups, k * Ng)
-        onehot = F.one_hot(e_gjt, E)
-        pos = (onehot.cumsum(1) - 1).gather(2, e_gjt[..., None])[..., 0]          # [G, k*Ng]
-        accept = pos < C
-        r.dropped = int((~accept).sum())
-        # permuted row = offsets[e] + (accepted before it for expert e, groups in order)
-        acc_oh = onehot * accept[..., None]
-        per_group = acc_oh.sum(1)                                                    # [G, E]
-        counts = per_group.sum(0)
-        offsets = torch.zeros(E + 1, dtype=torch.long, device=dev)
-        offsets[1:] = counts.cumsum(0)
-        group_base = per_group.cumsum(0) - per_group                                 # [G, E]
-        within = (acc_oh.cumsum(1) - 1).gather(2, e_gjt[..., None])[..., 0]
-        rows = offsets[:-1][e_gjt] + group_base.gather(1, e_gjt) + within
-        rows = torch.where(accept, rows, torch.full_like(rows, -1))
-        row = rows.view(spec.groups, k, Ng).permute(0, 2, 1).reshape(N, k)
-        r.row, r.offsets = row, offsets
-    else:
-        exp_l = expert.tolist()
-        order_l = order.tolist()
-        lists = [[[] for _ in range(spec.groups)] for _ in range(E)]
-        for g in range(spec.groups):
-            fill = [0] * E
-            for j in range(k):
-                for t in range(g * Ng, (g + 1) * Ng):
-                    e = exp_l[t][j]
-                    if fill[e] >= C:
-                        alt = -1
-                        for e2 in order_l[t]:
-                            if e2 not in exp_l[t] and fill[e2] < C:
-                                alt = e2
-                                break
-                        if alt < 0:
-                            r.dropped += 1
-                            continue
-                        r.rerouted += 1
-                        exp_l[t][j] = alt
-                        e = alt
-                    fill[e] += 1
-                    lists[e][g].append(t * k + j)
-        row = torch.full((N * k,), -1, dtype=torch.long)
-        offs = [0]
-        nxt = 0
-        for e in range(E):
-            for l in lists[e]:
-                for slot in l:
-                    row[slot] = nxt
-                    nxt += 1
-            offs.append(nxt)
-        r.expert = torch.tensor(exp_l, dtype=torch.long, device=dev)
-        r.row = row.view(N, k).to(dev)
-        r.offsets = torch.tensor(offs, dtype=torch.long, device=dev)
-    nrows = int(r.offsets[-1])
-    perm = torch.empty(nrows, dtype=torch.long, device=dev)
-    flat = r.row.reshape(-1)
-    ok = flat >= 0
-    perm[flat[ok]] = (torch.arange(N * k, device=dev) // k)[ok]
+    # the sequential walk (acceptance in (choice, token) order, reroute search, counting sort) runs in the native module
+    from .. import _native
+    reroute = spec.overflow != "drop"
+    ex, row, offsets, perm, r.dropped, r.rerouted = _native.moe_assign(
+        expert.cpu().numpy(), order.cpu().numpy() if reroute else np.zeros((0, 0), dtype=np.int64), E, spec.groups, C, reroute)
+    if reroute:
+        r.expert = torch.from_numpy(ex).to(dev)
+    r.row, r.offsets = torch.from_numpy(row).to(dev), torch.from_numpy(offsets).to(dev)
+    perm = torch.from_numpy(perm).to(dev)
     r.perm_token = perm
     return r
 

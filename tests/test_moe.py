@@ -86,3 +86,63 @@ def test_tensor_core_agrees_with_the_native_fp64_oracle_under_every_policy(group
     assert dropped == r.dropped and rerouted == r.rerouted and dropped + (rerouted if overflow == "reroute" else 0) > 0
     assert (y.double() - yr).abs().max() < 1e-5
     assert float(r.aux) == pytest.approx(aux, rel=1e-6) and float(r.z) == pytest.approx(z, rel=1e-6)
+
+
+def _assign_oracle(expert, order, E, groups, C, reroute):
+    """Plain-Python statement of the assignment rules, kept here as the oracle for the native walk."""
+    N, k = len(expert), len(expert[0])
+    Ng = N // groups
+    ex = [list(r) for r in expert]
+    lists = [[[] for _ in range(groups)] for _ in range(E)]
+    dropped = rerouted = 0
+    for g in range(groups):
+        fill = [0] * E
+        for j in range(k):
+            for t in range(g * Ng, (g + 1) * Ng):
+                e = ex[t][j]
+                if fill[e] >= C:
+                    alt = -1
+                    if reroute:
+                        for e2 in order[t]:
+                            if e2 not in ex[t] and fill[e2] < C:
+                                alt = e2
+                                break
+                    if alt < 0:
+                        dropped += 1
+                        continue
+                    rerouted += 1
+                    ex[t][j] = e = alt
+                fill[e] += 1
+                lists[e][g].append(t * k + j)
+    row, offs, perm = [-1] * (N * k), [0], []
+    for e in range(E):
+        for l in lists[e]:
+            for slot in l:
+                row[slot] = len(perm)
+                perm.append(slot // k)
+        offs.append(len(perm))
+    return ex, row, offs, perm, dropped, rerouted
+
+
+@pytest.mark.parametrize("reroute", [False, True])
+def test_native_capacity_assignment_matches_the_rules(reroute):
+    import numpy as np
+    from nexus_b200 import _native
+    rng = np.random.default_rng(5)
+    for N, E, k, groups, C in [(32, 4, 2, 1, 6), (48, 8, 2, 4, 2), (40, 5, 3, 2, 9), (16, 4, 1, 2, 1), (24, 6, 2, 3, 0), (8, 3, 3, 1, 50)]:
+        scores = rng.standard_normal((N, E)) + np.linspace(0, 1.5, E)        # skewed, so that experts overflow
+        order = np.argsort(-scores, axis=1, kind="stable")
+        expert = order[:, :k].copy()
+        got = _native.moe_assign(expert, order if reroute else np.zeros((0, 0), dtype=np.int64), E, groups, C, reroute)
+        want = _assign_oracle(expert.tolist(), order.tolist(), E, groups, C, reroute)
+        assert got[0].tolist() == want[0] and got[1].reshape(-1).tolist() == want[1]
+        assert got[2].tolist() == want[2] and got[3].tolist() == want[3] and (got[4], got[5]) == (want[4], want[5])
+        assert got[4] + int((got[1] >= 0).sum()) == N * k
+        if C * groups * E < N * k:
+            assert got[4] > 0
+    with pytest.raises(ValueError):
+        _native.moe_assign(np.zeros((10, 2), dtype=np.int64), np.zeros((0, 0), dtype=np.int64), 4, 3, 2, False)
+    with pytest.raises(IndexError):
+        _native.moe_assign(np.full((4, 1), 9, dtype=np.int64), np.zeros((0, 0), dtype=np.int64), 4, 1, 2, False)
+    with pytest.raises(ValueError):
+        _native.moe_assign(np.zeros((4, 1), dtype=np.int64), np.zeros((4, 3), dtype=np.int64), 4, 1, 2, True)
