@@ -119,6 +119,7 @@ class TokenShards {
   uint64_t cursor() const { return consumed_.load(); }
   uint64_t global_cursor() const { return consumed_.load() * static_cast<uint64_t>(world_); }
   void seek(uint64_t global) {
+    std::lock_guard<std::mutex> one_consumer(consumer_mu_);
     stop_worker();
     ring_.clear();
     consumed_ = global / static_cast<uint64_t>(world_);
@@ -199,6 +200,7 @@ class TokenShards {
   struct Batch { uint64_t first = 0; int rows = 0; std::vector<int32_t> data; };
 
   void fetch(int32_t* dst, int rows) {
+    std::lock_guard<std::mutex> one_consumer(consumer_mu_);   // calls from several threads are served one at a time
     if (depth_ > 0) {
       if (rows != worker_rows_) {          // first call, or the batch shape changed: restart the read-ahead
         stop_worker();
@@ -269,7 +271,7 @@ class TokenShards {
   std::atomic<uint64_t> prefetched_{0};
   int worker_rows_ = -1;
   std::thread worker_;
-  std::mutex mu_;
+  std::mutex mu_, consumer_mu_;
   std::condition_variable ready_, space_;
   std::deque<Batch> ring_;
   bool stop_ = false;
