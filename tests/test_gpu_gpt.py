@@ -46,12 +46,12 @@ def test_gpt_loss_and_grads_match_reference():
     P = {n: m.p[n].float().clone().requires_grad_(True) for n in PARAM_ORDER}
     ref = torch_reference(P, tok, cfg)
     ref.backward()
-    assert abs(loss - ref.item()) < 2e-2
+    assert abs(loss - ref.item()) < 2e-3          # measured: 4e-6 .. 4e-5 over seeds
     for n in PARAM_ORDER:
         g, r = m.g[n].float(), P[n].grad
         if n == "wte":
             g, r = g[: cfg.vocab_size], r[: cfg.vocab_size]
-        assert (g - r).norm() <= 5e-2 * r.norm(), n
+        assert (g - r).norm() <= 1.5e-2 * r.norm(), n   # measured: 0.3 % .. 0.6 % per tensor (BF16 activations)
 
 
 def test_gpt_training_reduces_loss_and_trainer_graph_matches_eager():
