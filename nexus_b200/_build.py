@@ -150,6 +150,36 @@ def build_host(force: bool = False, verbose: bool = False) -> Path:
     return out
 
 
+SANITIZERS = {"asan": ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"], "tsan": ["-fsanitize=thread"]}
+
+
+def build_host_sanitized(kind: str = "asan", verbose: bool = False) -> Path:
+    """A second build of the host module with AddressSanitizer + UBSan (``asan``) or ThreadSanitizer (``tsan``), written
+    to ``build/sanitized/<kind>/`` beside the package.  It is loaded instead of the regular module when ``NEXUS_B200_NATIVE`` names it and
+    the matching runtime is preloaded::
+
+        NEXUS_B200_NATIVE=$(python -m nexus_b200._build --sanitize asan) \
+        LD_PRELOAD=$(gcc -print-file-name=libasan.so) ASAN_OPTIONS=detect_leaks=0 python -m pytest tests/test_kv_sched.py
+    """
+    import pybind11
+
+    flags = SANITIZERS[kind]
+    odir = PKG.parent / "build" / "sanitized" / kind      # objects and module: outside the package, rebuilt on demand
+    odir.mkdir(parents=True, exist_ok=True)
+    out = odir / native_module_path().name
+    inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", str(CSRC / "host")]
+    base = [f for f in CXX_FLAGS if f != "-O2"] + ["-O1", "-g", "-fno-omit-frame-pointer", *flags]
+    hdr = _newest_header([CSRC / "host"])
+    jobs = [(src, odir / (src.stem + ".o"), ["g++", *base, *inc, "-c", str(src), "-o", str(odir / (src.stem + ".o"))], hdr)
+            for src in host_sources()]
+    rebuilt = _compile_many(jobs, False)
+    if rebuilt or not out.exists():
+        _run(["g++", "-shared", "-o", str(out), *[str(j[1]) for j in jobs], "-pthread", *flags])
+        if verbose:
+            print("linked", out, file=sys.stderr)
+    return out
+
+
 def build_tools(force: bool = False, verbose: bool = False):
     """Stand-alone native executables (launcher)."""
     outs = []
@@ -173,5 +203,8 @@ def build_all(force: bool = False, verbose: bool = False):
 
 
 if __name__ == "__main__":
-    build_all(force="--force" in sys.argv, verbose=True)
-    print("ok")
+    if "--sanitize" in sys.argv:
+        print(build_host_sanitized(sys.argv[sys.argv.index("--sanitize") + 1], verbose=True))
+    else:
+        build_all(force="--force" in sys.argv, verbose=True)
+        print("ok")
