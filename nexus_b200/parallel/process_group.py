@@ -161,6 +161,18 @@ class ProcessGroup:
         self._seq += 1
         return f"{self._seq}:{op}:{None if t is None else t.dtype}:{0 if t is None else t.numel()}:{root}"
 
+    def check_call(self, op: str, *fields) -> None:
+        """Validate mode only: compares (sequence number, ``op``, ``fields``) across the ranks and raises ``DistError``
+        on the first difference.  Callers that launch their own communicating kernels (the symmetric-memory ops) use
+        it before the launch, so a mismatched call becomes a named host error instead of a device-side time-out."""
+        if not self.validate:
+            return
+        self._seq += 1
+        self._exchange_fingerprint(f"{self._seq}:{op}:" + ":".join(str(f) for f in fields))
+
+    def _exchange_fingerprint(self, fp: str) -> None:
+        raise NotImplementedError
+
 
 # ================================================================================================
 # torch.distributed transport
@@ -187,6 +199,9 @@ class TorchProcessGroup(ProcessGroup):
         if not self.validate:
             return
         fp = self.fingerprint(op, t, root)
+        self._exchange_fingerprint(fp)
+
+    def _exchange_fingerprint(self, fp: str) -> None:
         gathered = [None] * self.size()
         self.dist.all_gather_object(gathered, fp, group=self.group)
         if any(g != gathered[0] for g in gathered):
@@ -374,6 +389,20 @@ class ThreadProcessGroup(ProcessGroup):
             return combine([v[0] for v in vals])
         try:
             return self.s.rendezvous(("c", self._n), self._rank, (value, fp), comb)
+        except DistError:
+            self.broken = True
+            raise
+
+    def _exchange_fingerprint(self, fp: str) -> None:
+        self._check_alive()
+        self._n += 1
+
+        def comb(vals):
+            if any(v != vals[0] for v in vals):
+                raise DistError(f"mismatched collective across ranks: {list(vals)}")
+            return None
+        try:
+            self.s.rendezvous(("c", self._n), self._rank, fp, comb)
         except DistError:
             self.broken = True
             raise

@@ -95,6 +95,14 @@ class SymmetricWorkspace:
                 mc = 0
         return SymmetricBuffer(t, ptrs, mc)
 
+    def check(self, op: str, *fields) -> None:
+        """Validate mode of the process group (``NEXUS_DIST_DEBUG=1``): before a communicating kernel is launched, the
+        ranks compare what they are about to launch (op name, sizes, dtypes) on the host and a difference raises a
+        named ``DistError`` here, where the kernel would otherwise wait for a peer until its bounded wait gives up.
+        Skipped while a CUDA graph is being captured (a host exchange cannot be captured)."""
+        if getattr(self.pg, "validate", False) and not torch.cuda.is_current_stream_capturing():
+            self.pg.check_call(op, *fields)
+
     def barrier(self) -> None:
         """Device-side barrier over the group on the current stream (bounded wait)."""
         K._check(K.lib().nx_comm_barrier(C.byref(self.flags.table), C.c_int(self.rank), C.c_int(self.n),
@@ -161,6 +169,7 @@ class FusedShardedOptimizer:
         # all-reduce only wins from four ranks up and this path has not been timed there.
         mc = bool(os.environ.get("NEXUS_B200_SHARDED_MULTIMEM", "0") == "1" and self.grads.multicast
                   and self.shadow.multicast and self.tail.multicast)
+        ws.check("sharded_optimizer_step", self.grads.local.numel(), mc)
         ws.barrier()  # every rank has finished its backward pass
         if self.count > 0 and mc:
             K._check(L.nx_comm_reduce_shard_multimem(C.c_void_p(self.grads.multicast), C.c_int64(self.off),
@@ -220,6 +229,7 @@ def fused_all_reduce(ws: SymmetricWorkspace, src: SymmetricBuffer, dst: Symmetri
     n, r = ws.n, ws.rank
     if count % 8:
         raise ValueError("fused_all_reduce: count must be a multiple of 8 elements")
+    ws.check("fused_all_reduce", count, src.local.dtype, dst.local.dtype, scale, one_shot, multimem)
     if one_shot is None:
         one_shot = count * src.local.element_size() <= (256 << 10)
     # same dtype on both sides and a multicast address: let NVSwitch do the sum (in place in `src`, then one local
@@ -260,6 +270,7 @@ def multimem_all_reduce(ws: SymmetricWorkspace, buf: SymmetricBuffer, count: int
     allocation has no multicast address; the caller then uses ``fused_all_reduce``."""
     if not buf.multicast:
         return False
+    ws.check("multimem_all_reduce", count, offset, buf.local.dtype, scale)
     if offset % 8 or count % 8:
         raise ValueError("multimem_all_reduce: offset and count must be multiples of 8 elements")
     n, r = ws.n, ws.rank
@@ -359,6 +370,7 @@ def gemm_ag(site: GatherSite, gather: SymmetricBuffer, b: torch.Tensor, out: tor
     two uses of the same gather buffer by ``ws.barrier()`` (peers may still be reading the old contents)."""
     ws = site.ws
     M = site.rows * ws.n
+    ws.check("gemm_ag", M, k, tuple(b.shape), b_mn, out.dtype, act)
     a = gather.local.view(M, k)
     g = K.GemmArgs()
     g.a, g.b, g.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
@@ -398,6 +410,7 @@ def gemm_rs(ws: SymmetricWorkspace, a: torch.Tensor, b: torch.Tensor, partial: t
     with ``ws.barrier()`` when the owners may still be reading the previous contents of their slots.  Unless
     ``copy_own``, the block this rank owns stays in ``partial`` only: pass `sum_slots` ``own=partial[rank block]``."""
     M = a.shape[1] if a_mn else a.shape[0]
+    ws.check("gemm_rs", tuple(a.shape), tuple(b.shape), a_mn, b_mn, partial.dtype, copy_own)
     g = K.GemmArgs()
     g.a, g.b, g.out = a.data_ptr(), b.data_ptr(), partial.data_ptr()
     g.lda, g.ldb, g.ldo = a.stride(0), b.stride(0), partial.stride(0)
@@ -433,6 +446,7 @@ def sum_slots(slots: torch.Tensor, n: int, rows: int, cols: int, out: torch.Tens
 def moe_dispatch(ws, x, token_of, expert_of, slot_of, bufs: SymmetricBuffer, local_experts: int, capacity: int,
                  row_scale=None, rows_per_token: int = 1):
     rows = expert_of.numel()
+    ws.check("moe_dispatch", x.shape[1], local_experts, capacity, rows_per_token, x.dtype)
     K._check(K.lib().nx_moe_dispatch(K._p(x), K._p(token_of), K._p(expert_of), K._p(slot_of), C.byref(bufs.table),
                                      C.c_int(rows), C.c_int(x.shape[1]), C.c_int(local_experts),
                                      C.c_int(capacity), C.c_int(ws.rank), C.c_int(ws.n), K._p(row_scale),
@@ -441,6 +455,7 @@ def moe_dispatch(ws, x, token_of, expert_of, slot_of, bufs: SymmetricBuffer, loc
 
 def moe_combine(ws, bufs: SymmetricBuffer, expert, slot, gate, y, local_experts: int, capacity: int):
     tokens, top_k = expert.shape
+    ws.check("moe_combine", top_k, y.shape[1], local_experts, capacity, y.dtype)
     K._check(K.lib().nx_moe_combine(C.byref(bufs.table), K._p(expert), K._p(slot), K._p(gate), K._p(y),
                                     C.c_int(tokens), C.c_int(top_k), C.c_int(y.shape[1]), C.c_int(local_experts),
                                     C.c_int(capacity), K._stream()), "nx_moe_combine")
@@ -473,6 +488,7 @@ class RingAttention:
         """q [B, Tl, H, D], k/v [B, Tl, Hkv, D] (this rank's tokens).  Returns (o BF16, lse FP32 [B, H, Tl])."""
         ws, n, r = self.ws, self.ws.n, self.ws.rank
         B, Tl, H, D = q.shape
+        ws.check("ring_attention_forward", tuple(q.shape), tuple(k.shape), causal, self.layout)
         self.k_sym.local.view(self.shape).copy_(k)
         self.v_sym.local.view(self.shape).copy_(v)
         ws.barrier()                                   # every rank's K/V chunk is published

@@ -414,3 +414,29 @@ def test_tcp_store_set_get_add_wait_barrier():
     for c in clients[1:]:
         c.close()
     server.close()
+
+
+def test_check_call_names_a_mismatched_fused_launch_on_thread_ranks():
+    """The host-side guard that the symmetric-memory ops run before their kernels: ranks that are about to launch the
+    same thing pass, a rank with a different size raises a named error on every rank, and the guard costs nothing when
+    validate mode is off."""
+    from nexus_b200.parallel.process_group import DistError, GroupOptions, run_threads
+
+    def agree(pg):
+        pg.check_call("gemm_ag", 4096, 1024, (2048, 1024), False)
+        pg.check_call("fused_all_reduce", 1 << 20, "bf16", "f32")
+        return "ok"
+    assert run_threads(3, agree, GroupOptions(validate=True)) == ["ok"] * 3
+
+    def differ(pg):
+        try:
+            pg.check_call("fused_all_reduce", 1024 if pg.rank() != 1 else 2048, "bf16")
+        except DistError as e:
+            return "mismatch" if "fused_all_reduce:1024" in str(e) and "fused_all_reduce:2048" in str(e) else str(e)
+        return "passed"
+    assert run_threads(2, differ, GroupOptions(validate=True)) == ["mismatch"] * 2
+
+    def off(pg):
+        pg.check_call("anything", pg.rank())          # validate off: no exchange, no error
+        return pg._seq
+    assert run_threads(2, off, GroupOptions(validate=False)) == [0, 0]
