@@ -55,6 +55,7 @@ uint64_t mix64(uint64_t x) {       // splitmix64 finaliser
 // Bijection on [0, n): four Feistel rounds on 2*half bits, re-applied while the image falls outside [0, n).
 uint64_t permute(uint64_t i, uint64_t n, uint64_t key) {
   if (n <= 1) return 0;
+  if (n > (1ull << 60)) throw std::invalid_argument("permute: domain too large");
   int half = 1;
   while ((1ull << (2 * half)) < n) ++half;
   const uint64_t mask = (1ull << half) - 1;
