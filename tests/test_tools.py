@@ -115,7 +115,8 @@ def test_docs_site_builds(tmp_path):
 
 
 @pytest.mark.parametrize("script,args", [("demo.py", []), ("dl_vision_classifier.py", []),
-                                         ("hybrid_cluster_benchmark.py", []), ("lm_baseline.py", ["--json", "{tmp}/r.json"])])
+                                         ("hybrid_cluster_benchmark.py", []), ("lm_baseline.py", ["--json", "{tmp}/r.json"]),
+                                         ("train_from_shards.py", ["--workdir", "{tmp}/shards"])])
 def test_examples_run_on_cpu(tmp_path, script, args):
     """The example programs exit 0 on a machine without a GPU (each checks its own result)."""
     import os
