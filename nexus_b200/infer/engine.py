@@ -1,8 +1,9 @@
 """GPT-2 inference engine with a paged KV cache.
 
 * KV pool per layer ``[blocks, block_size, heads, head_dim]`` (BF16, INT8 or FP8-E4M3 with one scale
-  per (slot, head)); a host block allocator with reference counts gives copy-on-write ``fork_sequence``
-  and ``truncate``.
+  per (slot, head)); the native host scheduler (`csrc/host/kv_sched.cpp`: block pool with reference counts,
+  per-sequence block and token lists, packing of a step's index rows into the pinned staging buffer) gives
+  copy-on-write ``fork_sequence`` and ``truncate``.
 * One ``forward`` takes a packed batch of chunks (sequence, new tokens).  Chunks of a sequence whose
   cache is empty run the tcgen05 flash-attention kernel; every other row (decode, speculative
   verification, continuation) runs the paged decode kernel with its own causal limit.

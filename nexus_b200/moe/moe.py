@@ -2,6 +2,8 @@
 capacity per group with (choice, token) priority, Drop / Reroute overflow, counting-sort
 permutation, grouped SwiGLU expert GEMMs over capacity-padded buffers, gate-weighted combine,
 load-balancing (aux) and router z losses, BF16 / FP8 expert storage, FP64 token-by-token oracle.
+The capacity assignment walk and the oracle run in the native host module (`csrc/host/moe_route.cpp`,
+`csrc/host/moe_ref.cpp`).
 
 ``MoEFFN(x) = sum_j g_j Expert_{e_j}(x)`` with ``Expert(x) = (silu(x W1) * (x W3)) W2``;
 ``up[e] = [W1 | W3]`` is stored [2F, d] and ``down[e]`` [d, F] (out-major, like every weight here).
