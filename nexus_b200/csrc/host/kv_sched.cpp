@@ -8,6 +8,7 @@
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <stdexcept>
 #include <string>
@@ -117,6 +118,47 @@ class KvScheduler {
                 const std::vector<int>& logits, const std::vector<int>& output, bool device_tokens, int max_tokens) {
     if (seqs.size() != counts.size() || seqs.size() != logits.size() || seqs.size() != output.size())
       throw std::invalid_argument("plan: chunk arrays differ in length");
+    // pass 0: everything that can fail is checked before any state changes, so a refused step leaves the sequences,
+    // the block pool and the previous plan exactly as they were
+    {
+      std::vector<int> grown(seqs_.size(), 0), new_blocks(seqs_.size(), 0);
+      std::vector<std::pair<int32_t, int>> released;               // shared blocks this step stops sharing, with counts
+      size_t have = 0;
+      long total = 0, need_blocks = 0;
+      for (size_t i = 0; i < seqs.size(); ++i) {
+        const int n = counts[i];
+        if (n < 0) throw std::invalid_argument("plan: negative token count");
+        if (n == 0) continue;
+        if (device_tokens && n != 1) throw std::invalid_argument("device_tokens needs one-token chunks");
+        have += static_cast<size_t>(n);
+        if (have > flat.size()) throw std::invalid_argument("plan: fewer tokens than the counts say");
+        const int sid = seqs[i];
+        const Seq& s = at(sid);
+        const size_t si = static_cast<size_t>(sid);
+        const int len = s.length + grown[si];
+        if (len + n > ctx_)
+          throw std::invalid_argument("sequence " + std::to_string(sid) + " would exceed the context length " + std::to_string(ctx_));
+        total += n;
+        if (total > max_tokens)
+          throw std::invalid_argument(std::to_string(total) + " tokens exceed max_tokens " + std::to_string(max_tokens));
+        long need = (len + n + bs_ - 1) / bs_ - static_cast<long>(s.blocks.size()) - new_blocks[si];
+        if (need < 0) need = 0;
+        if (grown[si] == 0 && s.length % bs_ != 0) {
+          const int32_t last = s.blocks[static_cast<size_t>(s.length / bs_)];
+          int refs = refcount_[static_cast<size_t>(last)];
+          auto it = std::find_if(released.begin(), released.end(), [&](const auto& p) { return p.first == last; });
+          if (it != released.end()) refs -= it->second;          // earlier chunks of this step already copied away
+          if (refs > 1) {                                        // copy-on-write of the shared partial block
+            ++need_blocks;
+            if (it != released.end()) ++it->second; else released.emplace_back(last, 1);
+          }
+        }
+        new_blocks[si] += static_cast<int>(need);
+        need_blocks += need;
+        grown[si] += n;
+      }
+      if (need_blocks > static_cast<long>(free_blocks_.size())) throw std::runtime_error("KV cache exhausted");
+    }
     tok_.clear(); pos_.clear(); slot_.clear(); rseq_.clear(); logit_rows_.clear();
     std::vector<int> out_rows, logit_seq, table_changed;
     std::vector<std::pair<int, int>> cows, patches;

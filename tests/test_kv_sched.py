@@ -120,3 +120,45 @@ def test_packing_a_large_decode_step_is_fast():
         best = min(best, time.perf_counter() - t0)
     assert best < 1e-3, best
     assert h[1, 0] == 719 and h[4, 0] == 720
+
+
+def test_a_refused_step_changes_nothing():
+    """Every failure of `plan` (pool exhausted by a later chunk, context overflow, too many tokens, unknown sequence) is
+    found before the first change: lengths, token lists, block lists, reference counts and the free count stay put."""
+    s = _native.KvScheduler(4, 4, 4, 12)
+    a, b = s.add(), s.add()
+    _plan(s, [(a, [1, 2, 3, 4, 5], 1, False), (b, [1, 2], 1, False)])             # a: 2 blocks, b: 1 block, 1 free
+    f = s.fork(b)
+
+    def state():
+        return ([(s.length(i), s.tokens(i), s.blocks(i), s.n_prompt(i)) for i in (a, b, f)], s.free_blocks(),
+                [s.refcount(i) for i in range(4)], _rows(s, 8).tolist())
+    before = state()
+    bad = [
+        ([(a, [9, 9, 9, 9], 1, True), (f, [7], 1, True)], RuntimeError),                      # a new block for a and a CoW copy, one free block
+        ([(a, [9], 1, True), (b, list(range(11)), 1, False)], ValueError),                    # context length on the second chunk
+        ([(a, [9], 1, True), (b, [1, 2], 1, False)], ValueError),                             # max_tokens (see below)
+        ([(a, [9], 1, True), (3, [1], 1, False)], KeyError),                                   # unknown sequence
+        ([(a, [9], 1, True), (a, list(range(7)), 1, True)], ValueError),                       # the same sequence twice: 6 + 7 > 12
+    ]
+    for chunks, err in bad:
+        with pytest.raises(err):
+            _plan(s, chunks, max_tokens=2 if err is ValueError and len(chunks[1][1]) == 2 else 4096)
+        assert state() == before
+    # two sequences sharing a partial block append in one step: only the first copies, the second then owns the block
+    g = _native.KvScheduler(3, 4, 3, 12)
+    x = g.add()
+    _plan(g, [(x, [1, 2], 1, False)])
+    y = g.fork(x)
+    p = _plan(g, [(x, [3], 1, True), (y, [4], 1, True)])
+    assert p["cows"] == [(0, 1)] and g.blocks(x) == [1] and g.blocks(y) == [0] and g.free_blocks() == 1
+    # the same sequence twice in one step is fine when it fits: blocks are counted once
+    p = _plan(s, [(a, [9], 1, True), (a, [8, 7], 1, True)])
+    assert s.length(a) == 8 and s.tokens(a)[-3:] == [9, 8, 7] and s.blocks(a) == [0, 1] and p["tokens"] == 3
+    p = _plan(s, [(f, [5], 1, True)])
+    assert p["cows"] == [(2, 3)] and s.free_blocks() == 0
+    with pytest.raises(RuntimeError):
+        _plan(s, [(b, [1, 2, 3], 1, True)])                                                   # would need a new block
+    assert s.length(b) == 2
+    _plan(s, [(b, [1, 2], 1, True)])                                                          # exactly fills its block
+    assert s.length(b) == 4 and s.refcount(2) == 1
