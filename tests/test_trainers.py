@@ -177,3 +177,22 @@ def test_in_process_data_parallel_step_equals_one_replica_on_the_whole_batch():
     ranks = [[1.0, 3.0], [3.0, 5.0]]
     all_reduce_mean(ranks)
     assert ranks == [[2.0, 4.0], [2.0, 4.0]] and LoopProfile().report().startswith("batches=0")
+
+
+def test_nano_cpu_training_reproduces_the_stored_losses():
+    """Regression anchor: the nano decoder (4 layers, d 128, vocabulary 256, 8 x 128 tokens, AdamW 3e-4) trained for
+    six steps on CPU FP32 from fixed seeds gives the loss and gradient-norm sequence stored beside the tests.  A change
+    of model maths, initialisation, loss, clipping or optimizer order shows up here first.  The tolerance leaves room
+    for a different BLAS summation order on another CPU, nothing more."""
+    import json
+    import os
+    torch.manual_seed(1234)
+    cfg = preset("nano")
+    toks = np.random.default_rng(7).integers(0, 256, size=8 * 128 * 6, dtype=np.int32)
+    tr = (LanguageTrainerBuilder(LanguageModel(cfg)).data(ArrayTokens(toks)).optimizer(AdamW(lr=3e-4)).micro_batch(8)
+          .seq_len(128).global_batch_tokens(8 * 128).precision("f32").execution_policy("cpu").log_every(0).build())
+    tr.train(6)
+    gold = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "nano_cpu_fp32_losses.json")))
+    for got, want in zip(tr.history, zip(gold["loss"], gold["grad_norm"])):
+        assert got.loss == pytest.approx(want[0], rel=2e-5) and got.grad_norm == pytest.approx(want[1], rel=2e-4)
+    assert len(tr.history) == len(gold["loss"]) == 6
