@@ -170,3 +170,26 @@ def test_native_host_dropout_matches_the_philox_stream():
     y.sum().backward()
     assert torch.equal(x.grad != 0, keep) and 0.65 < float(keep.float().mean()) < 0.75
     assert F.dropout_philox(x, 0.3, 1, 0, training=False) is x
+
+
+def test_philox_known_answers():
+    """Philox4x32-10 against the published known-answer vectors of the Random123 library, and the three host forms of
+    the uniform stream (numpy, native serial, native dropout) against each other."""
+    import numpy as np
+    from nexus_b200 import _native
+    from nexus_b200.fused import philox
+    kats = [((0, 0, 0, 0), (0, 0), (0x6627E8D5, 0xE169C58D, 0xBC57AC4C, 0x9B00DBD8)),
+            ((0xFFFFFFFF,) * 4, (0xFFFFFFFF, 0xFFFFFFFF), (0x408F276D, 0x41C83B0E, 0xA20BC7C6, 0x6D5451FD)),
+            ((0x243F6A88, 0x85A308D3, 0x13198A2E, 0x03707344), (0xA4093822, 0x299F31D0),
+             (0xD16CFE09, 0x94FDCCEB, 0x5001E420, 0x24126EA1))]
+    for ctr, key, want in kats:
+        got = philox.philox4x32_10(*[np.array([c], dtype=np.uint32) for c in ctr], key[0], key[1])
+        assert tuple(int(g[0]) for g in got) == want
+    # stream layout: element i = lane i % 4 of counter block offset + i // 4, uniform = top 24 bits / 2^24
+    u = philox.philox_uniform(8, 0, 0)
+    assert u[0] == np.float32((0x6627E8D5 >> 8) / 16777216.0) and u[3] == np.float32((0x9B00DBD8 >> 8) / 16777216.0)
+    seed, off = 0x299F31D0A4093822, 123456789012
+    a, b = philox.philox_uniform(1003, seed, off), _native.philox_uniform(1003, seed, off)
+    assert np.array_equal(a, b)
+    y = _native.cpu_dropout_philox(np.ones(1003, dtype=np.float32), 0.25, seed, off)
+    assert np.array_equal(y != 0, a >= np.float32(0.25))
