@@ -20,6 +20,7 @@ void bind_lowp(py::module_& m);
 void bind_fused_train_cpu(py::module_& m);
 void bind_moe_route(py::module_& m);
 void bind_pipeline_sched(py::module_& m);
+void bind_rl_core(py::module_& m);
 
 PYBIND11_MODULE(_native, m) {
   m.doc() = "nexus_b200 native host runtime";
@@ -39,4 +40,5 @@ PYBIND11_MODULE(_native, m) {
   bind_fused_train_cpu(m);
   bind_moe_route(m);
   bind_pipeline_sched(m);
+  bind_rl_core(m);
 }

@@ -158,69 +158,44 @@ class ReplayBuffer:
 
 
 class PrioritizedReplayBuffer(ReplayBuffer):
-    """Proportional prioritisation with a sum tree; importance weights ``(N p)^-beta / max``."""
+    """Proportional prioritisation with a sum tree (native: `csrc/host/rl_core.cpp`); stratified draws, one per segment
+    of the total priority; importance weights ``(N p)^-beta / max``."""
 
     def __init__(self, capacity: int, obs_dim: int, act_dim: int = 1, alpha: float = 0.6, beta: float = 0.4,
                  eps: float = 1e-3, seed: int = 0):
         super().__init__(capacity, obs_dim, act_dim, seed)
         self.alpha, self.beta, self.eps = alpha, beta, eps
-        self.size = 1
-        while self.size < capacity:
-            self.size *= 2
-        self.tree = np.zeros(2 * self.size, np.float64)
+        self._tree = _native.SumTree(capacity)
+        self.size = self._tree.leaves()
         self.max_p = 1.0
-
-    def _set(self, i: int, p: float) -> None:
-        j = i + self.size
-        self.tree[j] = p
-        j //= 2
-        while j >= 1:
-            self.tree[j] = self.tree[2 * j] + self.tree[2 * j + 1]
-            j //= 2
 
     def add(self, *a) -> int:
         i = super().add(*a)
-        self._set(i, self.max_p ** self.alpha)
+        self._tree.set(i, self.max_p ** self.alpha)
         return i
 
     def sample(self, batch: int):
-        total = self.tree[1]
+        total = self._tree.total()
         seg = total / batch
-        idx = np.empty(batch, np.int64)
-        for b in range(batch):
-            x = self.rng.uniform(seg * b, seg * (b + 1))
-            j = 1
-            while j < self.size:
-                if x <= self.tree[2 * j] or self.tree[2 * j + 1] <= 0:
-                    j = 2 * j
-                else:
-                    x -= self.tree[2 * j]
-                    j = 2 * j + 1
-            idx[b] = min(j - self.size, self.n - 1)
-        p = self.tree[idx + self.size] / total
-        w = (self.n * p) ** (-self.beta)
+        lo = seg * np.arange(batch, dtype=np.float64)
+        draws = self.rng.uniform(lo, lo + seg)
+        idx, pr = self._tree.sample(draws, self.n)
+        w = (self.n * (pr / total)) ** (-self.beta)
         out = self._batch(idx)
         out["weight"] = torch.from_numpy((w / w.max()).astype(np.float32))
         return out
 
     def update_priorities(self, idx, td_errors) -> None:
-        for i, e in zip(np.asarray(idx), np.abs(np.asarray(td_errors, dtype=np.float64)) + self.eps):
-            self.max_p = max(self.max_p, float(e))
-            self._set(int(i), float(e) ** self.alpha)
+        e = np.abs(np.asarray(td_errors, dtype=np.float64)) + self.eps
+        if e.size:
+            self.max_p = max(self.max_p, float(e.max()))
+        self._tree.set_many(np.asarray(idx, dtype=np.int64), e ** self.alpha)
 
 
 def gae(rewards, values, dones, last_value: float, gamma: float = 0.99, lam: float = 0.95):
     """Generalised advantage estimation over one trajectory.  Returns (advantages, returns)."""
-    T = len(rewards)
-    adv = np.zeros(T, np.float32)
-    run = 0.0
-    for t in range(T - 1, -1, -1):
-        nv = last_value if t == T - 1 else values[t + 1]
-        nonterm = 1.0 - float(dones[t])
-        delta = rewards[t] + gamma * nv * nonterm - values[t]
-        run = delta + gamma * lam * nonterm * run
-        adv[t] = run
-    return adv, adv + np.asarray(values, np.float32)
+    return _native.gae(np.asarray(rewards, dtype=np.float64), np.asarray(values, dtype=np.float64),
+                       np.asarray(dones, dtype=bool), float(last_value), gamma, lam)
 
 
 class RolloutBuffer:

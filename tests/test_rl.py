@@ -150,3 +150,33 @@ def test_league_elo_and_multi_agent_trainer(tmp_path):
     for _ in range(20):
         duel.run_episode()
     assert duel.league.size() >= 4
+
+
+def test_native_sum_tree_and_gae():
+    from nexus_b200 import _native
+    t = _native.SumTree(5)
+    assert t.leaves() == 8 and t.total() == 0.0
+    for i, p in enumerate([1.0, 0.0, 2.0, 0.5, 4.0]):
+        t.set(i, p)
+    assert t.total() == 7.5 and [t.find(x) for x in (0.5, 1.0, 1.5, 3.0, 3.2, 3.6, 7.5)] == [0, 0, 2, 2, 3, 4, 4]
+    t.set_many(np.array([0, 4]), np.array([0.0, 1.0]))
+    assert t.total() == 3.5 and t.find(0.1) == 2 and t.get(4) == 1.0
+    idx, pr = t.sample(np.array([0.1, 2.2, 3.4]), 5)
+    assert idx.tolist() == [2, 3, 4] and pr.tolist() == [2.0, 0.5, 1.0]
+    assert t.sample(np.array([3.4]), 3)[0].tolist() == [2]               # capped at the last written slot
+    with pytest.raises(IndexError):
+        t.set(8, 1.0)
+    with pytest.raises(ValueError):
+        t.set(0, -1.0)
+    # stratified sampling follows the priorities
+    big = _native.SumTree(1000)
+    pri = np.random.default_rng(0).random(1000) ** 3
+    big.set_many(np.arange(1000), pri)
+    draws = np.random.default_rng(1).uniform(0, big.total(), 200000)
+    counts = np.bincount(big.sample(draws, 1000)[0], minlength=1000)
+    assert np.abs(counts / counts.sum() - pri / pri.sum()).max() < 2e-3
+    # gae: closed form on a constant-reward episode and the episode boundary
+    adv, ret = _native.gae(np.ones(4), np.zeros(4), np.array([False, True, False, False]), 2.0, 0.5, 1.0)
+    assert np.allclose(ret, [1.5, 1.0, 1 + 0.5 * (1 + 0.5 * 2.0), 1 + 0.5 * 2.0]) and np.allclose(adv, ret)
+    with pytest.raises(ValueError):
+        _native.gae(np.ones(3), np.zeros(4), np.zeros(3, dtype=bool), 0.0)
