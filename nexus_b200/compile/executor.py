@@ -164,11 +164,14 @@ class Executor:
                 f: Node = n.attrs["fwd"]
                 ins, outs = taped[id(f)]
                 have = n.attrs["have"]
-                gouts = [env[v.id] for v in n.inputs[len(f.inputs) + len(f.outputs):]]
+                acc = n.attrs.get("accumulate", {})       # output index -> input position of a running sum (beta = 1)
+                n_g = len(n.inputs) - len(acc)
+                gouts = [env[v.id] for v in n.inputs[len(f.inputs) + len(f.outputs):n_g]]
                 wrt = [ins[i] for i in n.attrs["wrt"]]
                 gs = torch.autograd.grad([outs[i] for i in have], wrt, gouts, allow_unused=True)
-                for o, gval, w in zip(n.outputs, gs, wrt):
-                    env[o.id] = gval if gval is not None else torch.zeros_like(w)
+                for k, (o, gval, w) in enumerate(zip(n.outputs, gs, wrt)):
+                    gval = gval if gval is not None else torch.zeros_like(w)
+                    env[o.id] = env[n.inputs[acc[k]].id] + gval if k in acc else gval
                 continue
             if n.op == "Accumulate" and not want_grads:
                 continue
@@ -194,6 +197,7 @@ class CompileOptions:
     fuse: bool = True
     jit: bool = True
     joint: bool = True
+    epilogues: bool = True       # fold gradient accumulation / DGELU / bias gradients into the backward nodes
     cuda_graph: bool = False
 
 
@@ -212,6 +216,8 @@ class CompiledLm:
         self.pgrads: Dict[str, Value] = {}
         if self.opt.joint:
             g, self.pgrads = P.build_joint(g)
+            if self.opt.epilogues:
+                self.stats["epilogues"] = P.fuse_epilogues(g)
         self.graph = g
         params = dict(model.named_parameters())
         self.exec = Executor(g, {k: params[k] for k in g.params}, cfg, group, jit=self.opt.jit)

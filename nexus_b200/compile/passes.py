@@ -235,6 +235,67 @@ def build_joint(g: Graph) -> Tuple[Graph, Dict[str, Value]]:
     return g, pgrads
 
 
+def fuse_epilogues(g: Graph) -> Dict[str, int]:
+    """Folds what a GEMM epilogue can do into the backward nodes of a joint graph.
+
+    * ``beta1``: ``Accumulate(a, b)`` whose ``b`` is the only use of a ``Vjp`` output disappears; the ``Vjp`` node
+      takes ``a`` as an extra input and adds its result onto it (the weight-gradient GEMM run with beta = 1, the
+      residual-stream gradient added in the input-gradient GEMM's epilogue), so no separate add and no temporary.
+    * ``dgelu`` / ``bgrad``: the ``Vjp`` of a ``LinearBiasGelu`` node is marked as one fused backward (GELU derivative
+      in the input-gradient epilogue, bias gradient as the column sum taken with the weight gradient); the ``Vjp`` of a
+      ``Bias`` that follows a ``Linear`` is marked ``bgrad`` with the linear's ``Vjp`` it rides on.
+    Returns the number of each.  Values and results are unchanged; only nodes and temporaries go away.
+    Parity: ``fuse_epilogues`` (DGELU / BGRAD / beta = 1) of include/nexus/compile/passes.hpp in the reference."""
+    counts = {"beta1": 0, "dgelu": 0, "bgrad": 0}
+    users = g.users()
+    pos = {id(n): i for i, n in enumerate(g.nodes)}
+    drop = set()
+    for n in list(g.nodes):
+        if n.op != "Accumulate" or len(n.inputs) != 2:
+            continue
+        a, b = n.inputs
+        prod = b.producer
+        if prod is None or prod.op != "Vjp" or len(users.get(b, [])) != 1:
+            a, b = b, a                                   # the Vjp result may sit on either side
+            prod = b.producer
+            if prod is None or prod.op != "Vjp" or len(users.get(b, [])) != 1:
+                continue
+        if a.producer is not None and pos[id(a.producer)] > pos[id(prod)]:
+            continue                                      # the running sum must exist before the Vjp runs
+        if b in g.outputs:
+            continue
+        k = prod.outputs.index(b)
+        acc = dict(prod.attrs.get("accumulate", {}))
+        if k in acc:
+            continue
+        acc[k] = len(prod.inputs)                         # position of the running sum among the node's inputs
+        prod.attrs["accumulate"] = acc
+        prod.inputs.append(a)
+        _replace_uses(g, n.outputs[0], b)
+        g.outputs = [b if v is n.outputs[0] else v for v in g.outputs]
+        b.shape, b.name = n.outputs[0].shape, n.outputs[0].name or b.name
+        drop.add(id(n))
+        counts["beta1"] += 1
+    if drop:
+        g.nodes = [n for n in g.nodes if id(n) not in drop]
+    vjp_of = {id(n.attrs["fwd"]): n for n in g.nodes if n.op == "Vjp"}
+    for n in g.nodes:
+        if n.op != "Vjp":
+            continue
+        f = n.attrs["fwd"]
+        if f.op == "LinearBiasGelu":
+            n.attrs["epilogue"] = "dgelu+bgrad"
+            counts["dgelu"] += 1
+            counts["bgrad"] += 1
+        elif f.op == "Bias" and f.inputs and f.inputs[0].producer is not None and f.inputs[0].producer.op == "Linear":
+            lin = vjp_of.get(id(f.inputs[0].producer))
+            if lin is not None:
+                n.attrs["epilogue"] = "bgrad"
+                lin.attrs["epilogue"] = "bgrad"
+                counts["bgrad"] += 1
+    return counts
+
+
 # ---------------------------------------------------------------------------------------- fusion
 def fuse_elementwise(g: Graph) -> Dict[str, int]:
     """Vertical: a chain of element-wise nodes whose intermediate values have a single user becomes one

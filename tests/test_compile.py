@@ -144,3 +144,41 @@ def test_compiled_lm_gpu_jit_and_cuda_graph():
     a, b = torch.randn(1000, device="cuda"), torch.randn(1000, device="cuda")
     (o,) = k(a, b)
     assert torch.allclose(o, torch.nn.functional.silu(a + b), atol=1e-5)
+
+
+@pytest.mark.parametrize("kind", ["gpt2", "llama"])
+def test_fuse_epilogues_folds_accumulation_into_the_backward_nodes(kind):
+    """The joint graph with gradient accumulation folded into the Vjp nodes (beta = 1) and the GELU / bias gradients
+    marked as GEMM epilogues: fewer nodes, no Accumulate left where a Vjp result was its only source, and exactly the
+    losses and gradients of the unfused joint graph."""
+    from nexus_b200.lm.config import preset
+    cfg = preset("nano")
+    cfg.n_layer, cfg.d_model, cfg.n_head, cfg.d_ff, cfg.vocab_size, cfg.max_position = 2, 32, 2, 64, 61, 16
+    if kind == "llama":
+        cfg.norm, cfg.mlp, cfg.pos, cfg.bias, cfg.n_kv_head = "rmsnorm", "swiglu", "rope", False, 1
+    torch.manual_seed(0)
+    m = LanguageModel(cfg)
+    toks = torch.randint(0, cfg.vocab_size, (2, 16))
+    plain = C.compile_lm(m, C.CompileOptions(epilogues=False))
+    fused = C.compile_lm(m, C.CompileOptions())
+    st = fused.stats["epilogues"]
+    n_acc = lambda c: sum(1 for n in c.graph.nodes if n.op == "Accumulate")      # noqa: E731
+    assert st["beta1"] >= 1 and n_acc(fused) == n_acc(plain) - st["beta1"]
+    assert len(fused.graph.nodes) == len(plain.graph.nodes) - st["beta1"]
+    if kind == "gpt2":
+        assert st["dgelu"] == cfg.n_layer and st["bgrad"] >= cfg.n_layer
+        assert any(n.attrs.get("epilogue") == "dgelu+bgrad" for n in fused.graph.nodes if n.op == "Vjp")
+    assert any("accumulate" in n.attrs for n in fused.graph.nodes if n.op == "Vjp")
+    l0, g0 = plain.loss_and_grads(toks)
+    l1, g1 = fused.loss_and_grads(toks)
+    assert float(l0) == float(l1) and set(g0) == set(g1)
+    for k in g0:
+        assert torch.allclose(g0[k], g1[k], atol=1e-7, rtol=1e-6), k
+    assert float(fused.loss(toks)) == float(l1)
+    assert "accumulate=" in fused.graph.text() and fused.graph.fingerprint() != plain.graph.fingerprint()
+    # without the rewrite patterns the residual stream leaves many more accumulations: all of them fold away too
+    raw0 = C.compile_lm(m, C.CompileOptions(patterns=0, fuse=False, jit=False, epilogues=False))
+    raw1 = C.compile_lm(m, C.CompileOptions(patterns=0, fuse=False, jit=False))
+    assert raw1.stats["epilogues"]["beta1"] >= 2 * cfg.n_layer and n_acc(raw1) == n_acc(raw0) - raw1.stats["epilogues"]["beta1"]
+    (la, ga), (lb, gb) = raw0.loss_and_grads(toks), raw1.loss_and_grads(toks)
+    assert float(la) == float(lb) and all(torch.allclose(ga[k], gb[k], atol=1e-7, rtol=1e-6) for k in ga)
