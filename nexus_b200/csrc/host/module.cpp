@@ -21,6 +21,7 @@ void bind_fused_train_cpu(py::module_& m);
 void bind_moe_route(py::module_& m);
 void bind_pipeline_sched(py::module_& m);
 void bind_rl_core(py::module_& m);
+void bind_tb_events(py::module_& m);
 
 PYBIND11_MODULE(_native, m) {
   m.doc() = "nexus_b200 native host runtime";
@@ -41,4 +42,5 @@ PYBIND11_MODULE(_native, m) {
   bind_moe_route(m);
   bind_pipeline_sched(m);
   bind_rl_core(m);
+  bind_tb_events(m);
 }

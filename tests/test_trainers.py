@@ -196,3 +196,37 @@ def test_nano_cpu_training_reproduces_the_stored_losses():
     for got, want in zip(tr.history, zip(gold["loss"], gold["grad_norm"])):
         assert got.loss == pytest.approx(want[0], rel=2e-5) and got.grad_norm == pytest.approx(want[1], rel=2e-4)
     assert len(tr.history) == len(gold["loss"]) == 6
+
+
+def test_native_event_file_encoding(tmp_path):
+    """CRC32C known answers, a scalar record checked byte by byte against the TFRecord / protobuf wire format, and the
+    reader refusing damaged files."""
+    import struct
+    from nexus_b200 import _native
+    from nexus_b200.train.loggers import TensorBoardLogger, crc32c, masked_crc32c
+    assert crc32c(b"123456789") == 0xE3069283 and crc32c(b"") == 0 and crc32c(bytes(32)) == 0x8A9136AA
+    c = crc32c(b"abc")
+    assert masked_crc32c(b"abc") == (((c >> 15) | (c << 17)) + 0xA282EAD8) & 0xFFFFFFFF
+    rec = _native.tb_scalar_record(2.5, 300, "loss", 1.5)
+    (n,) = struct.unpack_from("<Q", rec, 0)
+    body = rec[12:12 + n]
+    assert len(rec) == 16 + n and struct.unpack_from("<I", rec, 8)[0] == masked_crc32c(rec[:8])
+    assert struct.unpack_from("<I", rec, 12 + n)[0] == masked_crc32c(body)
+    value = b"\x0a\x04loss" + b"\x15" + struct.pack("<f", 1.5)                  # Value{1: tag, 2: simple_value}
+    summary = b"\x0a" + bytes([len(value)]) + value                              # Summary{1: Value}
+    want = b"\x09" + struct.pack("<d", 2.5) + b"\x10\xac\x02" + b"\x2a" + bytes([len(summary)]) + summary
+    assert body == want                                                          # Event{1: wall_time, 2: step, 5: summary}
+    lg = TensorBoardLogger(str(tmp_path))
+    for i in range(3):
+        lg.scalar("a/b", i * 0.5, i)
+    lg.flush()
+    assert read_tensorboard_scalars(lg.path) == [(0, "a/b", 0.0), (1, "a/b", 0.5), (2, "a/b", 1.0)]
+    raw = bytearray(open(lg.path, "rb").read())
+    raw[-6] ^= 1
+    bad = tmp_path / "bad.tfevents"
+    bad.write_bytes(bytes(raw))
+    with pytest.raises(ValueError, match="checksum"):
+        read_tensorboard_scalars(str(bad))
+    bad.write_bytes(bytes(raw[:-3]))
+    with pytest.raises(ValueError, match="truncated"):
+        read_tensorboard_scalars(str(bad))
