@@ -116,7 +116,9 @@ def test_docs_site_builds(tmp_path):
 
 @pytest.mark.parametrize("script,args", [("demo.py", []), ("dl_vision_classifier.py", []),
                                          ("hybrid_cluster_benchmark.py", []), ("lm_baseline.py", ["--json", "{tmp}/r.json"]),
-                                         ("train_from_shards.py", ["--workdir", "{tmp}/shards"])])
+                                         ("train_from_shards.py", ["--workdir", "{tmp}/shards"]),
+                                         ("serve_demo.py", ["--small", "--requests", "6", "--max-new", "6", "--prompt-len", "12"]),
+                                         ("custom_ops_showcase.py", [])])
 def test_examples_run_on_cpu(tmp_path, script, args):
     """The example programs exit 0 on a machine without a GPU (each checks its own result)."""
     import os
